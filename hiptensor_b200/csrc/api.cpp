@@ -1,0 +1,709 @@
+// The hipTensor-compatible C++ entry points (include/hiptensor/hiptensor.hpp) for the three
+// hot paths. Validation order, status codes and scalar decoding follow the reference
+// (library/src/hiptensor.cpp, library/src/contraction/hiptensor_contraction.cpp,
+// library/src/permutation/hiptensor_permutation.cpp, library/src/reduction/hiptensor_reduction.cpp);
+// kernel selection is the closed-form planner in planner.cpp and the kernels are this
+// library's own. Unlike the reference nothing here exits the process or blocks the host:
+// CUDA failures come back as HIPTENSOR_STATUS_HIP_ERROR.
+#include <memory>
+#include <mutex>
+#include <set>
+#include <vector>
+
+#include <cuda_runtime_api.h>
+
+#include <hiptensor/hiptensor.hpp>
+
+#include "kernels.hpp"
+
+using namespace htb;
+
+namespace
+{
+    HandleState* mutableState(hiptensorHandle_t* h)
+    {
+        return reinterpret_cast<HandleState*>(h->fields);
+    }
+
+    // ARCH_MISMATCH unless the current device is the one the handle was made on
+    // (hiptensor_contraction.cpp:263-277).
+    hiptensorStatus_t checkDevice(const char* func, const HandleState* st)
+    {
+        int dev = -1;
+        if(cudaGetDevice(&dev) != cudaSuccess)
+            return HIPTENSOR_STATUS_HIP_ERROR;
+        if(dev != st->device)
+        {
+            HTB_LOG_ERROR(func, "Device mismatch error: current device id: %d, handle device id: %d (%s)", dev,
+                          st->device, hiptensorGetErrorString(HIPTENSOR_STATUS_ARCH_MISMATCH));
+            return HIPTENSOR_STATUS_ARCH_MISMATCH;
+        }
+        return HIPTENSOR_STATUS_SUCCESS;
+    }
+
+    std::vector<int64_t> toI64(const std::vector<std::size_t>& v)
+    {
+        return std::vector<int64_t>(v.begin(), v.end());
+    }
+
+    // Plans are owned by the library and shared between identical problems, like the
+    // singleton-owned solutions the reference's plan points to
+    // (hiptensor_contraction.cpp:600-601).
+    struct PlanRegistry
+    {
+        std::mutex                                    mutex;
+        std::vector<std::unique_ptr<ContractionPlan>> plans;
+        const ContractionPlan*                        intern(const ContractionPlan& p)
+        {
+            std::lock_guard<std::mutex> lock(mutex);
+            for(auto& q : plans)
+                if(std::memcmp(q.get(), &p, sizeof(p)) == 0)
+                    return q.get();
+            plans.emplace_back(new ContractionPlan(p));
+            return plans.back().get();
+        }
+        bool owns(const void* ptr)
+        {
+            std::lock_guard<std::mutex> lock(mutex);
+            for(auto& q : plans)
+                if(q.get() == ptr)
+                    return true;
+            return false;
+        }
+    };
+    PlanRegistry& registry()
+    {
+        static PlanRegistry r;
+        return r;
+    }
+
+    int buildContractionPlan(const hiptensorContractionDescriptor_t* desc, int smCount, ContractionPlan* out)
+    {
+        if(desc->mTensorDesc.size() != 4 || desc->mTensorMode.size() < 3)
+            return HIPTENSOR_STATUS_INVALID_VALUE;
+        const bool bilinear = (desc->mContractionOpId == 1);
+        if(desc->mContractionOpId != 0 && desc->mContractionOpId != 1)
+            return HIPTENSOR_STATUS_NOT_SUPPORTED; // complex forms are outside this library
+        auto lA = toI64(desc->mTensorDesc[0].mLengths), sA = toI64(desc->mTensorDesc[0].mStrides);
+        auto lB = toI64(desc->mTensorDesc[1].mLengths), sB = toI64(desc->mTensorDesc[1].mStrides);
+        // D is described by descriptor 3 and the mode list stored at index 2
+        // (hiptensor_contraction.cpp:772-775: modeD is never read)
+        auto lD = toI64(desc->mTensorDesc[3].mLengths), sD = toI64(desc->mTensorDesc[3].mStrides);
+        const auto& mA = desc->mTensorMode[0];
+        const auto& mB = desc->mTensorMode[1];
+        const auto& mD = desc->mTensorMode[2];
+        if(mA.size() != lA.size() || mB.size() != lB.size() || mD.size() != lD.size() || sA.size() != lA.size()
+           || sB.size() != lB.size() || sD.size() != lD.size())
+            return HIPTENSOR_STATUS_INVALID_VALUE;
+        TensorView A{int(lA.size()), lA.data(), sA.data(), mA.data(), int(desc->mTensorDesc[0].mType)};
+        TensorView B{int(lB.size()), lB.data(), sB.data(), mB.data(), int(desc->mTensorDesc[1].mType)};
+        TensorView D{int(lD.size()), lD.data(), sD.data(), mD.data(), int(desc->mTensorDesc[3].mType)};
+        return planContraction(A, B, D, int(desc->mTensorDesc[2].mType), bilinear, int(desc->mComputeType), smCount,
+                               out);
+    }
+} // namespace
+
+// ---------------------------------------------------------------------------- core
+hiptensorStatus_t hiptensorCreate(hiptensorHandle_t** handle)
+{
+    HTB_LOG_API("hiptensorCreate", "handle=%p", (void*)handle);
+    if(handle == nullptr)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    *handle = nullptr;
+    int dev = -1;
+    if(cudaGetDevice(&dev) != cudaSuccess)
+    {
+        cudaGetLastError();
+        HTB_LOG_ERROR("hiptensorCreate", "Initialization error: no CUDA device (%s)",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_HIP_ERROR));
+        return HIPTENSOR_STATUS_HIP_ERROR;
+    }
+    int major = 0, minor = 0, sms = 0, smem = 0;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if(major != 10)
+    {
+        // the kernels are built for sm_100a only (the reference exits the process on an
+        // unsupported GPU, library/src/hip_device.cpp:130-148; this returns a status)
+        HTB_LOG_ERROR("hiptensorCreate", "Unsupported device: compute capability %d.%d, need 10.x (%s)", major,
+                      minor, hiptensorGetErrorString(HIPTENSOR_STATUS_ARCH_MISMATCH));
+        return HIPTENSOR_STATUS_ARCH_MISMATCH;
+    }
+    auto* h = new(std::nothrow) hiptensorHandle_t;
+    if(h == nullptr)
+        return HIPTENSOR_STATUS_ALLOC_FAILED;
+    std::memset(h->fields, 0, sizeof(h->fields));
+    HandleState* st  = mutableState(h);
+    st->device       = dev;
+    st->smCount      = sms;
+    st->ccMajor      = major;
+    st->ccMinor      = minor;
+    st->maxSmemOptin = smem;
+    if(cudaMalloc((void**)&st->deviceStatus, 256) != cudaSuccess || cudaMemset(st->deviceStatus, 0, 256) != cudaSuccess)
+    {
+        cudaGetLastError();
+        delete h;
+        return HIPTENSOR_STATUS_ALLOC_FAILED;
+    }
+    st->magic = kHandleMagic;
+    *handle   = h;
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+hiptensorStatus_t hiptensorDestroy(hiptensorHandle_t* handle)
+{
+    HTB_LOG_API("hiptensorDestroy", "handle=%p", (void*)handle);
+    if(handle == nullptr)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    HandleState* st = mutableState(handle);
+    if(st->magic == kHandleMagic)
+    {
+        if(st->deviceStatus)
+            cudaFree(st->deviceStatus);
+        st->magic = 0;
+    }
+    delete handle;
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+const char* hiptensorGetErrorString(const hiptensorStatus_t error)
+{
+    switch(error)
+    {
+    case HIPTENSOR_STATUS_SUCCESS: return "HIPTENSOR_STATUS_SUCCESS";
+    case HIPTENSOR_STATUS_NOT_INITIALIZED: return "HIPTENSOR_STATUS_NOT_INITIALIZED";
+    case HIPTENSOR_STATUS_ALLOC_FAILED: return "HIPTENSOR_STATUS_ALLOC_FAILED";
+    case HIPTENSOR_STATUS_INVALID_VALUE: return "HIPTENSOR_STATUS_INVALID_VALUE";
+    case HIPTENSOR_STATUS_ARCH_MISMATCH: return "HIPTENSOR_STATUS_ARCH_MISMATCH";
+    case HIPTENSOR_STATUS_EXECUTION_FAILED: return "HIPTENSOR_STATUS_EXECUTION_FAILED";
+    case HIPTENSOR_STATUS_INTERNAL_ERROR: return "HIPTENSOR_STATUS_INTERNAL_ERROR";
+    case HIPTENSOR_STATUS_NOT_SUPPORTED: return "HIPTENSOR_STATUS_NOT_SUPPORTED";
+    case HIPTENSOR_STATUS_CK_ERROR: return "HIPTENSOR_STATUS_CK_ERROR";
+    case HIPTENSOR_STATUS_HIP_ERROR: return "HIPTENSOR_STATUS_HIP_ERROR";
+    case HIPTENSOR_STATUS_INSUFFICIENT_WORKSPACE: return "HIPTENSOR_STATUS_INSUFFICIENT_WORKSPACE";
+    case HIPTENSOR_STATUS_INSUFFICIENT_DRIVER: return "HIPTENSOR_STATUS_INSUFFICIENT_DRIVER";
+    case HIPTENSOR_STATUS_IO_ERROR: return "HIPTENSOR_STATUS_IO_ERROR";
+    }
+    return "HIPTENSOR_STATUS_UNKNOWN";
+}
+
+hiptensorStatus_t hiptensorInitTensorDescriptor(const hiptensorHandle_t* handle, hiptensorTensorDescriptor_t* desc,
+                                                const uint32_t numModes, const int64_t lens[],
+                                                const int64_t strides[], hipDataType dataType,
+                                                hiptensorOperator_t unaryOp)
+{
+    HTB_LOG_API("hiptensorInitTensorDescriptor", "handle=%p, desc=%p, numModes=%u, lens=%p, strides=%p, dataType=%d, unaryOp=%d",
+                (const void*)handle, (void*)desc, numModes, (const void*)lens, (const void*)strides, int(dataType),
+                int(unaryOp));
+    if(handle == nullptr || desc == nullptr)
+    {
+        HTB_LOG_ERROR("hiptensorInitTensorDescriptor", "Initialization Error : %s = nullptr (%s)",
+                      handle ? "descriptor" : "handle", hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_INITIALIZED));
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    }
+    const bool typeOk = dataType == HIP_R_16F || dataType == HIP_R_16BF || dataType == HIP_R_32F
+                        || dataType == HIP_R_64F || dataType == HIP_C_32F || dataType == HIP_C_64F;
+    const bool opOk = unaryOp == HIPTENSOR_OP_IDENTITY || unaryOp == HIPTENSOR_OP_SQRT;
+    if((lens == nullptr && strides != nullptr) || !typeOk || !opOk || (lens == nullptr && numModes > 0))
+    {
+        HTB_LOG_ERROR("hiptensorInitTensorDescriptor", "Tensor Initialization Error : bad lens/strides, data type or operator (%s)",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_INVALID_VALUE));
+        return HIPTENSOR_STATUS_INVALID_VALUE;
+    }
+    desc->mType    = dataType;
+    desc->mUnaryOp = unaryOp;
+    desc->mLengths.assign(lens, lens + numModes);
+    if(strides)
+    {
+        desc->mStrides.assign(strides, strides + numModes);
+    }
+    else
+    {
+        // packed with the LAST mode fastest (library/src/hiptensor.cpp:205,
+        // library/src/include/util.hpp:45-69 with col_major = false)
+        desc->mStrides.assign(numModes, 1);
+        for(int i = int(numModes) - 2; i >= 0; i--)
+            desc->mStrides[i] = desc->mStrides[i + 1] * desc->mLengths[i + 1];
+    }
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+hiptensorStatus_t hiptensorGetAlignmentRequirement(const hiptensorHandle_t* handle, const void* ptr,
+                                                   const hiptensorTensorDescriptor_t* desc,
+                                                   uint32_t*                          alignmentRequirement)
+{
+    if(!handle || !desc)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    if(!alignmentRequirement)
+        return HIPTENSOR_STATUS_INVALID_VALUE;
+    // largest power of two in [element size, 16] that divides the pointer
+    *alignmentRequirement = 0u;
+    for(uint32_t i = uint32_t(dtypeSize(desc->mType)); i > 0 && i <= 16u; i *= 2)
+        if(std::size_t(ptr) % std::size_t(i) == 0)
+            *alignmentRequirement = i;
+    if(*alignmentRequirement == 0)
+    {
+        HTB_LOG_ERROR("hiptensorGetAlignmentRequirement", "Error : alignment requirement is 0 (%s)",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_INVALID_VALUE));
+        return HIPTENSOR_STATUS_INVALID_VALUE;
+    }
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------- permutation
+hiptensorStatus_t hiptensorPermutation(const hiptensorHandle_t* handle, const void* alpha, const void* A,
+                                       const hiptensorTensorDescriptor_t* descA, const int32_t modeA[], void* B,
+                                       const hiptensorTensorDescriptor_t* descB, const int32_t modeB[],
+                                       const hipDataType typeScalar, const hipStream_t stream)
+{
+    const char* fn = "hiptensorPermutation";
+    HTB_LOG_API(fn, "handle=%p, alpha=%p, A=%p, descA=%p, modeA=%p, B=%p, descB=%p, modeB=%p, typeScalar=%d, stream=%p",
+                (const void*)handle, alpha, A, (const void*)descA, (const void*)modeA, B, (const void*)descB,
+                (const void*)modeB, int(typeScalar), (void*)stream);
+    if(!handle || !alpha || !A || !descA || !modeA || !B || !descB || !modeB)
+    {
+        HTB_LOG_ERROR(fn, "Initialization Error : a required argument is nullptr (%s)",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_INITIALIZED));
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    }
+    const HandleState* st = stateOf(handle);
+    if(!st)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    if(descA->mType != HIP_R_16F && descA->mType != HIP_R_32F)
+    {
+        HTB_LOG_ERROR(fn, "Unsupported Data Type Error : The supported data types of A are f16 and f32 (%s)",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_SUPPORTED));
+        return HIPTENSOR_STATUS_NOT_SUPPORTED;
+    }
+    if(typeScalar != HIP_R_16F && typeScalar != HIP_R_32F)
+    {
+        HTB_LOG_ERROR(fn, "Unsupported Data Type Error : The supported scalar types are f16 and f32 (%s)",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_SUPPORTED));
+        return HIPTENSOR_STATUS_NOT_SUPPORTED;
+    }
+    if(descA->mLengths.size() != descB->mLengths.size())
+        return HIPTENSOR_STATUS_INVALID_VALUE;
+    if(auto s = checkDevice(fn, st); s != HIPTENSOR_STATUS_SUCCESS)
+        return s;
+
+    const int rank = int(descA->mLengths.size());
+    auto      lA   = toI64(descA->mLengths);
+    // B's extents must be A's extents under the mode mapping
+    for(int i = 0; i < rank; i++)
+    {
+        int ia = -1;
+        for(int j = 0; j < rank; j++)
+            if(modeA[j] == modeB[i])
+                ia = j;
+        if(ia < 0 || descB->mLengths[i] != descA->mLengths[ia])
+        {
+            HTB_LOG_ERROR(fn, "Invalid Value Error : extents of B do not match the permuted extents of A (%s)",
+                          hiptensorGetErrorString(HIPTENSOR_STATUS_INVALID_VALUE));
+            return HIPTENSOR_STATUS_INVALID_VALUE;
+        }
+    }
+    PermPlan   plan;
+    const bool aligned = ((uintptr_t(A) | uintptr_t(B)) & 15) == 0;
+    int        rc = planPermutation(rank, lA.data(), modeA, modeB, int(descA->mType), int(descB->mType), aligned, &plan);
+    if(rc != PLAN_OK)
+    {
+        HTB_LOG_ERROR(fn, "The permutation cannot be planned (%s)", hiptensorGetErrorString(hiptensorStatus_t(rc)));
+        return hiptensorStatus_t(rc);
+    }
+    // alpha is read as typeScalar and widened to float (permutation_solution_impl.hpp:104-108)
+    float alphaF = (typeScalar == HIP_R_32F) ? *(const float*)alpha : __half2float(*(const __half*)alpha);
+    HTB_LOG_HEUR(fn, "%s", describe(plan).c_str());
+    cudaError_t e = launchPermutation(plan, int(descA->mType), int(descB->mType), A, B, alphaF, int(descA->mUnaryOp),
+                                      int(descB->mUnaryOp), st->deviceStatus, stream);
+    if(e != cudaSuccess)
+    {
+        HTB_LOG_ERROR(fn, "kernel launch failed: %s (%s)", cudaGetErrorString(e),
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_HIP_ERROR));
+        return HIPTENSOR_STATUS_HIP_ERROR;
+    }
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------- reduction
+namespace
+{
+    hiptensorStatus_t checkReduction(const char* fn, const hiptensorHandle_t* handle, const void* alpha, const void* A,
+                                     const hiptensorTensorDescriptor_t* descA, const int32_t* modeA, const void* beta,
+                                     const hiptensorTensorDescriptor_t* descC, const int32_t* modeC, const void* D,
+                                     const hiptensorTensorDescriptor_t* descD, hiptensorComputeType_t typeCompute)
+    {
+        if(!handle || !alpha || !A || !descA || !modeA || !beta || !descC || !D || !descD)
+        {
+            HTB_LOG_ERROR(fn, "Initialization Error : a required argument is nullptr (%s)",
+                          hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_INITIALIZED));
+            return HIPTENSOR_STATUS_NOT_INITIALIZED;
+        }
+        // the six legal (A, C, D, compute) tuples (hiptensor_reduction.cpp:132-139)
+        const auto tA = descA->mType, tC = descC->mType, tD = descD->mType;
+        bool       ok = (tA == tC && tA == tD)
+                  && ((tA == HIP_R_16F && (typeCompute == HIPTENSOR_COMPUTE_16F || typeCompute == HIPTENSOR_COMPUTE_32F))
+                      || (tA == HIP_R_16BF
+                          && (typeCompute == HIPTENSOR_COMPUTE_16BF || typeCompute == HIPTENSOR_COMPUTE_32F))
+                      || (tA == HIP_R_32F && typeCompute == HIPTENSOR_COMPUTE_32F)
+                      || (tA == HIP_R_64F && typeCompute == HIPTENSOR_COMPUTE_64F));
+        if(!ok)
+        {
+            HTB_LOG_ERROR(fn,
+                          "Unsupported Data Type Error : The combination of data types of A, C and D and compute type "
+                          "is not supported. (%s)",
+                          hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_SUPPORTED));
+            return HIPTENSOR_STATUS_NOT_SUPPORTED;
+        }
+        const std::size_t rankC = descC->mLengths.size();
+        bool same = descC->mType == descD->mType && descC->mLengths == descD->mLengths
+                    && descC->mStrides == descD->mStrides && descC->mUnaryOp == descD->mUnaryOp;
+        bool subset = (rankC == 0) || (modeC != nullptr);
+        if(subset)
+        {
+            std::set<int32_t> setA(modeA, modeA + descA->mLengths.size());
+            for(std::size_t i = 0; i < rankC; i++)
+                if(!setA.count(modeC[i]))
+                    subset = false;
+        }
+        if(descA->mLengths.size() < rankC || !same || !subset)
+        {
+            HTB_LOG_ERROR(fn,
+                          "Unsupported Data Error : The descriptor of C and D should be same and modes of C should be "
+                          "subset of modes A. (%s)",
+                          hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_SUPPORTED));
+            return HIPTENSOR_STATUS_NOT_SUPPORTED;
+        }
+        return HIPTENSOR_STATUS_SUCCESS;
+    }
+
+    int planFor(const HandleState* st, const void* A, const hiptensorTensorDescriptor_t* descA, const int32_t* modeA,
+                const void* C, const void* D, const hiptensorTensorDescriptor_t* descD, const int32_t* modeD,
+                ReducePlan* plan)
+    {
+        auto       lA = toI64(descA->mLengths), sA = toI64(descA->mStrides);
+        auto       lD = toI64(descD->mLengths), sD = toI64(descD->mStrides);
+        const bool aligned = ((uintptr_t(A) | uintptr_t(C) | uintptr_t(D)) & 15) == 0;
+        return planReduction(int(lA.size()), lA.data(), sA.data(), modeA, int(lD.size()), lD.data(), sD.data(), modeD,
+                             dtypeSize(descA->mType), aligned, st ? st->smCount : 148, plan);
+    }
+} // namespace
+
+hiptensorStatus_t hiptensorReduction(const hiptensorHandle_t* handle, const void* alpha, const void* A,
+                                     const hiptensorTensorDescriptor_t* descA, const int32_t modeA[],
+                                     const void* beta, const void* C, const hiptensorTensorDescriptor_t* descC,
+                                     const int32_t modeC[], void* D, const hiptensorTensorDescriptor_t* descD,
+                                     const int32_t modeD[], hiptensorOperator_t opReduce,
+                                     hiptensorComputeType_t typeCompute, void* workspace, uint64_t workspaceSize,
+                                     hipStream_t stream)
+{
+    const char* fn = "hiptensorReduction";
+    HTB_LOG_API(fn, "handle=%p, alpha=%p, A=%p, descA=%p, beta=%p, C=%p, descC=%p, D=%p, descD=%p, opReduce=%d, typeCompute=%d, workspace=%p, workspaceSize=%llu, stream=%p",
+                (const void*)handle, alpha, A, (const void*)descA, beta, C, (const void*)descC, D, (const void*)descD,
+                int(opReduce), int(typeCompute), workspace, (unsigned long long)workspaceSize, (void*)stream);
+    if(auto s = checkReduction(fn, handle, alpha, A, descA, modeA, beta, descC, modeC, D, descD, typeCompute);
+       s != HIPTENSOR_STATUS_SUCCESS)
+        return s;
+    const HandleState* st = stateOf(handle);
+    if(!st)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    if(opReduce != HIPTENSOR_OP_ADD && opReduce != HIPTENSOR_OP_MUL && opReduce != HIPTENSOR_OP_MIN
+       && opReduce != HIPTENSOR_OP_MAX)
+    {
+        HTB_LOG_ERROR(fn, "Internal Error : no kernel for this reduction operator (%s)",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_INTERNAL_ERROR));
+        return HIPTENSOR_STATUS_INTERNAL_ERROR; // the reference finds no instance (hiptensor_reduction.cpp:276-285)
+    }
+    if(auto s = checkDevice(fn, st); s != HIPTENSOR_STATUS_SUCCESS)
+        return s;
+    ReducePlan plan;
+    // the reference hands D's descriptor with modeD to its kernels (hiptensor_reduction.cpp:325-336);
+    // modeD == modeC by contract, and a null modeD falls back to modeC
+    const int32_t* modesOut = modeD ? modeD : modeC;
+    int            rc       = planFor(st, A, descA, modeA, C, D, descD, modesOut, &plan);
+    if(rc != PLAN_OK)
+    {
+        HTB_LOG_ERROR(fn, "No kernel is able to solve the problem (%s)", hiptensorGetErrorString(hiptensorStatus_t(rc)));
+        return hiptensorStatus_t(rc);
+    }
+    // alpha/beta: read as the given compute type, widened to double (hiptensor_reduction.cpp:287-296)
+    double alphaD = 0, betaD = 0;
+    if(!readScalar(alpha, int(typeCompute), &alphaD) || !readScalar(beta, int(typeCompute), &betaD))
+        return HIPTENSOR_STATUS_NOT_SUPPORTED;
+    // f16/bf16 compute is promoted to f32 (hiptensor_reduction.cpp:259-264)
+    const int internalCompute = (typeCompute == HIPTENSOR_COMPUTE_64F) ? HIPTENSOR_COMPUTE_64F : HIPTENSOR_COMPUTE_32F;
+    // the two-pass form needs scratch; without enough of it the single-pass kernels run
+    const uint64_t need = reductionWorkspaceBytes(plan, internalCompute);
+    void*          ws   = (need > 0 && workspace != nullptr && workspaceSize >= need) ? workspace : nullptr;
+    if(ws == nullptr)
+        plan.split = 1;
+    HTB_LOG_HEUR(fn, "%s", describe(plan).c_str());
+    // The reference copies C over D and then accumulates in place (hiptensor_reduction.cpp:298-307);
+    // reading C at D's offsets inside the kernel gives the same result without the extra pass.
+    cudaError_t e = launchReduction(plan, int(descA->mType), internalCompute, int(opReduce), alphaD, A, betaD,
+                                    C ? C : D, D, ws, stream);
+    if(e != cudaSuccess)
+    {
+        HTB_LOG_ERROR(fn, "kernel launch failed: %s (%s)", cudaGetErrorString(e),
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_HIP_ERROR));
+        return HIPTENSOR_STATUS_HIP_ERROR;
+    }
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+hiptensorStatus_t hiptensorReductionGetWorkspaceSize(
+    const hiptensorHandle_t* handle, const void* A, const hiptensorTensorDescriptor_t* descA, const int32_t modeA[],
+    const void* C, const hiptensorTensorDescriptor_t* descC, const int32_t modeC[], const void* D,
+    const hiptensorTensorDescriptor_t* descD, const int32_t modeD[], hiptensorOperator_t opReduce,
+    hiptensorComputeType_t typeCompute, uint64_t* workspaceSize)
+{
+    (void)opReduce;
+    (void)descC;
+    if(!handle)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    if(!workspaceSize || !descA || !descD || !modeA)
+        return HIPTENSOR_STATUS_INVALID_VALUE;
+    *workspaceSize = 0; // the reference always reports 0 (hiptensor_reduction.cpp:383-399)
+    ReducePlan plan;
+    if(planFor(stateOf(handle), A, descA, modeA, C, D, descD, modeD ? modeD : modeC, &plan) == PLAN_OK)
+    {
+        const int internalCompute
+            = (typeCompute == HIPTENSOR_COMPUTE_64F) ? HIPTENSOR_COMPUTE_64F : HIPTENSOR_COMPUTE_32F;
+        *workspaceSize = reductionWorkspaceBytes(plan, internalCompute);
+    }
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------- contraction
+hiptensorStatus_t hiptensorInitContractionDescriptor(
+    const hiptensorHandle_t* handle, hiptensorContractionDescriptor_t* desc,
+    const hiptensorTensorDescriptor_t* descA, const int32_t modeA[], const uint32_t alignmentRequirementA,
+    const hiptensorTensorDescriptor_t* descB, const int32_t modeB[], const uint32_t alignmentRequirementB,
+    const hiptensorTensorDescriptor_t* descC, const int32_t modeC[], const uint32_t alignmentRequirementC,
+    const hiptensorTensorDescriptor_t* descD, const int32_t modeD[], const uint32_t alignmentRequirementD,
+    hiptensorComputeType_t typeCompute)
+{
+    const char* fn = "hiptensorInitContractionDescriptor";
+    HTB_LOG_API(fn, "handle=%p, desc=%p, descA=%p, descB=%p, descC=%p, descD=%p, typeCompute=%d", (const void*)handle,
+                (void*)desc, (const void*)descA, (const void*)descB, (const void*)descC, (const void*)descD,
+                int(typeCompute));
+    if(!handle || !desc || !descA || !descB || !descD)
+    {
+        HTB_LOG_ERROR(fn, "Initialization Error : %s = nullptr (%s)",
+                      !handle ? "handle" : (!desc ? "contraction descriptor" : "Tensor descriptors"),
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_INITIALIZED));
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    }
+    if(!modeA || !modeB || !modeD)
+        return HIPTENSOR_STATUS_INVALID_VALUE;
+    if(descA->mUnaryOp != HIPTENSOR_OP_IDENTITY || descB->mUnaryOp != HIPTENSOR_OP_IDENTITY
+       || descD->mUnaryOp != HIPTENSOR_OP_IDENTITY || (descC && descC->mUnaryOp != HIPTENSOR_OP_IDENTITY))
+    {
+        HTB_LOG_ERROR(fn, "Unsupported Operator Type Error : The supported Operator is HIPTENSOR_OP_IDENTITY (%s)",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_SUPPORTED));
+        return HIPTENSOR_STATUS_NOT_SUPPORTED;
+    }
+    const bool complexCompute = typeCompute == HIPTENSOR_COMPUTE_C32F || typeCompute == HIPTENSOR_COMPUTE_C64F;
+    std::vector<int32_t> mA(modeA, modeA + descA->mLengths.size());
+    std::vector<int32_t> mB(modeB, modeB + descB->mLengths.size());
+    std::vector<int32_t> mD(modeD, modeD + descD->mLengths.size());
+    desc->mComputeType = typeCompute;
+    if(descC == nullptr || modeC == nullptr)
+    {
+        // scale form: the C slot holds a typeless placeholder, mode list 2 is D's
+        desc->mContractionOpId = complexCompute ? 2 : 0;
+        hiptensorTensorDescriptor_t none{hipDataType(31), std::vector<std::size_t>(descD->mLengths.size(), 0),
+                                         std::vector<std::size_t>(descD->mStrides.size(), 0), HIPTENSOR_OP_IDENTITY};
+        desc->mTensorDesc   = {*descA, *descB, none, *descD};
+        desc->mAlignmentReq = {alignmentRequirementA, alignmentRequirementB, 0, alignmentRequirementD};
+        desc->mTensorMode   = {mA, mB, mD};
+    }
+    else
+    {
+        desc->mContractionOpId = complexCompute ? 3 : 1;
+        std::vector<int32_t> mC(modeC, modeC + descC->mLengths.size());
+        desc->mTensorDesc   = {*descA, *descB, *descC, *descD};
+        desc->mAlignmentReq = {alignmentRequirementA, alignmentRequirementB, alignmentRequirementC,
+                               alignmentRequirementD};
+        desc->mTensorMode   = {mA, mB, mC, mD};
+    }
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+hiptensorStatus_t hiptensorInitContractionFind(const hiptensorHandle_t* handle, hiptensorContractionFind_t* find,
+                                               const hiptensorAlgo_t algo)
+{
+    const char* fn = "hiptensorInitContractionFind";
+    HTB_LOG_API(fn, "handle=%p, find=%p, algo=%d", (const void*)handle, (void*)find, int(algo));
+    if(!handle || !find)
+    {
+        HTB_LOG_ERROR(fn, "Initialization Error : %s = nullptr (%s)", handle ? "contraction find" : "handle",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_INITIALIZED));
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    }
+    const HandleState* st = stateOf(handle);
+    if(!st)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    if(auto s = checkDevice(fn, st); s != HIPTENSOR_STATUS_SUCCESS)
+        return s;
+    if(algo != HIPTENSOR_ALGO_DEFAULT && algo != HIPTENSOR_ALGO_DEFAULT_PATIENT && algo != HIPTENSOR_ALGO_ACTOR_CRITIC)
+        return HIPTENSOR_STATUS_INVALID_VALUE;
+    // Every algorithm id selects the same closed-form planner: there is no instance list
+    // to enumerate, so the candidate vector stays empty.
+    find->mSelectionAlgorithm = algo;
+    find->mCandidates.clear();
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+hiptensorStatus_t hiptensorContractionGetWorkspaceSize(const hiptensorHandle_t*                handle,
+                                                       const hiptensorContractionDescriptor_t* desc,
+                                                       const hiptensorContractionFind_t*       find,
+                                                       const hiptensorWorksizePreference_t     pref,
+                                                       uint64_t*                               workspaceSize)
+{
+    (void)pref;
+    if(!handle || !desc || !find || !workspaceSize)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    *workspaceSize = 0;
+    ContractionPlan    plan;
+    const HandleState* st = stateOf(handle);
+    if(buildContractionPlan(desc, st ? st->smCount : 148, &plan) == HIPTENSOR_STATUS_SUCCESS)
+        *workspaceSize = plan.workspaceBytes;
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+hiptensorStatus_t hiptensorInitContractionPlan(const hiptensorHandle_t* handle, hiptensorContractionPlan_t* plan,
+                                               const hiptensorContractionDescriptor_t* desc,
+                                               const hiptensorContractionFind_t* find, const uint64_t workspaceSize)
+{
+    const char* fn = "hiptensorInitContractionPlan";
+    HTB_LOG_API(fn, "handle=%p, plan=%p, desc=%p, find=%p, workspaceSize=%llu", (const void*)handle, (void*)plan,
+                (const void*)desc, (const void*)find, (unsigned long long)workspaceSize);
+    if(!handle || !plan || !desc || !find)
+    {
+        HTB_LOG_ERROR(fn, "Initialization Error : %s = nullptr (%s)",
+                      !handle ? "handle" : (!plan ? "plan" : (!desc ? "contraction descriptor" : "contraction find")),
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_INITIALIZED));
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    }
+    const HandleState* st = stateOf(handle);
+    if(!st)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    if(auto s = checkDevice(fn, st); s != HIPTENSOR_STATUS_SUCCESS)
+        return s;
+    ContractionPlan cp;
+    int             rc = buildContractionPlan(desc, st->smCount, &cp);
+    if(rc != HIPTENSOR_STATUS_SUCCESS)
+    {
+        // the reference ends with EXECUTION_FAILED when no candidate survives its type
+        // query (contraction_selection.cpp:185-190); the cause is reported more precisely here
+        HTB_LOG_ERROR(fn, "No kernel can run this contraction (%s)", hiptensorGetErrorString(hiptensorStatus_t(rc)));
+        return hiptensorStatus_t(rc);
+    }
+    HTB_LOG_HEUR(fn, "%s", describe(cp).c_str());
+    plan->mSolution        = const_cast<ContractionPlan*>(registry().intern(cp));
+    plan->mContractionDesc = *desc;
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+hiptensorStatus_t hiptensorContraction(const hiptensorHandle_t* handle, const hiptensorContractionPlan_t* plan,
+                                       const void* alpha, const void* A, const void* B, const void* beta,
+                                       const void* C, void* D, void* workspace, uint64_t workspaceSize,
+                                       hipStream_t stream)
+{
+    const char* fn = "hiptensorContraction";
+    HTB_LOG_API(fn, "handle=%p, plan=%p, alpha=%p, A=%p, B=%p, beta=%p, C=%p, D=%p, workspace=%p, workspaceSize=%llu, stream=%p",
+                (const void*)handle, (const void*)plan, alpha, A, B, beta, C, D, workspace,
+                (unsigned long long)workspaceSize, (void*)stream);
+    if(!handle || !plan)
+    {
+        HTB_LOG_ERROR(fn, "Initialization Error : %s = nullptr (%s)", handle ? "plan" : "handle",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_NOT_INITIALIZED));
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    }
+    if(!alpha || !A || !B || !D)
+    {
+        HTB_LOG_ERROR(fn, "Input Parameter Error : %s = nullptr (%s)", alpha ? "A/B/D" : "alpha",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_INVALID_VALUE));
+        return HIPTENSOR_STATUS_INVALID_VALUE;
+    }
+    if(plan->mSolution == nullptr || !registry().owns(plan->mSolution))
+    {
+        HTB_LOG_ERROR(fn, "Internal Error : solution = nullptr (%s)",
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_INTERNAL_ERROR));
+        return HIPTENSOR_STATUS_INTERNAL_ERROR;
+    }
+    const HandleState* st = stateOf(handle);
+    if(!st)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    if(auto s = checkDevice(fn, st); s != HIPTENSOR_STATUS_SUCCESS)
+        return s;
+    const ContractionPlan* cp = static_cast<const ContractionPlan*>(plan->mSolution);
+    if(cp->workspaceBytes > workspaceSize || (cp->workspaceBytes > 0 && workspace == nullptr))
+    {
+        HTB_LOG_ERROR(fn, "Insufficient workspace: req: %llu alloc: %llu (%s)", (unsigned long long)cp->workspaceBytes,
+                      (unsigned long long)workspaceSize,
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_INSUFFICIENT_WORKSPACE));
+        return HIPTENSOR_STATUS_INSUFFICIENT_WORKSPACE;
+    }
+    // alpha/beta are typed by the compute type and held as float by the epilogue
+    // (contraction_solution_impl.hpp:110-123)
+    double alphaD = 0, betaD = 0;
+    if(!readScalar(alpha, cp->computeType, &alphaD))
+        return HIPTENSOR_STATUS_NOT_SUPPORTED;
+    const bool bilinear = cp->bilinear != 0;
+    if(bilinear)
+    {
+        if(!beta || !C)
+        {
+            HTB_LOG_ERROR(fn, "Input Parameter Error : beta/C = nullptr for a bilinear contraction (%s)",
+                          hiptensorGetErrorString(HIPTENSOR_STATUS_INVALID_VALUE));
+            return HIPTENSOR_STATUS_INVALID_VALUE;
+        }
+        readScalar(beta, cp->computeType, &betaD);
+    }
+    cudaError_t e = launchContraction(*cp, float(alphaD), A, B, float(betaD), bilinear ? C : nullptr, D, workspace,
+                                      st->smCount, st->deviceStatus, stream);
+    if(e != cudaSuccess)
+    {
+        HTB_LOG_ERROR(fn, "kernel launch failed: %s (%s)", cudaGetErrorString(e),
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_HIP_ERROR));
+        return HIPTENSOR_STATUS_HIP_ERROR;
+    }
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------- logger, version
+hiptensorStatus_t hiptensorLoggerSetCallback(hiptensorLoggerCallback_t callback)
+{
+    return hiptensorStatus_t(Logger::instance().setCallback(callback));
+}
+hiptensorStatus_t hiptensorLoggerSetFile(FILE* file)
+{
+    return hiptensorStatus_t(Logger::instance().setFile(file));
+}
+hiptensorStatus_t hiptensorLoggerOpenFile(const char* logFile)
+{
+    return hiptensorStatus_t(Logger::instance().openFile(logFile));
+}
+hiptensorStatus_t hiptensorLoggerSetLevel(hiptensorLogLevel_t level)
+{
+    return hiptensorStatus_t(Logger::instance().setLevel(int32_t(level)));
+}
+hiptensorStatus_t hiptensorLoggerSetMask(int32_t mask)
+{
+    return hiptensorStatus_t(Logger::instance().setMask(mask));
+}
+hiptensorStatus_t hiptensorLoggerForceDisable()
+{
+    Logger::instance().disable();
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+int hiptensorGetHiprtVersion()
+{
+    int v = -1;
+    if(cudaRuntimeGetVersion(&v) != cudaSuccess)
+        return -1;
+    return v;
+}

@@ -1,0 +1,414 @@
+// Gathered tiled contraction kernel for sm_100a:  D = alpha * (A x B) + beta * C  on the
+// folded (M, N, K) view of arbitrary mode lists.
+//
+// One CTA owns a 64x64 tile of the folded output. Row/column offsets of the tile (M and N
+// multi-indices decomposed over the folded modes) are computed once into shared memory; K
+// offsets are computed per 16-wide K step. Operand tiles are gathered from the strided
+// tensors straight into shared memory (converted through the compute type), double
+// buffered with a register prefetch, and consumed either by
+//   - an FMA micro-kernel with a strided 4x4 register tile per thread (fp32 accumulate), or
+//   - the FP64 tensor pipe (mma.sync m8n8k4 f64) with 32x16 warp tiles.
+// The epilogue rounds the accumulator to the output type first and then applies
+// alpha*x + beta*c, which is the order of the reference's CPU implementation
+// (library/src/contraction/contraction_cpu_reference_impl.hpp:406-425).
+//
+// It stands where the reference enumerates CK DeviceContractionMultipleD_Xdl_CShuffle
+// instances (library/src/contraction/device/*_instance.cpp) and covers every mode layout,
+// including those a TMA box cannot describe.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "kernels.hpp"
+
+namespace htb
+{
+    cudaError_t launchContractionTcgen05(const ContractionPlan& plan, float alpha, const void* A, const void* B,
+                                         float beta, const void* C, void* D, int smCount, int* deviceStatus,
+                                         cudaStream_t stream);
+
+    namespace
+    {
+        constexpr int BM = 64, BN = 64, BK = 16, PAD = 4, THREADS = 256;
+
+        struct CtrArgs
+        {
+            int     nm, nn, nk;
+            ModeDim m[kMaxGroup], n[kMaxGroup], k[kMaxGroup];
+            int64_t M, N, K;
+            float   alpha, beta;
+            int     bilinear;
+            int     aKfast, bKfast;
+            int     tilesN;
+        };
+
+        template <typename T>
+        __device__ __forceinline__ float toFloat(T v);
+        template <>
+        __device__ __forceinline__ float toFloat<float>(float v)
+        {
+            return v;
+        }
+        template <>
+        __device__ __forceinline__ float toFloat<double>(double v)
+        {
+            return float(v);
+        }
+        template <>
+        __device__ __forceinline__ float toFloat<__half>(__half v)
+        {
+            return __half2float(v);
+        }
+        template <>
+        __device__ __forceinline__ float toFloat<__nv_bfloat16>(__nv_bfloat16 v)
+        {
+            return __bfloat162float(v);
+        }
+
+        // element -> accumulate type through the compute type (ROUND: 0 none, 1 f16, 2 bf16)
+        template <typename TAcc, typename T, int ROUND>
+        __device__ __forceinline__ TAcc loadConv(const T* p, int64_t off)
+        {
+            if constexpr(sizeof(TAcc) == 8)
+            {
+                return TAcc(p[off]);
+            }
+            else
+            {
+                float v = toFloat<T>(p[off]);
+                if(ROUND == 1)
+                    v = __half2float(__float2half_rn(v));
+                if(ROUND == 2)
+                    v = __bfloat162float(__float2bfloat16_rn(v));
+                return v;
+            }
+        }
+
+        template <typename TD, typename TAcc>
+        __device__ __forceinline__ void storeEpilogue(TD* D, const TD* C, int64_t off, TAcc acc, float alpha, float beta,
+                                                      int bilinear)
+        {
+            if constexpr(sizeof(TD) == 8)
+            {
+                double x = double(acc);
+                double y = __dmul_rn(double(alpha), x);
+                if(bilinear)
+                    y = __dadd_rn(y, __dmul_rn(double(beta), C[off]));
+                D[off] = y;
+            }
+            else if constexpr(sizeof(TD) == 4)
+            {
+                float x = float(acc);
+                float y = __fmul_rn(alpha, x);
+                if(bilinear)
+                    y = __fadd_rn(y, __fmul_rn(beta, C[off]));
+                D[off] = y;
+            }
+            else
+            {
+                TD    xr = TD(float(acc)); // round to the output type first
+                float y  = __fmul_rn(alpha, toFloat<TD>(xr));
+                if(bilinear)
+                    y = __fadd_rn(y, __fmul_rn(beta, toFloat<TD>(C[off])));
+                D[off] = TD(y);
+            }
+        }
+
+        __device__ __forceinline__ void decompose2(const ModeDim* dims, int nd, int64_t idx, int64_t& o0, int64_t& o1)
+        {
+            o0 = 0;
+            o1 = 0;
+            for(int d = 0; d < nd; d++)
+            {
+                int64_t c = idx % dims[d].ext;
+                idx /= dims[d].ext;
+                o0 += c * dims[d].s0;
+                o1 += c * dims[d].s1;
+            }
+        }
+
+        template <typename TA, typename TD, typename TAcc, int ROUND, bool DMMA>
+        __global__ void __launch_bounds__(THREADS)
+            contraction_tiled_kernel(const TA* __restrict__ A, const TA* __restrict__ B, const TD* C, TD* D, CtrArgs a)
+        {
+            __shared__ TAcc    sA[2][BK][BM + PAD];
+            __shared__ TAcc    sB[2][BK][BN + PAD];
+            __shared__ int64_t offAm[BM], offDm[BM], offBn[BN], offDn[BN];
+            __shared__ int64_t offAk[2][BK], offBk[2][BK];
+
+            const int     tid   = threadIdx.x;
+            const int64_t tileM = blockIdx.x / a.tilesN, tileN = blockIdx.x % a.tilesN;
+            const int64_t m0 = tileM * BM, n0 = tileN * BN;
+
+            if(tid < BM)
+            {
+                const int64_t mm = m0 + tid;
+                int64_t       oa = -1, od = -1;
+                if(mm < a.M)
+                    decompose2(a.m, a.nm, mm, oa, od);
+                offAm[tid] = oa;
+                offDm[tid] = od;
+            }
+            else if(tid < BM + BN)
+            {
+                const int     t  = tid - BM;
+                const int64_t nn = n0 + t;
+                int64_t       ob = -1, od = -1;
+                if(nn < a.N)
+                    decompose2(a.n, a.nn, nn, ob, od);
+                offBn[t] = ob;
+                offDn[t] = od;
+            }
+            auto computeK = [&](int buf, int64_t k0) {
+                if(tid >= BM + BN && tid < BM + BN + BK)
+                {
+                    const int     t  = tid - BM - BN;
+                    const int64_t kk = k0 + t;
+                    int64_t       oa = -1, ob = -1;
+                    if(kk < a.K)
+                        decompose2(a.k, a.nk, kk, oa, ob);
+                    offAk[buf][t] = oa;
+                    offBk[buf][t] = ob;
+                }
+            };
+            computeK(0, 0);
+            __syncthreads();
+
+            TAcc ra[4], rb[4];
+            auto gload = [&](int buf) {
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+                {
+                    int mi, ki;
+                    if(a.aKfast)
+                    {
+                        ki = tid & 15;
+                        mi = (tid >> 4) + 16 * j;
+                    }
+                    else
+                    {
+                        mi = tid & 63;
+                        ki = (tid >> 6) + 4 * j;
+                    }
+                    const int64_t om = offAm[mi], ok = offAk[buf][ki];
+                    ra[j] = (om >= 0 && ok >= 0) ? loadConv<TAcc, TA, ROUND>(A, om + ok) : TAcc(0);
+                    int ni, kj;
+                    if(a.bKfast)
+                    {
+                        kj = tid & 15;
+                        ni = (tid >> 4) + 16 * j;
+                    }
+                    else
+                    {
+                        ni = tid & 63;
+                        kj = (tid >> 6) + 4 * j;
+                    }
+                    const int64_t on = offBn[ni], ok2 = offBk[buf][kj];
+                    rb[j] = (on >= 0 && ok2 >= 0) ? loadConv<TAcc, TA, ROUND>(B, on + ok2) : TAcc(0);
+                }
+            };
+            auto sstore = [&](int buf) {
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+                {
+                    if(a.aKfast)
+                        sA[buf][tid & 15][(tid >> 4) + 16 * j] = ra[j];
+                    else
+                        sA[buf][(tid >> 6) + 4 * j][tid & 63] = ra[j];
+                    if(a.bKfast)
+                        sB[buf][tid & 15][(tid >> 4) + 16 * j] = rb[j];
+                    else
+                        sB[buf][(tid >> 6) + 4 * j][tid & 63] = rb[j];
+                }
+            };
+
+            const int64_t nkt = (a.K + BK - 1) / BK;
+            gload(0);
+            sstore(0);
+            computeK(1, BK);
+            __syncthreads();
+
+            // accumulators
+            TAcc      acc[4][4]; // SIMT: [i][j];  DMMA: [i][2*j + e] (i: 4 m-frags, j: 2 n-frags)
+#pragma unroll
+            for(int i = 0; i < 4; i++)
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+                    acc[i][j] = TAcc(0);
+
+            const int tx = tid & 15, ty = tid >> 4; // SIMT mapping
+            const int lane = tid & 31, warp = tid >> 5;
+            const int wm = warp & 1, wn = warp >> 1; // DMMA mapping
+
+            for(int64_t kt = 0; kt < nkt; kt++)
+            {
+                const int  cur     = int(kt & 1);
+                const bool hasNext = (kt + 1 < nkt);
+                if(hasNext)
+                    gload(cur ^ 1);
+                if constexpr(DMMA)
+                {
+#pragma unroll
+                    for(int k4 = 0; k4 < BK / 4; k4++)
+                    {
+                        double af[4], bf[2];
+                        const int kr = k4 * 4 + (lane & 3);
+#pragma unroll
+                        for(int i = 0; i < 4; i++)
+                            af[i] = sA[cur][kr][wm * 32 + i * 8 + (lane >> 2)];
+#pragma unroll
+                        for(int j = 0; j < 2; j++)
+                            bf[j] = sB[cur][kr][wn * 16 + j * 8 + (lane >> 2)];
+#pragma unroll
+                        for(int i = 0; i < 4; i++)
+#pragma unroll
+                            for(int j = 0; j < 2; j++)
+                            {
+                                asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, "
+                                             "{%0,%1};"
+                                             : "+d"(acc[i][2 * j]), "+d"(acc[i][2 * j + 1])
+                                             : "d"(af[i]), "d"(bf[j]));
+                            }
+                    }
+                }
+                else
+                {
+#pragma unroll
+                    for(int kk = 0; kk < BK; kk++)
+                    {
+                        TAcc av[4], bv[4];
+#pragma unroll
+                        for(int i = 0; i < 4; i++)
+                            av[i] = sA[cur][kk][ty + 16 * i];
+#pragma unroll
+                        for(int j = 0; j < 4; j++)
+                            bv[j] = sB[cur][kk][tx + 16 * j];
+#pragma unroll
+                        for(int i = 0; i < 4; i++)
+#pragma unroll
+                            for(int j = 0; j < 4; j++)
+                                acc[i][j] += av[i] * bv[j];
+                    }
+                }
+                if(hasNext)
+                {
+                    sstore(cur ^ 1);
+                    computeK(cur, (kt + 2) * BK);
+                }
+                __syncthreads();
+            }
+
+            // epilogue
+            if constexpr(DMMA)
+            {
+#pragma unroll
+                for(int i = 0; i < 4; i++)
+                {
+                    const int     mi = wm * 32 + i * 8 + (lane >> 2);
+                    const int64_t om = offDm[mi];
+                    if(om < 0)
+                        continue;
+#pragma unroll
+                    for(int j = 0; j < 2; j++)
+#pragma unroll
+                        for(int e = 0; e < 2; e++)
+                        {
+                            const int     ni = wn * 16 + j * 8 + 2 * (lane & 3) + e;
+                            const int64_t on = offDn[ni];
+                            if(on >= 0)
+                                storeEpilogue<TD, TAcc>(D, C, om + on, acc[i][2 * j + e], a.alpha, a.beta, a.bilinear);
+                        }
+                }
+            }
+            else
+            {
+#pragma unroll
+                for(int i = 0; i < 4; i++)
+                {
+                    const int64_t om = offDm[ty + 16 * i];
+                    if(om < 0)
+                        continue;
+#pragma unroll
+                    for(int j = 0; j < 4; j++)
+                    {
+                        const int64_t on = offDn[tx + 16 * j];
+                        if(on >= 0)
+                            storeEpilogue<TD, TAcc>(D, C, om + on, acc[i][j], a.alpha, a.beta, a.bilinear);
+                    }
+                }
+            }
+        }
+
+        template <typename TA, typename TD, typename TAcc, int ROUND, bool DMMA>
+        cudaError_t launchTiled(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
+                                const void* C, void* D, cudaStream_t stream)
+        {
+            CtrArgs a{};
+            a.nm = p.nm;
+            a.nn = p.nn;
+            a.nk = p.nk;
+            for(int i = 0; i < kMaxGroup; i++)
+            {
+                a.m[i] = p.m[i];
+                a.n[i] = p.n[i];
+                a.k[i] = p.k[i];
+            }
+            a.M        = p.M;
+            a.N        = p.N;
+            a.K        = p.K;
+            a.alpha    = alpha;
+            a.beta     = beta;
+            a.bilinear = (p.bilinear && C != nullptr) ? 1 : 0;
+            a.aKfast   = (p.k[0].s0 == 1 && p.k[0].ext > 1) ? 1 : 0;
+            a.bKfast   = (p.k[0].s1 == 1 && p.k[0].ext > 1) ? 1 : 0;
+            const int64_t tilesM = (p.M + BM - 1) / BM, tilesN = (p.N + BN - 1) / BN;
+            if(tilesM * tilesN > 0x7fffffffll)
+                return cudaErrorInvalidConfiguration;
+            a.tilesN = int(tilesN);
+            contraction_tiled_kernel<TA, TD, TAcc, ROUND, DMMA>
+                <<<unsigned(tilesM * tilesN), THREADS, 0, stream>>>((const TA*)A, (const TA*)B, (const TD*)C, (TD*)D, a);
+            noteLaunch(DMMA ? "contraction_tiled_dmma" : "contraction_tiled_simt");
+            return cudaGetLastError();
+        }
+    } // namespace
+
+    cudaError_t launchContraction(const ContractionPlan& plan, float alpha, const void* A0, const void* B0,
+                                  float beta, const void* C, void* D, void* workspace, int smCount,
+                                  int* deviceStatus, cudaStream_t stream)
+    {
+        (void)workspace;
+        if(plan.M == 0 || plan.N == 0)
+            return cudaSuccess;
+        const void* A = plan.swapped ? B0 : A0;
+        const void* B = plan.swapped ? A0 : B0;
+        if(plan.kind == CK_TCGEN05)
+        {
+            const bool aligned = ((uintptr_t(A) | uintptr_t(B)) & 15) == 0;
+            if(aligned)
+                return launchContractionTcgen05(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
+        }
+        const int ct = plan.computeType;
+        switch(plan.typeA)
+        {
+        case CUDA_R_32F:
+            if(ct == HIPTENSOR_COMPUTE_16F)
+                return launchTiled<float, float, float, 1, false>(plan, alpha, A, B, beta, C, D, stream);
+            if(ct == HIPTENSOR_COMPUTE_16BF)
+                return launchTiled<float, float, float, 2, false>(plan, alpha, A, B, beta, C, D, stream);
+            return launchTiled<float, float, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
+        case CUDA_R_64F:
+            if(ct == HIPTENSOR_COMPUTE_64F)
+                return launchTiled<double, double, double, 0, true>(plan, alpha, A, B, beta, C, D, stream);
+            return launchTiled<double, double, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
+        case CUDA_R_16F:
+            if(plan.typeD == CUDA_R_32F)
+                return launchTiled<__half, float, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
+            return launchTiled<__half, __half, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
+        case CUDA_R_16BF:
+            if(plan.typeD == CUDA_R_32F)
+                return launchTiled<__nv_bfloat16, float, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
+            return launchTiled<__nv_bfloat16, __nv_bfloat16, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
+        }
+        return cudaErrorInvalidValue;
+    }
+} // namespace htb

@@ -1,0 +1,34 @@
+// Launch entry points of the CUDA kernels (one translation unit per operation).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+
+#include "common.hpp"
+#include "planner.hpp"
+
+namespace htb
+{
+    // cuTensorMapEncodeTiled, resolved through the runtime so that the library does not
+    // link against libcuda (it must load on machines without a driver).
+    typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                        const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                        CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                        CUtensorMapFloatOOBfill);
+    PFN_encodeTiled tensorMapEncoder();
+
+    cudaError_t launchPermutation(const PermPlan& plan, int typeA, int typeB, const void* A, void* B, float alpha,
+                                  int opA, int opB, int* deviceStatus, cudaStream_t stream);
+
+    // alpha/beta already widened to double; C may alias D or be null (beta then ignored).
+    // workspace is used only when plan.split > 1.
+    cudaError_t launchReduction(const ReducePlan& plan, int typeA, int computeType, int op, double alpha,
+                                const void* A, double beta, const void* C, void* D, void* workspace,
+                                cudaStream_t stream);
+    uint64_t    reductionWorkspaceBytes(const ReducePlan& plan, int computeType);
+
+    // A/B are the caller's operands in the caller's order; the plan says whether to swap.
+    cudaError_t launchContraction(const ContractionPlan& plan, float alpha, const void* A, const void* B,
+                                  float beta, const void* C, void* D, void* workspace, int smCount,
+                                  int* deviceStatus, cudaStream_t stream);
+} // namespace htb

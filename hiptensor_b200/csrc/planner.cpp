@@ -1,0 +1,521 @@
+// Host-side planner (see planner.hpp). No CUDA calls in this file.
+#include "planner.hpp"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+
+#include <library_types.h>
+
+namespace htb
+{
+    namespace
+    {
+        int findMode(const int32_t* modes, int n, int32_t m)
+        {
+            for(int i = 0; i < n; i++)
+                if(modes[i] == m)
+                    return i;
+            return -1;
+        }
+
+        bool hasDuplicates(const int32_t* modes, int n)
+        {
+            for(int i = 0; i < n; i++)
+                for(int j = i + 1; j < n; j++)
+                    if(modes[i] == modes[j])
+                        return true;
+            return false;
+        }
+
+        int elemSizeOf(int dt)
+        {
+            switch(dt)
+            {
+            case CUDA_R_32F: return 4;
+            case CUDA_R_64F: return 8;
+            case CUDA_R_16F: return 2;
+            case CUDA_R_16BF: return 2;
+            default: return 0;
+            }
+        }
+
+        const char* typeName(int dt)
+        {
+            switch(dt)
+            {
+            case CUDA_R_32F: return "f32";
+            case CUDA_R_64F: return "f64";
+            case CUDA_R_16F: return "f16";
+            case CUDA_R_16BF: return "bf16";
+            default: return "none";
+            }
+        }
+
+        void appendDims(std::string& s, const char* name, const ModeDim* d, int n)
+        {
+            char buf[96];
+            s += name;
+            s += "[";
+            for(int i = 0; i < n; i++)
+            {
+                snprintf(buf, sizeof(buf), "%s%lld:%lld/%lld", i ? " " : "", (long long)d[i].ext,
+                         (long long)d[i].s0, (long long)d[i].s1);
+                s += buf;
+            }
+            s += "]";
+        }
+
+        bool isPow2(int64_t v)
+        {
+            return v > 0 && (v & (v - 1)) == 0;
+        }
+    } // namespace
+
+    int foldGroup(ModeDim* dims, int n)
+    {
+        int w = 0;
+        for(int i = 0; i < n; i++)
+        {
+            if(dims[i].ext == 1)
+                continue;
+            if(w > 0 && dims[i].s0 == dims[w - 1].s0 * dims[w - 1].ext
+               && dims[i].s1 == dims[w - 1].s1 * dims[w - 1].ext)
+            {
+                dims[w - 1].ext *= dims[i].ext;
+            }
+            else
+            {
+                dims[w++] = dims[i];
+            }
+        }
+        if(w == 0)
+        {
+            dims[0] = ModeDim{1, 0, 0};
+            w       = 1;
+        }
+        return w;
+    }
+
+    // ------------------------------------------------------------------ permutation
+    int planPermutation(int rank, const int64_t* lensA, const int32_t* modeA, const int32_t* modeB,
+                        int typeA, int typeB, bool pointersAligned16, PermPlan* out)
+    {
+        std::memset(out, 0, sizeof(*out));
+        if(rank < 1 || rank > kMaxGroup || !lensA || !modeA || !modeB)
+            return PLAN_INVALID;
+        // reference type rules: f16->f16, f16->f32, f32->f32
+        // (docs/api-reference/api-reference.rst:77-81, hiptensor_permutation.cpp:123-144)
+        const bool typesOk = (typeA == CUDA_R_32F && typeB == CUDA_R_32F)
+                             || (typeA == CUDA_R_16F && (typeB == CUDA_R_16F || typeB == CUDA_R_32F));
+        if(!typesOk)
+            return PLAN_NOT_SUPPORTED;
+        if(hasDuplicates(modeA, rank) || hasDuplicates(modeB, rank))
+            return PLAN_INVALID;
+        for(int i = 0; i < rank; i++)
+        {
+            if(lensA[i] <= 0)
+                return PLAN_INVALID;
+            if(findMode(modeA, rank, modeB[i]) < 0)
+                return PLAN_INVALID;
+        }
+
+        ModeDim dims[kMaxGroup];
+        int64_t s = 1;
+        for(int i = 0; i < rank; i++)
+        {
+            dims[i].ext = lensA[i];
+            dims[i].s0  = s;
+            s *= lensA[i];
+        }
+        out->total = s;
+        s          = 1;
+        for(int i = 0; i < rank; i++)
+        {
+            int ia      = findMode(modeA, rank, modeB[i]);
+            dims[ia].s1 = s;
+            s *= lensA[ia];
+        }
+        int n     = foldGroup(dims, rank);
+        out->ndim = n;
+        out->q    = 0;
+        for(int i = 0; i < n; i++)
+        {
+            out->ext[i] = dims[i].ext;
+            out->sA[i]  = dims[i].s0;
+            out->sB[i]  = dims[i].s1;
+            if(dims[i].s1 == 1 && dims[i].ext > 1)
+                out->q = i;
+        }
+        if(n == 1 && dims[0].ext == 1)
+        {
+            out->sA[0] = out->sB[0] = 1;
+        }
+        for(int i = 0; i < n; i++)
+            out->orderB[i] = i;
+        std::sort(out->orderB, out->orderB + n, [&](int a, int b) { return out->sB[a] < out->sB[b]; });
+        out->elemSize = elemSizeOf(typeA);
+
+        if(out->q == 0)
+        {
+            out->kind = PERM_COPY;
+        }
+        else
+        {
+            bool tma = (typeA == CUDA_R_32F && typeB == CUDA_R_32F) && pointersAligned16 && n <= 5
+                       && out->ext[0] % 4 == 0 && out->ext[out->q] % 4 == 0 && out->ext[0] >= 16
+                       && out->ext[out->q] >= 16;
+            for(int i = 0; i < n && tma; i++)
+            {
+                // cuTensorMapEncodeTiled limits: extent < 2^32, byte stride < 2^40
+                if(out->ext[i] >= (int64_t(1) << 32) || out->sA[i] * 4 >= (int64_t(1) << 40)
+                   || out->sB[i] * 4 >= (int64_t(1) << 40))
+                    tma = false;
+            }
+            out->kind = tma ? PERM_TMA : PERM_TILE;
+        }
+        return PLAN_OK;
+    }
+
+    std::string describe(const PermPlan& p)
+    {
+        static const char* kinds[] = {"copy", "tile", "tma"};
+        std::string        s       = "permutation kind=";
+        s += kinds[p.kind];
+        char buf[128];
+        snprintf(buf, sizeof(buf), " ndim=%d q=%d total=%lld dims=", p.ndim, p.q, (long long)p.total);
+        s += buf;
+        for(int i = 0; i < p.ndim; i++)
+        {
+            snprintf(buf, sizeof(buf), "%s%lld:%lld/%lld", i ? " " : "", (long long)p.ext[i], (long long)p.sA[i],
+                     (long long)p.sB[i]);
+            s += buf;
+        }
+        return s;
+    }
+
+    // ------------------------------------------------------------------ reduction
+    int planReduction(int rankA, const int64_t* lensA, const int64_t* stridesA, const int32_t* modeA, int rankD,
+                      const int64_t* lensD, const int64_t* stridesD, const int32_t* modeD, int elemSize,
+                      bool pointersAligned16, int smCount, ReducePlan* out)
+    {
+        std::memset(out, 0, sizeof(*out));
+        if(rankA < 1 || rankA > kMaxGroup || rankD < 0 || rankD > rankA || !lensA || !stridesA || !modeA)
+            return PLAN_INVALID;
+        if(rankD > 0 && (!lensD || !stridesD || !modeD))
+            return PLAN_INVALID;
+        if(hasDuplicates(modeA, rankA) || hasDuplicates(modeD, rankD))
+            return PLAN_INVALID;
+        for(int j = 0; j < rankD; j++)
+            if(findMode(modeA, rankA, modeD[j]) < 0)
+                return PLAN_NOT_SUPPORTED; // modes of D must be a subset of A's
+
+        ModeDim keep[kMaxGroup], red[kMaxGroup];
+        int     nk = 0, nr = 0;
+        for(int i = 0; i < rankA; i++)
+        {
+            if(lensA[i] <= 0)
+                return PLAN_INVALID;
+            if(findMode(modeD, rankD, modeA[i]) >= 0)
+            {
+                // positional contract of the reference: D's j-th extent/stride belongs to
+                // the j-th kept mode of A (reduction_solution_impl.hpp:105-143)
+                if(lensD[nk] != lensA[i])
+                    return PLAN_INVALID;
+                keep[nk] = ModeDim{lensA[i], stridesA[i], stridesD[nk]};
+                nk++;
+            }
+            else
+            {
+                red[nr++] = ModeDim{lensA[i], stridesA[i], 0};
+            }
+        }
+        auto byS0 = [](const ModeDim& a, const ModeDim& b) { return a.s0 < b.s0; };
+        std::stable_sort(keep, keep + nk, byS0);
+        std::stable_sort(red, red + nr, byS0);
+        nk = foldGroup(keep, nk);
+        nr = foldGroup(red, nr);
+        out->nk   = nk;
+        out->nr   = nr;
+        out->nOut = 1;
+        out->nRed = 1;
+        for(int i = 0; i < nk; i++)
+        {
+            out->kext[i] = keep[i].ext;
+            out->ksA[i]  = keep[i].s0;
+            out->ksD[i]  = keep[i].s1;
+            out->nOut *= keep[i].ext;
+        }
+        for(int i = 0; i < nr; i++)
+        {
+            out->rext[i] = red[i].ext;
+            out->rsA[i]  = red[i].s0;
+            out->nRed *= red[i].ext;
+        }
+        const bool redContig  = (out->rext[0] > 1 && out->rsA[0] == 1);
+        const bool keepContig = (out->kext[0] > 1 && out->ksA[0] == 1);
+        out->kind             = redContig ? RED_ROW : (keepContig ? RED_COL : RED_GENERIC);
+        if(out->nRed == 1 && out->kind == RED_GENERIC && out->nOut > 1)
+            out->kind = keepContig ? RED_COL : RED_GENERIC;
+
+        // vector width along the contiguous reduced axis (row kernel only)
+        out->vec = 1;
+        if(out->kind == RED_ROW && pointersAligned16)
+        {
+            int v = 16 / elemSize;
+            for(; v > 1; v >>= 1)
+            {
+                bool ok = (out->rext[0] % v == 0);
+                for(int i = 1; i < nr && ok; i++)
+                    ok = (out->rsA[i] % v == 0);
+                for(int i = 0; i < nk && ok; i++)
+                    ok = (out->kext[i] == 1) || (out->ksA[i] % v == 0);
+                if(ok)
+                    break;
+            }
+            out->vec = v;
+        }
+        // Few outputs and a long reduction: cut the reduced range into slices so that the
+        // whole GPU works on it (two passes through a scratch buffer).
+        out->split = 1;
+        if(smCount > 0 && out->nOut < int64_t(smCount) * 4 && out->nRed >= 16384)
+        {
+            int64_t want  = (int64_t(smCount) * 8 + out->nOut - 1) / out->nOut;
+            int64_t maxBy = out->nRed / 4096;
+            out->split    = int(std::max<int64_t>(1, std::min<int64_t>(std::min(want, maxBy), 1024)));
+        }
+        return PLAN_OK;
+    }
+
+    std::string describe(const ReducePlan& p)
+    {
+        static const char* kinds[] = {"row", "col", "generic"};
+        std::string        s       = "reduction kind=";
+        s += kinds[p.kind];
+        char buf[128];
+        snprintf(buf, sizeof(buf), " vec=%d split=%d nOut=%lld nRed=%lld keep=[", p.vec, p.split,
+                 (long long)p.nOut, (long long)p.nRed);
+        s += buf;
+        for(int i = 0; i < p.nk; i++)
+        {
+            snprintf(buf, sizeof(buf), "%s%lld:%lld/%lld", i ? " " : "", (long long)p.kext[i],
+                     (long long)p.ksA[i], (long long)p.ksD[i]);
+            s += buf;
+        }
+        s += "] red=[";
+        for(int i = 0; i < p.nr; i++)
+        {
+            snprintf(buf, sizeof(buf), "%s%lld:%lld", i ? " " : "", (long long)p.rext[i], (long long)p.rsA[i]);
+            s += buf;
+        }
+        s += "]";
+        return s;
+    }
+
+    // ------------------------------------------------------------------ contraction
+    int planContraction(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
+                        int computeType, int smCount, ContractionPlan* out)
+    {
+        std::memset(out, 0, sizeof(*out));
+        if(A.rank < 1 || B.rank < 1 || D.rank < 1 || A.rank > kMaxRank || B.rank > kMaxRank
+           || D.rank > kMaxRank)
+            return PLAN_INVALID;
+        if(hasDuplicates(A.modes, A.rank) || hasDuplicates(B.modes, B.rank) || hasDuplicates(D.modes, D.rank))
+            return PLAN_INVALID;
+
+        // ---- type tuples of the reference (contraction_solution_instances.cpp:36-284,
+        //      contraction_cpu_reference_instances.cpp:32-298) plus f16/bf16 inputs with f32 output
+        const int  tA = A.type, tB = B.type, tD = D.type;
+        const bool half = (tA == CUDA_R_16F || tA == CUDA_R_16BF);
+        bool       ok   = false;
+        if(tA == tB)
+        {
+            if(half && computeType == 4 /*32F*/ && (tD == tA || tD == CUDA_R_32F))
+                ok = true;
+            if(tA == CUDA_R_32F && tD == CUDA_R_32F
+               && (computeType == 4 || computeType == 1 /*16F*/ || computeType == 1024 /*16BF*/))
+                ok = true;
+            if(tA == CUDA_R_64F && tD == CUDA_R_64F && (computeType == 16 /*64F*/ || computeType == 4))
+                ok = true;
+        }
+        if(bilinear && typeC != tD)
+            ok = false;
+        if(!ok)
+            return PLAN_NOT_SUPPORTED;
+
+        ModeDim gm[kMaxRank], gn[kMaxRank], gk[kMaxRank];
+        int     nm = 0, nn = 0, nk = 0;
+        for(int i = 0; i < D.rank; i++)
+        {
+            if(D.lens[i] <= 0)
+                return PLAN_INVALID;
+            int ia = findMode(A.modes, A.rank, D.modes[i]);
+            int ib = findMode(B.modes, B.rank, D.modes[i]);
+            if(ia >= 0 && ib >= 0)
+                return PLAN_NOT_SUPPORTED; // batch mode (the reference mis-classifies it)
+            if(ia >= 0)
+            {
+                if(A.lens[ia] != D.lens[i])
+                    return PLAN_INVALID;
+                gm[nm++] = ModeDim{A.lens[ia], A.strides[ia], D.strides[i]};
+            }
+            else if(ib >= 0)
+            {
+                if(B.lens[ib] != D.lens[i])
+                    return PLAN_INVALID;
+                gn[nn++] = ModeDim{B.lens[ib], B.strides[ib], D.strides[i]};
+            }
+            else
+                return PLAN_INVALID; // a mode of D that neither A nor B carries
+        }
+        for(int i = 0; i < A.rank; i++)
+        {
+            if(A.lens[i] <= 0)
+                return PLAN_INVALID;
+            int ib = findMode(B.modes, B.rank, A.modes[i]);
+            int id = findMode(D.modes, D.rank, A.modes[i]);
+            if(ib >= 0)
+            {
+                if(A.lens[i] != B.lens[ib])
+                    return PLAN_INVALID;
+                gk[nk++] = ModeDim{A.lens[i], A.strides[i], B.strides[ib]};
+            }
+            else if(id < 0)
+                return PLAN_INVALID; // a mode of A that is neither contracted nor kept
+        }
+        for(int i = 0; i < B.rank; i++)
+        {
+            if(B.lens[i] <= 0)
+                return PLAN_INVALID;
+            if(findMode(A.modes, A.rank, B.modes[i]) < 0 && findMode(D.modes, D.rank, B.modes[i]) < 0)
+                return PLAN_INVALID;
+        }
+        if(nm > kMaxGroup || nn > kMaxGroup || nk > kMaxGroup)
+            return PLAN_NOT_SUPPORTED;
+
+        // ---- make D contiguous along N when it is contiguous along some M mode
+        int64_t minM = INT64_MAX, minN = INT64_MAX;
+        for(int i = 0; i < nm; i++)
+            if(gm[i].ext > 1)
+                minM = std::min(minM, gm[i].s1);
+        for(int i = 0; i < nn; i++)
+            if(gn[i].ext > 1)
+                minN = std::min(minN, gn[i].s1);
+        out->swapped = (minM < minN) ? 1 : 0;
+        if(out->swapped)
+        {
+            std::swap_ranges(gm, gm + kMaxRank, gn);
+            std::swap(nm, nn);
+            for(int i = 0; i < nk; i++)
+                std::swap(gk[i].s0, gk[i].s1);
+        }
+        out->typeA = out->swapped ? tB : tA;
+        out->typeB = out->swapped ? tA : tB;
+        out->typeC = bilinear ? typeC : -1;
+        out->typeD = tD;
+        out->computeType = computeType;
+        out->bilinear    = bilinear ? 1 : 0;
+
+        // ---- order and fold: M by its stride in A, N by its stride in D, K by its stride in A
+        std::stable_sort(gm, gm + nm, [](const ModeDim& a, const ModeDim& b) { return a.s0 < b.s0; });
+        std::stable_sort(gn, gn + nn, [](const ModeDim& a, const ModeDim& b) { return a.s1 < b.s1; });
+        std::stable_sort(gk, gk + nk, [](const ModeDim& a, const ModeDim& b) { return a.s0 < b.s0; });
+        nm = foldGroup(gm, nm);
+        nn = foldGroup(gn, nn);
+        nk = foldGroup(gk, nk);
+        out->nm = nm;
+        out->nn = nn;
+        out->nk = nk;
+        out->M = out->N = out->K = 1;
+        for(int i = 0; i < nm; i++)
+        {
+            out->m[i] = gm[i];
+            out->M *= gm[i].ext;
+        }
+        for(int i = 0; i < nn; i++)
+        {
+            out->n[i] = gn[i];
+            out->N *= gn[i].ext;
+        }
+        for(int i = 0; i < nk; i++)
+        {
+            out->k[i] = gk[i];
+            out->K *= gk[i].ext;
+        }
+
+        out->aKContig = (nk == 1 && gk[0].s0 == 1) ? 1 : 0;
+        out->bKContig = (nk == 1 && gk[0].s1 == 1) ? 1 : 0;
+        out->splitK   = 1;
+        out->workspaceBytes = 0;
+
+        // ---- kernel family
+        if(tA == CUDA_R_64F && computeType == 16)
+        {
+            out->kind = CK_TILED_DMMA;
+        }
+        else if(half)
+        {
+            // tcgen05 path: both operands K-major with one folded stride-1 K mode, row
+            // strides that are multiples of 16 bytes, and M/N tiles that a TMA box can gather
+            bool tc = out->aKContig && out->bKContig && (out->K % 8 == 0) && nm <= 4 && nn <= 4
+                      && out->K >= 64;
+            auto boxable = [](const ModeDim* d, int n, int tile) {
+                int64_t remaining = tile;
+                for(int i = 0; i < n && remaining > 1; i++)
+                {
+                    if(d[i].s0 % 8 != 0)
+                        return false;
+                    if(d[i].ext >= remaining)
+                        return true;
+                    if(!isPow2(d[i].ext))
+                        return false;
+                    remaining /= d[i].ext;
+                }
+                return true;
+            };
+            for(int i = 0; i < nm && tc; i++)
+                tc = (gm[i].ext == 1) || (gm[i].s0 % 8 == 0 && gm[i].ext < (int64_t(1) << 31));
+            for(int i = 0; i < nn && tc; i++)
+                tc = (gn[i].ext == 1) || (gn[i].s0 % 8 == 0 && gn[i].ext < (int64_t(1) << 31));
+            tc = tc && boxable(gm, nm, 128) && boxable(gn, nn, 128);
+            // small problems do not fill the machine with 128-row tiles: leave them to the
+            // gathered tiled kernel
+            tc = tc && (out->M >= 128 && out->N >= 64);
+            out->kind = tc ? CK_TCGEN05 : CK_TILED_SIMT;
+            if(tc)
+            {
+                out->tileM  = 128;
+                out->tileN  = (out->N >= 256) ? 256 : (out->N >= 128 ? 128 : 64);
+                out->tileK  = 64;
+                out->stages = (out->tileN == 256) ? 4 : 6;
+            }
+        }
+        else
+        {
+            out->kind = CK_TILED_SIMT;
+        }
+        (void)smCount;
+        return PLAN_OK;
+    }
+
+    std::string describe(const ContractionPlan& p)
+    {
+        static const char* kinds[] = {"tiled_simt", "tiled_dmma", "tcgen05"};
+        std::string        s       = "contraction kind=";
+        s += kinds[p.kind];
+        char buf[192];
+        snprintf(buf, sizeof(buf), " M=%lld N=%lld K=%lld types=%s,%s,%s->%s compute=%d swapped=%d ",
+                 (long long)p.M, (long long)p.N, (long long)p.K, typeName(p.typeA), typeName(p.typeB),
+                 p.bilinear ? typeName(p.typeC) : "-", typeName(p.typeD), p.computeType, p.swapped);
+        s += buf;
+        appendDims(s, "m", p.m, p.nm);
+        appendDims(s, " n", p.n, p.nn);
+        appendDims(s, " k", p.k, p.nk);
+        if(p.kind == CK_TCGEN05)
+        {
+            snprintf(buf, sizeof(buf), " tile=%dx%dx%d stages=%d", p.tileM, p.tileN, p.tileK, p.stages);
+            s += buf;
+        }
+        return s;
+    }
+} // namespace htb

@@ -1,0 +1,134 @@
+// Host-side planner: mode-label parsing, stride folding and kernel selection for the
+// three operations. Pure C++ (no CUDA calls) so that it can be tested without a GPU.
+// The structs are plain data and are passed by value to the kernels.
+//
+// It replaces, in the reference:
+//   contraction : normalizeTensorModes (library/src/contraction/contraction_solution.cpp:34-160)
+//                 and the CK instance selection (contraction_selection.cpp:44-195,1687-2214)
+//   permutation : PermutationSolutionImpl::initArgs (permutation_solution_impl.hpp:103-145)
+//   reduction   : ReductionSolutionImpl::initArgs (reduction_solution_impl.hpp:105-163)
+#pragma once
+
+#include <cstdint>
+#include <string>
+
+namespace htb
+{
+    constexpr int kMaxRank  = 12; // reference limit: 6 M + 6 N or 6 K modes per tensor
+    constexpr int kMaxGroup = 6; // modes per group (contraction_meta_traits.hpp:41-43)
+
+    enum PlanStatus : int
+    {
+        PLAN_OK            = 0,
+        PLAN_INVALID       = 7, // HIPTENSOR_STATUS_INVALID_VALUE
+        PLAN_NOT_SUPPORTED = 15 // HIPTENSOR_STATUS_NOT_SUPPORTED
+    };
+
+    // ------------------------------------------------------------------ permutation
+    enum PermKind : int
+    {
+        PERM_COPY = 0, // A's and B's fastest folded modes coincide: row copy
+        PERM_TILE = 1, // 2-D tiled transpose through shared memory, plain loads/stores
+        PERM_TMA  = 2 // same tiling, TMA box loads/stores with 128B-swizzled staging
+    };
+
+    struct PermPlan
+    {
+        int     ndim; // folded modes, in A's order; dim 0 has strideA == 1
+        int     q; // folded mode whose strideB == 1
+        int     kind;
+        int     elemSize; // bytes of A's element
+        int64_t ext[kMaxGroup];
+        int64_t sA[kMaxGroup];
+        int64_t sB[kMaxGroup];
+        int64_t total;
+        // B-side view for the TMA store map: folded modes sorted by ascending strideB
+        int orderB[kMaxGroup];
+    };
+
+    // lens/modeA describe A; B's extents follow from modeB. Strides are recomputed
+    // packed with the first mode fastest, as the reference does.
+    int planPermutation(int rank, const int64_t* lensA, const int32_t* modeA, const int32_t* modeB,
+                        int typeA, int typeB, bool pointersAligned16, PermPlan* out);
+    std::string describe(const PermPlan& p);
+
+    // ------------------------------------------------------------------ reduction
+    enum ReduceKind : int
+    {
+        RED_ROW     = 0, // a reduced mode is contiguous in A: lanes run along the reduced axis
+        RED_COL     = 1, // a kept mode is contiguous in A: lanes run along the kept axis
+        RED_GENERIC = 2 // neither has stride 1
+    };
+
+    struct ReducePlan
+    {
+        int     nk, nr; // folded kept / reduced modes, each sorted by ascending strideA
+        int     kind;
+        int     vec; // elements per vector load along the contiguous axis (1, 2 or 4)
+        int64_t kext[kMaxGroup], ksA[kMaxGroup], ksD[kMaxGroup];
+        int64_t rext[kMaxGroup], rsA[kMaxGroup];
+        int64_t nOut, nRed;
+        int     split; // >1: the reduced range is cut into this many slices (two-pass, needs scratch)
+    };
+
+    int planReduction(int rankA, const int64_t* lensA, const int64_t* stridesA, const int32_t* modeA, int rankD,
+                      const int64_t* lensD, const int64_t* stridesD, const int32_t* modeD, int elemSize,
+                      bool pointersAligned16, int smCount, ReducePlan* out);
+    std::string describe(const ReducePlan& p);
+
+    // ------------------------------------------------------------------ contraction
+    enum ContractionKind : int
+    {
+        CK_TILED_SIMT = 0, // shared-memory tiled FMA kernel with gathered operands (f32 accumulate)
+        CK_TILED_DMMA = 1, // same tiling, FP64 tensor-pipe MMA
+        CK_TCGEN05    = 2 // TMA + tcgen05.mma with TMEM accumulators (f16/bf16 inputs)
+    };
+
+    struct ModeDim
+    {
+        int64_t ext;
+        int64_t s0; // stride in the group's first tensor
+        int64_t s1; // stride in the group's second tensor
+    };
+
+    struct ContractionPlan
+    {
+        // groups after classification and folding; first/second tensor per group:
+        //   m: (A, D)   n: (B, D)   k: (A, B)
+        int     nm, nn, nk;
+        ModeDim m[kMaxGroup], n[kMaxGroup], k[kMaxGroup];
+        int64_t M, N, K;
+        int     typeA, typeB, typeC, typeD; // cudaDataType; typeC < 0 when there is no C
+        int     computeType;
+        int     bilinear;
+        int     swapped; // A and B (and M and N) exchanged so that D is contiguous along N
+        int     kind;
+        // tcgen05 path only
+        int tileM, tileN, tileK, stages;
+        int aKContig, bKContig; // operand has its K group folded to one stride-1 mode
+        // split of the K range over several CTAs (needs workspace); 1 = none
+        int      splitK;
+        uint64_t workspaceBytes;
+    };
+
+    struct TensorView
+    {
+        int            rank;
+        const int64_t* lens;
+        const int64_t* strides;
+        const int32_t* modes;
+        int            type;
+    };
+
+    // D's modes are looked up in A first, then in B (as the reference does); C, when
+    // present, is addressed with D's strides (contraction_solution_impl.hpp:125-140).
+    int planContraction(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
+                        int computeType, int smCount, ContractionPlan* out);
+    std::string describe(const ContractionPlan& p);
+
+    // Shared helper: fold adjacent modes of one group. dims must already be sorted by
+    // ascending s0 (or any order the caller wants to keep); two neighbours merge when
+    // both strides of the second equal stride*extent of the first. Extent-1 modes are
+    // dropped. Returns the new count (at least 1: a group that folds away becomes {1,0,0}).
+    int foldGroup(ModeDim* dims, int n);
+} // namespace htb

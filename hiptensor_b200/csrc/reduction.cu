@@ -1,0 +1,569 @@
+// Reduction kernels for sm_100a: D = alpha * reduce_op(A over the reduced modes) + beta * C.
+//
+//   red_row_kernel : a reduced mode is contiguous in A. A group of G threads (one warp or
+//                    one block) owns one output; lanes stride along the contiguous run with
+//                    128-bit loads and four independent accumulators, then warp shuffles and
+//                    (for G=256) a shared-memory step combine them.
+//   red_col_kernel : a kept mode is contiguous in A. Lanes run along the kept mode
+//                    (coalesced), threadIdx.y cuts the reduced range, shared memory combines.
+//   red_gen_kernel : no stride-1 mode: G threads per output over the flattened reduced range.
+//   red_finalize_kernel : second pass when the reduced range was cut into slices (few outputs,
+//                    long reductions); partial results live in caller-provided scratch.
+//
+// Semantics follow CK's host ReferenceReduce as used by the reference
+// (library/src/reduction/reduction_cpu_reference_impl.hpp:45-64): accumulate in the compute
+// type, NaN propagates through MIN/MAX, then "if alpha != 1: acc *= alpha; if beta != 0:
+// acc += C * beta". They replace CK's DeviceReduceMultiBlock instances
+// (library/src/reduction/reduction_solution_impl.hpp:224-267: 256 threads, vector width 1).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cfloat>
+
+#include "kernels.hpp"
+
+namespace htb
+{
+    namespace
+    {
+        struct RedArgs
+        {
+            int     nk, nr;
+            int64_t kext[kMaxGroup], ksA[kMaxGroup], ksD[kMaxGroup];
+            int64_t rext[kMaxGroup], rsA[kMaxGroup];
+            int64_t nOut, nRed;
+            int     split; // slices of the reduced range (1 = single pass)
+            int     sliceOuter; // 1: slices cut the outer reduced index, 0: the innermost reduced mode
+            int64_t sliceLen;
+        };
+
+        enum
+        {
+            OP_ADD = 3,
+            OP_MUL = 5,
+            OP_MAX = 6,
+            OP_MIN = 7
+        };
+
+        template <typename T>
+        __device__ __forceinline__ T lowestOf();
+        template <>
+        __device__ __forceinline__ float lowestOf<float>()
+        {
+            return -FLT_MAX;
+        }
+        template <>
+        __device__ __forceinline__ double lowestOf<double>()
+        {
+            return -DBL_MAX;
+        }
+
+        template <typename T, int OP>
+        struct Op
+        {
+            static __device__ __forceinline__ T identity()
+            {
+                if(OP == OP_ADD)
+                    return T(0);
+                if(OP == OP_MUL)
+                    return T(1);
+                if(OP == OP_MAX)
+                    return lowestOf<T>();
+                return -lowestOf<T>();
+            }
+            static __device__ __forceinline__ T combine(T acc, T v)
+            {
+                if(OP == OP_ADD)
+                    return acc + v;
+                if(OP == OP_MUL)
+                    return acc * v;
+                if(OP == OP_MAX)
+                    return (v != v || acc < v) ? ((acc != acc) ? acc : v) : acc;
+                return (v != v || acc > v) ? ((acc != acc) ? acc : v) : acc;
+            }
+        };
+
+        template <typename TAcc, typename TIn>
+        __device__ __forceinline__ TAcc widen(TIn v);
+        template <>
+        __device__ __forceinline__ float widen<float, float>(float v)
+        {
+            return v;
+        }
+        template <>
+        __device__ __forceinline__ double widen<double, double>(double v)
+        {
+            return v;
+        }
+        template <>
+        __device__ __forceinline__ float widen<float, __half>(__half v)
+        {
+            return __half2float(v);
+        }
+        template <>
+        __device__ __forceinline__ float widen<float, __nv_bfloat16>(__nv_bfloat16 v)
+        {
+            return __bfloat162float(v);
+        }
+        template <typename TOut, typename TAcc>
+        __device__ __forceinline__ TOut narrow(TAcc v);
+        template <>
+        __device__ __forceinline__ float narrow<float, float>(float v)
+        {
+            return v;
+        }
+        template <>
+        __device__ __forceinline__ double narrow<double, double>(double v)
+        {
+            return v;
+        }
+        template <>
+        __device__ __forceinline__ __half narrow<__half, float>(float v)
+        {
+            return __float2half_rn(v);
+        }
+        template <>
+        __device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16, float>(float v)
+        {
+            return __float2bfloat16_rn(v);
+        }
+
+        __device__ __forceinline__ float mulRn(float a, float b)
+        {
+            return __fmul_rn(a, b);
+        }
+        __device__ __forceinline__ double mulRn(double a, double b)
+        {
+            return __dmul_rn(a, b);
+        }
+        __device__ __forceinline__ float addRn(float a, float b)
+        {
+            return __fadd_rn(a, b);
+        }
+        __device__ __forceinline__ double addRn(double a, double b)
+        {
+            return __dadd_rn(a, b);
+        }
+
+        template <typename TIn, typename TAcc>
+        __device__ __forceinline__ void epilogue(TAcc acc, TAcc alpha, TAcc beta, const TIn* C, TIn* D, int64_t offD)
+        {
+            if(alpha != TAcc(1))
+                acc = mulRn(acc, alpha);
+            if(beta != TAcc(0) && C != nullptr)
+                acc = addRn(acc, mulRn(widen<TAcc, TIn>(C[offD]), beta));
+            D[offD] = narrow<TIn, TAcc>(acc);
+        }
+
+        // 16-byte vector of TIn
+        template <typename TIn, int VEC>
+        struct alignas(sizeof(TIn) * VEC) Vec
+        {
+            TIn v[VEC];
+        };
+
+        __device__ __forceinline__ void keptOffsets(const RedArgs& a, int64_t o, int64_t& offA, int64_t& offD)
+        {
+            offA = 0;
+            offD = 0;
+            for(int d = 0; d < a.nk; d++)
+            {
+                int64_t c = o % a.kext[d];
+                o /= a.kext[d];
+                offA += c * a.ksA[d];
+                offD += c * a.ksD[d];
+            }
+        }
+        // offset of outer reduced index ro (reduced modes 1..nr-1)
+        __device__ __forceinline__ int64_t outerRedOffset(const RedArgs& a, int64_t ro)
+        {
+            int64_t off = 0;
+            for(int d = 1; d < a.nr; d++)
+            {
+                int64_t c = ro % a.rext[d];
+                ro /= a.rext[d];
+                off += c * a.rsA[d];
+            }
+            return off;
+        }
+
+        template <typename TAcc, int OP, int G>
+        __device__ __forceinline__ TAcc groupReduce(TAcc acc, TAcc* smem)
+        {
+#pragma unroll
+            for(int s = 16; s > 0; s >>= 1)
+                acc = Op<TAcc, OP>::combine(acc, __shfl_xor_sync(0xffffffffu, acc, s));
+            if(G > 32)
+            {
+                const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+                if(lane == 0)
+                    smem[warp] = acc;
+                __syncthreads();
+                if(warp == 0)
+                {
+                    acc = (lane < G / 32) ? smem[lane] : Op<TAcc, OP>::identity();
+#pragma unroll
+                    for(int s = 16; s > 0; s >>= 1)
+                        acc = Op<TAcc, OP>::combine(acc, __shfl_xor_sync(0xffffffffu, acc, s));
+                }
+            }
+            return acc;
+        }
+
+        // ------------------------------------------------------------ row kernel
+        // blockDim.x = 256. G = 32: eight outputs per block; G = 256: one output per block.
+        // gridDim.y = split.
+        template <typename TIn, typename TAcc, int OP, int G, int VEC>
+        __global__ void __launch_bounds__(256)
+            red_row_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
+                           TAcc alpha, TAcc beta)
+        {
+            __shared__ TAcc smem[8];
+            constexpr int   perBlock = 256 / G;
+            const int       sub = threadIdx.x / G, lane = threadIdx.x % G;
+            const int64_t   o = int64_t(blockIdx.x) * perBlock + sub;
+            if(G == 32 && o >= a.nOut)
+                return;
+            const int64_t L0 = a.rext[0], RO = a.nRed / L0;
+            int64_t       roLo = 0, roHi = RO, iLo = 0, iHi = L0;
+            if(a.split > 1)
+            {
+                const int64_t s = blockIdx.y;
+                if(a.sliceOuter)
+                {
+                    roLo = s * a.sliceLen;
+                    roHi = min(RO, roLo + a.sliceLen);
+                }
+                else
+                {
+                    iLo = s * a.sliceLen;
+                    iHi = min(L0, iLo + a.sliceLen);
+                }
+            }
+            int64_t offA, offD;
+            keptOffsets(a, o, offA, offD);
+            TAcc acc0 = Op<TAcc, OP>::identity(), acc1 = acc0, acc2 = acc0, acc3 = acc0;
+            for(int64_t ro = roLo; ro < roHi; ro++)
+            {
+                const TIn*    row  = A + offA + outerRedOffset(a, ro);
+                const int64_t step = int64_t(G) * VEC;
+                int64_t       i    = iLo + int64_t(lane) * VEC;
+                // four loads in flight per thread
+                for(; i + 3 * step < iHi; i += 4 * step)
+                {
+                    Vec<TIn, VEC> v0 = *(const Vec<TIn, VEC>*)(row + i);
+                    Vec<TIn, VEC> v1 = *(const Vec<TIn, VEC>*)(row + i + step);
+                    Vec<TIn, VEC> v2 = *(const Vec<TIn, VEC>*)(row + i + 2 * step);
+                    Vec<TIn, VEC> v3 = *(const Vec<TIn, VEC>*)(row + i + 3 * step);
+#pragma unroll
+                    for(int e = 0; e < VEC; e++)
+                    {
+                        acc0 = Op<TAcc, OP>::combine(acc0, widen<TAcc, TIn>(v0.v[e]));
+                        acc1 = Op<TAcc, OP>::combine(acc1, widen<TAcc, TIn>(v1.v[e]));
+                        acc2 = Op<TAcc, OP>::combine(acc2, widen<TAcc, TIn>(v2.v[e]));
+                        acc3 = Op<TAcc, OP>::combine(acc3, widen<TAcc, TIn>(v3.v[e]));
+                    }
+                }
+                for(; i < iHi; i += step)
+                {
+                    Vec<TIn, VEC> v0 = *(const Vec<TIn, VEC>*)(row + i);
+#pragma unroll
+                    for(int e = 0; e < VEC; e++)
+                        acc0 = Op<TAcc, OP>::combine(acc0, widen<TAcc, TIn>(v0.v[e]));
+                }
+            }
+            TAcc acc = Op<TAcc, OP>::combine(Op<TAcc, OP>::combine(acc0, acc1), Op<TAcc, OP>::combine(acc2, acc3));
+            acc      = groupReduce<TAcc, OP, G>(acc, smem);
+            if(lane == 0 && o < a.nOut)
+            {
+                if(a.split > 1)
+                    partial[int64_t(blockIdx.y) * a.nOut + o] = acc;
+                else
+                    epilogue<TIn, TAcc>(acc, alpha, beta, C, D, offD);
+            }
+        }
+
+        // ------------------------------------------------------------ column kernel
+        // blockDim = (TX, TY); gridDim.x = ceil(kext0/TX) * (other kept modes); gridDim.y = split
+        template <typename TIn, typename TAcc, int OP>
+        __global__ void __launch_bounds__(256)
+            red_col_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
+                           TAcc alpha, TAcc beta, int tiles0)
+        {
+            __shared__ TAcc smem[256];
+            const int       tx = threadIdx.x, ty = threadIdx.y, TX = blockDim.x, TY = blockDim.y;
+            int64_t         bid  = blockIdx.x;
+            const int64_t   i0   = (bid % tiles0) * TX + tx;
+            int64_t         rest = bid / tiles0;
+            const bool      ok   = i0 < a.kext[0];
+            int64_t         offA = i0 * a.ksA[0], offD = i0 * a.ksD[0], o = i0, mul = a.kext[0];
+            for(int d = 1; d < a.nk; d++)
+            {
+                int64_t c = rest % a.kext[d];
+                rest /= a.kext[d];
+                offA += c * a.ksA[d];
+                offD += c * a.ksD[d];
+                o += c * mul;
+                mul *= a.kext[d];
+            }
+            const int64_t L0 = a.rext[0], RO = a.nRed / L0, s0 = a.rsA[0];
+            int64_t       roLo = 0, roHi = RO, iLo = 0, iHi = L0;
+            if(a.split > 1)
+            {
+                const int64_t s = blockIdx.y;
+                if(a.sliceOuter)
+                {
+                    roLo = s * a.sliceLen;
+                    roHi = min(RO, roLo + a.sliceLen);
+                }
+                else
+                {
+                    iLo = s * a.sliceLen;
+                    iHi = min(L0, iLo + a.sliceLen);
+                }
+            }
+            TAcc acc0 = Op<TAcc, OP>::identity(), acc1 = acc0, acc2 = acc0, acc3 = acc0;
+            if(ok)
+            {
+                for(int64_t ro = roLo; ro < roHi; ro++)
+                {
+                    const TIn* col = A + offA + outerRedOffset(a, ro);
+                    int64_t    i   = iLo + ty;
+                    for(; i + 3 * TY < iHi; i += 4 * TY)
+                    {
+                        TIn v0 = col[i * s0], v1 = col[(i + TY) * s0], v2 = col[(i + 2 * TY) * s0],
+                            v3 = col[(i + 3 * TY) * s0];
+                        acc0   = Op<TAcc, OP>::combine(acc0, widen<TAcc, TIn>(v0));
+                        acc1   = Op<TAcc, OP>::combine(acc1, widen<TAcc, TIn>(v1));
+                        acc2   = Op<TAcc, OP>::combine(acc2, widen<TAcc, TIn>(v2));
+                        acc3   = Op<TAcc, OP>::combine(acc3, widen<TAcc, TIn>(v3));
+                    }
+                    for(; i < iHi; i += TY)
+                        acc0 = Op<TAcc, OP>::combine(acc0, widen<TAcc, TIn>(col[i * s0]));
+                }
+            }
+            TAcc acc = Op<TAcc, OP>::combine(Op<TAcc, OP>::combine(acc0, acc1), Op<TAcc, OP>::combine(acc2, acc3));
+            smem[ty * TX + tx] = acc;
+            __syncthreads();
+            if(ty == 0 && ok)
+            {
+                for(int y = 1; y < TY; y++)
+                    acc = Op<TAcc, OP>::combine(acc, smem[y * TX + tx]);
+                if(a.split > 1)
+                    partial[int64_t(blockIdx.y) * a.nOut + o] = acc;
+                else
+                    epilogue<TIn, TAcc>(acc, alpha, beta, C, D, offD);
+            }
+        }
+
+        // ------------------------------------------------------------ generic kernel
+        // G threads per output over the flattened reduced range [lo, hi).
+        template <typename TIn, typename TAcc, int OP, int G>
+        __global__ void __launch_bounds__(256)
+            red_gen_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
+                           TAcc alpha, TAcc beta)
+        {
+            __shared__ TAcc smem[8];
+            constexpr int   perBlock = 256 / G;
+            const int       sub = threadIdx.x / G, lane = threadIdx.x % G;
+            const int64_t   o = int64_t(blockIdx.x) * perBlock + sub;
+            if(G == 32 && o >= a.nOut)
+                return;
+            int64_t lo = 0, hi = a.nRed;
+            if(a.split > 1)
+            {
+                lo = int64_t(blockIdx.y) * a.sliceLen;
+                hi = min(a.nRed, lo + a.sliceLen);
+            }
+            int64_t offA, offD;
+            keptOffsets(a, o, offA, offD);
+            TAcc acc = Op<TAcc, OP>::identity();
+            for(int64_t r = lo + lane; r < hi; r += G)
+            {
+                int64_t rem = r, off = 0;
+                for(int d = 0; d < a.nr; d++)
+                {
+                    int64_t c = rem % a.rext[d];
+                    rem /= a.rext[d];
+                    off += c * a.rsA[d];
+                }
+                acc = Op<TAcc, OP>::combine(acc, widen<TAcc, TIn>(A[offA + off]));
+            }
+            acc = groupReduce<TAcc, OP, G>(acc, smem);
+            if(lane == 0 && o < a.nOut)
+            {
+                if(a.split > 1)
+                    partial[int64_t(blockIdx.y) * a.nOut + o] = acc;
+                else
+                    epilogue<TIn, TAcc>(acc, alpha, beta, C, D, offD);
+            }
+        }
+
+        // ------------------------------------------------------------ second pass
+        template <typename TIn, typename TAcc, int OP>
+        __global__ void __launch_bounds__(256)
+            red_finalize_kernel(const TAcc* __restrict__ partial, const TIn* C, TIn* D, RedArgs a, TAcc alpha,
+                                TAcc beta)
+        {
+            const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+            if(o >= a.nOut)
+                return;
+            TAcc acc = Op<TAcc, OP>::identity();
+            for(int s = 0; s < a.split; s++)
+                acc = Op<TAcc, OP>::combine(acc, partial[int64_t(s) * a.nOut + o]);
+            int64_t offA, offD;
+            keptOffsets(a, o, offA, offD);
+            epilogue<TIn, TAcc>(acc, alpha, beta, C, D, offD);
+        }
+
+        template <typename TIn, typename TAcc, int OP>
+        cudaError_t launchTyped(const ReducePlan& p, TAcc alpha, const void* Av, TAcc beta, const void* Cv, void* Dv,
+                                void* workspace, cudaStream_t stream)
+        {
+            const TIn* A = (const TIn*)Av;
+            const TIn* C = (const TIn*)Cv;
+            TIn*       D = (TIn*)Dv;
+            RedArgs    a{};
+            a.nk = p.nk;
+            a.nr = p.nr;
+            for(int i = 0; i < kMaxGroup; i++)
+            {
+                a.kext[i] = p.kext[i];
+                a.ksA[i]  = p.ksA[i];
+                a.ksD[i]  = p.ksD[i];
+                a.rext[i] = p.rext[i];
+                a.rsA[i]  = p.rsA[i];
+            }
+            a.nOut  = p.nOut;
+            a.nRed  = p.nRed;
+            a.split = (workspace != nullptr) ? p.split : 1;
+            TAcc*         partial = (TAcc*)workspace;
+            const int64_t L0 = p.rext[0], RO = p.nRed / L0;
+            if(a.split > 1)
+            {
+                if(p.kind == RED_GENERIC)
+                {
+                    a.sliceLen = (p.nRed + a.split - 1) / a.split;
+                }
+                else if(RO >= a.split)
+                {
+                    a.sliceOuter = 1;
+                    a.sliceLen   = (RO + a.split - 1) / a.split;
+                }
+                else
+                {
+                    a.sliceOuter = 0;
+                    int64_t len  = (L0 + a.split - 1) / a.split;
+                    len          = (len + 15) / 16 * 16; // keeps vector loads aligned
+                    a.sliceLen   = len;
+                    a.split      = int((L0 + len - 1) / len);
+                }
+            }
+            const unsigned gy = unsigned(a.split);
+            if(p.nOut > 0x7fffffffll)
+                return cudaErrorInvalidConfiguration;
+            if(p.kind == RED_ROW)
+            {
+                const bool perBlock = (p.nRed >= 8192 && p.nOut < 4096) || a.split > 1;
+                if(perBlock)
+                {
+                    dim3 grid(unsigned(p.nOut), gy);
+                    if(p.vec == 16 / int(sizeof(TIn)))
+                        red_row_kernel<TIn, TAcc, OP, 256, 16 / sizeof(TIn)>
+                            <<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta);
+                    else
+                        red_row_kernel<TIn, TAcc, OP, 256, 1><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta);
+                }
+                else
+                {
+                    dim3 grid(unsigned((p.nOut + 7) / 8), gy);
+                    if(p.vec == 16 / int(sizeof(TIn)))
+                        red_row_kernel<TIn, TAcc, OP, 32, 16 / sizeof(TIn)>
+                            <<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta);
+                    else
+                        red_row_kernel<TIn, TAcc, OP, 32, 1><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta);
+                }
+                noteLaunch("red_row");
+            }
+            else if(p.kind == RED_COL)
+            {
+                int tx = 32;
+                while(tx < 128 && tx < p.kext[0])
+                    tx <<= 1;
+                int ty = 256 / tx;
+                while(ty > 1 && ty > L0)
+                    ty >>= 1;
+                const int tiles0 = int((p.kext[0] + tx - 1) / tx);
+                int64_t   blocks = tiles0;
+                for(int d = 1; d < p.nk; d++)
+                    blocks *= p.kext[d];
+                if(blocks > 0x7fffffffll)
+                    return cudaErrorInvalidConfiguration;
+                red_col_kernel<TIn, TAcc, OP>
+                    <<<dim3(unsigned(blocks), gy), dim3(tx, ty), 0, stream>>>(A, C, D, partial, a, alpha, beta, tiles0);
+                noteLaunch("red_col");
+            }
+            else
+            {
+                if(p.nRed >= 4096 || a.split > 1)
+                    red_gen_kernel<TIn, TAcc, OP, 256>
+                        <<<dim3(unsigned(p.nOut), gy), 256, 0, stream>>>(A, C, D, partial, a, alpha, beta);
+                else
+                    red_gen_kernel<TIn, TAcc, OP, 32>
+                        <<<dim3(unsigned((p.nOut + 7) / 8), gy), 256, 0, stream>>>(A, C, D, partial, a, alpha, beta);
+                noteLaunch("red_generic");
+            }
+            cudaError_t e = cudaGetLastError();
+            if(e != cudaSuccess)
+                return e;
+            if(a.split > 1)
+            {
+                red_finalize_kernel<TIn, TAcc, OP>
+                    <<<unsigned((p.nOut + 255) / 256), 256, 0, stream>>>(partial, C, D, a, alpha, beta);
+                noteLaunch("red_finalize");
+                e = cudaGetLastError();
+            }
+            return e;
+        }
+
+        template <typename TIn, typename TAcc>
+        cudaError_t launchOp(const ReducePlan& p, int op, double alpha, const void* A, double beta, const void* C,
+                             void* D, void* ws, cudaStream_t s)
+        {
+            switch(op)
+            {
+            case OP_ADD: return launchTyped<TIn, TAcc, OP_ADD>(p, TAcc(alpha), A, TAcc(beta), C, D, ws, s);
+            case OP_MUL: return launchTyped<TIn, TAcc, OP_MUL>(p, TAcc(alpha), A, TAcc(beta), C, D, ws, s);
+            case OP_MAX: return launchTyped<TIn, TAcc, OP_MAX>(p, TAcc(alpha), A, TAcc(beta), C, D, ws, s);
+            case OP_MIN: return launchTyped<TIn, TAcc, OP_MIN>(p, TAcc(alpha), A, TAcc(beta), C, D, ws, s);
+            }
+            return cudaErrorInvalidValue;
+        }
+    } // namespace
+
+    uint64_t reductionWorkspaceBytes(const ReducePlan& plan, int computeType)
+    {
+        if(plan.split <= 1)
+            return 0;
+        const uint64_t accSize = (computeType == HIPTENSOR_COMPUTE_64F) ? 8 : 4;
+        return uint64_t(plan.split) * uint64_t(plan.nOut) * accSize;
+    }
+
+    cudaError_t launchReduction(const ReducePlan& plan, int typeA, int computeType, int op, double alpha,
+                                const void* A, double beta, const void* C, void* D, void* workspace,
+                                cudaStream_t stream)
+    {
+        if(plan.nOut == 0)
+            return cudaSuccess;
+        switch(typeA)
+        {
+        case CUDA_R_32F: return launchOp<float, float>(plan, op, alpha, A, beta, C, D, workspace, stream);
+        case CUDA_R_64F: return launchOp<double, double>(plan, op, alpha, A, beta, C, D, workspace, stream);
+        case CUDA_R_16F: return launchOp<__half, float>(plan, op, alpha, A, beta, C, D, workspace, stream);
+        case CUDA_R_16BF: return launchOp<__nv_bfloat16, float>(plan, op, alpha, A, beta, C, D, workspace, stream);
+        }
+        (void)computeType;
+        return cudaErrorInvalidValue;
+    }
+} // namespace htb

@@ -1,0 +1,178 @@
+"""GPU parity: hiptensorContraction through the C ABI against the CPU oracle.
+
+Metric: the reference's max|d-h|/(|d|+|h|+1) (test/device/common.hpp:122-151).
+Tolerances (BASELINE north star): 1e-5 for fp32/fp64 accumulation, 1e-2 for f16/bf16 inputs;
+next to them the reference's own bound 2*K*eps (+2*2^-10 f16, +2*2^-7 bf16 outputs),
+test/01_contraction/contraction_test.cpp:882-905, is checked where it is the stricter one.
+Mode lists and extents of the shuffled cases are those of
+test/01_contraction/configs/mode_test_params.yaml:15-59."""
+import numpy as np
+import pytest
+
+from helpers import rel_error, run_contraction
+from oracle import binding as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def env():
+    import hiptensor_b200 as ht
+
+    return ht, ht.Handle()
+
+
+def ext_of(modes, lens):
+    return {m: l for ms, ls in zip(modes, lens) for m, l in zip(ms, ls)}
+
+
+# (lengths of A, B, D) and (modes of A, B, D)
+MODE_CASES = [
+    ([[3, 2, 3, 3, 4, 3, 1, 2, 4, 5, 3, 5], [2, 4, 3, 3, 1, 4, 1, 2, 4, 5, 3, 5], [3, 2, 3, 3, 4, 3, 2, 4, 3, 3, 1, 4]],
+     [[0, 1, 2, 3, 4, 5, 12, 13, 14, 15, 16, 17], [6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17],
+      [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11]]),
+    ([[3, 2, 3, 3, 4, 3, 3], [2, 4, 3, 3, 1, 4, 3], [3, 2, 3, 3, 4, 3, 2, 4, 3, 3, 1, 4]],
+     [[0, 1, 2, 3, 4, 5, 16], [6, 7, 8, 9, 10, 11, 16], [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11]]),
+    ([[3, 3], [2, 3], [3, 2]], [[0, 16], [6, 16], [0, 6]]),
+    ([[3, 1, 2, 2, 3, 4, 3, 5, 4, 3, 3, 5], [2, 1, 4, 2, 3, 4, 3, 5, 1, 3, 4, 5], [3, 2, 2, 4, 3, 3, 3, 3, 4, 1, 3, 4]],
+     [[0, 12, 1, 13, 2, 14, 3, 15, 4, 16, 5, 17], [6, 12, 7, 13, 8, 14, 9, 15, 10, 16, 11, 17],
+      [0, 6, 1, 7, 2, 8, 3, 9, 4, 10, 5, 11]]),
+    ([[3, 3, 4, 3, 2, 5, 1, 2, 5, 3, 3, 4], [2, 5, 1, 4, 4, 2, 4, 5, 3, 3, 1, 3], [3, 4, 3, 1, 3, 3, 3, 4, 3, 2, 4, 2]],
+     [[5, 2, 14, 16, 13, 15, 12, 1, 17, 3, 0, 4], [13, 15, 12, 11, 7, 6, 14, 17, 16, 8, 10, 9],
+      [8, 4, 9, 10, 2, 5, 3, 7, 0, 1, 11, 6]]),
+]
+
+
+@pytest.mark.parametrize("case", range(len(MODE_CASES)))
+@pytest.mark.parametrize("dt", [orc.F32, orc.F64])
+def test_mode_orders(env, case, dt):
+    ht, h = env
+    lens, modes = MODE_CASES[case]
+    ext = ext_of(modes, lens)
+    for ab in ((1.0, 2.0), (1.0, 0.0), (0.0, 2.0)):
+        got, exp, td = run_contraction(ht, h, ext, modes[0], modes[1], modes[2], typeAB=dt, alpha=ab[0], beta=ab[1])
+        err = rel_error(got, exp, td)
+        assert 0 <= err < 1e-5, (case, dt, ab, err, ht.last_kernel_name())
+
+
+@pytest.mark.parametrize("dt,ct", [(orc.F32, orc.COMPUTE_32F), (orc.F32, orc.COMPUTE_16F), (orc.F32, orc.COMPUTE_16BF),
+                                   (orc.F64, orc.COMPUTE_64F), (orc.F64, orc.COMPUTE_32F)])
+@pytest.mark.parametrize("with_c", [True, False])
+def test_rank2_type_tuples(env, dt, ct, with_c):
+    """2M2N2K shapes of the reference's validation lists (bilinear/scale_test_params_rank2.yaml)."""
+    ht, h = env
+    m0, m1, n0, n1, k0, k1 = range(6)
+    ext = {m0: 5, m1: 6, n0: 3, n1: 4, k0: 7, k1: 8}
+    for ff in (False, True):
+        got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=dt,
+                                       compute=ct, alpha=1.1, beta=2.2 if with_c else 0.0, with_c=with_c,
+                                       first_fastest=ff)
+        err = rel_error(got, exp, td)
+        # f64 data with f32 compute accumulates in float on both sides
+        assert 0 <= err < 1e-5, (dt, ct, with_c, ff, err)
+
+
+@pytest.mark.parametrize("dt", [orc.F16, orc.BF16])
+@pytest.mark.parametrize("out32", [False, True])
+def test_half_inputs_small(env, dt, out32):
+    ht, h = env
+    m0, m1, n0, n1, k0, k1 = range(6)
+    ext = {m0: 6, m1: 5, n0: 4, n1: 7, k0: 8, k1: 3}
+    got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=dt,
+                                   typeD=orc.F32 if out32 else dt, alpha=1.0, beta=1.0)
+    err = rel_error(got, exp, td)
+    tol = 1e-5 if out32 else (2 * 2.0 ** -10 if dt == orc.F16 else 2 * 2.0 ** -7)
+    assert 0 <= err < tol, (dt, out32, err)
+
+
+def test_config1_fp32_bilinear(env):
+    """D[m0,m1,n0,n1] = 1.0*A[m0,m1,k0,k1]*B[n0,n1,k0,k1] + 1.0*C, all extents 24, first mode fastest."""
+    ht, h = env
+    m0, m1, n0, n1, k0, k1 = range(6)
+    ext = {m: 24 for m in range(6)}
+    got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F32,
+                                   alpha=1.0, beta=1.0, first_fastest=True)
+    err = rel_error(got, exp, td)
+    assert 0 <= err < 1e-5, err
+    assert err < 2 * 576 * np.finfo(np.float32).eps  # the reference's own bound
+
+
+def test_config5_scaled_down(env):
+    """fp64 3M2N2K with interleaved modes at extents m=4, n=12, k=12: whole tensor against the oracle."""
+    ht, h = env
+    m0, m1, m2, n0, n1, k0, k1 = range(7)
+    ext = {m0: 4, m1: 4, m2: 4, n0: 12, n1: 12, k0: 12, k1: 12}
+    got, exp, td = run_contraction(ht, h, ext, [m0, k0, m1, k1, m2], [k1, n0, k0, n1], [m0, m1, m2, n0, n1],
+                                   typeAB=orc.F64, alpha=2.0, beta=0.5)
+    err = rel_error(got, exp, td)
+    assert 0 <= err < 1e-12, err
+    assert ht.last_kernel_name() == "contraction_tiled_dmma"
+
+
+def test_config5_full_size_sampled(env):
+    """fp64 M=4096, N=K=2304: 4096 sampled outputs against the exact-order oracle."""
+    ht, h = env
+    m0, m1, m2, n0, n1, k0, k1 = range(7)
+    ext = {m0: 16, m1: 16, m2: 16, n0: 48, n1: 48, k0: 48, k1: 48}
+    rng = np.random.default_rng(5)
+    smp = rng.integers(0, 16 ** 3 * 48 ** 2, 4096)
+    got, exp, td = run_contraction(ht, h, ext, [m0, k0, m1, k1, m2], [k1, n0, k0, n1], [m0, m1, m2, n0, n1],
+                                   typeAB=orc.F64, alpha=2.0, beta=0.5, sample=smp)
+    err = rel_error(got, exp, td)
+    assert 0 <= err < 2 * 2304 * np.finfo(np.float64).eps, err
+    assert not np.isnan(got).any()
+
+
+def test_config4_scaled_down(env):
+    """f16 x f16 -> f32, k modes innermost, extents 16 (M=N=K=256): whole tensor."""
+    ht, h = env
+    m0, m1, n0, n1, k0, k1 = range(6)
+    ext = {m: 16 for m in range(6)}
+    got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F16,
+                                   typeD=orc.F32, alpha=1.0, beta=0.0, with_c=False, fill="normal")
+    err = rel_error(got, exp, td)
+    assert 0 <= err < 1e-2, err
+    assert err < 1e-4
+
+
+def test_config4_full_size_sampled(env):
+    """f16 inputs, fp32 output, extents 64 (M=N=K=4096): 8192 sampled outputs, plus linearity in alpha."""
+    ht, h = env
+    m0, m1, n0, n1, k0, k1 = range(6)
+    ext = {m: 64 for m in range(6)}
+    rng = np.random.default_rng(4)
+    smp = rng.integers(0, 64 ** 4, 8192)
+    got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F16,
+                                   typeD=orc.F32, alpha=1.0, beta=0.0, with_c=False, fill="normal", sample=smp)
+    err = rel_error(got, exp, td)
+    assert 0 <= err < 1e-2, err
+    assert not np.isnan(got).any()
+    got2, _, _ = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F16,
+                                 typeD=orc.F32, alpha=2.0, beta=0.0, with_c=False, fill="normal", sample=smp[:8])
+    assert np.array_equal(got2, 2.0 * got)  # scaling by a power of two is exact
+
+
+def test_argument_errors(env):
+    import torch
+
+    ht, h = env
+    d = h.tensor_descriptor([4, 4], None, ht.R_32F)
+    x = torch.zeros(16, device="cuda")
+    # a mode of D that neither A nor B has
+    cd = h.contraction_descriptor(d, [0, 1], d, [2, 1], d, [0, 3], d, [0, 3], ht.COMPUTE_32F)
+    with pytest.raises(ht.HiptensorError) as e:
+        h.contraction_plan(cd, h.contraction_find())
+    assert e.value.status == ht.STATUS_INVALID_VALUE
+    # unsupported type tuple: f32 data with f64 compute
+    cd = h.contraction_descriptor(d, [0, 1], d, [2, 1], d, [0, 2], d, [0, 2], ht.COMPUTE_64F)
+    with pytest.raises(ht.HiptensorError) as e:
+        h.contraction_plan(cd, h.contraction_find())
+    assert e.value.status == ht.STATUS_NOT_SUPPORTED
+    with pytest.raises(ht.HiptensorError) as e:
+        h.contraction_find(123)
+    assert e.value.status == ht.STATUS_INVALID_VALUE
+    cd = h.contraction_descriptor(d, [0, 1], d, [2, 1], d, [0, 2], d, [0, 2], ht.COMPUTE_32F)
+    plan = h.contraction_plan(cd, h.contraction_find())
+    with pytest.raises(ht.HiptensorError) as e:
+        h.contraction(plan, 1.0, None, x, 0.0, x, x)
+    assert e.value.status == ht.STATUS_INVALID_VALUE

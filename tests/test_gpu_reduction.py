@@ -1,0 +1,174 @@
+"""GPU parity: hiptensorReduction through the C ABI against the CPU oracle.
+Tolerance: the reference's metric max|d-h|/(|d|+|h|+1) (test/device/common.hpp:122-151) below
+1e-5 for f32/f64 accumulation (stricter than the reference's reduce_len*eps,
+test/03_reduction/reduction_test.cpp:518-543) and 2*2^-10 / 2*2^-7 for f16 / bf16 outputs."""
+import itertools
+import json
+import os
+
+import numpy as np
+import pytest
+
+from helpers import rel_error, run_reduction
+from oracle import binding as orc
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TOL = {orc.F32: 1e-5, orc.F64: 1e-5, orc.F16: 2 * 2.0 ** -10, orc.BF16: 2 * 2.0 ** -7}
+
+
+@pytest.fixture(scope="module")
+def env():
+    import hiptensor_b200 as ht
+
+    return ht, ht.Handle()
+
+
+@pytest.mark.parametrize("dt", [orc.F32, orc.F64])
+def test_golden_vector(env, dt):
+    ht, h = env
+    g = json.load(open(os.path.join(GOLD, "reduction_mhkv_kv.json")))
+    modeA, modeC = [ord(c) for c in g["modeA"]], [ord(c) for c in g["modeC"]]
+    lensA = [g["extent"][c] for c in g["modeA"]]
+    import torch
+
+    from helpers import to_device, to_host
+
+    A = np.arange(int(np.prod(lensA)), dtype=orc.np_dtype(dt))
+    lensC = [g["extent"][c] for c in g["modeC"]]
+    D = np.full(int(np.prod(lensC)), g["C"], dtype=orc.np_dtype(dt))
+    dA, dC = h.tensor_descriptor(lensA, None, dt), h.tensor_descriptor(lensC, None, dt)
+    A_d, D_d = to_device(A, dt), to_device(D, dt)
+    ct = orc.COMPUTE_64F if dt == orc.F64 else orc.COMPUTE_32F
+    h.reduction(g["alpha"], A_d, dA, modeA, g["beta"], D_d, dC, modeC, D_d, dC, modeC, ht.OP_ADD, ct)
+    got = to_host(D_d, dt)
+    exp = np.array(g["expected_default_build"], dtype=orc.np_dtype(dt))
+    assert 0 <= rel_error(got, exp, dt) < 1e-6
+
+
+@pytest.mark.parametrize("op", [orc.OP_ADD, orc.OP_MUL, orc.OP_MIN, orc.OP_MAX])
+def test_rank4_every_output_subset(env, op):
+    """All subsets of kept modes incl. the full reduction and the identity (reference:
+    test/03_reduction/configs/validation/rank4_test_params.yaml:21-39)."""
+    ht, h = env
+    lens, modeA = [6, 5, 9, 8], [0, 1, 2, 3]
+    for r in range(0, 5):
+        for kept in itertools.combinations(modeA, r):
+            got, exp = run_reduction(ht, h, lens, modeA, list(kept), op=op, alpha=1.0, beta=0.0)
+            err = rel_error(got, exp, orc.F32)
+            assert 0 <= err < 1e-5, (op, kept, err, ht.last_kernel_name())
+
+
+@pytest.mark.parametrize("first_fastest", [False, True])
+@pytest.mark.parametrize("kept", [[0, 1], [2, 3], [0, 3], [1], [3]])
+def test_layouts_and_beta(env, first_fastest, kept):
+    ht, h = env
+    lens, modeA = [36, 20, 24, 40], [0, 1, 2, 3]
+    sA = orc.packed_strides(lens, first_fastest)
+    lensD = [lens[m] for m in kept]
+    sD = orc.packed_strides(lensD, first_fastest)
+    for alias in (False, True):
+        got, exp = run_reduction(ht, h, lens, modeA, kept, alpha=1.2, beta=2.1, stridesA=sA, stridesD=sD, alias=alias)
+        err = rel_error(got, exp, orc.F32)
+        assert 0 <= err < 1e-5, (first_fastest, kept, alias, err, ht.last_kernel_name())
+
+
+def test_permuted_output_strides(env):
+    """Output extents in A's order, permutation expressed by strides
+    (test/03_reduction/reduction_test.cpp:334-372)."""
+    ht, h = env
+    lens, modeA, kept = [3, 5, 8], [0, 1, 2], [1, 2]
+    got, exp = run_reduction(ht, h, lens, modeA, kept, stridesD=[1, 5], alpha=1.0, beta=0.0)
+    assert 0 <= rel_error(got, exp, orc.F32) < 1e-5
+
+
+@pytest.mark.parametrize("dt,ct", [(orc.F16, orc.COMPUTE_16F), (orc.F16, orc.COMPUTE_32F),
+                                   (orc.BF16, orc.COMPUTE_16BF), (orc.BF16, orc.COMPUTE_32F),
+                                   (orc.F64, orc.COMPUTE_64F)])
+def test_other_types(env, dt, ct):
+    ht, h = env
+    for kept in ([0], [2], [0, 2]):
+        for op in (orc.OP_ADD, orc.OP_MAX):
+            got, exp = run_reduction(ht, h, [24, 16, 40], [0, 1, 2], kept, dt=dt, compute=ct, op=op, alpha=0.5,
+                                     beta=1.0)
+            err = rel_error(got, exp, dt)
+            assert 0 <= err < TOL[dt], (dt, ct, kept, op, err)
+
+
+def test_nan_propagates_through_max_and_min(env):
+    ht, h = env
+    lens = [8, 64]
+    A = orc.fill_uniform(8 * 64, orc.F32, 17)
+    A[3 * 64 + 11] = np.nan
+    for op in (orc.OP_MAX, orc.OP_MIN):
+        got, exp = run_reduction(ht, h, lens, [0, 1], [0], op=op, A=A.copy())
+        assert np.isnan(got[3]) and np.isnan(exp[3])
+        keep = np.arange(8) != 3
+        assert np.array_equal(got[keep], exp[keep])
+
+
+def test_few_outputs_long_reduction_two_pass(env):
+    """Few outputs and a long reduced range: the sliced two-pass path through the workspace, and
+    the single-pass path when the caller gives no workspace."""
+    ht, h = env
+    lens, modeA = [3, 512, 1024], [0, 1, 2]
+    for kept in ([0], []):
+        for op in (orc.OP_ADD, orc.OP_MAX):
+            got, exp = run_reduction(ht, h, lens, modeA, kept, op=op, alpha=2.0, beta=0.5, use_workspace=True)
+            name = ht.last_kernel_name()
+            err = rel_error(got, exp, orc.F32)
+            assert 0 <= err < 1e-5, (kept, op, err, name)
+            assert name == "red_finalize"
+            got2, exp2 = run_reduction(ht, h, lens, modeA, kept, op=op, alpha=2.0, beta=0.5, use_workspace=False)
+            assert 0 <= rel_error(got2, exp2, orc.F32) < 1e-5
+            assert ht.last_kernel_name() != "red_finalize"
+
+
+def test_rejects_mismatched_descriptors(env):
+    import torch
+
+    ht, h = env
+    x = torch.zeros(64, device="cuda")
+    dA = h.tensor_descriptor([8, 8], None, ht.R_32F)
+    dC = h.tensor_descriptor([8], None, ht.R_32F)
+    dD = h.tensor_descriptor([8], [2], ht.R_32F)
+    with pytest.raises(ht.HiptensorError) as e:
+        h.reduction(1.0, x, dA, [0, 1], 0.0, x, dC, [0], x, dD, [0], ht.OP_ADD, ht.COMPUTE_32F)
+    assert e.value.status == ht.STATUS_NOT_SUPPORTED
+    with pytest.raises(ht.HiptensorError) as e:
+        h.reduction(1.0, x, dA, [0, 1], 0.0, x, dC, [5], x, dC, [5], ht.OP_ADD, ht.COMPUTE_32F)
+    assert e.value.status == ht.STATUS_NOT_SUPPORTED
+    with pytest.raises(ht.HiptensorError) as e:
+        h.reduction(1.0, x, dA, [0, 1], 0.0, x, dC, [0], x, dC, [0], ht.OP_ADD, ht.COMPUTE_64F)
+    assert e.value.status == ht.STATUS_NOT_SUPPORTED
+
+
+@pytest.mark.parametrize("first_fastest", [False, True])
+def test_config3_full_size(env, first_fastest):
+    """A[m,n,k,h] = {4096,64,64,32} fp32 (2 GiB) reduced over {k,h}: D = 1.0*reduce + 0.5*C, ADD then MAX,
+    against the oracle on the full tensor. first_fastest=False is the NULL-stride layout (contiguous
+    2048-element rows), True the strided-column layout."""
+    import torch
+
+    from helpers import to_host
+
+    ht, h = env
+    lens, modeA, kept = [4096, 64, 64, 32], [0, 1, 2, 3], [0, 1]
+    sA = orc.packed_strides(lens, first_fastest)
+    sD = orc.packed_strides(lens[:2], first_fastest)
+    n = int(np.prod(lens))
+    A = orc.fill_uniform(n, orc.F32, 17)
+    C = orc.fill_uniform(4096 * 64, orc.F32, 19)
+    A_d, C_d = torch.from_numpy(A).cuda(), torch.from_numpy(C).cuda()
+    dA = h.tensor_descriptor(lens, sA, ht.R_32F)
+    dD = h.tensor_descriptor(lens[:2], sD, ht.R_32F)
+    for op in (orc.OP_ADD, orc.OP_MAX):
+        D_d = torch.zeros(4096 * 64, device="cuda")
+        h.reduction(1.0, A_d, dA, modeA, 0.5, C_d, dD, kept, D_d, dD, kept, op, ht.COMPUTE_32F)
+        exp = np.zeros(4096 * 64, dtype=np.float32)
+        orc.reduction(1.0, A, lens, sA, modeA, orc.F32, 0.5, C, exp, lens[:2], sD, kept, orc.F32, op,
+                      orc.COMPUTE_32F)
+        err = rel_error(to_host(D_d, orc.F32), exp, orc.F32)
+        assert 0 <= err < 1e-5, (op, first_fastest, err)
+        if op == orc.OP_MAX:  # max is order independent: bit-exact
+            assert np.array_equal(to_host(D_d, orc.F32), exp)

@@ -1,0 +1,132 @@
+"""CPU-only tests of the host-side planner (mode classification, stride folding, kernel choice)
+through the introspection entry points of the C ABI."""
+import re
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def ht():
+    from hiptensor_b200 import build
+
+    build.build()
+    import hiptensor_b200
+
+    return hiptensor_b200
+
+
+def packed(lens, first_fastest):
+    n = len(lens)
+    s = [1] * n
+    if first_fastest:
+        for i in range(1, n):
+            s[i] = s[i - 1] * lens[i - 1]
+    else:
+        for i in range(n - 2, -1, -1):
+            s[i] = s[i + 1] * lens[i + 1]
+    return s
+
+
+def test_permutation_config2_uses_tma(ht):
+    d = ht.describe_permutation_plan([128] * 4, [0, 1, 2, 3], [3, 2, 1, 0])
+    assert "kind=tma" in d and "ndim=4" in d and "q=3" in d
+
+
+def test_permutation_folding(ht):
+    # B[a,b,d,c] = A[a,b,c,d]: a and b fold, inner mode shared -> row copy
+    d = ht.describe_permutation_plan([8, 4, 6, 10], [0, 1, 2, 3], [0, 1, 3, 2])
+    assert "kind=copy" in d and "dims=32:1/1 6:32/320 10:192/32" in d
+    # identity folds to one mode
+    d = ht.describe_permutation_plan([8, 4, 6, 10], [0, 1, 2, 3], [0, 1, 2, 3])
+    assert "ndim=1" in d and "dims=1920:1/1" in d
+    # golden-vector case: c and n fold
+    d = ht.describe_permutation_plan([3, 2, 4, 5], [ord(c) for c in "whcn"], [ord(c) for c in "cnhw"])
+    assert "kind=tile" in d and "dims=3:1/40 2:3/20 20:6/1" in d
+    # extent-1 modes vanish
+    d = ht.describe_permutation_plan([1, 6, 1, 70], [0, 1, 2, 3], [3, 2, 1, 0])
+    assert "ndim=2" in d
+
+
+def test_permutation_rejects(ht):
+    with pytest.raises(ht.HiptensorError) as e:
+        ht.describe_permutation_plan([4, 4], [0, 1], [0, 2])
+    assert e.value.status == ht.STATUS_INVALID_VALUE
+    with pytest.raises(ht.HiptensorError) as e:
+        ht.describe_permutation_plan([4, 4], [0, 1], [1, 0], ht.R_64F)
+    assert e.value.status == ht.STATUS_NOT_SUPPORTED
+    with pytest.raises(ht.HiptensorError) as e:
+        ht.describe_permutation_plan([4, 4], [0, 1], [1, 0], ht.R_32F, ht.R_16F)
+    assert e.value.status == ht.STATUS_NOT_SUPPORTED
+
+
+def test_reduction_config3_layouts(ht):
+    lens = [4096, 64, 64, 32]
+    d = ht.describe_reduction_plan(lens, packed(lens, False), [0, 1, 2, 3], lens[:2], packed(lens[:2], False), [0, 1])
+    assert "kind=row" in d and "vec=4" in d and "nOut=262144" in d and "red=[2048:1]" in d
+    d = ht.describe_reduction_plan(lens, packed(lens, True), [0, 1, 2, 3], lens[:2], packed(lens[:2], True), [0, 1])
+    assert "kind=col" in d and "keep=[262144:1/1]" in d and "red=[2048:262144]" in d
+
+
+def test_reduction_split_and_errors(ht):
+    lens = [3, 512, 1024]
+    d = ht.describe_reduction_plan(lens, packed(lens, False), [0, 1, 2], [3], [1], [0])
+    assert "kind=row" in d and int(re.search(r"split=(\d+)", d).group(1)) > 1
+    d = ht.describe_reduction_plan(lens, packed(lens, False), [0, 1, 2], [], [], [])
+    assert "nOut=1" in d and "nRed=1572864" in d
+    with pytest.raises(ht.HiptensorError) as e:  # extent of D does not match the kept mode of A
+        ht.describe_reduction_plan(lens, packed(lens, False), [0, 1, 2], [4], [1], [0])
+    assert e.value.status == ht.STATUS_INVALID_VALUE
+    with pytest.raises(ht.HiptensorError) as e:  # mode of D missing from A
+        ht.describe_reduction_plan(lens, packed(lens, False), [0, 1, 2], [3], [1], [9])
+    assert e.value.status == ht.STATUS_NOT_SUPPORTED
+
+
+def test_contraction_config1(ht):
+    e = 24
+    s = packed([e] * 4, True)
+    d = ht.describe_contraction_plan([e] * 4, s, [0, 1, 4, 5], ht.R_32F, [e] * 4, s, [2, 3, 4, 5], ht.R_32F, [e] * 4, s,
+                                     [0, 1, 2, 3], ht.R_32F, True, ht.COMPUTE_32F)
+    # D is contiguous along m0: operands are exchanged so that the kernel sees it along N
+    assert "M=576 N=576 K=576" in d and "swapped=1" in d and "n[576:1/1]" in d and "k[576:576/576]" in d
+
+
+def test_contraction_config4(ht):
+    e = 64
+    s = packed([e] * 4, False)
+    d = ht.describe_contraction_plan([e] * 4, s, [0, 1, 4, 5], ht.R_16F, [e] * 4, s, [2, 3, 4, 5], ht.R_16F, [e] * 4, s,
+                                     [0, 1, 2, 3], ht.R_32F, False, ht.COMPUTE_32F)
+    assert "kind=tcgen05" in d and "M=4096 N=4096 K=4096" in d and "k[4096:1/1]" in d and "swapped=0" in d
+
+
+def test_contraction_config5(ht):
+    lA, lB, lD = [16, 48, 16, 48, 16], [48, 48, 48, 48], [16, 16, 16, 48, 48]
+    m0, m1, m2, n0, n1, k0, k1 = range(7)
+    d = ht.describe_contraction_plan(lA, packed(lA, False), [m0, k0, m1, k1, m2], ht.R_64F, lB, packed(lB, False),
+                                     [k1, n0, k0, n1], ht.R_64F, lD, packed(lD, False), [m0, m1, m2, n0, n1],
+                                     ht.R_64F, True, ht.COMPUTE_64F)
+    assert "kind=tiled_dmma" in d and "M=4096 N=2304 K=2304" in d
+    assert "m[16:1/2304 16:768/36864 16:589824/589824]" in d and "k[48:16/110592 48:12288/48]" in d
+
+
+def test_contraction_errors(ht):
+    s = [4, 1]
+    args = dict(lensA=[4, 4], stridesA=s, modeA=[0, 1], dtypeA=ht.R_32F, lensB=[4, 4], stridesB=s, modeB=[2, 1],
+                dtypeB=ht.R_32F, lensD=[4, 4], stridesD=s, modeD=[0, 2], dtypeD=ht.R_32F, has_c=True,
+                type_compute=ht.COMPUTE_32F)
+    assert "M=4 N=4 K=4" in ht.describe_contraction_plan(**args)
+    bad = dict(args, modeD=[0, 3])
+    with pytest.raises(ht.HiptensorError) as e:
+        ht.describe_contraction_plan(**bad)
+    assert e.value.status == ht.STATUS_INVALID_VALUE
+    bad = dict(args, modeB=[2, 0], modeD=[0, 2])  # mode 0 in A, B and D: batch mode
+    with pytest.raises(ht.HiptensorError) as e:
+        ht.describe_contraction_plan(**bad)
+    assert e.value.status == ht.STATUS_NOT_SUPPORTED
+    bad = dict(args, lensB=[4, 5])  # contracted extents differ
+    with pytest.raises(ht.HiptensorError) as e:
+        ht.describe_contraction_plan(**bad)
+    assert e.value.status == ht.STATUS_INVALID_VALUE
+    bad = dict(args, type_compute=ht.COMPUTE_64F)
+    with pytest.raises(ht.HiptensorError) as e:
+        ht.describe_contraction_plan(**bad)
+    assert e.value.status == ht.STATUS_NOT_SUPPORTED
