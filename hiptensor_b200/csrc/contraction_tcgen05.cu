@@ -1,10 +1,551 @@
-// placeholder, replaced below
+// Tensor-core contraction for sm_100a: f16/bf16 operands, fp32 accumulation in tensor memory.
+//
+//   D[m, n] = alpha * sum_k A[m, k] * B[n, k]  (+ beta * C[m, n])
+//
+// on the folded view of the mode lists. Both operands are K-major: their K group folds to one
+// stride-1 mode. The M (N) rows of a tile may span several folded modes of the strided tensor:
+// one multi-dimensional TMA tensor map per operand gathers a [rows x 64] box straight from the
+// tensor into 128-byte-swizzled shared memory, no transposed or packed copy is made.
+//
+// Persistent, warp-specialised CTA (192 threads, one CTA per SM):
+//   warp 0      TMA producer: waits for a free stage, arms the stage's mbarrier with the
+//               expected byte count, issues the A and B box loads.
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (128 x tileN x 16, four
+//               per 64-wide K block) from shared-memory descriptors, commits each stage back
+//               to the producer and each finished accumulator to the epilogue.
+//   warps 2-5   epilogue: tcgen05.ld of their 32-lane quadrant, alpha/beta, rounding to the
+//               output type, stores to the strided D. Two accumulators in tensor memory let
+//               the epilogue of tile i overlap the main loop of tile i+1.
+// Every mbarrier wait is bounded by a clock limit; when it runs out the kernel raises the
+// device status word, skips the remaining work and still frees its tensor memory.
+//
+// No cluster launch and no multicast loads: every CTA loads its own operands.
+// It stands where the reference instantiates CK's xdl contraction kernels for f16/bf16
+// (library/src/contraction/device/*f16*_instance.cpp, *bf16*_instance.cpp).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
 #include "kernels.hpp"
+
 namespace htb
 {
-    cudaError_t launchContractionTcgen05(const ContractionPlan&, float, const void*, const void*, float, const void*,
-                                         void*, int, int*, cudaStream_t)
+    namespace
     {
+        constexpr int kThreads   = 192;
+        constexpr int kTileM     = 128;
+        constexpr int kTileK     = 64; // 64 half-precision elements = one 128-byte swizzle row
+        constexpr int kMaxStages = 8;
+        constexpr long long kWaitCycles = 4000000000ll; // about two seconds
+
+        struct TcArgs
+        {
+            int     nm, nn; // folded modes per group
+            int     boxM[4], boxN[4];
+            int     tilesPerDimM[4], tilesPerDimN[4];
+            int64_t extM[4], extN[4], sDm[4], sDn[4];
+            int     tilesM, tilesN;
+            int     kBlocks;
+            int     stages;
+            int     tileN;
+            uint32_t stageBytes;
+            float   alpha, beta;
+            int     bilinear;
+            int     nContig; // N is one folded mode with stride 1 in D and D is 16-byte aligned
+            int*    status;
+        };
+
+        __device__ __forceinline__ uint32_t smemAddr(const void* p)
+        {
+            return uint32_t(__cvta_generic_to_shared(p));
+        }
+
+        __device__ __forceinline__ void mbarInit(uint32_t bar, uint32_t count)
+        {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+        }
+        __device__ __forceinline__ void mbarArriveExpectTx(uint32_t bar, uint32_t bytes)
+        {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        }
+        __device__ __forceinline__ void mbarArrive(uint32_t bar)
+        {
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+        }
+        // bounded wait; false when the limit ran out or another role already gave up
+        __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity, volatile int* abortFlag)
+        {
+            const long long t0 = clock64();
+            for(;;)
+            {
+                uint32_t done;
+                asm volatile("{\n\t.reg .pred p;\n\t"
+                             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                             "selp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(done)
+                             : "r"(bar), "r"(parity)
+                             : "memory");
+                if(done)
+                    return true;
+                if(*abortFlag)
+                    return false;
+                if(clock64() - t0 > kWaitCycles)
+                {
+                    *abortFlag = 1;
+                    return false;
+                }
+            }
+        }
+
+        // shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+        __device__ __forceinline__ uint64_t smemDesc(uint32_t addr)
+        {
+            uint64_t d = 0;
+            d |= uint64_t((addr & 0x3FFFF) >> 4); // start address
+            d |= uint64_t(1) << 16; // leading byte offset (unused for swizzled K-major)
+            d |= uint64_t(1024 >> 4) << 32; // stride byte offset
+            d |= uint64_t(1) << 46; // descriptor version of sm_100
+            d |= uint64_t(2) << 61; // SWIZZLE_128B
+            return d;
+        }
+
+        template <int RANK>
+        __device__ __forceinline__ void tmaLoad(uint32_t dst, const CUtensorMap* map, uint32_t bar, const int* c)
+        {
+            if constexpr(RANK == 2)
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+                             "{%3, %4}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1])
+                             : "memory");
+            else if constexpr(RANK == 3)
+                asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+                             "{%3, %4, %5}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2])
+                             : "memory");
+            else if constexpr(RANK == 4)
+                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+                             "{%3, %4, %5, %6}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3])
+                             : "memory");
+            else
+                asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+                             "{%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4])
+                             : "memory");
+        }
+        __device__ __forceinline__ void tmaLoadRank(int rank, uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                    const int* c)
+        {
+            switch(rank)
+            {
+            case 2: tmaLoad<2>(dst, map, bar, c); break;
+            case 3: tmaLoad<3>(dst, map, bar, c); break;
+            case 4: tmaLoad<4>(dst, map, bar, c); break;
+            default: tmaLoad<5>(dst, map, bar, c); break;
+            }
+        }
+
+        template <typename T>
+        __device__ __forceinline__ float outToFloat(T v);
+        template <>
+        __device__ __forceinline__ float outToFloat<float>(float v)
+        {
+            return v;
+        }
+        template <>
+        __device__ __forceinline__ float outToFloat<__half>(__half v)
+        {
+            return __half2float(v);
+        }
+        template <>
+        __device__ __forceinline__ float outToFloat<__nv_bfloat16>(__nv_bfloat16 v)
+        {
+            return __bfloat162float(v);
+        }
+
+        // round the accumulator to the output type first, then alpha*x + beta*c in float
+        // (contraction_cpu_reference_impl.hpp:406-425)
+        template <typename TD>
+        __device__ __forceinline__ TD finish(float acc, float alpha, float beta, bool bilinear, const TD* C, int64_t off)
+        {
+            float x = outToFloat<TD>(TD(acc));
+            float y = __fmul_rn(alpha, x);
+            if(bilinear)
+                y = __fadd_rn(y, __fmul_rn(beta, outToFloat<TD>(C[off])));
+            return TD(y);
+        }
+
+        // tile index -> per-mode tile coordinates (first folded mode fastest)
+        __device__ __forceinline__ void tileCoords(int t, const int* tilesPerDim, const int* box, int n, int* coord)
+        {
+            for(int d = 0; d < n; d++)
+            {
+                const int q = t % tilesPerDim[d];
+                t /= tilesPerDim[d];
+                coord[d] = q * box[d];
+            }
+        }
+        // row r of a tile -> offset in D along this group, or -1 outside the tensor
+        __device__ __forceinline__ int64_t rowOffset(int r, const int* coord, const int* box, const int64_t* ext,
+                                                     const int64_t* sD, int n)
+        {
+            int64_t off = 0;
+            for(int d = 0; d < n; d++)
+            {
+                const int     i = r % box[d];
+                r /= box[d];
+                const int64_t g = int64_t(coord[d]) + i;
+                if(g >= ext[d])
+                    return -1;
+                off += g * sD[d];
+            }
+            return (r == 0) ? off : -1; // rows beyond the boxes' product do not exist
+        }
+
+        template <typename TD>
+        __global__ void __launch_bounds__(kThreads, 1)
+            contraction_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                                       const TD* __restrict__ C, TD* __restrict__ D, TcArgs a, uint32_t idesc)
+        {
+            extern __shared__ unsigned char smemRaw[];
+            unsigned char* tiles = (unsigned char*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
+
+            __shared__ __align__(8) unsigned long long fullBar[kMaxStages], emptyBar[kMaxStages];
+            __shared__ __align__(8) unsigned long long tmemFullBar[2], tmemEmptyBar[2];
+            __shared__ uint32_t tmemBase;
+            __shared__ int      abortFlag;
+            __shared__ int64_t  colOff[4][256]; // one table per epilogue warp
+
+            const int      warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            const int      tileN      = a.tileN;
+            const uint32_t aBytes     = kTileM * kTileK * 2; // the stage always reserves a full A tile
+            const uint32_t stageStride = aBytes + uint32_t(tileN) * kTileK * 2;
+            const int      numTiles   = a.tilesM * a.tilesN;
+            const uint32_t tmemCols   = (2 * tileN <= 128) ? 128 : (2 * tileN <= 256 ? 256 : 512);
+
+            if(threadIdx.x == 0)
+            {
+                abortFlag = 0;
+                for(int s = 0; s < a.stages; s++)
+                {
+                    mbarInit(smemAddr(&fullBar[s]), 1);
+                    mbarInit(smemAddr(&emptyBar[s]), 1);
+                }
+                for(int i = 0; i < 2; i++)
+                {
+                    mbarInit(smemAddr(&tmemFullBar[i]), 1);
+                    mbarInit(smemAddr(&tmemEmptyBar[i]), 128);
+                }
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            }
+            if(warp == 1)
+            {
+                asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&tmemBase)),
+                             "r"(tmemCols)
+                             : "memory");
+                asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem = tmemBase;
+            volatile int*  abortP = &abortFlag;
+
+            if(warp == 0)
+            {
+                // ---------------------------------------------------------------- TMA producer
+                if(lane == 0)
+                {
+                    int      stage = 0;
+                    uint32_t phase = 0;
+                    bool     ok    = true;
+                    for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x)
+                    {
+                        const int tm = t % a.tilesM, tn = t / a.tilesM;
+                        int       cA[5] = {0, 0, 0, 0, 0}, cB[5] = {0, 0, 0, 0, 0};
+                        tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cA + 1);
+                        tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB + 1);
+                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        {
+                            ok = mbarWait(smemAddr(&emptyBar[stage]), phase ^ 1, abortP);
+                            if(!ok)
+                                break;
+                            const uint32_t bar = smemAddr(&fullBar[stage]);
+                            mbarArriveExpectTx(bar, a.stageBytes);
+                            cA[0] = kb * kTileK;
+                            cB[0] = kb * kTileK;
+                            const uint32_t dstA = smemAddr(tiles + size_t(stage) * stageStride);
+                            tmaLoadRank(a.nm + 1, dstA, &mapA, bar, cA);
+                            tmaLoadRank(a.nn + 1, dstA + aBytes, &mapB, bar, cB);
+                            if(++stage == a.stages)
+                            {
+                                stage = 0;
+                                phase ^= 1;
+                            }
+                        }
+                    }
+                }
+            }
+            else if(warp == 1)
+            {
+                // ---------------------------------------------------------------- MMA issuer
+                if(lane == 0)
+                {
+                    int      stage = 0;
+                    uint32_t phase = 0;
+                    int      local = 0;
+                    bool     ok    = true;
+                    for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, local++)
+                    {
+                        const int      acc      = local & 1;
+                        const uint32_t accPhase = (local >> 1) & 1;
+                        ok = mbarWait(smemAddr(&tmemEmptyBar[acc]), accPhase ^ 1, abortP);
+                        if(!ok)
+                            break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t dTmem = tmem + uint32_t(acc * tileN);
+                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        {
+                            ok = mbarWait(smemAddr(&fullBar[stage]), phase, abortP);
+                            if(!ok)
+                                break;
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            const uint32_t sa    = smemAddr(tiles + size_t(stage) * stageStride);
+                            const uint64_t descA = smemDesc(sa), descB = smemDesc(sa + aBytes);
+#pragma unroll
+                            for(int k = 0; k < kTileK / 16; k++)
+                            {
+                                const uint32_t accumulate = (kb | k) ? 1u : 0u;
+                                // 16 half-precision elements = 32 bytes = 2 descriptor address units
+                                asm volatile("{\n\t.reg .pred p;\n\t"
+                                             "setp.ne.b32 p, %4, 0;\n\t"
+                                             "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
+                                             "l"(descA + uint64_t(2 * k)), "l"(descB + uint64_t(2 * k)), "r"(idesc),
+                                             "r"(accumulate)
+                                             : "memory");
+                            }
+                            // the stage is free once these MMAs have read it
+                            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                             smemAddr(&emptyBar[stage]))
+                                         : "memory");
+                            if(++stage == a.stages)
+                            {
+                                stage = 0;
+                                phase ^= 1;
+                            }
+                        }
+                        if(ok)
+                            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                             smemAddr(&tmemFullBar[acc]))
+                                         : "memory");
+                    }
+                }
+            }
+            else
+            {
+                // ---------------------------------------------------------------- epilogue
+                const int quad = warp & 3; // TMEM lane quadrant this warp may read
+                const int row  = quad * 32 + lane;
+                int64_t*  cols = colOff[quad];
+                int       local = 0;
+                for(int t = blockIdx.x; t < numTiles; t += gridDim.x, local++)
+                {
+                    const int      acc      = local & 1;
+                    const uint32_t accPhase = (local >> 1) & 1;
+                    const int      tm = t % a.tilesM, tn = t / a.tilesM;
+                    int            cM[4], cN[4];
+                    tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cM);
+                    tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cN);
+                    // this warp's table of column offsets for the tile
+                    __syncwarp();
+                    for(int c = lane; c < tileN; c += 32)
+                        cols[c] = rowOffset(c, cN, a.boxN, a.extN, a.sDn, a.nn);
+                    __syncwarp();
+                    const int64_t offM = rowOffset(row, cM, a.boxM, a.extM, a.sDm, a.nm);
+
+                    // one lane waits, the warp follows its verdict
+                    int ok = 1;
+                    if(lane == 0)
+                        ok = mbarWait(smemAddr(&tmemFullBar[acc]), accPhase, abortP) ? 1 : 0;
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if(!ok)
+                        break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(acc * tileN);
+                    for(int c0 = 0; c0 < tileN; c0 += 32)
+                    {
+                        uint32_t v[32];
+                        asm volatile(
+                            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                              "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+                              "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+                              "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                              "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                            : "r"(taddr + uint32_t(c0)));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if(offM < 0)
+                            continue;
+                        const int64_t first = cols[c0];
+                        const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] >= 0;
+                        if(fullChunk && sizeof(TD) == 4 && ((offM + first) & 3) == 0)
+                        {
+                            // 32 consecutive floats of this row: eight 128-bit stores
+                            float*       dst = (float*)D + offM + first;
+                            const float* src = (const float*)C + offM + first;
+#pragma unroll
+                            for(int j = 0; j < 32; j += 4)
+                            {
+                                float4 o;
+                                o.x = __fmul_rn(a.alpha, __uint_as_float(v[j]));
+                                o.y = __fmul_rn(a.alpha, __uint_as_float(v[j + 1]));
+                                o.z = __fmul_rn(a.alpha, __uint_as_float(v[j + 2]));
+                                o.w = __fmul_rn(a.alpha, __uint_as_float(v[j + 3]));
+                                if(a.bilinear)
+                                {
+                                    const float4 c4 = *(const float4*)(src + j);
+                                    o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4.x));
+                                    o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4.y));
+                                    o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4.z));
+                                    o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4.w));
+                                }
+                                *(float4*)(dst + j) = o;
+                            }
+                        }
+                        else
+                        {
+#pragma unroll
+                            for(int j = 0; j < 32; j++)
+                            {
+                                const int64_t oc = cols[c0 + j];
+                                if(oc >= 0)
+                                    D[offM + oc] = finish<TD>(__uint_as_float(v[j]), a.alpha, a.beta, a.bilinear != 0, C,
+                                                              offM + oc);
+                            }
+                        }
+                    }
+                    // hand the accumulator back to the MMA warp
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbarArrive(smemAddr(&tmemEmptyBar[acc]));
+                }
+            }
+
+            // ---------------------------------------------------------------- teardown
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();
+            if(threadIdx.x == 0 && abortFlag && a.status)
+                atomicExch(a.status, 2);
+            if(warp == 1)
+            {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmemCols) : "memory");
+            }
+        }
+
+        bool encodeOperand(PFN_encodeTiled encode, CUtensorMap* map, const void* base, bool bf16, int64_t K,
+                           const ModeDim* dims, int n, const int* box)
+        {
+            cuuint64_t gdim[5], gstr[4];
+            cuuint32_t bx[5], estr[5] = {1, 1, 1, 1, 1};
+            gdim[0] = cuuint64_t(K);
+            bx[0]   = kTileK;
+            for(int d = 0; d < n; d++)
+            {
+                gdim[d + 1] = cuuint64_t(dims[d].ext);
+                // a degenerate mode (extent 1) may carry stride 0: any 16-byte multiple is legal
+                gstr[d]   = (dims[d].ext == 1) ? cuuint64_t(K) * 2 : cuuint64_t(dims[d].s0) * 2;
+                bx[d + 1] = cuuint32_t(box[d]);
+                if(gstr[d] % 16 != 0 || gstr[d] == 0)
+                    return false;
+            }
+            return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, n + 1,
+                          const_cast<void*>(base), gdim, gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+                   == CUDA_SUCCESS;
+        }
+
+        template <typename TD>
+        cudaError_t launchTyped(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
+                                const void* C, void* D, int smCount, int* status, cudaStream_t stream)
+        {
+            PFN_encodeTiled encode = tensorMapEncoder();
+            if(!encode)
+                return cudaErrorNotSupported;
+            const bool  bf16 = (p.typeA == CUDA_R_16BF);
+            CUtensorMap mapA, mapB;
+            if(!encodeOperand(encode, &mapA, A, bf16, p.K, p.m, p.nm, p.boxM)
+               || !encodeOperand(encode, &mapB, B, bf16, p.K, p.n, p.nn, p.boxN))
+                return cudaErrorNotSupported;
+
+            TcArgs a{};
+            a.nm     = p.nm;
+            a.nn     = p.nn;
+            a.tilesM = 1;
+            a.tilesN = 1;
+            for(int d = 0; d < p.nm; d++)
+            {
+                a.boxM[d]         = p.boxM[d];
+                a.extM[d]         = p.m[d].ext;
+                a.sDm[d]          = p.m[d].s1;
+                a.tilesPerDimM[d] = int((p.m[d].ext + p.boxM[d] - 1) / p.boxM[d]);
+                a.tilesM *= a.tilesPerDimM[d];
+            }
+            for(int d = 0; d < p.nn; d++)
+            {
+                a.boxN[d]         = p.boxN[d];
+                a.extN[d]         = p.n[d].ext;
+                a.sDn[d]          = p.n[d].s1;
+                a.tilesPerDimN[d] = int((p.n[d].ext + p.boxN[d] - 1) / p.boxN[d]);
+                a.tilesN *= a.tilesPerDimN[d];
+            }
+            a.kBlocks    = int((p.K + kTileK - 1) / kTileK);
+            a.tileN      = p.tileN;
+            a.stages     = p.stages;
+            a.stageBytes = uint32_t(p.rowsM + p.rowsN) * kTileK * 2;
+            a.alpha      = alpha;
+            a.beta       = beta;
+            a.bilinear   = (p.bilinear && C != nullptr) ? 1 : 0;
+            a.nContig    = (p.nn == 1 && p.n[0].s1 == 1 && (uintptr_t(D) & 15) == 0
+                         && (!a.bilinear || (uintptr_t(C) & 15) == 0))
+                               ? 1
+                               : 0;
+            a.status     = status;
+            if(int64_t(a.tilesM) * a.tilesN > 0x7fffffffll || a.stages > kMaxStages)
+                return cudaErrorInvalidConfiguration;
+
+            // instruction descriptor: fp32 accumulate, A/B format, both K-major, N/8, M/16
+            const uint32_t fmt   = bf16 ? 1u : 0u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(p.tileN >> 3) << 17)
+                                   | (uint32_t(kTileM >> 4) << 24);
+
+            const size_t smem = size_t(a.stages) * (size_t(kTileM) + p.tileN) * kTileK * 2 + 1024;
+            cudaError_t  e = cudaFuncSetAttribute(contraction_tcgen05_kernel<TD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  int(smem));
+            if(e != cudaSuccess)
+                return e;
+            const int grid = int(std::min<int64_t>(int64_t(a.tilesM) * a.tilesN, smCount > 0 ? smCount : 148));
+            contraction_tcgen05_kernel<TD>
+                <<<grid, kThreads, smem, stream>>>(mapA, mapB, (const TD*)C, (TD*)D, a, idesc);
+            noteLaunch("contraction_tcgen05");
+            return cudaGetLastError();
+        }
+    } // namespace
+
+    cudaError_t launchContractionTcgen05(const ContractionPlan& plan, float alpha, const void* A, const void* B,
+                                         float beta, const void* C, void* D, int smCount, int* deviceStatus,
+                                         cudaStream_t stream)
+    {
+        switch(plan.typeD)
+        {
+        case CUDA_R_32F: return launchTyped<float>(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
+        case CUDA_R_16F: return launchTyped<__half>(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
+        case CUDA_R_16BF:
+            return launchTyped<__nv_bfloat16>(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
+        }
         return cudaErrorNotSupported;
     }
-}
+} // namespace htb

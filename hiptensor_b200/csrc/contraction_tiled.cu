@@ -273,6 +273,15 @@ namespace htb
                 }
                 else
                 {
+                    // the 16 products of a K step are summed on their own and then added to the
+                    // running total: short partial sums keep the fp32 rounding error of long
+                    // contractions well below that of one sequential sum
+                    TAcc part[4][4];
+#pragma unroll
+                    for(int i = 0; i < 4; i++)
+#pragma unroll
+                        for(int j = 0; j < 4; j++)
+                            part[i][j] = TAcc(0);
 #pragma unroll
                     for(int kk = 0; kk < BK; kk++)
                     {
@@ -287,8 +296,13 @@ namespace htb
                         for(int i = 0; i < 4; i++)
 #pragma unroll
                             for(int j = 0; j < 4; j++)
-                                acc[i][j] += av[i] * bv[j];
+                                part[i][j] += av[i] * bv[j];
                     }
+#pragma unroll
+                    for(int i = 0; i < 4; i++)
+#pragma unroll
+                        for(int j = 0; j < 4; j++)
+                            acc[i][j] += part[i][j];
                 }
                 if(hasNext)
                 {

@@ -97,6 +97,29 @@ namespace htb
         return w;
     }
 
+    int boxDecompose(const ModeDim* dims, int n, int tile, int* box)
+    {
+        int64_t remaining = tile;
+        for(int i = 0; i < n; i++)
+        {
+            if(remaining == 1)
+                box[i] = 1;
+            else if(dims[i].ext >= remaining)
+            {
+                box[i]    = int(remaining);
+                remaining = 1;
+            }
+            else if(isPow2(dims[i].ext))
+            {
+                box[i] = int(dims[i].ext);
+                remaining /= dims[i].ext;
+            }
+            else
+                return 0;
+        }
+        return int(tile / remaining);
+    }
+
     // ------------------------------------------------------------------ permutation
     int planPermutation(int rank, const int64_t* lensA, const int32_t* modeA, const int32_t* modeB,
                         int typeA, int typeB, bool pointersAligned16, PermPlan* out)
@@ -459,36 +482,28 @@ namespace htb
             // strides that are multiples of 16 bytes, and M/N tiles that a TMA box can gather
             bool tc = out->aKContig && out->bKContig && (out->K % 8 == 0) && nm <= 4 && nn <= 4
                       && out->K >= 64;
-            auto boxable = [](const ModeDim* d, int n, int tile) {
-                int64_t remaining = tile;
-                for(int i = 0; i < n && remaining > 1; i++)
-                {
-                    if(d[i].s0 % 8 != 0)
-                        return false;
-                    if(d[i].ext >= remaining)
-                        return true;
-                    if(!isPow2(d[i].ext))
-                        return false;
-                    remaining /= d[i].ext;
-                }
-                return true;
-            };
             for(int i = 0; i < nm && tc; i++)
-                tc = (gm[i].ext == 1) || (gm[i].s0 % 8 == 0 && gm[i].ext < (int64_t(1) << 31));
+                tc = (gm[i].s0 % 8 == 0 && gm[i].ext < (int64_t(1) << 31));
             for(int i = 0; i < nn && tc; i++)
-                tc = (gn[i].ext == 1) || (gn[i].s0 % 8 == 0 && gn[i].ext < (int64_t(1) << 31));
-            tc = tc && boxable(gm, nm, 128) && boxable(gn, nn, 128);
+                tc = (gn[i].s0 % 8 == 0 && gn[i].ext < (int64_t(1) << 31));
             // small problems do not fill the machine with 128-row tiles: leave them to the
             // gathered tiled kernel
             tc = tc && (out->M >= 128 && out->N >= 64);
-            out->kind = tc ? CK_TCGEN05 : CK_TILED_SIMT;
             if(tc)
             {
-                out->tileM  = 128;
-                out->tileN  = (out->N >= 256) ? 256 : (out->N >= 128 ? 128 : 64);
-                out->tileK  = 64;
+                out->tileM = 128;
+                out->tileK = 64;
+                out->rowsM = boxDecompose(gm, nm, 128, out->boxM);
+                out->rowsN = 0;
+                for(int tn = (out->N >= 256 ? 256 : (out->N >= 128 ? 128 : 64)); tn >= 64 && out->rowsN == 0; tn >>= 1)
+                {
+                    out->tileN = tn;
+                    out->rowsN = boxDecompose(gn, nn, tn, out->boxN);
+                }
+                tc = out->rowsM > 0 && out->rowsN > 0;
                 out->stages = (out->tileN == 256) ? 4 : 6;
             }
+            out->kind = tc ? CK_TCGEN05 : CK_TILED_SIMT;
         }
         else
         {
@@ -513,8 +528,21 @@ namespace htb
         appendDims(s, " k", p.k, p.nk);
         if(p.kind == CK_TCGEN05)
         {
-            snprintf(buf, sizeof(buf), " tile=%dx%dx%d stages=%d", p.tileM, p.tileN, p.tileK, p.stages);
+            snprintf(buf, sizeof(buf), " tile=%dx%dx%d stages=%d rows=%d/%d boxM=[", p.tileM, p.tileN, p.tileK,
+                     p.stages, p.rowsM, p.rowsN);
             s += buf;
+            for(int i = 0; i < p.nm; i++)
+            {
+                snprintf(buf, sizeof(buf), "%s%d", i ? " " : "", p.boxM[i]);
+                s += buf;
+            }
+            s += "] boxN=[";
+            for(int i = 0; i < p.nn; i++)
+            {
+                snprintf(buf, sizeof(buf), "%s%d", i ? " " : "", p.boxN[i]);
+                s += buf;
+            }
+            s += "]";
         }
         return s;
     }

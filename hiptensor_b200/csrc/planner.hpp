@@ -105,6 +105,8 @@ namespace htb
         int     kind;
         // tcgen05 path only
         int tileM, tileN, tileK, stages;
+        int boxM[4], boxN[4]; // TMA box extent per folded M / N mode (product = rows gathered per tile)
+        int rowsM, rowsN; // rows of the tile that the boxes fill (<= tileM / tileN)
         int aKContig, bKContig; // operand has its K group folded to one stride-1 mode
         // split of the K range over several CTAs (needs workspace); 1 = none
         int      splitK;
@@ -125,6 +127,12 @@ namespace htb
     int planContraction(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
                         int computeType, int smCount, ContractionPlan* out);
     std::string describe(const ContractionPlan& p);
+
+    // Splits `tile` rows over the folded modes of a group, fastest mode first: a mode is taken
+    // whole while it is a power of two smaller than what is left, the first mode at least as
+    // large as what is left takes the rest (ragged ends are zero-filled by TMA), later modes
+    // get 1. Returns the rows covered (0 if the group cannot be boxed).
+    int boxDecompose(const ModeDim* dims, int n, int tile, int* box);
 
     // Shared helper: fold adjacent modes of one group. dims must already be sorted by
     // ascending s0 (or any order the caller wants to keep); two neighbours merge when

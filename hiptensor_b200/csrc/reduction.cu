@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include <cfloat>
+#include <type_traits>
 
 #include "kernels.hpp"
 
@@ -81,6 +82,54 @@ namespace htb
                 if(OP == OP_MAX)
                     return (v != v || acc < v) ? ((acc != acc) ? acc : v) : acc;
                 return (v != v || acc > v) ? ((acc != acc) ? acc : v) : acc;
+            }
+        };
+
+        // Two-level accumulator of one thread. Four independent running values take the
+        // elements in turn; every 8 rounds (32 elements) they are folded into a top-level value.
+        // For fp32 sums the top level is fp64, so that the rounding error of a long sum stays
+        // that of its short fp32 partial sums (the reference accumulates sequentially in fp32;
+        // its own tolerance is reduce_len * eps). The other operators fold only once, at the end.
+        template <typename TAcc, int OP>
+        struct Accum
+        {
+            using Top = typename std::conditional<(OP == OP_ADD && sizeof(TAcc) == 4), double, TAcc>::type;
+            static constexpr bool kTwoLevel = !std::is_same<Top, TAcc>::value;
+            TAcc a0, a1, a2, a3;
+            Top  top;
+            int  cnt;
+            __device__ __forceinline__ void init()
+            {
+                a0 = a1 = a2 = a3 = Op<TAcc, OP>::identity();
+                top               = Op<Top, OP>::identity();
+                cnt               = 0;
+            }
+            __device__ __forceinline__ void fold()
+            {
+                TAcc s = Op<TAcc, OP>::combine(Op<TAcc, OP>::combine(a0, a1), Op<TAcc, OP>::combine(a2, a3));
+                top    = Op<Top, OP>::combine(top, Top(s));
+                a0 = a1 = a2 = a3 = Op<TAcc, OP>::identity();
+                cnt               = 0;
+            }
+            __device__ __forceinline__ void add4(TAcc v0, TAcc v1, TAcc v2, TAcc v3)
+            {
+                a0 = Op<TAcc, OP>::combine(a0, v0);
+                a1 = Op<TAcc, OP>::combine(a1, v1);
+                a2 = Op<TAcc, OP>::combine(a2, v2);
+                a3 = Op<TAcc, OP>::combine(a3, v3);
+                if(kTwoLevel && ++cnt == 8)
+                    fold();
+            }
+            __device__ __forceinline__ void add1(TAcc v)
+            {
+                a0 = Op<TAcc, OP>::combine(a0, v);
+                if(kTwoLevel && ++cnt == 8)
+                    fold();
+            }
+            __device__ __forceinline__ Top result()
+            {
+                fold();
+                return top;
             }
         };
 
@@ -219,7 +268,7 @@ namespace htb
             red_row_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
                            TAcc alpha, TAcc beta)
         {
-            __shared__ TAcc smem[8];
+            __shared__ double smem[8];
             constexpr int   perBlock = 256 / G;
             const int       sub = threadIdx.x / G, lane = threadIdx.x % G;
             const int64_t   o = int64_t(blockIdx.x) * perBlock + sub;
@@ -243,7 +292,8 @@ namespace htb
             }
             int64_t offA, offD;
             keptOffsets(a, o, offA, offD);
-            TAcc acc0 = Op<TAcc, OP>::identity(), acc1 = acc0, acc2 = acc0, acc3 = acc0;
+            Accum<TAcc, OP> accum;
+            accum.init();
             for(int64_t ro = roLo; ro < roHi; ro++)
             {
                 const TIn*    row  = A + offA + outerRedOffset(a, ro);
@@ -258,29 +308,25 @@ namespace htb
                     Vec<TIn, VEC> v3 = *(const Vec<TIn, VEC>*)(row + i + 3 * step);
 #pragma unroll
                     for(int e = 0; e < VEC; e++)
-                    {
-                        acc0 = Op<TAcc, OP>::combine(acc0, widen<TAcc, TIn>(v0.v[e]));
-                        acc1 = Op<TAcc, OP>::combine(acc1, widen<TAcc, TIn>(v1.v[e]));
-                        acc2 = Op<TAcc, OP>::combine(acc2, widen<TAcc, TIn>(v2.v[e]));
-                        acc3 = Op<TAcc, OP>::combine(acc3, widen<TAcc, TIn>(v3.v[e]));
-                    }
+                        accum.add4(widen<TAcc, TIn>(v0.v[e]), widen<TAcc, TIn>(v1.v[e]), widen<TAcc, TIn>(v2.v[e]),
+                                   widen<TAcc, TIn>(v3.v[e]));
                 }
                 for(; i < iHi; i += step)
                 {
                     Vec<TIn, VEC> v0 = *(const Vec<TIn, VEC>*)(row + i);
 #pragma unroll
                     for(int e = 0; e < VEC; e++)
-                        acc0 = Op<TAcc, OP>::combine(acc0, widen<TAcc, TIn>(v0.v[e]));
+                        accum.add1(widen<TAcc, TIn>(v0.v[e]));
                 }
             }
-            TAcc acc = Op<TAcc, OP>::combine(Op<TAcc, OP>::combine(acc0, acc1), Op<TAcc, OP>::combine(acc2, acc3));
-            acc      = groupReduce<TAcc, OP, G>(acc, smem);
+            using Top = typename Accum<TAcc, OP>::Top;
+            Top acc   = groupReduce<Top, OP, G>(accum.result(), (Top*)smem);
             if(lane == 0 && o < a.nOut)
             {
                 if(a.split > 1)
-                    partial[int64_t(blockIdx.y) * a.nOut + o] = acc;
+                    partial[int64_t(blockIdx.y) * a.nOut + o] = TAcc(acc);
                 else
-                    epilogue<TIn, TAcc>(acc, alpha, beta, C, D, offD);
+                    epilogue<TIn, TAcc>(TAcc(acc), alpha, beta, C, D, offD);
             }
         }
 
@@ -291,7 +337,7 @@ namespace htb
             red_col_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
                            TAcc alpha, TAcc beta, int tiles0)
         {
-            __shared__ TAcc smem[256];
+            __shared__ double smemRaw[256];
             const int       tx = threadIdx.x, ty = threadIdx.y, TX = blockDim.x, TY = blockDim.y;
             int64_t         bid  = blockIdx.x;
             const int64_t   i0   = (bid % tiles0) * TX + tx;
@@ -323,7 +369,8 @@ namespace htb
                     iHi = min(L0, iLo + a.sliceLen);
                 }
             }
-            TAcc acc0 = Op<TAcc, OP>::identity(), acc1 = acc0, acc2 = acc0, acc3 = acc0;
+            Accum<TAcc, OP> accum;
+            accum.init();
             if(ok)
             {
                 for(int64_t ro = roLo; ro < roHi; ro++)
@@ -334,26 +381,26 @@ namespace htb
                     {
                         TIn v0 = col[i * s0], v1 = col[(i + TY) * s0], v2 = col[(i + 2 * TY) * s0],
                             v3 = col[(i + 3 * TY) * s0];
-                        acc0   = Op<TAcc, OP>::combine(acc0, widen<TAcc, TIn>(v0));
-                        acc1   = Op<TAcc, OP>::combine(acc1, widen<TAcc, TIn>(v1));
-                        acc2   = Op<TAcc, OP>::combine(acc2, widen<TAcc, TIn>(v2));
-                        acc3   = Op<TAcc, OP>::combine(acc3, widen<TAcc, TIn>(v3));
+                        accum.add4(widen<TAcc, TIn>(v0), widen<TAcc, TIn>(v1), widen<TAcc, TIn>(v2),
+                                   widen<TAcc, TIn>(v3));
                     }
                     for(; i < iHi; i += TY)
-                        acc0 = Op<TAcc, OP>::combine(acc0, widen<TAcc, TIn>(col[i * s0]));
+                        accum.add1(widen<TAcc, TIn>(col[i * s0]));
                 }
             }
-            TAcc acc = Op<TAcc, OP>::combine(Op<TAcc, OP>::combine(acc0, acc1), Op<TAcc, OP>::combine(acc2, acc3));
+            using Top          = typename Accum<TAcc, OP>::Top;
+            Top* smem          = (Top*)smemRaw;
+            Top  acc           = accum.result();
             smem[ty * TX + tx] = acc;
             __syncthreads();
             if(ty == 0 && ok)
             {
                 for(int y = 1; y < TY; y++)
-                    acc = Op<TAcc, OP>::combine(acc, smem[y * TX + tx]);
+                    acc = Op<Top, OP>::combine(acc, smem[y * TX + tx]);
                 if(a.split > 1)
-                    partial[int64_t(blockIdx.y) * a.nOut + o] = acc;
+                    partial[int64_t(blockIdx.y) * a.nOut + o] = TAcc(acc);
                 else
-                    epilogue<TIn, TAcc>(acc, alpha, beta, C, D, offD);
+                    epilogue<TIn, TAcc>(TAcc(acc), alpha, beta, C, D, offD);
             }
         }
 
@@ -364,7 +411,7 @@ namespace htb
             red_gen_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
                            TAcc alpha, TAcc beta)
         {
-            __shared__ TAcc smem[8];
+            __shared__ double smem[8];
             constexpr int   perBlock = 256 / G;
             const int       sub = threadIdx.x / G, lane = threadIdx.x % G;
             const int64_t   o = int64_t(blockIdx.x) * perBlock + sub;
@@ -378,7 +425,8 @@ namespace htb
             }
             int64_t offA, offD;
             keptOffsets(a, o, offA, offD);
-            TAcc acc = Op<TAcc, OP>::identity();
+            Accum<TAcc, OP> accum;
+            accum.init();
             for(int64_t r = lo + lane; r < hi; r += G)
             {
                 int64_t rem = r, off = 0;
@@ -388,15 +436,16 @@ namespace htb
                     rem /= a.rext[d];
                     off += c * a.rsA[d];
                 }
-                acc = Op<TAcc, OP>::combine(acc, widen<TAcc, TIn>(A[offA + off]));
+                accum.add1(widen<TAcc, TIn>(A[offA + off]));
             }
-            acc = groupReduce<TAcc, OP, G>(acc, smem);
+            using Top = typename Accum<TAcc, OP>::Top;
+            Top acc   = groupReduce<Top, OP, G>(accum.result(), (Top*)smem);
             if(lane == 0 && o < a.nOut)
             {
                 if(a.split > 1)
-                    partial[int64_t(blockIdx.y) * a.nOut + o] = acc;
+                    partial[int64_t(blockIdx.y) * a.nOut + o] = TAcc(acc);
                 else
-                    epilogue<TIn, TAcc>(acc, alpha, beta, C, D, offD);
+                    epilogue<TIn, TAcc>(TAcc(acc), alpha, beta, C, D, offD);
             }
         }
 
@@ -409,12 +458,13 @@ namespace htb
             const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
             if(o >= a.nOut)
                 return;
-            TAcc acc = Op<TAcc, OP>::identity();
+            Accum<TAcc, OP> accum;
+            accum.init();
             for(int s = 0; s < a.split; s++)
-                acc = Op<TAcc, OP>::combine(acc, partial[int64_t(s) * a.nOut + o]);
+                accum.add1(partial[int64_t(s) * a.nOut + o]);
             int64_t offA, offD;
             keptOffsets(a, o, offA, offD);
-            epilogue<TIn, TAcc>(acc, alpha, beta, C, D, offD);
+            epilogue<TIn, TAcc>(TAcc(accum.result()), alpha, beta, C, D, offD);
         }
 
         template <typename TIn, typename TAcc, int OP>

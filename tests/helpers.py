@@ -71,8 +71,10 @@ def run_permutation(ht, h, lensA, modeA, modeB, typeA=orc.F32, typeB=None, alpha
 
 
 def run_reduction(ht, h, lensA, modeA, modeD, dt=orc.F32, compute=None, op=orc.OP_ADD, alpha=1.0, beta=0.0,
-                  stridesA=None, stridesD=None, alias=False, seeds=SEED_REDUCTION, A=None, use_workspace=True):
-    """modeD lists the kept modes; extents of D follow A's order (positional contract)."""
+                  stridesA=None, stridesD=None, alias=False, seeds=SEED_REDUCTION, A=None, use_workspace=True,
+                  want_exact=False):
+    """modeD lists the kept modes; extents of D follow A's order (positional contract).
+    want_exact adds a third result: the oracle run on the same values widened to fp64."""
     import torch
 
     compute = compute if compute is not None else (orc.COMPUTE_64F if dt == orc.F64 else orc.COMPUTE_32F)
@@ -99,7 +101,26 @@ def run_reduction(ht, h, lensA, modeA, modeD, dt=orc.F32, compute=None, op=orc.O
     got = to_host(D_d, dt)
     exp = C.copy() if alias else np.zeros(nD, dtype=orc.np_dtype(dt))
     orc.reduction(alpha, A, lensA, sA, modeA, dt, beta, None if alias else C, exp, lensD, sD, kept, dt, op, compute)
-    return got, exp
+    if not want_exact:
+        return got, exp
+    A64, C64 = orc.to_f64(A, dt), orc.to_f64(C, dt)
+    exact = C64.copy() if alias else np.zeros(nD, dtype=np.float64)
+    orc.reduction(alpha, A64, lensA, sA, modeA, orc.F64, beta, None if alias else C64, exact, lensD, sD, kept,
+                  orc.F64, op, orc.COMPUTE_64F)
+    return got, exp, exact
+
+
+def check_f32(got, exp, exact, terms):
+    """fp32 results. Against the reference's CPU algorithm (sequential fp32 accumulation) the
+    reference's own bound terms*eps (reduction_test.cpp:518-543; 2*K*eps for contraction,
+    contraction_test.cpp:882-905) holds; two fp32 summation orders of thousands of terms differ by
+    more than 1e-5 under the metric, so the 1e-5 bound is checked against the same operation
+    evaluated by the oracle in fp64 on the same values, i.e. against the exact result."""
+    e1 = rel_error(got, exp, orc.F32)
+    assert 0 <= e1 < max(terms * float(np.finfo(np.float32).eps), 1e-6), ("vs reference algorithm", e1)
+    e2 = rel_error(got.astype(np.float64), exact, orc.F64)
+    assert 0 <= e2 < 1e-5, ("vs exact", e2)
+    return e1, e2
 
 
 def run_contraction(ht, h, extent, modeA, modeB, modeD, typeAB=orc.F32, typeD=None, compute=None, alpha=1.0,

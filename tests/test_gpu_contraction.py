@@ -9,7 +9,7 @@ test/01_contraction/configs/mode_test_params.yaml:15-59."""
 import numpy as np
 import pytest
 
-from helpers import rel_error, run_contraction
+from helpers import check_f32, rel_error, run_contraction
 from oracle import binding as orc
 
 pytestmark = pytest.mark.gpu
@@ -24,6 +24,25 @@ def env():
 
 def ext_of(modes, lens):
     return {m: l for ms, ls in zip(modes, lens) for m, l in zip(ms, ls)}
+
+
+
+def exact_f64(ext, modeA, modeB, modeD, dt, alpha, beta, first_fastest, fill="uniform"):
+    """The same seeded problem evaluated by the oracle with fp64 data and accumulation."""
+    from helpers import SEED_CONTRACTION as S
+
+    lA, lB, lD = ([ext[m] for m in ms] for ms in (modeA, modeB, modeD))
+    sA, sB, sD = (orc.packed_strides(l, first_fastest) for l in (lA, lB, lD))
+    n = [int(np.prod(l)) for l in (lA, lB, lD)]
+    gen = (lambda k, d, s: orc.fill_uniform(k, d, s)) if fill == "uniform" else (
+        lambda k, d, s: orc.fill_normal(k, d, s, 0.5))
+    A = orc.to_f64(gen(n[0], dt, S[0]), dt)
+    B = orc.to_f64(gen(n[1], dt, S[1]), dt)
+    C = orc.to_f64(orc.fill_uniform(n[2], dt, S[2]), dt)
+    D = np.full(n[2], np.nan)
+    orc.contraction(alpha, A, lA, sA, modeA, orc.F64, B, lB, sB, modeB, orc.F64, beta, C, D, lD, sD, modeD, orc.F64,
+                    orc.COMPUTE_64F)
+    return D
 
 
 # (lengths of A, B, D) and (modes of A, B, D)
@@ -49,10 +68,15 @@ def test_mode_orders(env, case, dt):
     ht, h = env
     lens, modes = MODE_CASES[case]
     ext = ext_of(modes, lens)
+    K = int(np.prod([ext[m] for m in modes[0] if m in modes[1]]))
     for ab in ((1.0, 2.0), (1.0, 0.0), (0.0, 2.0)):
         got, exp, td = run_contraction(ht, h, ext, modes[0], modes[1], modes[2], typeAB=dt, alpha=ab[0], beta=ab[1])
-        err = rel_error(got, exp, td)
-        assert 0 <= err < 1e-5, (case, dt, ab, err, ht.last_kernel_name())
+        if dt == orc.F32:
+            exact = exact_f64(ext, modes[0], modes[1], modes[2], dt, ab[0], ab[1], False)
+            check_f32(got, exp, exact, 2 * K)
+        else:
+            err = rel_error(got, exp, td)
+            assert 0 <= err < 1e-5, (case, dt, ab, err, ht.last_kernel_name())
 
 
 @pytest.mark.parametrize("dt,ct", [(orc.F32, orc.COMPUTE_32F), (orc.F32, orc.COMPUTE_16F), (orc.F32, orc.COMPUTE_16BF),
@@ -86,15 +110,19 @@ def test_half_inputs_small(env, dt, out32):
 
 
 def test_config1_fp32_bilinear(env):
-    """D[m0,m1,n0,n1] = 1.0*A[m0,m1,k0,k1]*B[n0,n1,k0,k1] + 1.0*C, all extents 24, first mode fastest."""
+    """D[m0,m1,n0,n1] = 1.0*A[m0,m1,k0,k1]*B[n0,n1,k0,k1] + 1.0*C, all extents 24, first mode fastest.
+
+    Two statements. Against the reference's CPU algorithm (fp32 accumulation in its own k order) the
+    reference's own bound 2*K*eps holds; two fp32 summation orders of 576 terms differ by more than
+    1e-5 under the metric, so the 1e-5 bound is checked against the same contraction evaluated by
+    the oracle in fp64 (inputs widened exactly), i.e. against the exact product."""
     ht, h = env
     m0, m1, n0, n1, k0, k1 = range(6)
     ext = {m: 24 for m in range(6)}
     got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F32,
                                    alpha=1.0, beta=1.0, first_fastest=True)
-    err = rel_error(got, exp, td)
-    assert 0 <= err < 1e-5, err
-    assert err < 2 * 576 * np.finfo(np.float32).eps  # the reference's own bound
+    exact = exact_f64(ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], orc.F32, 1.0, 1.0, True)
+    check_f32(got, exp, exact, 2 * 576)
 
 
 def test_config5_scaled_down(env):
@@ -176,3 +204,39 @@ def test_argument_errors(env):
     with pytest.raises(ht.HiptensorError) as e:
         h.contraction(plan, 1.0, None, x, 0.0, x, x)
     assert e.value.status == ht.STATUS_INVALID_VALUE
+
+
+@pytest.mark.parametrize("dt", [orc.F16, orc.BF16])
+def test_tensor_core_path_gathered_tiles(env, dt):
+    """K-major operands whose tile rows span two modes (power-of-two inner mode, ragged outer mode),
+    K not a multiple of the 64-wide K block, interleaved output modes: the TMA boxes gather the rows."""
+    ht, h = env
+    m0, m1, n0, n1, k0 = range(5)
+    ext = {m0: 12, m1: 16, n0: 32, n1: 6, k0: 192 + 8}
+    for out32 in (True, False):
+        got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0], [n1, n0, k0], [m1, n1, m0, n0], typeAB=dt,
+                                       typeD=orc.F32 if out32 else dt, alpha=1.5, beta=0.5, fill="normal")
+        assert ht.last_kernel_name() == "contraction_tcgen05"
+        err = rel_error(got, exp, td)
+        tol = 1e-4 if out32 else (2 * 2.0 ** -10 if dt == orc.F16 else 2 * 2.0 ** -7)
+        assert 0 <= err < tol, (dt, out32, err)
+
+
+@pytest.mark.parametrize("shape", [(256, 320, 96), (128, 64, 64), (384, 1000, 520)])
+def test_tensor_core_path_plain_matrices(env, shape):
+    ht, h = env
+    M, N, K = shape
+    m, n, k = 0, 1, 2
+    ext = {m: M, n: N, k: K}
+    for with_c in (True, False):
+        got, exp, td = run_contraction(ht, h, ext, [m, k], [n, k], [m, n], typeAB=orc.F16, typeD=orc.F16, alpha=1.0,
+                                       beta=2.0 if with_c else 0.0, with_c=with_c, fill="normal")
+        assert ht.last_kernel_name() == "contraction_tcgen05"
+        err = rel_error(got, exp, td)
+        assert 0 <= err < 2 * 2.0 ** -10, (shape, with_c, err)
+    # M-major output: the planner exchanges the operands
+    got, exp, td = run_contraction(ht, h, ext, [m, k], [n, k], [n, m], typeAB=orc.BF16, typeD=orc.F32, alpha=1.0,
+                                   beta=1.0, fill="normal")
+    if N >= 128:  # after the exchange the 128-row tile runs along the original N
+        assert ht.last_kernel_name() == "contraction_tcgen05"
+    assert 0 <= rel_error(got, exp, td) < 1e-4

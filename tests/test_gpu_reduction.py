@@ -1,7 +1,8 @@
 """GPU parity: hiptensorReduction through the C ABI against the CPU oracle.
-Tolerance: the reference's metric max|d-h|/(|d|+|h|+1) (test/device/common.hpp:122-151) below
-1e-5 for f32/f64 accumulation (stricter than the reference's reduce_len*eps,
-test/03_reduction/reduction_test.cpp:518-543) and 2*2^-10 / 2*2^-7 for f16 / bf16 outputs."""
+Metric: the reference's max|d-h|/(|d|+|h|+1) (test/device/common.hpp:122-151). Short reductions are
+held to 1e-5 against the oracle directly; long fp32 ADD reductions are held to the reference's own
+bound reduce_len*eps (test/03_reduction/reduction_test.cpp:518-543) against the oracle and to 1e-5
+against the exact (fp64) result, see helpers.check_f32. f16 / bf16 outputs: 2*2^-10 / 2*2^-7."""
 import itertools
 import json
 import os
@@ -9,7 +10,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import rel_error, run_reduction
+from helpers import check_f32, rel_error, run_reduction
 from oracle import binding as orc
 
 pytestmark = pytest.mark.gpu
@@ -67,10 +68,11 @@ def test_layouts_and_beta(env, first_fastest, kept):
     sA = orc.packed_strides(lens, first_fastest)
     lensD = [lens[m] for m in kept]
     sD = orc.packed_strides(lensD, first_fastest)
+    terms = int(np.prod(lens)) // int(np.prod(lensD))
     for alias in (False, True):
-        got, exp = run_reduction(ht, h, lens, modeA, kept, alpha=1.2, beta=2.1, stridesA=sA, stridesD=sD, alias=alias)
-        err = rel_error(got, exp, orc.F32)
-        assert 0 <= err < 1e-5, (first_fastest, kept, alias, err, ht.last_kernel_name())
+        got, exp, exact = run_reduction(ht, h, lens, modeA, kept, alpha=1.2, beta=2.1, stridesA=sA, stridesD=sD,
+                                        alias=alias, want_exact=True)
+        check_f32(got, exp, exact, terms)
 
 
 def test_permuted_output_strides(env):
@@ -114,14 +116,15 @@ def test_few_outputs_long_reduction_two_pass(env):
     lens, modeA = [3, 512, 1024], [0, 1, 2]
     for kept in ([0], []):
         for op in (orc.OP_ADD, orc.OP_MAX):
-            got, exp = run_reduction(ht, h, lens, modeA, kept, op=op, alpha=2.0, beta=0.5, use_workspace=True)
-            name = ht.last_kernel_name()
-            err = rel_error(got, exp, orc.F32)
-            assert 0 <= err < 1e-5, (kept, op, err, name)
-            assert name == "red_finalize"
-            got2, exp2 = run_reduction(ht, h, lens, modeA, kept, op=op, alpha=2.0, beta=0.5, use_workspace=False)
-            assert 0 <= rel_error(got2, exp2, orc.F32) < 1e-5
+            terms = 512 * 1024 * (1 if kept else 3)
+            got, exp, exact = run_reduction(ht, h, lens, modeA, kept, op=op, alpha=2.0, beta=0.5, use_workspace=True,
+                                            want_exact=True)
+            assert ht.last_kernel_name() == "red_finalize"
+            check_f32(got, exp, exact, terms)
+            got2, exp2, exact2 = run_reduction(ht, h, lens, modeA, kept, op=op, alpha=2.0, beta=0.5,
+                                               use_workspace=False, want_exact=True)
             assert ht.last_kernel_name() != "red_finalize"
+            check_f32(got2, exp2, exact2, terms)
 
 
 def test_rejects_mismatched_descriptors(env):
@@ -168,7 +171,11 @@ def test_config3_full_size(env, first_fastest):
         exp = np.zeros(4096 * 64, dtype=np.float32)
         orc.reduction(1.0, A, lens, sA, modeA, orc.F32, 0.5, C, exp, lens[:2], sD, kept, orc.F32, op,
                       orc.COMPUTE_32F)
-        err = rel_error(to_host(D_d, orc.F32), exp, orc.F32)
-        assert 0 <= err < 1e-5, (op, first_fastest, err)
+        got = to_host(D_d, orc.F32)
         if op == orc.OP_MAX:  # max is order independent: bit-exact
-            assert np.array_equal(to_host(D_d, orc.F32), exp)
+            assert np.array_equal(got, exp)
+        else:
+            exact = np.zeros(4096 * 64, dtype=np.float64)
+            orc.reduction(1.0, A.astype(np.float64), lens, sA, modeA, orc.F64, 0.5, C.astype(np.float64), exact,
+                          lens[:2], sD, kept, orc.F64, op, orc.COMPUTE_64F)
+            check_f32(got, exp, exact, 2048)
