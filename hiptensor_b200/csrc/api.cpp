@@ -316,7 +316,7 @@ hiptensorStatus_t hiptensorPermutation(const hiptensorHandle_t* handle, const vo
     float alphaF = (typeScalar == HIP_R_32F) ? *(const float*)alpha : __half2float(*(const __half*)alpha);
     HTB_LOG_HEUR(fn, "%s", describe(plan).c_str());
     cudaError_t e = launchPermutation(plan, int(descA->mType), int(descB->mType), A, B, alphaF, int(descA->mUnaryOp),
-                                      int(descB->mUnaryOp), st->deviceStatus, stream);
+                                      int(descB->mUnaryOp), st->smCount, st->deviceStatus, stream);
     if(e != cudaSuccess)
     {
         HTB_LOG_ERROR(fn, "kernel launch failed: %s (%s)", cudaGetErrorString(e),

@@ -18,7 +18,7 @@ namespace htb
     PFN_encodeTiled tensorMapEncoder();
 
     cudaError_t launchPermutation(const PermPlan& plan, int typeA, int typeB, const void* A, void* B, float alpha,
-                                  int opA, int opB, int* deviceStatus, cudaStream_t stream);
+                                  int opA, int opB, int smCount, int* deviceStatus, cudaStream_t stream);
 
     // alpha/beta already widened to double; C may alias D or be null (beta then ignored).
     // workspace is used only when plan.split > 1.

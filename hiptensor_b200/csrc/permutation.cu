@@ -15,6 +15,9 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "kernels.hpp"
 
 namespace htb
@@ -78,27 +81,64 @@ namespace htb
         }
 
         // ------------------------------------------------------------ copy kernel
-        // grid.x covers rows (all folded modes but the first); blockDim = (TX, 256/TX).
-        template <typename TI, typename TO>
-        __global__ void __launch_bounds__(256) perm_copy_kernel(const TI* __restrict__ A, TO* __restrict__ B,
-                                                                PermArgs a, int64_t rows)
+        // A's and B's contiguous folded mode coincide (mode 0): rows of ext[0] elements move
+        // unchanged, only the outer modes are permuted. A block copies a tile of T0 elements of
+        // mode 0 by T1 rows of mode 1 with 16-byte accesses (VEC elements) and four independent
+        // accesses per thread; the outer modes are decomposed once per block.
+        template <typename T, int N>
+        struct alignas(sizeof(T) * N) VecT
         {
-            const int     tx  = threadIdx.x;
-            const int64_t row = int64_t(blockIdx.x) * blockDim.y + threadIdx.y;
-            if(row >= rows)
-                return;
-            int64_t rem = row, offA = 0, offB = 0;
-            for(int d = 1; d < a.ndim; d++)
+            T v[N];
+        };
+
+        template <typename TI, typename TO, int VEC>
+        __global__ void __launch_bounds__(256)
+            perm_copy_kernel(const TI* __restrict__ A, TO* __restrict__ B, PermArgs a, int chunks0Log2, int tiles0,
+                             int tiles1, int64_t flatTotal)
+        {
+            const int chunks0 = 1 << chunks0Log2; // 16-byte chunks of mode 0 per tile
+            const int T1      = 1024 >> chunks0Log2; // rows of mode 1 per tile
+            int64_t   bid     = blockIdx.x;
+            const int t0      = int(bid % tiles0);
+            bid /= tiles0;
+            const int t1 = int(bid % tiles1);
+            bid /= tiles1;
+            int64_t offA = 0, offB = 0;
+            for(int d = 2; d < a.ndim; d++)
             {
-                int64_t c = rem % a.ext[d];
-                rem /= a.ext[d];
+                int64_t c = bid % a.ext[d];
+                bid /= a.ext[d];
                 offA += c * a.sA[d];
                 offB += c * a.sB[d];
             }
-            for(int64_t i = tx; i < a.ext[0]; i += blockDim.x)
+            const int64_t ext1 = (a.ndim > 1) ? a.ext[1] : 1;
+            const int64_t sA1 = (a.ndim > 1) ? a.sA[1] : 0, sB1 = (a.ndim > 1) ? a.sB[1] : 0;
+            VecT<TI, VEC> v[4];
+            bool          ok[4];
+#pragma unroll
+            for(int k = 0; k < 4; k++)
             {
-                TI v          = A[offA + i];
-                B[offB + i] = convertOut<TO, TI>(Elem<TI>::apply(v, a.alpha, a.opA, a.opB));
+                const int     item = threadIdx.x + 256 * k;
+                const int64_t i0   = (int64_t(t0) * chunks0 + (item & (chunks0 - 1))) * VEC;
+                const int64_t i1   = int64_t(t1) * T1 + (item >> chunks0Log2);
+                ok[k]              = (i0 < a.ext[0]) && (i1 < ext1) && (flatTotal == 0 || i1 * sA1 + i0 < flatTotal);
+                if(ok[k])
+                    v[k] = *(const VecT<TI, VEC>*)(A + offA + i1 * sA1 + i0);
+            }
+#pragma unroll
+            for(int k = 0; k < 4; k++)
+            {
+                const int     item = threadIdx.x + 256 * k;
+                const int64_t i0   = (int64_t(t0) * chunks0 + (item & (chunks0 - 1))) * VEC;
+                const int64_t i1   = int64_t(t1) * T1 + (item >> chunks0Log2);
+                if(ok[k])
+                {
+                    VecT<TO, VEC> w;
+#pragma unroll
+                    for(int e = 0; e < VEC; e++)
+                        w.v[e] = convertOut<TO, TI>(Elem<TI>::apply(v[k].v[e], a.alpha, a.opA, a.opB));
+                    *(VecT<TO, VEC>*)(B + offB + i1 * sB1 + i0) = w;
+                }
             }
         }
 
@@ -160,20 +200,29 @@ namespace htb
         }
 
         // ------------------------------------------------------------ TMA kernel (f32)
-        // Tile = (32*NP) x (32*NQ) elements of the (p, q) plane. Input boxes: NP boxes of
-        // [32*NQ rows of q][32 floats of p]; output boxes: NQ boxes of [32*NP rows of p]
-        // [32 floats of q]. Rows are 128 bytes, swizzled by TMA (16-byte chunk index XOR
-        // row index mod 8), buffers 1024-byte aligned.
+        // Tile = (32*NP) x (32*NQ) elements of the (p, q) plane, p = A's fastest folded mode,
+        // q = B's fastest folded mode. Input stage: NP boxes of [32*NQ rows of q][32 floats of p];
+        // output stage: NQ boxes of [32*NP rows of p][32 floats of q]. Rows are 128 bytes, swizzled
+        // by TMA (16-byte chunk index XOR row index mod 8), stages 1024-byte aligned.
+        //
+        // Persistent CTA: a producer warp keeps the input stages' tile loads in flight (full/empty
+        // mbarriers per stage); 64*NP*NQ consumer threads transpose 4x4 blocks in registers and
+        // hand finished tiles to TMA stores that drain asynchronously from kOutStages buffers.
+        constexpr int kMaxInStages = 8, kOutStages = 2;
+
         struct PermTmaArgs
         {
-            int     ndim, q;
-            int     posP_B, posQ_B; // position of folded modes 0 and q in B's tensor map
-            int     mapPosB[kMaxGroup]; // folded mode -> position in B's tensor map
-            int64_t ext[kMaxGroup];
-            float   alpha;
-            int     opA, opB;
-            int     tilesP, tilesQ;
-            int*    status;
+            int       ndim, q;
+            int       posP_B, posQ_B; // position of folded modes 0 and q in B's tensor map
+            int       mapPosB[kMaxGroup]; // folded mode -> position in B's tensor map
+            uint32_t  ext[kMaxGroup];
+            float     alpha;
+            int       opA, opB;
+            uint32_t  tilesP, tilesQ;
+            int       inStages; // input stages in flight per CTA
+            int       wide; // 1: modes p and q are split 32 x (extent/32) in the tensor maps (see launchTma)
+            uint32_t  numTiles;
+            int*      status;
         };
 
         __device__ __forceinline__ uint32_t smemAddr(const void* p)
@@ -181,169 +230,309 @@ namespace htb
             return uint32_t(__cvta_generic_to_shared(p));
         }
 
-        template <int NP, int NQ>
-        __global__ void __launch_bounds__(64 * NP * NQ)
-            perm_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                            PermTmaArgs a)
+        __device__ __forceinline__ bool mbarWaitBounded(uint32_t bar, uint32_t parity, volatile int* abortFlag)
         {
-            constexpr int TP = 32 * NP, TQ = 32 * NQ;
-            extern __shared__ unsigned char smemRaw[];
-            // 1024-byte alignment for the 128B swizzle pattern
-            unsigned char* base = (unsigned char*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
-            float*         in   = (float*)base; // NP boxes * TQ rows * 32 floats
-            float*         outb = in + NP * TQ * 32; // NQ boxes * TP rows * 32 floats
-            __shared__ __align__(8) unsigned long long bar;
+            const long long t0 = clock64();
+            for(;;)
+            {
+                uint32_t done;
+                asm volatile("{\n\t.reg .pred p;\n\t"
+                             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                             "selp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(done)
+                             : "r"(bar), "r"(parity)
+                             : "memory");
+                if(done)
+                    return true;
+                if(*abortFlag)
+                    return false;
+                if(clock64() - t0 > 4000000000ll)
+                {
+                    *abortFlag = 1;
+                    return false;
+                }
+            }
+        }
 
-            int64_t   bid = blockIdx.x;
-            const int tp  = int(bid % a.tilesP);
-            bid /= a.tilesP;
-            const int tq = int(bid % a.tilesQ);
-            bid /= a.tilesQ;
-            int coordA[5] = {0, 0, 0, 0, 0};
-            int coordB[5] = {0, 0, 0, 0, 0};
+        __device__ __forceinline__ void tmaLoadN(int ndim, uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                 const int* c)
+        {
+            if(ndim == 2)
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+                             "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1])
+                             : "memory");
+            else if(ndim == 3)
+                asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+                             "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2])
+                             : "memory");
+            else if(ndim == 4)
+                asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+                             "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3])
+                             : "memory");
+            else
+                asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes "
+                             "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4])
+                             : "memory");
+        }
+
+        __device__ __forceinline__ void tmaStoreN(int ndim, const CUtensorMap* map, uint32_t src, const int* c)
+        {
+            if(ndim == 2)
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                             "r"(src), "r"(c[0]), "r"(c[1])
+                             : "memory");
+            else if(ndim == 3)
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map),
+                             "r"(src), "r"(c[0]), "r"(c[1]), "r"(c[2])
+                             : "memory");
+            else if(ndim == 4)
+                asm volatile(
+                    "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+                    "r"(src), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3])
+                    : "memory");
+            else
+                asm volatile(
+                    "cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];" ::"l"(map),
+                    "r"(src), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4])
+                    : "memory");
+        }
+
+        // tile index -> TMA coordinates of the tile's origin in A's map and in B's map.
+        // Narrow maps: one dimension per folded mode (A's order / ascending stride in B).
+        // Wide maps: the contiguous mode of each tensor is split into (32, extent/32), which
+        // shifts every other dimension up by one.
+        __device__ __forceinline__ void permTileCoords(const PermTmaArgs& a, uint32_t tile, int NP, int NQ, int* cA,
+                                                       int* cB)
+        {
+            const int tp = int(tile % a.tilesP);
+            tile /= a.tilesP;
+            const int tq = int(tile % a.tilesQ);
+            tile /= a.tilesQ;
+            const int sh = a.wide ? 1 : 0;
+            for(int d = 0; d < 5; d++)
+            {
+                cA[d] = 0;
+                cB[d] = 0;
+            }
             for(int d = 1; d < a.ndim; d++)
             {
                 if(d == a.q)
                     continue;
-                int c = int(bid % a.ext[d]);
-                bid /= a.ext[d];
-                coordA[d]            = c;
-                coordB[a.mapPosB[d]] = c;
+                const int c = int(tile % a.ext[d]);
+                tile /= a.ext[d];
+                cA[d + sh]            = c;
+                cB[a.mapPosB[d] + sh] = c;
             }
-            const int p0 = tp * TP, q0 = tq * TQ;
-
-            const uint32_t barAddr = smemAddr(&bar);
-            if(threadIdx.x == 0)
+            if(a.wide)
             {
-                asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(barAddr));
-                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                cA[1]            = tp * NP; // p: 128-byte group index
+                cA[a.q + 1]      = tq * NQ * 32; // q: rows of the input tile
+                cB[1]            = tq * NQ; // q: 128-byte group index
+                cB[a.posP_B + 1] = tp * NP * 32; // p: rows of the output tile
             }
-            __syncthreads();
-            if(threadIdx.x == 0)
+            else
             {
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(barAddr),
-                             "r"(uint32_t(NP * TQ * 128))
-                             : "memory");
-#pragma unroll
-                for(int i = 0; i < NP; i++)
-                {
-                    coordA[0]   = p0 + 32 * i;
-                    coordA[a.q] = q0;
-                    const uint32_t dst = smemAddr(in + i * TQ * 32);
-                    if(a.ndim == 2)
-                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-                                     "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-                                     "l"(&mapA), "r"(barAddr), "r"(coordA[0]), "r"(coordA[1])
-                                     : "memory");
-                    else if(a.ndim == 3)
-                        asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
-                                     "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
-                                     "l"(&mapA), "r"(barAddr), "r"(coordA[0]), "r"(coordA[1]), "r"(coordA[2])
-                                     : "memory");
-                    else if(a.ndim == 4)
-                        asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
-                                     "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
-                                     "l"(&mapA), "r"(barAddr), "r"(coordA[0]), "r"(coordA[1]), "r"(coordA[2]),
-                                     "r"(coordA[3])
-                                     : "memory");
-                    else
-                        asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes "
-                                     "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
-                                     "l"(&mapA), "r"(barAddr), "r"(coordA[0]), "r"(coordA[1]), "r"(coordA[2]),
-                                     "r"(coordA[3]), "r"(coordA[4])
-                                     : "memory");
-                }
-            }
-            // bounded wait for the boxes to land
-            {
-                uint32_t done = 0;
-                for(int spin = 0; spin < (1 << 22) && !done; spin++)
-                {
-                    asm volatile("{\n\t.reg .pred p;\n\t"
-                                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                                 "selp.u32 %0, 1, 0, p;\n\t}"
-                                 : "=r"(done)
-                                 : "r"(barAddr), "r"(0u)
-                                 : "memory");
-                }
-                if(!done)
-                {
-                    if(a.status)
-                        atomicExch(a.status, 1);
-                    return; // no store is issued; the loads complete on their own
-                }
-            }
-
-            // 4x4 register transpose; 64 threads per 32x32 sub-tile
-            const int t   = threadIdx.x;
-            const int sub = t >> 6; // sub-tile index: pi = sub % NP, qj = sub / NP
-            const int pi = sub % NP, qj = sub / NP;
-            const int e = t & 7, kk = (t >> 3) & 7;
-            const int c = e, g = (e + kk) & 7;
-            float4    v[4];
-            const unsigned char* inBox = (const unsigned char*)(in + pi * TQ * 32);
-#pragma unroll
-            for(int i = 0; i < 4; i++)
-            {
-                const int r = 32 * qj + 4 * g + i;
-                v[i]        = *(const float4*)(inBox + r * 128 + ((c ^ (r & 7)) << 4));
-            }
-            unsigned char* outBox = (unsigned char*)(outb + qj * TP * 32);
-#pragma unroll
-            for(int j = 0; j < 4; j++)
-            {
-                float4 w;
-                w.x = Elem<float>::apply(((const float*)&v[0])[j], a.alpha, a.opA, a.opB);
-                w.y = Elem<float>::apply(((const float*)&v[1])[j], a.alpha, a.opA, a.opB);
-                w.z = Elem<float>::apply(((const float*)&v[2])[j], a.alpha, a.opA, a.opB);
-                w.w = Elem<float>::apply(((const float*)&v[3])[j], a.alpha, a.opA, a.opB);
-                const int rr = 32 * pi + 4 * c + j;
-                *(float4*)(outBox + rr * 128 + ((g ^ (rr & 7)) << 4)) = w;
-            }
-            // make the generic-proxy writes visible to the async proxy, then store
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncthreads();
-            if(threadIdx.x == 0)
-            {
-#pragma unroll
-                for(int j = 0; j < NQ; j++)
-                {
-                    coordB[a.posQ_B] = q0 + 32 * j;
-                    coordB[a.posP_B] = p0;
-                    const uint32_t src = smemAddr(outb + j * TP * 32);
-                    if(a.ndim == 2)
-                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                                         &mapB),
-                                     "r"(src), "r"(coordB[0]), "r"(coordB[1])
-                                     : "memory");
-                    else if(a.ndim == 3)
-                        asm volatile(
-                            "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
-                                &mapB),
-                            "r"(src), "r"(coordB[0]), "r"(coordB[1]), "r"(coordB[2])
-                            : "memory");
-                    else if(a.ndim == 4)
-                        asm volatile(
-                            "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
-                                &mapB),
-                            "r"(src), "r"(coordB[0]), "r"(coordB[1]), "r"(coordB[2]), "r"(coordB[3])
-                            : "memory");
-                    else
-                        asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, "
-                                     "%6}], [%1];" ::"l"(&mapB),
-                                     "r"(src), "r"(coordB[0]), "r"(coordB[1]), "r"(coordB[2]), "r"(coordB[3]),
-                                     "r"(coordB[4])
-                                     : "memory");
-                }
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                // shared memory must stay valid until the stores have read it
-                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                cA[0]        = tp * NP * 32;
+                cA[a.q]      = tq * NQ * 32;
+                cB[a.posQ_B] = tq * NQ * 32;
+                cB[a.posP_B] = tp * NP * 32;
             }
         }
 
         template <int NP, int NQ>
+        __global__ void __launch_bounds__(64 * NP * NQ + 32)
+            perm_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                            PermTmaArgs a)
+        {
+            constexpr int TP = 32 * NP, TQ = 32 * NQ;
+            constexpr int kConsumers = 64 * NP * NQ;
+            constexpr int kStageFloats = TP * TQ;
+            extern __shared__ unsigned char smemRaw[];
+            float* in   = (float*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
+            float* outb = in + a.inStages * kStageFloats;
+            __shared__ __align__(8) unsigned long long fullBar[kMaxInStages], emptyBar[kMaxInStages];
+            __shared__ int abortFlag;
+            __shared__ int coordB[kMaxInStages][5], coordOut[kOutStages][5];
+
+            if(threadIdx.x == 0)
+            {
+                abortFlag = 0;
+                for(int s = 0; s < a.inStages; s++)
+                {
+                    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smemAddr(&fullBar[s])));
+                    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(&emptyBar[s])),
+                                 "r"(kConsumers / 32));
+                }
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            }
+            __syncthreads();
+            volatile int* abortP = &abortFlag;
+
+            if(threadIdx.x >= kConsumers)
+            {
+                // ---------------------------------------------------------------- producer warp
+                if(threadIdx.x == kConsumers)
+                {
+                    int      stage = 0;
+                    uint32_t phase = 0;
+                    for(uint32_t tile = blockIdx.x; tile < a.numTiles; tile += gridDim.x)
+                    {
+                        int cA[5], cB[5];
+                        permTileCoords(a, tile, NP, NQ, cA, cB);
+                        if(!mbarWaitBounded(smemAddr(&emptyBar[stage]), phase ^ 1, abortP))
+                            break;
+                        // the storing thread reads the tile's B coordinates from shared memory
+#pragma unroll
+                        for(int d = 0; d < 5; d++)
+                            coordB[stage][d] = cB[d];
+                        const uint32_t bar = smemAddr(&fullBar[stage]);
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                                     "r"(uint32_t(kStageFloats * 4))
+                                     : "memory");
+                        if(a.wide)
+                        {
+                            // one box [32][NP][..][TQ]: the NP 128-byte pieces of a row arrive together
+                            tmaLoadN(a.ndim + 1, smemAddr(in + stage * kStageFloats), &mapA, bar, cA);
+                        }
+                        else
+                        {
+                            const int p0 = cA[0];
+#pragma unroll
+                            for(int i = 0; i < NP; i++)
+                            {
+                                cA[0] = p0 + 32 * i;
+                                tmaLoadN(a.ndim, smemAddr(in + stage * kStageFloats + i * TQ * 32), &mapA, bar, cA);
+                            }
+                        }
+                        if(++stage == a.inStages)
+                        {
+                            stage = 0;
+                            phase ^= 1;
+                        }
+                    }
+                }
+                return;
+            }
+
+            // -------------------------------------------------------------------- consumers
+            const int t   = threadIdx.x;
+            const int sub = t >> 6; // sub-tile: pi = sub % NP, qj = sub / NP
+            const int pi = sub % NP, qj = sub / NP;
+            const int e = t & 7, kk = (t >> 3) & 7;
+            const int c = e, g = (e + kk) & 7; // diagonal assignment: conflict free on both sides
+            int      stage = 0, ostage = 0;
+            uint32_t phase = 0;
+            for(uint32_t tile = blockIdx.x; tile < a.numTiles; tile += gridDim.x)
+            {
+                // one lane per warp waits for the tile, the warp follows its verdict
+                int ok = 1;
+                if((t & 31) == 0)
+                    ok = mbarWaitBounded(smemAddr(&fullBar[stage]), phase, abortP) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                // the output buffer about to be written must have been read by its last store
+                if(t == 0)
+                    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kOutStages - 1) : "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+                if(!ok || *abortP)
+                    break;
+
+                // the tile's B coordinates move to a slot of the output stage before this input
+                // stage is handed back to the producer
+                if(t == 0)
+                {
+#pragma unroll
+                    for(int d = 0; d < 5; d++)
+                        coordOut[ostage][d] = coordB[stage][d];
+                }
+                // row of (sub-tile pi, tile-local q index ql) in the input stage, and of
+                // (sub-tile qj, tile-local p index pl) in the output stage
+                float4               v[4];
+                const unsigned char* inStage = (const unsigned char*)(in + stage * kStageFloats);
+#pragma unroll
+                for(int i = 0; i < 4; i++)
+                {
+                    const int ql = 32 * qj + 4 * g + i;
+                    const int r  = a.wide ? (pi + NP * ql) : (pi * TQ + ql);
+                    v[i]         = *(const float4*)(inStage + r * 128 + ((c ^ (r & 7)) << 4));
+                }
+                // this warp is done with the input stage
+                __syncwarp();
+                if((t & 31) == 0)
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(&emptyBar[stage])) : "memory");
+
+                unsigned char* outStage = (unsigned char*)(outb + ostage * kStageFloats);
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+                {
+                    float4 w;
+                    w.x = Elem<float>::apply(((const float*)&v[0])[j], a.alpha, a.opA, a.opB);
+                    w.y = Elem<float>::apply(((const float*)&v[1])[j], a.alpha, a.opA, a.opB);
+                    w.z = Elem<float>::apply(((const float*)&v[2])[j], a.alpha, a.opA, a.opB);
+                    w.w = Elem<float>::apply(((const float*)&v[3])[j], a.alpha, a.opA, a.opB);
+                    const int pl = 32 * pi + 4 * c + j;
+                    const int rr = a.wide ? (qj + NQ * pl) : (qj * TP + pl);
+                    *(float4*)(outStage + rr * 128 + ((g ^ (rr & 7)) << 4)) = w;
+                }
+                // generic-proxy writes -> async proxy, then one thread stores the tile
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+                if(t == 0)
+                {
+                    int cB[5];
+#pragma unroll
+                    for(int d = 0; d < 5; d++)
+                        cB[d] = coordOut[ostage][d];
+                    if(a.wide)
+                    {
+                        tmaStoreN(a.ndim + 1, &mapB, smemAddr(outb + ostage * kStageFloats), cB);
+                    }
+                    else
+                    {
+                        const int q0 = cB[a.posQ_B];
+#pragma unroll
+                        for(int j = 0; j < NQ; j++)
+                        {
+                            cB[a.posQ_B] = q0 + 32 * j;
+                            tmaStoreN(a.ndim, &mapB, smemAddr(outb + ostage * kStageFloats + j * TP * 32), cB);
+                        }
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                if(++stage == a.inStages)
+                {
+                    stage = 0;
+                    phase ^= 1;
+                }
+                if(++ostage == kOutStages)
+                    ostage = 0;
+            }
+            if(t == 0)
+            {
+                // shared memory must stay valid until the stores have read it
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                if(abortFlag && a.status)
+                    atomicExch(a.status, 1);
+            }
+        }
+
+        // Launch-time choices of the TMA kernel. Measured on B200 over the rank-4 orders of a
+        // 128^4 fp32 tensor: 64x64 tiles with TWO input stages and two CTAs per SM gave the highest
+        // bandwidth on every order (deeper pipelines or more CTAs per SM lost 5-25%: more tiles in
+        // flight mix more read and write streams in DRAM), see profiles/perm_tma_sweep.md.
+        struct PermTune
+        {
+            int shape     = 22; // NP*10 + NQ
+            int inStages  = 2;
+            int ctasPerSm = 2;
+        };
+
+        template <int NP, int NQ>
         cudaError_t launchTma(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB,
-                              int* status, cudaStream_t stream)
+                              const PermTune& tune, int smCount, int* status, cudaStream_t stream)
         {
             constexpr int TP = 32 * NP, TQ = 32 * NQ;
             PFN_encodeTiled encode = tensorMapEncoder();
@@ -352,37 +541,61 @@ namespace htb
             CUtensorMap mapA, mapB;
             cuuint64_t  gdim[5], gstr[4];
             cuuint32_t  box[5], estr[5] = {1, 1, 1, 1, 1};
+            PermTmaArgs a{};
+            // Wide maps: the contiguous mode is described as (32, extent/32) so that ONE box
+            // [32][NP] covers NP consecutive 128-byte pieces of a row; the pieces of one row are
+            // then requested back to back and DRAM serves them from one open page.
+            const bool wide = (NP > 1 || NQ > 1) && p.ndim <= 4 && p.ext[0] % 32 == 0 && p.ext[p.q] % 32 == 0;
+            a.wide          = wide ? 1 : 0;
+            const int sh    = wide ? 1 : 0;
             // A: folded modes in A's order
             for(int d = 0; d < p.ndim; d++)
             {
-                gdim[d] = cuuint64_t(p.ext[d]);
-                box[d]  = 1;
+                gdim[d + sh] = cuuint64_t(p.ext[d]);
+                box[d + sh]  = 1;
                 if(d > 0)
-                    gstr[d - 1] = cuuint64_t(p.sA[d]) * 4;
+                    gstr[d - 1 + sh] = cuuint64_t(p.sA[d]) * 4;
             }
-            box[0]   = 32;
-            box[p.q] = TQ;
-            if(encode(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.ndim, const_cast<void*>(A), gdim, gstr, box, estr,
+            if(wide)
+            {
+                gdim[0] = 32;
+                gdim[1] = cuuint64_t(p.ext[0] / 32);
+                gstr[0] = 128;
+                box[0]  = 32;
+                box[1]  = NP;
+            }
+            else
+                box[0] = 32;
+            box[p.q + sh] = TQ;
+            if(encode(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.ndim + sh, const_cast<void*>(A), gdim, gstr, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
                != CUDA_SUCCESS)
                 return cudaErrorInvalidValue;
             // B: folded modes by ascending stride in B
-            PermTmaArgs a{};
             for(int i = 0; i < p.ndim; i++)
             {
                 const int d  = p.orderB[i];
-                gdim[i]      = cuuint64_t(p.ext[d]);
-                box[i]       = 1;
+                gdim[i + sh] = cuuint64_t(p.ext[d]);
+                box[i + sh]  = 1;
                 a.mapPosB[d] = i;
                 if(i > 0)
-                    gstr[i - 1] = cuuint64_t(p.sB[d]) * 4;
+                    gstr[i - 1 + sh] = cuuint64_t(p.sB[d]) * 4;
             }
-            a.posP_B     = a.mapPosB[0];
-            a.posQ_B     = a.mapPosB[p.q];
-            box[a.posQ_B] = 32;
-            box[a.posP_B] = TP;
-            if(encode(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.ndim, B, gdim, gstr, box, estr,
+            a.posP_B = a.mapPosB[0];
+            a.posQ_B = a.mapPosB[p.q];
+            if(wide)
+            {
+                gdim[0] = 32;
+                gdim[1] = cuuint64_t(p.ext[p.q] / 32);
+                gstr[0] = 128;
+                box[0]  = 32;
+                box[1]  = NQ;
+            }
+            else
+                box[a.posQ_B] = 32;
+            box[a.posP_B + sh] = TP;
+            if(encode(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.ndim + sh, B, gdim, gstr, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
                != CUDA_SUCCESS)
@@ -390,27 +603,35 @@ namespace htb
             a.ndim = p.ndim;
             a.q    = p.q;
             for(int d = 0; d < p.ndim; d++)
-                a.ext[d] = p.ext[d];
+                a.ext[d] = uint32_t(p.ext[d]);
             a.alpha  = alpha;
             a.opA    = opA;
             a.opB    = opB;
-            a.tilesP = int((p.ext[0] + TP - 1) / TP);
-            a.tilesQ = int((p.ext[p.q] + TQ - 1) / TQ);
+            a.tilesP = uint32_t((p.ext[0] + TP - 1) / TP);
+            a.tilesQ = uint32_t((p.ext[p.q] + TQ - 1) / TQ);
             a.status = status;
-            int64_t blocks = int64_t(a.tilesP) * a.tilesQ;
+            long long tiles = (long long)a.tilesP * a.tilesQ;
             for(int d = 1; d < p.ndim; d++)
                 if(d != p.q)
-                    blocks *= p.ext[d];
-            if(blocks > 0x7fffffffll)
+                    tiles *= p.ext[d];
+            if(tiles > 0x7fffffffll)
                 return cudaErrorInvalidConfiguration;
-            const int   smem = 2 * TP * TQ * 4 + 1024;
-            static bool attrSet = false;
-            if(!attrSet)
+            a.numTiles = uint32_t(tiles);
+            a.inStages  = tune.inStages;
+            const int   smem = (a.inStages + kOutStages) * TP * TQ * 4 + 1024;
+            static int  attrSmem = 0;
+            if(smem > attrSmem)
             {
-                cudaFuncSetAttribute(perm_tma_kernel<NP, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-                attrSet = true;
+                cudaError_t e
+                    = cudaFuncSetAttribute(perm_tma_kernel<NP, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+                if(e != cudaSuccess)
+                    return e;
+                attrSmem = smem;
             }
-            perm_tma_kernel<NP, NQ><<<unsigned(blocks), 64 * NP * NQ, smem, stream>>>(mapA, mapB, a);
+            const int       fit   = std::max(1, (227 * 1024) / (smem + 1024));
+            const int       perSm = std::min(fit, tune.ctasPerSm);
+            const long long grid  = std::min<long long>(tiles, (long long)(smCount > 0 ? smCount : 148) * perSm);
+            perm_tma_kernel<NP, NQ><<<unsigned(grid), 64 * NP * NQ + 32, smem, stream>>>(mapA, mapB, a);
             return cudaGetLastError();
         }
 
@@ -432,16 +653,63 @@ namespace htb
             a.opB   = opB;
             if(p.kind == PERM_COPY)
             {
-                int tx = 32;
-                while(tx < 256 && tx < p.ext[0])
-                    tx <<= 1;
-                const int     ty   = 256 / tx;
-                const int64_t rows = p.total / p.ext[0];
-                const int64_t grid = (rows + ty - 1) / ty;
-                if(grid > 0x7fffffffll)
+                // widest vector that keeps every access aligned
+                int vec = 16 / int(sizeof(TI));
+                if(sizeof(TO) > sizeof(TI))
+                    vec /= 2; // 16-byte stores of the wider output type
+                auto aligned = [&](int v) {
+                    if((uintptr_t(A) % (sizeof(TI) * v)) || (uintptr_t(B) % (sizeof(TO) * v)) || p.ext[0] % v)
+                        return false;
+                    for(int d = 1; d < p.ndim; d++)
+                        if(p.sA[d] % v || p.sB[d] % v)
+                            return false;
+                    return true;
+                };
+                while(vec > 1 && !aligned(vec))
+                    vec >>= 1;
+                // a single folded mode (plain scaled copy) is viewed as rows of 256 vectors
+                int64_t flatTotal = 0;
+                if(p.ndim == 1 && p.ext[0] > 256 * vec)
+                {
+                    flatTotal = p.ext[0];
+                    a.ndim    = 2;
+                    a.ext[0]  = 256 * vec;
+                    a.ext[1]  = (flatTotal + a.ext[0] - 1) / a.ext[0];
+                    a.sA[1] = a.sB[1] = a.ext[0];
+                }
+                const PermArgs& q = a; // extents as the kernel sees them
+                const int64_t chunks = (q.ext[0] + vec - 1) / vec;
+                int           log2c  = 0;
+                while(log2c < 8 && (int64_t(1) << log2c) < chunks)
+                    log2c++;
+                const int     T1     = 1024 >> log2c;
+                const int64_t ext1   = (q.ndim > 1) ? q.ext[1] : 1;
+                const int64_t tiles0 = (chunks + (int64_t(1) << log2c) - 1) >> log2c;
+                const int64_t tiles1 = (ext1 + T1 - 1) / T1;
+                int64_t       grid   = tiles0 * tiles1;
+                for(int d = 2; d < q.ndim; d++)
+                    grid *= q.ext[d];
+                if(grid > 0x7fffffffll || tiles0 > 0x7fffffffll || tiles1 > 0x7fffffffll)
                     return cudaErrorInvalidConfiguration;
-                perm_copy_kernel<TI, TO>
-                    <<<unsigned(grid), dim3(tx, ty), 0, stream>>>((const TI*)A, (TO*)B, a, rows);
+                const TI* Ap = (const TI*)A;
+                TO*       Bp = (TO*)B;
+                switch(vec)
+                {
+                case 8:
+                    if constexpr(sizeof(TI) == 2 && sizeof(TO) == 2)
+                        perm_copy_kernel<TI, TO, 8>
+                            <<<unsigned(grid), 256, 0, stream>>>(Ap, Bp, a, log2c, int(tiles0), int(tiles1), flatTotal);
+                    break;
+                case 4:
+                    perm_copy_kernel<TI, TO, 4><<<unsigned(grid), 256, 0, stream>>>(Ap, Bp, a, log2c, int(tiles0), int(tiles1), flatTotal);
+                    break;
+                case 2:
+                    perm_copy_kernel<TI, TO, 2><<<unsigned(grid), 256, 0, stream>>>(Ap, Bp, a, log2c, int(tiles0), int(tiles1), flatTotal);
+                    break;
+                default:
+                    perm_copy_kernel<TI, TO, 1><<<unsigned(grid), 256, 0, stream>>>(Ap, Bp, a, log2c, int(tiles0), int(tiles1), flatTotal);
+                    break;
+                }
                 noteLaunch("perm_copy");
             }
             else
@@ -462,13 +730,32 @@ namespace htb
     } // namespace
 
     cudaError_t launchPermutation(const PermPlan& plan, int typeA, int typeB, const void* A, void* B, float alpha,
-                                  int opA, int opB, int* deviceStatus, cudaStream_t stream)
+                                  int opA, int opB, int smCount, int* deviceStatus, cudaStream_t stream)
     {
         if(plan.total == 0)
             return cudaSuccess;
         if(plan.kind == PERM_TMA)
         {
-            cudaError_t e = launchTma<2, 2>(plan, A, B, alpha, opA, opB, deviceStatus, stream);
+            // tile shape: long runs on the store side (rows of the output tile are 32*NQ... wide)
+            PermTune tune;
+            auto     envInt = [](const char* name, int& v) {
+                if(const char* e = getenv(name))
+                    v = atoi(e);
+            };
+            // overrides for tuning runs: "HTB_PERM_TILE" (22, 14, 41, 24, 42), "HTB_PERM_STAGES", "HTB_PERM_CTAS"
+            envInt("HTB_PERM_TILE", tune.shape);
+            envInt("HTB_PERM_STAGES", tune.inStages);
+            envInt("HTB_PERM_CTAS", tune.ctasPerSm);
+            tune.inStages = std::min(std::max(tune.inStages, 1), kMaxInStages);
+            cudaError_t e;
+            switch(tune.shape)
+            {
+            case 14: e = launchTma<1, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+            case 41: e = launchTma<4, 1>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+            case 24: e = launchTma<2, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+            case 42: e = launchTma<4, 2>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+            default: e = launchTma<2, 2>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+            }
             if(e == cudaSuccess)
                 noteLaunch("perm_tma");
             return e;
