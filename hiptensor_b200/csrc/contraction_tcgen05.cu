@@ -27,6 +27,9 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "kernels.hpp"
 
 namespace htb
@@ -53,6 +56,7 @@ namespace htb
             float   alpha, beta;
             int     bilinear;
             int     nContig; // N is one folded mode with stride 1 in D and D is 16-byte aligned
+            int     probe; // measurement aid: 1 = producer skips the loads, 2 = issuer skips the MMAs (results invalid)
             int*    status;
         };
 
@@ -445,6 +449,346 @@ namespace htb
             }
         }
 
+        // ------------------------------------------------------------------ CTA-pair kernel
+        // Two CTAs of a cluster (two neighbouring SMs) work on one 256 x 256 output tile with
+        // tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of A and 128 of the 256 rows
+        // of B, the leader CTA (cluster rank 0) issues the MMAs for both, and each CTA's tensor
+        // memory receives the accumulators of its own 128 rows. Against the single-CTA kernel
+        // this halves the B traffic per SM (L2 and shared memory) and leaves room for six stages.
+        //   * the TMA loads of both CTAs complete on the LEADER's full barrier (cta_group::2 form,
+        //     barrier address mapped to rank 0), which expects the bytes of both;
+        //   * tcgen05.commit with a CTA mask releases a stage, or publishes an accumulator, in both
+        //     CTAs at once;
+        //   * the epilogue threads of both CTAs arrive on the leader's accumulator-empty barrier.
+        // Loads carry no multicast qualifier: every CTA fetches its own operands.
+        struct TcPairArgs
+        {
+            TcArgs base; // boxN / tilesPerDimN / tilesN describe 128-row N sub-tiles here
+            int    pairsM, pairsN;
+        };
+
+        __device__ __forceinline__ uint32_t clusterRank()
+        {
+            uint32_t r;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+            return r;
+        }
+        __device__ __forceinline__ uint32_t mapToRank(uint32_t addr, uint32_t rank)
+        {
+            uint32_t r;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+            return r;
+        }
+        __device__ __forceinline__ void clusterSync()
+        {
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
+
+        template <int RANK>
+        __device__ __forceinline__ void tmaLoadPair(uint32_t dst, const CUtensorMap* map, uint32_t bar, const int* c)
+        {
+            if constexpr(RANK == 2)
+                asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                             "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1])
+                             : "memory");
+            else if constexpr(RANK == 3)
+                asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                             "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2])
+                             : "memory");
+            else if constexpr(RANK == 4)
+                asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                             "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3])
+                             : "memory");
+            else
+                asm volatile("cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                             "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
+                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4])
+                             : "memory");
+        }
+        __device__ __forceinline__ void tmaLoadPairRank(int rank, uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                        const int* c)
+        {
+            switch(rank)
+            {
+            case 2: tmaLoadPair<2>(dst, map, bar, c); break;
+            case 3: tmaLoadPair<3>(dst, map, bar, c); break;
+            case 4: tmaLoadPair<4>(dst, map, bar, c); break;
+            default: tmaLoadPair<5>(dst, map, bar, c); break;
+            }
+        }
+
+        template <typename TD>
+        __global__ void __launch_bounds__(kThreads, 1)
+            contraction_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
+                                            const __grid_constant__ CUtensorMap mapB, const TD* __restrict__ C,
+                                            TD* __restrict__ D, TcPairArgs pa, uint32_t idesc)
+        {
+            const TcArgs& a = pa.base;
+            extern __shared__ unsigned char smemRaw[];
+            unsigned char* tiles = (unsigned char*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
+
+            __shared__ __align__(8) unsigned long long fullBar[kMaxStages], emptyBar[kMaxStages];
+            __shared__ __align__(8) unsigned long long tmemFullBar[2], tmemEmptyBar[2];
+            __shared__ uint32_t tmemBase;
+            __shared__ int      abortFlag;
+            __shared__ int64_t  colOff[4][256]; // one table per epilogue warp
+
+            const int      warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            const uint32_t rank = clusterRank();
+            const bool     leader = (rank == 0);
+            constexpr uint32_t kHalfBytes = 128 * kTileK * 2; // 16 KiB: A rows, or this CTA's half of B
+            constexpr uint32_t kStage     = 2 * kHalfBytes;
+            const int      numPairs    = pa.pairsM * pa.pairsN;
+            const int      clusterId   = blockIdx.x >> 1;
+            const int      numClusters = gridDim.x >> 1;
+
+            if(threadIdx.x == 0)
+            {
+                abortFlag = 0;
+                for(int s = 0; s < a.stages; s++)
+                {
+                    mbarInit(smemAddr(&fullBar[s]), 1);
+                    mbarInit(smemAddr(&emptyBar[s]), 1);
+                }
+                for(int i = 0; i < 2; i++)
+                {
+                    mbarInit(smemAddr(&tmemFullBar[i]), 1);
+                    mbarInit(smemAddr(&tmemEmptyBar[i]), 256);
+                }
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            }
+            if(warp == 1)
+            {
+                asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&tmemBase)),
+                             "r"(512u)
+                             : "memory");
+                asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();
+            clusterSync(); // the peer's barriers exist before anything signals them
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem   = tmemBase;
+            volatile int*  abortP = &abortFlag;
+
+            if(warp == 0)
+            {
+                // ---------------------------------------------------------------- TMA producer
+                if(lane == 0)
+                {
+                    int      stage = 0;
+                    uint32_t phase = 0;
+                    bool     ok    = true;
+                    for(int t = clusterId; t < numPairs && ok; t += numClusters)
+                    {
+                        const int pm = t % pa.pairsM, pn = t / pa.pairsM;
+                        const int tm = min(2 * pm + int(rank), a.tilesM - 1);
+                        const int tn = min(2 * pn + int(rank), a.tilesN - 1);
+                        int       cA[5] = {0, 0, 0, 0, 0}, cB[5] = {0, 0, 0, 0, 0};
+                        tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cA + 1);
+                        tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB + 1);
+                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        {
+                            ok = mbarWait(smemAddr(&emptyBar[stage]), phase ^ 1, abortP);
+                            if(!ok)
+                                break;
+                            const uint32_t localBar  = smemAddr(&fullBar[stage]);
+                            const uint32_t leaderBar = mapToRank(localBar, 0);
+                            if(a.probe == 1)
+                            {
+                                if(leader)
+                                    mbarArrive(localBar);
+                            }
+                            else
+                            {
+                                if(leader)
+                                    mbarArriveExpectTx(localBar, 2 * a.stageBytes); // both CTAs' boxes
+                                cA[0] = kb * kTileK;
+                                cB[0] = kb * kTileK;
+                                const uint32_t dstA = smemAddr(tiles + size_t(stage) * kStage);
+                                tmaLoadPairRank(a.nm + 1, dstA, &mapA, leaderBar, cA);
+                                tmaLoadPairRank(a.nn + 1, dstA + kHalfBytes, &mapB, leaderBar, cB);
+                            }
+                            if(++stage == a.stages)
+                            {
+                                stage = 0;
+                                phase ^= 1;
+                            }
+                        }
+                    }
+                }
+            }
+            else if(warp == 1)
+            {
+                // ---------------------------------------------------------------- MMA issuer (leader CTA)
+                if(lane == 0 && leader)
+                {
+                    int      stage = 0;
+                    uint32_t phase = 0;
+                    int      local = 0;
+                    bool     ok    = true;
+                    for(int t = clusterId; t < numPairs && ok; t += numClusters, local++)
+                    {
+                        const int      acc      = local & 1;
+                        const uint32_t accPhase = (local >> 1) & 1;
+                        ok = mbarWait(smemAddr(&tmemEmptyBar[acc]), accPhase ^ 1, abortP);
+                        if(!ok)
+                            break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t dTmem = tmem + uint32_t(acc * 256);
+                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        {
+                            ok = mbarWait(smemAddr(&fullBar[stage]), phase, abortP);
+                            if(!ok)
+                                break;
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            const uint32_t sa    = smemAddr(tiles + size_t(stage) * kStage);
+                            const uint64_t descA = smemDesc(sa), descB = smemDesc(sa + kHalfBytes);
+#pragma unroll
+                            for(int k = 0; k < kTileK / 16; k++)
+                            {
+                                if(a.probe == 2)
+                                    break;
+                                const uint32_t accumulate = (kb | k) ? 1u : 0u;
+                                asm volatile("{\n\t.reg .pred p;\n\t"
+                                             "setp.ne.b32 p, %4, 0;\n\t"
+                                             "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
+                                             "l"(descA + uint64_t(2 * k)), "l"(descB + uint64_t(2 * k)), "r"(idesc),
+                                             "r"(accumulate)
+                                             : "memory");
+                            }
+                            // frees the stage in both CTAs once these MMAs have read it
+                            asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+                                         "[%0], %1;" ::"r"(smemAddr(&emptyBar[stage])),
+                                         "h"((unsigned short)3)
+                                         : "memory");
+                            if(++stage == a.stages)
+                            {
+                                stage = 0;
+                                phase ^= 1;
+                            }
+                        }
+                        if(ok)
+                            asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+                                         "[%0], %1;" ::"r"(smemAddr(&tmemFullBar[acc])),
+                                         "h"((unsigned short)3)
+                                         : "memory");
+                    }
+                }
+            }
+            else
+            {
+                // ---------------------------------------------------------------- epilogue (both CTAs)
+                const int quad = warp & 3;
+                const int row  = quad * 32 + lane;
+                int64_t*  cols = colOff[quad];
+                int       local = 0;
+                for(int t = clusterId; t < numPairs; t += numClusters, local++)
+                {
+                    const int      acc      = local & 1;
+                    const uint32_t accPhase = (local >> 1) & 1;
+                    const int      pm = t % pa.pairsM, pn = t / pa.pairsM;
+                    const int      tmRaw = 2 * pm + int(rank);
+                    const bool     dupM  = tmRaw >= a.tilesM; // this CTA repeats its peer's rows: no stores
+                    const int      tm    = min(tmRaw, a.tilesM - 1);
+                    int            cM[4], cN[4];
+                    tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cM);
+                    __syncwarp();
+                    for(int h = 0; h < 2; h++)
+                    {
+                        const int tnRaw = 2 * pn + h;
+                        tileCoords(min(tnRaw, a.tilesN - 1), a.tilesPerDimN, a.boxN, a.nn, cN);
+                        for(int c = lane; c < 128; c += 32)
+                            cols[h * 128 + c] = (tnRaw < a.tilesN) ? rowOffset(c, cN, a.boxN, a.extN, a.sDn, a.nn) : -1;
+                    }
+                    __syncwarp();
+                    const int64_t offM = dupM ? -1 : rowOffset(row, cM, a.boxM, a.extM, a.sDm, a.nm);
+
+                    int ok = 1;
+                    if(lane == 0)
+                        ok = mbarWait(smemAddr(&tmemFullBar[acc]), accPhase, abortP) ? 1 : 0;
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if(!ok)
+                        break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(acc * 256);
+                    for(int c0 = 0; c0 < 256; c0 += 32)
+                    {
+                        uint32_t v[32];
+                        asm volatile(
+                            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                              "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+                              "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+                              "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+                              "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                            : "r"(taddr + uint32_t(c0)));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if(offM < 0)
+                            continue;
+                        const int64_t first     = cols[c0];
+                        const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] >= 0;
+                        if(fullChunk && sizeof(TD) == 4 && ((offM + first) & 3) == 0)
+                        {
+                            float*       dst = (float*)D + offM + first;
+                            const float* src = (const float*)C + offM + first;
+#pragma unroll
+                            for(int j = 0; j < 32; j += 4)
+                            {
+                                float4 o;
+                                o.x = __fmul_rn(a.alpha, __uint_as_float(v[j]));
+                                o.y = __fmul_rn(a.alpha, __uint_as_float(v[j + 1]));
+                                o.z = __fmul_rn(a.alpha, __uint_as_float(v[j + 2]));
+                                o.w = __fmul_rn(a.alpha, __uint_as_float(v[j + 3]));
+                                if(a.bilinear)
+                                {
+                                    const float4 c4 = *(const float4*)(src + j);
+                                    o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4.x));
+                                    o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4.y));
+                                    o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4.z));
+                                    o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4.w));
+                                }
+                                *(float4*)(dst + j) = o;
+                            }
+                        }
+                        else
+                        {
+#pragma unroll
+                            for(int j = 0; j < 32; j++)
+                            {
+                                const int64_t oc = cols[c0 + j];
+                                if(oc >= 0)
+                                    D[offM + oc] = finish<TD>(__uint_as_float(v[j]), a.alpha, a.beta, a.bilinear != 0, C,
+                                                              offM + oc);
+                            }
+                        }
+                    }
+                    // hand the accumulator back: every epilogue thread of the pair arrives on the leader's barrier
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    const uint32_t emptyAddr = mapToRank(smemAddr(&tmemEmptyBar[acc]), 0);
+                    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(emptyAddr) : "memory");
+                }
+            }
+
+            // ---------------------------------------------------------------- teardown
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();
+            clusterSync(); // both CTAs are done with tensor memory and with each other's barriers
+            if(threadIdx.x == 0 && abortFlag && a.status)
+                atomicExch(a.status, 3);
+            if(warp == 1)
+            {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+            }
+        }
+
         bool encodeOperand(PFN_encodeTiled encode, CUtensorMap* map, const void* base, bool bf16, int64_t K,
                            const ModeDim* dims, int n, const int* box)
         {
@@ -468,6 +812,20 @@ namespace htb
                    == CUDA_SUCCESS;
         }
 
+        void fillGroupArgs(const ModeDim* dims, int n, const int* box, int* boxOut, int64_t* ext, int64_t* sD,
+                           int* tilesPerDim, int& tiles)
+        {
+            tiles = 1;
+            for(int d = 0; d < n; d++)
+            {
+                boxOut[d]      = box[d];
+                ext[d]         = dims[d].ext;
+                sD[d]          = dims[d].s1;
+                tilesPerDim[d] = int((dims[d].ext + box[d] - 1) / box[d]);
+                tiles *= tilesPerDim[d];
+            }
+        }
+
         template <typename TD>
         cudaError_t launchTyped(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
                                 const void* C, void* D, int smCount, int* status, cudaStream_t stream)
@@ -476,36 +834,22 @@ namespace htb
             if(!encode)
                 return cudaErrorNotSupported;
             const bool  bf16 = (p.typeA == CUDA_R_16BF);
+            const bool  pair = (p.pair != 0) && getenv("HTB_TC_SINGLE") == nullptr;
+            const int*  boxN = pair ? p.boxN128 : p.boxN;
             CUtensorMap mapA, mapB;
             if(!encodeOperand(encode, &mapA, A, bf16, p.K, p.m, p.nm, p.boxM)
-               || !encodeOperand(encode, &mapB, B, bf16, p.K, p.n, p.nn, p.boxN))
+               || !encodeOperand(encode, &mapB, B, bf16, p.K, p.n, p.nn, boxN))
                 return cudaErrorNotSupported;
 
             TcArgs a{};
-            a.nm     = p.nm;
-            a.nn     = p.nn;
-            a.tilesM = 1;
-            a.tilesN = 1;
-            for(int d = 0; d < p.nm; d++)
-            {
-                a.boxM[d]         = p.boxM[d];
-                a.extM[d]         = p.m[d].ext;
-                a.sDm[d]          = p.m[d].s1;
-                a.tilesPerDimM[d] = int((p.m[d].ext + p.boxM[d] - 1) / p.boxM[d]);
-                a.tilesM *= a.tilesPerDimM[d];
-            }
-            for(int d = 0; d < p.nn; d++)
-            {
-                a.boxN[d]         = p.boxN[d];
-                a.extN[d]         = p.n[d].ext;
-                a.sDn[d]          = p.n[d].s1;
-                a.tilesPerDimN[d] = int((p.n[d].ext + p.boxN[d] - 1) / p.boxN[d]);
-                a.tilesN *= a.tilesPerDimN[d];
-            }
+            a.nm = p.nm;
+            a.nn = p.nn;
+            fillGroupArgs(p.m, p.nm, p.boxM, a.boxM, a.extM, a.sDm, a.tilesPerDimM, a.tilesM);
+            fillGroupArgs(p.n, p.nn, boxN, a.boxN, a.extN, a.sDn, a.tilesPerDimN, a.tilesN);
             a.kBlocks    = int((p.K + kTileK - 1) / kTileK);
-            a.tileN      = p.tileN;
-            a.stages     = p.stages;
-            a.stageBytes = uint32_t(p.rowsM + p.rowsN) * kTileK * 2;
+            a.tileN      = pair ? 256 : p.tileN;
+            a.stages     = pair ? 6 : p.stages;
+            a.stageBytes = uint32_t(p.rowsM + (pair ? p.rowsN128 : p.rowsN)) * kTileK * 2;
             a.alpha      = alpha;
             a.beta       = beta;
             a.bilinear   = (p.bilinear && C != nullptr) ? 1 : 0;
@@ -514,20 +858,68 @@ namespace htb
                                ? 1
                                : 0;
             a.status     = status;
+            if(const char* env = getenv("HTB_TC_PROBE"))
+                a.probe = atoi(env);
             if(int64_t(a.tilesM) * a.tilesN > 0x7fffffffll || a.stages > kMaxStages)
                 return cudaErrorInvalidConfiguration;
 
             // instruction descriptor: fp32 accumulate, A/B format, both K-major, N/8, M/16
-            const uint32_t fmt   = bf16 ? 1u : 0u;
+            const uint32_t fmt = bf16 ? 1u : 0u;
+            const int      sms = smCount > 0 ? smCount : 148;
+            if(pair)
+            {
+                TcPairArgs pa{};
+                pa.base   = a;
+                pa.pairsM = (a.tilesM + 1) / 2;
+                pa.pairsN = (a.tilesN + 1) / 2;
+                const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(256 >> 3) << 17)
+                                       | (uint32_t(256 >> 4) << 24);
+                const size_t smem = size_t(a.stages) * 2 * 128 * kTileK * 2 + 1024;
+                cudaError_t  e    = cudaFuncSetAttribute(contraction_tcgen05_pair_kernel<TD>,
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+                if(e != cudaSuccess)
+                    return e;
+                cudaLaunchConfig_t cfg{};
+                cudaLaunchAttribute attr[1];
+                attr[0].id               = cudaLaunchAttributeClusterDimension;
+                attr[0].val.clusterDim.x = 2;
+                attr[0].val.clusterDim.y = 1;
+                attr[0].val.clusterDim.z = 1;
+                cfg.blockDim             = dim3(kThreads);
+                cfg.dynamicSmemBytes     = smem;
+                cfg.stream               = stream;
+                cfg.attrs                = attr;
+                cfg.numAttrs             = 1;
+                // clusters that can be resident at once (GPCs with an odd SM count lose one SM)
+                static int maxClusters = 0;
+                if(maxClusters == 0)
+                {
+                    cfg.gridDim = dim3(unsigned(sms / 2 * 2));
+                    int n       = 0;
+                    if(cudaOccupancyMaxActiveClusters(&n, contraction_tcgen05_pair_kernel<TD>, &cfg) != cudaSuccess || n <= 0)
+                    {
+                        cudaGetLastError();
+                        n = sms / 2;
+                    }
+                    maxClusters = n;
+                }
+                const int64_t pairs    = int64_t(pa.pairsM) * pa.pairsN;
+                const int     clusters = int(std::min<int64_t>(pairs, maxClusters));
+                cfg.gridDim            = dim3(unsigned(2 * clusters));
+                e = cudaLaunchKernelEx(&cfg, contraction_tcgen05_pair_kernel<TD>, mapA, mapB, (const TD*)C, (TD*)D, pa,
+                                       idesc);
+                if(e == cudaSuccess)
+                    noteLaunch("contraction_tcgen05_pair");
+                return e;
+            }
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(p.tileN >> 3) << 17)
                                    | (uint32_t(kTileM >> 4) << 24);
-
             const size_t smem = size_t(a.stages) * (size_t(kTileM) + p.tileN) * kTileK * 2 + 1024;
             cudaError_t  e = cudaFuncSetAttribute(contraction_tcgen05_kernel<TD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   int(smem));
             if(e != cudaSuccess)
                 return e;
-            const int grid = int(std::min<int64_t>(int64_t(a.tilesM) * a.tilesN, smCount > 0 ? smCount : 148));
+            const int grid = int(std::min<int64_t>(int64_t(a.tilesM) * a.tilesN, sms));
             contraction_tcgen05_kernel<TD>
                 <<<grid, kThreads, smem, stream>>>(mapA, mapB, (const TD*)C, (TD*)D, a, idesc);
             noteLaunch("contraction_tcgen05");

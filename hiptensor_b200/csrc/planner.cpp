@@ -502,6 +502,12 @@ namespace htb
                 }
                 tc = out->rowsM > 0 && out->rowsN > 0;
                 out->stages = (out->tileN == 256) ? 4 : 6;
+                // large problems: 256 x 256 tiles over CTA pairs
+                out->rowsN128 = boxDecompose(gn, nn, 128, out->boxN128);
+                out->pair     = (tc && out->tileN == 256 && out->rowsN128 == 128 && out->rowsM == 128 && out->M >= 512
+                             && out->N >= 512)
+                                    ? 1
+                                    : 0;
             }
             out->kind = tc ? CK_TCGEN05 : CK_TILED_SIMT;
         }
@@ -542,7 +548,7 @@ namespace htb
                 snprintf(buf, sizeof(buf), "%s%d", i ? " " : "", p.boxN[i]);
                 s += buf;
             }
-            s += "]";
+            s += p.pair ? "] pair" : "]";
         }
         return s;
     }

@@ -107,6 +107,8 @@ namespace htb
         int tileM, tileN, tileK, stages;
         int boxM[4], boxN[4]; // TMA box extent per folded M / N mode (product = rows gathered per tile)
         int rowsM, rowsN; // rows of the tile that the boxes fill (<= tileM / tileN)
+        int pair; // 256 x 256 tile over a CTA pair (tcgen05 cta_group::2), each CTA loading 128 rows of B
+        int boxN128[4], rowsN128; // N boxes of the 128-row sub-tiles of the pair kernel
         int aKContig, bKContig; // operand has its K group folded to one stride-1 mode
         // split of the K range over several CTAs (needs workspace); 1 = none
         int      splitK;

@@ -175,6 +175,7 @@ def test_config4_full_size_sampled(env):
     err = rel_error(got, exp, td)
     assert 0 <= err < 1e-2, err
     assert not np.isnan(got).any()
+    assert ht.last_kernel_name() == "contraction_tcgen05_pair"
     got2, _, _ = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F16,
                                  typeD=orc.F32, alpha=2.0, beta=0.0, with_c=False, fill="normal", sample=smp[:8])
     assert np.array_equal(got2, 2.0 * got)  # scaling by a power of two is exact
@@ -222,7 +223,7 @@ def test_tensor_core_path_gathered_tiles(env, dt):
         assert 0 <= err < tol, (dt, out32, err)
 
 
-@pytest.mark.parametrize("shape", [(256, 320, 96), (128, 64, 64), (384, 1000, 520)])
+@pytest.mark.parametrize("shape", [(256, 320, 96), (128, 64, 64), (384, 1000, 520), (640, 896, 200), (1024, 512, 64)])
 def test_tensor_core_path_plain_matrices(env, shape):
     ht, h = env
     M, N, K = shape
@@ -231,12 +232,27 @@ def test_tensor_core_path_plain_matrices(env, shape):
     for with_c in (True, False):
         got, exp, td = run_contraction(ht, h, ext, [m, k], [n, k], [m, n], typeAB=orc.F16, typeD=orc.F16, alpha=1.0,
                                        beta=2.0 if with_c else 0.0, with_c=with_c, fill="normal")
-        assert ht.last_kernel_name() == "contraction_tcgen05"
+        assert ht.last_kernel_name() == ("contraction_tcgen05_pair" if min(M, N) >= 512 else "contraction_tcgen05")
         err = rel_error(got, exp, td)
         assert 0 <= err < 2 * 2.0 ** -10, (shape, with_c, err)
     # M-major output: the planner exchanges the operands
     got, exp, td = run_contraction(ht, h, ext, [m, k], [n, k], [n, m], typeAB=orc.BF16, typeD=orc.F32, alpha=1.0,
                                    beta=1.0, fill="normal")
     if N >= 128:  # after the exchange the 128-row tile runs along the original N
-        assert ht.last_kernel_name() == "contraction_tcgen05"
+        assert ht.last_kernel_name().startswith("contraction_tcgen05")
     assert 0 <= rel_error(got, exp, td) < 1e-4
+
+
+@pytest.mark.parametrize("dt", [orc.F16, orc.BF16])
+def test_cta_pair_kernel_gathered_odd_tiles(env, dt):
+    """256 x 256 tiles over CTA pairs with an odd number of 128-row sub-tiles along M and N (the last
+    pair repeats a sub-tile and must not store it twice) and rows gathered from two modes."""
+    ht, h = env
+    m0, m1, n0, n1, k0 = range(5)
+    ext = {m0: 40, m1: 16, n0: 32, n1: 20, k0: 136}
+    got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0], [n1, n0, k0], [m1, n1, m0, n0], typeAB=dt,
+                                   typeD=orc.F32, alpha=0.5, beta=2.0, fill="normal")
+    assert ht.last_kernel_name() == "contraction_tcgen05_pair"
+    err = rel_error(got, exp, td)
+    assert 0 <= err < 1e-4, (dt, err)
+    assert not np.isnan(got).any()
