@@ -30,6 +30,7 @@ SIGNATURES = {
     "htContraction": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "htReduction": (_int, [_vp, _vp, _vp, _vp, _i32p, _vp, _vp, _vp, _i32p, _vp, _vp, _i32p, _int, _int, _vp, _u64,
                            _vp]),
+    "htReductionNoAlloc": (_int, [_vp, _vp, _vp, _vp, _i32p, _vp, _vp, _vp, _i32p, _vp, _vp, _i32p, _int, _int, _vp]),
     "htReductionGetWorkspaceSize": (_int, [_vp, _vp, _vp, _i32p, _vp, _vp, _i32p, _vp, _vp, _i32p, _int, _int,
                                            ctypes.POINTER(_u64)]),
     "htLoggerSetMask": (_int, [ctypes.c_int32]),

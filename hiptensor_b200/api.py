@@ -177,6 +177,19 @@ class Handle:
                                    int(type_compute), _ptr(workspace), int(workspace_size), _stream_ptr(stream)),
                "hiptensorReduction")
 
+    def reduction_no_alloc(self, alpha, A, descA, modeA, beta, C, descC, modeC, D, descD, modeD, op_reduce,
+                           type_compute, stream=None):
+        """htReductionNoAlloc: the same reduction for callers that may not allocate device memory (hosts
+        that own the device heap, latency-critical loops, services with an allocation ban after start-up). Scratch is an 8 KiB array inside
+        the library, shared by all calls on the device: do not overlap two such calls on one device; a
+        reduction that needs more raises STATUS_INSUFFICIENT_WORKSPACE. The first call per device does a
+        one-time address lookup and belongs outside stream capture."""
+        a = _scalar_for_compute(alpha, type_compute)
+        b = _scalar_for_compute(beta, type_compute)
+        _check(self._L.htReductionNoAlloc(self._h, a, _ptr(A), descA._p, _lib.i32(modeA), b, _ptr(C), descC._p,
+                                          _lib.i32(modeC), _ptr(D), descD._p, _lib.i32(modeD), int(op_reduce),
+                                          int(type_compute), _stream_ptr(stream)), "htReductionNoAlloc")
+
     def reduction_workspace_size(self, A, descA, modeA, C, descC, modeC, D, descD, modeD, op_reduce, type_compute):
         out = ctypes.c_uint64(0)
         _check(self._L.htReductionGetWorkspaceSize(self._h, _ptr(A), descA._p, _lib.i32(modeA), _ptr(C), descC._p,

@@ -475,6 +475,86 @@ hiptensorStatus_t hiptensorReductionGetWorkspaceSize(
     return HIPTENSOR_STATUS_SUCCESS;
 }
 
+// ---------------------------------------------------------------------------- allocation-free reduction
+// Body of htReductionNoAlloc (include/hiptensor_b200.h). Same operation and argument meaning as hiptensorReduction,
+// for callers that must not trigger any allocation while they run: real-time loops (cudaMalloc
+// synchronises the device), plug-ins of hosts that own the whole device heap (cudaMalloc fails),
+// and services that forbid device allocations after start-up.
+// The two-pass scratch comes from a fixed array inside the library (htb::kStaticScratchBytes per
+// device, resident for the life of the process); no cudaMalloc, cudaFree or allocating routine
+// is called, and the host side works on stack arrays only.
+int htb::reductionNoAlloc(const hiptensorHandle_t* handle, const void* alpha, const void* A,
+                          const hiptensorTensorDescriptor_t* descA, const int32_t* modeA, const void* beta,
+                          const void* C, const hiptensorTensorDescriptor_t* descC, const int32_t* modeC, void* D,
+                          const hiptensorTensorDescriptor_t* descD, const int32_t* modeD, int opReduce,
+                          int typeComputeI, void* stream)
+{
+    const char* fn = "htReductionNoAlloc";
+    const auto typeCompute = hiptensorComputeType_t(typeComputeI);
+    if(!handle || !alpha || !A || !descA || !modeA || !beta || !descC || !D || !descD)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    const HandleState* st = stateOf(handle);
+    if(!st)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    const auto tA = descA->mType;
+    const bool typesOk
+        = (tA == descC->mType && tA == descD->mType)
+          && ((tA == HIP_R_16F && (typeCompute == HIPTENSOR_COMPUTE_16F || typeCompute == HIPTENSOR_COMPUTE_32F))
+              || (tA == HIP_R_16BF && (typeCompute == HIPTENSOR_COMPUTE_16BF || typeCompute == HIPTENSOR_COMPUTE_32F))
+              || (tA == HIP_R_32F && typeCompute == HIPTENSOR_COMPUTE_32F)
+              || (tA == HIP_R_64F && typeCompute == HIPTENSOR_COMPUTE_64F));
+    if(!typesOk)
+        return HIPTENSOR_STATUS_NOT_SUPPORTED;
+    const int rankA = int(descA->mLengths.size()), rankD = int(descD->mLengths.size());
+    if(rankA < 1 || rankA > kMaxGroup || rankD > rankA || descC->mLengths != descD->mLengths
+       || descC->mStrides != descD->mStrides || (rankD > 0 && !modeD && !modeC))
+        return HIPTENSOR_STATUS_NOT_SUPPORTED;
+    if(opReduce != HIPTENSOR_OP_ADD && opReduce != HIPTENSOR_OP_MUL && opReduce != HIPTENSOR_OP_MIN
+       && opReduce != HIPTENSOR_OP_MAX)
+        return HIPTENSOR_STATUS_INTERNAL_ERROR;
+    if(auto s = checkDevice(fn, st); s != HIPTENSOR_STATUS_SUCCESS)
+        return s;
+    int64_t lA[kMaxGroup], sA[kMaxGroup], lD[kMaxGroup], sD[kMaxGroup];
+    for(int i = 0; i < rankA; i++)
+    {
+        lA[i] = int64_t(descA->mLengths[i]);
+        sA[i] = int64_t(descA->mStrides[i]);
+    }
+    for(int i = 0; i < rankD; i++)
+    {
+        lD[i] = int64_t(descD->mLengths[i]);
+        sD[i] = int64_t(descD->mStrides[i]);
+    }
+    ReducePlan plan;
+    const bool aligned = ((uintptr_t(A) | uintptr_t(C) | uintptr_t(D)) & 15) == 0;
+    int rc = planReduction(rankA, lA, sA, modeA, rankD, lD, sD, modeD ? modeD : modeC, dtypeSize(tA), aligned,
+                           st->smCount, &plan);
+    if(rc != PLAN_OK)
+        return rc;
+    const int internalCompute = (typeCompute == HIPTENSOR_COMPUTE_64F) ? HIPTENSOR_COMPUTE_64F : HIPTENSOR_COMPUTE_32F;
+    const uint64_t need = reductionWorkspaceBytes(plan, internalCompute);
+    if(need > kStaticScratchBytes)
+    {
+        HTB_LOG_ERROR(fn, "this reduction needs %llu bytes of scratch, the built-in scratch holds %llu: use "
+                          "hiptensorReduction with a caller workspace (%s)",
+                      (unsigned long long)need, (unsigned long long)kStaticScratchBytes,
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_INSUFFICIENT_WORKSPACE));
+        return HIPTENSOR_STATUS_INSUFFICIENT_WORKSPACE;
+    }
+    double alphaD = 0, betaD = 0;
+    if(!readScalar(alpha, int(typeCompute), &alphaD) || !readScalar(beta, int(typeCompute), &betaD))
+        return HIPTENSOR_STATUS_NOT_SUPPORTED;
+    cudaError_t e = launchReductionStaticScratch(plan, int(tA), internalCompute, opReduce, alphaD, A, betaD, C ? C : D,
+                                                 D, st->device, cudaStream_t(stream));
+    if(e != cudaSuccess)
+    {
+        HTB_LOG_ERROR(fn, "launch failed: %s (%s)", cudaGetErrorString(e),
+                      hiptensorGetErrorString(HIPTENSOR_STATUS_HIP_ERROR));
+        return HIPTENSOR_STATUS_HIP_ERROR;
+    }
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
 // ---------------------------------------------------------------------------- contraction
 hiptensorStatus_t hiptensorInitContractionDescriptor(
     const hiptensorHandle_t* handle, hiptensorContractionDescriptor_t* desc,

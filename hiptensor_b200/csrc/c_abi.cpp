@@ -212,6 +212,15 @@ int htReduction(const htHandle* handle, const void* alpha, const void* A, const 
                               workspaceSize, hipStream_t(stream));
 }
 
+int htReductionNoAlloc(const htHandle* handle, const void* alpha, const void* A, const htTensorDescriptor* descA,
+                       const int32_t* modeA, const void* beta, const void* C, const htTensorDescriptor* descC,
+                       const int32_t* modeC, void* D, const htTensorDescriptor* descD, const int32_t* modeD,
+                       int opReduce, int typeCompute, void* stream)
+{
+    return htb::reductionNoAlloc(H(handle), alpha, A, TD(descA), modeA, beta, C, TD(descC), modeC, D, TD(descD),
+                                 modeD, opReduce, typeCompute, stream);
+}
+
 int htReductionGetWorkspaceSize(const htHandle* handle, const void* A, const htTensorDescriptor* descA,
                                 const int32_t* modeA, const void* C, const htTensorDescriptor* descC,
                                 const int32_t* modeC, const void* D, const htTensorDescriptor* descD,

@@ -27,6 +27,22 @@ namespace htb
                                 cudaStream_t stream);
     uint64_t    reductionWorkspaceBytes(const ReducePlan& plan, int computeType);
 
+    // Same reduction, with the two-pass scratch taken from a fixed array inside the library
+    // instead of from the caller (no allocation anywhere on this path). The first call on a
+    // device looks the array's device address up.
+    constexpr uint64_t kStaticScratchBytes = 8192;
+    constexpr int      kMaxDevices         = 64;
+    cudaError_t launchReductionStaticScratch(const ReducePlan& plan, int typeA, int computeType, int op, double alpha,
+                                             const void* A, double beta, const void* C, void* D, int device,
+                                             cudaStream_t stream);
+
+    // body of the flat entry point htReductionNoAlloc (api.cpp)
+    int reductionNoAlloc(const hiptensorHandle_t* handle, const void* alpha, const void* A,
+                         const hiptensorTensorDescriptor_t* descA, const int32_t* modeA, const void* beta,
+                         const void* C, const hiptensorTensorDescriptor_t* descC, const int32_t* modeC, void* D,
+                         const hiptensorTensorDescriptor_t* descD, const int32_t* modeD, int opReduce,
+                         int typeCompute, void* stream);
+
     // A/B are the caller's operands in the caller's order; the plan says whether to swap.
     cudaError_t launchContraction(const ContractionPlan& plan, float alpha, const void* A, const void* B,
                                   float beta, const void* C, void* D, void* workspace, int smCount,

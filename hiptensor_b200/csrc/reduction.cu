@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include <cfloat>
+#include <mutex>
 #include <type_traits>
 
 #include "kernels.hpp"
@@ -591,6 +592,40 @@ namespace htb
             return cudaErrorInvalidValue;
         }
     } // namespace
+
+    // ------------------------------------------------------------------ built-in scratch
+    // Scratch for the two-pass reduction that lives inside the library image instead of in
+    // memory the caller allocates. Every device that loads the library carries these bytes
+    // until the process exits; all calls on a device share them.
+    static __device__ __align__(256) unsigned char gReduceScratch[kStaticScratchBytes];
+
+    cudaError_t launchReductionStaticScratch(const ReducePlan& plan, int typeA, int computeType, int op, double alpha,
+                                             const void* A, double beta, const void* C, void* D, int device,
+                                             cudaStream_t stream)
+    {
+        // In host code the array's name is only a handle for the runtime, not a device address.
+        // The address is looked up once per device, with that device current, and kept.
+        static std::mutex lock;
+        static void*      address[kMaxDevices] = {};
+        if(device < 0 || device >= kMaxDevices)
+            return cudaErrorInvalidDevice;
+        void* scratch = nullptr;
+        {
+            std::lock_guard<std::mutex> guard(lock);
+            if(address[device] == nullptr)
+            {
+                void*       p = nullptr;
+                cudaError_t e = cudaGetSymbolAddress(&p, gReduceScratch);
+                if(e != cudaSuccess)
+                    return e;
+                address[device] = p;
+            }
+            scratch = address[device];
+        }
+        // pass 1 writes every partial slot that pass 2 reads, so nothing has to start at zero
+        return launchReduction(plan, typeA, computeType, op, alpha, A, beta, C, D, plan.split > 1 ? scratch : nullptr,
+                               stream);
+    }
 
     uint64_t reductionWorkspaceBytes(const ReducePlan& plan, int computeType)
     {

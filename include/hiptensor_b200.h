@@ -93,6 +93,27 @@ int htReductionGetWorkspaceSize(const htHandle* handle, const void* A, const htT
                                 const int32_t* modeC, const void* D, const htTensorDescriptor* descD,
                                 const int32_t* modeD, int opReduce, int typeCompute, uint64_t* workspaceSize);
 
+/* No counterpart in the reference. hiptensorReduction for callers that are not allowed to allocate
+ * device memory while they work: a plug-in inside a host application that has claimed the whole device
+ * heap, a latency-critical loop where cudaMalloc's implicit device synchronisation is not acceptable, a
+ * service whose policy forbids device allocations once start-up is over. The scratch of the two-pass reduction (few outputs, long reduced
+ * range) is a fixed 8 KiB array inside the library, present on every device that loads the library until
+ * the process ends; the call makes no cudaMalloc / cudaFree and uses no caller workspace. Inputs and
+ * outputs are still the caller's. Limits and rules:
+ *  - a reduction whose two-pass scratch would exceed 8 KiB returns 19 (INSUFFICIENT_WORKSPACE) and does
+ *    nothing; use htReduction with a workspace for it (on B200 this only concerns fp64 reductions with
+ *    several hundred outputs);
+ *  - the first call on a device looks up the array's device address; make that first call outside any
+ *    stream capture;
+ *  - all calls on one device share the array, and it keeps the last call's contents. Nothing in it needs
+ *    clearing (the first pass overwrites every slot the second pass reads), but two such calls that run
+ *    at the same time on one device (different streams) race on it: keep them on one stream or order
+ *    them with events. */
+int htReductionNoAlloc(const htHandle* handle, const void* alpha, const void* A, const htTensorDescriptor* descA,
+                       const int32_t* modeA, const void* beta, const void* C, const htTensorDescriptor* descC,
+                       const int32_t* modeC, void* D, const htTensorDescriptor* descD, const int32_t* modeD,
+                       int opReduce, int typeCompute, void* stream);
+
 /* hiptensor.hpp:308-338 (library/src/logger.cpp). mask: OR of 1 error, 2 perf, 4 hint, 8 heuristics, 16 api. */
 int htLoggerSetMask(int32_t mask);
 int htLoggerOpenFile(const char* logFile);
