@@ -642,13 +642,15 @@ hiptensorStatus_t hiptensorContractionGetWorkspaceSize(const hiptensorHandle_t* 
                                                        const hiptensorWorksizePreference_t     pref,
                                                        uint64_t*                               workspaceSize)
 {
-    (void)pref;
     if(!handle || !desc || !find || !workspaceSize)
         return HIPTENSOR_STATUS_NOT_INITIALIZED;
     *workspaceSize = 0;
     ContractionPlan    plan;
     const HandleState* st = stateOf(handle);
-    if(buildContractionPlan(desc, st ? st->smCount : 148, &plan) == HIPTENSOR_STATUS_SUCCESS)
+    // every kernel runs without scratch (WORKSPACE_MIN = 0); the recommended size lets the
+    // tensor-core kernel split the tiles of its last wave along K
+    if(pref != HIPTENSOR_WORKSPACE_MIN
+       && buildContractionPlan(desc, st ? st->smCount : 148, &plan) == HIPTENSOR_STATUS_SUCCESS)
         *workspaceSize = plan.workspaceBytes;
     return HIPTENSOR_STATUS_SUCCESS;
 }
@@ -681,6 +683,8 @@ hiptensorStatus_t hiptensorInitContractionPlan(const hiptensorHandle_t* handle, 
         HTB_LOG_ERROR(fn, "No kernel can run this contraction (%s)", hiptensorGetErrorString(hiptensorStatus_t(rc)));
         return hiptensorStatus_t(rc);
     }
+    if(cp.workspaceBytes > workspaceSize)
+        cp.workspaceBytes = 0; // planned for the workspace the caller said it has: no split
     HTB_LOG_HEUR(fn, "%s", describe(cp).c_str());
     plan->mSolution        = const_cast<ContractionPlan*>(registry().intern(cp));
     plan->mContractionDesc = *desc;
@@ -743,8 +747,10 @@ hiptensorStatus_t hiptensorContraction(const hiptensorHandle_t* handle, const hi
         }
         readScalar(beta, cp->computeType, &betaD);
     }
-    cudaError_t e = launchContraction(*cp, float(alphaD), A, B, float(betaD), bilinear ? C : nullptr, D, workspace,
-                                      st->smCount, st->deviceStatus, stream);
+    // scratch is used only up to what the plan was made for
+    cudaError_t e = launchContraction(*cp, float(alphaD), A, B, float(betaD), bilinear ? C : nullptr, D,
+                                      cp->workspaceBytes ? workspace : nullptr, cp->workspaceBytes, st->smCount,
+                                      st->deviceStatus, stream);
     if(e != cudaSuccess)
     {
         HTB_LOG_ERROR(fn, "kernel launch failed: %s (%s)", cudaGetErrorString(e),

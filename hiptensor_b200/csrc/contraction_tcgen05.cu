@@ -19,7 +19,8 @@
 // Every mbarrier wait is bounded by a clock limit; when it runs out the kernel raises the
 // device status word, skips the remaining work and still frees its tensor memory.
 //
-// No cluster launch and no multicast loads: every CTA loads its own operands.
+// A second kernel (further down) runs 256 x 256 tiles on pairs of CTAs. Neither uses multicast loads:
+// every CTA fetches its own operands.
 // It stands where the reference instantiates CK's xdl contraction kernels for f16/bf16
 // (library/src/contraction/device/*f16*_instance.cpp, *bf16*_instance.cpp).
 #include <cuda.h>
@@ -56,7 +57,8 @@ namespace htb
             float   alpha, beta;
             int     bilinear;
             int     nContig; // N is one folded mode with stride 1 in D and D is 16-byte aligned
-            int     probe; // measurement aid: 1 = producer skips the loads, 2 = issuer skips the MMAs (results invalid)
+            int     probe; // measurement aid, bit mask: 1 = producer skips the loads, 2 = issuer skips the MMAs,
+                           // 4 = epilogue skips the stores (results invalid)
             int*    status;
         };
 
@@ -280,8 +282,8 @@ namespace htb
                             cA[0] = kb * kTileK;
                             cB[0] = kb * kTileK;
                             const uint32_t dstA = smemAddr(tiles + size_t(stage) * stageStride);
-                            tmaLoadRank(a.nm + 1, dstA, &mapA, bar, cA);
-                            tmaLoadRank(a.nn + 1, dstA + aBytes, &mapB, bar, cB);
+                            tmaLoad<5>(dstA, &mapA, bar, cA);
+                            tmaLoad<5>(dstA + aBytes, &mapB, bar, cB);
                             if(++stage == a.stages)
                             {
                                 stage = 0;
@@ -465,7 +467,43 @@ namespace htb
         {
             TcArgs base; // boxN / tilesPerDimN / tilesN describe 128-row N sub-tiles here
             int    pairsM, pairsN;
+            int    iters; // pipeline stages per whole tile: ceil(K blocks / blocks per stage)
+            // Tail split. The first fullUnits work units are whole tiles. The tiles that would form a
+            // last, partly filled wave are cut into `parts` ranges of K blocks each, one unit per
+            // range: part 0 owns the tile (adds the other parts' partial sums, applies alpha/beta,
+            // writes D); parts 1.. write their raw accumulators to a scratch slot and raise the tile's
+            // flag. All units of the last wave run at the same time on different CTA pairs.
+            int    fullUnits, numUnits, parts;
+            float* slots; // [tail tile][part-1][256 rows][256 columns] fp32
+            int*   flags; // one counter per tail tile, zeroed before the launch
         };
+
+        struct TcUnit
+        {
+            int tile, kbBegin, kbEnd, part, tail; // stage range [kbBegin, kbEnd); tail: index of the split tile or -1
+        };
+        __device__ __forceinline__ TcUnit unitOf(const TcPairArgs& pa, int u)
+        {
+            TcUnit w;
+            if(u < pa.fullUnits)
+            {
+                w.tile    = u;
+                w.kbBegin = 0;
+                w.kbEnd   = pa.iters;
+                w.part    = 0;
+                w.tail    = -1;
+            }
+            else
+            {
+                const int x = u - pa.fullUnits;
+                w.tail      = x / pa.parts;
+                w.part      = x % pa.parts;
+                w.tile      = pa.fullUnits + w.tail;
+                w.kbBegin   = int((long long)pa.iters * w.part / pa.parts);
+                w.kbEnd     = int((long long)pa.iters * (w.part + 1) / pa.parts);
+            }
+            return w;
+        }
 
         __device__ __forceinline__ uint32_t clusterRank()
         {
@@ -485,43 +523,60 @@ namespace htb
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         }
 
-        template <int RANK>
-        __device__ __forceinline__ void tmaLoadPair(uint32_t dst, const CUtensorMap* map, uint32_t bar, const int* c)
+        // bounded wait for the two single-thread roles: a tight try_wait loop, the clock is read
+        // only every 256th unsuccessful poll
+#ifndef HTB_TC_SPIN
+#define HTB_TC_SPIN 0
+#endif
+        constexpr bool kSpinWaits = HTB_TC_SPIN != 0; // poll with test_wait instead of the suspending try_wait
+        __device__ __forceinline__ bool mbarWaitTight(uint32_t bar, uint32_t parity, volatile int* abortFlag)
         {
-            if constexpr(RANK == 2)
-                asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-                             "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1])
-                             : "memory");
-            else if constexpr(RANK == 3)
-                asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-                             "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
-                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2])
-                             : "memory");
-            else if constexpr(RANK == 4)
-                asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-                             "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
-                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3])
-                             : "memory");
-            else
-                asm volatile("cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-                             "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
-                             "l"(map), "r"(bar), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]), "r"(c[4])
-                             : "memory");
-        }
-        __device__ __forceinline__ void tmaLoadPairRank(int rank, uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                                        const int* c)
-        {
-            switch(rank)
+            long long t0 = 0;
+            for(uint32_t it = 1;; it++)
             {
-            case 2: tmaLoadPair<2>(dst, map, bar, c); break;
-            case 3: tmaLoadPair<3>(dst, map, bar, c); break;
-            case 4: tmaLoadPair<4>(dst, map, bar, c); break;
-            default: tmaLoadPair<5>(dst, map, bar, c); break;
+                uint32_t done;
+                if(kSpinWaits)
+                    asm volatile("{\n\t.reg .pred p;\n\t"
+                                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                                 "selp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(done)
+                                 : "r"(bar), "r"(parity)
+                                 : "memory");
+                else
+                    asm volatile("{\n\t.reg .pred p;\n\t"
+                                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                                 "selp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(done)
+                                 : "r"(bar), "r"(parity)
+                                 : "memory");
+                if(done)
+                    return true;
+                if((it & 255) == 0)
+                {
+                    if(t0 == 0)
+                        t0 = clock64();
+                    if(*abortFlag)
+                        return false;
+                    if(clock64() - t0 > kWaitCycles)
+                    {
+                        *abortFlag = 1;
+                        return false;
+                    }
+                }
             }
         }
 
-        template <typename TD>
+        __device__ __forceinline__ void tmaLoadPair5(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                                     int c2, int c3, int c4)
+        {
+            asm volatile("cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                         "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(dst),
+                         "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+                         : "memory");
+        }
+
+        // KSUB: 64-wide K blocks per pipeline stage (1: six 32 KiB stages, 2: three 64 KiB stages)
+        template <typename TD, int KSUB>
         __global__ void __launch_bounds__(kThreads, 1)
             contraction_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
                                             const __grid_constant__ CUtensorMap mapB, const TD* __restrict__ C,
@@ -540,9 +595,8 @@ namespace htb
             const int      warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
             const uint32_t rank = clusterRank();
             const bool     leader = (rank == 0);
-            constexpr uint32_t kHalfBytes = 128 * kTileK * 2; // 16 KiB: A rows, or this CTA's half of B
-            constexpr uint32_t kStage     = 2 * kHalfBytes;
-            const int      numPairs    = pa.pairsM * pa.pairsN;
+            constexpr uint32_t kHalfBytes = 128 * kTileK * 2; // 16 KiB: 128 rows of one 64-wide K block
+            constexpr uint32_t kStage     = 2 * KSUB * kHalfBytes; // A blocks, then this CTA's half of the B blocks
             const int      clusterId   = blockIdx.x >> 1;
             const int      numClusters = gridDim.x >> 1;
 
@@ -574,46 +628,54 @@ namespace htb
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tmem   = tmemBase;
             volatile int*  abortP = &abortFlag;
+            const uint32_t tilesAddr = smemAddr(tiles);
+            const uint32_t fullAddr = smemAddr(&fullBar[0]), emptyAddr = smemAddr(&emptyBar[0]);
 
             if(warp == 0)
             {
                 // ---------------------------------------------------------------- TMA producer
                 if(lane == 0)
                 {
-                    int      stage = 0;
-                    uint32_t phase = 0;
-                    bool     ok    = true;
-                    for(int t = clusterId; t < numPairs && ok; t += numClusters)
+                    const uint32_t leaderFull = mapToRank(fullAddr, 0);
+                    const uint32_t txBytes    = 2 * KSUB * a.stageBytes; // both CTAs' boxes of one stage
+                    uint32_t       stage = 0, phase = 0;
+                    bool           ok = true;
+                    for(int u = clusterId; u < pa.numUnits && ok; u += numClusters)
                     {
-                        const int pm = t % pa.pairsM, pn = t / pa.pairsM;
-                        const int tm = min(2 * pm + int(rank), a.tilesM - 1);
-                        const int tn = min(2 * pn + int(rank), a.tilesN - 1);
-                        int       cA[5] = {0, 0, 0, 0, 0}, cB[5] = {0, 0, 0, 0, 0};
-                        tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cA + 1);
-                        tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB + 1);
-                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        const TcUnit w  = unitOf(pa, u);
+                        const int    pm = w.tile % pa.pairsM, pn = w.tile / pa.pairsM;
+                        const int    tm = min(2 * pm + int(rank), a.tilesM - 1);
+                        const int    tn = min(2 * pn + int(rank), a.tilesN - 1);
+                        int          cA[4] = {0, 0, 0, 0}, cB[4] = {0, 0, 0, 0};
+                        tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cA);
+                        tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB);
+                        const int a1 = cA[0], a2 = cA[1], a3 = cA[2], a4 = cA[3];
+                        const int b1 = cB[0], b2 = cB[1], b3 = cB[2], b4 = cB[3];
+                        for(int it = w.kbBegin; it < w.kbEnd; it++)
                         {
-                            ok = mbarWait(smemAddr(&emptyBar[stage]), phase ^ 1, abortP);
+                            ok = mbarWaitTight(emptyAddr + 8 * stage, phase ^ 1, abortP);
                             if(!ok)
                                 break;
-                            const uint32_t localBar  = smemAddr(&fullBar[stage]);
-                            const uint32_t leaderBar = mapToRank(localBar, 0);
-                            if(a.probe == 1)
+                            if(a.probe & 1)
                             {
                                 if(leader)
-                                    mbarArrive(localBar);
+                                    mbarArrive(fullAddr + 8 * stage);
                             }
                             else
                             {
                                 if(leader)
-                                    mbarArriveExpectTx(localBar, 2 * a.stageBytes); // both CTAs' boxes
-                                cA[0] = kb * kTileK;
-                                cB[0] = kb * kTileK;
-                                const uint32_t dstA = smemAddr(tiles + size_t(stage) * kStage);
-                                tmaLoadPairRank(a.nm + 1, dstA, &mapA, leaderBar, cA);
-                                tmaLoadPairRank(a.nn + 1, dstA + kHalfBytes, &mapB, leaderBar, cB);
+                                    mbarArriveExpectTx(fullAddr + 8 * stage, txBytes);
+                                const uint32_t bar = leaderFull + 8 * stage;
+                                const uint32_t dst = tilesAddr + stage * kStage;
+#pragma unroll
+                                for(int q = 0; q < KSUB; q++)
+                                {
+                                    const int k0 = (it * KSUB + q) * kTileK; // beyond K: the box is zero-filled
+                                    tmaLoadPair5(dst + q * kHalfBytes, &mapA, bar, k0, a1, a2, a3, a4);
+                                    tmaLoadPair5(dst + (KSUB + q) * kHalfBytes, &mapB, bar, k0, b1, b2, b3, b4);
+                                }
                             }
-                            if(++stage == a.stages)
+                            if(++stage == uint32_t(a.stages))
                             {
                                 stage = 0;
                                 phase ^= 1;
@@ -627,46 +689,50 @@ namespace htb
                 // ---------------------------------------------------------------- MMA issuer (leader CTA)
                 if(lane == 0 && leader)
                 {
-                    int      stage = 0;
-                    uint32_t phase = 0;
-                    int      local = 0;
-                    bool     ok    = true;
-                    for(int t = clusterId; t < numPairs && ok; t += numClusters, local++)
+                    const uint64_t descBase = smemDesc(tilesAddr);
+                    uint32_t       stage = 0, phase = 0;
+                    int            local = 0;
+                    bool           ok    = true;
+                    for(int u = clusterId; u < pa.numUnits && ok; u += numClusters, local++)
                     {
+                        const TcUnit   w        = unitOf(pa, u);
                         const int      acc      = local & 1;
                         const uint32_t accPhase = (local >> 1) & 1;
-                        ok = mbarWait(smemAddr(&tmemEmptyBar[acc]), accPhase ^ 1, abortP);
+                        ok = mbarWaitTight(smemAddr(&tmemEmptyBar[acc]), accPhase ^ 1, abortP);
                         if(!ok)
                             break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint32_t dTmem = tmem + uint32_t(acc * 256);
-                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        for(int it = w.kbBegin; it < w.kbEnd; it++)
                         {
-                            ok = mbarWait(smemAddr(&fullBar[stage]), phase, abortP);
+                            ok = mbarWaitTight(fullAddr + 8 * stage, phase, abortP);
                             if(!ok)
                                 break;
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                            const uint32_t sa    = smemAddr(tiles + size_t(stage) * kStage);
-                            const uint64_t descA = smemDesc(sa), descB = smemDesc(sa + kHalfBytes);
-#pragma unroll
-                            for(int k = 0; k < kTileK / 16; k++)
+                            // descriptor address field counts 16-byte units
+                            const uint64_t descA = descBase + uint64_t((stage * kStage) >> 4);
+                            const uint64_t descB = descA + uint64_t((KSUB * kHalfBytes) >> 4);
+                            if(!(a.probe & 2))
                             {
-                                if(a.probe == 2)
-                                    break;
-                                const uint32_t accumulate = (kb | k) ? 1u : 0u;
-                                asm volatile("{\n\t.reg .pred p;\n\t"
-                                             "setp.ne.b32 p, %4, 0;\n\t"
-                                             "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
-                                             "l"(descA + uint64_t(2 * k)), "l"(descB + uint64_t(2 * k)), "r"(idesc),
-                                             "r"(accumulate)
-                                             : "memory");
+#pragma unroll
+                                for(int k = 0; k < KSUB * (kTileK / 16); k++)
+                                {
+                                    // 16 elements = 32 bytes = 2 units inside a 64-wide block; blocks are 16 KiB apart
+                                    const uint64_t off = uint64_t((k / 4) * (kHalfBytes >> 4) + 2 * (k % 4));
+                                    const uint32_t accumulate = (it != w.kbBegin || k != 0) ? 1u : 0u;
+                                    asm volatile("{\n\t.reg .pred p;\n\t"
+                                                 "setp.ne.b32 p, %4, 0;\n\t"
+                                                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
+                                                 "l"(descA + off), "l"(descB + off), "r"(idesc), "r"(accumulate)
+                                                 : "memory");
+                                }
                             }
                             // frees the stage in both CTAs once these MMAs have read it
                             asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
-                                         "[%0], %1;" ::"r"(smemAddr(&emptyBar[stage])),
+                                         "[%0], %1;" ::"r"(emptyAddr + 8 * stage),
                                          "h"((unsigned short)3)
                                          : "memory");
-                            if(++stage == a.stages)
+                            if(++stage == uint32_t(a.stages))
                             {
                                 stage = 0;
                                 phase ^= 1;
@@ -687,11 +753,12 @@ namespace htb
                 const int row  = quad * 32 + lane;
                 int64_t*  cols = colOff[quad];
                 int       local = 0;
-                for(int t = clusterId; t < numPairs; t += numClusters, local++)
+                for(int u = clusterId; u < pa.numUnits; u += numClusters, local++)
                 {
+                    const TcUnit   w        = unitOf(pa, u);
                     const int      acc      = local & 1;
                     const uint32_t accPhase = (local >> 1) & 1;
-                    const int      pm = t % pa.pairsM, pn = t / pa.pairsM;
+                    const int      pm = w.tile % pa.pairsM, pn = w.tile / pa.pairsM;
                     const int      tmRaw = 2 * pm + int(rank);
                     const bool     dupM  = tmRaw >= a.tilesM; // this CTA repeats its peer's rows: no stores
                     const int      tm    = min(tmRaw, a.tilesM - 1);
@@ -716,6 +783,38 @@ namespace htb
                         break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(acc * 256);
+                    // scratch rows of this thread in a split tile: row = CTA rank * 128 + TMEM lane
+                    float* slotRow = nullptr;
+                    if(w.tail >= 0)
+                    {
+                        slotRow = pa.slots + (size_t(w.tail) * (pa.parts - 1)) * 65536 + size_t(rank * 128 + row) * 256;
+                        if(w.part == 0)
+                        {
+                            // owner: the other parts' partial sums must be in the scratch (8 warps each)
+                            int ready = 1;
+                            if(lane == 0)
+                            {
+                                const int       want = (pa.parts - 1) * 8;
+                                const long long t0   = clock64();
+                                for(;;)
+                                {
+                                    int seen;
+                                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(pa.flags + w.tail) : "memory");
+                                    if(seen >= want)
+                                        break;
+                                    if(*abortP || clock64() - t0 > kWaitCycles)
+                                    {
+                                        *abortP = 1;
+                                        ready   = 0;
+                                        break;
+                                    }
+                                }
+                            }
+                            ready = __shfl_sync(0xffffffffu, ready, 0);
+                            if(!ready)
+                                break;
+                        }
+                    }
                     for(int c0 = 0; c0 < 256; c0 += 32)
                     {
                         uint32_t v[32];
@@ -730,6 +829,32 @@ namespace htb
                               "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                             : "r"(taddr + uint32_t(c0)));
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if(w.tail >= 0)
+                        {
+                            if(w.part > 0)
+                            {
+                                // contributor: raw accumulators to this part's scratch slot
+                                float4* dst = (float4*)(slotRow + size_t(w.part - 1) * 65536 + c0);
+#pragma unroll
+                                for(int j = 0; j < 8; j++)
+                                    dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                         __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                                continue;
+                            }
+                            for(int q = 0; q < pa.parts - 1; q++)
+                            {
+                                const float4* src = (const float4*)(slotRow + size_t(q) * 65536 + c0);
+#pragma unroll
+                                for(int j = 0; j < 8; j++)
+                                {
+                                    const float4 p4 = src[j];
+                                    v[4 * j]     = __float_as_uint(__uint_as_float(v[4 * j]) + p4.x);
+                                    v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + p4.y);
+                                    v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + p4.z);
+                                    v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + p4.w);
+                                }
+                            }
+                        }
                         if(offM < 0)
                             continue;
                         const int64_t first     = cols[c0];
@@ -769,6 +894,14 @@ namespace htb
                             }
                         }
                     }
+                    if(w.tail >= 0 && w.part > 0)
+                    {
+                        // publish this warp's rows of the partial sum
+                        __threadfence();
+                        __syncwarp();
+                        if(lane == 0)
+                            atomicAdd(pa.flags + w.tail, 1);
+                    }
                     // hand the accumulator back: every epilogue thread of the pair arrives on the leader's barrier
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     const uint32_t emptyAddr = mapToRank(smemAddr(&tmemEmptyBar[acc]), 0);
@@ -789,6 +922,9 @@ namespace htb
             }
         }
 
+        // Tensor map of one operand: dimension 0 is K (contiguous), dimensions 1.. are the folded
+        // modes of the row group. The map always has rank 5 (missing dimensions have extent 1) so
+        // that the kernels use one fixed form of the load instruction with register coordinates.
         bool encodeOperand(PFN_encodeTiled encode, CUtensorMap* map, const void* base, bool bf16, int64_t K,
                            const ModeDim* dims, int n, const int* box)
         {
@@ -796,16 +932,17 @@ namespace htb
             cuuint32_t bx[5], estr[5] = {1, 1, 1, 1, 1};
             gdim[0] = cuuint64_t(K);
             bx[0]   = kTileK;
-            for(int d = 0; d < n; d++)
+            for(int d = 0; d < 4; d++)
             {
-                gdim[d + 1] = cuuint64_t(dims[d].ext);
-                // a degenerate mode (extent 1) may carry stride 0: any 16-byte multiple is legal
-                gstr[d]   = (dims[d].ext == 1) ? cuuint64_t(K) * 2 : cuuint64_t(dims[d].s0) * 2;
-                bx[d + 1] = cuuint32_t(box[d]);
+                const bool real = d < n && dims[d].ext > 1;
+                gdim[d + 1]     = real ? cuuint64_t(dims[d].ext) : 1;
+                // a degenerate mode may carry stride 0: any 16-byte multiple is legal for extent 1
+                gstr[d]   = real ? cuuint64_t(dims[d].s0) * 2 : cuuint64_t(K) * 2;
+                bx[d + 1] = (d < n) ? cuuint32_t(box[d]) : 1;
                 if(gstr[d] % 16 != 0 || gstr[d] == 0)
                     return false;
             }
-            return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, n + 1,
+            return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
                           const_cast<void*>(base), gdim, gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
@@ -828,7 +965,8 @@ namespace htb
 
         template <typename TD>
         cudaError_t launchTyped(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
-                                const void* C, void* D, int smCount, int* status, cudaStream_t stream)
+                                const void* C, void* D, void* workspace, uint64_t workspaceBytes, int smCount,
+                                int* status, cudaStream_t stream)
         {
             PFN_encodeTiled encode = tensorMapEncoder();
             if(!encode)
@@ -874,9 +1012,17 @@ namespace htb
                 pa.pairsN = (a.tilesN + 1) / 2;
                 const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(256 >> 3) << 17)
                                        | (uint32_t(256 >> 4) << 24);
-                const size_t smem = size_t(a.stages) * 2 * 128 * kTileK * 2 + 1024;
-                cudaError_t  e    = cudaFuncSetAttribute(contraction_tcgen05_pair_kernel<TD>,
-                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+                // two 64-wide K blocks per stage (three 64 KiB stages) beat one (six 32 KiB stages) by 8 %
+                // on 4096^3: the same bytes are in flight with half as many barrier round trips
+                int ksub = 2;
+                if(const char* env = getenv("HTB_TC_KSUB"))
+                    ksub = atoi(env) == 1 ? 1 : 2;
+                a.stages  = 6 / ksub;
+                pa.base   = a;
+                pa.iters  = (a.kBlocks + ksub - 1) / ksub;
+                auto kernel = (ksub == 2) ? contraction_tcgen05_pair_kernel<TD, 2> : contraction_tcgen05_pair_kernel<TD, 1>;
+                const size_t smem = size_t(6) * 2 * 128 * kTileK * 2 + 1024;
+                cudaError_t  e    = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
                 if(e != cudaSuccess)
                     return e;
                 cudaLaunchConfig_t cfg{};
@@ -896,7 +1042,7 @@ namespace htb
                 {
                     cfg.gridDim = dim3(unsigned(sms / 2 * 2));
                     int n       = 0;
-                    if(cudaOccupancyMaxActiveClusters(&n, contraction_tcgen05_pair_kernel<TD>, &cfg) != cudaSuccess || n <= 0)
+                    if(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0)
                     {
                         cudaGetLastError();
                         n = sms / 2;
@@ -906,8 +1052,32 @@ namespace htb
                 const int64_t pairs    = int64_t(pa.pairsM) * pa.pairsN;
                 const int     clusters = int(std::min<int64_t>(pairs, maxClusters));
                 cfg.gridDim            = dim3(unsigned(2 * clusters));
-                e = cudaLaunchKernelEx(&cfg, contraction_tcgen05_pair_kernel<TD>, mapA, mapB, (const TD*)C, (TD*)D, pa,
-                                       idesc);
+                // tail split, if the caller's workspace can hold its scratch
+                pa.fullUnits = int(pairs);
+                pa.numUnits  = int(pairs);
+                pa.parts     = 1;
+                {
+                    int       parts;
+                    uint64_t  bytes;
+                    const int tail = tailSplit(pairs, maxClusters, pa.iters, &parts, &bytes);
+                    if(tail > 0 && workspace != nullptr && bytes <= workspaceBytes && (uintptr_t(workspace) & 15) == 0
+                       && getenv("HTB_TC_NOSPLIT") == nullptr)
+                    {
+                        pa.fullUnits = int(pairs - tail);
+                        pa.parts     = parts;
+                        pa.numUnits  = pa.fullUnits + tail * parts;
+                        pa.flags     = (int*)workspace;
+                        pa.slots     = (float*)((char*)workspace + 1024);
+                        e            = cudaMemsetAsync(workspace, 0, 1024, stream);
+                        if(e != cudaSuccess)
+                            return e;
+                        if(tail > 256)
+                            return cudaErrorInvalidConfiguration;
+                    }
+                    HTB_LOG_HEUR("hiptensorContraction", "pair kernel: %lld tiles on %d CTA pairs, tail %d tiles in %d parts, %d work units",
+                                 (long long)pairs, maxClusters, tail, pa.parts, pa.numUnits);
+                }
+                e = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, (const TD*)C, (TD*)D, pa, idesc);
                 if(e == cudaSuccess)
                     noteLaunch("contraction_tcgen05_pair");
                 return e;
@@ -928,15 +1098,20 @@ namespace htb
     } // namespace
 
     cudaError_t launchContractionTcgen05(const ContractionPlan& plan, float alpha, const void* A, const void* B,
-                                         float beta, const void* C, void* D, int smCount, int* deviceStatus,
-                                         cudaStream_t stream)
+                                         float beta, const void* C, void* D, void* workspace, uint64_t workspaceBytes,
+                                         int smCount, int* deviceStatus, cudaStream_t stream)
     {
         switch(plan.typeD)
         {
-        case CUDA_R_32F: return launchTyped<float>(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
-        case CUDA_R_16F: return launchTyped<__half>(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
+        case CUDA_R_32F:
+            return launchTyped<float>(plan, alpha, A, B, beta, C, D, workspace, workspaceBytes, smCount, deviceStatus,
+                                      stream);
+        case CUDA_R_16F:
+            return launchTyped<__half>(plan, alpha, A, B, beta, C, D, workspace, workspaceBytes, smCount, deviceStatus,
+                                       stream);
         case CUDA_R_16BF:
-            return launchTyped<__nv_bfloat16>(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
+            return launchTyped<__nv_bfloat16>(plan, alpha, A, B, beta, C, D, workspace, workspaceBytes, smCount,
+                                              deviceStatus, stream);
         }
         return cudaErrorNotSupported;
     }

@@ -24,8 +24,8 @@
 namespace htb
 {
     cudaError_t launchContractionTcgen05(const ContractionPlan& plan, float alpha, const void* A, const void* B,
-                                         float beta, const void* C, void* D, int smCount, int* deviceStatus,
-                                         cudaStream_t stream);
+                                         float beta, const void* C, void* D, void* workspace, uint64_t workspaceBytes,
+                                         int smCount, int* deviceStatus, cudaStream_t stream);
 
     namespace
     {
@@ -387,10 +387,9 @@ namespace htb
     } // namespace
 
     cudaError_t launchContraction(const ContractionPlan& plan, float alpha, const void* A0, const void* B0,
-                                  float beta, const void* C, void* D, void* workspace, int smCount,
-                                  int* deviceStatus, cudaStream_t stream)
+                                  float beta, const void* C, void* D, void* workspace, uint64_t workspaceBytes,
+                                  int smCount, int* deviceStatus, cudaStream_t stream)
     {
-        (void)workspace;
         if(plan.M == 0 || plan.N == 0)
             return cudaSuccess;
         const void* A = plan.swapped ? B0 : A0;
@@ -399,7 +398,8 @@ namespace htb
         {
             const bool aligned = ((uintptr_t(A) | uintptr_t(B)) & 15) == 0;
             if(aligned)
-                return launchContractionTcgen05(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
+                return launchContractionTcgen05(plan, alpha, A, B, beta, C, D, workspace, workspaceBytes, smCount,
+                                                deviceStatus, stream);
         }
         const int ct = plan.computeType;
         switch(plan.typeA)

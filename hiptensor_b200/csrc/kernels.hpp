@@ -45,6 +45,6 @@ namespace htb
 
     // A/B are the caller's operands in the caller's order; the plan says whether to swap.
     cudaError_t launchContraction(const ContractionPlan& plan, float alpha, const void* A, const void* B,
-                                  float beta, const void* C, void* D, void* workspace, int smCount,
-                                  int* deviceStatus, cudaStream_t stream);
+                                  float beta, const void* C, void* D, void* workspace, uint64_t workspaceBytes,
+                                  int smCount, int* deviceStatus, cudaStream_t stream);
 } // namespace htb

@@ -97,6 +97,28 @@ namespace htb
         return w;
     }
 
+    int tailSplit(int64_t tiles, int clusters, int kBlocks, int* parts, uint64_t* scratchBytes)
+    {
+        *parts        = 1;
+        *scratchBytes = 0;
+        if(clusters <= 0 || tiles <= 0)
+            return 0;
+        // Only a machine that is less than half full is worth splitting. With several waves, cutting
+        // the tiles of the last wave gained nothing on B200 (4096^3: 126 us split, 121 us unsplit):
+        // the partly filled wave already runs faster, and the scratch round trip is not free.
+        if(tiles * 2 > clusters)
+            return 0;
+        const int64_t tail = tiles;
+        int p = int(std::min<int64_t>(4, clusters / tail));
+        while(p > 1 && kBlocks / p < 4)
+            p--;
+        if(p < 2)
+            return 0;
+        *parts        = p;
+        *scratchBytes = 1024 + uint64_t(tail) * uint64_t(p - 1) * 256 * 256 * 4; // flags + fp32 slots
+        return int(tail);
+    }
+
     int boxDecompose(const ModeDim* dims, int n, int tile, int* box)
     {
         int64_t remaining = tile;
@@ -510,6 +532,26 @@ namespace htb
                                     : 0;
             }
             out->kind = tc ? CK_TCGEN05 : CK_TILED_SIMT;
+            if(tc && out->pair)
+            {
+                // scratch for the tail split, sized for the largest need over the pair counts the
+                // device may grant (GPCs with an odd SM count lose a pair)
+                int64_t tilesM = 1, tilesN = 1;
+                for(int i = 0; i < nm; i++)
+                    tilesM *= (gm[i].ext + out->boxM[i] - 1) / out->boxM[i];
+                for(int i = 0; i < nn; i++)
+                    tilesN *= (gn[i].ext + out->boxN128[i] - 1) / out->boxN128[i];
+                const int64_t tiles   = ((tilesM + 1) / 2) * ((tilesN + 1) / 2);
+                const int     kBlocks = int((out->K + 63) / 64);
+                const int     maxC    = (smCount > 0 ? smCount : 148) / 2;
+                for(int c = std::max(1, maxC - 10); c <= maxC; c++)
+                {
+                    int      parts;
+                    uint64_t bytes;
+                    tailSplit(tiles, c, kBlocks, &parts, &bytes);
+                    out->workspaceBytes = std::max(out->workspaceBytes, bytes);
+                }
+            }
         }
         else
         {

@@ -130,6 +130,11 @@ namespace htb
                         int computeType, int smCount, ContractionPlan* out);
     std::string describe(const ContractionPlan& p);
 
+    // K split of the CTA-pair contraction kernel: when `tiles` output tiles fill less than half of the
+    // `clusters` CTA pairs, every tile is cut into `parts` K ranges so that more pairs work. Returns
+    // the number of split tiles (0: no split) and the scratch bytes the split needs.
+    int tailSplit(int64_t tiles, int clusters, int kBlocks, int* parts, uint64_t* scratchBytes);
+
     // Splits `tile` rows over the folded modes of a group, fastest mode first: a mode is taken
     // whole while it is a power of two smaller than what is left, the first mode at least as
     // large as what is left takes the rest (ragged ends are zero-filled by TMA), later modes

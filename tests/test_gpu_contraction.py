@@ -256,3 +256,39 @@ def test_cta_pair_kernel_gathered_odd_tiles(env, dt):
     err = rel_error(got, exp, td)
     assert 0 <= err < 1e-4, (dt, err)
     assert not np.isnan(got).any()
+
+
+@pytest.mark.parametrize("shape", [(512, 768, 1536), (640, 896, 520), (1024, 2304, 2048)])
+def test_cta_pair_kernel_k_split(env, shape):
+    """Fewer tiles than half the CTA pairs: the tiles are cut along K, partial sums travel through the workspace. Same inputs without a workspace (no split) must agree closely, and both
+    must match the oracle."""
+    import torch
+
+    ht, h = env
+    M, N, K = shape
+    m, n, k = 0, 1, 2
+    ext = {m: M, n: N, k: K}
+    smp = np.random.default_rng(7).integers(0, M * N, 4096)
+    got, exp, td = run_contraction(ht, h, ext, [m, k], [n, k], [m, n], typeAB=orc.F16, typeD=orc.F32, alpha=1.5,
+                                   beta=0.5, fill="normal", sample=smp)
+    assert ht.last_kernel_name() == "contraction_tcgen05_pair"
+    assert not np.isnan(got).any()
+    assert 0 <= rel_error(got, exp, td) < 1e-4
+    # the same problem planned with no workspace
+    from helpers import SEED_CONTRACTION as S, to_device, to_host
+
+    lA, lB, lD = [M, K], [N, K], [M, N]
+    A = to_device(orc.fill_normal(M * K, orc.F16, S[0], 0.5), orc.F16)
+    B = to_device(orc.fill_normal(N * K, orc.F16, S[1], 0.5), orc.F16)
+    C = to_device(orc.fill_uniform(M * N, orc.F32, S[2]), orc.F32)
+    D = torch.empty(M * N, device="cuda")
+    dA, dB, dD = (h.tensor_descriptor(l, None, t) for l, t in ((lA, ht.R_16F), (lB, ht.R_16F), (lD, ht.R_32F)))
+    cd = h.contraction_descriptor(dA, [m, k], dB, [n, k], dD, [m, n], dD, [m, n], ht.COMPUTE_32F)
+    find = h.contraction_find()
+    assert h.contraction_workspace_size(cd, find, ht.WORKSPACE_MIN) == 0
+    assert h.contraction_workspace_size(cd, find, ht.WORKSPACE_RECOMMENDED) > 0
+    plan = h.contraction_plan(cd, find, 0)
+    h.contraction(plan, 1.5, A, B, 0.5, C, D)
+    unsplit = to_host(D, orc.F32)
+    # the tensor cores' fp32 accumulation is not associative: regrouping K moves results by a few 1e-5
+    assert 0 <= rel_error(got, unsplit, orc.F32) < 2e-4
