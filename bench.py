@@ -35,8 +35,8 @@ FALLBACK_BF16_TFLOPS = 1590.0
 NOMINAL_FP64_TFLOPS = 40.0  # FP64 tensor pipe, nominal: no measured figure exists for it
 
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the
-# ncu captures summarised under profiles/); None until a capture exists for the workload.
-NCU_TRAFFIC_BYTES = {"c2": None, "c3": None, "c4": None, "c1": None, "c5": None}
+# ncu captures summarised under profiles/, full-size workloads, one launch each).
+NCU_TRAFFIC_BYTES = {"c2": 2113114000, "c3": 2153492640, "c4": 108542464, "c1": 4046848, "c5": 310886656}
 
 
 def peaks():
