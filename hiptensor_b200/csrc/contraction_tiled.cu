@@ -19,6 +19,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "kernels.hpp"
 
 namespace htb
@@ -353,6 +355,220 @@ namespace htb
             }
         }
 
+        // ------------------------------------------------------------------ FP64 tensor-pipe kernel
+        // 128 x 64 output tile per CTA, 8 warps in a 4 x 2 grid, each warp a 32 x 32 tile made of
+        // 4 x 4 mma.sync.m8n8k4.f64 fragments (16 MMAs for 8 shared-memory loads per 4-wide K step).
+        // Operands are gathered exactly as in the kernel above; shared tiles are [k][m + 4] so that
+        // the fragment loads of a half warp fall on 16 different 8-byte banks.
+        constexpr int DM = 128, DN = 64;
+
+        template <int DK>
+        __global__ void __launch_bounds__(THREADS)
+            contraction_dmma_kernel(const double* __restrict__ A, const double* __restrict__ B, const double* C,
+                                    double* D, CtrArgs a)
+        {
+            extern __shared__ __align__(16) unsigned char dsmem[];
+            double(*sA)[DK][DM + PAD] = reinterpret_cast<double(*)[DK][DM + PAD]>(dsmem);
+            double(*sB)[DK][DN + PAD] = reinterpret_cast<double(*)[DK][DN + PAD]>(dsmem + sizeof(double) * 2 * DK * (DM + PAD));
+            __shared__ int64_t offAm[DM], offDm[DM], offBn[DN], offDn[DN];
+            __shared__ int64_t offAk[2][DK], offBk[2][DK];
+
+            const int     tid   = threadIdx.x;
+            const int64_t tileM = blockIdx.x / a.tilesN, tileN = blockIdx.x % a.tilesN;
+            const int64_t m0 = tileM * DM, n0 = tileN * DN;
+
+            if(tid < DM)
+            {
+                const int64_t mm = m0 + tid;
+                int64_t       oa = -1, od = -1;
+                if(mm < a.M)
+                    decompose2(a.m, a.nm, mm, oa, od);
+                offAm[tid] = oa;
+                offDm[tid] = od;
+            }
+            else if(tid < DM + DN)
+            {
+                const int     t  = tid - DM;
+                const int64_t nn = n0 + t;
+                int64_t       ob = -1, od = -1;
+                if(nn < a.N)
+                    decompose2(a.n, a.nn, nn, ob, od);
+                offBn[t] = ob;
+                offDn[t] = od;
+            }
+            auto computeK = [&](int buf, int64_t k0) {
+                if(tid >= DM + DN && tid < DM + DN + DK)
+                {
+                    const int     t  = tid - DM - DN;
+                    const int64_t kk = k0 + t;
+                    int64_t       oa = -1, ob = -1;
+                    if(kk < a.K)
+                        decompose2(a.k, a.nk, kk, oa, ob);
+                    offAk[buf][t] = oa;
+                    offBk[buf][t] = ob;
+                }
+            };
+            computeK(0, 0);
+            __syncthreads();
+
+            constexpr int EA = DM * DK / THREADS, EB = DN * DK / THREADS; // elements per thread and tile
+            double        ra[EA], rb[EB];
+            auto          gload = [&](int buf) {
+#pragma unroll
+                for(int j = 0; j < EA; j++)
+                {
+                    const int idx = tid + THREADS * j;
+                    const int mi  = a.aKfast ? idx / DK : idx % DM;
+                    const int ki  = a.aKfast ? idx % DK : idx / DM;
+                    const int64_t om = offAm[mi], ok = offAk[buf][ki];
+                    ra[j] = (om >= 0 && ok >= 0) ? A[om + ok] : 0.0;
+                }
+#pragma unroll
+                for(int j = 0; j < EB; j++)
+                {
+                    const int idx = tid + THREADS * j;
+                    const int ni  = a.bKfast ? idx / DK : idx % DN;
+                    const int ki  = a.bKfast ? idx % DK : idx / DN;
+                    const int64_t on = offBn[ni], ok = offBk[buf][ki];
+                    rb[j] = (on >= 0 && ok >= 0) ? B[on + ok] : 0.0;
+                }
+            };
+            auto sstore = [&](int buf) {
+#pragma unroll
+                for(int j = 0; j < EA; j++)
+                {
+                    const int idx = tid + THREADS * j;
+                    if(a.aKfast)
+                        sA[buf][idx % DK][idx / DK] = ra[j];
+                    else
+                        sA[buf][idx / DM][idx % DM] = ra[j];
+                }
+#pragma unroll
+                for(int j = 0; j < EB; j++)
+                {
+                    const int idx = tid + THREADS * j;
+                    if(a.bKfast)
+                        sB[buf][idx % DK][idx / DK] = rb[j];
+                    else
+                        sB[buf][idx / DN][idx % DN] = rb[j];
+                }
+            };
+
+            const int64_t nkt = (a.K + DK - 1) / DK;
+            gload(0);
+            sstore(0);
+            computeK(1, DK);
+            __syncthreads();
+
+            double acc[4][4][2];
+#pragma unroll
+            for(int i = 0; i < 4; i++)
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+                    acc[i][j][0] = acc[i][j][1] = 0.0;
+
+            const int lane = tid & 31, warp = tid >> 5;
+            const int wm = warp & 3, wn = warp >> 2;
+
+            for(int64_t kt = 0; kt < nkt; kt++)
+            {
+                const int  cur     = int(kt & 1);
+                const bool hasNext = (kt + 1 < nkt);
+                if(hasNext)
+                    gload(cur ^ 1);
+#pragma unroll
+                for(int k4 = 0; k4 < DK / 4; k4++)
+                {
+                    double    af[4], bf[4];
+                    const int kr = k4 * 4 + (lane & 3);
+#pragma unroll
+                    for(int i = 0; i < 4; i++)
+                        af[i] = sA[cur][kr][wm * 32 + i * 8 + (lane >> 2)];
+#pragma unroll
+                    for(int j = 0; j < 4; j++)
+                        bf[j] = sB[cur][kr][wn * 32 + j * 8 + (lane >> 2)];
+#pragma unroll
+                    for(int i = 0; i < 4; i++)
+#pragma unroll
+                        for(int j = 0; j < 4; j++)
+                            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                                         : "+d"(acc[i][j][0]), "+d"(acc[i][j][1])
+                                         : "d"(af[i]), "d"(bf[j]));
+                }
+                if(hasNext)
+                {
+                    sstore(cur ^ 1);
+                    computeK(cur, (kt + 2) * DK);
+                }
+                __syncthreads();
+            }
+
+#pragma unroll
+            for(int i = 0; i < 4; i++)
+            {
+                const int64_t om = offDm[wm * 32 + i * 8 + (lane >> 2)];
+                if(om < 0)
+                    continue;
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+#pragma unroll
+                    for(int e = 0; e < 2; e++)
+                    {
+                        const int64_t on = offDn[wn * 32 + j * 8 + 2 * (lane & 3) + e];
+                        if(on >= 0)
+                            storeEpilogue<double, double>(D, C, om + on, acc[i][j][e], a.alpha, a.beta, a.bilinear);
+                    }
+            }
+        }
+
+        CtrArgs makeArgs(const ContractionPlan& p, float alpha, float beta, const void* C)
+        {
+            CtrArgs a{};
+            a.nm = p.nm;
+            a.nn = p.nn;
+            a.nk = p.nk;
+            for(int i = 0; i < kMaxGroup; i++)
+            {
+                a.m[i] = p.m[i];
+                a.n[i] = p.n[i];
+                a.k[i] = p.k[i];
+            }
+            a.M        = p.M;
+            a.N        = p.N;
+            a.K        = p.K;
+            a.alpha    = alpha;
+            a.beta     = beta;
+            a.bilinear = (p.bilinear && C != nullptr) ? 1 : 0;
+            a.aKfast   = (p.k[0].s0 == 1 && p.k[0].ext > 1) ? 1 : 0;
+            a.bKfast   = (p.k[0].s1 == 1 && p.k[0].ext > 1) ? 1 : 0;
+            return a;
+        }
+
+        template <int DK>
+        cudaError_t launchDmma(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
+                               const void* C, void* D, cudaStream_t stream)
+        {
+            CtrArgs       a      = makeArgs(p, alpha, beta, C);
+            const int64_t tilesM = (p.M + DM - 1) / DM, tilesN = (p.N + DN - 1) / DN;
+            if(tilesM * tilesN > 0x7fffffffll)
+                return cudaErrorInvalidConfiguration;
+            a.tilesN          = int(tilesN);
+            const size_t smem = sizeof(double) * 2 * DK * (DM + PAD + DN + PAD);
+            static bool  attr = false;
+            if(!attr)
+            {
+                cudaError_t e = cudaFuncSetAttribute(contraction_dmma_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     int(smem));
+                if(e != cudaSuccess)
+                    return e;
+                attr = true;
+            }
+            contraction_dmma_kernel<DK><<<unsigned(tilesM * tilesN), THREADS, smem, stream>>>(
+                (const double*)A, (const double*)B, (const double*)C, (double*)D, a);
+            noteLaunch("contraction_tiled_dmma");
+            return cudaGetLastError();
+        }
+
         template <typename TA, typename TD, typename TAcc, int ROUND, bool DMMA>
         cudaError_t launchTiled(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
                                 const void* C, void* D, cudaStream_t stream)
@@ -412,7 +628,12 @@ namespace htb
             return launchTiled<float, float, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
         case CUDA_R_64F:
             if(ct == HIPTENSOR_COMPUTE_64F)
-                return launchTiled<double, double, double, 0, true>(plan, alpha, A, B, beta, C, D, stream);
+            {
+                if(const char* env = getenv("HTB_DMMA_BK"))
+                    if(atoi(env) == 32)
+                        return launchDmma<32>(plan, alpha, A, B, beta, C, D, stream);
+                return launchDmma<16>(plan, alpha, A, B, beta, C, D, stream);
+            }
             return launchTiled<double, double, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
         case CUDA_R_16F:
             if(plan.typeD == CUDA_R_32F)
