@@ -1,13 +1,13 @@
 // Gathered tiled contraction kernel for sm_100a:  D = alpha * (A x B) + beta * C  on the
 // folded (M, N, K) view of arbitrary mode lists.
 //
-// One CTA owns a 64x64 tile of the folded output. Row/column offsets of the tile (M and N
+// One CTA owns a tile of the folded output. Row/column offsets of the tile (M and N
 // multi-indices decomposed over the folded modes) are computed once into shared memory; K
-// offsets are computed per 16-wide K step. Operand tiles are gathered from the strided
-// tensors straight into shared memory (converted through the compute type), double
-// buffered with a register prefetch, and consumed either by
-//   - an FMA micro-kernel with a strided 4x4 register tile per thread (fp32 accumulate), or
-//   - the FP64 tensor pipe (mma.sync m8n8k4 f64) with 32x16 warp tiles.
+// offsets are computed per K step. Operand tiles are gathered from the strided tensors
+// straight into shared memory (converted through the compute type), double buffered with
+// a register prefetch, and consumed either by
+//   - an FMA micro-kernel, 64x64 tile, 4x4 register tile per thread (fp32 accumulate), or
+//   - the FP64 tensor pipe (mma.sync m8n8k4 f64), 128x64 tile, 32x32 warp tiles.
 // The epilogue rounds the accumulator to the output type first and then applies
 // alpha*x + beta*c, which is the order of the reference's CPU implementation
 // (library/src/contraction/contraction_cpu_reference_impl.hpp:406-425).
@@ -31,7 +31,9 @@ namespace htb
 
     namespace
     {
-        constexpr int BM = 64, BN = 64, BK = 16, PAD = 4, THREADS = 256;
+        constexpr int BM = 64, BN = 64, BK = 32, PAD = 4, THREADS = 256;
+        constexpr int NL     = BM * BK / THREADS; // elements of each operand tile gathered per thread and K step
+        constexpr int KSLOTS = 4; // ring of K-offset tables (steps kt .. kt+3 are live at once)
 
         struct CtrArgs
         {
@@ -129,19 +131,33 @@ namespace htb
             }
         }
 
-        template <typename TA, typename TD, typename TAcc, int ROUND, bool DMMA>
+        // ------------------------------------------------------------------ FMA kernel
+        // 64 x 64 output tile per CTA, 256 threads, a contiguous 4 x 4 register tile per thread read
+        // from shared memory with 128-bit loads. The K loop runs in steps of 32 with two shared
+        // buffers and two register sets: the gather of step kt+2 is issued before the arithmetic of
+        // step kt and is stored to shared memory after the arithmetic of step kt+1, so that every
+        // global load has two compute phases to land in.
+        template <typename TA, typename TD, int ROUND>
         __global__ void __launch_bounds__(THREADS)
-            contraction_tiled_kernel(const TA* __restrict__ A, const TA* __restrict__ B, const TD* C, TD* D, CtrArgs a)
+            contraction_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ B, const TD* C, TD* D, CtrArgs a)
         {
-            __shared__ TAcc    sA[2][BK][BM + PAD];
-            __shared__ TAcc    sB[2][BK][BN + PAD];
-            __shared__ int64_t offAm[BM], offDm[BM], offBn[BN], offDn[BN];
-            __shared__ int64_t offAk[2][BK], offBk[2][BK];
+            __shared__ __align__(16) float sA[2][BK][BM + PAD];
+            __shared__ __align__(16) float sB[2][BK][BN + PAD];
+            __shared__ int64_t             offAm[BM], offDm[BM], offBn[BN], offDn[BN];
+            __shared__ int64_t             offAk[KSLOTS][BK], offBk[KSLOTS][BK];
 
             const int     tid   = threadIdx.x;
             const int64_t tileM = blockIdx.x / a.tilesN, tileN = blockIdx.x % a.tilesN;
             const int64_t m0 = tileM * BM, n0 = tileN * BN;
 
+            auto computeK = [&](int slot, int64_t k0, int t) {
+                const int64_t kk = k0 + t;
+                int64_t       oa = -1, ob = -1;
+                if(kk < a.K)
+                    decompose2(a.k, a.nk, kk, oa, ob);
+                offAk[slot][t] = oa;
+                offBk[slot][t] = ob;
+            };
             if(tid < BM)
             {
                 const int64_t mm = m0 + tid;
@@ -161,196 +177,146 @@ namespace htb
                 offBn[t] = ob;
                 offDn[t] = od;
             }
-            auto computeK = [&](int buf, int64_t k0) {
-                if(tid >= BM + BN && tid < BM + BN + BK)
-                {
-                    const int     t  = tid - BM - BN;
-                    const int64_t kk = k0 + t;
-                    int64_t       oa = -1, ob = -1;
-                    if(kk < a.K)
-                        decompose2(a.k, a.nk, kk, oa, ob);
-                    offAk[buf][t] = oa;
-                    offBk[buf][t] = ob;
-                }
-            };
-            computeK(0, 0);
+            else if(tid < BM + BN + 3 * BK)
+            {
+                const int t = tid - BM - BN; // K offsets of the first three steps
+                computeK(t / BK, int64_t(t / BK) * BK, t % BK);
+            }
             __syncthreads();
 
-            TAcc ra[4], rb[4];
-            auto gload = [&](int buf) {
+            auto gload = [&](int64_t step, float(&ra)[NL], float(&rb)[NL]) {
+                const int slot = int(step & (KSLOTS - 1));
 #pragma unroll
-                for(int j = 0; j < 4; j++)
+                for(int j = 0; j < NL; j++)
                 {
-                    int mi, ki;
-                    if(a.aKfast)
-                    {
-                        ki = tid & 15;
-                        mi = (tid >> 4) + 16 * j;
-                    }
-                    else
-                    {
-                        mi = tid & 63;
-                        ki = (tid >> 6) + 4 * j;
-                    }
-                    const int64_t om = offAm[mi], ok = offAk[buf][ki];
-                    ra[j] = (om >= 0 && ok >= 0) ? loadConv<TAcc, TA, ROUND>(A, om + ok) : TAcc(0);
-                    int ni, kj;
-                    if(a.bKfast)
-                    {
-                        kj = tid & 15;
-                        ni = (tid >> 4) + 16 * j;
-                    }
-                    else
-                    {
-                        ni = tid & 63;
-                        kj = (tid >> 6) + 4 * j;
-                    }
-                    const int64_t on = offBn[ni], ok2 = offBk[buf][kj];
-                    rb[j] = (on >= 0 && ok2 >= 0) ? loadConv<TAcc, TA, ROUND>(B, on + ok2) : TAcc(0);
+                    const int     idx = tid + THREADS * j;
+                    const int     mi  = a.aKfast ? idx / BK : idx % BM;
+                    const int     ki  = a.aKfast ? idx % BK : idx / BM;
+                    const int64_t om = offAm[mi], ok = offAk[slot][ki];
+                    ra[j]            = (om >= 0 && ok >= 0) ? loadConv<float, TA, ROUND>(A, om + ok) : 0.f;
+                    const int     ni  = a.bKfast ? idx / BK : idx % BN;
+                    const int     kj  = a.bKfast ? idx % BK : idx / BN;
+                    const int64_t on = offBn[ni], ok2 = offBk[slot][kj];
+                    rb[j]            = (on >= 0 && ok2 >= 0) ? loadConv<float, TA, ROUND>(B, on + ok2) : 0.f;
                 }
             };
-            auto sstore = [&](int buf) {
+            auto sstore = [&](int buf, const float(&ra)[NL], const float(&rb)[NL]) {
 #pragma unroll
-                for(int j = 0; j < 4; j++)
+                for(int j = 0; j < NL; j++)
                 {
+                    const int idx = tid + THREADS * j;
                     if(a.aKfast)
-                        sA[buf][tid & 15][(tid >> 4) + 16 * j] = ra[j];
+                        sA[buf][idx % BK][idx / BK] = ra[j];
                     else
-                        sA[buf][(tid >> 6) + 4 * j][tid & 63] = ra[j];
+                        sA[buf][idx / BM][idx % BM] = ra[j];
                     if(a.bKfast)
-                        sB[buf][tid & 15][(tid >> 4) + 16 * j] = rb[j];
+                        sB[buf][idx % BK][idx / BK] = rb[j];
                     else
-                        sB[buf][(tid >> 6) + 4 * j][tid & 63] = rb[j];
+                        sB[buf][idx / BN][idx % BN] = rb[j];
                 }
             };
 
             const int64_t nkt = (a.K + BK - 1) / BK;
-            gload(0);
-            sstore(0);
-            computeK(1, BK);
-            __syncthreads();
-
-            // accumulators
-            TAcc      acc[4][4]; // SIMT: [i][j];  DMMA: [i][2*j + e] (i: 4 m-frags, j: 2 n-frags)
+            const int     tx = tid & 15, ty = tid >> 4;
+            float         r0a[NL], r0b[NL], r1a[NL], r1b[NL];
+            float         acc[4][4];
 #pragma unroll
             for(int i = 0; i < 4; i++)
 #pragma unroll
                 for(int j = 0; j < 4; j++)
-                    acc[i][j] = TAcc(0);
+                    acc[i][j] = 0.f;
 
-            const int tx = tid & 15, ty = tid >> 4; // SIMT mapping
-            const int lane = tid & 31, warp = tid >> 5;
-            const int wm = warp & 1, wn = warp >> 1; // DMMA mapping
+            gload(0, r0a, r0b);
+            sstore(0, r0a, r0b);
+            if(nkt > 1)
+                gload(1, r1a, r1b);
+            __syncthreads();
 
-            for(int64_t kt = 0; kt < nkt; kt++)
-            {
-                const int  cur     = int(kt & 1);
-                const bool hasNext = (kt + 1 < nkt);
-                if(hasNext)
-                    gload(cur ^ 1);
-                if constexpr(DMMA)
-                {
-#pragma unroll
-                    for(int k4 = 0; k4 < BK / 4; k4++)
-                    {
-                        double af[4], bf[2];
-                        const int kr = k4 * 4 + (lane & 3);
-#pragma unroll
-                        for(int i = 0; i < 4; i++)
-                            af[i] = sA[cur][kr][wm * 32 + i * 8 + (lane >> 2)];
-#pragma unroll
-                        for(int j = 0; j < 2; j++)
-                            bf[j] = sB[cur][kr][wn * 16 + j * 8 + (lane >> 2)];
-#pragma unroll
-                        for(int i = 0; i < 4; i++)
-#pragma unroll
-                            for(int j = 0; j < 2; j++)
-                            {
-                                asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, "
-                                             "{%0,%1};"
-                                             : "+d"(acc[i][2 * j]), "+d"(acc[i][2 * j + 1])
-                                             : "d"(af[i]), "d"(bf[j]));
-                            }
-                    }
-                }
-                else
-                {
-                    // the 16 products of a K step are summed on their own and then added to the
-                    // running total: short partial sums keep the fp32 rounding error of long
-                    // contractions well below that of one sequential sum
-                    TAcc part[4][4];
-#pragma unroll
-                    for(int i = 0; i < 4; i++)
-#pragma unroll
-                        for(int j = 0; j < 4; j++)
-                            part[i][j] = TAcc(0);
-#pragma unroll
-                    for(int kk = 0; kk < BK; kk++)
-                    {
-                        TAcc av[4], bv[4];
-#pragma unroll
-                        for(int i = 0; i < 4; i++)
-                            av[i] = sA[cur][kk][ty + 16 * i];
-#pragma unroll
-                        for(int j = 0; j < 4; j++)
-                            bv[j] = sB[cur][kk][tx + 16 * j];
-#pragma unroll
-                        for(int i = 0; i < 4; i++)
-#pragma unroll
-                            for(int j = 0; j < 4; j++)
-                                part[i][j] += av[i] * bv[j];
-                    }
-#pragma unroll
-                    for(int i = 0; i < 4; i++)
-#pragma unroll
-                        for(int j = 0; j < 4; j++)
-                            acc[i][j] += part[i][j];
-                }
-                if(hasNext)
-                {
-                    sstore(cur ^ 1);
-                    computeK(cur, (kt + 2) * BK);
-                }
-                __syncthreads();
-            }
-
-            // epilogue
-            if constexpr(DMMA)
-            {
+            // one K step: `held` carries step kt+1 (loaded one iteration ago), `fresh` receives kt+2
+            auto iteration = [&](int64_t kt, int cur, float(&heldA)[NL], float(&heldB)[NL], float(&freshA)[NL],
+                                 float(&freshB)[NL]) {
+                if(kt + 2 < nkt)
+                    gload(kt + 2, freshA, freshB);
+                // the 32 products of a K step are summed on their own and then added to the running
+                // total: short partial sums keep the fp32 rounding error of long contractions well
+                // below that of one sequential sum
+                float part[4][4];
 #pragma unroll
                 for(int i = 0; i < 4; i++)
-                {
-                    const int     mi = wm * 32 + i * 8 + (lane >> 2);
-                    const int64_t om = offDm[mi];
-                    if(om < 0)
-                        continue;
-#pragma unroll
-                    for(int j = 0; j < 2; j++)
-#pragma unroll
-                        for(int e = 0; e < 2; e++)
-                        {
-                            const int     ni = wn * 16 + j * 8 + 2 * (lane & 3) + e;
-                            const int64_t on = offDn[ni];
-                            if(on >= 0)
-                                storeEpilogue<TD, TAcc>(D, C, om + on, acc[i][2 * j + e], a.alpha, a.beta, a.bilinear);
-                        }
-                }
-            }
-            else
-            {
-#pragma unroll
-                for(int i = 0; i < 4; i++)
-                {
-                    const int64_t om = offDm[ty + 16 * i];
-                    if(om < 0)
-                        continue;
 #pragma unroll
                     for(int j = 0; j < 4; j++)
+                        part[i][j] = 0.f;
+#pragma unroll
+                for(int kk = 0; kk < BK; kk++)
+                {
+                    const float4 av4   = *reinterpret_cast<const float4*>(&sA[cur][kk][ty * 4]);
+                    const float4 bv4   = *reinterpret_cast<const float4*>(&sB[cur][kk][tx * 4]);
+                    const float  av[4] = {av4.x, av4.y, av4.z, av4.w};
+                    const float  bv[4] = {bv4.x, bv4.y, bv4.z, bv4.w};
+#pragma unroll
+                    for(int i = 0; i < 4; i++)
+#pragma unroll
+                        for(int j = 0; j < 4; j++)
+                            part[i][j] += av[i] * bv[j];
+                }
+#pragma unroll
+                for(int i = 0; i < 4; i++)
+#pragma unroll
+                    for(int j = 0; j < 4; j++)
+                        acc[i][j] += part[i][j];
+                if(kt + 1 < nkt)
+                    sstore(cur ^ 1, heldA, heldB);
+                if(kt + 3 < nkt && tid >= BM + BN && tid < BM + BN + BK)
+                    computeK(int((kt + 3) & (KSLOTS - 1)), (kt + 3) * BK, tid - BM - BN);
+                __syncthreads();
+            };
+            for(int64_t kt = 0; kt < nkt; kt += 2)
+            {
+                iteration(kt, 0, r1a, r1b, r0a, r0b);
+                if(kt + 1 < nkt)
+                    iteration(kt + 1, 1, r0a, r0b, r1a, r1b);
+            }
+
+            // epilogue: four consecutive N positions per thread, written as one 128-bit store when
+            // D (and C) are contiguous and aligned there
+#pragma unroll
+            for(int i = 0; i < 4; i++)
+            {
+                const int64_t om = offDm[ty * 4 + i];
+                if(om < 0)
+                    continue;
+                const int64_t on0 = offDn[tx * 4], on3 = offDn[tx * 4 + 3];
+                if constexpr(sizeof(TD) == 4)
+                {
+                    const int64_t off = om + on0;
+                    bool          vec = on0 >= 0 && on3 == on0 + 3 && ((uintptr_t(D + off) & 15) == 0);
+                    if(a.bilinear)
+                        vec = vec && ((uintptr_t(C + off) & 15) == 0);
+                    if(vec)
                     {
-                        const int64_t on = offDn[tx + 16 * j];
-                        if(on >= 0)
-                            storeEpilogue<TD, TAcc>(D, C, om + on, acc[i][j], a.alpha, a.beta, a.bilinear);
+                        float4 y;
+                        y.x = __fmul_rn(a.alpha, acc[i][0]);
+                        y.y = __fmul_rn(a.alpha, acc[i][1]);
+                        y.z = __fmul_rn(a.alpha, acc[i][2]);
+                        y.w = __fmul_rn(a.alpha, acc[i][3]);
+                        if(a.bilinear)
+                        {
+                            const float4 c = *reinterpret_cast<const float4*>(C + off);
+                            y.x            = __fadd_rn(y.x, __fmul_rn(a.beta, c.x));
+                            y.y            = __fadd_rn(y.y, __fmul_rn(a.beta, c.y));
+                            y.z            = __fadd_rn(y.z, __fmul_rn(a.beta, c.z));
+                            y.w            = __fadd_rn(y.w, __fmul_rn(a.beta, c.w));
+                        }
+                        *reinterpret_cast<float4*>(D + off) = y;
+                        continue;
                     }
+                }
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+                {
+                    const int64_t on = offDn[tx * 4 + j];
+                    if(on >= 0)
+                        storeEpilogue<TD, float>(D, C, om + on, acc[i][j], a.alpha, a.beta, a.bilinear);
                 }
             }
         }
@@ -569,7 +535,7 @@ namespace htb
             return cudaGetLastError();
         }
 
-        template <typename TA, typename TD, typename TAcc, int ROUND, bool DMMA>
+        template <typename TA, typename TD, int ROUND>
         cudaError_t launchTiled(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
                                 const void* C, void* D, cudaStream_t stream)
         {
@@ -595,9 +561,9 @@ namespace htb
             if(tilesM * tilesN > 0x7fffffffll)
                 return cudaErrorInvalidConfiguration;
             a.tilesN = int(tilesN);
-            contraction_tiled_kernel<TA, TD, TAcc, ROUND, DMMA>
+            contraction_simt_kernel<TA, TD, ROUND>
                 <<<unsigned(tilesM * tilesN), THREADS, 0, stream>>>((const TA*)A, (const TA*)B, (const TD*)C, (TD*)D, a);
-            noteLaunch(DMMA ? "contraction_tiled_dmma" : "contraction_tiled_simt");
+            noteLaunch("contraction_tiled_simt");
             return cudaGetLastError();
         }
     } // namespace
@@ -622,10 +588,10 @@ namespace htb
         {
         case CUDA_R_32F:
             if(ct == HIPTENSOR_COMPUTE_16F)
-                return launchTiled<float, float, float, 1, false>(plan, alpha, A, B, beta, C, D, stream);
+                return launchTiled<float, float, 1>(plan, alpha, A, B, beta, C, D, stream);
             if(ct == HIPTENSOR_COMPUTE_16BF)
-                return launchTiled<float, float, float, 2, false>(plan, alpha, A, B, beta, C, D, stream);
-            return launchTiled<float, float, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
+                return launchTiled<float, float, 2>(plan, alpha, A, B, beta, C, D, stream);
+            return launchTiled<float, float, 0>(plan, alpha, A, B, beta, C, D, stream);
         case CUDA_R_64F:
             if(ct == HIPTENSOR_COMPUTE_64F)
             {
@@ -634,15 +600,15 @@ namespace htb
                         return launchDmma<32>(plan, alpha, A, B, beta, C, D, stream);
                 return launchDmma<16>(plan, alpha, A, B, beta, C, D, stream);
             }
-            return launchTiled<double, double, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
+            return launchTiled<double, double, 0>(plan, alpha, A, B, beta, C, D, stream);
         case CUDA_R_16F:
             if(plan.typeD == CUDA_R_32F)
-                return launchTiled<__half, float, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
-            return launchTiled<__half, __half, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
+                return launchTiled<__half, float, 0>(plan, alpha, A, B, beta, C, D, stream);
+            return launchTiled<__half, __half, 0>(plan, alpha, A, B, beta, C, D, stream);
         case CUDA_R_16BF:
             if(plan.typeD == CUDA_R_32F)
-                return launchTiled<__nv_bfloat16, float, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
-            return launchTiled<__nv_bfloat16, __nv_bfloat16, float, 0, false>(plan, alpha, A, B, beta, C, D, stream);
+                return launchTiled<__nv_bfloat16, float, 0>(plan, alpha, A, B, beta, C, D, stream);
+            return launchTiled<__nv_bfloat16, __nv_bfloat16, 0>(plan, alpha, A, B, beta, C, D, stream);
         }
         return cudaErrorInvalidValue;
     }
