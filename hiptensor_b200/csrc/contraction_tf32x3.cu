@@ -1,0 +1,880 @@
+// Tensor-core contraction for fp32 operands on sm_100a with fp32-grade accuracy (the "3xTF32" split):
+//
+//   D[m, n] = alpha * sum_k A[m, k] * B[n, k]  (+ beta * C[m, n]),   A, B, C, D fp32, compute type fp32.
+//
+// Every operand element x is split into big = tf32(x) and small = tf32(x - big); the tensor cores
+// accumulate  small_a*big_b + big_a*small_b + big_a*big_b  in fp32 in tensor memory. The dropped
+// small*small term is below 2^-22 of the product, i.e. below fp32 rounding of the sum.
+//
+// kind::tf32 takes K-major shared-memory operands only, so the split doubles as the layout change:
+//   TMA            strided tensor -> staging tile, in whichever order the operand is contiguous:
+//                    K-major operand  : one box  [rows x 32 k], 128-byte swizzle, rows gathered over the
+//                                       folded modes of the row group;
+//                    MN-major operand : one box per 32 rows [32 k x 32 rows], the 32 rows being
+//                                       consecutive elements of the group's stride-1 mode;
+//   converter      4 warps, one thread per tile row: read the row from staging (conflict-free in
+//                  both orders), split, write the big and the small row into the K-major,
+//                  128-byte-swizzled operand ring;
+//   tcgen05.mma    three MMAs per 8-wide K step from the ring into the accumulator;
+//   epilogue       tcgen05.ld, alpha/beta, stores to the strided D.
+//
+// Warp roles (320 threads): 0 TMA producer, 1 MMA issuer + tensor-memory owner, 2-5 epilogue,
+// 6-9 converter. PAIR = true runs a 256 x 256 tile on a cluster of two CTAs (cta_group::2): each
+// CTA stages and converts its own 128 rows of A and 128 of the 256 rows of B; the leader CTA issues
+// the MMAs for both. Loads carry no multicast qualifier.
+//
+// All mbarrier waits are bounded; on a timeout the kernel raises the device status word, skips the
+// remaining work and frees its tensor memory.
+//
+// It stands where the reference instantiates CK's xdl contraction kernels for f32
+// (library/src/contraction/device/*f32_f32_f32_f32*_instance.cpp, compute type f32).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdlib>
+
+#include "kernels.hpp"
+#include "tcgen05_util.cuh"
+
+namespace htb
+{
+    namespace
+    {
+        constexpr int      kTfThreads    = 320;
+        constexpr int      kTfK          = 32; // fp32 elements per K block = one 128-byte swizzle row
+        constexpr int      kStagingSlots = 2, kOpSlots = 2;
+        constexpr uint32_t kTileBytes    = 128 * kTfK * 4; // 16 KiB: 128 rows of one K block
+        constexpr uint32_t kStagingBytes = 2 * kTileBytes; // A rows, B rows
+        constexpr uint32_t kOpBytes      = 4 * kTileBytes; // A big, A small, B big, B small
+
+        // One row group of the tile: the M side (rows of A and D) or the N side (rows of B, columns of D).
+        struct TfGroup
+        {
+            int     major; // 0: operand K-major, rows gathered by a TMA box over the folded modes
+                           // 1: operand MN-major, rows taken in chunks of 32 along the stride-1 mode 0
+            int     n; // folded modes
+            int     rows; // rows of this group per CTA tile (128, or 64 for a narrow N tile)
+            int     tiles;
+            int     box[4], tilesPerDim[4]; // major 0
+            int     chunks0; // major 1: 32-row chunks along mode 0
+            int64_t restExt; // major 1: product of the extents of modes 1..
+            int64_t ext[4], sD[4];
+        };
+
+        struct TfArgs
+        {
+            TfGroup  gm, gn;
+            int      boxK[2], kTilesPerDim[2]; // K block -> coordinates of the (at most two) folded K modes
+            int      kBlocks;
+            uint32_t bytesA, bytesB; // TMA bytes per K block into one CTA's staging slot
+            float    alpha, beta;
+            int      bilinear;
+            int      nContig; // 32 consecutive columns of a tile are 32 consecutive, 16-byte aligned floats of D
+            int      pairsM, pairsN; // PAIR only
+            int*     status;
+        };
+
+        // position of a tile inside its group
+        struct TfTile
+        {
+            int c[4]; // major 0: first coordinate per mode
+            int chunkBase; // major 1: first chunk
+        };
+
+        __device__ __forceinline__ TfTile tfTileOf(const TfGroup& g, int t)
+        {
+            TfTile w;
+            w.chunkBase = t * (g.rows >> 5);
+#pragma unroll
+            for(int d = 0; d < 4; d++)
+            {
+                const int per = (d < g.n) ? g.tilesPerDim[d] : 1;
+                w.c[d]        = (t % per) * ((d < g.n) ? g.box[d] : 1);
+                t /= per;
+            }
+            return w;
+        }
+
+        // row r of a tile -> offset in D along this group, or -1 outside the tensor
+        __device__ __forceinline__ int64_t tfRowOffset(const TfGroup& g, const TfTile& w, int r)
+        {
+            if(g.major == 0)
+            {
+                int64_t off = 0;
+                for(int d = 0; d < g.n; d++)
+                {
+                    const int i = r % g.box[d];
+                    r /= g.box[d];
+                    const int64_t x = int64_t(w.c[d]) + i;
+                    if(x >= g.ext[d])
+                        return -1;
+                    off += x * g.sD[d];
+                }
+                return (r == 0) ? off : -1;
+            }
+            const int     chunk = w.chunkBase + (r >> 5);
+            const int64_t i0    = int64_t(chunk % g.chunks0) * 32 + (r & 31);
+            int64_t       rest  = chunk / g.chunks0;
+            if(i0 >= g.ext[0] || rest >= g.restExt)
+                return -1;
+            int64_t off = i0 * g.sD[0];
+            for(int d = 1; d < g.n; d++)
+            {
+                off += (rest % g.ext[d]) * g.sD[d];
+                rest /= g.ext[d];
+            }
+            return off;
+        }
+
+        // TMA loads of one operand's rows of one K block into a staging tile
+        //   major 0 map: {K, mode0, mode1, mode2, mode3}         one box
+        //   major 1 map: {mode0, k0, k1, mode1, mode2}           one box per 32-row chunk
+        __device__ __forceinline__ void tfLoadRows(const TfGroup& g, const TfTile& w, const CUtensorMap* map, uint32_t dst,
+                                                   uint32_t bar, int kb, const TfArgs& a)
+        {
+            if(g.major == 0)
+            {
+                const int c[5] = {kb * kTfK, w.c[0], w.c[1], w.c[2], w.c[3]};
+                tmaLoad<5>(dst, map, bar, c);
+                return;
+            }
+            const int kc0 = (kb % a.kTilesPerDim[0]) * a.boxK[0];
+            const int kc1 = (kb / a.kTilesPerDim[0]) * a.boxK[1];
+            const int64_t e1 = (g.n > 1) ? g.ext[1] : 1;
+            for(int q = 0; q < (g.rows >> 5); q++)
+            {
+                const int     chunk = w.chunkBase + q;
+                const int64_t rest  = chunk / g.chunks0;
+                // beyond the tensor the coordinates fall outside the map and the box is zero-filled
+                const int c[5] = {(chunk % g.chunks0) * 32, kc0, kc1, int(rest % e1), int(rest / e1)};
+                tmaLoad<5>(dst + uint32_t(q) * (kTfK * 128), map, bar, c);
+            }
+        }
+
+        __device__ __forceinline__ void tfSplit(float x, float& big, float& small)
+        {
+            uint32_t b, s;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(b) : "f"(x));
+            big = __uint_as_float(b);
+            // an infinite big (x infinite, or rounded up past the largest finite value) must not make a NaN
+            const float rest = (fabsf(big) == INFINITY) ? 0.f : x - big;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(s) : "f"(rest));
+            small = __uint_as_float(s);
+        }
+
+        __device__ __forceinline__ float4 lds128(uint32_t addr)
+        {
+            float4 v;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+            return v;
+        }
+        __device__ __forceinline__ float lds32(uint32_t addr)
+        {
+            float v;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+            return v;
+        }
+        __device__ __forceinline__ void sts128(uint32_t addr, float4 v)
+        {
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+        }
+
+        // One thread converts row r of a 128 x 32 tile: staging -> (big, small) in the K-major ring layout, where
+        // the 16-byte piece j of row r sits at r*128 + ((j ^ (r & 7)) << 4). Within a quarter warp the eight rows
+        // touch eight different pieces, so the 128-bit accesses are free of bank conflicts.
+        __device__ __forceinline__ void tfConvertRow(int major, uint32_t src, uint32_t dstBig, uint32_t dstSmall, int r)
+        {
+            const uint32_t rowOff = uint32_t(r) * 128;
+            if(major == 0)
+            {
+                // staging has the ring layout already (TMA 128-byte swizzle)
+#pragma unroll
+                for(int j = 0; j < 8; j++)
+                {
+                    const uint32_t off = rowOff + (uint32_t(j ^ (r & 7)) << 4);
+                    const float4   v   = lds128(src + off);
+                    float4         b, s;
+                    tfSplit(v.x, b.x, s.x);
+                    tfSplit(v.y, b.y, s.y);
+                    tfSplit(v.z, b.z, s.z);
+                    tfSplit(v.w, b.w, s.w);
+                    sts128(dstBig + off, b);
+                    sts128(dstSmall + off, s);
+                }
+            }
+            else
+            {
+                // staging: chunk r/32 holds [32 k][32 rows], unswizzled; the lanes of a warp read 32 consecutive floats
+                const uint32_t col = src + uint32_t(r >> 5) * (kTfK * 128) + uint32_t(r & 31) * 4;
+                float          x[kTfK];
+#pragma unroll
+                for(int k = 0; k < kTfK; k++)
+                    x[k] = lds32(col + uint32_t(k) * 128);
+#pragma unroll
+                for(int j = 0; j < 8; j++)
+                {
+                    const uint32_t off = rowOff + (uint32_t(j ^ (r & 7)) << 4);
+                    float4         b, s;
+                    tfSplit(x[4 * j], b.x, s.x);
+                    tfSplit(x[4 * j + 1], b.y, s.y);
+                    tfSplit(x[4 * j + 2], b.z, s.z);
+                    tfSplit(x[4 * j + 3], b.w, s.w);
+                    sts128(dstBig + off, b);
+                    sts128(dstSmall + off, s);
+                }
+            }
+        }
+
+        // every thread of the warp polls: the data behind the barrier is then visible to each of them
+        __device__ __forceinline__ bool mbarWaitAll(uint32_t bar, uint32_t parity, volatile int* abortFlag)
+        {
+            const bool ok = mbarWait(bar, parity, abortFlag);
+            return __all_sync(0xffffffffu, ok);
+        }
+
+        // Accumulation. The tensor cores add each 8-wide group of products to the fp32 accumulator with
+        // truncation, which over a long K would cost several digits. So
+        //   * the two correction products (small*big, big*small), whose sum is 2^-11 of the result and whose
+        //     truncation error is therefore negligible, go to an accumulator of their own for the whole tile;
+        //   * the main product (big*big) is accumulated over kSegBlocks K blocks only, then the epilogue warps
+        //     add that segment to running sums held in registers (round to nearest) while the tensor cores
+        //     fill the other segment accumulator.
+        // Tensor memory, 512 columns per CTA: segment accumulators at columns 0 and 128, correction
+        // accumulators (double buffered across tiles) at 256 and 384.
+        constexpr int kSegBlocks = 2;
+
+        template <bool PAIR>
+        __global__ void __launch_bounds__(kTfThreads, 1)
+            contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                                      const float* __restrict__ C, float* __restrict__ D, TfArgs a, uint32_t idesc)
+        {
+            extern __shared__ unsigned char smemRaw[];
+            unsigned char* tiles = (unsigned char*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
+
+            __shared__ __align__(8) unsigned long long stFullBar[kStagingSlots], stEmptyBar[kStagingSlots];
+            __shared__ __align__(8) unsigned long long opFullBar[kOpSlots], opEmptyBar[kOpSlots];
+            __shared__ __align__(8) unsigned long long segFullBar[2], segEmptyBar[2], corrFullBar[2], corrEmptyBar[2];
+            __shared__ uint32_t tmemBase;
+            __shared__ int      abortFlag;
+            __shared__ int64_t  colOff[4][128]; // one table per epilogue warp
+
+            const int      warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            const uint32_t rank   = PAIR ? clusterRank() : 0u;
+            const bool     leader = (rank == 0);
+            const int      ctas   = PAIR ? 2 : 1;
+            const int      worker = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x); // CTA or CTA pair
+            const int      numWorkers = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
+            const int      numUnits   = PAIR ? a.pairsM * a.pairsN : a.gm.tiles * a.gn.tiles;
+            const int      unitsM     = PAIR ? a.pairsM : a.gm.tiles;
+            const int      accCols    = ctas * a.gn.rows; // accumulator columns per tile (a pair: two 64-row B tiles)
+            const int      numSegs    = (a.kBlocks + kSegBlocks - 1) / kSegBlocks;
+            constexpr uint32_t kTmemCols = 512;
+
+            if(threadIdx.x == 0)
+            {
+                abortFlag = 0;
+                for(int s = 0; s < kStagingSlots; s++)
+                {
+                    mbarInit(smemAddr(&stFullBar[s]), 1);
+                    mbarInit(smemAddr(&stEmptyBar[s]), 4); // the four converter warps
+                }
+                for(int s = 0; s < kOpSlots; s++)
+                {
+                    mbarInit(smemAddr(&opFullBar[s]), 4 * ctas); // converter warps of the whole pair (leader's copy is used)
+                    mbarInit(smemAddr(&opEmptyBar[s]), 1);
+                }
+                for(int i = 0; i < 2; i++)
+                {
+                    mbarInit(smemAddr(&segFullBar[i]), 1);
+                    mbarInit(smemAddr(&segEmptyBar[i]), 128 * ctas);
+                    mbarInit(smemAddr(&corrFullBar[i]), 1);
+                    mbarInit(smemAddr(&corrEmptyBar[i]), 128 * ctas);
+                }
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            }
+            if(warp == 1)
+            {
+                if(PAIR)
+                {
+                    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&tmemBase)),
+                                 "r"(kTmemCols)
+                                 : "memory");
+                    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+                }
+                else
+                {
+                    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&tmemBase)),
+                                 "r"(kTmemCols)
+                                 : "memory");
+                    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();
+            if(PAIR)
+                clusterSync(); // the peer's barriers exist before anything signals them
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem      = tmemBase;
+            volatile int*  abortP    = &abortFlag;
+            const uint32_t stagingAddr = smemAddr(tiles);
+            const uint32_t opAddr      = stagingAddr + kStagingSlots * kStagingBytes;
+            const uint32_t stFull = smemAddr(&stFullBar[0]), stEmpty = smemAddr(&stEmptyBar[0]);
+            const uint32_t opFull = smemAddr(&opFullBar[0]), opEmpty = smemAddr(&opEmptyBar[0]);
+            const uint32_t segFull = smemAddr(&segFullBar[0]), segEmpty = smemAddr(&segEmptyBar[0]);
+            const uint32_t corrFull = smemAddr(&corrFullBar[0]), corrEmpty = smemAddr(&corrEmptyBar[0]);
+
+            // this CTA's row tiles of a unit (a pair's second CTA takes the next tile of each group;
+            // past the edge it repeats the last one and its results are not stored)
+            auto tilesOf = [&](int u, int& tm, int& tn) {
+                const int um = u % unitsM, un = u / unitsM;
+                tm = PAIR ? min(2 * um + int(rank), a.gm.tiles - 1) : um;
+                tn = PAIR ? min(2 * un + int(rank), a.gn.tiles - 1) : un;
+            };
+            // signal a barrier of the issuing CTA from any CTA of the pair / commit MMAs to both CTAs
+            auto arriveIssuer = [&](uint32_t bar) {
+                if(PAIR)
+                    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(mapToRank(bar, 0)) : "memory");
+                else
+                    mbarArrive(bar);
+            };
+            auto commitTo = [&](uint32_t bar) {
+                if(PAIR)
+                    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                                 "h"((unsigned short)3)
+                                 : "memory");
+                else
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+            };
+            auto mma = [&](uint32_t d, uint64_t da, uint64_t db, uint32_t accumulate) {
+                if(PAIR)
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                 "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
+                                 "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+                                 : "memory");
+                else
+                    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
+                                 "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+                                 : "memory");
+            };
+
+            if(warp == 0)
+            {
+                // ---------------------------------------------------------------- TMA producer
+                if(lane == 0)
+                {
+                    uint32_t slot = 0, phase = 0;
+                    bool     ok = true;
+                    for(int u = worker; u < numUnits && ok; u += numWorkers)
+                    {
+                        int tm, tn;
+                        tilesOf(u, tm, tn);
+                        const TfTile wm = tfTileOf(a.gm, tm), wn = tfTileOf(a.gn, tn);
+                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        {
+                            ok = mbarWaitTight(stEmpty + 8 * slot, phase ^ 1, abortP);
+                            if(!ok)
+                                break;
+                            const uint32_t bar = stFull + 8 * slot;
+                            mbarArriveExpectTx(bar, a.bytesA + a.bytesB);
+                            const uint32_t dst = stagingAddr + slot * kStagingBytes;
+                            tfLoadRows(a.gm, wm, &mapA, dst, bar, kb, a);
+                            tfLoadRows(a.gn, wn, &mapB, dst + kTileBytes, bar, kb, a);
+                            if(++slot == kStagingSlots)
+                            {
+                                slot = 0;
+                                phase ^= 1;
+                            }
+                        }
+                    }
+                }
+            }
+            else if(warp == 1)
+            {
+                // ---------------------------------------------------------------- MMA issuer (leader CTA of a pair)
+                if(lane == 0 && leader)
+                {
+                    const uint64_t descBase = smemDesc(opAddr);
+                    uint32_t       slot = 0, phase = 0;
+                    uint32_t       seg = 0; // running count of segments: buffer seg & 1, use (seg >> 1)
+                    int            local = 0;
+                    bool           ok    = true;
+                    for(int u = worker; u < numUnits && ok; u += numWorkers, local++)
+                    {
+                        const int      cb     = local & 1;
+                        const uint32_t dCorr  = tmem + 256u + uint32_t(cb) * 128u;
+                        bool           corrReady = false;
+                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        {
+                            const bool     segStart = (kb % kSegBlocks) == 0;
+                            const uint32_t sb       = seg & 1;
+                            if(segStart)
+                            {
+                                ok = mbarWaitTight(segEmpty + 8 * sb, ((seg >> 1) & 1) ^ 1, abortP);
+                                if(!ok)
+                                    break;
+                            }
+                            ok = mbarWaitTight(opFull + 8 * slot, phase, abortP);
+                            if(!ok)
+                                break;
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            const uint32_t dMain = tmem + sb * 128u;
+                            // descriptor addresses count 16-byte units; 8 fp32 = 32 bytes = 2 units
+                            const uint64_t aBig = descBase + uint64_t((slot * kOpBytes) >> 4);
+                            const uint64_t aSml = aBig + (kTileBytes >> 4), bBig = aBig + (2 * kTileBytes >> 4),
+                                           bSml = aBig + (3 * kTileBytes >> 4);
+#pragma unroll
+                            for(int k = 0; k < kTfK / 8; k++)
+                                mma(dMain, aBig + uint64_t(2 * k), bBig + uint64_t(2 * k), (!segStart || k) ? 1u : 0u);
+                            if(!corrReady)
+                            {
+                                // the epilogue must have read this correction accumulator's previous tile
+                                ok = mbarWaitTight(corrEmpty + 8 * cb, ((local >> 1) & 1) ^ 1, abortP);
+                                if(!ok)
+                                    break;
+                                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                                corrReady = true;
+                            }
+#pragma unroll
+                            for(int k = 0; k < kTfK / 8; k++)
+                            {
+                                mma(dCorr, aSml + uint64_t(2 * k), bBig + uint64_t(2 * k), (kb | k) ? 1u : 0u);
+                                mma(dCorr, aBig + uint64_t(2 * k), bSml + uint64_t(2 * k), 1u);
+                            }
+                            commitTo(opEmpty + 8 * slot); // the ring slot is free (in both CTAs) once these MMAs have read it
+                            if(++slot == kOpSlots)
+                            {
+                                slot = 0;
+                                phase ^= 1;
+                            }
+                            if((kb % kSegBlocks) == kSegBlocks - 1 || kb == a.kBlocks - 1)
+                            {
+                                commitTo(segFull + 8 * sb);
+                                seg++;
+                            }
+                        }
+                        if(ok)
+                            commitTo(corrFull + 8 * cb);
+                    }
+                }
+            }
+            else if(warp < 6)
+            {
+                // ---------------------------------------------------------------- epilogue (every CTA: its own rows)
+                const int      quad  = warp & 3; // tensor-memory lane quadrant this warp may read
+                const int      row   = quad * 32 + lane;
+                int64_t*       cols  = colOff[quad];
+                const uint32_t lanes = tmem + (uint32_t(quad * 32) << 16);
+                uint32_t       seg   = 0;
+                int            local = 0;
+                bool           alive = true;
+                auto waitWarp = [&](uint32_t bar, uint32_t parity) {
+                    int ok = 1;
+                    if(lane == 0)
+                        ok = mbarWait(bar, parity, abortP) ? 1 : 0;
+                    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+                };
+                auto loadChunk = [&](uint32_t taddr, uint32_t(&v)[32]) {
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]),
+                          "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]),
+                          "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                };
+                for(int u = worker; u < numUnits && alive; u += numWorkers, local++)
+                {
+                    const int    cb = local & 1;
+                    const int    um = u % unitsM, un = u / unitsM;
+                    const int    tmRaw = PAIR ? 2 * um + int(rank) : um;
+                    const bool   dupM  = tmRaw >= a.gm.tiles; // this CTA repeats its peer's rows: no stores
+                    const TfTile wm    = tfTileOf(a.gm, min(tmRaw, a.gm.tiles - 1));
+                    __syncwarp();
+                    for(int h = 0; h < ctas; h++)
+                    {
+                        const int    tnRaw = PAIR ? 2 * un + h : un;
+                        const TfTile wn    = tfTileOf(a.gn, min(tnRaw, a.gn.tiles - 1));
+                        for(int c = lane; c < a.gn.rows; c += 32)
+                            cols[h * a.gn.rows + c] = (tnRaw < a.gn.tiles) ? tfRowOffset(a.gn, wn, c) : -1;
+                    }
+                    __syncwarp();
+                    const int64_t offM = dupM ? -1 : tfRowOffset(a.gm, wm, row);
+
+                    // running sums of the main product, one segment at a time
+                    float sum[128];
+#pragma unroll
+                    for(int j = 0; j < 128; j++)
+                        sum[j] = 0.f;
+                    for(int s = 0; s < numSegs && alive; s++, seg++)
+                    {
+                        const uint32_t sb = seg & 1;
+                        alive = waitWarp(segFull + 8 * sb, (seg >> 1) & 1);
+                        if(!alive)
+                            break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                        for(int c0 = 0; c0 < 128; c0 += 32)
+                        {
+                            if(c0 < accCols)
+                            {
+                                uint32_t v[32];
+                                loadChunk(lanes + sb * 128u + uint32_t(c0), v);
+#pragma unroll
+                                for(int j = 0; j < 32; j++)
+                                    sum[c0 + j] = __fadd_rn(sum[c0 + j], __uint_as_float(v[j]));
+                            }
+                        }
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        arriveIssuer(segEmpty + 8 * sb);
+                    }
+                    if(!alive)
+                        break;
+                    alive = waitWarp(corrFull + 8 * cb, (local >> 1) & 1);
+                    if(!alive)
+                        break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for(int c0 = 0; c0 < 128; c0 += 32)
+                    {
+                        if(c0 < accCols)
+                        {
+                            uint32_t v[32];
+                            loadChunk(lanes + 256u + uint32_t(cb) * 128u + uint32_t(c0), v);
+                            if(offM >= 0)
+                            {
+                                const int64_t first     = cols[c0];
+                                const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] == first + 31;
+                                if(fullChunk && ((offM + first) & 3) == 0)
+                                {
+                                    // 32 consecutive floats of this row: eight 128-bit stores
+                                    float*       dst = D + offM + first;
+                                    const float* src = C + offM + first;
+#pragma unroll
+                                    for(int j = 0; j < 32; j += 4)
+                                    {
+                                        float4 o;
+                                        o.x = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j], __uint_as_float(v[j])));
+                                        o.y = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 1], __uint_as_float(v[j + 1])));
+                                        o.z = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 2], __uint_as_float(v[j + 2])));
+                                        o.w = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 3], __uint_as_float(v[j + 3])));
+                                        if(a.bilinear)
+                                        {
+                                            const float4 c4 = *(const float4*)(src + j);
+                                            o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4.x));
+                                            o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4.y));
+                                            o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4.z));
+                                            o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4.w));
+                                        }
+                                        *(float4*)(dst + j) = o;
+                                    }
+                                }
+                                else
+                                {
+#pragma unroll
+                                    for(int j = 0; j < 32; j++)
+                                    {
+                                        const int64_t oc = cols[c0 + j];
+                                        if(oc >= 0)
+                                        {
+                                            float y = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j], __uint_as_float(v[j])));
+                                            if(a.bilinear)
+                                                y = __fadd_rn(y, __fmul_rn(a.beta, C[offM + oc]));
+                                            D[offM + oc] = y;
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    // hand the correction accumulator back
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    arriveIssuer(corrEmpty + 8 * cb);
+                }
+            }
+            else
+            {
+                // ---------------------------------------------------------------- converter (every CTA: its own rows)
+                const int r    = int(threadIdx.x) - 192;
+                const bool hasB = r < a.gn.rows;
+                uint32_t   sSlot = 0, sPhase = 0, oSlot = 0, oPhase = 0;
+                bool       ok = true;
+                for(int u = worker; u < numUnits && ok; u += numWorkers)
+                {
+                    for(int kb = 0; kb < a.kBlocks; kb++)
+                    {
+                        ok = mbarWaitAll(stFull + 8 * sSlot, sPhase, abortP) && mbarWaitAll(opEmpty + 8 * oSlot, oPhase ^ 1, abortP);
+                        if(!ok)
+                            break;
+                        const uint32_t st = stagingAddr + sSlot * kStagingBytes;
+                        const uint32_t op = opAddr + oSlot * kOpBytes;
+                        tfConvertRow(a.gm.major, st, op, op + kTileBytes, r);
+                        if(hasB)
+                            tfConvertRow(a.gn.major, st + kTileBytes, op + 2 * kTileBytes, op + 3 * kTileBytes, r);
+                        // the ring is read by the tensor cores (async proxy): order this thread's stores before it
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if(lane == 0)
+                        {
+                            mbarArrive(stEmpty + 8 * sSlot);
+                            arriveIssuer(opFull + 8 * oSlot);
+                        }
+                        if(++sSlot == kStagingSlots)
+                        {
+                            sSlot = 0;
+                            sPhase ^= 1;
+                        }
+                        if(++oSlot == kOpSlots)
+                        {
+                            oSlot = 0;
+                            oPhase ^= 1;
+                        }
+                    }
+                }
+            }
+
+            // ---------------------------------------------------------------- teardown
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();
+            if(PAIR)
+                clusterSync(); // both CTAs are done with tensor memory and with each other's barriers
+            if(threadIdx.x == 0 && abortFlag && a.status)
+                atomicExch(a.status, 4);
+            if(warp == 1)
+            {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if(PAIR)
+                    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+                else
+                    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+            }
+        }
+
+        // ------------------------------------------------------------------ host side
+        struct RowGroupView
+        {
+            int     n;
+            int64_t ext[4], sOp[4], sD[4]; // extent, stride in the operand, stride in D; mode 0 first
+        };
+
+        // K-major operand: {K, mode0 .. mode3}, one [rows x 32] box, 128-byte swizzle
+        bool encodeKMajor(PFN_encodeTiled encode, CUtensorMap* map, const void* base, int64_t K, const RowGroupView& g,
+                          const int* box)
+        {
+            cuuint64_t gdim[5], gstr[4];
+            cuuint32_t bx[5], estr[5] = {1, 1, 1, 1, 1};
+            gdim[0] = cuuint64_t(K);
+            bx[0]   = kTfK;
+            for(int d = 0; d < 4; d++)
+            {
+                const bool real = d < g.n && g.ext[d] > 1;
+                gdim[d + 1]     = real ? cuuint64_t(g.ext[d]) : 1;
+                gstr[d]         = real ? cuuint64_t(g.sOp[d]) * 4 : 16; // extent 1: any 16-byte multiple is legal
+                bx[d + 1]       = (d < g.n) ? cuuint32_t(box[d]) : 1;
+                if(gstr[d] % 16 != 0 || gstr[d] == 0)
+                    return false;
+            }
+            return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<void*>(base), gdim, gstr, bx, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+                   == CUDA_SUCCESS;
+        }
+
+        // MN-major operand: {mode0 (stride 1), k0, k1, mode1, mode2}, one [32 k x 32 rows] box per chunk, unswizzled
+        bool encodeMnMajor(PFN_encodeTiled encode, CUtensorMap* map, const void* base, const RowGroupView& g, int nk,
+                           const int64_t* extK, const int64_t* sK, const int* boxK)
+        {
+            cuuint64_t gdim[5], gstr[4];
+            cuuint32_t bx[5] = {32, 1, 1, 1, 1}, estr[5] = {1, 1, 1, 1, 1};
+            gdim[0] = cuuint64_t(g.ext[0]);
+            for(int d = 0; d < 2; d++)
+            {
+                const bool real = d < nk && extK[d] > 1;
+                gdim[1 + d]     = real ? cuuint64_t(extK[d]) : 1;
+                gstr[d]         = real ? cuuint64_t(sK[d]) * 4 : 16;
+                bx[1 + d]       = (d < nk) ? cuuint32_t(boxK[d]) : 1;
+            }
+            for(int d = 1; d < 3; d++)
+            {
+                const bool real = d < g.n && g.ext[d] > 1;
+                gdim[2 + d]     = real ? cuuint64_t(g.ext[d]) : 1;
+                gstr[1 + d]     = real ? cuuint64_t(g.sOp[d]) * 4 : 16;
+            }
+            for(int d = 0; d < 4; d++)
+                if(gstr[d] % 16 != 0 || gstr[d] == 0)
+                    return false;
+            return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<void*>(base), gdim, gstr, bx, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+                   == CUDA_SUCCESS;
+        }
+
+        // planner group -> view with the chunked (stride-1) mode first
+        RowGroupView viewOf(const ModeDim* dims, int n, int fast)
+        {
+            RowGroupView v{};
+            int          k = 0;
+            auto         put = [&](int i) {
+                v.ext[k] = dims[i].ext;
+                v.sOp[k] = dims[i].s0;
+                v.sD[k]  = dims[i].s1;
+                k++;
+            };
+            if(fast >= 0)
+                put(fast);
+            for(int i = 0; i < n && k < 4; i++)
+                if(i != fast)
+                    put(i);
+            v.n = k;
+            return v;
+        }
+
+        void fillGroup(TfGroup& g, const RowGroupView& v, int major, int rows, const int* box)
+        {
+            g.major = major;
+            g.n     = v.n;
+            g.rows  = rows;
+            g.tiles = 1;
+            g.restExt = 1;
+            for(int d = 0; d < 4; d++)
+            {
+                g.ext[d]         = d < v.n ? v.ext[d] : 1;
+                g.sD[d]          = d < v.n ? v.sD[d] : 0;
+                g.box[d]         = (major == 0 && d < v.n) ? box[d] : 1;
+                g.tilesPerDim[d] = int((g.ext[d] + g.box[d] - 1) / g.box[d]);
+                if(major == 0)
+                    g.tiles *= g.tilesPerDim[d];
+                else if(d >= 1)
+                    g.restExt *= g.ext[d];
+            }
+            g.chunks0 = int((g.ext[0] + 31) / 32);
+            if(major == 1)
+            {
+                const int64_t chunks = int64_t(g.chunks0) * g.restExt, per = rows / 32;
+                g.tiles              = int((chunks + per - 1) / per);
+            }
+        }
+
+        template <bool PAIR>
+        cudaError_t launchKernel(const CUtensorMap& mapA, const CUtensorMap& mapB, const float* C, float* D, TfArgs& a, int sms,
+                                 cudaStream_t stream)
+        {
+            auto         kernel = contraction_tf32x3_kernel<PAIR>;
+            const size_t smem   = size_t(kStagingSlots) * kStagingBytes + size_t(kOpSlots) * kOpBytes + 1024;
+            static bool  attrSet = false;
+            if(!attrSet)
+            {
+                cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+                if(e != cudaSuccess)
+                    return e;
+                attrSet = true;
+            }
+            const int      accCols = PAIR ? 128 : a.gn.rows;
+            const uint32_t idesc   = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(accCols >> 3) << 17)
+                                   | (uint32_t((PAIR ? 256 : 128) >> 4) << 24); // fp32 accumulate, tf32 x tf32, K-major
+            if(!PAIR)
+            {
+                const int grid = int(std::min<int64_t>(int64_t(a.gm.tiles) * a.gn.tiles, sms));
+                kernel<<<grid, kTfThreads, smem, stream>>>(mapA, mapB, C, D, a, idesc);
+                noteLaunch("contraction_tf32x3");
+                return cudaGetLastError();
+            }
+            cudaLaunchConfig_t  cfg{};
+            cudaLaunchAttribute attr[1];
+            attr[0].id               = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.blockDim             = dim3(kTfThreads);
+            cfg.dynamicSmemBytes     = smem;
+            cfg.stream               = stream;
+            cfg.attrs                = attr;
+            cfg.numAttrs             = 1;
+            static int maxClusters   = 0; // CTA pairs that can be resident at once
+            if(maxClusters == 0)
+            {
+                cfg.gridDim = dim3(unsigned(sms / 2 * 2));
+                int n       = 0;
+                if(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0)
+                {
+                    cudaGetLastError();
+                    n = sms / 2;
+                }
+                maxClusters = n;
+            }
+            const int64_t pairs = int64_t(a.pairsM) * a.pairsN;
+            cfg.gridDim         = dim3(unsigned(2 * std::min<int64_t>(pairs, maxClusters)));
+            cudaError_t e       = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, C, D, a, idesc);
+            if(e == cudaSuccess)
+                noteLaunch("contraction_tf32x3_pair");
+            return e;
+        }
+    } // namespace
+
+    cudaError_t launchContractionTf32x3(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
+                                        const void* C, void* D, int smCount, int* deviceStatus, cudaStream_t stream)
+    {
+        PFN_encodeTiled encode = tensorMapEncoder();
+        if(!encode)
+            return cudaErrorNotSupported;
+        const int          sms = smCount > 0 ? smCount : 148;
+        const RowGroupView vm = viewOf(p.m, p.nm, p.aMajor ? 0 : -1), vn = viewOf(p.n, p.nn, p.bMajor ? p.nFast : -1);
+        int64_t            extK[2] = {1, 1}, sKa[2] = {0, 0}, sKb[2] = {0, 0};
+        for(int i = 0; i < p.nk && i < 2; i++)
+        {
+            extK[i] = p.k[i].ext;
+            sKa[i]  = p.k[i].s0;
+            sKb[i]  = p.k[i].s1;
+        }
+        // CTA pairs (256 x 128 tiles, each CTA loading 64 rows of B) unless a repeated edge tile would waste
+        // more than a tenth of the work
+        bool pair = p.pair != 0;
+        if(const char* env = getenv("HTB_TF32_PAIR"))
+            pair = pair && atoi(env) != 0;
+
+        TfArgs a{};
+        fillGroup(a.gm, vm, p.aMajor, 128, p.boxM);
+        fillGroup(a.gn, vn, p.bMajor, pair ? 64 : p.tileN, pair ? p.boxN128 : p.boxN);
+        if(pair && getenv("HTB_TF32_PAIR") == nullptr)
+        {
+            const int wasteM = 2 * ((a.gm.tiles + 1) / 2) - a.gm.tiles, wasteN = 2 * ((a.gn.tiles + 1) / 2) - a.gn.tiles;
+            if(wasteM * 10 > a.gm.tiles || wasteN * 10 > a.gn.tiles)
+            {
+                pair = false;
+                fillGroup(a.gn, vn, p.bMajor, p.tileN, p.boxN);
+            }
+        }
+        CUtensorMap mapA, mapB;
+        const bool  okA = p.aMajor ? encodeMnMajor(encode, &mapA, A, vm, p.nk, extK, sKa, p.boxK)
+                                   : encodeKMajor(encode, &mapA, A, p.K, vm, p.boxM);
+        const bool  okB = p.bMajor ? encodeMnMajor(encode, &mapB, B, vn, p.nk, extK, sKb, p.boxK)
+                                   : encodeKMajor(encode, &mapB, B, p.K, vn, pair ? p.boxN128 : p.boxN);
+        if(!okA || !okB)
+            return cudaErrorNotSupported;
+        a.boxK[0] = p.boxK[0];
+        a.boxK[1] = p.boxK[1];
+        a.kTilesPerDim[0] = int((extK[0] + a.boxK[0] - 1) / a.boxK[0]);
+        a.kTilesPerDim[1] = int((extK[1] + a.boxK[1] - 1) / a.boxK[1]);
+        a.kBlocks  = (p.aMajor || p.bMajor) ? a.kTilesPerDim[0] * a.kTilesPerDim[1] : int((p.K + kTfK - 1) / kTfK);
+        a.bytesA   = uint32_t(p.aMajor ? 128 : p.rowsM) * kTfK * 4;
+        a.bytesB   = uint32_t(p.bMajor ? a.gn.rows : (pair ? p.rowsN128 : p.rowsN)) * kTfK * 4;
+        a.alpha    = alpha;
+        a.beta     = beta;
+        a.bilinear = (p.bilinear && C != nullptr) ? 1 : 0;
+        a.nContig  = (vn.sD[0] == 1 && (uintptr_t(D) & 15) == 0 && (!a.bilinear || (uintptr_t(C) & 15) == 0)) ? 1 : 0;
+        a.pairsM   = (a.gm.tiles + 1) / 2;
+        a.pairsN   = (a.gn.tiles + 1) / 2;
+        a.status   = deviceStatus;
+        if(int64_t(a.gm.tiles) * a.gn.tiles > 0x7fffffffll)
+            return cudaErrorInvalidConfiguration;
+        HTB_LOG_HEUR("hiptensorContraction", "tf32x3: %d x %d row tiles (%d B rows each), %d K blocks, %s", a.gm.tiles,
+                     a.gn.tiles, a.gn.rows, a.kBlocks, pair ? "CTA pairs" : "single CTAs");
+        return pair ? launchKernel<true>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream)
+                    : launchKernel<false>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream);
+    }
+} // namespace htb

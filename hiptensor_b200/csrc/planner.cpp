@@ -553,6 +553,71 @@ namespace htb
                 }
             }
         }
+        else if(tA == CUDA_R_32F && computeType == 4)
+        {
+            // fp32 on the tensor cores. An operand is taken K-major (one stride-1 K mode) or MN-major (a
+            // stride-1 mode in its row group); all other strides must be multiples of 16 bytes for TMA.
+            bool tf = out->K >= 32 && out->M >= 128 && out->N >= 64 && nk <= 2;
+            out->aMajor = out->aKContig ? 0 : ((gm[0].s0 == 1 && gm[0].ext > 1) ? 1 : -1);
+            out->bMajor = out->bKContig ? 0 : -1;
+            out->nFast  = 0;
+            for(int i = 0; i < nn && out->bMajor < 0; i++)
+                if(gn[i].s0 == 1 && gn[i].ext > 1)
+                {
+                    out->bMajor = 1;
+                    out->nFast  = i;
+                }
+            tf = tf && out->aMajor >= 0 && out->bMajor >= 0;
+            auto stridesOk = [](const ModeDim* g, int n, int skip) {
+                for(int i = 0; i < n; i++)
+                    if(i != skip && g[i].ext > 1 && (g[i].s0 % 4 != 0 || g[i].ext >= (int64_t(1) << 31)))
+                        return false;
+                return true;
+            };
+            if(tf)
+            {
+                tf = stridesOk(gm, nm, out->aMajor ? 0 : -1) && stridesOk(gn, nn, out->bMajor ? out->nFast : -1);
+                tf = tf && nm <= (out->aMajor ? 3 : 4) && nn <= (out->bMajor ? 3 : 4);
+                for(int i = 0; i < nm && tf; i++)
+                    tf = gm[i].ext < (int64_t(1) << 31);
+                for(int i = 0; i < nn && tf; i++)
+                    tf = gn[i].ext < (int64_t(1) << 31);
+            }
+            if(tf)
+            {
+                out->boxK[0] = 32;
+                out->boxK[1] = 1;
+                if(out->aMajor || out->bMajor)
+                {
+                    int bk[kMaxGroup] = {1, 1, 1, 1, 1, 1};
+                    tf = boxDecompose(gk, nk, 32, bk) == 32;
+                    out->boxK[0] = bk[0];
+                    out->boxK[1] = bk[1];
+                    for(int i = 0; i < nk && tf; i++)
+                        tf = (!out->aMajor || gk[i].s0 % 4 == 0) && (!out->bMajor || gk[i].s1 % 4 == 0)
+                             && gk[i].ext < (int64_t(1) << 31);
+                }
+            }
+            if(tf)
+            {
+                out->tileM = 128;
+                out->tileK = 32;
+                out->tileN = out->N >= 128 ? 128 : 64;
+                out->rowsM = out->aMajor ? 128 : boxDecompose(gm, nm, 128, out->boxM);
+                out->rowsN = out->bMajor ? out->tileN : boxDecompose(gn, nn, out->tileN, out->boxN);
+                if(out->rowsN == 0 && out->tileN == 128)
+                {
+                    out->tileN = 64;
+                    out->rowsN = boxDecompose(gn, nn, 64, out->boxN);
+                }
+                tf          = out->rowsM > 0 && out->rowsN > 0;
+                out->stages = 2;
+                // CTA pairs work on 256 x 128 tiles, each CTA loading 64 rows of B
+                out->rowsN128 = out->bMajor ? 64 : boxDecompose(gn, nn, 64, out->boxN128);
+                out->pair     = (tf && out->tileN == 128 && out->rowsM == 128 && out->rowsN128 == 64 && out->M >= 256) ? 1 : 0;
+            }
+            out->kind = tf ? CK_TF32X3 : CK_TILED_SIMT;
+        }
         else
         {
             out->kind = CK_TILED_SIMT;
@@ -563,7 +628,7 @@ namespace htb
 
     std::string describe(const ContractionPlan& p)
     {
-        static const char* kinds[] = {"tiled_simt", "tiled_dmma", "tcgen05"};
+        static const char* kinds[] = {"tiled_simt", "tiled_dmma", "tcgen05", "tf32x3"};
         std::string        s       = "contraction kind=";
         s += kinds[p.kind];
         char buf[192];
@@ -574,7 +639,13 @@ namespace htb
         appendDims(s, "m", p.m, p.nm);
         appendDims(s, " n", p.n, p.nn);
         appendDims(s, " k", p.k, p.nk);
-        if(p.kind == CK_TCGEN05)
+        if(p.kind == CK_TF32X3)
+        {
+            snprintf(buf, sizeof(buf), " major=%s/%s boxK=[%d %d]", p.aMajor ? "mn" : "k", p.bMajor ? "mn" : "k", p.boxK[0],
+                     p.boxK[1]);
+            s += buf;
+        }
+        if(p.kind == CK_TCGEN05 || p.kind == CK_TF32X3)
         {
             snprintf(buf, sizeof(buf), " tile=%dx%dx%d stages=%d rows=%d/%d boxM=[", p.tileM, p.tileN, p.tileK,
                      p.stages, p.rowsM, p.rowsN);

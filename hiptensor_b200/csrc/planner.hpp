@@ -81,7 +81,8 @@ namespace htb
     {
         CK_TILED_SIMT = 0, // shared-memory tiled FMA kernel with gathered operands (f32 accumulate)
         CK_TILED_DMMA = 1, // same tiling, FP64 tensor-pipe MMA
-        CK_TCGEN05    = 2 // TMA + tcgen05.mma with TMEM accumulators (f16/bf16 inputs)
+        CK_TCGEN05    = 2, // TMA + tcgen05.mma with TMEM accumulators (f16/bf16 inputs)
+        CK_TF32X3     = 3 // fp32 inputs on the tensor cores: big/small TF32 split, three tcgen05.mma per K step
     };
 
     struct ModeDim
@@ -108,8 +109,12 @@ namespace htb
         int boxM[4], boxN[4]; // TMA box extent per folded M / N mode (product = rows gathered per tile)
         int rowsM, rowsN; // rows of the tile that the boxes fill (<= tileM / tileN)
         int pair; // 256 x 256 tile over a CTA pair (tcgen05 cta_group::2), each CTA loading 128 rows of B
-        int boxN128[4], rowsN128; // N boxes of the 128-row sub-tiles of the pair kernel
+        int boxN128[4], rowsN128; // N boxes of one CTA's sub-tile in the pair kernels (128 rows; 64 for CK_TF32X3)
         int aKContig, bKContig; // operand has its K group folded to one stride-1 mode
+        // CK_TF32X3 only: 0 = operand K-major (rows gathered by boxM / boxN), 1 = MN-major (32-row chunks along
+        // the row group's stride-1 mode: m[0] for A, n[nFast] for B; K rows gathered by boxK)
+        int aMajor, bMajor, nFast;
+        int boxK[2];
         // split of the K range over several CTAs (needs workspace); 1 = none
         int      splitK;
         uint64_t workspaceBytes;
