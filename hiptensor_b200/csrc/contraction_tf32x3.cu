@@ -12,16 +12,16 @@
 //                                       folded modes of the row group;
 //                    MN-major operand : one box per 32 rows [32 k x 32 rows], the 32 rows being
 //                                       consecutive elements of the group's stride-1 mode;
-//   converter      4 warps, one thread per tile row: read the row from staging (conflict-free in
-//                  both orders), split, write the big and the small row into the K-major,
+//   converter      8 warps, two threads per tile row (16 k each): read from staging (conflict-free in
+//                  both orders), split, write the big and the small half row into the K-major,
 //                  128-byte-swizzled operand ring;
 //   tcgen05.mma    three MMAs per 8-wide K step from the ring into the accumulator;
 //   epilogue       tcgen05.ld, alpha/beta, stores to the strided D.
 //
-// Warp roles (320 threads): 0 TMA producer, 1 MMA issuer + tensor-memory owner, 2-5 epilogue,
-// 6-9 converter. PAIR = true runs a 256 x 256 tile on a cluster of two CTAs (cta_group::2): each
-// CTA stages and converts its own 128 rows of A and 128 of the 256 rows of B; the leader CTA issues
-// the MMAs for both. Loads carry no multicast qualifier.
+// Warp roles (576 threads): 0 TMA producer, 1 MMA issuer + tensor-memory owner, 2-9 epilogue (two warps
+// per tensor-memory lane quadrant, 64 columns each), 10-17 converter. PAIR = true runs a 256 x 128 tile
+// on a cluster of two CTAs (cta_group::2): each CTA stages and converts its own 128 rows of A and 64 of
+// the 128 rows of B; the leader CTA issues the MMAs for both. Loads carry no multicast qualifier.
 //
 // All mbarrier waits are bounded; on a timeout the kernel raises the device status word, skips the
 // remaining work and frees its tensor memory.
@@ -41,12 +41,23 @@ namespace htb
 {
     namespace
     {
-        constexpr int      kTfThreads    = 320;
+        constexpr int      kTfThreads    = 576;
+        constexpr int      kEpiWarps = 8, kConvWarps = 8; // warps 2..9 and 10..17
         constexpr int      kTfK          = 32; // fp32 elements per K block = one 128-byte swizzle row
-        constexpr int      kStagingSlots = 2, kOpSlots = 2;
         constexpr uint32_t kTileBytes    = 128 * kTfK * 4; // 16 KiB: 128 rows of one K block
-        constexpr uint32_t kStagingBytes = 2 * kTileBytes; // A rows, B rows
-        constexpr uint32_t kOpBytes      = 4 * kTileBytes; // A big, A small, B big, B small
+        constexpr int      kMaxSlots     = 4;
+
+        // Shared-memory rings. A staging slot holds the raw A rows and B rows of one K block, an operand slot
+        // A big, A small, B big, B small. A CTA of a pair carries 64 rows of B and so affords three slots of each.
+        template <bool PAIR>
+        struct TfRing
+        {
+            static constexpr uint32_t kBBytes       = PAIR ? kTileBytes / 2 : kTileBytes;
+            static constexpr int      kStagingSlots = PAIR ? 3 : 2, kOpSlots = PAIR ? 3 : 2;
+            static constexpr uint32_t kStagingBytes = kTileBytes + kBBytes;
+            static constexpr uint32_t kOpBytes      = 2 * kTileBytes + 2 * kBBytes;
+            static constexpr uint32_t kTotal        = kStagingSlots * kStagingBytes + kOpSlots * kOpBytes;
+        };
 
         // One row group of the tile: the M side (rows of A and D) or the N side (rows of B, columns of D).
         struct TfGroup
@@ -72,6 +83,9 @@ namespace htb
             int      bilinear;
             int      nContig; // 32 consecutive columns of a tile are 32 consecutive, 16-byte aligned floats of D
             int      pairsM, pairsN; // PAIR only
+            uint32_t sleepNs; // pause between barrier polls of the multi-warp roles
+            int      probe; // measurement aid, bit mask: 1 = converter skips its work, 2 = issuer skips the MMAs,
+                            // 8 = producer skips the loads (results invalid)
             int*     status;
         };
 
@@ -127,11 +141,33 @@ namespace htb
             return off;
         }
 
+        // TMA coordinates of a tile's 32-row chunks (MN-major operands), fixed for the whole K loop
+        struct TfChunks
+        {
+            int c0[4], i1[4], i2[4];
+        };
+        __device__ __forceinline__ TfChunks tfChunksOf(const TfGroup& g, const TfTile& w)
+        {
+            TfChunks      q;
+            const int64_t e1 = (g.n > 1) ? g.ext[1] : 1;
+#pragma unroll
+            for(int j = 0; j < 4; j++)
+            {
+                const int     chunk = w.chunkBase + j;
+                const int64_t rest  = chunk / g.chunks0;
+                // beyond the tensor the coordinates fall outside the map and the box is zero-filled
+                q.c0[j] = (chunk % g.chunks0) * 32;
+                q.i1[j] = int(rest % e1);
+                q.i2[j] = int(rest / e1);
+            }
+            return q;
+        }
+
         // TMA loads of one operand's rows of one K block into a staging tile
         //   major 0 map: {K, mode0, mode1, mode2, mode3}         one box
         //   major 1 map: {mode0, k0, k1, mode1, mode2}           one box per 32-row chunk
-        __device__ __forceinline__ void tfLoadRows(const TfGroup& g, const TfTile& w, const CUtensorMap* map, uint32_t dst,
-                                                   uint32_t bar, int kb, const TfArgs& a)
+        __device__ __forceinline__ void tfLoadRows(const TfGroup& g, const TfTile& w, const TfChunks& q, const CUtensorMap* map,
+                                                   uint32_t dst, uint32_t bar, int kb, int kc0, int kc1)
         {
             if(g.major == 0)
             {
@@ -139,28 +175,41 @@ namespace htb
                 tmaLoad<5>(dst, map, bar, c);
                 return;
             }
-            const int kc0 = (kb % a.kTilesPerDim[0]) * a.boxK[0];
-            const int kc1 = (kb / a.kTilesPerDim[0]) * a.boxK[1];
-            const int64_t e1 = (g.n > 1) ? g.ext[1] : 1;
-            for(int q = 0; q < (g.rows >> 5); q++)
+#pragma unroll
+            for(int j = 0; j < 4; j++)
             {
-                const int     chunk = w.chunkBase + q;
-                const int64_t rest  = chunk / g.chunks0;
-                // beyond the tensor the coordinates fall outside the map and the box is zero-filled
-                const int c[5] = {(chunk % g.chunks0) * 32, kc0, kc1, int(rest % e1), int(rest / e1)};
-                tmaLoad<5>(dst + uint32_t(q) * (kTfK * 128), map, bar, c);
+                if(j < (g.rows >> 5))
+                {
+                    const int c[5] = {q.c0[j], kc0, kc1, q.i1[j], q.i2[j]};
+                    tmaLoad<5>(dst + uint32_t(j) * (kTfK * 128), map, bar, c);
+                }
             }
         }
 
-        __device__ __forceinline__ void tfSplit(float x, float& big, float& small)
+        // big = x rounded to TF32 (nearest, ties away: add half an ulp to the magnitude, drop 13 bits),
+        // small = x - big, exact in fp32; the tensor cores drop the last bits of small, 2^-21 of x.
+        __device__ __forceinline__ float tfBig(float x)
         {
-            uint32_t b, s;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(b) : "f"(x));
-            big = __uint_as_float(b);
-            // an infinite big (x infinite, or rounded up past the largest finite value) must not make a NaN
-            const float rest = (fabsf(big) == INFINITY) ? 0.f : x - big;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(s) : "f"(rest));
-            small = __uint_as_float(s);
+            return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+        }
+        __device__ __forceinline__ void tfSplit4(const float4& v, float4& b, float4& s)
+        {
+            b.x = tfBig(v.x);
+            b.y = tfBig(v.y);
+            b.z = tfBig(v.z);
+            b.w = tfBig(v.w);
+            s.x = v.x - b.x;
+            s.y = v.y - b.y;
+            s.z = v.z - b.z;
+            s.w = v.w - b.w;
+            // an infinite big (x infinite, or rounded up past the largest finite value) must not make a NaN small
+            if(!(fabsf(b.x) + fabsf(b.y) + fabsf(b.z) + fabsf(b.w) < INFINITY))
+            {
+                s.x = (fabsf(b.x) < INFINITY) ? s.x : 0.f;
+                s.y = (fabsf(b.y) < INFINITY) ? s.y : 0.f;
+                s.z = (fabsf(b.z) < INFINITY) ? s.z : 0.f;
+                s.w = (fabsf(b.w) < INFINITY) ? s.w : 0.f;
+            }
         }
 
         __device__ __forceinline__ float4 lds128(uint32_t addr)
@@ -180,25 +229,22 @@ namespace htb
             asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
         }
 
-        // One thread converts row r of a 128 x 32 tile: staging -> (big, small) in the K-major ring layout, where
-        // the 16-byte piece j of row r sits at r*128 + ((j ^ (r & 7)) << 4). Within a quarter warp the eight rows
-        // touch eight different pieces, so the 128-bit accesses are free of bank conflicts.
-        __device__ __forceinline__ void tfConvertRow(int major, uint32_t src, uint32_t dstBig, uint32_t dstSmall, int r)
+        // One thread converts half h (16 k) of row r of a 128 x 32 tile: staging -> (big, small) in the K-major ring
+        // layout, where the 16-byte piece j of row r sits at r*128 + ((j ^ (r & 7)) << 4). Within a quarter warp the
+        // eight rows touch eight different pieces, so the 128-bit accesses are free of bank conflicts.
+        __device__ __forceinline__ void tfConvertRow(int major, uint32_t src, uint32_t dstBig, uint32_t dstSmall, int r, int h)
         {
             const uint32_t rowOff = uint32_t(r) * 128;
             if(major == 0)
             {
                 // staging has the ring layout already (TMA 128-byte swizzle)
 #pragma unroll
-                for(int j = 0; j < 8; j++)
+                for(int jj = 0; jj < 4; jj++)
                 {
-                    const uint32_t off = rowOff + (uint32_t(j ^ (r & 7)) << 4);
+                    const uint32_t off = rowOff + (uint32_t((4 * h + jj) ^ (r & 7)) << 4);
                     const float4   v   = lds128(src + off);
                     float4         b, s;
-                    tfSplit(v.x, b.x, s.x);
-                    tfSplit(v.y, b.y, s.y);
-                    tfSplit(v.z, b.z, s.z);
-                    tfSplit(v.w, b.w, s.w);
+                    tfSplit4(v, b, s);
                     sts128(dstBig + off, b);
                     sts128(dstSmall + off, s);
                 }
@@ -206,33 +252,63 @@ namespace htb
             else
             {
                 // staging: chunk r/32 holds [32 k][32 rows], unswizzled; the lanes of a warp read 32 consecutive floats
-                const uint32_t col = src + uint32_t(r >> 5) * (kTfK * 128) + uint32_t(r & 31) * 4;
-                float          x[kTfK];
+                const uint32_t col = src + uint32_t(r >> 5) * (kTfK * 128) + uint32_t(r & 31) * 4 + uint32_t(h) * (16 * 128);
+                float          x[16];
 #pragma unroll
-                for(int k = 0; k < kTfK; k++)
+                for(int k = 0; k < 16; k++)
                     x[k] = lds32(col + uint32_t(k) * 128);
 #pragma unroll
-                for(int j = 0; j < 8; j++)
+                for(int jj = 0; jj < 4; jj++)
                 {
-                    const uint32_t off = rowOff + (uint32_t(j ^ (r & 7)) << 4);
+                    const uint32_t off = rowOff + (uint32_t((4 * h + jj) ^ (r & 7)) << 4);
                     float4         b, s;
-                    tfSplit(x[4 * j], b.x, s.x);
-                    tfSplit(x[4 * j + 1], b.y, s.y);
-                    tfSplit(x[4 * j + 2], b.z, s.z);
-                    tfSplit(x[4 * j + 3], b.w, s.w);
+                    tfSplit4(make_float4(x[4 * jj], x[4 * jj + 1], x[4 * jj + 2], x[4 * jj + 3]), b, s);
                     sts128(dstBig + off, b);
                     sts128(dstSmall + off, s);
                 }
             }
         }
 
-        // every thread of the warp polls: the data behind the barrier is then visible to each of them
-        __device__ __forceinline__ bool mbarWaitAll(uint32_t bar, uint32_t parity, volatile int* abortFlag)
+        // Bounded wait by one thread. spin: poll with test_wait instead of the suspending try_wait. sleepNs: pause
+        // between polls, so that a waiting warp leaves the issue slots of its scheduler to the warps that work.
+        __device__ __forceinline__ bool tfWait(uint32_t bar, uint32_t parity, volatile int* abortFlag, bool spin, uint32_t sleepNs = 0)
         {
-            const bool ok = mbarWait(bar, parity, abortFlag);
-            return __all_sync(0xffffffffu, ok);
+            long long t0 = 0;
+            for(uint32_t it = 1;; it++)
+            {
+                uint32_t done;
+                if(spin)
+                    asm volatile("{\n\t.reg .pred p;\n\t"
+                                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                                 "selp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(done)
+                                 : "r"(bar), "r"(parity)
+                                 : "memory");
+                else
+                    asm volatile("{\n\t.reg .pred p;\n\t"
+                                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                                 "selp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(done)
+                                 : "r"(bar), "r"(parity)
+                                 : "memory");
+                if(done)
+                    return true;
+                if(sleepNs)
+                    __nanosleep(sleepNs);
+                if((it & 255) == 0)
+                {
+                    if(t0 == 0)
+                        t0 = clock64();
+                    if(*abortFlag)
+                        return false;
+                    if(clock64() - t0 > kWaitCycles)
+                    {
+                        *abortFlag = 1;
+                        return false;
+                    }
+                }
+            }
         }
-
         // Accumulation. The tensor cores add each 8-wide group of products to the fp32 accumulator with
         // truncation, which over a long K would cost several digits. So
         //   * the two correction products (small*big, big*small), whose sum is 2^-11 of the result and whose
@@ -252,12 +328,15 @@ namespace htb
             extern __shared__ unsigned char smemRaw[];
             unsigned char* tiles = (unsigned char*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
 
-            __shared__ __align__(8) unsigned long long stFullBar[kStagingSlots], stEmptyBar[kStagingSlots];
-            __shared__ __align__(8) unsigned long long opFullBar[kOpSlots], opEmptyBar[kOpSlots];
+            using Ring = TfRing<PAIR>;
+            constexpr int      kStagingSlots = Ring::kStagingSlots, kOpSlots = Ring::kOpSlots;
+            constexpr uint32_t kStagingBytes = Ring::kStagingBytes, kOpBytes = Ring::kOpBytes, kBBytes = Ring::kBBytes;
+            __shared__ __align__(8) unsigned long long stFullBar[kMaxSlots], stEmptyBar[kMaxSlots];
+            __shared__ __align__(8) unsigned long long opFullBar[kMaxSlots], opEmptyBar[kMaxSlots];
             __shared__ __align__(8) unsigned long long segFullBar[2], segEmptyBar[2], corrFullBar[2], corrEmptyBar[2];
             __shared__ uint32_t tmemBase;
             __shared__ int      abortFlag;
-            __shared__ int64_t  colOff[4][128]; // one table per epilogue warp
+            __shared__ int64_t  colOff[kEpiWarps][64]; // one table per epilogue warp
 
             const int      warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
             const uint32_t rank   = PAIR ? clusterRank() : 0u;
@@ -277,19 +356,19 @@ namespace htb
                 for(int s = 0; s < kStagingSlots; s++)
                 {
                     mbarInit(smemAddr(&stFullBar[s]), 1);
-                    mbarInit(smemAddr(&stEmptyBar[s]), 4); // the four converter warps
+                    mbarInit(smemAddr(&stEmptyBar[s]), kConvWarps);
                 }
                 for(int s = 0; s < kOpSlots; s++)
                 {
-                    mbarInit(smemAddr(&opFullBar[s]), 4 * ctas); // converter warps of the whole pair (leader's copy is used)
+                    mbarInit(smemAddr(&opFullBar[s]), kConvWarps * ctas); // converter warps of the whole pair (leader's copy is used)
                     mbarInit(smemAddr(&opEmptyBar[s]), 1);
                 }
                 for(int i = 0; i < 2; i++)
                 {
                     mbarInit(smemAddr(&segFullBar[i]), 1);
-                    mbarInit(smemAddr(&segEmptyBar[i]), 128 * ctas);
+                    mbarInit(smemAddr(&segEmptyBar[i]), kEpiWarps * ctas); // one arrival per epilogue warp
                     mbarInit(smemAddr(&corrFullBar[i]), 1);
-                    mbarInit(smemAddr(&corrEmptyBar[i]), 128 * ctas);
+                    mbarInit(smemAddr(&corrEmptyBar[i]), kEpiWarps * ctas);
                 }
                 asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             }
@@ -317,6 +396,7 @@ namespace htb
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tmem      = tmemBase;
             volatile int*  abortP    = &abortFlag;
+            const bool     spin      = (a.probe & 32) != 0;
             const uint32_t stagingAddr = smemAddr(tiles);
             const uint32_t opAddr      = stagingAddr + kStagingSlots * kStagingBytes;
             const uint32_t stFull = smemAddr(&stFullBar[0]), stEmpty = smemAddr(&stEmptyBar[0]);
@@ -347,6 +427,8 @@ namespace htb
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
             };
             auto mma = [&](uint32_t d, uint64_t da, uint64_t db, uint32_t accumulate) {
+                if(a.probe & 2)
+                    return;
                 if(PAIR)
                     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                                  "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
@@ -362,7 +444,8 @@ namespace htb
             if(warp == 0)
             {
                 // ---------------------------------------------------------------- TMA producer
-                if(lane == 0)
+                // The whole warp waits (a warp that waits converged is woken promptly; a single diverged lane is not),
+                // lane 0 issues.
                 {
                     uint32_t slot = 0, phase = 0;
                     bool     ok = true;
@@ -370,17 +453,35 @@ namespace htb
                     {
                         int tm, tn;
                         tilesOf(u, tm, tn);
-                        const TfTile wm = tfTileOf(a.gm, tm), wn = tfTileOf(a.gn, tn);
+                        const TfTile   wm = tfTileOf(a.gm, tm), wn = tfTileOf(a.gn, tn);
+                        const TfChunks qm = tfChunksOf(a.gm, wm), qn = tfChunksOf(a.gn, wn);
+                        int            kc0 = 0, kc1 = 0, kq = 0; // K coordinates of the block (MN-major operands)
                         for(int kb = 0; kb < a.kBlocks; kb++)
                         {
-                            ok = mbarWaitTight(stEmpty + 8 * slot, phase ^ 1, abortP);
+                            ok = __all_sync(0xffffffffu, tfWait(stEmpty + 8 * slot, phase ^ 1, abortP, spin));
                             if(!ok)
                                 break;
-                            const uint32_t bar = stFull + 8 * slot;
-                            mbarArriveExpectTx(bar, a.bytesA + a.bytesB);
-                            const uint32_t dst = stagingAddr + slot * kStagingBytes;
-                            tfLoadRows(a.gm, wm, &mapA, dst, bar, kb, a);
-                            tfLoadRows(a.gn, wn, &mapB, dst + kTileBytes, bar, kb, a);
+                            if(lane == 0)
+                            {
+                                const uint32_t bar = stFull + 8 * slot;
+                                if(a.probe & 8)
+                                    mbarArrive(bar);
+                                else
+                                {
+                                    mbarArriveExpectTx(bar, a.bytesA + a.bytesB);
+                                    const uint32_t dst = stagingAddr + slot * kStagingBytes;
+                                    tfLoadRows(a.gm, wm, qm, &mapA, dst, bar, kb, kc0, kc1);
+                                    tfLoadRows(a.gn, wn, qn, &mapB, dst + kTileBytes, bar, kb, kc0, kc1);
+                                }
+                            }
+                            __syncwarp();
+                            kc0 += a.boxK[0];
+                            if(++kq == a.kTilesPerDim[0])
+                            {
+                                kq  = 0;
+                                kc0 = 0;
+                                kc1 += a.boxK[1];
+                            }
                             if(++slot == kStagingSlots)
                             {
                                 slot = 0;
@@ -393,7 +494,8 @@ namespace htb
             else if(warp == 1)
             {
                 // ---------------------------------------------------------------- MMA issuer (leader CTA of a pair)
-                if(lane == 0 && leader)
+                // the whole warp waits, lane 0 issues
+                if(leader)
                 {
                     const uint64_t descBase = smemDesc(opAddr);
                     uint32_t       slot = 0, phase = 0;
@@ -409,71 +511,73 @@ namespace htb
                         {
                             const bool     segStart = (kb % kSegBlocks) == 0;
                             const uint32_t sb       = seg & 1;
-                            if(segStart)
+                            if(segStart && !(a.probe & 16))
                             {
-                                ok = mbarWaitTight(segEmpty + 8 * sb, ((seg >> 1) & 1) ^ 1, abortP);
+                                ok = __all_sync(0xffffffffu, tfWait(segEmpty + 8 * sb, ((seg >> 1) & 1) ^ 1, abortP, spin));
                                 if(!ok)
                                     break;
                             }
-                            ok = mbarWaitTight(opFull + 8 * slot, phase, abortP);
-                            if(!ok)
-                                break;
-                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                            const uint32_t dMain = tmem + sb * 128u;
-                            // descriptor addresses count 16-byte units; 8 fp32 = 32 bytes = 2 units
-                            const uint64_t aBig = descBase + uint64_t((slot * kOpBytes) >> 4);
-                            const uint64_t aSml = aBig + (kTileBytes >> 4), bBig = aBig + (2 * kTileBytes >> 4),
-                                           bSml = aBig + (3 * kTileBytes >> 4);
-#pragma unroll
-                            for(int k = 0; k < kTfK / 8; k++)
-                                mma(dMain, aBig + uint64_t(2 * k), bBig + uint64_t(2 * k), (!segStart || k) ? 1u : 0u);
                             if(!corrReady)
                             {
                                 // the epilogue must have read this correction accumulator's previous tile
-                                ok = mbarWaitTight(corrEmpty + 8 * cb, ((local >> 1) & 1) ^ 1, abortP);
+                                ok = __all_sync(0xffffffffu, tfWait(corrEmpty + 8 * cb, ((local >> 1) & 1) ^ 1, abortP, spin));
                                 if(!ok)
                                     break;
-                                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                                 corrReady = true;
                             }
-#pragma unroll
-                            for(int k = 0; k < kTfK / 8; k++)
+                            ok = __all_sync(0xffffffffu, tfWait(opFull + 8 * slot, phase, abortP, spin));
+                            if(!ok)
+                                break;
+                            if(lane == 0)
                             {
-                                mma(dCorr, aSml + uint64_t(2 * k), bBig + uint64_t(2 * k), (kb | k) ? 1u : 0u);
-                                mma(dCorr, aBig + uint64_t(2 * k), bSml + uint64_t(2 * k), 1u);
+                                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                                const uint32_t dMain = tmem + sb * 128u;
+                                // descriptor addresses count 16-byte units; 8 fp32 = 32 bytes = 2 units
+                                const uint64_t aBig = descBase + uint64_t((slot * kOpBytes) >> 4);
+                                const uint64_t aSml = aBig + (kTileBytes >> 4), bBig = aBig + (2 * kTileBytes >> 4),
+                                               bSml = bBig + (kBBytes >> 4);
+#pragma unroll
+                                for(int k = 0; k < kTfK / 8; k++)
+                                    mma(dMain, aBig + uint64_t(2 * k), bBig + uint64_t(2 * k), (!segStart || k) ? 1u : 0u);
+#pragma unroll
+                                for(int k = 0; k < kTfK / 8; k++)
+                                {
+                                    mma(dCorr, aSml + uint64_t(2 * k), bBig + uint64_t(2 * k), (kb | k) ? 1u : 0u);
+                                    mma(dCorr, aBig + uint64_t(2 * k), bSml + uint64_t(2 * k), 1u);
+                                }
+                                commitTo(opEmpty + 8 * slot); // the ring slot is free (in both CTAs) once these MMAs have read it
+                                if(((kb % kSegBlocks) == kSegBlocks - 1 || kb == a.kBlocks - 1) && !(a.probe & 16))
+                                    commitTo(segFull + 8 * sb);
+                                if(kb == a.kBlocks - 1)
+                                    commitTo(corrFull + 8 * cb);
                             }
-                            commitTo(opEmpty + 8 * slot); // the ring slot is free (in both CTAs) once these MMAs have read it
+                            __syncwarp();
                             if(++slot == kOpSlots)
                             {
                                 slot = 0;
                                 phase ^= 1;
                             }
                             if((kb % kSegBlocks) == kSegBlocks - 1 || kb == a.kBlocks - 1)
-                            {
-                                commitTo(segFull + 8 * sb);
                                 seg++;
-                            }
                         }
-                        if(ok)
-                            commitTo(corrFull + 8 * cb);
                     }
                 }
             }
-            else if(warp < 6)
+            else if(warp < 2 + kEpiWarps)
             {
                 // ---------------------------------------------------------------- epilogue (every CTA: its own rows)
                 const int      quad  = warp & 3; // tensor-memory lane quadrant this warp may read
+                const int      half  = (warp - 2) >> 2; // which 64 accumulator columns
                 const int      row   = quad * 32 + lane;
-                int64_t*       cols  = colOff[quad];
-                const uint32_t lanes = tmem + (uint32_t(quad * 32) << 16);
+                const int      cbase = half * 64;
+                const bool     active = cbase < accCols; // a 64-column tile leaves the second half idle
+                int64_t*       cols  = colOff[warp - 2];
+                const uint32_t lanes = tmem + (uint32_t(quad * 32) << 16) + uint32_t(cbase);
                 uint32_t       seg   = 0;
                 int            local = 0;
                 bool           alive = true;
                 auto waitWarp = [&](uint32_t bar, uint32_t parity) {
-                    int ok = 1;
-                    if(lane == 0)
-                        ok = mbarWait(bar, parity, abortP) ? 1 : 0;
-                    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+                    return __all_sync(0xffffffffu, tfWait(bar, parity, abortP, spin, a.sleepNs)) != 0;
                 };
                 auto loadChunk = [&](uint32_t taddr, uint32_t(&v)[32]) {
                     asm volatile(
@@ -495,33 +599,35 @@ namespace htb
                     const int    tmRaw = PAIR ? 2 * um + int(rank) : um;
                     const bool   dupM  = tmRaw >= a.gm.tiles; // this CTA repeats its peer's rows: no stores
                     const TfTile wm    = tfTileOf(a.gm, min(tmRaw, a.gm.tiles - 1));
+                    // D offsets of this warp's 64 columns: a pair's accumulator holds the two CTAs' 64-row B tiles side
+                    // by side, a single CTA's holds one B tile of 64 or 128 rows
                     __syncwarp();
-                    for(int h = 0; h < ctas; h++)
                     {
-                        const int    tnRaw = PAIR ? 2 * un + h : un;
+                        const int    tnRaw = PAIR ? 2 * un + half : un;
                         const TfTile wn    = tfTileOf(a.gn, min(tnRaw, a.gn.tiles - 1));
-                        for(int c = lane; c < a.gn.rows; c += 32)
-                            cols[h * a.gn.rows + c] = (tnRaw < a.gn.tiles) ? tfRowOffset(a.gn, wn, c) : -1;
+                        const int    first = PAIR ? 0 : cbase;
+                        for(int c = lane; c < 64; c += 32)
+                            cols[c] = (tnRaw < a.gn.tiles && first + c < a.gn.rows) ? tfRowOffset(a.gn, wn, first + c) : -1;
                     }
                     __syncwarp();
-                    const int64_t offM = dupM ? -1 : tfRowOffset(a.gm, wm, row);
+                    const int64_t offM = (dupM || !active) ? -1 : tfRowOffset(a.gm, wm, row);
 
                     // running sums of the main product, one segment at a time
-                    float sum[128];
+                    float sum[64];
 #pragma unroll
-                    for(int j = 0; j < 128; j++)
+                    for(int j = 0; j < 64; j++)
                         sum[j] = 0.f;
-                    for(int s = 0; s < numSegs && alive; s++, seg++)
+                    for(int s = 0; s < ((a.probe & 16) ? 0 : numSegs) && alive; s++, seg++)
                     {
                         const uint32_t sb = seg & 1;
                         alive = waitWarp(segFull + 8 * sb, (seg >> 1) & 1);
                         if(!alive)
                             break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                        for(int c0 = 0; c0 < 128; c0 += 32)
+                        if(active && !(a.probe & 4))
                         {
-                            if(c0 < accCols)
+#pragma unroll
+                            for(int c0 = 0; c0 < 64; c0 += 32)
                             {
                                 uint32_t v[32];
                                 loadChunk(lanes + sb * 128u + uint32_t(c0), v);
@@ -530,8 +636,11 @@ namespace htb
                                     sum[c0 + j] = __fadd_rn(sum[c0 + j], __uint_as_float(v[j]));
                             }
                         }
+                        // the warp's loads have completed (wait::ld); one lane hands the buffer back for all
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        arriveIssuer(segEmpty + 8 * sb);
+                        __syncwarp();
+                        if(lane == 0)
+                            arriveIssuer(segEmpty + 8 * sb);
                     }
                     if(!alive)
                         break;
@@ -539,54 +648,53 @@ namespace htb
                     if(!alive)
                         break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                    for(int c0 = 0; c0 < 128; c0 += 32)
+                    if(active)
                     {
-                        if(c0 < accCols)
+#pragma unroll
+                        for(int c0 = 0; c0 < 64; c0 += 32)
                         {
                             uint32_t v[32];
                             loadChunk(lanes + 256u + uint32_t(cb) * 128u + uint32_t(c0), v);
-                            if(offM >= 0)
+                            if(offM < 0)
+                                continue;
+                            const int64_t first     = cols[c0];
+                            const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] == first + 31;
+                            if(fullChunk && ((offM + first) & 3) == 0)
                             {
-                                const int64_t first     = cols[c0];
-                                const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] == first + 31;
-                                if(fullChunk && ((offM + first) & 3) == 0)
-                                {
-                                    // 32 consecutive floats of this row: eight 128-bit stores
-                                    float*       dst = D + offM + first;
-                                    const float* src = C + offM + first;
+                                // 32 consecutive floats of this row: eight 128-bit stores
+                                float*       dst = D + offM + first;
+                                const float* src = C + offM + first;
 #pragma unroll
-                                    for(int j = 0; j < 32; j += 4)
+                                for(int j = 0; j < 32; j += 4)
+                                {
+                                    float4 o;
+                                    o.x = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j], __uint_as_float(v[j])));
+                                    o.y = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 1], __uint_as_float(v[j + 1])));
+                                    o.z = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 2], __uint_as_float(v[j + 2])));
+                                    o.w = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 3], __uint_as_float(v[j + 3])));
+                                    if(a.bilinear)
                                     {
-                                        float4 o;
-                                        o.x = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j], __uint_as_float(v[j])));
-                                        o.y = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 1], __uint_as_float(v[j + 1])));
-                                        o.z = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 2], __uint_as_float(v[j + 2])));
-                                        o.w = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 3], __uint_as_float(v[j + 3])));
-                                        if(a.bilinear)
-                                        {
-                                            const float4 c4 = *(const float4*)(src + j);
-                                            o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4.x));
-                                            o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4.y));
-                                            o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4.z));
-                                            o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4.w));
-                                        }
-                                        *(float4*)(dst + j) = o;
+                                        const float4 c4 = *(const float4*)(src + j);
+                                        o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4.x));
+                                        o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4.y));
+                                        o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4.z));
+                                        o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4.w));
                                     }
+                                    *(float4*)(dst + j) = o;
                                 }
-                                else
-                                {
+                            }
+                            else
+                            {
 #pragma unroll
-                                    for(int j = 0; j < 32; j++)
+                                for(int j = 0; j < 32; j++)
+                                {
+                                    const int64_t oc = cols[c0 + j];
+                                    if(oc >= 0)
                                     {
-                                        const int64_t oc = cols[c0 + j];
-                                        if(oc >= 0)
-                                        {
-                                            float y = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j], __uint_as_float(v[j])));
-                                            if(a.bilinear)
-                                                y = __fadd_rn(y, __fmul_rn(a.beta, C[offM + oc]));
-                                            D[offM + oc] = y;
-                                        }
+                                        float y = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j], __uint_as_float(v[j])));
+                                        if(a.bilinear)
+                                            y = __fadd_rn(y, __fmul_rn(a.beta, C[offM + oc]));
+                                        D[offM + oc] = y;
                                     }
                                 }
                             }
@@ -594,13 +702,16 @@ namespace htb
                     }
                     // hand the correction accumulator back
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    arriveIssuer(corrEmpty + 8 * cb);
+                    __syncwarp();
+                    if(lane == 0)
+                        arriveIssuer(corrEmpty + 8 * cb);
                 }
             }
             else
             {
                 // ---------------------------------------------------------------- converter (every CTA: its own rows)
-                const int r    = int(threadIdx.x) - 192;
+                const int  ct   = int(threadIdx.x) - 32 * (2 + kEpiWarps);
+                const int  r    = ct & 127, kh = ct >> 7; // tile row, half of the K block
                 const bool hasB = r < a.gn.rows;
                 uint32_t   sSlot = 0, sPhase = 0, oSlot = 0, oPhase = 0;
                 bool       ok = true;
@@ -608,14 +719,19 @@ namespace htb
                 {
                     for(int kb = 0; kb < a.kBlocks; kb++)
                     {
-                        ok = mbarWaitAll(stFull + 8 * sSlot, sPhase, abortP) && mbarWaitAll(opEmpty + 8 * oSlot, oPhase ^ 1, abortP);
+                        ok = tfWait(stFull + 8 * sSlot, sPhase, abortP, spin, a.sleepNs)
+                             && tfWait(opEmpty + 8 * oSlot, oPhase ^ 1, abortP, spin, a.sleepNs);
+                        ok = __all_sync(0xffffffffu, ok);
                         if(!ok)
                             break;
                         const uint32_t st = stagingAddr + sSlot * kStagingBytes;
                         const uint32_t op = opAddr + oSlot * kOpBytes;
-                        tfConvertRow(a.gm.major, st, op, op + kTileBytes, r);
-                        if(hasB)
-                            tfConvertRow(a.gn.major, st + kTileBytes, op + 2 * kTileBytes, op + 3 * kTileBytes, r);
+                        if(!(a.probe & 1))
+                        {
+                            tfConvertRow(a.gm.major, st, op, op + kTileBytes, r, kh);
+                            if(hasB)
+                                tfConvertRow(a.gn.major, st + kTileBytes, op + 2 * kTileBytes, op + 2 * kTileBytes + kBBytes, r, kh);
+                        }
                         // the ring is read by the tensor cores (async proxy): order this thread's stores before it
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
@@ -765,7 +881,7 @@ namespace htb
                                  cudaStream_t stream)
         {
             auto         kernel = contraction_tf32x3_kernel<PAIR>;
-            const size_t smem   = size_t(kStagingSlots) * kStagingBytes + size_t(kOpSlots) * kOpBytes + 1024;
+            const size_t smem   = size_t(TfRing<PAIR>::kTotal) + 1024;
             static bool  attrSet = false;
             if(!attrSet)
             {
@@ -831,24 +947,16 @@ namespace htb
             sKa[i]  = p.k[i].s0;
             sKb[i]  = p.k[i].s1;
         }
-        // CTA pairs (256 x 128 tiles, each CTA loading 64 rows of B) unless a repeated edge tile would waste
-        // more than a tenth of the work
-        bool pair = p.pair != 0;
+        // Single CTAs with 128 x 128 tiles by default. CTA pairs (256 x 128 tiles, each CTA loading 64 rows of B,
+        // three ring slots instead of two) measured slower on 4096^3 (1.53 ms against 1.14 ms): the kernel is
+        // bound by the latency around its rings, which the cross-CTA signalling lengthens, not by the shared-memory
+        // bandwidth that a pair saves. HTB_TF32_PAIR=1 selects them.
+        bool pair = false;
         if(const char* env = getenv("HTB_TF32_PAIR"))
-            pair = pair && atoi(env) != 0;
-
+            pair = p.pair != 0 && atoi(env) != 0;
         TfArgs a{};
         fillGroup(a.gm, vm, p.aMajor, 128, p.boxM);
         fillGroup(a.gn, vn, p.bMajor, pair ? 64 : p.tileN, pair ? p.boxN128 : p.boxN);
-        if(pair && getenv("HTB_TF32_PAIR") == nullptr)
-        {
-            const int wasteM = 2 * ((a.gm.tiles + 1) / 2) - a.gm.tiles, wasteN = 2 * ((a.gn.tiles + 1) / 2) - a.gn.tiles;
-            if(wasteM * 10 > a.gm.tiles || wasteN * 10 > a.gn.tiles)
-            {
-                pair = false;
-                fillGroup(a.gn, vn, p.bMajor, p.tileN, p.boxN);
-            }
-        }
         CUtensorMap mapA, mapB;
         const bool  okA = p.aMajor ? encodeMnMajor(encode, &mapA, A, vm, p.nk, extK, sKa, p.boxK)
                                    : encodeKMajor(encode, &mapA, A, p.K, vm, p.boxM);
@@ -870,6 +978,11 @@ namespace htb
         a.pairsM   = (a.gm.tiles + 1) / 2;
         a.pairsN   = (a.gn.tiles + 1) / 2;
         a.status   = deviceStatus;
+        if(const char* env = getenv("HTB_TF32_PROBE"))
+            a.probe = atoi(env);
+        a.sleepNs = 0;
+        if(const char* env = getenv("HTB_TF32_SLEEP"))
+            a.sleepNs = uint32_t(atoi(env));
         if(int64_t(a.gm.tiles) * a.gn.tiles > 0x7fffffffll)
             return cudaErrorInvalidConfiguration;
         HTB_LOG_HEUR("hiptensorContraction", "tf32x3: %d x %d row tiles (%d B rows each), %d K blocks, %s", a.gm.tiles,

@@ -113,15 +113,22 @@ def test_cta_pair_kernel_forced(env, layout):
 
 
 @pytest.mark.parametrize("layout", ["kk", "mn_mn"])
-def test_cta_pair_kernel_large(env, layout):
-    """Large enough for the pair kernel to be chosen; checked on 4096 sampled outputs."""
+@pytest.mark.parametrize("pair", [False, True])
+def test_large_sampled(env, layout, pair):
+    """Several tiles per CTA (the rings, segment accumulators and correction accumulators wrap around many times);
+    checked on 4096 sampled outputs. Single CTAs (the default) and CTA pairs."""
     ht, h = env
     M, N, K = 2048, 2560, 512
     modeA, modeB = LAYOUTS[layout]
     smp = np.random.default_rng(11).integers(0, M * N, 4096)
-    got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F32, alpha=1.0, beta=0.5,
-                                   sample=smp)
-    assert ht.last_kernel_name() == "contraction_tf32x3_pair"
+    if pair:
+        os.environ["HTB_TF32_PAIR"] = "1"
+    try:
+        got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F32, alpha=1.0,
+                                       beta=0.5, sample=smp)
+    finally:
+        os.environ.pop("HTB_TF32_PAIR", None)
+    assert ht.last_kernel_name() == ("contraction_tf32x3_pair" if pair else "contraction_tf32x3")
     assert not np.isnan(got).any()
     err = rel_error(got, exp, td)
     assert 0 <= err < 2 * K * EPS, err
