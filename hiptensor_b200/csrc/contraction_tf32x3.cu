@@ -83,7 +83,6 @@ namespace htb
             int      bilinear;
             int      nContig; // 32 consecutive columns of a tile are 32 consecutive, 16-byte aligned floats of D
             int      pairsM, pairsN; // PAIR only
-            uint32_t sleepNs; // pause between barrier polls of the multi-warp roles
             int      probe; // measurement aid, bit mask: 1 = converter skips its work, 2 = issuer skips the MMAs,
                             // 8 = producer skips the loads (results invalid)
             int*     status;
@@ -269,32 +268,22 @@ namespace htb
             }
         }
 
-        // Bounded wait by one thread. spin: poll with test_wait instead of the suspending try_wait. sleepNs: pause
-        // between polls, so that a waiting warp leaves the issue slots of its scheduler to the warps that work.
-        __device__ __forceinline__ bool tfWait(uint32_t bar, uint32_t parity, volatile int* abortFlag, bool spin, uint32_t sleepNs = 0)
+        // Bounded wait, executed by every thread of the waiting warp: a tight try_wait loop, the clock is read only
+        // every 256th unsuccessful poll.
+        __device__ __forceinline__ bool tfWait(uint32_t bar, uint32_t parity, volatile int* abortFlag)
         {
             long long t0 = 0;
             for(uint32_t it = 1;; it++)
             {
                 uint32_t done;
-                if(spin)
-                    asm volatile("{\n\t.reg .pred p;\n\t"
-                                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                                 "selp.u32 %0, 1, 0, p;\n\t}"
-                                 : "=r"(done)
-                                 : "r"(bar), "r"(parity)
-                                 : "memory");
-                else
-                    asm volatile("{\n\t.reg .pred p;\n\t"
-                                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                                 "selp.u32 %0, 1, 0, p;\n\t}"
-                                 : "=r"(done)
-                                 : "r"(bar), "r"(parity)
-                                 : "memory");
+                asm volatile("{\n\t.reg .pred p;\n\t"
+                             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                             "selp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(done)
+                             : "r"(bar), "r"(parity)
+                             : "memory");
                 if(done)
                     return true;
-                if(sleepNs)
-                    __nanosleep(sleepNs);
                 if((it & 255) == 0)
                 {
                     if(t0 == 0)
@@ -309,6 +298,7 @@ namespace htb
                 }
             }
         }
+
         // Accumulation. The tensor cores add each 8-wide group of products to the fp32 accumulator with
         // truncation, which over a long K would cost several digits. So
         //   * the two correction products (small*big, big*small), whose sum is 2^-11 of the result and whose
@@ -396,7 +386,6 @@ namespace htb
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tmem      = tmemBase;
             volatile int*  abortP    = &abortFlag;
-            const bool     spin      = (a.probe & 32) != 0;
             const uint32_t stagingAddr = smemAddr(tiles);
             const uint32_t opAddr      = stagingAddr + kStagingSlots * kStagingBytes;
             const uint32_t stFull = smemAddr(&stFullBar[0]), stEmpty = smemAddr(&stEmptyBar[0]);
@@ -427,8 +416,6 @@ namespace htb
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
             };
             auto mma = [&](uint32_t d, uint64_t da, uint64_t db, uint32_t accumulate) {
-                if(a.probe & 2)
-                    return;
                 if(PAIR)
                     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                                  "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d),
@@ -458,7 +445,7 @@ namespace htb
                         int            kc0 = 0, kc1 = 0, kq = 0; // K coordinates of the block (MN-major operands)
                         for(int kb = 0; kb < a.kBlocks; kb++)
                         {
-                            ok = __all_sync(0xffffffffu, tfWait(stEmpty + 8 * slot, phase ^ 1, abortP, spin));
+                            ok = __all_sync(0xffffffffu, tfWait(stEmpty + 8 * slot, phase ^ 1, abortP));
                             if(!ok)
                                 break;
                             if(lane == 0)
@@ -498,6 +485,8 @@ namespace htb
                 if(leader)
                 {
                     const uint64_t descBase = smemDesc(opAddr);
+                    const uint32_t descLo = uint32_t(descBase), descHi = uint32_t(descBase >> 32);
+                    auto           descOf = [&](uint32_t lo) { return (uint64_t(descHi) << 32) | lo; };
                     uint32_t       slot = 0, phase = 0;
                     uint32_t       seg = 0; // running count of segments: buffer seg & 1, use (seg >> 1)
                     int            local = 0;
@@ -511,42 +500,50 @@ namespace htb
                         {
                             const bool     segStart = (kb % kSegBlocks) == 0;
                             const uint32_t sb       = seg & 1;
-                            if(segStart && !(a.probe & 16))
+                            if(segStart)
                             {
-                                ok = __all_sync(0xffffffffu, tfWait(segEmpty + 8 * sb, ((seg >> 1) & 1) ^ 1, abortP, spin));
+                                ok = __all_sync(0xffffffffu, tfWait(segEmpty + 8 * sb, ((seg >> 1) & 1) ^ 1, abortP));
                                 if(!ok)
                                     break;
                             }
                             if(!corrReady)
                             {
                                 // the epilogue must have read this correction accumulator's previous tile
-                                ok = __all_sync(0xffffffffu, tfWait(corrEmpty + 8 * cb, ((local >> 1) & 1) ^ 1, abortP, spin));
+                                ok = __all_sync(0xffffffffu, tfWait(corrEmpty + 8 * cb, ((local >> 1) & 1) ^ 1, abortP));
                                 if(!ok)
                                     break;
                                 corrReady = true;
                             }
-                            ok = __all_sync(0xffffffffu, tfWait(opFull + 8 * slot, phase, abortP, spin));
+                            ok = __all_sync(0xffffffffu, tfWait(opFull + 8 * slot, phase, abortP));
                             if(!ok)
                                 break;
                             if(lane == 0)
                             {
                                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                                 const uint32_t dMain = tmem + sb * 128u;
-                                // descriptor addresses count 16-byte units; 8 fp32 = 32 bytes = 2 units
-                                const uint64_t aBig = descBase + uint64_t((slot * kOpBytes) >> 4);
-                                const uint64_t aSml = aBig + (kTileBytes >> 4), bBig = aBig + (2 * kTileBytes >> 4),
-                                               bSml = bBig + (kBBytes >> 4);
-#pragma unroll
-                                for(int k = 0; k < kTfK / 8; k++)
-                                    mma(dMain, aBig + uint64_t(2 * k), bBig + uint64_t(2 * k), (!segStart || k) ? 1u : 0u);
-#pragma unroll
-                                for(int k = 0; k < kTfK / 8; k++)
+                                // Descriptors differ in their low word only (the start address in 16-byte units, which
+                                // cannot carry out of its field): four running low words, advanced by 2 units (8 fp32 =
+                                // 32 bytes) per K step, keep the issue loop short. The tensor cores need 64 cycles per
+                                // MMA; a longer issue sequence would leave them idle.
+                                uint32_t aBig = descLo + slot * (kOpBytes >> 4);
+                                uint32_t aSml = aBig + (kTileBytes >> 4), bBig = aBig + (2 * kTileBytes >> 4),
+                                         bSml = bBig + (kBBytes >> 4);
+                                if(!(a.probe & 2))
                                 {
-                                    mma(dCorr, aSml + uint64_t(2 * k), bBig + uint64_t(2 * k), (kb | k) ? 1u : 0u);
-                                    mma(dCorr, aBig + uint64_t(2 * k), bSml + uint64_t(2 * k), 1u);
+#pragma unroll
+                                    for(int k = 0; k < kTfK / 8; k++)
+                                    {
+                                        mma(dMain, descOf(aBig), descOf(bBig), (!segStart || k) ? 1u : 0u);
+                                        mma(dCorr, descOf(aSml), descOf(bBig), (kb | k) ? 1u : 0u);
+                                        mma(dCorr, descOf(aBig), descOf(bSml), 1u);
+                                        aBig += 2;
+                                        aSml += 2;
+                                        bBig += 2;
+                                        bSml += 2;
+                                    }
                                 }
                                 commitTo(opEmpty + 8 * slot); // the ring slot is free (in both CTAs) once these MMAs have read it
-                                if(((kb % kSegBlocks) == kSegBlocks - 1 || kb == a.kBlocks - 1) && !(a.probe & 16))
+                                if((kb % kSegBlocks) == kSegBlocks - 1 || kb == a.kBlocks - 1)
                                     commitTo(segFull + 8 * sb);
                                 if(kb == a.kBlocks - 1)
                                     commitTo(corrFull + 8 * cb);
@@ -577,7 +574,7 @@ namespace htb
                 int            local = 0;
                 bool           alive = true;
                 auto waitWarp = [&](uint32_t bar, uint32_t parity) {
-                    return __all_sync(0xffffffffu, tfWait(bar, parity, abortP, spin, a.sleepNs)) != 0;
+                    return __all_sync(0xffffffffu, tfWait(bar, parity, abortP)) != 0;
                 };
                 auto loadChunk = [&](uint32_t taddr, uint32_t(&v)[32]) {
                     asm volatile(
@@ -617,14 +614,14 @@ namespace htb
 #pragma unroll
                     for(int j = 0; j < 64; j++)
                         sum[j] = 0.f;
-                    for(int s = 0; s < ((a.probe & 16) ? 0 : numSegs) && alive; s++, seg++)
+                    for(int s = 0; s < numSegs && alive; s++, seg++)
                     {
                         const uint32_t sb = seg & 1;
                         alive = waitWarp(segFull + 8 * sb, (seg >> 1) & 1);
                         if(!alive)
                             break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        if(active && !(a.probe & 4))
+                        if(active)
                         {
 #pragma unroll
                             for(int c0 = 0; c0 < 64; c0 += 32)
@@ -719,8 +716,8 @@ namespace htb
                 {
                     for(int kb = 0; kb < a.kBlocks; kb++)
                     {
-                        ok = tfWait(stFull + 8 * sSlot, sPhase, abortP, spin, a.sleepNs)
-                             && tfWait(opEmpty + 8 * oSlot, oPhase ^ 1, abortP, spin, a.sleepNs);
+                        ok = tfWait(stFull + 8 * sSlot, sPhase, abortP)
+                             && tfWait(opEmpty + 8 * oSlot, oPhase ^ 1, abortP);
                         ok = __all_sync(0xffffffffu, ok);
                         if(!ok)
                             break;
@@ -980,9 +977,6 @@ namespace htb
         a.status   = deviceStatus;
         if(const char* env = getenv("HTB_TF32_PROBE"))
             a.probe = atoi(env);
-        a.sleepNs = 0;
-        if(const char* env = getenv("HTB_TF32_SLEEP"))
-            a.sleepNs = uint32_t(atoi(env));
         if(int64_t(a.gm.tiles) * a.gn.tiles > 0x7fffffffll)
             return cudaErrorInvalidConfiguration;
         HTB_LOG_HEUR("hiptensorContraction", "tf32x3: %d x %d row tiles (%d B rows each), %d K blocks, %s", a.gm.tiles,
