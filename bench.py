@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the three hot paths on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5|c4f32] [--impl reference]
 
 One step = one pass of the hot path over one batch of seeded synthetic input, called through the
 library's C ABI. The default workload is BASELINE configs[1] (c2): the fp32 rank-4 permutation
@@ -331,6 +331,41 @@ class ContractionC4(ContractionBase):
         return 2 * 65536 * 4096 / dt / 1e12, "oracle on 65536 sampled outputs (268 M multiply-adds), exact k order"
 
 
+class ContractionC4F32(ContractionBase):
+    """Not a BASELINE config: config 4's shape with fp32 operands, the large case of the fp32 tensor-core kernel."""
+    name, metric, dtype = "c4f32", "contraction_tflops", "f32 (TF32 big/small split, three MMAs per product)"
+
+    def setup(self):
+        m0, m1, n0, n1, k0, k1 = range(6)
+        self._setup({m: 64 for m in range(6)}, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], 0, 0,
+                    self.ht.COMPUTE_32F, 1.0, 0.0, False, False, True, (255, 256, 257))
+        self.flops = 2 * 4096 ** 3
+
+    def config(self):
+        return {"workload": "c4f32: config 4 with fp32 operands, D[m0,m1,n0,n1]=A[m0,m1,k0,k1]*B[n0,n1,k0,k1], extents 64 "
+                            "(folded M=N=K=4096), k modes innermost, alpha=1, beta=0, values normal(0,0.5)",
+                "parallelism": "mode m0 sharded, one slab of 64 per GPU, B replicated, no collective",
+                "cache": "operands (128 MiB) about fill L2 (126 MB); a 256 MiB buffer is written between steps to flush it"}
+
+    flush_l2 = True
+
+    def cpu_sample(self, nthreads):
+        import numpy as np
+        from oracle import binding as orc
+        m0, m1, n0, n1, k0, k1 = range(6)
+        l = [64] * 4
+        s = packed(l, False)
+        A = orc.fill_normal(64 ** 4, orc.F32, 255, 0.5)
+        B = orc.fill_normal(64 ** 4, orc.F32, 256, 0.5)
+        D = np.empty(64 ** 4, dtype=np.float32)
+        smp = np.random.default_rng(0).integers(0, 64 ** 4, 65536)
+        t0 = time.perf_counter()
+        orc.contraction(1.0, A, l, s, [m0, m1, k0, k1], orc.F32, B, l, s, [n0, n1, k0, k1], orc.F32, 0.0, None, D, l, s,
+                        [m0, m1, n0, n1], orc.F32, orc.COMPUTE_32F, sample=smp, nthreads=nthreads)
+        dt = time.perf_counter() - t0
+        return 2 * 65536 * 4096 / dt / 1e12, "oracle on 65536 sampled outputs (268 M multiply-adds), exact k order"
+
+
 class ContractionC1(ContractionBase):
     name, metric, dtype = "c1", "contraction_tflops", "f32"
 
@@ -399,7 +434,8 @@ class ContractionC5(ContractionBase):
         return 2 * 65536 * 2304 / dt / 1e12, "oracle on 65536 sampled outputs (151 M multiply-adds), exact k order"
 
 
-WORKLOADS = {"c1": ContractionC1, "c2": PermutationC2, "c3": ReductionC3, "c4": ContractionC4, "c5": ContractionC5}
+WORKLOADS = {"c1": ContractionC1, "c2": PermutationC2, "c3": ReductionC3, "c4": ContractionC4, "c5": ContractionC5,
+             "c4f32": ContractionC4F32}
 
 
 # --------------------------------------------------------------------------------------------- timing
@@ -501,12 +537,16 @@ def run_gpu(args):
             peak, punit = pk["hbm"], "GB/s"
         elif wl.name == "c5":
             peak, punit = NOMINAL_FP64_TFLOPS, "TFLOP/s"
+        elif wl.name in ("c1", "c4f32"):
+            # fp32 on the tensor cores: TF32 runs at half the bf16 rate and every product takes three MMAs
+            peak, punit = round(pk["bf16"] / 6.0, 1), "TFLOP/s"
         else:
             peak, punit = pk["bf16"], "TFLOP/s"
         roof = {"bound": wl.bound, "achieved": round(achieved, 2), "peak": peak, "unit": punit,
                 "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
                 "peak_source": "nominal FP64 tensor pipe (no measured figure)" if wl.name == "c5" else
-                ("of measured (MEASURED_PEAKS.json)" if pk["source"] == "measured" else "of fallback"),
+                (("of measured (MEASURED_PEAKS.json)" if pk["source"] == "measured" else "of fallback")
+                 + ("; bf16 rate / 2 for TF32 / 3 MMAs per product" if wl.name in ("c1", "c4f32") else "")),
                 "kernel": ht.last_kernel_name()}
         ncores = os.cpu_count() or 1
         cpu_value, sample = wl.cpu_sample(ncores)

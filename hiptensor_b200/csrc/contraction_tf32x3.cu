@@ -228,19 +228,24 @@ namespace htb
             asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
         }
 
-        // One thread converts half h (16 k) of row r of a 128 x 32 tile: staging -> (big, small) in the K-major ring
-        // layout, where the 16-byte piece j of row r sits at r*128 + ((j ^ (r & 7)) << 4). Within a quarter warp the
-        // eight rows touch eight different pieces, so the 128-bit accesses are free of bank conflicts.
-        __device__ __forceinline__ void tfConvertRow(int major, uint32_t src, uint32_t dstBig, uint32_t dstSmall, int r, int h)
+        // Conversion of a rows x 32 tile by the 256 converter threads (thread: row r = 0..127, K half h):
+        // staging -> (big, small) in the K-major ring layout, where the 16-byte piece j of row r sits at
+        // r*128 + ((j ^ (r & 7)) << 4).
+        __device__ __forceinline__ void tfConvertRow(int major, uint32_t src, uint32_t dstBig, uint32_t dstSmall, int r, int h, int rows)
         {
             const uint32_t rowOff = uint32_t(r) * 128;
             if(major == 0)
             {
-                // staging has the ring layout already (TMA 128-byte swizzle)
+                // Staging has the ring layout already (TMA 128-byte swizzle): the copy is position by position. Eight
+                // consecutive threads take the eight 16-byte pieces of one row, a warp four rows, the 256 converter
+                // threads 32 rows per pass.
+                const int t = r + 128 * h; // converter thread index
 #pragma unroll
-                for(int jj = 0; jj < 4; jj++)
+                for(int pass = 0; pass < 4; pass++)
                 {
-                    const uint32_t off = rowOff + (uint32_t((4 * h + jj) ^ (r & 7)) << 4);
+                    if(pass * 32 >= rows)
+                        break;
+                    const uint32_t off = uint32_t(pass * 32 + (t >> 3)) * 128 + (uint32_t(t & 7) << 4);
                     const float4   v   = lds128(src + off);
                     float4         b, s;
                     tfSplit4(v, b, s);
@@ -248,7 +253,7 @@ namespace htb
                     sts128(dstSmall + off, s);
                 }
             }
-            else
+            else if(r < rows)
             {
                 // staging: chunk r/32 holds [32 k][32 rows], unswizzled; the lanes of a warp read 32 consecutive floats
                 const uint32_t col = src + uint32_t(r >> 5) * (kTfK * 128) + uint32_t(r & 31) * 4 + uint32_t(h) * (16 * 128);
@@ -709,7 +714,6 @@ namespace htb
                 // ---------------------------------------------------------------- converter (every CTA: its own rows)
                 const int  ct   = int(threadIdx.x) - 32 * (2 + kEpiWarps);
                 const int  r    = ct & 127, kh = ct >> 7; // tile row, half of the K block
-                const bool hasB = r < a.gn.rows;
                 uint32_t   sSlot = 0, sPhase = 0, oSlot = 0, oPhase = 0;
                 bool       ok = true;
                 for(int u = worker; u < numUnits && ok; u += numWorkers)
@@ -725,9 +729,9 @@ namespace htb
                         const uint32_t op = opAddr + oSlot * kOpBytes;
                         if(!(a.probe & 1))
                         {
-                            tfConvertRow(a.gm.major, st, op, op + kTileBytes, r, kh);
-                            if(hasB)
-                                tfConvertRow(a.gn.major, st + kTileBytes, op + 2 * kTileBytes, op + 2 * kTileBytes + kBBytes, r, kh);
+                            tfConvertRow(a.gm.major, st, op, op + kTileBytes, r, kh, 128);
+                            tfConvertRow(a.gn.major, st + kTileBytes, op + 2 * kTileBytes, op + 2 * kTileBytes + kBBytes, r, kh,
+                                         a.gn.rows);
                         }
                         // the ring is read by the tensor cores (async proxy): order this thread's stores before it
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
