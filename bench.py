@@ -36,7 +36,8 @@ NOMINAL_FP64_TFLOPS = 40.0  # FP64 tensor pipe, nominal: no measured figure exis
 
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the
 # ncu captures summarised under profiles/, full-size workloads, one launch each).
-NCU_TRAFFIC_BYTES = {"c2": 2113114000, "c3": 2153492640, "c4": 108542464, "c1": 4046848, "c5": 310886656}
+NCU_TRAFFIC_BYTES = {"c2": 2113114000, "c3": 2153492640, "c4": 108542464, "c1": 4097024, "c5": 351778816,
+                     "c4f32": 636672256}
 
 
 def peaks():
