@@ -88,6 +88,32 @@ def test_contraction_config1(ht):
                                      [0, 1, 2, 3], ht.R_32F, True, ht.COMPUTE_32F)
     # D is contiguous along m0: operands are exchanged so that the kernel sees it along N
     assert "M=576 N=576 K=576" in d and "swapped=1" in d and "n[576:1/1]" in d and "k[576:576/576]" in d
+    # fp32 with 16-byte aligned strides: tensor-core path, both operands taken MN-major in 32-row chunks
+    assert "kind=tf32x3" in d and "major=mn/mn" in d and "boxK=[32 1]" in d
+
+
+def test_contraction_fp32_tensor_core_layouts(ht):
+    """The four K-/MN-major operand layouts of plain matrices, a two-mode K box, and the cases that stay on the
+    FMA kernel (strides that are not multiples of 16 bytes, tiles smaller than 128 x 64, f16/bf16 compute)."""
+    f = ht.R_32F
+
+    def plan(lA, mA, lB, mB, lD, mD, compute=None):
+        return ht.describe_contraction_plan(lA, packed(lA, False), mA, f, lB, packed(lB, False), mB, f, lD,
+                                            packed(lD, False), mD, f, True, compute or ht.COMPUTE_32F)
+
+    M, N, K = 384, 1000, 136
+    assert "kind=tf32x3" in plan([M, K], [0, 2], [N, K], [1, 2], [M, N], [0, 1]) and "major=k/k" in plan(
+        [M, K], [0, 2], [N, K], [1, 2], [M, N], [0, 1])
+    assert "major=mn/mn" in plan([K, M], [2, 0], [K, N], [2, 1], [M, N], [0, 1])
+    assert "major=k/mn" in plan([M, K], [0, 2], [K, N], [2, 1], [M, N], [0, 1])
+    assert "major=mn/k" in plan([K, M], [2, 0], [N, K], [1, 2], [M, N], [0, 1])
+    # two K modes that do not fold: 16 x 2 box
+    d = plan([6, 5, 16, 40], [5, 1, 4, 0], [6, 3, 16, 72], [5, 3, 4, 2], [5, 3, 40, 72], [1, 3, 0, 2])
+    assert "kind=tf32x3" in d and "boxK=[16 2]" in d and "M=200 N=216 K=96" in d
+    # not eligible
+    assert "kind=tiled_simt" in plan([130, 34], [0, 2], [70, 34], [1, 2], [130, 70], [0, 1])
+    assert "kind=tiled_simt" in plan([64, 64], [0, 2], [64, 64], [1, 2], [64, 64], [0, 1])
+    assert "kind=tiled_simt" in plan([M, K], [0, 2], [N, K], [1, 2], [M, N], [0, 1], ht.COMPUTE_16F)
 
 
 def test_contraction_config4(ht):
