@@ -33,6 +33,7 @@
 
 #include "kernels.hpp"
 #include "tcgen05_util.cuh"
+#include "row_groups.cuh"
 
 namespace htb
 {
@@ -60,6 +61,8 @@ namespace htb
             int     probe; // measurement aid, bit mask: 1 = producer skips the loads, 2 = issuer skips the MMAs,
                            // 4 = epilogue skips the stores (results invalid)
             int*    status;
+            // chunked row groups of MN-major operands (kernel instantiations with LAYOUT != 0 only)
+            TfGroup gm, gn;
         };
 
         template <typename T>
@@ -119,7 +122,9 @@ namespace htb
             return (r == 0) ? off : -1; // rows beyond the boxes' product do not exist
         }
 
-        template <typename TD>
+        // LAYOUT: bit 0 = A is MN-major, bit 1 = B is MN-major (64-row chunks instead of boxes, transposed
+        // shared-memory descriptors); 0 = both K-major.
+        template <typename TD, int LAYOUT>
         __global__ void __launch_bounds__(kThreads, 1)
             contraction_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                        const TD* __restrict__ C, TD* __restrict__ D, TcArgs a, uint32_t idesc)
@@ -180,8 +185,15 @@ namespace htb
                     {
                         const int tm = t % a.tilesM, tn = t / a.tilesM;
                         int       cA[5] = {0, 0, 0, 0, 0}, cB[5] = {0, 0, 0, 0, 0};
-                        tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cA + 1);
-                        tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB + 1);
+                        TfChunks  qA{}, qB{};
+                        if constexpr(LAYOUT & 1)
+                            qA = tfChunksOf(a.gm, tfTileOf(a.gm, tm));
+                        else
+                            tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cA + 1);
+                        if constexpr(LAYOUT & 2)
+                            qB = tfChunksOf(a.gn, tfTileOf(a.gn, tn));
+                        else
+                            tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB + 1);
                         for(int kb = 0; kb < a.kBlocks; kb++)
                         {
                             ok = mbarWait(smemAddr(&emptyBar[stage]), phase ^ 1, abortP);
@@ -192,8 +204,28 @@ namespace htb
                             cA[0] = kb * kTileK;
                             cB[0] = kb * kTileK;
                             const uint32_t dstA = smemAddr(tiles + size_t(stage) * stageStride);
-                            tmaLoad<5>(dstA, &mapA, bar, cA);
-                            tmaLoad<5>(dstA + aBytes, &mapB, bar, cB);
+                            if constexpr(LAYOUT & 1)
+                            {
+                                // MN-major map {mode0, K, mode1, mode2, 1}: one [64 k][64 rows] box per chunk
+#pragma unroll
+                                for(int j = 0; j < kTileM / 64; j++)
+                                {
+                                    const int c[5] = {qA.c0[j], kb * kTileK, qA.i1[j], qA.i2[j], 0};
+                                    tmaLoad<5>(dstA + uint32_t(j) * 8192, &mapA, bar, c);
+                                }
+                            }
+                            else
+                                tmaLoad<5>(dstA, &mapA, bar, cA);
+                            if constexpr(LAYOUT & 2)
+                            {
+                                for(int j = 0; j < (tileN >> 6); j++)
+                                {
+                                    const int c[5] = {qB.c0[j], kb * kTileK, qB.i1[j], qB.i2[j], 0};
+                                    tmaLoad<5>(dstA + aBytes + uint32_t(j) * 8192, &mapB, bar, c);
+                                }
+                            }
+                            else
+                                tmaLoad<5>(dstA + aBytes, &mapB, bar, cB);
                             if(++stage == a.stages)
                             {
                                 stage = 0;
@@ -228,16 +260,19 @@ namespace htb
                                 break;
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                             const uint32_t sa    = smemAddr(tiles + size_t(stage) * stageStride);
-                            const uint64_t descA = smemDesc(sa), descB = smemDesc(sa + aBytes);
+                            const uint64_t descA = (LAYOUT & 1) ? smemDescMn(sa) : smemDesc(sa);
+                            const uint64_t descB = (LAYOUT & 2) ? smemDescMn(sa + aBytes) : smemDesc(sa + aBytes);
+                            // a 16-wide K step: 32 bytes = 2 address units along a K-major row, 16 rows of 128 bytes = 128
+                            // units down an MN-major chunk
+                            constexpr uint64_t stepA = (LAYOUT & 1) ? 128 : 2, stepB = (LAYOUT & 2) ? 128 : 2;
 #pragma unroll
                             for(int k = 0; k < kTileK / 16; k++)
                             {
                                 const uint32_t accumulate = (kb | k) ? 1u : 0u;
-                                // 16 half-precision elements = 32 bytes = 2 descriptor address units
                                 asm volatile("{\n\t.reg .pred p;\n\t"
                                              "setp.ne.b32 p, %4, 0;\n\t"
                                              "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
-                                             "l"(descA + uint64_t(2 * k)), "l"(descB + uint64_t(2 * k)), "r"(idesc),
+                                             "l"(descA + stepA * uint64_t(k)), "l"(descB + stepB * uint64_t(k)), "r"(idesc),
                                              "r"(accumulate)
                                              : "memory");
                             }
@@ -275,10 +310,20 @@ namespace htb
                     tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cN);
                     // this warp's table of column offsets for the tile
                     __syncwarp();
-                    for(int c = lane; c < tileN; c += 32)
-                        cols[c] = rowOffset(c, cN, a.boxN, a.extN, a.sDn, a.nn);
+                    if constexpr(LAYOUT & 2)
+                    {
+                        const TfTile wn = tfTileOf(a.gn, tn);
+                        for(int c = lane; c < tileN; c += 32)
+                            cols[c] = tfRowOffset(a.gn, wn, c);
+                    }
+                    else
+                    {
+                        for(int c = lane; c < tileN; c += 32)
+                            cols[c] = rowOffset(c, cN, a.boxN, a.extN, a.sDn, a.nn);
+                    }
                     __syncwarp();
-                    const int64_t offM = rowOffset(row, cM, a.boxM, a.extM, a.sDm, a.nm);
+                    const int64_t offM = (LAYOUT & 1) ? tfRowOffset(a.gm, tfTileOf(a.gm, tm), row)
+                                                      : rowOffset(row, cM, a.boxM, a.extM, a.sDm, a.nm);
 
                     // one lane waits, the warp follows its verdict
                     int ok = 1;
@@ -306,7 +351,7 @@ namespace htb
                         if(offM < 0)
                             continue;
                         const int64_t first = cols[c0];
-                        const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] >= 0;
+                        const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] == first + 31;
                         if(fullChunk && sizeof(TD) == 4 && ((offM + first) & 3) == 0)
                         {
                             // 32 consecutive floats of this row: eight 128-bit stores
@@ -416,7 +461,8 @@ namespace htb
         }
 
         // KSUB: 64-wide K blocks per pipeline stage (1: six 32 KiB stages, 2: three 64 KiB stages)
-        template <typename TD, int KSUB>
+        // LAYOUT as in the single-CTA kernel: bit 0 = A MN-major, bit 1 = B MN-major
+        template <typename TD, int KSUB, int LAYOUT>
         __global__ void __launch_bounds__(kThreads, 1)
             contraction_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
                                             const __grid_constant__ CUtensorMap mapB, const TD* __restrict__ C,
@@ -487,8 +533,15 @@ namespace htb
                         const int    tm = min(2 * pm + int(rank), a.tilesM - 1);
                         const int    tn = min(2 * pn + int(rank), a.tilesN - 1);
                         int          cA[4] = {0, 0, 0, 0}, cB[4] = {0, 0, 0, 0};
-                        tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cA);
-                        tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB);
+                        TfChunks     qA{}, qB{};
+                        if constexpr(LAYOUT & 1)
+                            qA = tfChunksOf(a.gm, tfTileOf(a.gm, tm));
+                        else
+                            tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cA);
+                        if constexpr(LAYOUT & 2)
+                            qB = tfChunksOf(a.gn, tfTileOf(a.gn, tn));
+                        else
+                            tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB);
                         const int a1 = cA[0], a2 = cA[1], a3 = cA[2], a4 = cA[3];
                         const int b1 = cB[0], b2 = cB[1], b3 = cB[2], b4 = cB[3];
                         for(int it = w.kbBegin; it < w.kbEnd; it++)
@@ -511,8 +564,22 @@ namespace htb
                                 for(int q = 0; q < KSUB; q++)
                                 {
                                     const int k0 = (it * KSUB + q) * kTileK; // beyond K: the box is zero-filled
-                                    tmaLoadPair5(dst + q * kHalfBytes, &mapA, bar, k0, a1, a2, a3, a4);
-                                    tmaLoadPair5(dst + (KSUB + q) * kHalfBytes, &mapB, bar, k0, b1, b2, b3, b4);
+                                    if constexpr(LAYOUT & 1)
+                                    {
+                                        // MN-major map {mode0, K, mode1, mode2, 1}: two [64 k][64 rows] boxes
+                                        tmaLoadPair5(dst + q * kHalfBytes, &mapA, bar, qA.c0[0], k0, qA.i1[0], qA.i2[0], 0);
+                                        tmaLoadPair5(dst + q * kHalfBytes + 8192, &mapA, bar, qA.c0[1], k0, qA.i1[1], qA.i2[1], 0);
+                                    }
+                                    else
+                                        tmaLoadPair5(dst + q * kHalfBytes, &mapA, bar, k0, a1, a2, a3, a4);
+                                    if constexpr(LAYOUT & 2)
+                                    {
+                                        tmaLoadPair5(dst + (KSUB + q) * kHalfBytes, &mapB, bar, qB.c0[0], k0, qB.i1[0], qB.i2[0], 0);
+                                        tmaLoadPair5(dst + (KSUB + q) * kHalfBytes + 8192, &mapB, bar, qB.c0[1], k0, qB.i1[1],
+                                                     qB.i2[1], 0);
+                                    }
+                                    else
+                                        tmaLoadPair5(dst + (KSUB + q) * kHalfBytes, &mapB, bar, k0, b1, b2, b3, b4);
                                 }
                             }
                             if(++stage == uint32_t(a.stages))
@@ -529,7 +596,10 @@ namespace htb
                 // ---------------------------------------------------------------- MMA issuer (leader CTA)
                 if(lane == 0 && leader)
                 {
-                    const uint64_t descBase = smemDesc(tilesAddr);
+                    const uint64_t descBaseA = (LAYOUT & 1) ? smemDescMn(tilesAddr) : smemDesc(tilesAddr);
+                    const uint64_t descBaseB = (LAYOUT & 2) ? smemDescMn(tilesAddr) : smemDesc(tilesAddr);
+                    // a 16-wide K step: 2 address units along a K-major row, 128 down an MN-major chunk
+                    constexpr int  stepA = (LAYOUT & 1) ? 128 : 2, stepB = (LAYOUT & 2) ? 128 : 2;
                     uint32_t       stage = 0, phase = 0;
                     int            local = 0;
                     bool           ok    = true;
@@ -550,20 +620,21 @@ namespace htb
                                 break;
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                             // descriptor address field counts 16-byte units
-                            const uint64_t descA = descBase + uint64_t((stage * kStage) >> 4);
-                            const uint64_t descB = descA + uint64_t((KSUB * kHalfBytes) >> 4);
+                            const uint64_t descA = descBaseA + uint64_t((stage * kStage) >> 4);
+                            const uint64_t descB = descBaseB + uint64_t((stage * kStage + KSUB * kHalfBytes) >> 4);
                             if(!(a.probe & 2))
                             {
 #pragma unroll
                                 for(int k = 0; k < KSUB * (kTileK / 16); k++)
                                 {
-                                    // 16 elements = 32 bytes = 2 units inside a 64-wide block; blocks are 16 KiB apart
-                                    const uint64_t off = uint64_t((k / 4) * (kHalfBytes >> 4) + 2 * (k % 4));
+                                    // 64-wide K blocks are 16 KiB apart
+                                    const uint64_t offA = uint64_t((k / 4) * (kHalfBytes >> 4) + stepA * (k % 4));
+                                    const uint64_t offB = uint64_t((k / 4) * (kHalfBytes >> 4) + stepB * (k % 4));
                                     const uint32_t accumulate = (it != w.kbBegin || k != 0) ? 1u : 0u;
                                     asm volatile("{\n\t.reg .pred p;\n\t"
                                                  "setp.ne.b32 p, %4, 0;\n\t"
                                                  "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
-                                                 "l"(descA + off), "l"(descB + off), "r"(idesc), "r"(accumulate)
+                                                 "l"(descA + offA), "l"(descB + offB), "r"(idesc), "r"(accumulate)
                                                  : "memory");
                                 }
                             }
@@ -608,12 +679,23 @@ namespace htb
                     for(int h = 0; h < 2; h++)
                     {
                         const int tnRaw = 2 * pn + h;
-                        tileCoords(min(tnRaw, a.tilesN - 1), a.tilesPerDimN, a.boxN, a.nn, cN);
-                        for(int c = lane; c < 128; c += 32)
-                            cols[h * 128 + c] = (tnRaw < a.tilesN) ? rowOffset(c, cN, a.boxN, a.extN, a.sDn, a.nn) : -1;
+                        if constexpr(LAYOUT & 2)
+                        {
+                            const TfTile wn = tfTileOf(a.gn, min(tnRaw, a.tilesN - 1));
+                            for(int c = lane; c < 128; c += 32)
+                                cols[h * 128 + c] = (tnRaw < a.tilesN) ? tfRowOffset(a.gn, wn, c) : -1;
+                        }
+                        else
+                        {
+                            tileCoords(min(tnRaw, a.tilesN - 1), a.tilesPerDimN, a.boxN, a.nn, cN);
+                            for(int c = lane; c < 128; c += 32)
+                                cols[h * 128 + c] = (tnRaw < a.tilesN) ? rowOffset(c, cN, a.boxN, a.extN, a.sDn, a.nn) : -1;
+                        }
                     }
                     __syncwarp();
-                    const int64_t offM = dupM ? -1 : rowOffset(row, cM, a.boxM, a.extM, a.sDm, a.nm);
+                    const int64_t offM = dupM ? -1
+                                              : ((LAYOUT & 1) ? tfRowOffset(a.gm, tfTileOf(a.gm, tm), row)
+                                                              : rowOffset(row, cM, a.boxM, a.extM, a.sDm, a.nm));
 
                     int ok = 1;
                     if(lane == 0)
@@ -698,7 +780,7 @@ namespace htb
                         if(offM < 0)
                             continue;
                         const int64_t first     = cols[c0];
-                        const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] >= 0;
+                        const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] == first + 31;
                         if(fullChunk && sizeof(TD) == 4 && ((offM + first) & 3) == 0)
                         {
                             float*       dst = (float*)D + offM + first;
@@ -789,6 +871,28 @@ namespace htb
                    == CUDA_SUCCESS;
         }
 
+        // Tensor map of an MN-major operand: {mode0 (stride 1), K, mode1, mode2, 1}; one box is [64 k][64 rows]
+        bool encodeOperandMn(PFN_encodeTiled encode, CUtensorMap* map, const void* base, bool bf16, const RowGroupView& g,
+                             int64_t K, int64_t sK)
+        {
+            cuuint64_t gdim[5] = {cuuint64_t(g.ext[0]), cuuint64_t(K), 1, 1, 1}, gstr[4] = {cuuint64_t(sK) * 2, 16, 16, 16};
+            cuuint32_t bx[5] = {64, kTileK, 1, 1, 1}, estr[5] = {1, 1, 1, 1, 1};
+            for(int d = 1; d < 3; d++)
+                if(d < g.n && g.ext[d] > 1)
+                {
+                    gdim[1 + d] = cuuint64_t(g.ext[d]);
+                    gstr[d]     = cuuint64_t(g.sOp[d]) * 2;
+                }
+            for(int d = 0; d < 4; d++)
+                if(gstr[d] % 16 != 0 || gstr[d] == 0)
+                    return false;
+            return encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
+                          const_cast<void*>(base), gdim, gstr, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+                   == CUDA_SUCCESS;
+        }
+
         void fillGroupArgs(const ModeDim* dims, int n, const int* box, int* boxOut, int64_t* ext, int64_t* sD,
                            int* tilesPerDim, int& tiles)
         {
@@ -814,24 +918,38 @@ namespace htb
             const bool  bf16 = (p.typeA == CUDA_R_16BF);
             const bool  pair = (p.pair != 0) && getenv("HTB_TC_SINGLE") == nullptr;
             const int*  boxN = pair ? p.boxN128 : p.boxN;
+            const int   layout = (p.aMajor ? 1 : 0) | (p.bMajor ? 2 : 0);
+            const RowGroupView vm = viewOf(p.m, p.nm, p.aMajor ? 0 : -1), vn = viewOf(p.n, p.nn, p.bMajor ? p.nFast : -1);
             CUtensorMap mapA, mapB;
-            if(!encodeOperand(encode, &mapA, A, bf16, p.K, p.m, p.nm, p.boxM)
-               || !encodeOperand(encode, &mapB, B, bf16, p.K, p.n, p.nn, boxN))
+            const bool  okA = p.aMajor ? encodeOperandMn(encode, &mapA, A, bf16, vm, p.K, p.k[0].s0)
+                                       : encodeOperand(encode, &mapA, A, bf16, p.K, p.m, p.nm, p.boxM);
+            const bool  okB = p.bMajor ? encodeOperandMn(encode, &mapB, B, bf16, vn, p.K, p.k[0].s1)
+                                       : encodeOperand(encode, &mapB, B, bf16, p.K, p.n, p.nn, boxN);
+            if(!okA || !okB)
                 return cudaErrorNotSupported;
 
             TcArgs a{};
             a.nm = p.nm;
             a.nn = p.nn;
-            fillGroupArgs(p.m, p.nm, p.boxM, a.boxM, a.extM, a.sDm, a.tilesPerDimM, a.tilesM);
-            fillGroupArgs(p.n, p.nn, boxN, a.boxN, a.extN, a.sDn, a.tilesPerDimN, a.tilesN);
+            const int ones[4] = {1, 1, 1, 1}; // MN-major groups have no boxes
+            fillGroupArgs(p.m, p.nm, p.aMajor ? ones : p.boxM, a.boxM, a.extM, a.sDm, a.tilesPerDimM, a.tilesM);
+            fillGroupArgs(p.n, p.nn, p.bMajor ? ones : boxN, a.boxN, a.extN, a.sDn, a.tilesPerDimN, a.tilesN);
+            // chunked description of MN-major groups (64 half-precision elements per chunk)
+            fillGroup(a.gm, vm, p.aMajor, 128, p.boxM, 6);
+            fillGroup(a.gn, vn, p.bMajor, pair ? 128 : p.tileN, boxN, 6);
+            if(p.aMajor)
+                a.tilesM = a.gm.tiles;
+            if(p.bMajor)
+                a.tilesN = a.gn.tiles;
             a.kBlocks    = int((p.K + kTileK - 1) / kTileK);
             a.tileN      = pair ? 256 : p.tileN;
             a.stages     = pair ? 6 : p.stages;
-            a.stageBytes = uint32_t(p.rowsM + (pair ? p.rowsN128 : p.rowsN)) * kTileK * 2;
+            a.stageBytes = uint32_t((p.aMajor ? 128 : p.rowsM) + (p.bMajor ? (pair ? 128 : p.tileN) : (pair ? p.rowsN128 : p.rowsN)))
+                           * kTileK * 2;
             a.alpha      = alpha;
             a.beta       = beta;
             a.bilinear   = (p.bilinear && C != nullptr) ? 1 : 0;
-            a.nContig    = (p.nn == 1 && p.n[0].s1 == 1 && (uintptr_t(D) & 15) == 0
+            a.nContig    = (((p.bMajor && vn.sD[0] == 1) || (p.nn == 1 && p.n[0].s1 == 1)) && (uintptr_t(D) & 15) == 0
                          && (!a.bilinear || (uintptr_t(C) & 15) == 0))
                                ? 1
                                : 0;
@@ -841,8 +959,9 @@ namespace htb
             if(int64_t(a.tilesM) * a.tilesN > 0x7fffffffll || a.stages > kMaxStages)
                 return cudaErrorInvalidConfiguration;
 
-            // instruction descriptor: fp32 accumulate, A/B format, both K-major, N/8, M/16
+            // instruction descriptor: fp32 accumulate, A/B format, transposed (MN-major) A / B, N/8, M/16
             const uint32_t fmt = bf16 ? 1u : 0u;
+            const uint32_t majors = (p.aMajor ? (1u << 15) : 0u) | (p.bMajor ? (1u << 16) : 0u);
             const int      sms = smCount > 0 ? smCount : 148;
             if(pair)
             {
@@ -850,7 +969,7 @@ namespace htb
                 pa.base   = a;
                 pa.pairsM = (a.tilesM + 1) / 2;
                 pa.pairsN = (a.tilesN + 1) / 2;
-                const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(256 >> 3) << 17)
+                const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | majors | (uint32_t(256 >> 3) << 17)
                                        | (uint32_t(256 >> 4) << 24);
                 // two 64-wide K blocks per stage (three 64 KiB stages) beat one (six 32 KiB stages) by 8 %
                 // on 4096^3: the same bytes are in flight with half as many barrier round trips
@@ -860,7 +979,13 @@ namespace htb
                 a.stages  = 6 / ksub;
                 pa.base   = a;
                 pa.iters  = (a.kBlocks + ksub - 1) / ksub;
-                auto kernel = (ksub == 2) ? contraction_tcgen05_pair_kernel<TD, 2> : contraction_tcgen05_pair_kernel<TD, 1>;
+                using PairKernel = void (*)(const CUtensorMap, const CUtensorMap, const TD*, TD*, TcPairArgs, uint32_t);
+                static const PairKernel kernels[2][4] = {
+                    {contraction_tcgen05_pair_kernel<TD, 1, 0>, contraction_tcgen05_pair_kernel<TD, 1, 1>,
+                     contraction_tcgen05_pair_kernel<TD, 1, 2>, contraction_tcgen05_pair_kernel<TD, 1, 3>},
+                    {contraction_tcgen05_pair_kernel<TD, 2, 0>, contraction_tcgen05_pair_kernel<TD, 2, 1>,
+                     contraction_tcgen05_pair_kernel<TD, 2, 2>, contraction_tcgen05_pair_kernel<TD, 2, 3>}};
+                PairKernel kernel = kernels[ksub - 1][layout];
                 const size_t smem = size_t(6) * 2 * 128 * kTileK * 2 + 1024;
                 cudaError_t  e    = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
                 if(e != cudaSuccess)
@@ -877,7 +1002,7 @@ namespace htb
                 cfg.attrs                = attr;
                 cfg.numAttrs             = 1;
                 // clusters that can be resident at once (GPCs with an odd SM count lose one SM)
-                static int maxClusters = 0;
+                static int maxClusters = 0; // the same for every instantiation: one CTA of 192 threads per SM
                 if(maxClusters == 0)
                 {
                     cfg.gridDim = dim3(unsigned(sms / 2 * 2));
@@ -922,16 +1047,18 @@ namespace htb
                     noteLaunch("contraction_tcgen05_pair");
                 return e;
             }
-            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(p.tileN >> 3) << 17)
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | majors | (uint32_t(p.tileN >> 3) << 17)
                                    | (uint32_t(kTileM >> 4) << 24);
             const size_t smem = size_t(a.stages) * (size_t(kTileM) + p.tileN) * kTileK * 2 + 1024;
-            cudaError_t  e = cudaFuncSetAttribute(contraction_tcgen05_kernel<TD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  int(smem));
+            using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const TD*, TD*, TcArgs, uint32_t);
+            static const Kernel kernels[4] = {contraction_tcgen05_kernel<TD, 0>, contraction_tcgen05_kernel<TD, 1>,
+                                              contraction_tcgen05_kernel<TD, 2>, contraction_tcgen05_kernel<TD, 3>};
+            Kernel      kernel = kernels[layout];
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
             if(e != cudaSuccess)
                 return e;
             const int grid = int(std::min<int64_t>(int64_t(a.tilesM) * a.tilesN, sms));
-            contraction_tcgen05_kernel<TD>
-                <<<grid, kThreads, smem, stream>>>(mapA, mapB, (const TD*)C, (TD*)D, a, idesc);
+            kernel<<<grid, kThreads, smem, stream>>>(mapA, mapB, (const TD*)C, (TD*)D, a, idesc);
             noteLaunch("contraction_tcgen05");
             return cudaGetLastError();
         }

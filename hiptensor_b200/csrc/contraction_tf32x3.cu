@@ -36,6 +36,7 @@
 
 #include "kernels.hpp"
 #include "tcgen05_util.cuh"
+#include "row_groups.cuh"
 
 namespace htb
 {
@@ -59,20 +60,6 @@ namespace htb
             static constexpr uint32_t kTotal        = kStagingSlots * kStagingBytes + kOpSlots * kOpBytes;
         };
 
-        // One row group of the tile: the M side (rows of A and D) or the N side (rows of B, columns of D).
-        struct TfGroup
-        {
-            int     major; // 0: operand K-major, rows gathered by a TMA box over the folded modes
-                           // 1: operand MN-major, rows taken in chunks of 32 along the stride-1 mode 0
-            int     n; // folded modes
-            int     rows; // rows of this group per CTA tile (128, or 64 for a narrow N tile)
-            int     tiles;
-            int     box[4], tilesPerDim[4]; // major 0
-            int     chunks0; // major 1: 32-row chunks along mode 0
-            int64_t restExt; // major 1: product of the extents of modes 1..
-            int64_t ext[4], sD[4];
-        };
-
         struct TfArgs
         {
             TfGroup  gm, gn;
@@ -87,80 +74,6 @@ namespace htb
                             // 8 = producer skips the loads (results invalid)
             int*     status;
         };
-
-        // position of a tile inside its group
-        struct TfTile
-        {
-            int c[4]; // major 0: first coordinate per mode
-            int chunkBase; // major 1: first chunk
-        };
-
-        __device__ __forceinline__ TfTile tfTileOf(const TfGroup& g, int t)
-        {
-            TfTile w;
-            w.chunkBase = t * (g.rows >> 5);
-#pragma unroll
-            for(int d = 0; d < 4; d++)
-            {
-                const int per = (d < g.n) ? g.tilesPerDim[d] : 1;
-                w.c[d]        = (t % per) * ((d < g.n) ? g.box[d] : 1);
-                t /= per;
-            }
-            return w;
-        }
-
-        // row r of a tile -> offset in D along this group, or -1 outside the tensor
-        __device__ __forceinline__ int64_t tfRowOffset(const TfGroup& g, const TfTile& w, int r)
-        {
-            if(g.major == 0)
-            {
-                int64_t off = 0;
-                for(int d = 0; d < g.n; d++)
-                {
-                    const int i = r % g.box[d];
-                    r /= g.box[d];
-                    const int64_t x = int64_t(w.c[d]) + i;
-                    if(x >= g.ext[d])
-                        return -1;
-                    off += x * g.sD[d];
-                }
-                return (r == 0) ? off : -1;
-            }
-            const int     chunk = w.chunkBase + (r >> 5);
-            const int64_t i0    = int64_t(chunk % g.chunks0) * 32 + (r & 31);
-            int64_t       rest  = chunk / g.chunks0;
-            if(i0 >= g.ext[0] || rest >= g.restExt)
-                return -1;
-            int64_t off = i0 * g.sD[0];
-            for(int d = 1; d < g.n; d++)
-            {
-                off += (rest % g.ext[d]) * g.sD[d];
-                rest /= g.ext[d];
-            }
-            return off;
-        }
-
-        // TMA coordinates of a tile's 32-row chunks (MN-major operands), fixed for the whole K loop
-        struct TfChunks
-        {
-            int c0[4], i1[4], i2[4];
-        };
-        __device__ __forceinline__ TfChunks tfChunksOf(const TfGroup& g, const TfTile& w)
-        {
-            TfChunks      q;
-            const int64_t e1 = (g.n > 1) ? g.ext[1] : 1;
-#pragma unroll
-            for(int j = 0; j < 4; j++)
-            {
-                const int     chunk = w.chunkBase + j;
-                const int64_t rest  = chunk / g.chunks0;
-                // beyond the tensor the coordinates fall outside the map and the box is zero-filled
-                q.c0[j] = (chunk % g.chunks0) * 32;
-                q.i1[j] = int(rest % e1);
-                q.i2[j] = int(rest / e1);
-            }
-            return q;
-        }
 
         // TMA loads of one operand's rows of one K block into a staging tile
         //   major 0 map: {K, mode0, mode1, mode2, mode3}         one box
@@ -773,12 +686,6 @@ namespace htb
         }
 
         // ------------------------------------------------------------------ host side
-        struct RowGroupView
-        {
-            int     n;
-            int64_t ext[4], sOp[4], sD[4]; // extent, stride in the operand, stride in D; mode 0 first
-        };
-
         // K-major operand: {K, mode0 .. mode3}, one [rows x 32] box, 128-byte swizzle
         bool encodeKMajor(PFN_encodeTiled encode, CUtensorMap* map, const void* base, int64_t K, const RowGroupView& g,
                           const int* box)
@@ -829,52 +736,6 @@ namespace htb
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
                    == CUDA_SUCCESS;
-        }
-
-        // planner group -> view with the chunked (stride-1) mode first
-        RowGroupView viewOf(const ModeDim* dims, int n, int fast)
-        {
-            RowGroupView v{};
-            int          k = 0;
-            auto         put = [&](int i) {
-                v.ext[k] = dims[i].ext;
-                v.sOp[k] = dims[i].s0;
-                v.sD[k]  = dims[i].s1;
-                k++;
-            };
-            if(fast >= 0)
-                put(fast);
-            for(int i = 0; i < n && k < 4; i++)
-                if(i != fast)
-                    put(i);
-            v.n = k;
-            return v;
-        }
-
-        void fillGroup(TfGroup& g, const RowGroupView& v, int major, int rows, const int* box)
-        {
-            g.major = major;
-            g.n     = v.n;
-            g.rows  = rows;
-            g.tiles = 1;
-            g.restExt = 1;
-            for(int d = 0; d < 4; d++)
-            {
-                g.ext[d]         = d < v.n ? v.ext[d] : 1;
-                g.sD[d]          = d < v.n ? v.sD[d] : 0;
-                g.box[d]         = (major == 0 && d < v.n) ? box[d] : 1;
-                g.tilesPerDim[d] = int((g.ext[d] + g.box[d] - 1) / g.box[d]);
-                if(major == 0)
-                    g.tiles *= g.tilesPerDim[d];
-                else if(d >= 1)
-                    g.restExt *= g.ext[d];
-            }
-            g.chunks0 = int((g.ext[0] + 31) / 32);
-            if(major == 1)
-            {
-                const int64_t chunks = int64_t(g.chunks0) * g.restExt, per = rows / 32;
-                g.tiles              = int((chunks + per - 1) / per);
-            }
         }
 
         template <bool PAIR>
@@ -956,8 +817,8 @@ namespace htb
         if(const char* env = getenv("HTB_TF32_PAIR"))
             pair = p.pair != 0 && atoi(env) != 0;
         TfArgs a{};
-        fillGroup(a.gm, vm, p.aMajor, 128, p.boxM);
-        fillGroup(a.gn, vn, p.bMajor, pair ? 64 : p.tileN, pair ? p.boxN128 : p.boxN);
+        fillGroup(a.gm, vm, p.aMajor, 128, p.boxM, 5);
+        fillGroup(a.gn, vn, p.bMajor, pair ? 64 : p.tileN, pair ? p.boxN128 : p.boxN, 5);
         CUtensorMap mapA, mapB;
         const bool  okA = p.aMajor ? encodeMnMajor(encode, &mapA, A, vm, p.nk, extK, sKa, p.boxK)
                                    : encodeKMajor(encode, &mapA, A, p.K, vm, p.boxM);

@@ -500,14 +500,30 @@ namespace htb
         }
         else if(half)
         {
-            // tcgen05 path: both operands K-major with one folded stride-1 K mode, row
-            // strides that are multiples of 16 bytes, and M/N tiles that a TMA box can gather
-            bool tc = out->aKContig && out->bKContig && (out->K % 8 == 0) && nm <= 4 && nn <= 4
-                      && out->K >= 64;
+            // tcgen05 path. An operand is taken K-major (one folded stride-1 K mode, rows gathered by a TMA box
+            // over the folded modes of its row group) or MN-major (a stride-1 mode in its row group, rows taken in
+            // 64-element chunks of that mode, K one folded mode). All other strides must be multiples of 16 bytes.
+            out->aMajor = out->aKContig ? 0 : ((nk == 1 && gm[0].s0 == 1 && gm[0].ext > 1) ? 1 : -1);
+            out->bMajor = out->bKContig ? 0 : -1;
+            out->nFast  = 0;
+            for(int i = 0; i < nn && out->bMajor < 0 && nk == 1; i++)
+                if(gn[i].s0 == 1 && gn[i].ext > 1)
+                {
+                    out->bMajor = 1;
+                    out->nFast  = i;
+                }
+            bool tc = out->aMajor >= 0 && out->bMajor >= 0 && out->K >= 64 && nm <= (out->aMajor == 1 ? 3 : 4)
+                      && nn <= (out->bMajor == 1 ? 3 : 4);
+            if(tc && (out->aMajor == 0 || out->bMajor == 0))
+                tc = out->K % 8 == 0;
+            if(tc && out->aMajor == 1)
+                tc = gk[0].s0 % 8 == 0 && gk[0].ext < (int64_t(1) << 31);
+            if(tc && out->bMajor == 1)
+                tc = gk[0].s1 % 8 == 0 && gk[0].ext < (int64_t(1) << 31);
             for(int i = 0; i < nm && tc; i++)
-                tc = (gm[i].s0 % 8 == 0 && gm[i].ext < (int64_t(1) << 31));
+                tc = ((gm[i].s0 % 8 == 0 || (out->aMajor == 1 && i == 0)) && gm[i].ext < (int64_t(1) << 31));
             for(int i = 0; i < nn && tc; i++)
-                tc = (gn[i].s0 % 8 == 0 && gn[i].ext < (int64_t(1) << 31));
+                tc = ((gn[i].s0 % 8 == 0 || (out->bMajor == 1 && i == out->nFast)) && gn[i].ext < (int64_t(1) << 31));
             // small problems do not fill the machine with 128-row tiles: leave them to the
             // gathered tiled kernel
             tc = tc && (out->M >= 128 && out->N >= 64);
@@ -515,17 +531,17 @@ namespace htb
             {
                 out->tileM = 128;
                 out->tileK = 64;
-                out->rowsM = boxDecompose(gm, nm, 128, out->boxM);
+                out->rowsM = out->aMajor ? 128 : boxDecompose(gm, nm, 128, out->boxM);
                 out->rowsN = 0;
                 for(int tn = (out->N >= 256 ? 256 : (out->N >= 128 ? 128 : 64)); tn >= 64 && out->rowsN == 0; tn >>= 1)
                 {
                     out->tileN = tn;
-                    out->rowsN = boxDecompose(gn, nn, tn, out->boxN);
+                    out->rowsN = out->bMajor ? tn : boxDecompose(gn, nn, tn, out->boxN);
                 }
                 tc = out->rowsM > 0 && out->rowsN > 0;
                 out->stages = (out->tileN == 256) ? 4 : 6;
                 // large problems: 256 x 256 tiles over CTA pairs
-                out->rowsN128 = boxDecompose(gn, nn, 128, out->boxN128);
+                out->rowsN128 = out->bMajor ? 128 : boxDecompose(gn, nn, 128, out->boxN128);
                 out->pair     = (tc && out->tileN == 256 && out->rowsN128 == 128 && out->rowsM == 128 && out->M >= 512
                              && out->N >= 512)
                                     ? 1
@@ -537,10 +553,16 @@ namespace htb
                 // scratch for the tail split, sized for the largest need over the pair counts the
                 // device may grant (GPCs with an odd SM count lose a pair)
                 int64_t tilesM = 1, tilesN = 1;
-                for(int i = 0; i < nm; i++)
-                    tilesM *= (gm[i].ext + out->boxM[i] - 1) / out->boxM[i];
-                for(int i = 0; i < nn; i++)
-                    tilesN *= (gn[i].ext + out->boxN128[i] - 1) / out->boxN128[i];
+                if(out->aMajor)
+                    tilesM = (((gm[0].ext + 63) / 64) * (out->M / gm[0].ext) + 1) / 2;
+                else
+                    for(int i = 0; i < nm; i++)
+                        tilesM *= (gm[i].ext + out->boxM[i] - 1) / out->boxM[i];
+                if(out->bMajor)
+                    tilesN = (((gn[out->nFast].ext + 63) / 64) * (out->N / gn[out->nFast].ext) + 1) / 2;
+                else
+                    for(int i = 0; i < nn; i++)
+                        tilesN *= (gn[i].ext + out->boxN128[i] - 1) / out->boxN128[i];
                 const int64_t tiles   = ((tilesM + 1) / 2) * ((tilesN + 1) / 2);
                 const int     kBlocks = int((out->K + 63) / 64);
                 const int     maxC    = (smCount > 0 ? smCount : 148) / 2;
@@ -643,6 +665,11 @@ namespace htb
         {
             snprintf(buf, sizeof(buf), " major=%s/%s boxK=[%d %d]", p.aMajor ? "mn" : "k", p.bMajor ? "mn" : "k", p.boxK[0],
                      p.boxK[1]);
+            s += buf;
+        }
+        if(p.kind == CK_TCGEN05)
+        {
+            snprintf(buf, sizeof(buf), " major=%s/%s", p.aMajor ? "mn" : "k", p.bMajor ? "mn" : "k");
             s += buf;
         }
         if(p.kind == CK_TCGEN05 || p.kind == CK_TF32X3)

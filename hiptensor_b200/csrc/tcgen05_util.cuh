@@ -68,6 +68,20 @@ namespace htb
             return d;
         }
 
+        // shared-memory matrix descriptor of an MN-major half-precision operand: the tile is a row of chunks, each
+        // chunk [64 k][64 rows = 128 bytes] with 128-byte swizzle; chunks (leading dimension) 8192 bytes apart,
+        // 8-k groups (stride dimension) 1024 bytes apart. A 16-wide K step advances the start by 2048 bytes.
+        __device__ __forceinline__ uint64_t smemDescMn(uint32_t addr)
+        {
+            uint64_t d = 0;
+            d |= uint64_t((addr & 0x3FFFF) >> 4);
+            d |= uint64_t(8192 >> 4) << 16;
+            d |= uint64_t(1024 >> 4) << 32;
+            d |= uint64_t(1) << 46;
+            d |= uint64_t(2) << 61;
+            return d;
+        }
+
         template <int RANK>
         __device__ __forceinline__ void tmaLoad(uint32_t dst, const CUtensorMap* map, uint32_t bar, const int* c)
         {

@@ -292,3 +292,42 @@ def test_cta_pair_kernel_k_split(env, shape):
     unsplit = to_host(D, orc.F32)
     # the tensor cores' fp32 accumulation is not associative: regrouping K moves results by a few 1e-5
     assert 0 <= rel_error(got, unsplit, orc.F32) < 2e-4
+
+
+# A / B mode orders (last mode fastest) of D[m, n] = A x B for the reference's four layout variants
+# (which of A/B has K or M/N fastest, contraction_solution_instances.cpp:40-106)
+HALF_LAYOUTS = {"kk": ([0, 2], [1, 2]), "mn_mn": ([2, 0], [2, 1]), "k_mn": ([0, 2], [2, 1]), "mn_k": ([2, 0], [1, 2])}
+
+
+@pytest.mark.parametrize("layout", sorted(HALF_LAYOUTS))
+@pytest.mark.parametrize("shape", [(256, 320, 96), (384, 1000, 520), (640, 896, 200), (1024, 512, 72)])
+def test_tensor_core_path_operand_layouts(env, layout, shape):
+    """f16/bf16 operands that are contiguous along M/N instead of K run on the tensor cores as well: rows are
+    taken in 64-element chunks of the stride-1 mode and the shared-memory descriptors are the transposed form.
+    Ragged M, N (1000 = 15.6 chunks) and K tails; single CTAs and CTA pairs."""
+    ht, h = env
+    M, N, K = shape
+    modeA, modeB = HALF_LAYOUTS[layout]
+    for dt, td in ((orc.F16, orc.F32), (orc.BF16, orc.BF16)):
+        got, exp, tdo = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=dt, typeD=td, alpha=1.5,
+                                        beta=0.5, fill="normal")
+        assert ht.last_kernel_name() == ("contraction_tcgen05_pair" if min(M, N) >= 512 else "contraction_tcgen05")
+        assert not np.isnan(orc.to_f64(got, tdo)).any()
+        err = rel_error(got, exp, tdo)
+        assert 0 <= err < (1e-4 if td == orc.F32 else 2 * 2.0 ** -7), (layout, shape, dt, err)
+
+
+@pytest.mark.parametrize("dt", [orc.F16, orc.BF16])
+def test_tensor_core_path_chunked_rows(env, dt):
+    """M/N-major half-precision operands whose row groups hold a ragged stride-1 mode (40, 72: chunks of 64 with a
+    zero-filled rest) and a second mode; D's stride-1 mode on either operand."""
+    ht, h = env
+    m0, m1, n0, n1, k0 = range(5)
+    ext = {m0: 40, m1: 5, n0: 72, n1: 3, k0: 136}
+    for modeD in ([m1, n1, m0, n0], [n1, m1, n0, m0]):
+        got, exp, td = run_contraction(ht, h, ext, [m1, k0, m0], [n1, k0, n0], modeD, typeAB=dt, typeD=orc.F32, alpha=2.0,
+                                       beta=0.25, fill="normal")
+        assert ht.last_kernel_name() == "contraction_tcgen05"
+        assert not np.isnan(got).any()
+        err = rel_error(got, exp, td)
+        assert 0 <= err < 1e-4, (dt, modeD, err)

@@ -122,6 +122,12 @@ def test_contraction_config4(ht):
     d = ht.describe_contraction_plan([e] * 4, s, [0, 1, 4, 5], ht.R_16F, [e] * 4, s, [2, 3, 4, 5], ht.R_16F, [e] * 4, s,
                                      [0, 1, 2, 3], ht.R_32F, False, ht.COMPUTE_32F)
     assert "kind=tcgen05" in d and "M=4096 N=4096 K=4096" in d and "k[4096:1/1]" in d and "swapped=0" in d
+    assert "major=k/k" in d and "pair" in d
+    # the same extents with the first mode fastest: both operands contiguous along M/N, still the tensor-core path
+    s = packed([e] * 4, True)
+    d = ht.describe_contraction_plan([e] * 4, s, [0, 1, 4, 5], ht.R_16F, [e] * 4, s, [2, 3, 4, 5], ht.R_16F, [e] * 4, s,
+                                     [0, 1, 2, 3], ht.R_32F, False, ht.COMPUTE_32F)
+    assert "kind=tcgen05" in d and "major=mn/mn" in d and "swapped=1" in d and "pair" in d
 
 
 def test_contraction_config5(ht):
