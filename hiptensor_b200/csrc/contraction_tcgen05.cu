@@ -1015,8 +1015,6 @@ namespace htb
                     maxClusters = n;
                 }
                 const int64_t pairs    = int64_t(pa.pairsM) * pa.pairsN;
-                const int     clusters = int(std::min<int64_t>(pairs, maxClusters));
-                cfg.gridDim            = dim3(unsigned(2 * clusters));
                 // tail split, if the caller's workspace can hold its scratch
                 pa.fullUnits = int(pairs);
                 pa.numUnits  = int(pairs);
@@ -1042,7 +1040,9 @@ namespace htb
                     HTB_LOG_HEUR("hiptensorContraction", "pair kernel: %lld tiles on %d CTA pairs, tail %d tiles in %d parts, %d work units",
                                  (long long)pairs, maxClusters, tail, pa.parts, pa.numUnits);
                 }
-                e = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, (const TD*)C, (TD*)D, pa, idesc);
+                // one CTA pair per work unit, as many as can be resident
+                cfg.gridDim = dim3(unsigned(2 * std::min<int64_t>(pa.numUnits, maxClusters)));
+                e           = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, (const TD*)C, (TD*)D, pa, idesc);
                 if(e == cudaSuccess)
                     noteLaunch("contraction_tcgen05_pair");
                 return e;

@@ -258,7 +258,7 @@ def test_cta_pair_kernel_gathered_odd_tiles(env, dt):
     assert not np.isnan(got).any()
 
 
-@pytest.mark.parametrize("shape", [(512, 768, 1536), (640, 896, 520), (1024, 2304, 2048)])
+@pytest.mark.parametrize("shape", [(512, 768, 4096), (640, 896, 4104), (512, 512, 8192)])
 def test_cta_pair_kernel_k_split(env, shape):
     """Fewer tiles than half the CTA pairs: the tiles are cut along K, partial sums travel through the workspace. Same inputs without a workspace (no split) must agree closely, and both
     must match the oracle."""
@@ -273,7 +273,9 @@ def test_cta_pair_kernel_k_split(env, shape):
                                    beta=0.5, fill="normal", sample=smp)
     assert ht.last_kernel_name() == "contraction_tcgen05_pair"
     assert not np.isnan(got).any()
-    assert 0 <= rel_error(got, exp, td) < 1e-4
+    # stated tolerance for f16 inputs is 1e-2; over 4096-8192 terms the tensor cores' truncating fp32 accumulation
+    # stays within 5e-4 of the reference's sequential fp32 sum
+    assert 0 <= rel_error(got, exp, td) < 5e-4
     # the same problem planned with no workspace
     from helpers import SEED_CONTRACTION as S, to_device, to_host
 
@@ -290,8 +292,9 @@ def test_cta_pair_kernel_k_split(env, shape):
     plan = h.contraction_plan(cd, find, 0)
     h.contraction(plan, 1.5, A, B, 0.5, C, D)
     unsplit = to_host(D, orc.F32)
-    # the tensor cores' fp32 accumulation is not associative: regrouping K moves results by a few 1e-5
-    assert 0 <= rel_error(got, unsplit, orc.F32) < 2e-4
+    # the tensor cores' fp32 accumulation truncates and is not associative: regrouping 4096-8192 terms moves results
+    # by up to 5e-4 under the metric (the stated tolerance for f16 inputs is 1e-2)
+    assert 0 <= rel_error(got, unsplit, orc.F32) < 1e-3
 
 
 # A / B mode orders (last mode fastest) of D[m, n] = A x B for the reference's four layout variants
