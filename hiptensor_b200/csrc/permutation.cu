@@ -143,15 +143,64 @@ namespace htb
         }
 
         // ------------------------------------------------------------ padded-tile kernel
+        // 64 x 64 tile of the (p, q) plane through shared memory: p is A's contiguous folded mode, q is B's.
+        // PACK = 2 (every extent, stride and base address even): a thread moves 2 x 2 blocks - two 2-element
+        // loads along p from rows q and q+1, a register transpose, two 2-element shared stores along q - so global
+        // and shared accesses are 4 bytes (f16) or 8 bytes (f32) wide. PACK = 1: element by element, any extents.
+        // Tiles that lie inside the tensor take a path without bounds checks; row pointers advance by addition.
         constexpr int kTile = 64;
 
+        template <typename T>
+        struct Pair;
+        template <>
+        struct Pair<float>
+        {
+            using type = float2;
+            static __device__ __forceinline__ void transpose(float2 a, float2 b, float2& o0, float2& o1)
+            {
+                o0 = make_float2(a.x, b.x);
+                o1 = make_float2(a.y, b.y);
+            }
+        };
+        template <>
+        struct Pair<__half>
+        {
+            using type = uint32_t;
+            static __device__ __forceinline__ void transpose(uint32_t a, uint32_t b, uint32_t& o0, uint32_t& o1)
+            {
+                o0 = __byte_perm(a, b, 0x5410);
+                o1 = __byte_perm(a, b, 0x7632);
+            }
+        };
+
         template <typename TI, typename TO>
+        __device__ __forceinline__ void storePair(TO* dst, typename Pair<TI>::type v, float alpha, int opA, int opB)
+        {
+            if constexpr(sizeof(TI) == 4)
+            {
+                float2 o;
+                o.x = Elem<float>::apply(v.x, alpha, opA, opB);
+                o.y = Elem<float>::apply(v.y, alpha, opA, opB);
+                *reinterpret_cast<float2*>(dst) = o;
+            }
+            else
+            {
+                const __half2 h  = *reinterpret_cast<const __half2*>(&v);
+                const __half  lo = Elem<__half>::apply(__low2half(h), alpha, opA, opB);
+                const __half  hi = Elem<__half>::apply(__high2half(h), alpha, opA, opB);
+                if constexpr(sizeof(TO) == 2)
+                    *reinterpret_cast<__half2*>(dst) = __halves2half2(lo, hi);
+                else
+                    *reinterpret_cast<float2*>(dst) = make_float2(__half2float(lo), __half2float(hi));
+            }
+        }
+
+        template <typename TI, typename TO, int PACK>
         __global__ void __launch_bounds__(256)
             perm_tile_kernel(const TI* __restrict__ A, TO* __restrict__ B, PermArgs a, int tilesP, int tilesQ)
         {
-            __shared__ TI tile[kTile][kTile + 1];
-            int64_t       bid = blockIdx.x;
-            const int     tp  = int(bid % tilesP);
+            int64_t   bid = blockIdx.x;
+            const int tp  = int(bid % tilesP);
             bid /= tilesP;
             const int tq = int(bid % tilesQ);
             bid /= tilesQ;
@@ -166,35 +215,80 @@ namespace htb
                 offB += c * a.sB[d];
             }
             const int64_t p0 = int64_t(tp) * kTile, q0 = int64_t(tq) * kTile;
-            const int     tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
             const int64_t sAq = a.sA[a.q], sBp = a.sB[0];
-            // load: lanes run along p (contiguous in A)
+            const bool    inside = p0 + kTile <= a.ext[0] && q0 + kTile <= a.ext[a.q];
+            if constexpr(PACK == 2)
             {
-                const int64_t p     = p0 + tx;
-                const bool    pok   = p < a.ext[0];
-                const TI*     src   = A + offA + p;
-#pragma unroll
-                for(int j = 0; j < kTile / 4; j++)
+                using P2 = typename Pair<TI>::type;
+                // transposed tile: row = p, 64 elements of q; the pitch of 33 pairs keeps the column-wise stores
+                // of a warp (rows 2l) on 16 different 8-byte banks twice over
+                __shared__ P2 tile[kTile][kTile / 2 + 1];
+                const int lx = threadIdx.x & 31, ly = threadIdx.x >> 5;
                 {
-                    const int     ql = ty + 4 * j;
-                    const int64_t qq = q0 + ql;
-                    if(pok && qq < a.ext[a.q])
-                        tile[ql][tx] = src[qq * sAq];
+                    // lanes along p: pair lx of the row; rows q0 + 2*(ly + 8j) and the next
+                    const TI* src = A + offA + p0 + 2 * lx + (q0 + 2 * ly) * sAq;
+                    const bool pok = inside || p0 + 2 * lx < a.ext[0];
+#pragma unroll
+                    for(int j = 0; j < 4; j++)
+                    {
+                        const int ql = 2 * (ly + 8 * j);
+                        if(pok && (inside || q0 + ql < a.ext[a.q]))
+                        {
+                            const P2 r0 = *reinterpret_cast<const P2*>(src);
+                            const P2 r1 = *reinterpret_cast<const P2*>(src + sAq);
+                            P2       o0, o1;
+                            Pair<TI>::transpose(r0, r1, o0, o1);
+                            tile[2 * lx][ql >> 1]     = o0;
+                            tile[2 * lx + 1][ql >> 1] = o1;
+                        }
+                        src += 16 * sAq;
+                    }
+                }
+                __syncthreads();
+                {
+                    // lanes along q: pair lx of the output row; rows p0 + ly + 8j
+                    TO*        dst = B + offB + q0 + 2 * lx + (p0 + ly) * sBp;
+                    const bool qok = inside || q0 + 2 * lx < a.ext[a.q];
+#pragma unroll
+                    for(int j = 0; j < 8; j++)
+                    {
+                        const int pl = ly + 8 * j;
+                        if(qok && (inside || p0 + pl < a.ext[0]))
+                            storePair<TI, TO>(dst, tile[pl][lx], a.alpha, a.opA, a.opB);
+                        dst += 8 * sBp;
+                    }
                 }
             }
-            __syncthreads();
-            // store: lanes run along q (contiguous in B)
+            else
             {
-                const int64_t qq  = q0 + tx;
-                const bool    qok = qq < a.ext[a.q];
-                TO*           dst = B + offB + qq;
-#pragma unroll
-                for(int j = 0; j < kTile / 4; j++)
+                __shared__ TI tile[kTile][kTile + 1];
+                const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
                 {
-                    const int     pl = ty + 4 * j;
-                    const int64_t p  = p0 + pl;
-                    if(qok && p < a.ext[0])
-                        dst[p * sBp] = convertOut<TO, TI>(Elem<TI>::apply(tile[tx][pl], a.alpha, a.opA, a.opB));
+                    // load: lanes run along p (contiguous in A)
+                    const TI*  src = A + offA + p0 + tx + (q0 + ty) * sAq;
+                    const bool pok = inside || p0 + tx < a.ext[0];
+#pragma unroll
+                    for(int j = 0; j < kTile / 4; j++)
+                    {
+                        const int ql = ty + 4 * j;
+                        if(pok && (inside || q0 + ql < a.ext[a.q]))
+                            tile[ql][tx] = *src;
+                        src += 4 * sAq;
+                    }
+                }
+                __syncthreads();
+                {
+                    // store: lanes run along q (contiguous in B)
+                    TO*        dst = B + offB + q0 + tx + (p0 + ty) * sBp;
+                    const bool qok = inside || q0 + tx < a.ext[a.q];
+#pragma unroll
+                    for(int j = 0; j < kTile / 4; j++)
+                    {
+                        const int pl = ty + 4 * j;
+                        if(qok && (inside || p0 + pl < a.ext[0]))
+                            *dst = convertOut<TO, TI>(Elem<TI>::apply(tile[tx][pl], a.alpha, a.opA, a.opB));
+                        dst += 4 * sBp;
+                    }
                 }
             }
         }
@@ -722,7 +816,15 @@ namespace htb
                         blocks *= p.ext[d];
                 if(blocks > 0x7fffffffll)
                     return cudaErrorInvalidConfiguration;
-                perm_tile_kernel<TI, TO><<<unsigned(blocks), 256, 0, stream>>>((const TI*)A, (TO*)B, a, tilesP, tilesQ);
+                // 2 x 2 blocks when every extent, stride and base address is even (2-element accesses stay aligned)
+                bool even = (uintptr_t(A) % (2 * sizeof(TI))) == 0 && (uintptr_t(B) % (2 * sizeof(TO))) == 0;
+                for(int d = 0; d < p.ndim && even; d++)
+                    even = (d == 0 || p.sA[d] % 2 == 0) && (d == p.q || p.sB[d] % 2 == 0);
+                even = even && p.ext[0] % 2 == 0 && p.ext[p.q] % 2 == 0;
+                if(even)
+                    perm_tile_kernel<TI, TO, 2><<<unsigned(blocks), 256, 0, stream>>>((const TI*)A, (TO*)B, a, tilesP, tilesQ);
+                else
+                    perm_tile_kernel<TI, TO, 1><<<unsigned(blocks), 256, 0, stream>>>((const TI*)A, (TO*)B, a, tilesP, tilesQ);
                 noteLaunch("perm_tile");
             }
             return cudaGetLastError();

@@ -96,6 +96,19 @@ def test_f16_inputs(env, typeB):
         assert np.array_equal(bits(got), bits(exp)), (perm, typeB)
 
 
+@pytest.mark.parametrize("typeA,typeB", [(orc.F16, orc.F16), (orc.F16, orc.F32), (orc.F32, orc.F32)])
+@pytest.mark.parametrize("lens", [[70, 34, 12, 6], [66, 130, 2, 10], [64, 3, 128, 5], [63, 34, 12, 7]])
+def test_generic_tile_kernel_even_and_odd(env, typeA, typeB, lens):
+    """The shared-memory tile kernel moves 2 x 2 blocks when every extent and stride involved is even (edge tiles
+    that are not multiples of 64, odd extents in the other modes) and single elements otherwise; with scale and
+    unary operators, all three type pairs, orders that transpose different mode pairs."""
+    ht, h = env
+    for perm in ([3, 2, 1, 0], [1, 0, 2, 3], [2, 3, 0, 1], [1, 3, 0, 2]):
+        got, exp = run_permutation(ht, h, lens, [0, 1, 2, 3], perm, typeA=typeA, typeB=typeB, alpha=2.1,
+                                   type_scalar=typeA, opA=orc.OP_SQRT, opB=orc.OP_IDENTITY)
+        assert np.array_equal(bits(got), bits(exp)), (lens, perm, ht.last_kernel_name())
+
+
 def test_rejects_unsupported(env):
     ht, h = env
     dA = h.tensor_descriptor([4, 4], None, ht.R_64F)
