@@ -80,6 +80,17 @@ namespace htb
                     return acc + v;
                 if(OP == OP_MUL)
                     return acc * v;
+                // MAX / MIN propagate NaN (PropagateNan = true in the reference's host reduction)
+                if constexpr(sizeof(T) == 4)
+                {
+                    // one instruction: the result is NaN when either operand is
+                    float r;
+                    if(OP == OP_MAX)
+                        asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(acc), "f"(v));
+                    else
+                        asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(acc), "f"(v));
+                    return r;
+                }
                 if(OP == OP_MAX)
                     return (v != v || acc < v) ? ((acc != acc) ? acc : v) : acc;
                 return (v != v || acc > v) ? ((acc != acc) ? acc : v) : acc;
@@ -405,6 +416,105 @@ namespace htb
             }
         }
 
+        // ------------------------------------------------------------ column kernel, 16-byte loads
+        // The same decomposition with VEC consecutive kept elements per thread: one 16-byte load per row, four rows
+        // in flight, VEC accumulators. Needs the kept extent, every other stride of A and the base address to be
+        // multiples of VEC elements.
+        template <typename TIn, typename TAcc, int OP, int VEC>
+        __global__ void __launch_bounds__(256)
+            red_colv_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
+                            TAcc alpha, TAcc beta, int tiles0)
+        {
+            using Top = typename Accum<TAcc, OP>::Top;
+            extern __shared__ __align__(16) unsigned char smemDyn[];
+            Top*          smem = (Top*)smemDyn; // [TY][TX][VEC]
+            const int     tx = threadIdx.x, ty = threadIdx.y, TX = blockDim.x, TY = blockDim.y;
+            int64_t       bid  = blockIdx.x;
+            const int64_t i0   = ((bid % tiles0) * TX + tx) * VEC;
+            int64_t       rest = bid / tiles0;
+            const bool    ok   = i0 < a.kext[0];
+            int64_t       offA = i0 * a.ksA[0], offD = i0 * a.ksD[0], o = i0, mul = a.kext[0];
+            for(int d = 1; d < a.nk; d++)
+            {
+                int64_t c = rest % a.kext[d];
+                rest /= a.kext[d];
+                offA += c * a.ksA[d];
+                offD += c * a.ksD[d];
+                o += c * mul;
+                mul *= a.kext[d];
+            }
+            const int64_t L0 = a.rext[0], RO = a.nRed / L0, s0 = a.rsA[0];
+            int64_t       roLo = 0, roHi = RO, iLo = 0, iHi = L0;
+            if(a.split > 1)
+            {
+                const int64_t s = blockIdx.y;
+                if(a.sliceOuter)
+                {
+                    roLo = s * a.sliceLen;
+                    roHi = min(RO, roLo + a.sliceLen);
+                }
+                else
+                {
+                    iLo = s * a.sliceLen;
+                    iHi = min(L0, iLo + a.sliceLen);
+                }
+            }
+            using V = Vec<TIn, VEC>;
+            Accum<TAcc, OP> accum[VEC];
+#pragma unroll
+            for(int e = 0; e < VEC; e++)
+                accum[e].init();
+            if(ok)
+            {
+                for(int64_t ro = roLo; ro < roHi; ro++)
+                {
+                    const TIn* col = A + offA + outerRedOffset(a, ro);
+                    int64_t    i   = iLo + ty;
+                    for(; i + 3 * TY < iHi; i += 4 * TY)
+                    {
+                        const V v0 = *reinterpret_cast<const V*>(col + i * s0);
+                        const V v1 = *reinterpret_cast<const V*>(col + (i + TY) * s0);
+                        const V v2 = *reinterpret_cast<const V*>(col + (i + 2 * TY) * s0);
+                        const V v3 = *reinterpret_cast<const V*>(col + (i + 3 * TY) * s0);
+#pragma unroll
+                        for(int e = 0; e < VEC; e++)
+                            accum[e].add4(widen<TAcc, TIn>(v0.v[e]), widen<TAcc, TIn>(v1.v[e]), widen<TAcc, TIn>(v2.v[e]),
+                                          widen<TAcc, TIn>(v3.v[e]));
+                    }
+                    for(; i < iHi; i += TY)
+                    {
+                        const V v = *reinterpret_cast<const V*>(col + i * s0);
+#pragma unroll
+                        for(int e = 0; e < VEC; e++)
+                            accum[e].add1(widen<TAcc, TIn>(v.v[e]));
+                    }
+                }
+            }
+            Top acc[VEC];
+#pragma unroll
+            for(int e = 0; e < VEC; e++)
+            {
+                acc[e]                             = accum[e].result();
+                smem[(ty * TX + tx) * VEC + e] = acc[e];
+            }
+            __syncthreads();
+            if(ty == 0 && ok)
+            {
+                for(int y = 1; y < TY; y++)
+#pragma unroll
+                    for(int e = 0; e < VEC; e++)
+                        acc[e] = Op<Top, OP>::combine(acc[e], smem[(y * TX + tx) * VEC + e]);
+#pragma unroll
+                for(int e = 0; e < VEC; e++)
+                {
+                    if(a.split > 1)
+                        partial[int64_t(blockIdx.y) * a.nOut + o + e] = TAcc(acc[e]);
+                    else
+                        epilogue<TIn, TAcc>(TAcc(acc[e]), alpha, beta, C, D, offD + e * a.ksD[0]);
+                }
+            }
+        }
+
         // ------------------------------------------------------------ generic kernel
         // G threads per output over the flattened reduced range [lo, hi).
         template <typename TIn, typename TAcc, int OP, int G>
@@ -539,20 +649,48 @@ namespace htb
             }
             else if(p.kind == RED_COL)
             {
-                int tx = 32;
-                while(tx < 128 && tx < p.kext[0])
-                    tx <<= 1;
-                int ty = 256 / tx;
-                while(ty > 1 && ty > L0)
-                    ty >>= 1;
-                const int tiles0 = int((p.kext[0] + tx - 1) / tx);
-                int64_t   blocks = tiles0;
-                for(int d = 1; d < p.nk; d++)
-                    blocks *= p.kext[d];
-                if(blocks > 0x7fffffffll)
-                    return cudaErrorInvalidConfiguration;
-                red_col_kernel<TIn, TAcc, OP>
-                    <<<dim3(unsigned(blocks), gy), dim3(tx, ty), 0, stream>>>(A, C, D, partial, a, alpha, beta, tiles0);
+                // 16-byte loads along the kept mode when it, the other strides and the base address allow
+                constexpr int VEC = 16 / int(sizeof(TIn));
+                bool          vecOk = VEC > 1 && p.ksA[0] == 1 && p.kext[0] % VEC == 0 && (uintptr_t(A) & 15) == 0
+                             && p.kext[0] >= 32 * VEC;
+                for(int d = 1; d < p.nk && vecOk; d++)
+                    vecOk = p.ksA[d] % VEC == 0;
+                for(int d = 0; d < p.nr && vecOk; d++)
+                    vecOk = p.rsA[d] % VEC == 0;
+                if(vecOk)
+                {
+                    const int tx = 32;
+                    int       ty = 8;
+                    while(ty > 1 && ty > L0)
+                        ty >>= 1;
+                    const int tiles0 = int((p.kext[0] / VEC + tx - 1) / tx);
+                    int64_t   blocks = tiles0;
+                    for(int d = 1; d < p.nk; d++)
+                        blocks *= p.kext[d];
+                    if(blocks > 0x7fffffffll)
+                        return cudaErrorInvalidConfiguration;
+                    using Top         = typename Accum<TAcc, OP>::Top;
+                    const size_t smem = size_t(tx) * ty * VEC * sizeof(Top);
+                    red_colv_kernel<TIn, TAcc, OP, VEC>
+                        <<<dim3(unsigned(blocks), gy), dim3(tx, ty), smem, stream>>>(A, C, D, partial, a, alpha, beta, tiles0);
+                }
+                else
+                {
+                    int tx = 32;
+                    while(tx < 128 && tx < p.kext[0])
+                        tx <<= 1;
+                    int ty = 256 / tx;
+                    while(ty > 1 && ty > L0)
+                        ty >>= 1;
+                    const int tiles0 = int((p.kext[0] + tx - 1) / tx);
+                    int64_t   blocks = tiles0;
+                    for(int d = 1; d < p.nk; d++)
+                        blocks *= p.kext[d];
+                    if(blocks > 0x7fffffffll)
+                        return cudaErrorInvalidConfiguration;
+                    red_col_kernel<TIn, TAcc, OP>
+                        <<<dim3(unsigned(blocks), gy), dim3(tx, ty), 0, stream>>>(A, C, D, partial, a, alpha, beta, tiles0);
+                }
                 noteLaunch("red_col");
             }
             else
