@@ -179,3 +179,24 @@ def test_config3_full_size(env, first_fastest):
             orc.reduction(1.0, A.astype(np.float64), lens, sA, modeA, orc.F64, 0.5, C.astype(np.float64), exact,
                           lens[:2], sD, kept, orc.F64, op, orc.COMPUTE_64F)
             check_f32(got, exp, exact, 2048)
+
+
+@pytest.mark.parametrize("rank", [1, 2, 3, 5, 6])
+def test_other_ranks(env, rank):
+    """Ranks 1 to 6 (reference: test/03_reduction/configs/validation/rank{1..6}_test_params.yaml): the full
+    reduction, each single kept mode, and a split in the middle, both memory orders."""
+    ht, h = env
+    lens = [7, 4, 6, 3, 5, 2][:rank]
+    modeA = list(range(rank))
+    keeps = [[]] + [[m] for m in modeA] + ([modeA[: rank // 2]] if rank > 1 else []) + ([modeA[rank // 2:]] if rank > 1 else [])
+    for kept in keeps:
+        if len(kept) == rank:
+            continue
+        for first in (False, True):
+            sA = orc.packed_strides(lens, first)
+            lensD = [lens[m] for m in kept]
+            sD = orc.packed_strides(lensD, first)
+            got, exp, exact = run_reduction(ht, h, lens, modeA, kept, op=orc.OP_ADD, alpha=1.5, beta=0.0, stridesA=sA,
+                                            stridesD=sD, want_exact=True)
+            reduce_len = int(np.prod(lens)) // max(int(np.prod(lensD)), 1)
+            check_f32(got, exp, exact, reduce_len)
