@@ -431,15 +431,22 @@ namespace htb
             int    fullUnits, numUnits, parts;
             float* slots; // [tail tile][part-1][256 rows][256 columns] fp32
             int*   flags; // one counter per tail tile, zeroed before the launch
+            // Half tiles. With several waves of tiles, the tiles of a last wave that fills at most half of the
+            // CTA pairs are cut into two 256 x 128 halves along N, one unit each (halves = 1): the last wave then
+            // takes half as long. A half unit loads 64 rows of B per CTA and issues MMAs with N = 128.
+            int      halves;
+            uint32_t idescHalf;
         };
 
         struct TcUnit
         {
             int tile, kbBegin, kbEnd, part, tail; // stage range [kbBegin, kbEnd); tail: index of the split tile or -1
+            int half; // -1: whole tile; 0 / 1: N half of the tile
         };
         __device__ __forceinline__ TcUnit unitOf(const TcPairArgs& pa, int u)
         {
             TcUnit w;
+            w.half = -1;
             if(u < pa.fullUnits)
             {
                 w.tile    = u;
@@ -447,6 +454,16 @@ namespace htb
                 w.kbEnd   = pa.iters;
                 w.part    = 0;
                 w.tail    = -1;
+            }
+            else if(pa.halves)
+            {
+                const int x = u - pa.fullUnits;
+                w.tile      = pa.fullUnits + (x >> 1);
+                w.half      = x & 1;
+                w.kbBegin   = 0;
+                w.kbEnd     = pa.iters;
+                w.part      = 0;
+                w.tail      = -1;
             }
             else
             {
@@ -465,7 +482,8 @@ namespace htb
         template <typename TD, int KSUB, int LAYOUT>
         __global__ void __launch_bounds__(kThreads, 1)
             contraction_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
-                                            const __grid_constant__ CUtensorMap mapB, const TD* __restrict__ C,
+                                            const __grid_constant__ CUtensorMap mapB,
+                                            const __grid_constant__ CUtensorMap mapB64, const TD* __restrict__ C,
                                             TD* __restrict__ D, TcPairArgs pa, uint32_t idesc)
         {
             const TcArgs& a = pa.base;
@@ -523,7 +541,7 @@ namespace htb
                 if(lane == 0)
                 {
                     const uint32_t leaderFull = mapToRank(fullAddr, 0);
-                    const uint32_t txBytes    = 2 * KSUB * a.stageBytes; // both CTAs' boxes of one stage
+                    const uint32_t txWhole    = 2 * KSUB * a.stageBytes; // both CTAs' boxes of one stage
                     uint32_t       stage = 0, phase = 0;
                     bool           ok = true;
                     for(int u = clusterId; u < pa.numUnits && ok; u += numClusters)
@@ -531,7 +549,12 @@ namespace htb
                         const TcUnit w  = unitOf(pa, u);
                         const int    pm = w.tile % pa.pairsM, pn = w.tile / pa.pairsM;
                         const int    tm = min(2 * pm + int(rank), a.tilesM - 1);
-                        const int    tn = min(2 * pn + int(rank), a.tilesN - 1);
+                        // B rows of this CTA: 128-row sub-tile `rank` of the tile, or 64-row piece `rank` of sub-tile
+                        // `half` (K-major: second tensor map with 64-row boxes; MN-major: one chunk instead of two)
+                        const bool   isHalf = w.half >= 0;
+                        const int    tn = isHalf ? 2 * pn + w.half : min(2 * pn + int(rank), a.tilesN - 1);
+                        const CUtensorMap* mb = isHalf ? &mapB64 : &mapB;
+                        const uint32_t txBytes = isHalf ? txWhole - 2 * KSUB * 8192 : txWhole;
                         int          cA[4] = {0, 0, 0, 0}, cB[4] = {0, 0, 0, 0};
                         TfChunks     qA{}, qB{};
                         if constexpr(LAYOUT & 1)
@@ -542,6 +565,13 @@ namespace htb
                             qB = tfChunksOf(a.gn, tfTileOf(a.gn, tn));
                         else
                             tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB);
+                        if(isHalf)
+                        {
+                            cB[0] += int(rank) * 64;
+                            qB.c0[0] = qB.c0[rank];
+                            qB.i1[0] = qB.i1[rank];
+                            qB.i2[0] = qB.i2[rank];
+                        }
                         const int a1 = cA[0], a2 = cA[1], a3 = cA[2], a4 = cA[3];
                         const int b1 = cB[0], b2 = cB[1], b3 = cB[2], b4 = cB[3];
                         for(int it = w.kbBegin; it < w.kbEnd; it++)
@@ -575,11 +605,12 @@ namespace htb
                                     if constexpr(LAYOUT & 2)
                                     {
                                         tmaLoadPair5(dst + (KSUB + q) * kHalfBytes, &mapB, bar, qB.c0[0], k0, qB.i1[0], qB.i2[0], 0);
-                                        tmaLoadPair5(dst + (KSUB + q) * kHalfBytes + 8192, &mapB, bar, qB.c0[1], k0, qB.i1[1],
-                                                     qB.i2[1], 0);
+                                        if(!isHalf)
+                                            tmaLoadPair5(dst + (KSUB + q) * kHalfBytes + 8192, &mapB, bar, qB.c0[1], k0, qB.i1[1],
+                                                         qB.i2[1], 0);
                                     }
                                     else
-                                        tmaLoadPair5(dst + (KSUB + q) * kHalfBytes, &mapB, bar, k0, b1, b2, b3, b4);
+                                        tmaLoadPair5(dst + (KSUB + q) * kHalfBytes, mb, bar, k0, b1, b2, b3, b4);
                                 }
                             }
                             if(++stage == uint32_t(a.stages))
@@ -613,6 +644,7 @@ namespace htb
                             break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint32_t dTmem = tmem + uint32_t(acc * 256);
+                        const uint32_t idescU = (w.half >= 0) ? pa.idescHalf : idesc; // N = 128 for a half tile
                         for(int it = w.kbBegin; it < w.kbEnd; it++)
                         {
                             ok = mbarWaitTight(fullAddr + 8 * stage, phase, abortP);
@@ -634,7 +666,7 @@ namespace htb
                                     asm volatile("{\n\t.reg .pred p;\n\t"
                                                  "setp.ne.b32 p, %4, 0;\n\t"
                                                  "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
-                                                 "l"(descA + offA), "l"(descB + offB), "r"(idesc), "r"(accumulate)
+                                                 "l"(descA + offA), "l"(descB + offB), "r"(idescU), "r"(accumulate)
                                                  : "memory");
                                 }
                             }
@@ -676,9 +708,10 @@ namespace htb
                     int            cM[4], cN[4];
                     tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cM);
                     __syncwarp();
-                    for(int h = 0; h < 2; h++)
+                    const int ncols = (w.half >= 0) ? 128 : 256; // a half tile: the 128 columns of sub-tile `half`
+                    for(int h = 0; h < (ncols >> 7); h++)
                     {
-                        const int tnRaw = 2 * pn + h;
+                        const int tnRaw = 2 * pn + ((w.half >= 0) ? w.half : h);
                         if constexpr(LAYOUT & 2)
                         {
                             const TfTile wn = tfTileOf(a.gn, min(tnRaw, a.tilesN - 1));
@@ -737,7 +770,7 @@ namespace htb
                                 break;
                         }
                     }
-                    for(int c0 = 0; c0 < 256; c0 += 32)
+                    for(int c0 = 0; c0 < ncols; c0 += 32)
                     {
                         uint32_t v[32];
                         asm volatile(
@@ -979,7 +1012,8 @@ namespace htb
                 a.stages  = 6 / ksub;
                 pa.base   = a;
                 pa.iters  = (a.kBlocks + ksub - 1) / ksub;
-                using PairKernel = void (*)(const CUtensorMap, const CUtensorMap, const TD*, TD*, TcPairArgs, uint32_t);
+                using PairKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const TD*, TD*, TcPairArgs,
+                                            uint32_t);
                 static const PairKernel kernels[2][4] = {
                     {contraction_tcgen05_pair_kernel<TD, 1, 0>, contraction_tcgen05_pair_kernel<TD, 1, 1>,
                      contraction_tcgen05_pair_kernel<TD, 1, 2>, contraction_tcgen05_pair_kernel<TD, 1, 3>},
@@ -1040,9 +1074,32 @@ namespace htb
                     HTB_LOG_HEUR("hiptensorContraction", "pair kernel: %lld tiles on %d CTA pairs, tail %d tiles in %d parts, %d work units",
                                  (long long)pairs, maxClusters, tail, pa.parts, pa.numUnits);
                 }
+                // Half tiles: several waves, the last at most half full. K-major B needs its 128-row sub-tile to be one
+                // box along the first N mode, so that rows 64.. are a coordinate offset; the N tiles must pair up evenly.
+                CUtensorMap mapB64 = mapB;
+                if(pa.parts == 1 && pairs > maxClusters && getenv("HTB_TC_NOHALF") == nullptr && a.tilesN % 2 == 0)
+                {
+                    const int64_t tail   = pairs % maxClusters;
+                    bool          halfOk = tail > 0 && 2 * tail <= maxClusters;
+                    if(halfOk && !p.bMajor)
+                    {
+                        const int box64[4] = {64, 1, 1, 1};
+                        halfOk = p.boxN128[0] == 128 && encodeOperand(encode, &mapB64, B, bf16, p.K, p.n, p.nn, box64);
+                    }
+                    if(halfOk)
+                    {
+                        pa.halves    = 1;
+                        pa.fullUnits = int(pairs - tail);
+                        pa.numUnits  = int(pairs + tail);
+                        pa.idescHalf = (1u << 4) | (fmt << 7) | (fmt << 10) | majors | (uint32_t(128 >> 3) << 17)
+                                       | (uint32_t(256 >> 4) << 24);
+                        HTB_LOG_HEUR("hiptensorContraction", "pair kernel: last wave of %lld tiles cut into %lld half tiles",
+                                     (long long)tail, (long long)(2 * tail));
+                    }
+                }
                 // one CTA pair per work unit, as many as can be resident
                 cfg.gridDim = dim3(unsigned(2 * std::min<int64_t>(pa.numUnits, maxClusters)));
-                e           = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, (const TD*)C, (TD*)D, pa, idesc);
+                e           = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, mapB64, (const TD*)C, (TD*)D, pa, idesc);
                 if(e == cudaSuccess)
                     noteLaunch("contraction_tcgen05_pair");
                 return e;

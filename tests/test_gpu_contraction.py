@@ -6,6 +6,8 @@ next to them the reference's own bound 2*K*eps (+2*2^-10 f16, +2*2^-7 bf16 outpu
 test/01_contraction/contraction_test.cpp:882-905, is checked where it is the stricter one.
 Mode lists and extents of the shuffled cases are those of
 test/01_contraction/configs/mode_test_params.yaml:15-59."""
+import os
+
 import numpy as np
 import pytest
 
@@ -334,3 +336,28 @@ def test_tensor_core_path_chunked_rows(env, dt):
         assert not np.isnan(got).any()
         err = rel_error(got, exp, td)
         assert 0 <= err < 1e-4, (dt, modeD, err)
+
+
+@pytest.mark.parametrize("layout", sorted(HALF_LAYOUTS))
+def test_cta_pair_kernel_half_tiles_in_last_wave(env, layout):
+    """More tiles than CTA pairs with a last wave that is at most half full (80 tiles on 74 pairs): its tiles are
+    cut into 256 x 128 halves. Checked on sampled outputs and, against the same problem with the cut disabled,
+    bit for bit (each output is accumulated in the same order either way)."""
+    import torch
+
+    ht, h = env
+    M, N, K = 2560, 2048, 136
+    modeA, modeB = HALF_LAYOUTS[layout]
+    smp = np.random.default_rng(5).integers(0, M * N, 8192)
+    got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F16, typeD=orc.F32,
+                                   alpha=1.5, beta=0.5, fill="normal", sample=smp)
+    assert ht.last_kernel_name() == "contraction_tcgen05_pair"
+    assert not np.isnan(got).any()
+    assert 0 <= rel_error(got, exp, td) < 1e-4
+    os.environ["HTB_TC_NOHALF"] = "1"
+    try:
+        whole, _, _ = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F16, typeD=orc.F32,
+                                      alpha=1.5, beta=0.5, fill="normal", sample=smp[:1])
+    finally:
+        del os.environ["HTB_TC_NOHALF"]
+    assert np.array_equal(got.view(np.uint32), whole.view(np.uint32))
