@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the three hot paths on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5|c4f32] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5|c4f32|c2f16|c3col] [--impl reference]
 
 One step = one pass of the hot path over one batch of seeded synthetic input, called through the
 library's C ABI. The default workload is BASELINE configs[1] (c2): the fp32 rank-4 permutation
@@ -36,8 +36,8 @@ NOMINAL_FP64_TFLOPS = 40.0  # FP64 tensor pipe, nominal: no measured figure exis
 
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the
 # ncu captures summarised under profiles/, full-size workloads, one launch each).
-NCU_TRAFFIC_BYTES = {"c2": 2113114000, "c3": 2153492640, "c4": 108542464, "c1": 4097024, "c5": 351778816,
-                     "c4f32": 636672256}
+NCU_TRAFFIC_BYTES = {"c2": 2113114000, "c3": 2153492640, "c4": 112387840, "c1": 4097024, "c5": 351778816,
+                     "c4f32": 636672256, "c2f16": 1030652672, "c3col": 2155740184}
 
 
 def peaks():
@@ -192,6 +192,49 @@ class PermutationC2(Workload):
         return 2 * n * 4 / dt / 1e9, "oracle permutation of the slab extents [128,128,128,64] (512 MiB in + 512 MiB out)"
 
 
+class PermutationC2F16(PermutationC2):
+    """Not a BASELINE config: config 2 with f16 elements (the generic shared-memory tile kernel)."""
+    name, dtype = "c2f16", "f16"
+
+    def setup(self):
+        import torch
+        ht = self.ht
+        e = self.E
+        n = e ** 4
+        self.A_host = _fill(n, 2, 256 + self.rank).pin_memory()
+        self.A = self.A_host.cuda(non_blocking=True)
+        self.B = torch.empty(n, dtype=torch.float16, device="cuda")
+        self.B_host = torch.empty(n, dtype=torch.float16).pin_memory()
+        self.desc = self.h.tensor_descriptor([e] * 4, None, ht.R_16F)
+        self.bytes = 2 * n * 2
+
+    def step(self, stream):
+        self.h.permutation(1.0, self.A, self.desc, [0, 1, 2, 3], self.B, self.desc, [3, 2, 1, 0], self.ht.R_16F, stream)
+
+    def e2e_step(self, stream):
+        self.A.copy_(self.A_host, non_blocking=True)
+        self.step(stream)
+        self.B_host.copy_(self.B, non_blocking=True)
+        return self.A_host.numel() * 2, self.B_host.numel() * 2
+
+    def config(self):
+        return {"workload": "c2f16: f16 permutation B[d,c,b,a]=A[a,b,c,d], extents 128, 512 MiB in + 512 MiB out per GPU",
+                "parallelism": "mode d sharded, one slab of 128 per GPU, no collective",
+                "cache": "inputs (512 MiB) larger than L2 (126 MB), no flush needed", "alpha": 1.0}
+
+    def cpu_sample(self, nthreads):
+        import numpy as np
+        from oracle import binding as orc
+        lens = [self.E, self.E, self.E, 64]
+        n = int(np.prod(lens))
+        A = orc.fill_uniform(n, orc.F16, 256)
+        B = np.empty(n, dtype=np.float16)
+        t0 = time.perf_counter()
+        orc.permutation(1.0, orc.F16, A, lens, [0, 1, 2, 3], orc.F16, B, [3, 2, 1, 0], orc.F16, nthreads=nthreads)
+        dt = time.perf_counter() - t0
+        return 2 * n * 2 / dt / 1e9, "oracle permutation of the slab extents [128,128,128,64] (256 MiB in + 256 MiB out)"
+
+
 class ReductionC3(Workload):
     name, metric, unit, dtype, bound = "c3", "reduction_hbm_gbs", "GB/s", "f32", "hbm"
     LENS = [4096, 64, 64, 32]
@@ -247,6 +290,39 @@ class ReductionC3(Workload):
                       packed(lens[:2], False), [0, 1], orc.F32, orc.OP_ADD, orc.COMPUTE_32F, nthreads=nthreads)
         dt = time.perf_counter() - t0
         return (n * 4 + 2 * D.size * 4) / dt / 1e9, "oracle reduction of the slab m=512 (256 MiB in)"
+
+
+class ReductionC3Col(ReductionC3):
+    """Not a separate BASELINE config: config 3 with explicit first-mode-fastest strides (m contiguous), the
+    strided "column" reduction."""
+    name = "c3col"
+
+    def setup(self, op=None):
+        super().setup(op)
+        ht = self.ht
+        lens = self.LENS
+        self.dA = self.h.tensor_descriptor(lens, packed(lens, True), ht.R_32F)
+        self.dD = self.h.tensor_descriptor(lens[:2], packed(lens[:2], True), ht.R_32F)
+
+    def config(self):
+        c = super().config()
+        c["workload"] = ("c3col: fp32 reduction A[4096,64,64,32] over {k,h} -> D[4096,64] = 1.0*sum + 0.5*C (ADD), "
+                         "first mode fastest (m contiguous, reduced elements 1 MiB apart), 2 GiB in per GPU")
+        return c
+
+    def cpu_sample(self, nthreads):
+        import numpy as np
+        from oracle import binding as orc
+        lens = [512, 64, 64, 32]
+        n = int(np.prod(lens))
+        A = orc.fill_uniform(n, orc.F32, 17)
+        C = orc.fill_uniform(lens[0] * lens[1], orc.F32, 19)
+        D = np.zeros(lens[0] * lens[1], dtype=np.float32)
+        t0 = time.perf_counter()
+        orc.reduction(1.0, A, lens, packed(lens, True), [0, 1, 2, 3], orc.F32, 0.5, C, D, lens[:2],
+                      packed(lens[:2], True), [0, 1], orc.F32, orc.OP_ADD, orc.COMPUTE_32F, nthreads=nthreads)
+        dt = time.perf_counter() - t0
+        return (n * 4 + 2 * D.size * 4) / dt / 1e9, "oracle reduction of the slab m=512 (256 MiB in), first mode fastest"
 
 
 class ContractionBase(Workload):
@@ -436,7 +512,7 @@ class ContractionC5(ContractionBase):
 
 
 WORKLOADS = {"c1": ContractionC1, "c2": PermutationC2, "c3": ReductionC3, "c4": ContractionC4, "c5": ContractionC5,
-             "c4f32": ContractionC4F32}
+             "c4f32": ContractionC4F32, "c2f16": PermutationC2F16, "c3col": ReductionC3Col}
 
 
 # --------------------------------------------------------------------------------------------- timing
