@@ -6,6 +6,10 @@
 // accumulate  small_a*big_b + big_a*small_b + big_a*big_b  in fp32 in tensor memory. The dropped
 // small*small term is below 2^-22 of the product, i.e. below fp32 rounding of the sum.
 //
+// With compute type f16 or bf16 (fp32 data whose elements the reference first converts to the compute type,
+// contraction_cpu_reference_impl.hpp:359-384) the converter rounds each element to that type instead: the result
+// is exactly representable in TF32, so one MMA per K step multiplies exactly what the reference multiplies.
+//
 // kind::tf32 takes K-major shared-memory operands only, so the split doubles as the layout change:
 //   TMA            strided tensor -> staging tile, in whichever order the operand is contiguous:
 //                    K-major operand  : one box  [rows x 32 k], 128-byte swizzle, rows gathered over the
@@ -29,6 +33,8 @@
 // It stands where the reference instantiates CK's xdl contraction kernels for f32
 // (library/src/contraction/device/*f32_f32_f32_f32*_instance.cpp, compute type f32).
 #include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -70,6 +76,7 @@ namespace htb
             int      bilinear;
             int      nContig; // 32 consecutive columns of a tile are 32 consecutive, 16-byte aligned floats of D
             int      pairsM, pairsN; // PAIR only
+            int      round; // 0: big/small split (compute f32); 1 / 2: elements rounded to f16 / bf16, one MMA per K step
             int      probe; // measurement aid, bit mask: 1 = converter skips its work, 2 = issuer skips the MMAs,
                             // 8 = producer skips the loads (results invalid)
             int*     status;
@@ -103,6 +110,19 @@ namespace htb
         __device__ __forceinline__ float tfBig(float x)
         {
             return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+        }
+        // elements rounded to f16 (ROUND 1) or bf16 (ROUND 2) and widened again; no small part
+        template <int ROUND>
+        __device__ __forceinline__ float tfRound(float x)
+        {
+            if(ROUND == 1)
+                return __half2float(__float2half_rn(x));
+            return __bfloat162float(__float2bfloat16_rn(x));
+        }
+        template <int ROUND>
+        __device__ __forceinline__ float4 tfRound4(const float4& v)
+        {
+            return make_float4(tfRound<ROUND>(v.x), tfRound<ROUND>(v.y), tfRound<ROUND>(v.z), tfRound<ROUND>(v.w));
         }
         __device__ __forceinline__ void tfSplit4(const float4& v, float4& b, float4& s)
         {
@@ -144,7 +164,9 @@ namespace htb
         // Conversion of a rows x 32 tile by the 256 converter threads (thread: row r = 0..127, K half h):
         // staging -> (big, small) in the K-major ring layout, where the 16-byte piece j of row r sits at
         // r*128 + ((j ^ (r & 7)) << 4).
-        __device__ __forceinline__ void tfConvertRow(int major, uint32_t src, uint32_t dstBig, uint32_t dstSmall, int r, int h, int rows)
+        // round: 0 = big/small split, 1 = round to f16, 2 = round to bf16 (big tile only)
+        __device__ __forceinline__ void tfConvertRow(int major, uint32_t src, uint32_t dstBig, uint32_t dstSmall, int r, int h, int rows,
+                                                     int round)
         {
             const uint32_t rowOff = uint32_t(r) * 128;
             if(major == 0)
@@ -160,10 +182,15 @@ namespace htb
                         break;
                     const uint32_t off = uint32_t(pass * 32 + (t >> 3)) * 128 + (uint32_t(t & 7) << 4);
                     const float4   v   = lds128(src + off);
-                    float4         b, s;
-                    tfSplit4(v, b, s);
-                    sts128(dstBig + off, b);
-                    sts128(dstSmall + off, s);
+                    if(round == 0)
+                    {
+                        float4 b, s;
+                        tfSplit4(v, b, s);
+                        sts128(dstBig + off, b);
+                        sts128(dstSmall + off, s);
+                    }
+                    else
+                        sts128(dstBig + off, round == 1 ? tfRound4<1>(v) : tfRound4<2>(v));
                 }
             }
             else if(r < rows)
@@ -178,10 +205,16 @@ namespace htb
                 for(int jj = 0; jj < 4; jj++)
                 {
                     const uint32_t off = rowOff + (uint32_t((4 * h + jj) ^ (r & 7)) << 4);
-                    float4         b, s;
-                    tfSplit4(make_float4(x[4 * jj], x[4 * jj + 1], x[4 * jj + 2], x[4 * jj + 3]), b, s);
-                    sts128(dstBig + off, b);
-                    sts128(dstSmall + off, s);
+                    const float4   v   = make_float4(x[4 * jj], x[4 * jj + 1], x[4 * jj + 2], x[4 * jj + 3]);
+                    if(round == 0)
+                    {
+                        float4 b, s;
+                        tfSplit4(v, b, s);
+                        sts128(dstBig + off, b);
+                        sts128(dstSmall + off, s);
+                    }
+                    else
+                        sts128(dstBig + off, round == 1 ? tfRound4<1>(v) : tfRound4<2>(v));
                 }
             }
         }
@@ -452,8 +485,11 @@ namespace htb
                                     for(int k = 0; k < kTfK / 8; k++)
                                     {
                                         mma(dMain, descOf(aBig), descOf(bBig), (!segStart || k) ? 1u : 0u);
-                                        mma(dCorr, descOf(aSml), descOf(bBig), (kb | k) ? 1u : 0u);
-                                        mma(dCorr, descOf(aBig), descOf(bSml), 1u);
+                                        if(a.round == 0)
+                                        {
+                                            mma(dCorr, descOf(aSml), descOf(bBig), (kb | k) ? 1u : 0u);
+                                            mma(dCorr, descOf(aBig), descOf(bSml), 1u);
+                                        }
                                         aBig += 2;
                                         aSml += 2;
                                         bBig += 2;
@@ -569,7 +605,14 @@ namespace htb
                         for(int c0 = 0; c0 < 64; c0 += 32)
                         {
                             uint32_t v[32];
-                            loadChunk(lanes + 256u + uint32_t(cb) * 128u + uint32_t(c0), v);
+                            if(a.round == 0)
+                                loadChunk(lanes + 256u + uint32_t(cb) * 128u + uint32_t(c0), v);
+                            else
+                            {
+#pragma unroll
+                                for(int j = 0; j < 32; j++)
+                                    v[j] = 0u; // no correction products
+                            }
                             if(offM < 0)
                                 continue;
                             const int64_t first     = cols[c0];
@@ -642,9 +685,9 @@ namespace htb
                         const uint32_t op = opAddr + oSlot * kOpBytes;
                         if(!(a.probe & 1))
                         {
-                            tfConvertRow(a.gm.major, st, op, op + kTileBytes, r, kh, 128);
+                            tfConvertRow(a.gm.major, st, op, op + kTileBytes, r, kh, 128, a.round);
                             tfConvertRow(a.gn.major, st + kTileBytes, op + 2 * kTileBytes, op + 2 * kTileBytes + kBBytes, r, kh,
-                                         a.gn.rows);
+                                         a.gn.rows, a.round);
                         }
                         // the ring is read by the tensor cores (async proxy): order this thread's stores before it
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -840,6 +883,7 @@ namespace htb
         a.pairsM   = (a.gm.tiles + 1) / 2;
         a.pairsN   = (a.gn.tiles + 1) / 2;
         a.status   = deviceStatus;
+        a.round    = (p.computeType == HIPTENSOR_COMPUTE_16F) ? 1 : (p.computeType == HIPTENSOR_COMPUTE_16BF ? 2 : 0);
         if(const char* env = getenv("HTB_TF32_PROBE"))
             a.probe = atoi(env);
         if(int64_t(a.gm.tiles) * a.gn.tiles > 0x7fffffffll)

@@ -578,9 +578,10 @@ namespace htb
                 }
             }
         }
-        else if(tA == CUDA_R_32F && computeType == 4)
+        else if(tA == CUDA_R_32F && (computeType == 4 || computeType == 1 || computeType == 1024))
         {
-            // fp32 on the tensor cores. An operand is taken K-major (one stride-1 K mode) or MN-major (a
+            // fp32 data on the tensor cores (compute f32: TF32 big/small split; compute f16 / bf16: elements
+            // rounded to that type, one MMA). An operand is taken K-major (one stride-1 K mode) or MN-major (a
             // stride-1 mode in its row group); all other strides must be multiples of 16 bytes for TMA.
             bool tf = out->K >= 32 && out->M >= 128 && out->N >= 64 && nk <= 2;
             out->aMajor = out->aKContig ? 0 : ((gm[0].s0 == 1 && gm[0].ext > 1) ? 1 : -1);

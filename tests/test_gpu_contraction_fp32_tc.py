@@ -143,3 +143,21 @@ def test_unaligned_or_small_problems_keep_the_fma_kernel(env):
     got, exp, td = run_contraction(ht, h, {0: 64, 1: 64, 2: 64}, [0, 2], [1, 2], [0, 1], typeAB=orc.F32)
     assert ht.last_kernel_name() == "contraction_tiled_simt"
     assert 0 <= rel_error(got, exp, td) < 1e-5
+
+
+@pytest.mark.parametrize("compute", [orc.COMPUTE_16F, orc.COMPUTE_16BF])
+@pytest.mark.parametrize("layout", sorted(LAYOUTS))
+def test_f32_data_with_half_precision_compute(env, compute, layout):
+    """fp32 tensors with compute type f16 / bf16 (reference tuples f32,f32,f32 with ComputeT half / bhalf,
+    contraction_cpu_reference_instances.cpp): every element is rounded to the compute type, products and sums are
+    fp32. The kernel rounds in its converter and issues one TF32 MMA per K step (the rounded values are exact in
+    TF32), so only the summation order differs from the reference's CPU loop."""
+    ht, h = env
+    modeA, modeB = LAYOUTS[layout]
+    for M, N, K in ((256, 320, 96), (384, 1000, 136)):
+        got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F32, compute=compute,
+                                       alpha=1.5, beta=0.5)
+        assert ht.last_kernel_name().startswith("contraction_tf32x3"), ht.last_kernel_name()
+        assert not np.isnan(got).any()
+        err = rel_error(got, exp, td)
+        assert 0 <= err < 1e-5, (compute, layout, (M, N, K), err)

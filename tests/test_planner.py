@@ -94,7 +94,7 @@ def test_contraction_config1(ht):
 
 def test_contraction_fp32_tensor_core_layouts(ht):
     """The four K-/MN-major operand layouts of plain matrices, a two-mode K box, and the cases that stay on the
-    FMA kernel (strides that are not multiples of 16 bytes, tiles smaller than 128 x 64, f16/bf16 compute)."""
+    FMA kernel (strides that are not multiples of 16 bytes, tiles smaller than 128 x 64)."""
     f = ht.R_32F
 
     def plan(lA, mA, lB, mB, lD, mD, compute=None):
@@ -113,7 +113,9 @@ def test_contraction_fp32_tensor_core_layouts(ht):
     # not eligible
     assert "kind=tiled_simt" in plan([130, 34], [0, 2], [70, 34], [1, 2], [130, 70], [0, 1])
     assert "kind=tiled_simt" in plan([64, 64], [0, 2], [64, 64], [1, 2], [64, 64], [0, 1])
-    assert "kind=tiled_simt" in plan([M, K], [0, 2], [N, K], [1, 2], [M, N], [0, 1], ht.COMPUTE_16F)
+    # f16 / bf16 compute on fp32 data: the same kernel with rounding instead of the split
+    assert "kind=tf32x3" in plan([M, K], [0, 2], [N, K], [1, 2], [M, N], [0, 1], ht.COMPUTE_16F)
+    assert "kind=tf32x3" in plan([K, M], [2, 0], [K, N], [2, 1], [M, N], [0, 1], ht.COMPUTE_16BF)
 
 
 def test_contraction_config4(ht):
