@@ -787,13 +787,12 @@ namespace htb
         {
             auto         kernel = contraction_tf32x3_kernel<PAIR>;
             const size_t smem   = size_t(TfRing<PAIR>::kTotal) + 1024;
-            static bool  attrSet = false;
-            if(!attrSet)
+            static unsigned char attrSet[kMaxDevices] = {};
+            if(firstUseOnDevice(attrSet))
             {
                 cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
                 if(e != cudaSuccess)
                     return e;
-                attrSet = true;
             }
             const int      accCols = PAIR ? 128 : a.gn.rows;
             const uint32_t idesc   = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(accCols >> 3) << 17)

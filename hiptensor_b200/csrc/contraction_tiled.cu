@@ -522,14 +522,13 @@ namespace htb
                 return cudaErrorInvalidConfiguration;
             a.tilesN          = int(tilesN);
             const size_t smem = sizeof(double) * 2 * DK * (DM + PAD + DN + PAD);
-            static bool  attr = false;
-            if(!attr)
+            static unsigned char attr[kMaxDevices] = {};
+            if(firstUseOnDevice(attr))
             {
                 cudaError_t e = cudaFuncSetAttribute(contraction_dmma_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                      int(smem));
                 if(e != cudaSuccess)
                     return e;
-                attr = true;
             }
             contraction_dmma_kernel<DK><<<unsigned(tilesM * tilesN), THREADS, smem, stream>>>(
                 (const double*)A, (const double*)B, (const double*)C, (double*)D, a);

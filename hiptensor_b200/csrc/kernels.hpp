@@ -47,4 +47,17 @@ namespace htb
     cudaError_t launchContraction(const ContractionPlan& plan, float alpha, const void* A, const void* B,
                                   float beta, const void* C, void* D, void* workspace, uint64_t workspaceBytes,
                                   int smCount, int* deviceStatus, cudaStream_t stream);
+
+    // Function attributes (dynamic shared-memory limit) belong to one device: true the first time the calling
+    // site is reached with the current device, so that a process that drives several GPUs sets them on each.
+    inline bool firstUseOnDevice(unsigned char (&seen)[kMaxDevices])
+    {
+        int dev = 0;
+        if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+            return true;
+        if(seen[dev])
+            return false;
+        seen[dev] = 1;
+        return true;
+    }
 } // namespace htb

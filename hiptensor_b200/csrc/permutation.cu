@@ -713,14 +713,18 @@ namespace htb
             a.numTiles = uint32_t(tiles);
             a.inStages  = tune.inStages;
             const int   smem = (a.inStages + kOutStages) * TP * TQ * 4 + 1024;
-            static int  attrSmem = 0;
-            if(smem > attrSmem)
+            // the limit is a property of the function on the current device; the stage count can change between calls
+            static int attrSmem[kMaxDevices] = {};
+            int        dev = 0;
+            cudaGetDevice(&dev);
+            if(dev < 0 || dev >= kMaxDevices || smem > attrSmem[dev])
             {
                 cudaError_t e
                     = cudaFuncSetAttribute(perm_tma_kernel<NP, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
                 if(e != cudaSuccess)
                     return e;
-                attrSmem = smem;
+                if(dev >= 0 && dev < kMaxDevices)
+                    attrSmem[dev] = smem;
             }
             const int       fit   = std::max(1, (227 * 1024) / (smem + 1024));
             const int       perSm = std::min(fit, tune.ctasPerSm);
