@@ -56,11 +56,14 @@ namespace htb
 
         // Shared-memory rings. A staging slot holds the raw A rows and B rows of one K block, an operand slot
         // A big, A small, B big, B small. A CTA of a pair carries 64 rows of B and so affords three slots of each.
-        template <bool PAIR>
+        // INPLACE (both operands K-major, compute f32): TMA writes the raw rows straight into the "big" tiles of an
+        // operand slot - the tensor cores read fp32 bits as TF32 by dropping the low 13 mantissa bits - and the
+        // converter adds only the small tiles. No staging ring, three operand slots, a third less conversion traffic.
+        template <bool PAIR, bool INPLACE>
         struct TfRing
         {
             static constexpr uint32_t kBBytes       = PAIR ? kTileBytes / 2 : kTileBytes;
-            static constexpr int      kStagingSlots = PAIR ? 3 : 2, kOpSlots = PAIR ? 3 : 2;
+            static constexpr int      kStagingSlots = INPLACE ? 0 : (PAIR ? 3 : 2), kOpSlots = (PAIR || INPLACE) ? 3 : 2;
             static constexpr uint32_t kStagingBytes = kTileBytes + kBBytes;
             static constexpr uint32_t kOpBytes      = 2 * kTileBytes + 2 * kBBytes;
             static constexpr uint32_t kTotal        = kStagingSlots * kStagingBytes + kOpSlots * kOpBytes;
@@ -219,6 +222,38 @@ namespace htb
             }
         }
 
+        // In-place variant: the tile at `big` holds the raw fp32 rows (K-major, TMA-swizzled); write the small tile.
+        // The tensor cores will use big = x with the low 13 mantissa bits dropped, so small = x - that, rounded to
+        // TF32 (nearest, by integer add-and-mask) so that their truncation of it loses nothing more.
+        __device__ __forceinline__ void tfConvertSmall(uint32_t big, uint32_t dstSmall, int t, int rows)
+        {
+#pragma unroll
+            for(int pass = 0; pass < 4; pass++)
+            {
+                if(pass * 32 >= rows)
+                    break;
+                const uint32_t off = uint32_t(pass * 32 + (t >> 3)) * 128 + (uint32_t(t & 7) << 4);
+                const float4   v   = lds128(big + off);
+                const float    x[4] = {v.x, v.y, v.z, v.w};
+                float          sm[4];
+#pragma unroll
+                for(int e = 0; e < 4; e++)
+                {
+                    const float b = __uint_as_float(__float_as_uint(x[e]) & 0xFFFFE000u);
+                    const float r = x[e] - b; // exact
+                    sm[e]         = tfBig(r);
+                }
+                // infinite or NaN elements: keep them in the big part only
+                if(!(fabsf(v.x) + fabsf(v.y) + fabsf(v.z) + fabsf(v.w) < INFINITY))
+                {
+#pragma unroll
+                    for(int e = 0; e < 4; e++)
+                        sm[e] = (fabsf(x[e]) < INFINITY) ? sm[e] : 0.f;
+                }
+                sts128(dstSmall + off, make_float4(sm[0], sm[1], sm[2], sm[3]));
+            }
+        }
+
         // Bounded wait, executed by every thread of the waiting warp: a tight try_wait loop, the clock is read only
         // every 256th unsuccessful poll.
         __device__ __forceinline__ bool tfWait(uint32_t bar, uint32_t parity, volatile int* abortFlag)
@@ -261,7 +296,7 @@ namespace htb
         // accumulators (double buffered across tiles) at 256 and 384.
         constexpr int kSegBlocks = 2;
 
-        template <bool PAIR>
+        template <bool PAIR, bool INPLACE>
         __global__ void __launch_bounds__(kTfThreads, 1)
             contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                       const float* __restrict__ C, float* __restrict__ D, TfArgs a, uint32_t idesc)
@@ -269,8 +304,10 @@ namespace htb
             extern __shared__ unsigned char smemRaw[];
             unsigned char* tiles = (unsigned char*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
 
-            using Ring = TfRing<PAIR>;
+            using Ring = TfRing<PAIR, INPLACE>;
+            static_assert(!(PAIR && INPLACE), "the in-place ring is built for single CTAs");
             constexpr int      kStagingSlots = Ring::kStagingSlots, kOpSlots = Ring::kOpSlots;
+            constexpr int      kLoadSlots = INPLACE ? kOpSlots : kStagingSlots; // slots that TMA writes
             constexpr uint32_t kStagingBytes = Ring::kStagingBytes, kOpBytes = Ring::kOpBytes, kBBytes = Ring::kBBytes;
             __shared__ __align__(8) unsigned long long stFullBar[kMaxSlots], stEmptyBar[kMaxSlots];
             __shared__ __align__(8) unsigned long long opFullBar[kMaxSlots], opEmptyBar[kMaxSlots];
@@ -294,7 +331,7 @@ namespace htb
             if(threadIdx.x == 0)
             {
                 abortFlag = 0;
-                for(int s = 0; s < kStagingSlots; s++)
+                for(int s = 0; s < kLoadSlots; s++)
                 {
                     mbarInit(smemAddr(&stFullBar[s]), 1);
                     mbarInit(smemAddr(&stEmptyBar[s]), kConvWarps);
@@ -396,7 +433,9 @@ namespace htb
                         int            kc0 = 0, kc1 = 0, kq = 0; // K coordinates of the block (MN-major operands)
                         for(int kb = 0; kb < a.kBlocks; kb++)
                         {
-                            ok = __all_sync(0xffffffffu, tfWait(stEmpty + 8 * slot, phase ^ 1, abortP));
+                            // a free slot: of the staging ring (released by the converter) or, in place, of the operand
+                            // ring (released by the MMAs that read it)
+                            ok = __all_sync(0xffffffffu, tfWait((INPLACE ? opEmpty : stEmpty) + 8 * slot, phase ^ 1, abortP));
                             if(!ok)
                                 break;
                             if(lane == 0)
@@ -407,9 +446,10 @@ namespace htb
                                 else
                                 {
                                     mbarArriveExpectTx(bar, a.bytesA + a.bytesB);
-                                    const uint32_t dst = stagingAddr + slot * kStagingBytes;
+                                    const uint32_t dst  = INPLACE ? opAddr + slot * kOpBytes : stagingAddr + slot * kStagingBytes;
+                                    const uint32_t dstB = dst + (INPLACE ? 2 * kTileBytes : kTileBytes);
                                     tfLoadRows(a.gm, wm, qm, &mapA, dst, bar, kb, kc0, kc1);
-                                    tfLoadRows(a.gn, wn, qn, &mapB, dst + kTileBytes, bar, kb, kc0, kc1);
+                                    tfLoadRows(a.gn, wn, qn, &mapB, dstB, bar, kb, kc0, kc1);
                                 }
                             }
                             __syncwarp();
@@ -420,7 +460,7 @@ namespace htb
                                 kc0 = 0;
                                 kc1 += a.boxK[1];
                             }
-                            if(++slot == kStagingSlots)
+                            if(++slot == kLoadSlots)
                             {
                                 slot = 0;
                                 phase ^= 1;
@@ -676,31 +716,50 @@ namespace htb
                 {
                     for(int kb = 0; kb < a.kBlocks; kb++)
                     {
-                        ok = tfWait(stFull + 8 * sSlot, sPhase, abortP)
-                             && tfWait(opEmpty + 8 * oSlot, oPhase ^ 1, abortP);
-                        ok = __all_sync(0xffffffffu, ok);
-                        if(!ok)
-                            break;
-                        const uint32_t st = stagingAddr + sSlot * kStagingBytes;
-                        const uint32_t op = opAddr + oSlot * kOpBytes;
-                        if(!(a.probe & 1))
+                        if constexpr(INPLACE)
                         {
-                            tfConvertRow(a.gm.major, st, op, op + kTileBytes, r, kh, 128, a.round);
-                            tfConvertRow(a.gn.major, st + kTileBytes, op + 2 * kTileBytes, op + 2 * kTileBytes + kBBytes, r, kh,
-                                         a.gn.rows, a.round);
+                            // the loads of this operand slot have landed (its producer had waited for the slot to be free)
+                            ok = __all_sync(0xffffffffu, tfWait(stFull + 8 * oSlot, oPhase, abortP));
+                            if(!ok)
+                                break;
+                            const uint32_t op = opAddr + oSlot * kOpBytes;
+                            if(!(a.probe & 1))
+                            {
+                                tfConvertSmall(op, op + kTileBytes, ct, 128);
+                                tfConvertSmall(op + 2 * kTileBytes, op + 2 * kTileBytes + kBBytes, ct, a.gn.rows);
+                            }
+                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            __syncwarp();
+                            if(lane == 0)
+                                arriveIssuer(opFull + 8 * oSlot);
                         }
-                        // the ring is read by the tensor cores (async proxy): order this thread's stores before it
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        __syncwarp();
-                        if(lane == 0)
+                        else
                         {
-                            mbarArrive(stEmpty + 8 * sSlot);
-                            arriveIssuer(opFull + 8 * oSlot);
-                        }
-                        if(++sSlot == kStagingSlots)
-                        {
-                            sSlot = 0;
-                            sPhase ^= 1;
+                            ok = tfWait(stFull + 8 * sSlot, sPhase, abortP) && tfWait(opEmpty + 8 * oSlot, oPhase ^ 1, abortP);
+                            ok = __all_sync(0xffffffffu, ok);
+                            if(!ok)
+                                break;
+                            const uint32_t st = stagingAddr + sSlot * kStagingBytes;
+                            const uint32_t op = opAddr + oSlot * kOpBytes;
+                            if(!(a.probe & 1))
+                            {
+                                tfConvertRow(a.gm.major, st, op, op + kTileBytes, r, kh, 128, a.round);
+                                tfConvertRow(a.gn.major, st + kTileBytes, op + 2 * kTileBytes, op + 2 * kTileBytes + kBBytes, r, kh,
+                                             a.gn.rows, a.round);
+                            }
+                            // the ring is read by the tensor cores (async proxy): order this thread's stores before it
+                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            __syncwarp();
+                            if(lane == 0)
+                            {
+                                mbarArrive(stEmpty + 8 * sSlot);
+                                arriveIssuer(opFull + 8 * oSlot);
+                            }
+                            if(++sSlot == (kStagingSlots > 0 ? kStagingSlots : 1))
+                            {
+                                sSlot = 0;
+                                sPhase ^= 1;
+                            }
                         }
                         if(++oSlot == kOpSlots)
                         {
@@ -781,12 +840,12 @@ namespace htb
                    == CUDA_SUCCESS;
         }
 
-        template <bool PAIR>
+        template <bool PAIR, bool INPLACE>
         cudaError_t launchKernel(const CUtensorMap& mapA, const CUtensorMap& mapB, const float* C, float* D, TfArgs& a, int sms,
                                  cudaStream_t stream)
         {
-            auto         kernel = contraction_tf32x3_kernel<PAIR>;
-            const size_t smem   = size_t(TfRing<PAIR>::kTotal) + 1024;
+            auto         kernel = contraction_tf32x3_kernel<PAIR, INPLACE>;
+            const size_t smem   = size_t(TfRing<PAIR, INPLACE>::kTotal) + 1024;
             static unsigned char attrSet[kMaxDevices] = {};
             if(firstUseOnDevice(attrSet))
             {
@@ -889,7 +948,11 @@ namespace htb
             return cudaErrorInvalidConfiguration;
         HTB_LOG_HEUR("hiptensorContraction", "tf32x3: %d x %d row tiles (%d B rows each), %d K blocks, %s", a.gm.tiles,
                      a.gn.tiles, a.gn.rows, a.kBlocks, pair ? "CTA pairs" : "single CTAs");
-        return pair ? launchKernel<true>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream)
-                    : launchKernel<false>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream);
+        if(pair)
+            return launchKernel<true, false>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream);
+        // both operands K-major and no rounding: TMA loads straight into the operand ring
+        const bool inplace = !p.aMajor && !p.bMajor && a.round == 0 && getenv("HTB_TF32_NOINPLACE") == nullptr;
+        return inplace ? launchKernel<false, true>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream)
+                       : launchKernel<false, false>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream);
     }
 } // namespace htb
