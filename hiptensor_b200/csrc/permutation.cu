@@ -185,13 +185,17 @@ namespace htb
             }
             else
             {
-                const __half2 h  = *reinterpret_cast<const __half2*>(&v);
-                const __half  lo = Elem<__half>::apply(__low2half(h), alpha, opA, opB);
-                const __half  hi = Elem<__half>::apply(__high2half(h), alpha, opA, opB);
+                // both halves at once: the paired multiply rounds each lane like the scalar one
+                __half2 h = *reinterpret_cast<const __half2*>(&v);
+                if(opA == 2)
+                    h = __hmul2(h, h);
+                h = __hmul2(__float2half2_rn(alpha), h);
+                if(opB == 2)
+                    h = __hmul2(h, h);
                 if constexpr(sizeof(TO) == 2)
-                    *reinterpret_cast<__half2*>(dst) = __halves2half2(lo, hi);
+                    *reinterpret_cast<__half2*>(dst) = h;
                 else
-                    *reinterpret_cast<float2*>(dst) = make_float2(__half2float(lo), __half2float(hi));
+                    *reinterpret_cast<float2*>(dst) = __half22float2(h);
             }
         }
 
