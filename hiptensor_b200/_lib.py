@@ -41,6 +41,8 @@ SIGNATURES = {
     "htDescribeContractionPlan": (_int, [_u32, _i64p, _i64p, _i32p, _int, _u32, _i64p, _i64p, _i32p, _int, _u32,
                                          _i64p, _i64p, _i32p, _int, _int, _int, ctypes.c_char_p, _u64]),
     "htLastKernelName": (ctypes.c_char_p, []),
+    "htGetDeviceStatus": (_int, [_vp, ctypes.POINTER(ctypes.c_int32)]),
+    "htInjectDeviceStatus": (_int, [_vp, ctypes.c_int32]),
     "htKernelLaunchCount": (_u64, []),
 }
 

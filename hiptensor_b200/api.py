@@ -19,6 +19,7 @@ __all__ = [
     "WORKSPACE_MIN", "WORKSPACE_RECOMMENDED", "WORKSPACE_MAX",
     "STATUS_SUCCESS", "STATUS_NOT_INITIALIZED", "STATUS_INVALID_VALUE", "STATUS_ARCH_MISMATCH",
     "STATUS_INTERNAL_ERROR", "STATUS_NOT_SUPPORTED", "STATUS_HIP_ERROR", "STATUS_INSUFFICIENT_WORKSPACE",
+    "STATUS_EXECUTION_FAILED",
     "error_string", "last_kernel_name", "kernel_launch_count",
     "describe_permutation_plan", "describe_reduction_plan", "describe_contraction_plan", "dtype_size",
 ]
@@ -36,6 +37,7 @@ WORKSPACE_MIN, WORKSPACE_RECOMMENDED, WORKSPACE_MAX = 1, 2, 3
 # hiptensorStatus_t (hiptensor_types.hpp:42-71)
 STATUS_SUCCESS, STATUS_NOT_INITIALIZED, STATUS_INVALID_VALUE, STATUS_ARCH_MISMATCH = 0, 1, 7, 8
 STATUS_INTERNAL_ERROR, STATUS_NOT_SUPPORTED, STATUS_HIP_ERROR, STATUS_INSUFFICIENT_WORKSPACE = 14, 15, 18, 19
+STATUS_EXECUTION_FAILED = 13
 
 _DTYPE_SIZE = {R_32F: 4, R_64F: 8, R_16F: 2, R_16BF: 2}
 
@@ -176,6 +178,12 @@ class Handle:
                                    _lib.i32(modeC), _ptr(D), descD._p, _lib.i32(modeD), int(op_reduce),
                                    int(type_compute), _ptr(workspace), int(workspace_size), _stream_ptr(stream)),
                "hiptensorReduction")
+
+    def device_status(self):
+        """The handle's device status word: 0, or the code left by a kernel whose bounded device-side wait ran out."""
+        out = ctypes.c_int32(0)
+        _check(self._L.htGetDeviceStatus(self._h, ctypes.byref(out)), "htGetDeviceStatus")
+        return out.value
 
     def reduction_no_alloc(self, alpha, A, descA, modeA, beta, C, descC, modeC, D, descD, modeD, op_reduce,
                            type_compute, stream=None):

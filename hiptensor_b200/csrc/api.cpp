@@ -38,6 +38,17 @@ namespace
                           st->device, hiptensorGetErrorString(HIPTENSOR_STATUS_ARCH_MISMATCH));
             return HIPTENSOR_STATUS_ARCH_MISMATCH;
         }
+        // A kernel of an earlier call gave up a bounded wait (it skipped its remaining work, so that call's
+        // output is incomplete): reported once, on the next call, then cleared. The kernels exit cleanly, the
+        // handle stays usable.
+        if(st->hostStatus && *st->hostStatus != 0)
+        {
+            const int code = *st->hostStatus;
+            *st->hostStatus = 0;
+            HTB_LOG_ERROR(func, "an earlier kernel on this handle timed out in a device-side wait (code %d) (%s)", code,
+                          hiptensorGetErrorString(HIPTENSOR_STATUS_EXECUTION_FAILED));
+            return HIPTENSOR_STATUS_EXECUTION_FAILED;
+        }
         return HIPTENSOR_STATUS_SUCCESS;
     }
 
@@ -141,12 +152,20 @@ hiptensorStatus_t hiptensorCreate(hiptensorHandle_t** handle)
     st->ccMajor      = major;
     st->ccMinor      = minor;
     st->maxSmemOptin = smem;
-    if(cudaMalloc((void**)&st->deviceStatus, 256) != cudaSuccess || cudaMemset(st->deviceStatus, 0, 256) != cudaSuccess)
+    // The status word lives in pinned host memory mapped into the device: a kernel that gives up a bounded wait
+    // writes it, the next call on the handle reads it without synchronising.
+    void* hostWord = nullptr;
+    if(cudaHostAlloc(&hostWord, 256, cudaHostAllocMapped) != cudaSuccess
+       || cudaHostGetDevicePointer((void**)&st->deviceStatus, hostWord, 0) != cudaSuccess)
     {
         cudaGetLastError();
+        if(hostWord)
+            cudaFreeHost(hostWord);
         delete h;
         return HIPTENSOR_STATUS_ALLOC_FAILED;
     }
+    std::memset(hostWord, 0, 256);
+    st->hostStatus = static_cast<volatile int*>(hostWord);
     st->magic = kHandleMagic;
     *handle   = h;
     return HIPTENSOR_STATUS_SUCCESS;
@@ -160,8 +179,8 @@ hiptensorStatus_t hiptensorDestroy(hiptensorHandle_t* handle)
     HandleState* st = mutableState(handle);
     if(st->magic == kHandleMagic)
     {
-        if(st->deviceStatus)
-            cudaFree(st->deviceStatus);
+        if(st->hostStatus)
+            cudaFreeHost(const_cast<int*>(st->hostStatus));
         st->magic = 0;
     }
     delete handle;

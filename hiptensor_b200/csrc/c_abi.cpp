@@ -285,6 +285,28 @@ const char* htLastKernelName(void)
 {
     return htb::lastKernelName();
 }
+int htGetDeviceStatus(const htHandle* handle, int32_t* status)
+{
+    if(!handle || !status)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    const htb::HandleState* st = htb::stateOf(H(handle));
+    if(!st)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    *status = st->hostStatus ? *st->hostStatus : 0;
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+int htInjectDeviceStatus(const htHandle* handle, int32_t code)
+{
+    if(!handle)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    const htb::HandleState* st = htb::stateOf(H(handle));
+    if(!st || !st->hostStatus)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    *st->hostStatus = code;
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
 uint64_t htKernelLaunchCount(void)
 {
     return htb::launchCount();

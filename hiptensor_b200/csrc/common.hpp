@@ -71,7 +71,8 @@ namespace htb
         int      ccMinor;
         int      maxSmemOptin;
         int      reserved;
-        int*     deviceStatus; // one int on the device, set by kernels whose bounded waits ran out
+        int*     deviceStatus; // device address of the status word that kernels raise when a bounded wait runs out
+        volatile int* hostStatus; // the same word as the host sees it (pinned, mapped memory)
     };
     constexpr uint64_t kHandleMagic = 0x4854423230300001ull;
 

@@ -138,6 +138,14 @@ int htDescribeContractionPlan(uint32_t numModesA, const int64_t* lensA, const in
 /* Name of the kernel family the last call on this thread launched ("" if none).
  * For tests and the bench, to show which CUDA path ran. */
 const char* htLastKernelName(void);
+/* Device status word of the handle: 0, or the code a kernel left when one of its bounded device-side waits ran
+ * out (1 permutation, 2 single-CTA f16 kernel, 3 CTA-pair f16 kernel, 4 fp32 tensor-core kernel). Reading does not
+ * clear it; the next operation on the handle reports HIPTENSOR_STATUS_EXECUTION_FAILED once and clears it. No
+ * reference counterpart: the reference's kernels have no device-side waits. */
+int htGetDeviceStatus(const htHandle* handle, int32_t* status);
+/* Test aid (host-side fault injection): writes the status word as a timed-out kernel would, so that the error
+ * path of the next operation can be exercised without making a kernel wait. */
+int htInjectDeviceStatus(const htHandle* handle, int32_t code);
 /* Number of kernel launches made by this library since load (all threads). */
 uint64_t htKernelLaunchCount(void);
 
