@@ -297,6 +297,117 @@ namespace htb
             }
         }
 
+        // ------------------------------------------------------------ 128 x 128 tile kernel for f16, 4 x 4 blocks
+        // Every extent and stride involved is a multiple of 4 elements: a thread loads four rows of 8 bytes
+        // (4 halves along p from rows q .. q+3), transposes the 4 x 4 block in registers (eight byte permutes) and
+        // stores four 8-byte units along q into the transposed shared tile [128 p][32 units]. Units are swizzled
+        // (unit ^ (p / 4)) so that both the column-wise stores and the row-wise loads of a half warp touch 16
+        // different 8-byte banks. A warp moves 256 contiguous bytes per row on both sides.
+        constexpr int kTile4 = 128;
+
+        __device__ __forceinline__ void transpose4x4Half(const uint2 (&r)[4], uint2 (&o)[4])
+        {
+            // r[i] = row q+i: halves p0..p3 (x: p0 p1, y: p2 p3);  o[j] = row p+j: halves q0..q3
+            o[0].x = __byte_perm(r[0].x, r[1].x, 0x5410);
+            o[0].y = __byte_perm(r[2].x, r[3].x, 0x5410);
+            o[1].x = __byte_perm(r[0].x, r[1].x, 0x7632);
+            o[1].y = __byte_perm(r[2].x, r[3].x, 0x7632);
+            o[2].x = __byte_perm(r[0].y, r[1].y, 0x5410);
+            o[2].y = __byte_perm(r[2].y, r[3].y, 0x5410);
+            o[3].x = __byte_perm(r[0].y, r[1].y, 0x7632);
+            o[3].y = __byte_perm(r[2].y, r[3].y, 0x7632);
+        }
+
+        template <typename TO>
+        __global__ void __launch_bounds__(256)
+            perm_tile4_half_kernel(const __half* __restrict__ A, TO* __restrict__ B, PermArgs a, int tilesP, int tilesQ)
+        {
+            __shared__ uint2 tile[kTile4][32];
+            int64_t          bid = blockIdx.x;
+            const int        tp  = int(bid % tilesP);
+            bid /= tilesP;
+            const int tq = int(bid % tilesQ);
+            bid /= tilesQ;
+            int64_t offA = 0, offB = 0;
+            for(int d = 1; d < a.ndim; d++)
+            {
+                if(d == a.q)
+                    continue;
+                int64_t c = bid % a.ext[d];
+                bid /= a.ext[d];
+                offA += c * a.sA[d];
+                offB += c * a.sB[d];
+            }
+            const int64_t p0 = int64_t(tp) * kTile4, q0 = int64_t(tq) * kTile4;
+            const int64_t sAq = a.sA[a.q], sBp = a.sB[0];
+            const bool    inside = p0 + kTile4 <= a.ext[0] && q0 + kTile4 <= a.ext[a.q];
+            const int     lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+            {
+                // lanes along p: halves 4*lane .. 4*lane+3; the warp takes q blocks warp, warp+8, warp+16, warp+24
+                const __half* src = A + offA + p0 + 4 * lane + (q0 + 4 * warp) * sAq;
+                const bool    pok = inside || p0 + 4 * lane < a.ext[0];
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+                {
+                    const int qb = warp + 8 * j;
+                    if(pok && (inside || q0 + 4 * qb < a.ext[a.q]))
+                    {
+                        uint2 r[4], o[4];
+#pragma unroll
+                        for(int i = 0; i < 4; i++)
+                            r[i] = *reinterpret_cast<const uint2*>(src + i * sAq);
+                        transpose4x4Half(r, o);
+#pragma unroll
+                        for(int i = 0; i < 4; i++)
+                            tile[4 * lane + i][qb ^ lane] = o[i];
+                    }
+                    src += 32 * sAq;
+                }
+            }
+            __syncthreads();
+            {
+                // lanes along q: unit `lane` (halves 4*lane .. +3) of the output row; the warp takes rows warp + 8j
+                TO*        dst = B + offB + q0 + 4 * lane + (p0 + warp) * sBp;
+                const bool qok = inside || q0 + 4 * lane < a.ext[a.q];
+                const __half2 alpha2 = __float2half2_rn(a.alpha);
+#pragma unroll 4
+                for(int j = 0; j < 16; j++)
+                {
+                    const int pl = warp + 8 * j;
+                    if(qok && (inside || p0 + pl < a.ext[0]))
+                    {
+                        const uint2 v  = tile[pl][lane ^ ((pl >> 2) & 31)];
+                        __half2     h0 = *reinterpret_cast<const __half2*>(&v.x), h1 = *reinterpret_cast<const __half2*>(&v.y);
+                        if(a.opA == 2)
+                        {
+                            h0 = __hmul2(h0, h0);
+                            h1 = __hmul2(h1, h1);
+                        }
+                        h0 = __hmul2(alpha2, h0);
+                        h1 = __hmul2(alpha2, h1);
+                        if(a.opB == 2)
+                        {
+                            h0 = __hmul2(h0, h0);
+                            h1 = __hmul2(h1, h1);
+                        }
+                        if constexpr(sizeof(TO) == 2)
+                        {
+                            uint2 o;
+                            o.x = *reinterpret_cast<const uint32_t*>(&h0);
+                            o.y = *reinterpret_cast<const uint32_t*>(&h1);
+                            *reinterpret_cast<uint2*>(dst) = o;
+                        }
+                        else
+                        {
+                            const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+                            *reinterpret_cast<float4*>(dst) = make_float4(f0.x, f0.y, f1.x, f1.y);
+                        }
+                    }
+                    dst += 8 * sBp;
+                }
+            }
+        }
+
         // ------------------------------------------------------------ TMA kernel (f32)
         // Tile = (32*NP) x (32*NQ) elements of the (p, q) plane, p = A's fastest folded mode,
         // q = B's fastest folded mode. Input stage: NP boxes of [32*NQ rows of q][32 floats of p];
@@ -824,6 +935,27 @@ namespace htb
                         blocks *= p.ext[d];
                 if(blocks > 0x7fffffffll)
                     return cudaErrorInvalidConfiguration;
+                // f16 with everything a multiple of 4 elements: 128 x 128 tiles, 4 x 4 blocks, 8-byte accesses
+                if constexpr(sizeof(TI) == 2)
+                {
+                    bool quad = (uintptr_t(A) % 8) == 0 && (uintptr_t(B) % (4 * sizeof(TO))) == 0 && p.ext[0] % 4 == 0
+                                && p.ext[p.q] % 4 == 0;
+                    for(int d = 0; d < p.ndim && quad; d++)
+                        quad = (d == 0 || p.sA[d] % 4 == 0) && (d == p.q || p.sB[d] % 4 == 0);
+                    if(quad)
+                    {
+                        const int tP = int((p.ext[0] + kTile4 - 1) / kTile4), tQ = int((p.ext[p.q] + kTile4 - 1) / kTile4);
+                        int64_t   nb = int64_t(tP) * tQ;
+                        for(int d = 1; d < p.ndim; d++)
+                            if(d != p.q)
+                                nb *= p.ext[d];
+                        if(nb > 0x7fffffffll)
+                            return cudaErrorInvalidConfiguration;
+                        perm_tile4_half_kernel<TO><<<unsigned(nb), 256, 0, stream>>>((const __half*)A, (TO*)B, a, tP, tQ);
+                        noteLaunch("perm_tile");
+                        return cudaGetLastError();
+                    }
+                }
                 // 2 x 2 blocks when every extent, stride and base address is even (2-element accesses stay aligned)
                 bool even = (uintptr_t(A) % (2 * sizeof(TI))) == 0 && (uintptr_t(B) % (2 * sizeof(TO))) == 0;
                 for(int d = 0; d < p.ndim && even; d++)

@@ -109,6 +109,19 @@ def test_generic_tile_kernel_even_and_odd(env, typeA, typeB, lens):
         assert np.array_equal(bits(got), bits(exp)), (lens, perm, ht.last_kernel_name())
 
 
+@pytest.mark.parametrize("typeB", [orc.F16, orc.F32])
+@pytest.mark.parametrize("lens", [[132, 8, 68, 12], [256, 4, 128, 4], [64, 3, 128, 5], [4, 4, 4, 4]])
+def test_f16_tile_kernel_blocks_of_four(env, typeB, lens):
+    """f16 tensors whose extents and strides are multiples of 4 take 128 x 128 tiles with 4 x 4 register blocks
+    (ragged tiles: 132 = 128 + 4, 68; tiny tensors); scale and unary operators; both output types."""
+    ht, h = env
+    for perm in ([3, 2, 1, 0], [1, 0, 2, 3], [2, 3, 0, 1], [2, 0, 3, 1]):
+        for opA, opB, alpha in ((orc.OP_IDENTITY, orc.OP_IDENTITY, 1.0), (orc.OP_SQRT, orc.OP_SQRT, 0.5)):
+            got, exp = run_permutation(ht, h, lens, [0, 1, 2, 3], perm, typeA=orc.F16, typeB=typeB, alpha=alpha,
+                                       type_scalar=orc.F16, opA=opA, opB=opB)
+            assert np.array_equal(bits(got), bits(exp)), (lens, perm, opA, ht.last_kernel_name())
+
+
 def test_rejects_unsupported(env):
     ht, h = env
     dA = h.tensor_descriptor([4, 4], None, ht.R_64F)
