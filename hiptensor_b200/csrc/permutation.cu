@@ -1,9 +1,10 @@
 // Permutation kernels for sm_100a: B[perm(i)] = opB(alpha * opA(A[i])).
 //
-// Three kernels, chosen by the planner (planner.hpp PermKind):
+// Kernels, chosen by the planner (planner.hpp PermKind) and, within PERM_TILE, by alignment:
 //   perm_copy_kernel : A's and B's fastest folded modes coincide; coalesced row copy.
-//   perm_tile_kernel : 64x64 tile through padded shared memory, plain loads/stores;
-//                      any extents, f32 and f16.
+//   perm_tile_kernel : 64x64 tile through padded shared memory, plain loads/stores; any extents, f32 and
+//                      f16; 2x2 register blocks when everything is even, else element by element.
+//   perm_tile4_half_kernel : f16 with extents and strides that are multiples of 4: 128x128 tiles, 4x4 blocks.
 //   perm_tma_kernel  : f32, extents multiple of 4: TMA box loads into 128B-swizzled
 //                      shared memory, a 4x4 register transpose per thread with a
 //                      diagonal thread->chunk assignment that is bank-conflict free on
