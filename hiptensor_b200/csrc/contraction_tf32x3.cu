@@ -79,6 +79,12 @@ namespace htb
             int      bilinear;
             int      nContig; // 32 consecutive columns of a tile are 32 consecutive, 16-byte aligned floats of D
             int      pairsM, pairsN; // PAIR only
+            // K split of small problems (single CTAs only): every tile is cut into `parts` ranges of K blocks, one work
+            // unit each, all resident at once. Part 0 owns the tile: it waits for the others' raw sums in `slots`
+            // (flag per tile), adds them in order and applies alpha/beta; parts 1.. write their sums and raise the flag.
+            int      parts;
+            float*   slots; // [tile][part - 1][128 rows][accumulator columns]
+            int*     flags; // one counter per tile, zeroed before the launch
             int      round; // 0: big/small split (compute f32); 1 / 2: elements rounded to f16 / bf16, one MMA per K step
             int      probe; // measurement aid, bit mask: 1 = converter skips its work, 2 = issuer skips the MMAs,
                             // 8 = producer skips the loads (results invalid)
@@ -322,10 +328,16 @@ namespace htb
             const int      ctas   = PAIR ? 2 : 1;
             const int      worker = PAIR ? int(blockIdx.x >> 1) : int(blockIdx.x); // CTA or CTA pair
             const int      numWorkers = PAIR ? int(gridDim.x >> 1) : int(gridDim.x);
-            const int      numUnits   = PAIR ? a.pairsM * a.pairsN : a.gm.tiles * a.gn.tiles;
+            const int      parts      = PAIR ? 1 : a.parts;
+            const int      numUnits   = PAIR ? a.pairsM * a.pairsN : a.gm.tiles * a.gn.tiles * parts;
             const int      unitsM     = PAIR ? a.pairsM : a.gm.tiles;
             const int      accCols    = ctas * a.gn.rows; // accumulator columns per tile (a pair: two 64-row B tiles)
-            const int      numSegs    = (a.kBlocks + kSegBlocks - 1) / kSegBlocks;
+            // K blocks of a unit: part (u % parts) of tile (u / parts)
+            auto kRange = [&](int u, int& kb0, int& kb1) {
+                const int part = u % parts;
+                kb0            = int((long long)a.kBlocks * part / parts);
+                kb1            = int((long long)a.kBlocks * (part + 1) / parts);
+            };
             constexpr uint32_t kTmemCols = 512;
 
             if(threadIdx.x == 0)
@@ -384,7 +396,8 @@ namespace htb
             // this CTA's row tiles of a unit (a pair's second CTA takes the next tile of each group;
             // past the edge it repeats the last one and its results are not stored)
             auto tilesOf = [&](int u, int& tm, int& tn) {
-                const int um = u % unitsM, un = u / unitsM;
+                const int t  = u / parts;
+                const int um = t % unitsM, un = t / unitsM;
                 tm = PAIR ? min(2 * um + int(rank), a.gm.tiles - 1) : um;
                 tn = PAIR ? min(2 * un + int(rank), a.gn.tiles - 1) : un;
             };
@@ -430,8 +443,11 @@ namespace htb
                         tilesOf(u, tm, tn);
                         const TfTile   wm = tfTileOf(a.gm, tm), wn = tfTileOf(a.gn, tn);
                         const TfChunks qm = tfChunksOf(a.gm, wm), qn = tfChunksOf(a.gn, wn);
-                        int            kc0 = 0, kc1 = 0, kq = 0; // K coordinates of the block (MN-major operands)
-                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        int kb0, kb1;
+                        kRange(u, kb0, kb1);
+                        // K coordinates of the block (MN-major operands)
+                        int kq = kb0 % a.kTilesPerDim[0], kc0 = kq * a.boxK[0], kc1 = (kb0 / a.kTilesPerDim[0]) * a.boxK[1];
+                        for(int kb = kb0; kb < kb1; kb++)
                         {
                             // a free slot: of the staging ring (released by the converter) or, in place, of the operand
                             // ring (released by the MMAs that read it)
@@ -487,9 +503,11 @@ namespace htb
                         const int      cb     = local & 1;
                         const uint32_t dCorr  = tmem + 256u + uint32_t(cb) * 128u;
                         bool           corrReady = false;
-                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        int            kb0, kb1;
+                        kRange(u, kb0, kb1);
+                        for(int kb = kb0; kb < kb1; kb++)
                         {
-                            const bool     segStart = (kb % kSegBlocks) == 0;
+                            const bool     segStart = ((kb - kb0) % kSegBlocks) == 0;
                             const uint32_t sb       = seg & 1;
                             if(segStart)
                             {
@@ -527,7 +545,7 @@ namespace htb
                                         mma(dMain, descOf(aBig), descOf(bBig), (!segStart || k) ? 1u : 0u);
                                         if(a.round == 0)
                                         {
-                                            mma(dCorr, descOf(aSml), descOf(bBig), (kb | k) ? 1u : 0u);
+                                            mma(dCorr, descOf(aSml), descOf(bBig), ((kb - kb0) | k) ? 1u : 0u);
                                             mma(dCorr, descOf(aBig), descOf(bSml), 1u);
                                         }
                                         aBig += 2;
@@ -537,9 +555,9 @@ namespace htb
                                     }
                                 }
                                 commitTo(opEmpty + 8 * slot); // the ring slot is free (in both CTAs) once these MMAs have read it
-                                if((kb % kSegBlocks) == kSegBlocks - 1 || kb == a.kBlocks - 1)
+                                if(((kb - kb0) % kSegBlocks) == kSegBlocks - 1 || kb == kb1 - 1)
                                     commitTo(segFull + 8 * sb);
-                                if(kb == a.kBlocks - 1)
+                                if(kb == kb1 - 1)
                                     commitTo(corrFull + 8 * cb);
                             }
                             __syncwarp();
@@ -548,7 +566,7 @@ namespace htb
                                 slot = 0;
                                 phase ^= 1;
                             }
-                            if((kb % kSegBlocks) == kSegBlocks - 1 || kb == a.kBlocks - 1)
+                            if(((kb - kb0) % kSegBlocks) == kSegBlocks - 1 || kb == kb1 - 1)
                                 seg++;
                         }
                     }
@@ -586,7 +604,7 @@ namespace htb
                 for(int u = worker; u < numUnits && alive; u += numWorkers, local++)
                 {
                     const int    cb = local & 1;
-                    const int    um = u % unitsM, un = u / unitsM;
+                    const int    um = (u / parts) % unitsM, un = (u / parts) / unitsM;
                     const int    tmRaw = PAIR ? 2 * um + int(rank) : um;
                     const bool   dupM  = tmRaw >= a.gm.tiles; // this CTA repeats its peer's rows: no stores
                     const TfTile wm    = tfTileOf(a.gm, min(tmRaw, a.gm.tiles - 1));
@@ -608,6 +626,9 @@ namespace htb
 #pragma unroll
                     for(int j = 0; j < 64; j++)
                         sum[j] = 0.f;
+                    int kb0, kb1;
+                    kRange(u, kb0, kb1);
+                    const int numSegs = (kb1 - kb0 + kSegBlocks - 1) / kSegBlocks;
                     for(int s = 0; s < numSegs && alive; s++, seg++)
                     {
                         const uint32_t sb = seg & 1;
@@ -639,22 +660,85 @@ namespace htb
                     if(!alive)
                         break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if(active)
+                    // the correction products complete the sums
+                    if(active && a.round == 0)
                     {
 #pragma unroll
                         for(int c0 = 0; c0 < 64; c0 += 32)
                         {
                             uint32_t v[32];
-                            if(a.round == 0)
-                                loadChunk(lanes + 256u + uint32_t(cb) * 128u + uint32_t(c0), v);
-                            else
-                            {
+                            loadChunk(lanes + 256u + uint32_t(cb) * 128u + uint32_t(c0), v);
 #pragma unroll
-                                for(int j = 0; j < 32; j++)
-                                    v[j] = 0u; // no correction products
+                            for(int j = 0; j < 32; j++)
+                                sum[c0 + j] = __fadd_rn(sum[c0 + j], __uint_as_float(v[j]));
+                        }
+                    }
+                    // K split: parts 1.. publish their sums, part 0 collects them in order
+                    const int part = u % parts, tileIdx = u / parts;
+                    if(parts > 1)
+                    {
+                        float* slotRow = a.slots + ((size_t(tileIdx) * (parts - 1)) * 128 + row) * 128 + cbase;
+                        if(part > 0)
+                        {
+                            if(active)
+                            {
+                                float4* dst = (float4*)(slotRow + size_t(part - 1) * 128 * 128);
+#pragma unroll
+                                for(int j = 0; j < 16; j++)
+                                    dst[j] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
                             }
-                            if(offM < 0)
-                                continue;
+                            __threadfence();
+                            __syncwarp();
+                            if(lane == 0)
+                                atomicAdd(a.flags + tileIdx, 1);
+                        }
+                        else
+                        {
+                            int ready = 1;
+                            if(lane == 0)
+                            {
+                                const int       want = (parts - 1) * kEpiWarps;
+                                const long long t0   = clock64();
+                                for(;;)
+                                {
+                                    int seen;
+                                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(a.flags + tileIdx) : "memory");
+                                    if(seen >= want)
+                                        break;
+                                    if(*abortP || clock64() - t0 > kWaitCycles)
+                                    {
+                                        *abortP = 1;
+                                        ready   = 0;
+                                        break;
+                                    }
+                                }
+                            }
+                            ready = __shfl_sync(0xffffffffu, ready, 0);
+                            if(!ready)
+                                alive = false;
+                            if(ready && active)
+                            {
+                                for(int q = 0; q < parts - 1; q++)
+                                {
+                                    const float4* src = (const float4*)(slotRow + size_t(q) * 128 * 128);
+#pragma unroll
+                                    for(int j = 0; j < 16; j++)
+                                    {
+                                        const float4 p4 = __ldcg(src + j);
+                                        sum[4 * j]     = __fadd_rn(sum[4 * j], p4.x);
+                                        sum[4 * j + 1] = __fadd_rn(sum[4 * j + 1], p4.y);
+                                        sum[4 * j + 2] = __fadd_rn(sum[4 * j + 2], p4.z);
+                                        sum[4 * j + 3] = __fadd_rn(sum[4 * j + 3], p4.w);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    if(active && offM >= 0 && part == 0 && alive)
+                    {
+#pragma unroll
+                        for(int c0 = 0; c0 < 64; c0 += 32)
+                        {
                             const int64_t first     = cols[c0];
                             const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] == first + 31;
                             if(fullChunk && ((offM + first) & 3) == 0)
@@ -666,10 +750,10 @@ namespace htb
                                 for(int j = 0; j < 32; j += 4)
                                 {
                                     float4 o;
-                                    o.x = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j], __uint_as_float(v[j])));
-                                    o.y = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 1], __uint_as_float(v[j + 1])));
-                                    o.z = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 2], __uint_as_float(v[j + 2])));
-                                    o.w = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j + 3], __uint_as_float(v[j + 3])));
+                                    o.x = __fmul_rn(a.alpha, sum[c0 + j]);
+                                    o.y = __fmul_rn(a.alpha, sum[c0 + j + 1]);
+                                    o.z = __fmul_rn(a.alpha, sum[c0 + j + 2]);
+                                    o.w = __fmul_rn(a.alpha, sum[c0 + j + 3]);
                                     if(a.bilinear)
                                     {
                                         const float4 c4 = *(const float4*)(src + j);
@@ -689,7 +773,7 @@ namespace htb
                                     const int64_t oc = cols[c0 + j];
                                     if(oc >= 0)
                                     {
-                                        float y = __fmul_rn(a.alpha, __fadd_rn(sum[c0 + j], __uint_as_float(v[j])));
+                                        float y = __fmul_rn(a.alpha, sum[c0 + j]);
                                         if(a.bilinear)
                                             y = __fadd_rn(y, __fmul_rn(a.beta, C[offM + oc]));
                                         D[offM + oc] = y;
@@ -714,7 +798,9 @@ namespace htb
                 bool       ok = true;
                 for(int u = worker; u < numUnits && ok; u += numWorkers)
                 {
-                    for(int kb = 0; kb < a.kBlocks; kb++)
+                    int kb0, kb1;
+                    kRange(u, kb0, kb1);
+                    for(int kb = kb0; kb < kb1; kb++)
                     {
                         if constexpr(INPLACE)
                         {
@@ -858,7 +944,7 @@ namespace htb
                                    | (uint32_t((PAIR ? 256 : 128) >> 4) << 24); // fp32 accumulate, tf32 x tf32, K-major
             if(!PAIR)
             {
-                const int grid = int(std::min<int64_t>(int64_t(a.gm.tiles) * a.gn.tiles, sms));
+                const int grid = int(std::min<int64_t>(int64_t(a.gm.tiles) * a.gn.tiles * std::max(a.parts, 1), sms));
                 kernel<<<grid, kTfThreads, smem, stream>>>(mapA, mapB, C, D, a, idesc);
                 noteLaunch("contraction_tf32x3");
                 return cudaGetLastError();
@@ -896,7 +982,8 @@ namespace htb
     } // namespace
 
     cudaError_t launchContractionTf32x3(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
-                                        const void* C, void* D, int smCount, int* deviceStatus, cudaStream_t stream)
+                                        const void* C, void* D, void* workspace, uint64_t workspaceBytes, int smCount,
+                                        int* deviceStatus, cudaStream_t stream)
     {
         PFN_encodeTiled encode = tensorMapEncoder();
         if(!encode)
@@ -950,6 +1037,23 @@ namespace htb
                      a.gn.tiles, a.gn.rows, a.kBlocks, pair ? "CTA pairs" : "single CTAs");
         if(pair)
             return launchKernel<true, false>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream);
+        // K split, if the plan asks for it, the caller's workspace holds its scratch and every unit gets a CTA
+        a.parts = 1;
+        {
+            const int64_t tiles = int64_t(a.gm.tiles) * a.gn.tiles;
+            const int     parts = p.splitK;
+            const uint64_t need = 1024 + uint64_t(tiles) * uint64_t(std::max(parts, 1) - 1) * 128 * 128 * 4;
+            if(parts > 1 && workspace != nullptr && need <= workspaceBytes && (uintptr_t(workspace) & 15) == 0 && tiles <= 256
+               && tiles * parts <= sms && a.kBlocks >= 4 * parts && getenv("HTB_TF32_NOSPLIT") == nullptr)
+            {
+                a.parts = parts;
+                a.flags = (int*)workspace;
+                a.slots = (float*)((char*)workspace + 1024);
+                cudaError_t e = cudaMemsetAsync(workspace, 0, 1024, stream);
+                if(e != cudaSuccess)
+                    return e;
+            }
+        }
         // both operands K-major and no rounding: TMA loads straight into the operand ring
         const bool inplace = !p.aMajor && !p.bMajor && a.round == 0 && getenv("HTB_TF32_NOINPLACE") == nullptr;
         return inplace ? launchKernel<false, true>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream)

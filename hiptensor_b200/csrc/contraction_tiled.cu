@@ -29,7 +29,8 @@ namespace htb
                                          float beta, const void* C, void* D, void* workspace, uint64_t workspaceBytes,
                                          int smCount, int* deviceStatus, cudaStream_t stream);
     cudaError_t launchContractionTf32x3(const ContractionPlan& plan, float alpha, const void* A, const void* B, float beta,
-                                        const void* C, void* D, int smCount, int* deviceStatus, cudaStream_t stream);
+                                        const void* C, void* D, void* workspace, uint64_t workspaceBytes, int smCount,
+                                        int* deviceStatus, cudaStream_t stream);
 
     namespace
     {
@@ -588,7 +589,8 @@ namespace htb
         {
             const bool aligned = ((uintptr_t(A) | uintptr_t(B)) & 15) == 0;
             if(aligned)
-                return launchContractionTf32x3(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
+                return launchContractionTf32x3(plan, alpha, A, B, beta, C, D, workspace, workspaceBytes, smCount, deviceStatus,
+                                               stream);
         }
         const int ct = plan.computeType;
         switch(plan.typeA)

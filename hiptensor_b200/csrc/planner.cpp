@@ -647,6 +647,39 @@ namespace htb
                 out->rowsN128 = out->bMajor ? 64 : boxDecompose(gn, nn, 64, out->boxN128);
                 out->pair     = (tf && out->N >= 128 && out->rowsM == 128 && out->rowsN128 == 64 && out->M >= 256) ? 1 : 0;
             }
+            if(tf)
+            {
+                // Small problems: cut every tile into ranges of K blocks so that more SMs work (the per-CTA chain of K
+                // blocks, each paying the ring latency, is what bounds them). All work units must be resident at once.
+                int64_t tilesM = 1, tilesN = 1, kBlocks = (out->K + 31) / 32;
+                if(out->aMajor)
+                    tilesM = (((gm[0].ext + 31) / 32) * (out->M / gm[0].ext) + 3) / 4;
+                else
+                    for(int i = 0; i < nm; i++)
+                        tilesM *= (gm[i].ext + out->boxM[i] - 1) / out->boxM[i];
+                if(out->bMajor)
+                {
+                    const int64_t per = out->tileN / 32;
+                    tilesN            = (((gn[out->nFast].ext + 31) / 32) * (out->N / gn[out->nFast].ext) + per - 1) / per;
+                }
+                else
+                    for(int i = 0; i < nn; i++)
+                        tilesN *= (gn[i].ext + out->boxN[i] - 1) / out->boxN[i];
+                if(out->aMajor || out->bMajor)
+                {
+                    kBlocks = 1;
+                    for(int i = 0; i < nk; i++)
+                        kBlocks *= (gk[i].ext + out->boxK[i < 2 ? i : 1] - 1) / out->boxK[i < 2 ? i : 1];
+                }
+                const int64_t sms   = smCount > 0 ? smCount : 148;
+                const int64_t tiles = tilesM * tilesN;
+                int           parts = int(std::min<int64_t>(std::min<int64_t>(4, sms / std::max<int64_t>(tiles, 1)), kBlocks / 4));
+                if(parts >= 2)
+                {
+                    out->splitK         = parts;
+                    out->workspaceBytes = 1024 + uint64_t(tiles) * uint64_t(parts - 1) * 128 * 128 * 4;
+                }
+            }
             out->kind = tf ? CK_TF32X3 : CK_TILED_SIMT;
         }
         else

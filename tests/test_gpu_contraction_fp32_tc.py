@@ -161,3 +161,36 @@ def test_f32_data_with_half_precision_compute(env, compute, layout):
         assert not np.isnan(got).any()
         err = rel_error(got, exp, td)
         assert 0 <= err < 1e-5, (compute, layout, (M, N, K), err)
+
+
+@pytest.mark.parametrize("layout", sorted(LAYOUTS))
+def test_k_split_of_small_problems(env, layout):
+    """Few tiles and a long K: every tile is cut into K ranges (one CTA each), the partial sums travel through the
+    workspace and are added in a fixed order. With and without the workspace the results must both satisfy the
+    bounds; the split one must be reproducible bit for bit."""
+    ht, h = env
+    modeA, modeB = LAYOUTS[layout]
+    M, N, K = 256, 192, 1024
+    ext = {0: M, 1: N, 2: K}
+    lA, lB, lD = ([ext[m] for m in ms] for ms in (modeA, modeB, [0, 1]))
+    dA, dB, dD = (h.tensor_descriptor(l, None, ht.R_32F) for l in (lA, lB, lD))
+    cd = h.contraction_descriptor(dA, modeA, dB, modeB, dD, [0, 1], dD, [0, 1], ht.COMPUTE_32F)
+    find = h.contraction_find()
+    assert h.contraction_workspace_size(cd, find, ht.WORKSPACE_RECOMMENDED) > 0
+    assert h.contraction_workspace_size(cd, find, ht.WORKSPACE_MIN) == 0
+    first = None
+    for _ in range(2):
+        got, exp, td = run_contraction(ht, h, ext, modeA, modeB, [0, 1], typeAB=orc.F32, alpha=1.5, beta=0.5)
+        assert ht.last_kernel_name() == "contraction_tf32x3"
+        assert not np.isnan(got).any()
+        exact = exact_f64(ext, modeA, modeB, [0, 1], 1.5, 0.5, False)
+        check_f32(got, exp, exact, 2 * K)
+        if first is None:
+            first = got.copy()
+    assert np.array_equal(first.view(np.uint32), got.view(np.uint32))
+    os.environ["HTB_TF32_NOSPLIT"] = "1"
+    try:
+        whole, exp, td = run_contraction(ht, h, ext, modeA, modeB, [0, 1], typeAB=orc.F32, alpha=1.5, beta=0.5)
+    finally:
+        del os.environ["HTB_TF32_NOSPLIT"]
+    assert 0 <= rel_error(whole, first, orc.F32) < 1e-5
