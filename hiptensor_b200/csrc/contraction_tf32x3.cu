@@ -38,6 +38,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 #include "kernels.hpp"
@@ -84,7 +85,8 @@ namespace htb
             // (flag per tile), adds them in order and applies alpha/beta; parts 1.. write their sums and raise the flag.
             int      parts;
             float*   slots; // [tile][part - 1][128 rows][accumulator columns]
-            int*     flags; // one counter per tile, zeroed before the launch
+            int*     flags; // [tile][part - 1][epilogue warp]: the launch's epoch once that warp's rows are in the slot
+            int      epoch; // differs from launch to launch: stale flag words never match, nothing has to be zeroed
             int      round; // 0: big/small split (compute f32); 1 / 2: elements rounded to f16 / bf16, one MMA per K step
             int      probe; // measurement aid, bit mask: 1 = converter skips its work, 2 = issuer skips the MMAs,
                             // 8 = producer skips the loads (results invalid)
@@ -690,20 +692,24 @@ namespace htb
                             __threadfence();
                             __syncwarp();
                             if(lane == 0)
-                                atomicAdd(a.flags + tileIdx, 1);
+                            {
+                                int* flag = a.flags + (size_t(tileIdx) * (parts - 1) + (part - 1)) * kEpiWarps + (warp - 2);
+                                asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(a.epoch) : "memory");
+                            }
                         }
                         else
                         {
+                            // lane j watches the j-th of the (parts - 1) * 8 flag words of this tile
                             int ready = 1;
-                            if(lane == 0)
+                            if(lane < (parts - 1) * kEpiWarps)
                             {
-                                const int       want = (parts - 1) * kEpiWarps;
+                                const int*      flag = a.flags + size_t(tileIdx) * (parts - 1) * kEpiWarps + lane;
                                 const long long t0   = clock64();
                                 for(;;)
                                 {
                                     int seen;
-                                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(a.flags + tileIdx) : "memory");
-                                    if(seen >= want)
+                                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+                                    if(seen == a.epoch)
                                         break;
                                     if(*abortP || clock64() - t0 > kWaitCycles)
                                     {
@@ -713,7 +719,7 @@ namespace htb
                                     }
                                 }
                             }
-                            ready = __shfl_sync(0xffffffffu, ready, 0);
+                            ready = __all_sync(0xffffffffu, ready);
                             if(!ready)
                                 alive = false;
                             if(ready && active)
@@ -1042,16 +1048,18 @@ namespace htb
         {
             const int64_t tiles = int64_t(a.gm.tiles) * a.gn.tiles;
             const int     parts = p.splitK;
-            const uint64_t need = 1024 + uint64_t(tiles) * uint64_t(std::max(parts, 1) - 1) * 128 * 128 * 4;
+            constexpr uint64_t kFlagBytes = 32768; // 256 tiles x 3 parts x 8 warps x 4 bytes, rounded up
+            const uint64_t need = kFlagBytes + uint64_t(tiles) * uint64_t(std::max(parts, 1) - 1) * 128 * 128 * 4;
             if(parts > 1 && workspace != nullptr && need <= workspaceBytes && (uintptr_t(workspace) & 15) == 0 && tiles <= 256
                && tiles * parts <= sms && a.kBlocks >= 4 * parts && getenv("HTB_TF32_NOSPLIT") == nullptr)
             {
+                static std::atomic<int> launches{0};
                 a.parts = parts;
                 a.flags = (int*)workspace;
-                a.slots = (float*)((char*)workspace + 1024);
-                cudaError_t e = cudaMemsetAsync(workspace, 0, 1024, stream);
-                if(e != cudaSuccess)
-                    return e;
+                a.slots = (float*)((char*)workspace + kFlagBytes);
+                a.epoch = launches.fetch_add(1) + 1;
+                if(a.epoch == 0) // the value an untouched buffer is most likely to hold
+                    a.epoch = launches.fetch_add(1) + 1;
             }
         }
         // both operands K-major and no rounding: TMA loads straight into the operand ring

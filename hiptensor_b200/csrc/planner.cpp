@@ -677,7 +677,7 @@ namespace htb
                 if(parts >= 2)
                 {
                     out->splitK         = parts;
-                    out->workspaceBytes = 1024 + uint64_t(tiles) * uint64_t(parts - 1) * 128 * 128 * 4;
+                    out->workspaceBytes = 32768 + uint64_t(tiles) * uint64_t(parts - 1) * 128 * 128 * 4; // flags + slots
                 }
             }
             out->kind = tf ? CK_TF32X3 : CK_TILED_SIMT;
