@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5|c4f32|c2f16|c3col] [--impl reference]
 
 One step = one pass of the hot path over one batch of seeded synthetic input, called through the
-library's C ABI. The default workload is BASELINE configs[1] (c2): the fp32 rank-4 permutation
+library's C ABI. The default workload is the second of the five benchmark configurations (c2): the fp32 rank-4 permutation
 B[d,c,b,a] = A[a,b,c,d] with all extents 128 (1 GiB in, 1 GiB out), metric HBM GB/s.
 With N > 1 (launched by torch.distributed.run) every rank owns one slab of the sharded mode and
 runs the same problem on it; no data-path collective is involved ("scaling": "weak").
@@ -193,7 +193,7 @@ class PermutationC2(Workload):
 
 
 class PermutationC2F16(PermutationC2):
-    """Not a BASELINE config: config 2 with f16 elements (the generic shared-memory tile kernel)."""
+    """Not one of the five benchmark configurations: config 2 with f16 elements (the generic shared-memory tile kernel)."""
     name, dtype = "c2f16", "f16"
 
     def setup(self):
@@ -293,7 +293,7 @@ class ReductionC3(Workload):
 
 
 class ReductionC3Col(ReductionC3):
-    """Not a separate BASELINE config: config 3 with explicit first-mode-fastest strides (m contiguous), the
+    """Not a separate benchmark configuration: config 3 with explicit first-mode-fastest strides (m contiguous), the
     strided "column" reduction."""
     name = "c3col"
 
@@ -409,7 +409,7 @@ class ContractionC4(ContractionBase):
 
 
 class ContractionC4F32(ContractionBase):
-    """Not a BASELINE config: config 4's shape with fp32 operands, the large case of the fp32 tensor-core kernel."""
+    """Not one of the five benchmark configurations: config 4's shape with fp32 operands, the large case of the fp32 tensor-core kernel."""
     name, metric, dtype = "c4f32", "contraction_tflops", "f32 (TF32 big/small split, three MMAs per product)"
 
     def setup(self):

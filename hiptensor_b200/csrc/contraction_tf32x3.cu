@@ -122,7 +122,7 @@ namespace htb
         {
             return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
         }
-        // elements rounded to f16 (ROUND 1) or bf16 (ROUND 2) and widened again; no small part
+        // elements rounded to f16 (ROUND == 1) or bf16 (ROUND == 2) and widened again; no small part
         template <int ROUND>
         __device__ __forceinline__ float tfRound(float x)
         {

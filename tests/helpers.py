@@ -125,8 +125,9 @@ def check_f32(got, exp, exact, terms):
 
 def run_contraction(ht, h, extent, modeA, modeB, modeD, typeAB=orc.F32, typeD=None, compute=None, alpha=1.0,
                     beta=0.0, with_c=True, first_fastest=False, stridesA=None, stridesB=None, stridesD=None,
-                    fill="uniform", sample=None, seeds=SEED_CONTRACTION, algo=None):
-    """extent: dict mode -> extent. Returns (got, expected, typeD) as flat memory images of D."""
+                    fill="uniform", sample=None, seeds=SEED_CONTRACTION, algo=None, alias=False):
+    """extent: dict mode -> extent. Returns (got, expected, typeD) as flat memory images of D.
+    alias: C and D are the same device buffer (the reference's samples call it that way)."""
     typeD = typeAB if typeD is None else typeD
     if compute is None:
         compute = orc.COMPUTE_64F if typeAB == orc.F64 else orc.COMPUTE_32F
@@ -152,7 +153,7 @@ def run_contraction(ht, h, extent, modeA, modeB, modeD, typeAB=orc.F32, typeD=No
     plan = h.contraction_plan(cd, find, ws_size)
     A_d, B_d = to_device(A, typeAB), to_device(B, typeAB)
     C_d = to_device(C, typeD) if with_c else None
-    D_d = to_device(nan_like(nD, typeD), typeD)
+    D_d = C_d if (alias and with_c) else to_device(nan_like(nD, typeD), typeD)
     ws = None
     if ws_size:
         import torch

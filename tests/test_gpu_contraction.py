@@ -1,7 +1,7 @@
 """GPU parity: hiptensorContraction through the C ABI against the CPU oracle.
 
 Metric: the reference's max|d-h|/(|d|+|h|+1) (test/device/common.hpp:122-151).
-Tolerances (BASELINE north star): 1e-5 for fp32/fp64 accumulation, 1e-2 for f16/bf16 inputs;
+Tolerances: 1e-5 for fp32/fp64 accumulation, 1e-2 for f16/bf16 inputs;
 next to them the reference's own bound 2*K*eps (+2*2^-10 f16, +2*2^-7 bf16 outputs),
 test/01_contraction/contraction_test.cpp:882-905, is checked where it is the stricter one.
 Mode lists and extents of the shuffled cases are those of
@@ -361,3 +361,22 @@ def test_cta_pair_kernel_half_tiles_in_last_wave(env, layout):
     finally:
         del os.environ["HTB_TC_NOHALF"]
     assert np.array_equal(got.view(np.uint32), whole.view(np.uint32))
+
+
+@pytest.mark.parametrize("case", ["f16_single", "f16_pair", "f32_tensor", "f32_fma", "f64"])
+def test_c_may_alias_d(env, case):
+    """D = alpha*A*B + beta*C with C and D the same buffer, as the reference's sample calls it
+    (samples/01_contraction/simple_bilinear_contraction.hpp:270-271): every kernel family reads an element of C
+    before the same thread overwrites it."""
+    ht, h = env
+    shapes = {"f16_single": (orc.F16, orc.F32, (256, 320, 96), "contraction_tcgen05"),
+              "f16_pair": (orc.F16, orc.F32, (640, 768, 136), "contraction_tcgen05_pair"),
+              "f32_tensor": (orc.F32, orc.F32, (256, 192, 96), "contraction_tf32x3"),
+              "f32_fma": (orc.F32, orc.F32, (70, 50, 33), "contraction_tiled_simt"),
+              "f64": (orc.F64, orc.F64, (96, 80, 40), "contraction_tiled_dmma")}
+    dt, td, (M, N, K), kernel = shapes[case]
+    got, exp, tdo = run_contraction(ht, h, {0: M, 1: N, 2: K}, [0, 2], [1, 2], [0, 1], typeAB=dt, typeD=td, alpha=1.5,
+                                    beta=0.5, fill="normal" if dt == orc.F16 else "uniform", alias=True)
+    assert ht.last_kernel_name() == kernel
+    err = rel_error(got, exp, tdo)
+    assert 0 <= err < (1e-4 if dt == orc.F16 else 1e-5), (case, err)
