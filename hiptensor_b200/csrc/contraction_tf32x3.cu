@@ -19,8 +19,12 @@
 //   converter      8 warps, two threads per tile row (16 k each): read from staging (conflict-free in
 //                  both orders), split, write the big and the small half row into the K-major,
 //                  128-byte-swizzled operand ring;
-//   tcgen05.mma    three MMAs per 8-wide K step from the ring into the accumulator;
-//   epilogue       tcgen05.ld, alpha/beta, stores to the strided D.
+//   tcgen05.mma    three MMAs per 8-wide K step from the ring: the main product into a segment accumulator that
+//                  the epilogue drains every 64 K elements, the two correction products into their own;
+//   epilogue       tcgen05.ld, running sums in registers, alpha/beta, stores to the strided D.
+// When both operands are K-major the staging step is skipped (INPLACE): TMA writes into the ring's big tiles and
+// the converter only adds the small ones. Small problems are cut along K over several CTAs (parts), with the
+// partial sums exchanged through the caller's workspace.
 //
 // Warp roles (576 threads): 0 TMA producer, 1 MMA issuer + tensor-memory owner, 2-9 epilogue (two warps
 // per tensor-memory lane quadrant, 64 columns each), 10-17 converter. PAIR = true runs a 256 x 128 tile
