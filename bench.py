@@ -122,6 +122,38 @@ class Workload:
     def units_per_step(self):  # bytes (hbm) or flops (tensor) one step processes on this rank
         raise NotImplementedError
 
+    # End-to-end pieces. h2d() and d2h() enqueue the copies of one step on the current torch stream and return
+    # the bytes moved; twin() gives a second buffer set (own device tensors and host result, shared pinned inputs)
+    # so that consecutive steps can overlap.
+    DEVICE_BUFFERS = ()
+    HOST_RESULTS = ()
+
+    def h2d(self):
+        raise NotImplementedError
+
+    def d2h(self):
+        raise NotImplementedError
+
+    def twin(self):
+        import copy
+        import torch
+        t = copy.copy(self)
+        for name in self.DEVICE_BUFFERS:
+            v = getattr(self, name)
+            setattr(t, name, None if v is None else torch.empty_like(v))
+        for name in self.HOST_RESULTS:
+            v = getattr(self, name)
+            setattr(t, name, torch.empty_like(v).pin_memory())
+        return t
+
+    def e2e_step(self, stream):
+        import torch
+        with torch.cuda.stream(stream):
+            nin = self.h2d()
+            self.step(stream)
+            nout = self.d2h()
+        return nin, nout
+
     def host_inputs(self):  # list of pinned host tensors that feed the step
         raise NotImplementedError
 
@@ -167,11 +199,16 @@ class PermutationC2(Workload):
     def units_per_step(self):
         return self.bytes
 
-    def e2e_step(self, stream):
+    DEVICE_BUFFERS = ("A", "B")
+    HOST_RESULTS = ("B_host",)
+
+    def h2d(self):
         self.A.copy_(self.A_host, non_blocking=True)
-        self.step(stream)
+        return self.A_host.numel() * self.A_host.element_size()
+
+    def d2h(self):
         self.B_host.copy_(self.B, non_blocking=True)
-        return self.A_host.numel() * 4, self.B_host.numel() * 4
+        return self.B_host.numel() * self.B_host.element_size()
 
     def config(self):
         return {"workload": "c2: fp32 permutation B[d,c,b,a]=A[a,b,c,d], extents 128, 1 GiB in + 1 GiB out per GPU",
@@ -210,12 +247,6 @@ class PermutationC2F16(PermutationC2):
 
     def step(self, stream):
         self.h.permutation(1.0, self.A, self.desc, [0, 1, 2, 3], self.B, self.desc, [3, 2, 1, 0], self.ht.R_16F, stream)
-
-    def e2e_step(self, stream):
-        self.A.copy_(self.A_host, non_blocking=True)
-        self.step(stream)
-        self.B_host.copy_(self.B, non_blocking=True)
-        return self.A_host.numel() * 2, self.B_host.numel() * 2
 
     def config(self):
         return {"workload": "c2f16: f16 permutation B[d,c,b,a]=A[a,b,c,d], extents 128, 512 MiB in + 512 MiB out per GPU",
@@ -264,12 +295,17 @@ class ReductionC3(Workload):
     def units_per_step(self):
         return self.bytes
 
-    def e2e_step(self, stream):
+    DEVICE_BUFFERS = ("A", "C", "D")
+    HOST_RESULTS = ("D_host",)
+
+    def h2d(self):
         self.A.copy_(self.A_host, non_blocking=True)
         self.C.copy_(self.C_host, non_blocking=True)
-        self.step(stream)
+        return (self.A_host.numel() + self.C_host.numel()) * 4
+
+    def d2h(self):
         self.D_host.copy_(self.D, non_blocking=True)
-        return (self.A_host.numel() + self.C_host.numel()) * 4, self.D_host.numel() * 4
+        return self.D_host.numel() * 4
 
     def config(self):
         return {"workload": "c3: fp32 reduction A[4096,64,64,32] over {k,h} -> D[4096,64] = 1.0*sum + 0.5*C (ADD), "
@@ -362,16 +398,21 @@ class ContractionBase(Workload):
     def units_per_step(self):
         return self.flops
 
-    def e2e_step(self, stream):
+    DEVICE_BUFFERS = ("A", "B", "C", "D", "ws")
+    HOST_RESULTS = ("D_host",)
+
+    def h2d(self):
         self.A.copy_(self.A_host, non_blocking=True)
         self.B.copy_(self.B_host, non_blocking=True)
         nb = self.A_host.numel() * self.A_host.element_size() + self.B_host.numel() * self.B_host.element_size()
         if self.C is not None:
             self.C.copy_(self.C_host, non_blocking=True)
             nb += self.C_host.numel() * self.C_host.element_size()
-        self.step(stream)
+        return nb
+
+    def d2h(self):
         self.D_host.copy_(self.D, non_blocking=True)
-        return nb, self.D_host.numel() * self.D_host.element_size()
+        return self.D_host.numel() * self.D_host.element_size()
 
 
 class ContractionC4(ContractionBase):
@@ -591,15 +632,39 @@ def run_gpu(args):
     scale = 1e9 if wl.bound == "hbm" else 1e12
     value = units / (ms_max / 1e3) / scale
 
-    # ---- end to end: pinned host buffers, H2D of the inputs and D2H of the result inside the region
-    e2e_steps = max(1, min(args.steps, 5))
-    wl.e2e_step(stream)
+    # ---- end to end: pinned host buffers, H2D of the inputs and D2H of the result of EVERY step inside the region.
+    # Two buffer sets and three streams let the copy-in of step i+1, the kernel of step i and the copy-out of step
+    # i-1 overlap (PCIe is full duplex), as an application streaming batches through the library would run it.
+    e2e_steps = max(2, min(args.steps, 8))
+    sets = [wl, wl.twin()]
+    for w in sets:
+        w.e2e_step(stream)
     barrier()
+    s_in, s_cmp, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_cmp, ev_out = [None, None], [None, None]
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record(stream)
-    for _ in range(e2e_steps):
-        h2d, d2h = wl.e2e_step(stream)
-    e.record(stream)
+    s.record(s_in)
+    for i in range(e2e_steps):
+        j = i % 2
+        w = sets[j]
+        if ev_cmp[j] is not None:
+            s_in.wait_event(ev_cmp[j])  # the set's inputs are free once its previous kernel has run
+        with torch.cuda.stream(s_in):
+            h2d = w.h2d()
+        ev_in = torch.cuda.Event()
+        ev_in.record(s_in)
+        s_cmp.wait_event(ev_in)
+        if ev_out[j] is not None:
+            s_cmp.wait_event(ev_out[j])  # its result buffer is free once the previous copy-out is done
+        w.step(s_cmp)
+        ev_cmp[j] = torch.cuda.Event()
+        ev_cmp[j].record(s_cmp)
+        s_out.wait_event(ev_cmp[j])
+        with torch.cuda.stream(s_out):
+            d2h = w.d2h()
+        ev_out[j] = torch.cuda.Event()
+        ev_out[j].record(s_out)
+    e.record(s_out)  # the last copy-out ends the region
     torch.cuda.synchronize()
     t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -635,7 +700,8 @@ def run_gpu(args):
             "cpu_baseline": {"value": round(cpu_value, 4), "unit": wl.unit, "cores": ncores, "kind": "port",
                              "sample": sample},
             "e2e": {"value": round(e2e_value, 3), "unit": wl.unit, "h2d_bytes_per_step": int(h2d),
-                    "d2h_bytes_per_step": int(d2h), "steps": e2e_steps},
+                    "d2h_bytes_per_step": int(d2h), "steps": e2e_steps,
+                    "overlap": "two buffer sets, three streams: copy-in, kernel and copy-out of consecutive steps overlap"},
             "gpu_launches": int(launches), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

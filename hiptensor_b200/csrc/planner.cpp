@@ -732,6 +732,11 @@ namespace htb
             }
             s += p.pair ? "] pair" : "]";
         }
+        if(p.splitK > 1)
+        {
+            snprintf(buf, sizeof(buf), " splitK=%d workspace=%lld", p.splitK, (long long)p.workspaceBytes);
+            s += buf;
+        }
         return s;
     }
 } // namespace htb

@@ -118,6 +118,30 @@ def test_contraction_fp32_tensor_core_layouts(ht):
     assert "kind=tf32x3" in plan([K, M], [2, 0], [K, N], [2, 1], [M, N], [0, 1], ht.COMPUTE_16BF)
 
 
+def test_contraction_k_split_plans(ht):
+    """Few tiles and a long K: the fp32 tensor-core plan cuts K into up to four ranges (at least four K blocks
+    each, never more CTAs than SMs) and asks for 32 KiB of flags plus one 128 x 128 fp32 slot per extra range
+    and tile; many tiles or a short K do not split. The f16 plan asks for tail-split workspace only when the
+    tile count leaves a tail of CTA pairs."""
+    import re
+
+    def plan(M, N, K, t):
+        return ht.describe_contraction_plan([M, K], [K, 1], [0, 2], t, [N, K], [K, 1], [1, 2], t, [M, N], [N, 1],
+                                            [0, 1], t, True, ht.COMPUTE_32F)
+
+    d = plan(256, 192, 1024, ht.R_32F)  # 2 x 3 tiles of 128 x 64, 32 K blocks
+    m = re.search(r"splitK=(\d+) workspace=(\d+)", d)
+    assert "kind=tf32x3" in d and m, d
+    assert int(m.group(1)) == 4 and int(m.group(2)) == 32768 + 6 * 3 * 128 * 128 * 4
+    d = plan(576, 576, 576, ht.R_32F)  # 5 x 9 tiles of 128 x 64: three ranges fit the SM count
+    m = re.search(r"splitK=(\d+)", d)
+    assert m and int(m.group(1)) == 3, d
+    assert "splitK" not in plan(256, 192, 96, ht.R_32F)  # too few K blocks
+    assert "splitK" not in plan(4096, 4096, 1024, ht.R_32F)  # enough tiles for every SM
+    # f16: one wave of 256 x 256 tiles has nothing to split; a few tiles more than a wave have a tail
+    assert "splitK" not in plan(256, 256, 4096, ht.R_16F)
+
+
 def test_contraction_config4(ht):
     e = 64
     s = packed([e] * 4, False)
