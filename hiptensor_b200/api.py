@@ -12,8 +12,8 @@ from . import _lib
 
 __all__ = [
     "HiptensorError", "Handle", "TensorDescriptor",
-    "R_32F", "R_64F", "R_16F", "R_16BF",
-    "COMPUTE_16F", "COMPUTE_32F", "COMPUTE_64F", "COMPUTE_16BF",
+    "R_32F", "R_64F", "R_16F", "R_16BF", "C_32F", "C_64F",
+    "COMPUTE_16F", "COMPUTE_32F", "COMPUTE_64F", "COMPUTE_16BF", "COMPUTE_C32F", "COMPUTE_C64F",
     "OP_IDENTITY", "OP_SQRT", "OP_ADD", "OP_MUL", "OP_MAX", "OP_MIN",
     "ALGO_DEFAULT", "ALGO_DEFAULT_PATIENT", "ALGO_ACTOR_CRITIC",
     "WORKSPACE_MIN", "WORKSPACE_RECOMMENDED", "WORKSPACE_MAX",
@@ -26,8 +26,10 @@ __all__ = [
 
 # hipDataType (hiptensor_types.hpp uses hipDataType; values equal cudaDataType)
 R_32F, R_64F, R_16F, R_16BF = 0, 1, 2, 14
+C_32F, C_64F = 4, 5
 # hiptensorComputeType_t (hiptensor_types.hpp:74-99)
 COMPUTE_16F, COMPUTE_32F, COMPUTE_64F, COMPUTE_16BF = 1, 4, 16, 1024
+COMPUTE_C32F, COMPUTE_C64F = 2048, 4096
 # hiptensorOperator_t (hiptensor_types.hpp:102-124)
 OP_IDENTITY, OP_SQRT, OP_ADD, OP_MUL, OP_MAX, OP_MIN = 1, 2, 3, 5, 6, 7
 # hiptensorAlgo_t (hiptensor_types.hpp:127-136)
@@ -39,7 +41,7 @@ STATUS_SUCCESS, STATUS_NOT_INITIALIZED, STATUS_INVALID_VALUE, STATUS_ARCH_MISMAT
 STATUS_INTERNAL_ERROR, STATUS_NOT_SUPPORTED, STATUS_HIP_ERROR, STATUS_INSUFFICIENT_WORKSPACE = 14, 15, 18, 19
 STATUS_EXECUTION_FAILED = 13
 
-_DTYPE_SIZE = {R_32F: 4, R_64F: 8, R_16F: 2, R_16BF: 2}
+_DTYPE_SIZE = {R_32F: 4, R_64F: 8, R_16F: 2, R_16BF: 2, C_32F: 8, C_64F: 16}
 
 
 def dtype_size(dt):
@@ -84,6 +86,12 @@ def _scalar_for_compute(value, compute_type):
         return ctypes.create_string_buffer(struct.pack("<e", float(value)), 8)
     if compute_type == COMPUTE_16BF:
         return ctypes.create_string_buffer(struct.pack("<H", _f32_to_bf16_bits(value)), 8)
+    if compute_type == COMPUTE_C32F:  # hipFloatComplex
+        v = complex(value)
+        return ctypes.create_string_buffer(struct.pack("<ff", v.real, v.imag), 8)
+    if compute_type == COMPUTE_C64F:  # hipDoubleComplex
+        v = complex(value)
+        return ctypes.create_string_buffer(struct.pack("<dd", v.real, v.imag), 16)
     raise HiptensorError(STATUS_NOT_SUPPORTED, "scalar conversion")
 
 

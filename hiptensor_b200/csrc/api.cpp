@@ -92,9 +92,12 @@ namespace
     {
         if(desc->mTensorDesc.size() != 4 || desc->mTensorMode.size() < 3)
             return HIPTENSOR_STATUS_INVALID_VALUE;
-        const bool bilinear = (desc->mContractionOpId == 1);
-        if(desc->mContractionOpId != 0 && desc->mContractionOpId != 1)
-            return HIPTENSOR_STATUS_NOT_SUPPORTED; // complex forms are outside this library
+        // operation ids: 0 scale, 1 bilinear, 2 / 3 the same with complex compute types
+        // (hiptensor_contraction.cpp:161-188)
+        const bool bilinear = (desc->mContractionOpId & 1) != 0;
+        const bool cplx     = desc->mContractionOpId >= 2;
+        if(desc->mContractionOpId < 0 || desc->mContractionOpId > 3)
+            return HIPTENSOR_STATUS_NOT_SUPPORTED;
         auto lA = toI64(desc->mTensorDesc[0].mLengths), sA = toI64(desc->mTensorDesc[0].mStrides);
         auto lB = toI64(desc->mTensorDesc[1].mLengths), sB = toI64(desc->mTensorDesc[1].mStrides);
         // D is described by descriptor 3 and the mode list stored at index 2
@@ -109,6 +112,9 @@ namespace
         TensorView A{int(lA.size()), lA.data(), sA.data(), mA.data(), int(desc->mTensorDesc[0].mType)};
         TensorView B{int(lB.size()), lB.data(), sB.data(), mB.data(), int(desc->mTensorDesc[1].mType)};
         TensorView D{int(lD.size()), lD.data(), sD.data(), mD.data(), int(desc->mTensorDesc[3].mType)};
+        if(cplx)
+            return planComplexContraction(A, B, D, int(desc->mTensorDesc[2].mType), bilinear, int(desc->mComputeType),
+                                          smCount, out);
         return planContraction(A, B, D, int(desc->mTensorDesc[2].mType), bilinear, int(desc->mComputeType), smCount,
                                out);
     }
@@ -666,11 +672,11 @@ hiptensorStatus_t hiptensorContractionGetWorkspaceSize(const hiptensorHandle_t* 
     *workspaceSize = 0;
     ContractionPlan    plan;
     const HandleState* st = stateOf(handle);
-    // every kernel runs without scratch (WORKSPACE_MIN = 0); the recommended size lets the
-    // tensor-core kernel split the tiles of its last wave along K
-    if(pref != HIPTENSOR_WORKSPACE_MIN
-       && buildContractionPlan(desc, st ? st->smCount : 148, &plan) == HIPTENSOR_STATUS_SUCCESS)
-        *workspaceSize = plan.workspaceBytes;
+    // every real kernel runs without scratch (WORKSPACE_MIN = 0); the recommended size lets the
+    // tensor-core kernels split tiles along K. Complex contractions need room for the expanded copy
+    // of their smaller operand at every preference.
+    if(buildContractionPlan(desc, st ? st->smCount : 148, &plan) == HIPTENSOR_STATUS_SUCCESS)
+        *workspaceSize = plan.expandBytes + (pref != HIPTENSOR_WORKSPACE_MIN ? plan.workspaceBytes : 0);
     return HIPTENSOR_STATUS_SUCCESS;
 }
 
@@ -702,7 +708,7 @@ hiptensorStatus_t hiptensorInitContractionPlan(const hiptensorHandle_t* handle, 
         HTB_LOG_ERROR(fn, "No kernel can run this contraction (%s)", hiptensorGetErrorString(hiptensorStatus_t(rc)));
         return hiptensorStatus_t(rc);
     }
-    if(cp.workspaceBytes > workspaceSize)
+    if(cp.expandBytes + cp.workspaceBytes > workspaceSize)
         cp.workspaceBytes = 0; // planned for the workspace the caller said it has: no split
     HTB_LOG_HEUR(fn, "%s", describe(cp).c_str());
     plan->mSolution        = const_cast<ContractionPlan*>(registry().intern(cp));
@@ -743,19 +749,47 @@ hiptensorStatus_t hiptensorContraction(const hiptensorHandle_t* handle, const hi
     if(auto s = checkDevice(fn, st); s != HIPTENSOR_STATUS_SUCCESS)
         return s;
     const ContractionPlan* cp = static_cast<const ContractionPlan*>(plan->mSolution);
-    if(cp->workspaceBytes > workspaceSize || (cp->workspaceBytes > 0 && workspace == nullptr))
+    const uint64_t needBytes = cp->expandBytes + cp->workspaceBytes;
+    if(needBytes > workspaceSize || (needBytes > 0 && workspace == nullptr))
     {
-        HTB_LOG_ERROR(fn, "Insufficient workspace: req: %llu alloc: %llu (%s)", (unsigned long long)cp->workspaceBytes,
+        HTB_LOG_ERROR(fn, "Insufficient workspace: req: %llu alloc: %llu (%s)", (unsigned long long)needBytes,
                       (unsigned long long)workspaceSize,
                       hiptensorGetErrorString(HIPTENSOR_STATUS_INSUFFICIENT_WORKSPACE));
         return HIPTENSOR_STATUS_INSUFFICIENT_WORKSPACE;
     }
     // alpha/beta are typed by the compute type and held as float by the epilogue
     // (contraction_solution_impl.hpp:110-123)
+    const bool bilinear = cp->bilinear != 0;
+    if(cp->complexKind)
+    {
+        // alpha / beta point to hipFloatComplex / hipDoubleComplex (data_types.cpp:187-196)
+        const bool c32 = cp->typeD == CUDA_R_32F;
+        double     al[2], be[2] = {0, 0};
+        if(bilinear && (!beta || !C))
+        {
+            HTB_LOG_ERROR(fn, "Input Parameter Error : beta/C = nullptr for a bilinear contraction (%s)",
+                          hiptensorGetErrorString(HIPTENSOR_STATUS_INVALID_VALUE));
+            return HIPTENSOR_STATUS_INVALID_VALUE;
+        }
+        for(int i = 0; i < 2; i++)
+        {
+            al[i] = c32 ? double(((const float*)alpha)[i]) : ((const double*)alpha)[i];
+            if(bilinear)
+                be[i] = c32 ? double(((const float*)beta)[i]) : ((const double*)beta)[i];
+        }
+        cudaError_t e = launchComplexContraction(*cp, al[0], al[1], A, B, be[0], be[1], bilinear ? C : nullptr, D,
+                                                 workspace, needBytes, st->smCount, st->deviceStatus, stream);
+        if(e != cudaSuccess)
+        {
+            HTB_LOG_ERROR(fn, "kernel launch failed: %s (%s)", cudaGetErrorString(e),
+                          hiptensorGetErrorString(HIPTENSOR_STATUS_HIP_ERROR));
+            return HIPTENSOR_STATUS_HIP_ERROR;
+        }
+        return HIPTENSOR_STATUS_SUCCESS;
+    }
     double alphaD = 0, betaD = 0;
     if(!readScalar(alpha, cp->computeType, &alphaD))
         return HIPTENSOR_STATUS_NOT_SUPPORTED;
-    const bool bilinear = cp->bilinear != 0;
     if(bilinear)
     {
         if(!beta || !C)

@@ -275,7 +275,9 @@ int htDescribeContractionPlan(uint32_t numModesA, const int64_t* lensA, const in
     htb::TensorView      B{int(numModesB), lensB, stridesB, modeB, dataTypeB};
     htb::TensorView      D{int(numModesD), lensD, stridesD, modeD, dataTypeD};
     htb::ContractionPlan p;
-    int rc = htb::planContraction(A, B, D, dataTypeD, hasC != 0, typeCompute, 148, &p);
+    const bool cplx = typeCompute == HIPTENSOR_COMPUTE_C32F || typeCompute == HIPTENSOR_COMPUTE_C64F;
+    int        rc   = cplx ? htb::planComplexContraction(A, B, D, dataTypeD, hasC != 0, typeCompute, 148, &p)
+                           : htb::planContraction(A, B, D, dataTypeD, hasC != 0, typeCompute, 148, &p);
     if(rc != htb::PLAN_OK)
         return rc;
     return copyOut(htb::describe(p), buf, bufSize);

@@ -48,6 +48,13 @@ namespace htb
                                   float beta, const void* C, void* D, void* workspace, uint64_t workspaceBytes,
                                   int smCount, int* deviceStatus, cudaStream_t stream);
 
+    // Complex plans (plan.complexKind != 0): alpha and beta as (re, im); the first plan.expandBytes of the
+    // workspace are required, plan.workspaceBytes more are optional.
+    cudaError_t launchComplexContraction(const ContractionPlan& plan, double alphaRe, double alphaIm, const void* A,
+                                         const void* B, double betaRe, double betaIm, const void* C, void* D,
+                                         void* workspace, uint64_t workspaceBytes, int smCount, int* deviceStatus,
+                                         cudaStream_t stream);
+
     // Function attributes (dynamic shared-memory limit) belong to one device: true the first time the calling
     // site is reached with the current device, so that a process that drives several GPUs sets them on each.
     inline bool firstUseOnDevice(unsigned char (&seen)[kMaxDevices])

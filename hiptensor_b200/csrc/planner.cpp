@@ -362,12 +362,29 @@ namespace htb
     }
 
     // ------------------------------------------------------------------ contraction
+    namespace
+    {
+        // two more modes than the interface allows: the real view of a complex tensor has one mode more, its
+        // expanded copy two (planComplexContraction)
+        constexpr int kPlanRank = kMaxRank + 2;
+        int planReal(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
+                     int computeType, int smCount, int rankLimit, ContractionPlan* out);
+    } // namespace
+
     int planContraction(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
                         int computeType, int smCount, ContractionPlan* out)
     {
+        return planReal(A, B, D, typeC, bilinear, computeType, smCount, kMaxRank, out);
+    }
+
+    namespace
+    {
+    int planReal(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
+                 int computeType, int smCount, int rankLimit, ContractionPlan* out)
+    {
         std::memset(out, 0, sizeof(*out));
-        if(A.rank < 1 || B.rank < 1 || D.rank < 1 || A.rank > kMaxRank || B.rank > kMaxRank
-           || D.rank > kMaxRank)
+        if(A.rank < 1 || B.rank < 1 || D.rank < 1 || A.rank > rankLimit || B.rank > rankLimit
+           || D.rank > rankLimit)
             return PLAN_INVALID;
         if(hasDuplicates(A.modes, A.rank) || hasDuplicates(B.modes, B.rank) || hasDuplicates(D.modes, D.rank))
             return PLAN_INVALID;
@@ -392,7 +409,7 @@ namespace htb
         if(!ok)
             return PLAN_NOT_SUPPORTED;
 
-        ModeDim gm[kMaxRank], gn[kMaxRank], gk[kMaxRank];
+        ModeDim gm[kPlanRank], gn[kPlanRank], gk[kPlanRank];
         int     nm = 0, nn = 0, nk = 0;
         for(int i = 0; i < D.rank; i++)
         {
@@ -439,9 +456,6 @@ namespace htb
             if(findMode(A.modes, A.rank, B.modes[i]) < 0 && findMode(D.modes, D.rank, B.modes[i]) < 0)
                 return PLAN_INVALID;
         }
-        if(nm > kMaxGroup || nn > kMaxGroup || nk > kMaxGroup)
-            return PLAN_NOT_SUPPORTED;
-
         // ---- make D contiguous along N when it is contiguous along some M mode
         int64_t minM = INT64_MAX, minN = INT64_MAX;
         for(int i = 0; i < nm; i++)
@@ -453,7 +467,7 @@ namespace htb
         out->swapped = (minM < minN) ? 1 : 0;
         if(out->swapped)
         {
-            std::swap_ranges(gm, gm + kMaxRank, gn);
+            std::swap_ranges(gm, gm + kPlanRank, gn);
             std::swap(nm, nn);
             for(int i = 0; i < nk; i++)
                 std::swap(gk[i].s0, gk[i].s1);
@@ -472,6 +486,8 @@ namespace htb
         nm = foldGroup(gm, nm);
         nn = foldGroup(gn, nn);
         nk = foldGroup(gk, nk);
+        if(nm > kMaxGroup || nn > kMaxGroup || nk > kMaxGroup)
+            return PLAN_NOT_SUPPORTED; // the reference's limit of six modes per group, applied after folding
         out->nm = nm;
         out->nn = nn;
         out->nk = nk;
@@ -689,11 +705,164 @@ namespace htb
         (void)smCount;
         return PLAN_OK;
     }
+    } // namespace
+
+    // Complex contraction as ONE real contraction. A complex tensor is, in memory, a real tensor with one more
+    // mode c of extent 2 and stride 1 (all other strides doubled). With Y the operand that stays in place and X
+    // the one that is copied,
+    //   Re D = sum_k Yr Xr - Yi Xi      Im D = sum_k Yr Xi + Yi Xr
+    // is the real contraction D'[.., cOut] = sum_{k, cK} Y'[.., k, cK] * X2[.., cOut, k, cK] with
+    //   X2[.., 0, k, :] = (Xr, -Xi)     X2[.., 1, k, :] = (Xi, Xr),
+    // i.e. M*2N*2K real multiply-adds, the same count as the four real contractions of the reference
+    // (device_contraction_bilinear_complex.hpp:454-470), on the real tensor-core kernels, with no
+    // split of Y or D into real and imaginary planes. X2 is packed: free modes of X (slowest, ordered by
+    // their stride in D), cOut, the contracted modes (ordered by their stride in Y), cK (fastest).
+    int planComplexContraction(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
+                               int computeType, int smCount, ContractionPlan* out)
+    {
+        std::memset(out, 0, sizeof(*out));
+        if(A.rank < 1 || B.rank < 1 || D.rank < 1 || A.rank > kMaxRank || B.rank > kMaxRank || D.rank > kMaxRank)
+            return PLAN_INVALID;
+        if(hasDuplicates(A.modes, A.rank) || hasDuplicates(B.modes, B.rank) || hasDuplicates(D.modes, D.rank))
+            return PLAN_INVALID;
+        // reference tuples: cf32 with compute C32F, cf64 with compute C64F
+        // (contraction_solution_instances.cpp:108-121,152-165,240-253,284-297)
+        const bool c32 = A.type == CUDA_C_32F && computeType == 2048, c64 = A.type == CUDA_C_64F && computeType == 4096;
+        if(!(c32 || c64) || B.type != A.type || D.type != A.type || (bilinear && typeC != A.type))
+            return PLAN_NOT_SUPPORTED;
+        const int realType = c32 ? CUDA_R_32F : CUDA_R_64F, realSize = c32 ? 4 : 8;
+        int64_t   nA = 1, nB = 1;
+        for(int i = 0; i < A.rank; i++)
+            nA *= A.lens[i];
+        for(int i = 0; i < B.rank; i++)
+            nB *= B.lens[i];
+        if(nA <= 0 || nB <= 0)
+            return PLAN_INVALID;
+        const bool        expandA = nA < nB; // copy the smaller operand
+        const TensorView& X = expandA ? A : B;
+        const TensorView& Y = expandA ? B : A;
+
+        // two mode labels that no tensor uses
+        int32_t fresh[2];
+        {
+            int32_t cand = 0x40000000;
+            for(int f = 0; f < 2; f++, cand++)
+            {
+                while(findMode(A.modes, A.rank, cand) >= 0 || findMode(B.modes, B.rank, cand) >= 0
+                      || findMode(D.modes, D.rank, cand) >= 0)
+                    cand++;
+                fresh[f] = cand;
+            }
+        }
+        const int32_t cK = fresh[0], cOut = fresh[1];
+
+        // X's modes in the copy's order: free modes by descending stride in D, then contracted modes by
+        // descending stride in Y
+        struct XMode
+        {
+            int     pos; // position in X
+            int64_t key; // stride in D (free) or in Y (contracted)
+        };
+        XMode freeM[kMaxRank], conM[kMaxRank];
+        int   nFree = 0, nCon = 0;
+        for(int i = 0; i < X.rank; i++)
+        {
+            if(X.lens[i] <= 0)
+                return PLAN_INVALID;
+            const int iy = findMode(Y.modes, Y.rank, X.modes[i]);
+            const int id = findMode(D.modes, D.rank, X.modes[i]);
+            if(iy >= 0 && id >= 0)
+                return PLAN_NOT_SUPPORTED; // batch mode
+            if(iy >= 0)
+                conM[nCon++] = XMode{i, Y.strides[iy]};
+            else if(id >= 0)
+                freeM[nFree++] = XMode{i, D.strides[id]};
+            else
+                return PLAN_INVALID;
+        }
+        auto byKey = [](const XMode& a, const XMode& b) { return a.key > b.key; };
+        std::stable_sort(freeM, freeM + nFree, byKey);
+        std::stable_sort(conM, conM + nCon, byKey);
+
+        int64_t lX[kPlanRank], sX[kPlanRank], lY[kPlanRank], sY[kPlanRank], lD[kPlanRank], sD[kPlanRank];
+        int32_t mX[kPlanRank], mY[kPlanRank], mD[kPlanRank];
+        int     r = 0;
+        for(int i = 0; i < nFree; i++, r++)
+        {
+            lX[r] = X.lens[freeM[i].pos];
+            mX[r] = X.modes[freeM[i].pos];
+        }
+        lX[r]   = 2;
+        mX[r++] = cOut;
+        for(int i = 0; i < nCon; i++, r++)
+        {
+            lX[r] = X.lens[conM[i].pos];
+            mX[r] = X.modes[conM[i].pos];
+        }
+        lX[r]   = 2;
+        mX[r++] = cK;
+        const int rankX2 = r;
+        sX[rankX2 - 1]   = 1;
+        for(int i = rankX2 - 2; i >= 0; i--)
+            sX[i] = sX[i + 1] * lX[i + 1];
+        for(int i = 0; i < Y.rank; i++)
+        {
+            lY[i] = Y.lens[i];
+            sY[i] = 2 * Y.strides[i];
+            mY[i] = Y.modes[i];
+        }
+        lY[Y.rank] = 2;
+        sY[Y.rank] = 1;
+        mY[Y.rank] = cK;
+        for(int i = 0; i < D.rank; i++)
+        {
+            lD[i] = D.lens[i];
+            sD[i] = 2 * D.strides[i];
+            mD[i] = D.modes[i];
+        }
+        lD[D.rank] = 2;
+        sD[D.rank] = 1;
+        mD[D.rank] = cOut;
+        const TensorView X2{rankX2, lX, sX, mX, realType}, Y2{Y.rank + 1, lY, sY, mY, realType},
+            D2{D.rank + 1, lD, sD, mD, realType};
+        const int rc = planReal(expandA ? X2 : Y2, expandA ? Y2 : X2, D2, realType, bilinear, c32 ? 4 : 16, smCount,
+                                kPlanRank, out);
+        if(rc != PLAN_OK)
+            return rc;
+        out->complexKind = expandA ? 1 : 2;
+        out->xRank       = nFree + nCon;
+        out->xFree       = nFree;
+        for(int i = 0; i < nFree; i++)
+        {
+            out->xExt[i]    = X.lens[freeM[i].pos];
+            out->xStride[i] = X.strides[freeM[i].pos];
+        }
+        for(int i = 0; i < nCon; i++)
+        {
+            out->xExt[nFree + i]    = X.lens[conM[i].pos];
+            out->xStride[nFree + i] = X.strides[conM[i].pos];
+        }
+        out->dRank = D.rank;
+        for(int i = 0; i < D.rank; i++)
+        {
+            out->dExt[i]    = D.lens[i];
+            out->dStride[i] = D.strides[i];
+        }
+        const uint64_t bytes = uint64_t(expandA ? nA : nB) * 4u * uint64_t(realSize);
+        out->expandBytes     = (bytes + 255u) & ~uint64_t(255);
+        return PLAN_OK;
+    }
 
     std::string describe(const ContractionPlan& p)
     {
         static const char* kinds[] = {"tiled_simt", "tiled_dmma", "tcgen05", "tf32x3"};
-        std::string        s       = "contraction kind=";
+        std::string        s       = p.complexKind ? "complex contraction (copy of " : "contraction kind=";
+        if(p.complexKind)
+        {
+            char cb[96];
+            snprintf(cb, sizeof(cb), "%s: %lld bytes) kind=", p.complexKind == 1 ? "A" : "B", (long long)p.expandBytes);
+            s += cb;
+        }
         s += kinds[p.kind];
         char buf[192];
         snprintf(buf, sizeof(buf), " M=%lld N=%lld K=%lld types=%s,%s,%s->%s compute=%d swapped=%d ",

@@ -118,6 +118,15 @@ namespace htb
         // split of the K range over several CTAs (needs workspace); 1 = none
         int      splitK;
         uint64_t workspaceBytes;
+        // Complex contraction run as one real contraction (planComplexContraction); the fields above then
+        // describe the real problem. 0: real; 1 / 2: operand A / B is replaced by its expanded real copy, which
+        // occupies the first expandBytes of the workspace (required), followed by workspaceBytes (optional).
+        int      complexKind;
+        int      xRank, xFree; // modes of the copied operand in the copy's order: xFree free modes, then contracted
+        int      dRank;
+        int64_t  xExt[kMaxRank], xStride[kMaxRank]; // extents and source strides (complex elements)
+        int64_t  dExt[kMaxRank], dStride[kMaxRank]; // D's modes (complex elements), for the beta pass over C
+        uint64_t expandBytes;
     };
 
     struct TensorView
@@ -133,6 +142,9 @@ namespace htb
     // present, is addressed with D's strides (contraction_solution_impl.hpp:125-140).
     int planContraction(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
                         int computeType, int smCount, ContractionPlan* out);
+    // cf32 / cf64 tensors with compute type C32F / C64F: see planner.cpp
+    int planComplexContraction(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
+                               int computeType, int smCount, ContractionPlan* out);
     std::string describe(const ContractionPlan& p);
 
     // K split of the CTA-pair contraction kernel: when `tiles` output tiles fill less than half of the

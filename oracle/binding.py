@@ -127,6 +127,26 @@ def contraction(alpha, A, lenA, strA, modeA, typeA, B, lenB, strB, modeB, typeB,
     return D
 
 
+C32F, C64F = 4, 5
+COMPUTE_C32F, COMPUTE_C64F = 2048, 4096
+
+
+def contraction_complex(alpha, A, lenA, strA, modeA, B, lenB, strB, modeB, beta, C, D, lenD, strD, modeD, dtype,
+                        nthreads=0):
+    """Complex contraction by the reference's CPU algorithm; A, B, C, D are numpy complex64 / complex128
+    arrays (dtype C32F / C64F), alpha and beta Python complex numbers."""
+    ct = np.complex64 if dtype == C32F else np.complex128
+    a = np.array([alpha], dtype=ct)
+    b = np.array([beta], dtype=ct)
+    rc = lib().orc_contraction_complex(
+        _ptr(a), _ptr(A), len(lenA), _i64(lenA), _i64(strA), _i32(modeA),
+        _ptr(B), len(lenB), _i64(lenB), _i64(strB), _i32(modeB),
+        _ptr(b), _ptr(C), _ptr(D), len(lenD), _i64(lenD), _i64(strD), _i32(modeD), int(dtype), int(nthreads))
+    if rc != 0:
+        raise RuntimeError("oracle complex contraction rejected the problem (code %d)" % rc)
+    return D
+
+
 def permutation(alpha, type_scalar, A, lenA, modeA, typeA, B, modeB, typeB, opA=OP_IDENTITY, opB=OP_IDENTITY,
                 nthreads=1):
     a = np.array([alpha], dtype=np.float32 if type_scalar == F32 else np.float16)

@@ -15,7 +15,8 @@
 //                 vendored; floor version composable_kernel 1.0.0,
 //                 library/src/CMakeLists.txt:27).
 //   contraction : parity unpinned (the reference holds no golden vector;
-//                 its tests only compare its GPU path with its CPU path).
+//                 its tests only compare its GPU path with its CPU path);
+//                 the same holds for the complex form.
 //
 // Every function cites the reference file:line whose behaviour it restates.
 // No reference source is copied: loop structure is re-expressed with
@@ -476,6 +477,99 @@ int orc_contraction(const void* alphaP, const void* A, int nA, const int64_t* le
             }
         }
     });
+    return 0;
+}
+
+// Complex contraction oracle (cf32: typeCode 4, cf64: typeCode 5; alpha/beta point to two floats / two doubles).
+//   contraction_cpu_reference_impl.hpp:166-323 : acc = (0,0); for k0..k5: acc = acc + a*b with the complex
+//       product (ar*br - ai*bi, ai*br + ar*bi) evaluated in the accumulator type (float for cf32, double for
+//       cf64: contraction_cpu_reference_instances.cpp:108-121,152-165); BilinearComplex:
+//       E = alpha*acc + beta*D, ScaleComplex: E = alpha*acc, complex products in the element type with alpha,
+//       beta narrowed to it.
+//   Parity unpinned: the reference holds no golden vector for complex contractions either.
+int orc_contraction_complex(const void* alphaP, const void* A, int nA, const int64_t* lenA, const int64_t* strA,
+                            const int32_t* modeA, const void* B, int nB, const int64_t* lenB, const int64_t* strB,
+                            const int32_t* modeB, const void* betaP, const void* C, void* D, int nD,
+                            const int64_t* lenD, const int64_t* strD, const int32_t* modeD, int typeCode, int nthreads)
+{
+    if(typeCode != 4 && typeCode != 5)
+        return 3;
+    ModeGroup gm, gn, gk;
+    for(int i = 0; i < nD; i++)
+    {
+        int ia = find_mode(modeA, nA, modeD[i]);
+        if(ia >= 0)
+        {
+            gm.len.push_back(lenA[ia]);
+            gm.s0.push_back(strA[ia]);
+            gm.s1.push_back(strD[i]);
+        }
+        else
+        {
+            int ib = find_mode(modeB, nB, modeD[i]);
+            if(ib < 0)
+                return 1;
+            gn.len.push_back(lenB[ib]);
+            gn.s0.push_back(strB[ib]);
+            gn.s1.push_back(strD[i]);
+        }
+    }
+    for(int i = 0; i < nA; i++)
+    {
+        int ib = find_mode(modeB, nB, modeA[i]);
+        if(ib >= 0)
+        {
+            if(find_mode(modeD, nD, modeA[i]) >= 0)
+                return 2;
+            gk.len.push_back(lenA[i]);
+            gk.s0.push_back(strA[i]);
+            gk.s1.push_back(strB[ib]);
+        }
+    }
+    std::vector<int64_t> aM, dM, bN, dN, aK, bK;
+    enumerate(gm, aM, dM);
+    enumerate(gn, bN, dN);
+    enumerate(gk, aK, bK);
+    const int64_t M = gm.total(), N = gn.total(), K = gk.total();
+    const bool    bilinear = (C != nullptr);
+    auto run = [&](auto zero) {
+        using T        = decltype(zero);
+        const T*  a    = (const T*)A;
+        const T*  b    = (const T*)B;
+        const T*  c    = (const T*)C;
+        T*        d    = (T*)D;
+        const T   ar = ((const T*)alphaP)[0], ai = ((const T*)alphaP)[1];
+        const T   br = (bilinear && betaP) ? ((const T*)betaP)[0] : T(0), bi = (bilinear && betaP) ? ((const T*)betaP)[1] : T(0);
+        parallel_for(M * N, nthreads, [&](int64_t lo, int64_t hi) {
+            for(int64_t t = lo; t < hi; t++)
+            {
+                const int64_t m = t / N, n = t % N;
+                const int64_t oa = aM[m], ob = bN[n], od = dM[m] + dN[n];
+                T             sr = 0, si = 0;
+                for(int64_t k = 0; k < K; k++)
+                {
+                    const T xr = a[2 * (oa + aK[k])], xi = a[2 * (oa + aK[k]) + 1];
+                    const T yr = b[2 * (ob + bK[k])], yi = b[2 * (ob + bK[k]) + 1];
+                    const T pr = xr * yr - xi * yi, pi = xi * yr + xr * yi;
+                    sr = sr + pr;
+                    si = si + pi;
+                }
+                T er = ar * sr - ai * si, ei = ai * sr + ar * si;
+                if(bilinear)
+                {
+                    const T cr = c[2 * od], ci = c[2 * od + 1];
+                    er = er + (br * cr - bi * ci);
+                    ei = ei + (bi * cr + br * ci);
+                }
+                d[2 * od]     = er;
+                d[2 * od + 1] = ei;
+            }
+        });
+    };
+    if(typeCode == 4)
+        run(0.0f);
+    else
+        run(0.0);
     return 0;
 }
 
