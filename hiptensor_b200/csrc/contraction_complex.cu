@@ -11,7 +11,8 @@
 // alpha is applied during the copy. beta * C is either the real epilogue of the contraction kernel (beta real)
 // or a pass D = beta * C before it (the kernel then adds D to the sums: C may alias D in every kernel).
 // The real kernels are the FP64 tensor-pipe kernel for cf64 and the TF32 big/small split kernel (or the FMA
-// kernel) for cf32, so accuracy is that of the real paths.
+// kernel) for cf32, so accuracy is that of the real paths. For cf32 the other operand is copied as well (packed,
+// contracted modes innermost) when its layout would otherwise keep the problem off the tensor cores.
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -42,8 +43,8 @@ namespace htb
         };
 
         // One thread per complex element of X, contracted index fastest (the copy's rows are written contiguously;
-        // the reads follow X's strides).
-        template <typename T>
+        // the reads follow X's strides). PLAIN: a packed copy of the elements as they are (one row per free index).
+        template <typename T, bool PLAIN>
         __global__ void __launch_bounds__(256) complex_expand_kernel(const typename Vec2<T>::type* __restrict__ X,
                                                                      typename Vec2<T>::type* __restrict__ X2, CxDims d,
                                                                      int64_t F, int64_t K, T ar, T ai, int unitAlpha)
@@ -66,6 +67,11 @@ namespace htb
                     rem /= d.ext[m];
                 }
                 const V x = X[off];
+                if(PLAIN)
+                {
+                    X2[i] = x;
+                    continue;
+                }
                 T       pr = x.x, pi = x.y;
                 if(!unitAlpha)
                 {
@@ -128,11 +134,33 @@ namespace htb
             const int64_t total = F * K;
             int           grid  = int(std::min<int64_t>((total + 255) / 256, int64_t(sms) * 8));
             const int     unit  = (ar == 1.0 && ai == 0.0) ? 1 : 0;
-            complex_expand_kernel<T><<<grid, 256, 0, stream>>>((const V*)X, (V*)X2, d, F, K, T(ar), T(ai), unit);
+            complex_expand_kernel<T, false><<<grid, 256, 0, stream>>>((const V*)X, (V*)X2, d, F, K, T(ar), T(ai), unit);
             cudaError_t e = cudaGetLastError();
             if(e != cudaSuccess)
                 return e;
             noteLaunch("complex_expand");
+            const void* Y = (p.complexKind == 1) ? B : A;
+            if(p.yCopy)
+            {
+                CxDims dy{};
+                dy.rank  = p.yRank;
+                dy.nFree = p.yFree;
+                int64_t FY = 1, KY = 1;
+                for(int i = 0; i < p.yRank; i++)
+                {
+                    dy.ext[i]    = p.yExt[i];
+                    dy.stride[i] = p.yStride[i];
+                    (i < p.yFree ? FY : KY) *= p.yExt[i];
+                }
+                void* Y2 = (char*)workspace + p.yOffset;
+                grid     = int(std::min<int64_t>((FY * KY + 255) / 256, int64_t(sms) * 8));
+                complex_expand_kernel<T, true><<<grid, 256, 0, stream>>>((const V*)Y, (V*)Y2, dy, FY, KY, T(0), T(0), 1);
+                e = cudaGetLastError();
+                if(e != cudaSuccess)
+                    return e;
+                noteLaunch("complex_copy");
+                Y = Y2;
+            }
 
             const bool bilinear = p.bilinear != 0 && C != nullptr;
             float      betaReal = 0.f;
@@ -177,7 +205,7 @@ namespace htb
             }
             void*          inner      = p.workspaceBytes ? (char*)workspace + p.expandBytes : nullptr;
             const uint64_t innerBytes = workspaceBytes > p.expandBytes ? workspaceBytes - p.expandBytes : 0;
-            return launchContraction(p, 1.0f, p.complexKind == 1 ? X2 : A, p.complexKind == 1 ? B : X2, betaReal, Cin, D,
+            return launchContraction(p, 1.0f, p.complexKind == 1 ? X2 : Y, p.complexKind == 1 ? Y : X2, betaReal, Cin, D,
                                      inner, std::min<uint64_t>(innerBytes, p.workspaceBytes), smCount, deviceStatus, stream);
         }
     } // namespace

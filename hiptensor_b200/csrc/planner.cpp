@@ -784,6 +784,23 @@ namespace htb
         std::stable_sort(freeM, freeM + nFree, byKey);
         std::stable_sort(conM, conM + nCon, byKey);
 
+        // Y's modes for a packed copy: free modes by descending stride in D, contracted modes in the order of X2's
+        XMode yFreeM[kMaxRank];
+        int   nYFree = 0;
+        for(int i = 0; i < Y.rank; i++)
+        {
+            if(Y.lens[i] <= 0)
+                return PLAN_INVALID;
+            if(findMode(X.modes, X.rank, Y.modes[i]) >= 0)
+                continue;
+            const int id = findMode(D.modes, D.rank, Y.modes[i]);
+            if(id < 0)
+                return PLAN_INVALID;
+            yFreeM[nYFree++] = XMode{i, D.strides[id]};
+        }
+        std::stable_sort(yFreeM, yFreeM + nYFree, byKey);
+
+        auto planWith = [&](bool copyY) -> int {
         int64_t lX[kPlanRank], sX[kPlanRank], lY[kPlanRank], sY[kPlanRank], lD[kPlanRank], sD[kPlanRank];
         int32_t mX[kPlanRank], mY[kPlanRank], mD[kPlanRank];
         int     r = 0;
@@ -805,14 +822,35 @@ namespace htb
         sX[rankX2 - 1]   = 1;
         for(int i = rankX2 - 2; i >= 0; i--)
             sX[i] = sX[i + 1] * lX[i + 1];
-        for(int i = 0; i < Y.rank; i++)
+        int posY[kMaxRank]; // Y's modes in the copy's order
+        if(copyY)
         {
-            lY[i] = Y.lens[i];
-            sY[i] = 2 * Y.strides[i];
-            mY[i] = Y.modes[i];
+            int q = 0;
+            for(int i = 0; i < nYFree; i++)
+                posY[q++] = yFreeM[i].pos;
+            for(int i = 0; i < nCon; i++)
+                posY[q++] = findMode(Y.modes, Y.rank, X.modes[conM[i].pos]);
+            for(int i = 0; i < Y.rank; i++)
+            {
+                lY[i] = Y.lens[posY[i]];
+                mY[i] = Y.modes[posY[i]];
+            }
+            sY[Y.rank] = 1;
+            sY[Y.rank - 1] = 2;
+            for(int i = Y.rank - 2; i >= 0; i--)
+                sY[i] = sY[i + 1] * lY[i + 1];
+        }
+        else
+        {
+            for(int i = 0; i < Y.rank; i++)
+            {
+                lY[i] = Y.lens[i];
+                sY[i] = 2 * Y.strides[i];
+                mY[i] = Y.modes[i];
+            }
+            sY[Y.rank] = 1;
         }
         lY[Y.rank] = 2;
-        sY[Y.rank] = 1;
         mY[Y.rank] = cK;
         for(int i = 0; i < D.rank; i++)
         {
@@ -850,6 +888,39 @@ namespace htb
         }
         const uint64_t bytes = uint64_t(expandA ? nA : nB) * 4u * uint64_t(realSize);
         out->expandBytes     = (bytes + 255u) & ~uint64_t(255);
+        if(copyY)
+        {
+            out->yCopy   = 1;
+            out->yRank   = Y.rank;
+            out->yFree   = nYFree;
+            out->yOffset = out->expandBytes;
+            for(int i = 0; i < Y.rank; i++)
+            {
+                out->yExt[i]    = Y.lens[posY[i]];
+                out->yStride[i] = Y.strides[posY[i]];
+            }
+            const uint64_t bytesY = uint64_t(expandA ? nB : nA) * 2u * uint64_t(realSize);
+            out->expandBytes += (bytesY + 255u) & ~uint64_t(255);
+        }
+        return PLAN_OK;
+        };
+
+        int rc = planWith(false);
+        if(rc != PLAN_OK)
+            return rc;
+        if(c32 && out->kind != CK_TF32X3)
+        {
+            // Y as it lies is neither K-major nor MN-major in its real view (e.g. first-mode-fastest strides: the
+            // (re, im) pairs sit between consecutive rows). A packed copy with the contracted modes innermost
+            // costs one pass over Y and puts the problem on the tensor cores.
+            ContractionPlan alt;
+            ContractionPlan* const keep = out;
+            out                         = &alt;
+            const int rc2               = planWith(true);
+            out                         = keep;
+            if(rc2 == PLAN_OK && alt.kind == CK_TF32X3)
+                *out = alt;
+        }
         return PLAN_OK;
     }
 
@@ -860,7 +931,8 @@ namespace htb
         if(p.complexKind)
         {
             char cb[96];
-            snprintf(cb, sizeof(cb), "%s: %lld bytes) kind=", p.complexKind == 1 ? "A" : "B", (long long)p.expandBytes);
+            snprintf(cb, sizeof(cb), "%s: %lld bytes) kind=", p.yCopy ? "A and B" : (p.complexKind == 1 ? "A" : "B"),
+                     (long long)p.expandBytes);
             s += cb;
         }
         s += kinds[p.kind];

@@ -127,6 +127,11 @@ namespace htb
         int64_t  xExt[kMaxRank], xStride[kMaxRank]; // extents and source strides (complex elements)
         int64_t  dExt[kMaxRank], dStride[kMaxRank]; // D's modes (complex elements), for the beta pass over C
         uint64_t expandBytes;
+        // cf32 only: the other operand is copied too (plain, contracted modes innermost) when the tensor-core
+        // kernel cannot read it where it lies; its copy follows the first one at byte offset yOffset
+        int      yCopy, yRank, yFree;
+        int64_t  yExt[kMaxRank], yStride[kMaxRank];
+        uint64_t yOffset;
     };
 
     struct TensorView

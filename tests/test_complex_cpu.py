@@ -73,6 +73,13 @@ def test_planner_rewrites_complex_as_one_real_contraction(ht):
     d = ht.describe_contraction_plan(*args, ht.C_32F, lB, packed(lB), [2, 3, 4, 5], ht.C_32F, lD, packed(lD),
                                      [0, 1, 2, 3], ht.C_32F, False, ht.COMPUTE_C32F)
     assert "copy of B: %d bytes" % (nB * 16) in d and "kind=tf32x3" in d and "M=9216 N=768 K=2048" in d, d
+    # first mode fastest: the in-place operand's real view has no stride-1 row or K mode, so cf32 copies both
+    d = ht.describe_contraction_plan(lA, packed(lA, True), [0, 1, 4, 5], ht.C_32F, lB, packed(lB, True), [2, 3, 4, 5],
+                                     ht.C_32F, lD, packed(lD, True), [0, 1, 2, 3], ht.C_32F, False, ht.COMPUTE_C32F)
+    assert "copy of A and B: %d bytes" % (nB * 16 + int(np.prod(lA)) * 8) in d and "kind=tf32x3" in d, d
+    d = ht.describe_contraction_plan(lA, packed(lA, True), [0, 1, 4, 5], ht.C_64F, lB, packed(lB, True), [2, 3, 4, 5],
+                                     ht.C_64F, lD, packed(lD, True), [0, 1, 2, 3], ht.C_64F, False, ht.COMPUTE_C64F)
+    assert "copy of B:" in d and "kind=tiled_dmma" in d, d
     # the smaller operand is the one copied
     d = ht.describe_contraction_plan(lB, packed(lB), [2, 3, 4, 5], ht.C_32F, lA, packed(lA), [0, 1, 4, 5], ht.C_32F,
                                      lD, packed(lD), [0, 1, 2, 3], ht.C_32F, False, ht.COMPUTE_C32F)

@@ -10,7 +10,7 @@ Shapes, alphas and betas are those the reference's harness sweeps
 (test/01_contraction/configs/validation/complex_{bilinear,scale}_test_params_rank{1..6}.yaml), plus larger
 problems that reach the tensor-core kernels. Tolerances: the reference accepts 2*K*eps(float) under
 max|d-h|/(|d|+|h|+1) for both precisions (contraction_test.cpp:882-905); here cf32 is held to that bound
-against the oracle and to 1e-5 against the fp64 evaluation of the same values, cf64 to 1e-12."""
+against the oracle and to 2e-5 against the fp64 evaluation of the same values, cf64 to 1e-12."""
 import numpy as np
 import pytest
 
@@ -82,7 +82,9 @@ def run(env, ext, modeA, modeB, modeD, dtype, alpha, beta, with_c=True, first_fa
                                 B.astype(np.complex128), lB, sB, modeB, complex(np.complex64(beta)),
                                 C.astype(np.complex128) if with_c else None, exact, lD, sD, modeD, orc.C64F)
         err2 = rel_error(g.astype(np.float64), exact.view(np.float64), orc.F64)
-        assert 0 <= err2 < 1e-5, ("vs exact", err2)
+        # twice the bound of the real fp32 tests: a complex output accumulates two sums of K products each,
+        # of magnitude up to 2 for inputs in [-1, 1)
+        assert 0 <= err2 < 2e-5, ("vs exact", err2)
     return ht.last_kernel_name()
 
 
@@ -138,18 +140,26 @@ def test_real_beta_uses_the_kernel_epilogue_and_alias(env, dtype):
 @pytest.mark.parametrize("first_fastest", [False, True])
 def test_cf32_on_the_tensor_cores(env, first_fastest):
     """Extents that give 16-byte aligned strides: the real problem runs on the TF32 big/small split kernel with
-    fp32-grade accuracy, whether the contracted modes are innermost (NULL strides) or outermost."""
+    fp32-grade accuracy. With the contracted modes innermost (NULL strides) the larger operand is read where it
+    lies; with the first mode fastest its real view is neither K-major nor M-major (the (re, im) pairs sit between
+    consecutive rows), so it is copied too."""
     ext = {0: 16, 1: 24, 2: 12, 3: 16, 4: 8, 5: 12}
     name = run(env, ext, [0, 1, 4, 5], [2, 3, 4, 5], [0, 1, 2, 3], orc.C32F, 1.1 + 1.2j, 2.2 + 2.3j,
                first_fastest=first_fastest)
     assert name.startswith("contraction_tf32x3"), name
+    ht = env[0]
+    n0 = ht.kernel_launch_count()
+    run(env, ext, [0, 1, 4, 5], [2, 3, 4, 5], [0, 1, 2, 3], orc.C32F, 1.0 + 0j, 0j, with_c=False,
+        first_fastest=first_fastest)
+    assert ht.kernel_launch_count() - n0 == (3 if first_fastest else 2)
 
 
 def test_cf64_on_the_fp64_tensor_pipe_and_operand_choice(env):
     """The smaller operand is the one copied, whichever side it is on; interleaved mode orders."""
     ext = {0: 12, 1: 10, 2: 6, 3: 14, 4: 9, 5: 7}
     assert run(env, ext, [0, 4, 1, 5], [5, 2, 4, 3], [0, 2, 1, 3], orc.C64F, 2 + 0.5j, 0.5 - 1j) == "contraction_tiled_dmma"
-    big = dict(ext, **{2: 30, 3: 28})  # now A is the smaller one
+    big = dict(ext)
+    big.update({2: 30, 3: 28})  # now A is the smaller one
     assert run(env, big, [0, 4, 1, 5], [5, 2, 4, 3], [3, 0, 2, 1], orc.C64F, 2 + 0.5j, 0.5 - 1j) == "contraction_tiled_dmma"
 
 
