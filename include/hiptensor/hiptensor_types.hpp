@@ -13,11 +13,15 @@
 #include <cstdio>
 #include <vector>
 
+#include <cuComplex.h>
 #include <cuda_runtime_api.h>
 #include <library_types.h>
 
 using hipDataType = cudaDataType;
 using hipStream_t = cudaStream_t;
+// element types of HIP_C_32F / HIP_C_64F tensors and of their alpha / beta (hip/hip_complex.h in the reference)
+using hipFloatComplex  = cuFloatComplex;
+using hipDoubleComplex = cuDoubleComplex;
 #define HIP_R_16F CUDA_R_16F
 #define HIP_R_16BF CUDA_R_16BF
 #define HIP_R_32F CUDA_R_32F

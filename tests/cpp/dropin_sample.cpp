@@ -1,5 +1,5 @@
 // A caller written against the reference's C++ API (hiptensor.hpp), compiled unchanged against this
-// library's header: permutation, reduction and a bilinear contraction, following the call sequences of
+// library's header: permutation, reduction, a bilinear contraction and a complex one, following the call sequences of
 // samples/02_permutation/permutation.cpp:107-130, samples/03_reduction/reduction.cpp:116-171 and
 // samples/01_contraction/simple_bilinear_contraction.hpp:86-271 of the reference. Each result is checked
 // on the host with plain loops. Prints "DROPIN OK" and returns 0 on success.
@@ -172,6 +172,66 @@ int main()
         if(worst > 1e-5)
         {
             printf("contraction mismatch %g\n", worst);
+            return 1;
+        }
+        cudaFree(dA);
+        cudaFree(dB);
+        cudaFree(dC);
+        if(work)
+            cudaFree(work);
+    }
+
+    // ---------------------------------------------------------------- complex: C[m,u] = (1.1+1.2i) * A[m,h,k]*B[u,h,k] + (2.2+2.3i) * C
+    {
+        std::vector<int32_t> modeC{'m', 'u'}, modeA{'m', 'h', 'k'}, modeB{'u', 'h', 'k'};
+        std::vector<int64_t> extA{7, 3, 4}, extB{5, 3, 4}, extC{7, 5};
+        const size_t         nA = 7 * 3 * 4, nB = 5 * 3 * 4, nC = 7 * 5;
+        std::vector<hipDoubleComplex> A(nA), B(nB), C(nC), D(nC);
+        for(auto& v : A)
+            v = make_cuDoubleComplex(frand(), frand());
+        for(auto& v : B)
+            v = make_cuDoubleComplex(frand(), frand());
+        for(auto& v : C)
+            v = make_cuDoubleComplex(frand(), frand());
+        hipDoubleComplex *dA, *dB, *dC;
+        CHECK_CUDA(cudaMalloc(&dA, nA * 16));
+        CHECK_CUDA(cudaMalloc(&dB, nB * 16));
+        CHECK_CUDA(cudaMalloc(&dC, nC * 16));
+        CHECK_CUDA(cudaMemcpy(dA, A.data(), nA * 16, cudaMemcpyHostToDevice));
+        CHECK_CUDA(cudaMemcpy(dB, B.data(), nB * 16, cudaMemcpyHostToDevice));
+        CHECK_CUDA(cudaMemcpy(dC, C.data(), nC * 16, cudaMemcpyHostToDevice));
+        hiptensorTensorDescriptor_t descA, descB, descC;
+        CHECK_HT(hiptensorInitTensorDescriptor(handle, &descA, 3, extA.data(), NULL, HIP_C_64F, HIPTENSOR_OP_IDENTITY));
+        CHECK_HT(hiptensorInitTensorDescriptor(handle, &descB, 3, extB.data(), NULL, HIP_C_64F, HIPTENSOR_OP_IDENTITY));
+        CHECK_HT(hiptensorInitTensorDescriptor(handle, &descC, 2, extC.data(), NULL, HIP_C_64F, HIPTENSOR_OP_IDENTITY));
+        hiptensorContractionDescriptor_t desc;
+        CHECK_HT(hiptensorInitContractionDescriptor(handle, &desc, &descA, modeA.data(), 16, &descB, modeB.data(), 16, &descC,
+                                                    modeC.data(), 16, &descC, modeC.data(), 16, HIPTENSOR_COMPUTE_C64F));
+        hiptensorContractionFind_t find;
+        CHECK_HT(hiptensorInitContractionFind(handle, &find, HIPTENSOR_ALGO_DEFAULT));
+        uint64_t worksize = 0;
+        CHECK_HT(hiptensorContractionGetWorkspaceSize(handle, &desc, &find, HIPTENSOR_WORKSPACE_RECOMMENDED, &worksize));
+        void* work = nullptr;
+        if(worksize > 0)
+            CHECK_CUDA(cudaMalloc(&work, worksize));
+        hiptensorContractionPlan_t plan;
+        CHECK_HT(hiptensorInitContractionPlan(handle, &plan, &desc, &find, worksize));
+        const hipDoubleComplex alpha = make_cuDoubleComplex(1.1, 1.2), beta = make_cuDoubleComplex(2.2, 2.3);
+        CHECK_HT(hiptensorContraction(handle, &plan, &alpha, dA, dB, &beta, dC, dC, work, worksize, 0));
+        CHECK_CUDA(cudaMemcpy(D.data(), dC, nC * 16, cudaMemcpyDeviceToHost));
+        double worst = 0;
+        for(int m = 0; m < 7; m++)
+            for(int u = 0; u < 5; u++)
+            {
+                hipDoubleComplex acc = make_cuDoubleComplex(0, 0);
+                for(int hk = 0; hk < 12; hk++)
+                    acc = cuCadd(acc, cuCmul(A[m * 12 + hk], B[u * 12 + hk]));
+                const hipDoubleComplex ref = cuCadd(cuCmul(alpha, acc), cuCmul(beta, C[m * 5 + u]));
+                worst = std::fmax(worst, cuCabs(cuCsub(ref, D[m * 5 + u])));
+            }
+        if(worst > 1e-12)
+        {
+            printf("complex contraction mismatch %g\n", worst);
             return 1;
         }
         cudaFree(dA);
