@@ -22,6 +22,7 @@
 #include <cstdlib>
 
 #include "kernels.hpp"
+#include "tcgen05_util.cuh"
 
 namespace htb
 {
@@ -324,172 +325,6 @@ namespace htb
             }
         }
 
-        // ------------------------------------------------------------------ FP64 tensor-pipe kernel
-        // 128 x 64 output tile per CTA, 8 warps in a 4 x 2 grid, each warp a 32 x 32 tile made of
-        // 4 x 4 mma.sync.m8n8k4.f64 fragments (16 MMAs for 8 shared-memory loads per 4-wide K step).
-        // Operands are gathered exactly as in the kernel above; shared tiles are [k][m + 4] so that
-        // the fragment loads of a half warp fall on 16 different 8-byte banks.
-        constexpr int DM = 128, DN = 64;
-
-        template <int DK>
-        __global__ void __launch_bounds__(THREADS)
-            contraction_dmma_kernel(const double* __restrict__ A, const double* __restrict__ B, const double* C,
-                                    double* D, CtrArgs a)
-        {
-            extern __shared__ __align__(16) unsigned char dsmem[];
-            double(*sA)[DK][DM + PAD] = reinterpret_cast<double(*)[DK][DM + PAD]>(dsmem);
-            double(*sB)[DK][DN + PAD] = reinterpret_cast<double(*)[DK][DN + PAD]>(dsmem + sizeof(double) * 2 * DK * (DM + PAD));
-            __shared__ int64_t offAm[DM], offDm[DM], offBn[DN], offDn[DN];
-            __shared__ int64_t offAk[2][DK], offBk[2][DK];
-
-            const int     tid   = threadIdx.x;
-            const int64_t tileM = blockIdx.x / a.tilesN, tileN = blockIdx.x % a.tilesN;
-            const int64_t m0 = tileM * DM, n0 = tileN * DN;
-
-            if(tid < DM)
-            {
-                const int64_t mm = m0 + tid;
-                int64_t       oa = -1, od = -1;
-                if(mm < a.M)
-                    decompose2(a.m, a.nm, mm, oa, od);
-                offAm[tid] = oa;
-                offDm[tid] = od;
-            }
-            else if(tid < DM + DN)
-            {
-                const int     t  = tid - DM;
-                const int64_t nn = n0 + t;
-                int64_t       ob = -1, od = -1;
-                if(nn < a.N)
-                    decompose2(a.n, a.nn, nn, ob, od);
-                offBn[t] = ob;
-                offDn[t] = od;
-            }
-            auto computeK = [&](int buf, int64_t k0) {
-                if(tid >= DM + DN && tid < DM + DN + DK)
-                {
-                    const int     t  = tid - DM - DN;
-                    const int64_t kk = k0 + t;
-                    int64_t       oa = -1, ob = -1;
-                    if(kk < a.K)
-                        decompose2(a.k, a.nk, kk, oa, ob);
-                    offAk[buf][t] = oa;
-                    offBk[buf][t] = ob;
-                }
-            };
-            computeK(0, 0);
-            __syncthreads();
-
-            constexpr int EA = DM * DK / THREADS, EB = DN * DK / THREADS; // elements per thread and tile
-            double        ra[EA], rb[EB];
-            auto          gload = [&](int buf) {
-#pragma unroll
-                for(int j = 0; j < EA; j++)
-                {
-                    const int idx = tid + THREADS * j;
-                    const int mi  = a.aKfast ? idx / DK : idx % DM;
-                    const int ki  = a.aKfast ? idx % DK : idx / DM;
-                    const int64_t om = offAm[mi], ok = offAk[buf][ki];
-                    ra[j] = (om >= 0 && ok >= 0) ? A[om + ok] : 0.0;
-                }
-#pragma unroll
-                for(int j = 0; j < EB; j++)
-                {
-                    const int idx = tid + THREADS * j;
-                    const int ni  = a.bKfast ? idx / DK : idx % DN;
-                    const int ki  = a.bKfast ? idx % DK : idx / DN;
-                    const int64_t on = offBn[ni], ok = offBk[buf][ki];
-                    rb[j] = (on >= 0 && ok >= 0) ? B[on + ok] : 0.0;
-                }
-            };
-            auto sstore = [&](int buf) {
-#pragma unroll
-                for(int j = 0; j < EA; j++)
-                {
-                    const int idx = tid + THREADS * j;
-                    if(a.aKfast)
-                        sA[buf][idx % DK][idx / DK] = ra[j];
-                    else
-                        sA[buf][idx / DM][idx % DM] = ra[j];
-                }
-#pragma unroll
-                for(int j = 0; j < EB; j++)
-                {
-                    const int idx = tid + THREADS * j;
-                    if(a.bKfast)
-                        sB[buf][idx % DK][idx / DK] = rb[j];
-                    else
-                        sB[buf][idx / DN][idx % DN] = rb[j];
-                }
-            };
-
-            const int64_t nkt = (a.K + DK - 1) / DK;
-            gload(0);
-            sstore(0);
-            computeK(1, DK);
-            __syncthreads();
-
-            double acc[4][4][2];
-#pragma unroll
-            for(int i = 0; i < 4; i++)
-#pragma unroll
-                for(int j = 0; j < 4; j++)
-                    acc[i][j][0] = acc[i][j][1] = 0.0;
-
-            const int lane = tid & 31, warp = tid >> 5;
-            const int wm = warp & 3, wn = warp >> 2;
-
-            for(int64_t kt = 0; kt < nkt; kt++)
-            {
-                const int  cur     = int(kt & 1);
-                const bool hasNext = (kt + 1 < nkt);
-                if(hasNext)
-                    gload(cur ^ 1);
-#pragma unroll
-                for(int k4 = 0; k4 < DK / 4; k4++)
-                {
-                    double    af[4], bf[4];
-                    const int kr = k4 * 4 + (lane & 3);
-#pragma unroll
-                    for(int i = 0; i < 4; i++)
-                        af[i] = sA[cur][kr][wm * 32 + i * 8 + (lane >> 2)];
-#pragma unroll
-                    for(int j = 0; j < 4; j++)
-                        bf[j] = sB[cur][kr][wn * 32 + j * 8 + (lane >> 2)];
-#pragma unroll
-                    for(int i = 0; i < 4; i++)
-#pragma unroll
-                        for(int j = 0; j < 4; j++)
-                            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
-                                         : "+d"(acc[i][j][0]), "+d"(acc[i][j][1])
-                                         : "d"(af[i]), "d"(bf[j]));
-                }
-                if(hasNext)
-                {
-                    sstore(cur ^ 1);
-                    computeK(cur, (kt + 2) * DK);
-                }
-                __syncthreads();
-            }
-
-#pragma unroll
-            for(int i = 0; i < 4; i++)
-            {
-                const int64_t om = offDm[wm * 32 + i * 8 + (lane >> 2)];
-                if(om < 0)
-                    continue;
-#pragma unroll
-                for(int j = 0; j < 4; j++)
-#pragma unroll
-                    for(int e = 0; e < 2; e++)
-                    {
-                        const int64_t on = offDn[wn * 32 + j * 8 + 2 * (lane & 3) + e];
-                        if(on >= 0)
-                            storeEpilogue<double, double>(D, C, om + on, acc[i][j][e], a.alpha, a.beta, a.bilinear);
-                    }
-            }
-        }
-
         CtrArgs makeArgs(const ContractionPlan& p, float alpha, float beta, const void* C)
         {
             CtrArgs a{};
@@ -513,26 +348,328 @@ namespace htb
             return a;
         }
 
-        template <int DK>
-        cudaError_t launchDmma(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
-                               const void* C, void* D, cudaStream_t stream)
+        // ------------------------------------------------------------------ FP64 tensor-pipe kernel
+        // 128 x 64 output tile per CTA, 16-wide K steps, eight MMA warps in a 4 x 2 grid, each warp a 32 x 32 tile
+        // made of 4 x 4 mma.sync.m8n8k4.f64 fragments (16 MMAs for 8 shared-memory loads per 4-wide K step).
+        // Operands are gathered through offset tables (row offsets once per CTA, K offsets per step), so any mode
+        // structure is read in place. The gathers are cp.async copies straight from global to shared memory into
+        // a ring of three stages, 16 bytes at a time when the operand's layout allows (two elements that are
+        // neighbours in memory: along M/N for an operand whose rows are contiguous, along K for a K-contiguous
+        // one), else 8 bytes. Shared layout per operand: rows contiguous in memory -> [k][rows + 4]; K contiguous
+        // -> [row][k + 4] (both free of bank conflicts for the fragment loads: 8 rows x 4 k per instruction).
+        constexpr int DM = 128, DN = 64;
+        constexpr int kDmmaStages = 3;
+        constexpr int kDmmaK      = 16;
+        constexpr int kDmmaATile  = DM * (kDmmaK + PAD); // doubles per stage, the larger of the two layouts
+        constexpr int kDmmaBTile  = DN * (kDmmaK + PAD);
+
+        __device__ __forceinline__ void cpAsync16(uint32_t dst, const void* src, bool valid)
         {
-            CtrArgs       a      = makeArgs(p, alpha, beta, C);
+            const int n = valid ? 16 : 0; // 0: the destination is filled with zeros
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+        }
+        __device__ __forceinline__ void cpAsync8(uint32_t dst, const void* src, bool valid)
+        {
+            const int n = valid ? 8 : 0;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+        }
+
+        struct DmmaArgs
+        {
+            CtrArgs base;
+            int     vecA, vecB; // 16-byte copies are legal for this operand
+            int     k32; // K fits 32 bits: the producers decompose K indices with 32-bit divisions
+            int*    status; // the handle's device status word (raised when a bounded wait runs out)
+        };
+
+        // Warp-specialised: eight MMA warps that execute nothing but fragment loads and MMAs, and two producer warps that own the
+        // gathers: they compute the K offsets of a tile, issue all of the tile's cp.async copies (24 sixteen-byte
+        // copies per lane, or 48 eight-byte ones) into a ring of three stages and let them arrive on the stage's
+        // "full" mbarrier; each MMA warp waits for that barrier, consumes the stage and arrives on its "empty"
+        // barrier. There is no CTA-wide barrier in the K loop. Waits are clock-bounded: when one runs out the
+        // kernel raises the status word and every role leaves its loop.
+        constexpr int kWsProducers = 2; // two producer warps cost nothing: registers are granted per pair of warps
+        constexpr int kWsThreads   = THREADS + 32 * kWsProducers;
+
+        __device__ __forceinline__ void decompose2u(const ModeDim* dims, int nd, uint32_t idx, int64_t& o0, int64_t& o1)
+        {
+            o0 = 0;
+            o1 = 0;
+            for(int d = 0; d < nd; d++)
+            {
+                const uint32_t e = uint32_t(dims[d].ext), q = idx / e, c = idx - q * e;
+                idx = q;
+                o0 += int64_t(c) * dims[d].s0;
+                o1 += int64_t(c) * dims[d].s1;
+            }
+        }
+
+        __global__ void __launch_bounds__(kWsThreads, 2)
+            contraction_dmma_kernel(const double* __restrict__ A, const double* __restrict__ B, const double* C,
+                                       double* D, DmmaArgs args)
+        {
+            const CtrArgs& a = args.base;
+            constexpr int  DK = kDmmaK, S = kDmmaStages;
+            extern __shared__ __align__(16) unsigned char dsmem[];
+            double* sA = reinterpret_cast<double*>(dsmem); // [S][kDmmaATile]
+            double* sB = sA + S * kDmmaATile; // [S][kDmmaBTile]
+            __shared__ int64_t offAm[DM], offDm[DM], offBn[DN], offDn[DN];
+            __shared__ int64_t offAkAll[kWsProducers][S][DK], offBkAll[kWsProducers][S][DK]; // one table per producer warp
+            __shared__ __align__(8) unsigned long long fullBar[S], emptyBar[S];
+            __shared__ int abortFlag;
+
+            const int     tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+            const int64_t tileM = blockIdx.x / a.tilesN, tileN = blockIdx.x % a.tilesN;
+            const int64_t m0 = tileM * DM, n0 = tileN * DN;
+            const int     nkt = int((a.K + DK - 1) / DK); // the launcher refuses K beyond 2^31 steps
+
+            if(tid < DM)
+            {
+                const int64_t mm = m0 + tid;
+                int64_t       oa = -1, od = -1;
+                if(mm < a.M)
+                    decompose2(a.m, a.nm, mm, oa, od);
+                offAm[tid] = oa;
+                offDm[tid] = od;
+            }
+            else if(tid < DM + DN)
+            {
+                const int     t  = tid - DM;
+                const int64_t nn = n0 + t;
+                int64_t       ob = -1, od = -1;
+                if(nn < a.N)
+                    decompose2(a.n, a.nn, nn, ob, od);
+                offBn[t] = ob;
+                offDn[t] = od;
+            }
+            else if(tid == DM + DN)
+            {
+                abortFlag = 0;
+                for(int s = 0; s < S; s++)
+                {
+                    mbarInit(smemAddr(&fullBar[s]), 32 * kWsProducers); // the producers' lanes, each when its copies have landed
+                    mbarInit(smemAddr(&emptyBar[s]), THREADS / 32); // one arrival per MMA warp
+                }
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            }
+            __syncthreads();
+            volatile int*  abortP    = &abortFlag;
+            const uint32_t fullAddr  = smemAddr(&fullBar[0]), emptyAddr = smemAddr(&emptyBar[0]);
+            const int      aRS = a.aKfast ? DK + PAD : 1, aKS = a.aKfast ? 1 : DM + PAD;
+            const int      bRS = a.bKfast ? DK + PAD : 1, bKS = a.bKfast ? 1 : DN + PAD;
+
+            if(warp >= THREADS / 32)
+            {
+                // ---------------------------------------------------------------- producer warps
+                const int      pw = warp - THREADS / 32; // takes every kWsProducers-th group of 32 copies
+                int64_t(*offAk)[DK] = offAkAll[pw];
+                int64_t(*offBk)[DK] = offBkAll[pw];
+                const int      first = lane + 32 * pw, step = 32 * kWsProducers;
+                const uint32_t sAaddr = smemAddr(sA), sBaddr = smemAddr(sB);
+                int      st = 0;
+                uint32_t ph = 0; // parity of the stage's current use
+                for(int kt = 0; kt < nkt; kt++)
+                {
+                    // the stage's previous use must have been consumed by every MMA warp
+                    if(kt >= S && !mbarWaitTight(emptyAddr + 8 * st, ph ^ 1u, abortP))
+                        break;
+                    if(lane < DK)
+                    {
+                        const int64_t kk = int64_t(kt) * DK + lane;
+                        int64_t       oa = -1, ob = -1;
+                        if(kk < a.K)
+                        {
+                            if(args.k32)
+                                decompose2u(a.k, a.nk, uint32_t(kk), oa, ob);
+                            else
+                                decompose2(a.k, a.nk, kk, oa, ob);
+                        }
+                        offAk[st][lane] = oa;
+                        offBk[st][lane] = ob;
+                    }
+                    __syncwarp();
+                    const uint32_t dA = sAaddr + 8u * uint32_t(st * kDmmaATile), dB = sBaddr + 8u * uint32_t(st * kDmmaBTile);
+                    if(args.vecA)
+                    {
+#pragma unroll 4
+                        for(int idx = first; idx < DM * DK / 2; idx += step)
+                        {
+                            const int r = a.aKfast ? idx / (DK / 2) : 2 * (idx % (DM / 2));
+                            const int k = a.aKfast ? 2 * (idx % (DK / 2)) : idx / (DM / 2);
+                            const int64_t om = offAm[r], ok = offAk[st][k];
+                            const bool    v  = om >= 0 && ok >= 0;
+                            cpAsync16(dA + 8u * uint32_t(r * aRS + k * aKS), v ? A + om + ok : A, v);
+                        }
+                    }
+                    else
+                    {
+#pragma unroll 4
+                        for(int idx = first; idx < DM * DK; idx += step)
+                        {
+                            const int r = a.aKfast ? idx / DK : idx % DM;
+                            const int k = a.aKfast ? idx % DK : idx / DM;
+                            const int64_t om = offAm[r], ok = offAk[st][k];
+                            const bool    v  = om >= 0 && ok >= 0;
+                            cpAsync8(dA + 8u * uint32_t(r * aRS + k * aKS), v ? A + om + ok : A, v);
+                        }
+                    }
+                    if(args.vecB)
+                    {
+#pragma unroll 4
+                        for(int idx = first; idx < DN * DK / 2; idx += step)
+                        {
+                            const int r = a.bKfast ? idx / (DK / 2) : 2 * (idx % (DN / 2));
+                            const int k = a.bKfast ? 2 * (idx % (DK / 2)) : idx / (DN / 2);
+                            const int64_t on = offBn[r], ok = offBk[st][k];
+                            const bool    v  = on >= 0 && ok >= 0;
+                            cpAsync16(dB + 8u * uint32_t(r * bRS + k * bKS), v ? B + on + ok : B, v);
+                        }
+                    }
+                    else
+                    {
+#pragma unroll 4
+                        for(int idx = first; idx < DN * DK; idx += step)
+                        {
+                            const int r = a.bKfast ? idx / DK : idx % DN;
+                            const int k = a.bKfast ? idx % DK : idx / DN;
+                            const int64_t on = offBn[r], ok = offBk[st][k];
+                            const bool    v  = on >= 0 && ok >= 0;
+                            cpAsync8(dB + 8u * uint32_t(r * bRS + k * bKS), v ? B + on + ok : B, v);
+                        }
+                    }
+                    // this lane's arrival on the stage's barrier happens when its copies above have landed
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(fullAddr + 8 * st) : "memory");
+                    if(++st == S)
+                    {
+                        st = 0;
+                        ph ^= 1u;
+                    }
+                }
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                if(lane == 0 && *abortP && args.status)
+                    atomicExch(args.status, 3);
+                return;
+            }
+
+            // -------------------------------------------------------------------- MMA warps
+            double acc[4][4][2];
+#pragma unroll
+            for(int i = 0; i < 4; i++)
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+                    acc[i][j][0] = acc[i][j][1] = 0.0;
+            const int wm = warp & 3, wn = warp >> 2;
+            const int aFrag = (wm * 32 + (lane >> 2)) * aRS + (lane & 3) * aKS;
+            const int bFrag = (wn * 32 + (lane >> 2)) * bRS + (lane & 3) * bKS;
+            bool      ok    = true;
+            int       st    = 0;
+            uint32_t  ph    = 0;
+            for(int kt = 0; kt < nkt; kt++)
+            {
+                ok = mbarWaitTight(fullAddr + 8 * st, ph, abortP);
+                if(!ok)
+                    break;
+                const double* tA = sA + st * kDmmaATile + aFrag;
+                const double* tB = sB + st * kDmmaBTile + bFrag;
+#pragma unroll
+                for(int k4 = 0; k4 < DK / 4; k4++)
+                {
+                    double af[4], bf[4];
+#pragma unroll
+                    for(int i = 0; i < 4; i++)
+                        af[i] = tA[i * 8 * aRS + k4 * 4 * aKS];
+#pragma unroll
+                    for(int j = 0; j < 4; j++)
+                        bf[j] = tB[j * 8 * bRS + k4 * 4 * bKS];
+#pragma unroll
+                    for(int i = 0; i < 4; i++)
+#pragma unroll
+                        for(int j = 0; j < 4; j++)
+                            asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                                         : "+d"(acc[i][j][0]), "+d"(acc[i][j][1])
+                                         : "d"(af[i]), "d"(bf[j]));
+                }
+                __syncwarp();
+                if(lane == 0)
+                    mbarArrive(emptyAddr + 8 * st);
+                if(++st == S)
+                {
+                    st = 0;
+                    ph ^= 1u;
+                }
+            }
+            if(!ok)
+            {
+                if(lane == 0 && args.status)
+                    atomicExch(args.status, 3);
+                return;
+            }
+#pragma unroll
+            for(int i = 0; i < 4; i++)
+            {
+                const int64_t om = offDm[wm * 32 + i * 8 + (lane >> 2)];
+                if(om < 0)
+                    continue;
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+#pragma unroll
+                    for(int e = 0; e < 2; e++)
+                    {
+                        const int64_t on = offDn[wn * 32 + j * 8 + 2 * (lane & 3) + e];
+                        if(on >= 0)
+                            storeEpilogue<double, double>(D, C, om + on, acc[i][j][e], a.alpha, a.beta, a.bilinear);
+                    }
+            }
+        }
+
+        // 16-byte copies along the operand's contiguous direction: the direction's extent and every other stride
+        // of the operand even, base address 16-byte aligned. (Tiles start at even indices, so pairs never
+        // straddle the end of the contiguous mode.)
+        bool dmmaVectorOk(const void* base, const ModeDim* rows, int nrows, const ModeDim* ks, int nks, bool second, bool kFast)
+        {
+            if(uintptr_t(base) & 15)
+                return false;
+            auto strideOf = [&](const ModeDim& d, bool kGroup) { return kGroup ? (second ? d.s1 : d.s0) : d.s0; };
+            const ModeDim& unit = kFast ? ks[0] : rows[0];
+            if(strideOf(unit, kFast) != 1 || (unit.ext & 1))
+                return false;
+            for(int i = 0; i < nrows; i++)
+                if(!(i == 0 && !kFast) && rows[i].ext > 1 && (strideOf(rows[i], false) & 1))
+                    return false;
+            for(int i = 0; i < nks; i++)
+                if(!(i == 0 && kFast) && ks[i].ext > 1 && (strideOf(ks[i], true) & 1))
+                    return false;
+            return true;
+        }
+
+        cudaError_t launchDmma(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
+                               const void* C, void* D, int* deviceStatus, cudaStream_t stream)
+        {
+            DmmaArgs args{};
+            args.base            = makeArgs(p, alpha, beta, C);
+            CtrArgs&      a      = args.base;
             const int64_t tilesM = (p.M + DM - 1) / DM, tilesN = (p.N + DN - 1) / DN;
-            if(tilesM * tilesN > 0x7fffffffll)
+            if(tilesM * tilesN > 0x7fffffffll || p.K / kDmmaK >= 0x7fffffffll)
                 return cudaErrorInvalidConfiguration;
-            a.tilesN          = int(tilesN);
-            const size_t smem = sizeof(double) * 2 * DK * (DM + PAD + DN + PAD);
+            a.tilesN = int(tilesN);
+            // operand A's rows are the M group (first strides), B's the N group (first strides); K strides: A first, B second
+            args.vecA = dmmaVectorOk(A, p.m, p.nm, p.k, p.nk, false, a.aKfast != 0) ? 1 : 0;
+            args.vecB = dmmaVectorOk(B, p.n, p.nn, p.k, p.nk, true, a.bKfast != 0) ? 1 : 0;
+            if(getenv("HTB_DMMA_NOVEC"))
+                args.vecA = args.vecB = 0;
+            args.k32    = p.K < (int64_t(1) << 31) ? 1 : 0;
+            args.status = deviceStatus;
+            const size_t smem = sizeof(double) * kDmmaStages * (kDmmaATile + kDmmaBTile);
             static unsigned char attr[kMaxDevices] = {};
             if(firstUseOnDevice(attr))
             {
-                cudaError_t e = cudaFuncSetAttribute(contraction_dmma_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                cudaError_t e = cudaFuncSetAttribute(contraction_dmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                      int(smem));
                 if(e != cudaSuccess)
                     return e;
             }
-            contraction_dmma_kernel<DK><<<unsigned(tilesM * tilesN), THREADS, smem, stream>>>(
-                (const double*)A, (const double*)B, (const double*)C, (double*)D, a);
+            contraction_dmma_kernel<<<unsigned(tilesM * tilesN), kWsThreads, smem, stream>>>(
+                (const double*)A, (const double*)B, (const double*)C, (double*)D, args);
             noteLaunch("contraction_tiled_dmma");
             return cudaGetLastError();
         }
@@ -604,10 +741,7 @@ namespace htb
         case CUDA_R_64F:
             if(ct == HIPTENSOR_COMPUTE_64F)
             {
-                if(const char* env = getenv("HTB_DMMA_BK"))
-                    if(atoi(env) == 32)
-                        return launchDmma<32>(plan, alpha, A, B, beta, C, D, stream);
-                return launchDmma<16>(plan, alpha, A, B, beta, C, D, stream);
+                return launchDmma(plan, alpha, A, B, beta, C, D, deviceStatus, stream);
             }
             return launchTiled<double, double, 0>(plan, alpha, A, B, beta, C, D, stream);
         case CUDA_R_16F:

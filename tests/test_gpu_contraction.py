@@ -139,6 +139,57 @@ def test_config5_scaled_down(env):
     assert ht.last_kernel_name() == "contraction_tiled_dmma"
 
 
+F64_LAYOUTS = {"kk": ([0, 2], [1, 2]), "mn_mn": ([2, 0], [2, 1]), "k_mn": ([0, 2], [2, 1]), "mn_k": ([2, 0], [1, 2])}
+
+
+@pytest.mark.parametrize("layout", sorted(F64_LAYOUTS))
+@pytest.mark.parametrize("shape", [(256, 192, 96), (200, 132, 72), (130, 70, 34), (129, 67, 35), (64, 64, 8)])
+def test_fp64_operand_layouts(env, layout, shape):
+    """fp64 on the FP64 tensor pipe with each operand contiguous along K or along its rows. Even extents take the
+    16-byte asynchronous copies (pairs along the contiguous direction), odd ones the 8-byte copies; ragged M, N
+    and K tails (K not a multiple of the 16-wide step, shorter than the copy ring) are zero-filled."""
+    ht, h = env
+    M, N, K = shape
+    modeA, modeB = F64_LAYOUTS[layout]
+    got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F64, alpha=1.5, beta=0.5)
+    assert ht.last_kernel_name() == "contraction_tiled_dmma"
+    assert not np.isnan(got).any()
+    err = rel_error(got, exp, td)
+    assert 0 <= err < 1e-12, (layout, shape, err)
+    # D contiguous along M: the planner exchanges the operands
+    got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [1, 0], typeAB=orc.F64, alpha=1.0, beta=0.0)
+    err = rel_error(got, exp, td)
+    assert 0 <= err < 1e-12, (layout, shape, err)
+
+
+def test_fp64_unaligned_base_and_strided_rows(env):
+    """Operands that start 8 bytes past a 16-byte boundary (8-byte copies) and rows with padding between them
+    (even strides: 16-byte copies stay legal)."""
+    import torch
+
+    from helpers import to_device
+
+    ht, h = env
+    M, N, K = 96, 80, 48
+    for pad, shift in ((0, 1), (2, 0), (3, 0)):
+        sA, sB, sD = [K + pad, 1], [K + pad, 1], [N, 1]
+        nA, nB = M * (K + pad), N * (K + pad)
+        A = orc.fill_uniform(nA + shift, orc.F64, 255)
+        B = orc.fill_uniform(nB + shift, orc.F64, 256)
+        dA, dB, dD = (h.tensor_descriptor(l, s, ht.R_64F) for l, s in (([M, K], sA), ([N, K], sB), ([M, N], sD)))
+        cd = h.contraction_descriptor(dA, [0, 2], dB, [1, 2], None, None, dD, [0, 1], ht.COMPUTE_64F)
+        find = h.contraction_find()
+        plan = h.contraction_plan(cd, find, 0)
+        A_d, B_d = to_device(A, orc.F64), to_device(B, orc.F64)
+        D_d = torch.full((M * N,), float("nan"), dtype=torch.float64, device="cuda")
+        h.contraction(plan, 2.0, A_d[shift:], B_d[shift:], 0.0, None, D_d)
+        exp = np.full(M * N, np.nan)
+        orc.contraction(2.0, A[shift:], [M, K], sA, [0, 2], orc.F64, B[shift:], [N, K], sB, [1, 2], orc.F64, 0.0, None,
+                        exp, [M, N], sD, [0, 1], orc.F64, orc.COMPUTE_64F)
+        err = rel_error(D_d.cpu().numpy(), exp, orc.F64)
+        assert 0 <= err < 1e-12, (pad, shift, err)
+
+
 def test_config5_full_size_sampled(env):
     """fp64 M=4096, N=K=2304: 4096 sampled outputs against the exact-order oracle."""
     ht, h = env
