@@ -800,7 +800,7 @@ namespace htb
         }
         std::stable_sort(yFreeM, yFreeM + nYFree, byKey);
 
-        auto planWith = [&](bool copyY) -> int {
+        auto planWith = [&](bool copyY, ContractionPlan* plan) -> int {
         int64_t lX[kPlanRank], sX[kPlanRank], lY[kPlanRank], sY[kPlanRank], lD[kPlanRank], sD[kPlanRank];
         int32_t mX[kPlanRank], mY[kPlanRank], mD[kPlanRank];
         int     r = 0;
@@ -864,48 +864,48 @@ namespace htb
         const TensorView X2{rankX2, lX, sX, mX, realType}, Y2{Y.rank + 1, lY, sY, mY, realType},
             D2{D.rank + 1, lD, sD, mD, realType};
         const int rc = planReal(expandA ? X2 : Y2, expandA ? Y2 : X2, D2, realType, bilinear, c32 ? 4 : 16, smCount,
-                                kPlanRank, out);
+                                kPlanRank, plan);
         if(rc != PLAN_OK)
             return rc;
-        out->complexKind = expandA ? 1 : 2;
-        out->xRank       = nFree + nCon;
-        out->xFree       = nFree;
+        plan->complexKind = expandA ? 1 : 2;
+        plan->xRank       = nFree + nCon;
+        plan->xFree       = nFree;
         for(int i = 0; i < nFree; i++)
         {
-            out->xExt[i]    = X.lens[freeM[i].pos];
-            out->xStride[i] = X.strides[freeM[i].pos];
+            plan->xExt[i]    = X.lens[freeM[i].pos];
+            plan->xStride[i] = X.strides[freeM[i].pos];
         }
         for(int i = 0; i < nCon; i++)
         {
-            out->xExt[nFree + i]    = X.lens[conM[i].pos];
-            out->xStride[nFree + i] = X.strides[conM[i].pos];
+            plan->xExt[nFree + i]    = X.lens[conM[i].pos];
+            plan->xStride[nFree + i] = X.strides[conM[i].pos];
         }
-        out->dRank = D.rank;
+        plan->dRank = D.rank;
         for(int i = 0; i < D.rank; i++)
         {
-            out->dExt[i]    = D.lens[i];
-            out->dStride[i] = D.strides[i];
+            plan->dExt[i]    = D.lens[i];
+            plan->dStride[i] = D.strides[i];
         }
         const uint64_t bytes = uint64_t(expandA ? nA : nB) * 4u * uint64_t(realSize);
-        out->expandBytes     = (bytes + 255u) & ~uint64_t(255);
+        plan->expandBytes     = (bytes + 255u) & ~uint64_t(255);
         if(copyY)
         {
-            out->yCopy   = 1;
-            out->yRank   = Y.rank;
-            out->yFree   = nYFree;
-            out->yOffset = out->expandBytes;
+            plan->yCopy   = 1;
+            plan->yRank   = Y.rank;
+            plan->yFree   = nYFree;
+            plan->yOffset = plan->expandBytes;
             for(int i = 0; i < Y.rank; i++)
             {
-                out->yExt[i]    = Y.lens[posY[i]];
-                out->yStride[i] = Y.strides[posY[i]];
+                plan->yExt[i]    = Y.lens[posY[i]];
+                plan->yStride[i] = Y.strides[posY[i]];
             }
             const uint64_t bytesY = uint64_t(expandA ? nB : nA) * 2u * uint64_t(realSize);
-            out->expandBytes += (bytesY + 255u) & ~uint64_t(255);
+            plan->expandBytes += (bytesY + 255u) & ~uint64_t(255);
         }
         return PLAN_OK;
         };
 
-        int rc = planWith(false);
+        const int rc = planWith(false, out);
         if(rc != PLAN_OK)
             return rc;
         if(c32 && out->kind != CK_TF32X3)
@@ -914,11 +914,7 @@ namespace htb
             // (re, im) pairs sit between consecutive rows). A packed copy with the contracted modes innermost
             // costs one pass over Y and puts the problem on the tensor cores.
             ContractionPlan alt;
-            ContractionPlan* const keep = out;
-            out                         = &alt;
-            const int rc2               = planWith(true);
-            out                         = keep;
-            if(rc2 == PLAN_OK && alt.kind == CK_TF32X3)
+            if(planWith(true, &alt) == PLAN_OK && alt.kind == CK_TF32X3)
                 *out = alt;
         }
         return PLAN_OK;
