@@ -357,23 +357,36 @@ namespace htb
                             // 32 consecutive floats of this row: eight 128-bit stores
                             float*       dst = (float*)D + offM + first;
                             const float* src = (const float*)C + offM + first;
+                            // C may be D, so every load of C stays ahead of the stores that follow it: the loads are
+                            // taken four at a time before their stores (one memory round trip per sixteen columns)
 #pragma unroll
-                            for(int j = 0; j < 32; j += 4)
+                            for(int j0 = 0; j0 < 32; j0 += 16)
                             {
-                                float4 o;
-                                o.x = __fmul_rn(a.alpha, __uint_as_float(v[j]));
-                                o.y = __fmul_rn(a.alpha, __uint_as_float(v[j + 1]));
-                                o.z = __fmul_rn(a.alpha, __uint_as_float(v[j + 2]));
-                                o.w = __fmul_rn(a.alpha, __uint_as_float(v[j + 3]));
+                                float4 c4[4];
                                 if(a.bilinear)
                                 {
-                                    const float4 c4 = *(const float4*)(src + j);
-                                    o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4.x));
-                                    o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4.y));
-                                    o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4.z));
-                                    o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4.w));
+#pragma unroll
+                                    for(int q = 0; q < 4; q++)
+                                        c4[q] = *(const float4*)(src + j0 + 4 * q);
                                 }
-                                *(float4*)(dst + j) = o;
+#pragma unroll
+                                for(int q = 0; q < 4; q++)
+                                {
+                                    const int j = j0 + 4 * q;
+                                    float4    o;
+                                    o.x = __fmul_rn(a.alpha, __uint_as_float(v[j]));
+                                    o.y = __fmul_rn(a.alpha, __uint_as_float(v[j + 1]));
+                                    o.z = __fmul_rn(a.alpha, __uint_as_float(v[j + 2]));
+                                    o.w = __fmul_rn(a.alpha, __uint_as_float(v[j + 3]));
+                                    if(a.bilinear)
+                                    {
+                                        o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4[q].x));
+                                        o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4[q].y));
+                                        o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4[q].z));
+                                        o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4[q].w));
+                                    }
+                                    *(float4*)(dst + j) = o;
+                                }
                             }
                         }
                         else
@@ -818,23 +831,36 @@ namespace htb
                         {
                             float*       dst = (float*)D + offM + first;
                             const float* src = (const float*)C + offM + first;
+                            // C may be D, so every load of C stays ahead of the stores that follow it: the loads are
+                            // taken four at a time before their stores (one memory round trip per sixteen columns)
 #pragma unroll
-                            for(int j = 0; j < 32; j += 4)
+                            for(int j0 = 0; j0 < 32; j0 += 16)
                             {
-                                float4 o;
-                                o.x = __fmul_rn(a.alpha, __uint_as_float(v[j]));
-                                o.y = __fmul_rn(a.alpha, __uint_as_float(v[j + 1]));
-                                o.z = __fmul_rn(a.alpha, __uint_as_float(v[j + 2]));
-                                o.w = __fmul_rn(a.alpha, __uint_as_float(v[j + 3]));
+                                float4 c4[4];
                                 if(a.bilinear)
                                 {
-                                    const float4 c4 = *(const float4*)(src + j);
-                                    o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4.x));
-                                    o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4.y));
-                                    o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4.z));
-                                    o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4.w));
+#pragma unroll
+                                    for(int q = 0; q < 4; q++)
+                                        c4[q] = *(const float4*)(src + j0 + 4 * q);
                                 }
-                                *(float4*)(dst + j) = o;
+#pragma unroll
+                                for(int q = 0; q < 4; q++)
+                                {
+                                    const int j = j0 + 4 * q;
+                                    float4    o;
+                                    o.x = __fmul_rn(a.alpha, __uint_as_float(v[j]));
+                                    o.y = __fmul_rn(a.alpha, __uint_as_float(v[j + 1]));
+                                    o.z = __fmul_rn(a.alpha, __uint_as_float(v[j + 2]));
+                                    o.w = __fmul_rn(a.alpha, __uint_as_float(v[j + 3]));
+                                    if(a.bilinear)
+                                    {
+                                        o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4[q].x));
+                                        o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4[q].y));
+                                        o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4[q].z));
+                                        o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4[q].w));
+                                    }
+                                    *(float4*)(dst + j) = o;
+                                }
                             }
                         }
                         else

@@ -626,6 +626,19 @@ namespace htb
                     }
                     __syncwarp();
                     const int64_t offM = (dupM || !active) ? -1 : tfRowOffset(a.gm, wm, row);
+                    // the tile's owner will read C at the very end: start bringing its rows into L2 now
+                    if(a.bilinear && offM >= 0 && (u % parts) == 0)
+                    {
+#pragma unroll
+                        for(int c0 = 0; c0 < 64; c0 += 32)
+                        {
+                            const int64_t f = cols[c0], l = cols[c0 + 31];
+                            if(f >= 0)
+                                asm volatile("prefetch.global.L2 [%0];" ::"l"(C + offM + f));
+                            if(l >= 0)
+                                asm volatile("prefetch.global.L2 [%0];" ::"l"(C + offM + l));
+                        }
+                    }
 
                     // running sums of the main product, one segment at a time
                     float sum[64];
@@ -683,15 +696,17 @@ namespace htb
                     const int part = u % parts, tileIdx = u / parts;
                     if(parts > 1)
                     {
-                        float* slotRow = a.slots + ((size_t(tileIdx) * (parts - 1)) * 128 + row) * 128 + cbase;
+                        // slot layout [part - 1][32 column groups of four][128 rows] of float4: a warp's 32 rows of one
+                        // column group are 512 contiguous bytes, for the writers and for the reader
+                        float4* slot4 = (float4*)a.slots + (size_t(tileIdx) * (parts - 1)) * 4096 + size_t(cbase >> 2) * 128 + row;
                         if(part > 0)
                         {
                             if(active)
                             {
-                                float4* dst = (float4*)(slotRow + size_t(part - 1) * 128 * 128);
+                                float4* dst = slot4 + size_t(part - 1) * 4096;
 #pragma unroll
                                 for(int j = 0; j < 16; j++)
-                                    dst[j] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
+                                    dst[j * 128] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
                             }
                             __threadfence();
                             __syncwarp();
@@ -730,11 +745,11 @@ namespace htb
                             {
                                 for(int q = 0; q < parts - 1; q++)
                                 {
-                                    const float4* src = (const float4*)(slotRow + size_t(q) * 128 * 128);
+                                    const float4* src = slot4 + size_t(q) * 4096;
 #pragma unroll
                                     for(int j = 0; j < 16; j++)
                                     {
-                                        const float4 p4 = __ldcg(src + j);
+                                        const float4 p4 = __ldcg(src + j * 128);
                                         sum[4 * j]     = __fadd_rn(sum[4 * j], p4.x);
                                         sum[4 * j + 1] = __fadd_rn(sum[4 * j + 1], p4.y);
                                         sum[4 * j + 2] = __fadd_rn(sum[4 * j + 2], p4.z);
@@ -756,23 +771,37 @@ namespace htb
                                 // 32 consecutive floats of this row: eight 128-bit stores
                                 float*       dst = D + offM + first;
                                 const float* src = C + offM + first;
+                                // C may be D: the compiler must keep every load of C before the stores that follow it,
+                                // so the loads are taken four at a time ahead of their stores (one memory round trip
+                                // per sixteen columns instead of one per four)
 #pragma unroll
-                                for(int j = 0; j < 32; j += 4)
+                                for(int j0 = 0; j0 < 32; j0 += 16)
                                 {
-                                    float4 o;
-                                    o.x = __fmul_rn(a.alpha, sum[c0 + j]);
-                                    o.y = __fmul_rn(a.alpha, sum[c0 + j + 1]);
-                                    o.z = __fmul_rn(a.alpha, sum[c0 + j + 2]);
-                                    o.w = __fmul_rn(a.alpha, sum[c0 + j + 3]);
+                                    float4 c4[4];
                                     if(a.bilinear)
                                     {
-                                        const float4 c4 = *(const float4*)(src + j);
-                                        o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4.x));
-                                        o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4.y));
-                                        o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4.z));
-                                        o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4.w));
+#pragma unroll
+                                        for(int q = 0; q < 4; q++)
+                                            c4[q] = *(const float4*)(src + j0 + 4 * q);
                                     }
-                                    *(float4*)(dst + j) = o;
+#pragma unroll
+                                    for(int q = 0; q < 4; q++)
+                                    {
+                                        const int j = j0 + 4 * q;
+                                        float4    o;
+                                        o.x = __fmul_rn(a.alpha, sum[c0 + j]);
+                                        o.y = __fmul_rn(a.alpha, sum[c0 + j + 1]);
+                                        o.z = __fmul_rn(a.alpha, sum[c0 + j + 2]);
+                                        o.w = __fmul_rn(a.alpha, sum[c0 + j + 3]);
+                                        if(a.bilinear)
+                                        {
+                                            o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4[q].x));
+                                            o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4[q].y));
+                                            o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4[q].z));
+                                            o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4[q].w));
+                                        }
+                                        *(float4*)(dst + j) = o;
+                                    }
                                 }
                             }
                             else

@@ -604,21 +604,36 @@ namespace htb
                     atomicExch(args.status, 3);
                 return;
             }
+            // C may be D, so a load of C cannot move above an earlier store to D: the eight values of C that a row
+            // block needs are loaded first, then the eight results are stored (4 memory round trips instead of 32)
 #pragma unroll
             for(int i = 0; i < 4; i++)
             {
                 const int64_t om = offDm[wm * 32 + i * 8 + (lane >> 2)];
                 if(om < 0)
                     continue;
+                int64_t off[4][2];
+                double  cv[4][2];
 #pragma unroll
                 for(int j = 0; j < 4; j++)
 #pragma unroll
                     for(int e = 0; e < 2; e++)
                     {
                         const int64_t on = offDn[wn * 32 + j * 8 + 2 * (lane & 3) + e];
-                        if(on >= 0)
-                            storeEpilogue<double, double>(D, C, om + on, acc[i][j][e], a.alpha, a.beta, a.bilinear);
+                        off[j][e]        = on >= 0 ? om + on : -1;
+                        cv[j][e]         = (a.bilinear && on >= 0) ? C[om + on] : 0.0;
                     }
+#pragma unroll
+                for(int j = 0; j < 4; j++)
+#pragma unroll
+                    for(int e = 0; e < 2; e++)
+                        if(off[j][e] >= 0)
+                        {
+                            double y = __dmul_rn(double(a.alpha), acc[i][j][e]);
+                            if(a.bilinear)
+                                y = __dadd_rn(y, __dmul_rn(double(a.beta), cv[j][e]));
+                            D[off[j][e]] = y;
+                        }
             }
         }
 

@@ -95,17 +95,17 @@ namespace htb
         };
         __device__ __forceinline__ TfChunks tfChunksOf(const TfGroup& g, const TfTile& w)
         {
-            TfChunks      q;
-            const int64_t e1 = (g.n > 1) ? g.ext[1] : 1;
+            TfChunks       q;
+            const uint32_t e1 = (g.n > 1) ? uint32_t(g.ext[1]) : 1u; // extents fit 32 bits (tensor-map limit)
 #pragma unroll
             for(int j = 0; j < 4; j++)
             {
-                const int     chunk = w.chunkBase + j;
-                const int64_t rest  = chunk / g.chunks0;
+                const uint32_t chunk = uint32_t(w.chunkBase + j);
+                const uint32_t rest  = chunk / uint32_t(g.chunks0);
                 // beyond the tensor the coordinates fall outside the map and the box is zero-filled
-                q.c0[j] = (chunk % g.chunks0) << g.chunkShift;
-                q.i1[j] = int(rest % e1);
+                q.c0[j] = int((chunk - rest * uint32_t(g.chunks0)) << g.chunkShift);
                 q.i2[j] = int(rest / e1);
+                q.i1[j] = int(rest - uint32_t(q.i2[j]) * e1);
             }
             return q;
         }
