@@ -23,8 +23,8 @@
 //                  the epilogue drains every 64 K elements, the two correction products into their own;
 //   epilogue       tcgen05.ld, running sums in registers, alpha/beta, stores to the strided D.
 // When both operands are K-major the staging step is skipped (INPLACE): TMA writes into the ring's big tiles and
-// the converter only adds the small ones. Small problems are cut along K over several CTAs (parts), with the
-// partial sums exchanged through the caller's workspace.
+// the converter only adds the small ones. Small problems are cut along K over the CTAs of a thread-block cluster
+// (parts); the partial sums go to the owner's shared memory over the cluster network.
 //
 // Warp roles (576 threads): 0 TMA producer, 1 MMA issuer + tensor-memory owner, 2-9 epilogue (two warps
 // per tensor-memory lane quadrant, 64 columns each), 10-17 converter. PAIR = true runs a 256 x 128 tile
@@ -42,7 +42,6 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
-#include <atomic>
 #include <cstdlib>
 
 #include "kernels.hpp"
@@ -84,13 +83,11 @@ namespace htb
             int      bilinear;
             int      nContig; // 32 consecutive columns of a tile are 32 consecutive, 16-byte aligned floats of D
             int      pairsM, pairsN; // PAIR only
-            // K split of small problems (single CTAs only): every tile is cut into `parts` ranges of K blocks, one work
-            // unit each, all resident at once. Part 0 owns the tile: it waits for the others' raw sums in `slots`
-            // (flag per tile), adds them in order and applies alpha/beta; parts 1.. write their sums and raise the flag.
+            // K split of small problems (single CTAs only): every tile is cut into `parts` ranges of K blocks, one CTA
+            // each, launched as one thread-block cluster per tile. Part 0 owns the tile: when every part has its sums,
+            // parts 1.. store theirs into part 0's (by then idle) shared-memory rings over the cluster network, and part 0
+            // adds them in order and applies alpha/beta.
             int      parts;
-            float*   slots; // [tile][part - 1][128 rows][accumulator columns]
-            int*     flags; // [tile][part - 1][epilogue warp]: the launch's epoch once that warp's rows are in the slot
-            int      epoch; // differs from launch to launch: stale flag words never match, nothing has to be zeroed
             int      round; // 0: big/small split (compute f32); 1 / 2: elements rounded to f16 / bf16, one MMA per K step
             int      probe; // measurement aid, bit mask: 1 = converter skips its work, 2 = issuer skips the MMAs,
                             // 8 = producer skips the loads (results invalid)
@@ -490,6 +487,11 @@ namespace htb
                         }
                     }
                 }
+                if(parts > 1)
+                {
+                    clusterSync(); // the two meeting points of the K-split hand-over (see the epilogue)
+                    clusterSync();
+                }
             }
             else if(warp == 1)
             {
@@ -577,6 +579,11 @@ namespace htb
                         }
                     }
                 }
+                if(parts > 1)
+                {
+                    clusterSync();
+                    clusterSync();
+                }
             }
             else if(warp < 2 + kEpiWarps)
             {
@@ -590,6 +597,7 @@ namespace htb
                 const uint32_t lanes = tmem + (uint32_t(quad * 32) << 16) + uint32_t(cbase);
                 uint32_t       seg   = 0;
                 int            local = 0;
+                int            syncs = 0; // cluster meeting points of the K-split hand-over passed so far
                 bool           alive = true;
                 auto waitWarp = [&](uint32_t bar, uint32_t parity) {
                     return __all_sync(0xffffffffu, tfWait(bar, parity, abortP)) != 0;
@@ -692,69 +700,42 @@ namespace htb
                                 sum[c0 + j] = __fadd_rn(sum[c0 + j], __uint_as_float(v[j]));
                         }
                     }
-                    // K split: parts 1.. publish their sums, part 0 collects them in order
-                    const int part = u % parts, tileIdx = u / parts;
+                    // K split: every part has its sums; parts 1.. hand theirs to part 0, which adds them in order
+                    const int part = u % parts;
                     if(parts > 1)
                     {
-                        // slot layout [part - 1][32 column groups of four][128 rows] of float4: a warp's 32 rows of one
-                        // column group are 512 contiguous bytes, for the writers and for the reader
-                        float4* slot4 = (float4*)a.slots + (size_t(tileIdx) * (parts - 1)) * 4096 + size_t(cbase >> 2) * 128 + row;
-                        if(part > 0)
+                        // zone of part q in the owner's ring memory: [q - 1][column groups of four][128 rows] of float4
+                        // (a warp's 32 rows of one column group are 512 contiguous bytes)
+                        const uint32_t zone = stagingAddr + uint32_t(cbase >> 2) * 2048u + uint32_t(row) * 16u;
+                        const uint32_t zoneBytes = 128u * uint32_t(accCols) * 4u;
+                        clusterSync(); // the owner's MMAs have read the last operands: its rings are free
+                        syncs++;
+                        if(part > 0 && active)
                         {
-                            if(active)
+                            const uint32_t dst = mapToRank(zone + uint32_t(part - 1) * zoneBytes, 0);
+#pragma unroll
+                            for(int j = 0; j < 16; j++)
+                                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst + uint32_t(j) * 2048u),
+                                             "f"(sum[4 * j]), "f"(sum[4 * j + 1]), "f"(sum[4 * j + 2]), "f"(sum[4 * j + 3])
+                                             : "memory");
+                        }
+                        clusterSync(); // the sums have arrived
+                        syncs++;
+                        if(part == 0 && active)
+                        {
+                            for(int q = 0; q < parts - 1; q++)
                             {
-                                float4* dst = slot4 + size_t(part - 1) * 4096;
 #pragma unroll
                                 for(int j = 0; j < 16; j++)
-                                    dst[j * 128] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
-                            }
-                            __threadfence();
-                            __syncwarp();
-                            if(lane == 0)
-                            {
-                                int* flag = a.flags + (size_t(tileIdx) * (parts - 1) + (part - 1)) * kEpiWarps + (warp - 2);
-                                asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(a.epoch) : "memory");
-                            }
-                        }
-                        else
-                        {
-                            // lane j watches the j-th of the (parts - 1) * 8 flag words of this tile
-                            int ready = 1;
-                            if(lane < (parts - 1) * kEpiWarps)
-                            {
-                                const int*      flag = a.flags + size_t(tileIdx) * (parts - 1) * kEpiWarps + lane;
-                                const long long t0   = clock64();
-                                for(;;)
                                 {
-                                    int seen;
-                                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-                                    if(seen == a.epoch)
-                                        break;
-                                    if(*abortP || clock64() - t0 > kWaitCycles)
-                                    {
-                                        *abortP = 1;
-                                        ready   = 0;
-                                        break;
-                                    }
-                                }
-                            }
-                            ready = __all_sync(0xffffffffu, ready);
-                            if(!ready)
-                                alive = false;
-                            if(ready && active)
-                            {
-                                for(int q = 0; q < parts - 1; q++)
-                                {
-                                    const float4* src = slot4 + size_t(q) * 4096;
-#pragma unroll
-                                    for(int j = 0; j < 16; j++)
-                                    {
-                                        const float4 p4 = __ldcg(src + j * 128);
-                                        sum[4 * j]     = __fadd_rn(sum[4 * j], p4.x);
-                                        sum[4 * j + 1] = __fadd_rn(sum[4 * j + 1], p4.y);
-                                        sum[4 * j + 2] = __fadd_rn(sum[4 * j + 2], p4.z);
-                                        sum[4 * j + 3] = __fadd_rn(sum[4 * j + 3], p4.w);
-                                    }
+                                    float4 p4;
+                                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                                 : "=f"(p4.x), "=f"(p4.y), "=f"(p4.z), "=f"(p4.w)
+                                                 : "r"(zone + uint32_t(q) * zoneBytes + uint32_t(j) * 2048u));
+                                    sum[4 * j]     = __fadd_rn(sum[4 * j], p4.x);
+                                    sum[4 * j + 1] = __fadd_rn(sum[4 * j + 1], p4.y);
+                                    sum[4 * j + 2] = __fadd_rn(sum[4 * j + 2], p4.z);
+                                    sum[4 * j + 3] = __fadd_rn(sum[4 * j + 3], p4.w);
                                 }
                             }
                         }
@@ -827,6 +808,8 @@ namespace htb
                     if(lane == 0)
                         arriveIssuer(corrEmpty + 8 * cb);
                 }
+                for(; parts > 1 && syncs < 2; syncs++)
+                    clusterSync(); // a role that gave up still meets the others
             }
             else
             {
@@ -892,6 +875,11 @@ namespace htb
                             oPhase ^= 1;
                         }
                     }
+                }
+                if(parts > 1)
+                {
+                    clusterSync();
+                    clusterSync();
                 }
             }
 
@@ -984,6 +972,26 @@ namespace htb
             if(!PAIR)
             {
                 const int grid = int(std::min<int64_t>(int64_t(a.gm.tiles) * a.gn.tiles * std::max(a.parts, 1), sms));
+                if(a.parts > 1)
+                {
+                    // one cluster per tile: its CTAs are the K ranges (the caller made sure every unit gets a CTA)
+                    cudaLaunchConfig_t  cfg{};
+                    cudaLaunchAttribute attr[1];
+                    attr[0].id               = cudaLaunchAttributeClusterDimension;
+                    attr[0].val.clusterDim.x = unsigned(a.parts);
+                    attr[0].val.clusterDim.y = 1;
+                    attr[0].val.clusterDim.z = 1;
+                    cfg.gridDim              = dim3(unsigned(grid));
+                    cfg.blockDim             = dim3(kTfThreads);
+                    cfg.dynamicSmemBytes     = smem;
+                    cfg.stream               = stream;
+                    cfg.attrs                = attr;
+                    cfg.numAttrs             = 1;
+                    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, C, D, a, idesc);
+                    if(e == cudaSuccess)
+                        noteLaunch("contraction_tf32x3");
+                    return e;
+                }
                 kernel<<<grid, kTfThreads, smem, stream>>>(mapA, mapB, C, D, a, idesc);
                 noteLaunch("contraction_tf32x3");
                 return cudaGetLastError();
@@ -1024,6 +1032,8 @@ namespace htb
                                         const void* C, void* D, void* workspace, uint64_t workspaceBytes, int smCount,
                                         int* deviceStatus, cudaStream_t stream)
     {
+        (void)workspace; // this kernel needs no scratch
+        (void)workspaceBytes;
         PFN_encodeTiled encode = tensorMapEncoder();
         if(!encode)
             return cudaErrorNotSupported;
@@ -1076,24 +1086,13 @@ namespace htb
                      a.gn.tiles, a.gn.rows, a.kBlocks, pair ? "CTA pairs" : "single CTAs");
         if(pair)
             return launchKernel<true, false>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream);
-        // K split, if the plan asks for it, the caller's workspace holds its scratch and every unit gets a CTA
+        // K split, if the plan asks for it and every unit gets a CTA (one cluster of `parts` CTAs per tile)
         a.parts = 1;
         {
             const int64_t tiles = int64_t(a.gm.tiles) * a.gn.tiles;
             const int     parts = p.splitK;
-            constexpr uint64_t kFlagBytes = 32768; // 256 tiles x 3 parts x 8 warps x 4 bytes, rounded up
-            const uint64_t need = kFlagBytes + uint64_t(tiles) * uint64_t(std::max(parts, 1) - 1) * 128 * 128 * 4;
-            if(parts > 1 && workspace != nullptr && need <= workspaceBytes && (uintptr_t(workspace) & 15) == 0 && tiles <= 256
-               && tiles * parts <= sms && a.kBlocks >= 4 * parts && getenv("HTB_TF32_NOSPLIT") == nullptr)
-            {
-                static std::atomic<int> launches{0};
+            if(parts > 1 && parts <= 4 && tiles * parts <= sms && a.kBlocks >= 4 * parts && getenv("HTB_TF32_NOSPLIT") == nullptr)
                 a.parts = parts;
-                a.flags = (int*)workspace;
-                a.slots = (float*)((char*)workspace + kFlagBytes);
-                a.epoch = launches.fetch_add(1) + 1;
-                if(a.epoch == 0) // the value an untouched buffer is most likely to hold
-                    a.epoch = launches.fetch_add(1) + 1;
-            }
         }
         // both operands K-major and no rounding: TMA loads straight into the operand ring
         const bool inplace = !p.aMajor && !p.bMajor && a.round == 0 && getenv("HTB_TF32_NOINPLACE") == nullptr;

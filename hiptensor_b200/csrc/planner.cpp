@@ -691,10 +691,7 @@ namespace htb
                 const int64_t tiles = tilesM * tilesN;
                 int           parts = int(std::min<int64_t>(std::min<int64_t>(4, sms / std::max<int64_t>(tiles, 1)), kBlocks / 4));
                 if(parts >= 2)
-                {
-                    out->splitK         = parts;
-                    out->workspaceBytes = 32768 + uint64_t(tiles) * uint64_t(parts - 1) * 128 * 128 * 4; // flags + slots
-                }
+                    out->splitK = parts; // a cluster of `parts` CTAs per tile; the sums meet in shared memory: no scratch
             }
             out->kind = tf ? CK_TF32X3 : CK_TILED_SIMT;
         }

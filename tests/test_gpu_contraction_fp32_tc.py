@@ -165,9 +165,9 @@ def test_f32_data_with_half_precision_compute(env, compute, layout):
 
 @pytest.mark.parametrize("layout", sorted(LAYOUTS))
 def test_k_split_of_small_problems(env, layout):
-    """Few tiles and a long K: every tile is cut into K ranges (one CTA each), the partial sums travel through the
-    workspace and are added in a fixed order. With and without the workspace the results must both satisfy the
-    bounds; the split one must be reproducible bit for bit."""
+    """Few tiles and a long K: every tile is cut into K ranges (the CTAs of one cluster), the partial sums travel
+    through the owner's shared memory and are added in a fixed order; no workspace is involved. Split and whole
+    results must both satisfy the bounds; the split one must be reproducible bit for bit."""
     ht, h = env
     modeA, modeB = LAYOUTS[layout]
     M, N, K = 256, 192, 1024
@@ -176,8 +176,11 @@ def test_k_split_of_small_problems(env, layout):
     dA, dB, dD = (h.tensor_descriptor(l, None, ht.R_32F) for l in (lA, lB, lD))
     cd = h.contraction_descriptor(dA, modeA, dB, modeB, dD, [0, 1], dD, [0, 1], ht.COMPUTE_32F)
     find = h.contraction_find()
-    assert h.contraction_workspace_size(cd, find, ht.WORKSPACE_RECOMMENDED) > 0
-    assert h.contraction_workspace_size(cd, find, ht.WORKSPACE_MIN) == 0
+    assert h.contraction_workspace_size(cd, find, ht.WORKSPACE_RECOMMENDED) == 0
+    assert "splitK=4" in ht.describe_contraction_plan(lA, orc.packed_strides(lA, False), modeA, ht.R_32F, lB,
+                                                      orc.packed_strides(lB, False), modeB, ht.R_32F, lD,
+                                                      orc.packed_strides(lD, False), [0, 1], ht.R_32F, True,
+                                                      ht.COMPUTE_32F)
     first = None
     for _ in range(2):
         got, exp, td = run_contraction(ht, h, ext, modeA, modeB, [0, 1], typeAB=orc.F32, alpha=1.5, beta=0.5)

@@ -120,8 +120,8 @@ def test_contraction_fp32_tensor_core_layouts(ht):
 
 def test_contraction_k_split_plans(ht):
     """Few tiles and a long K: the fp32 tensor-core plan cuts K into up to four ranges (at least four K blocks
-    each, never more CTAs than SMs) and asks for 32 KiB of flags plus one 128 x 128 fp32 slot per extra range
-    and tile; many tiles or a short K do not split. The f16 plan asks for tail-split workspace only when the
+    each, never more CTAs than SMs), one CTA of a cluster each; the sums meet in shared memory, so no workspace is
+    asked for. Many tiles or a short K do not split. The f16 plan asks for tail-split workspace only when the
     tile count leaves a tail of CTA pairs."""
     import re
 
@@ -132,7 +132,7 @@ def test_contraction_k_split_plans(ht):
     d = plan(256, 192, 1024, ht.R_32F)  # 2 x 3 tiles of 128 x 64, 32 K blocks
     m = re.search(r"splitK=(\d+) workspace=(\d+)", d)
     assert "kind=tf32x3" in d and m, d
-    assert int(m.group(1)) == 4 and int(m.group(2)) == 32768 + 6 * 3 * 128 * 128 * 4
+    assert int(m.group(1)) == 4 and int(m.group(2)) == 0
     d = plan(576, 576, 576, ht.R_32F)  # 5 x 9 tiles of 128 x 64: three ranges fit the SM count
     m = re.search(r"splitK=(\d+)", d)
     assert m and int(m.group(1)) == 3, d
