@@ -145,6 +145,11 @@ namespace htb
             const int      numTiles   = a.tilesM * a.tilesN;
             const uint32_t tmemCols   = (2 * tileN <= 128) ? 128 : (2 * tileN <= 256 ? 256 : 512);
 
+            if(threadIdx.x == 32)
+            {
+                prefetchTensorMap(&mapA);
+                prefetchTensorMap(&mapB);
+            }
             if(threadIdx.x == 0)
             {
                 abortFlag = 0;
@@ -517,6 +522,12 @@ namespace htb
             const int      clusterId   = blockIdx.x >> 1;
             const int      numClusters = gridDim.x >> 1;
 
+            if(threadIdx.x == 32)
+            {
+                prefetchTensorMap(&mapA);
+                prefetchTensorMap(&mapB);
+                prefetchTensorMap(&mapB64);
+            }
             if(threadIdx.x == 0)
             {
                 abortFlag = 0;

@@ -343,6 +343,11 @@ namespace htb
             };
             constexpr uint32_t kTmemCols = 512;
 
+            if(threadIdx.x == 32)
+            {
+                prefetchTensorMap(&mapA);
+                prefetchTensorMap(&mapB);
+            }
             if(threadIdx.x == 0)
             {
                 abortFlag = 0;

@@ -568,6 +568,12 @@ namespace htb
             __shared__ int abortFlag;
             __shared__ int coordB[kMaxInStages][5], coordOut[kOutStages][5];
 
+            if(threadIdx.x == 32)
+            {
+                // start fetching the tensor maps (kernel parameters) before the first copy needs them
+                asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mapA)) : "memory");
+                asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mapB)) : "memory");
+            }
             if(threadIdx.x == 0)
             {
                 abortFlag = 0;

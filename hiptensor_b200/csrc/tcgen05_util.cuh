@@ -19,6 +19,12 @@ namespace htb
             return uint32_t(__cvta_generic_to_shared(p));
         }
 
+        // starts fetching a tensor map (a kernel parameter) so that the first TMA instruction does not wait for it
+        __device__ __forceinline__ void prefetchTensorMap(const CUtensorMap* map)
+        {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+        }
+
         __device__ __forceinline__ void mbarInit(uint32_t bar, uint32_t count)
         {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
