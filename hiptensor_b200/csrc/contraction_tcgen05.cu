@@ -794,6 +794,11 @@ namespace htb
                                 break;
                         }
                     }
+                    // D offsets of the eight rows of this lane's group of eight lanes (for the line-wise stores below)
+                    int64_t rowOff[8];
+#pragma unroll
+                    for(int k = 0; k < 8; k++)
+                        rowOff[k] = __shfl_sync(0xffffffffu, offM, (lane & ~7) + k);
                     for(int c0 = 0; c0 < ncols; c0 += 32)
                     {
                         uint32_t v[32];
@@ -834,10 +839,77 @@ namespace htb
                                 }
                             }
                         }
-                        if(offM < 0)
-                            continue;
                         const int64_t first     = cols[c0];
                         const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] == first + 31;
+                        if constexpr(sizeof(TD) == 4)
+                        {
+                            // Line-wise stores. A lane holds 32 consecutive floats of its own row; stored as they are, one
+                            // instruction touches 32 different lines, and that request stream was measured to slow the
+                            // MMAs of the next tile (it shares the way out of the SM with the operand traffic between the
+                            // two CTAs): the first stages of a tile took twice as long while the previous tile was being
+                            // stored. The eight lanes of a group therefore transpose their 8 x 8 blocks of four floats
+                            // with three rounds of shuffles, after which lane m holds quarter-line m of each of the
+                            // group's eight rows and one store instruction writes four whole 128-byte lines.
+                            if(fullChunk && __all_sync(0xffffffffu, offM < 0 || ((offM + first) & 3) == 0))
+                            {
+                                float4 o[8];
+#pragma unroll
+                                for(int c = 0; c < 8; c++)
+                                {
+                                    o[c].x = __fmul_rn(a.alpha, __uint_as_float(v[4 * c]));
+                                    o[c].y = __fmul_rn(a.alpha, __uint_as_float(v[4 * c + 1]));
+                                    o[c].z = __fmul_rn(a.alpha, __uint_as_float(v[4 * c + 2]));
+                                    o[c].w = __fmul_rn(a.alpha, __uint_as_float(v[4 * c + 3]));
+                                }
+                                const int m = lane & 7;
+#pragma unroll
+                                for(int sft = 4; sft >= 1; sft >>= 1)
+                                {
+                                    const bool hi = (m & sft) != 0;
+#pragma unroll
+                                    for(int c = 0; c < 8; c++)
+                                    {
+                                        if(c & sft)
+                                            continue;
+                                        // the lane with the bit clear gives its o[c | sft] and takes the partner's o[c]
+                                        const float4 snd = hi ? o[c] : o[c | sft];
+                                        float4       rcv;
+                                        rcv.x = __shfl_xor_sync(0xffffffffu, snd.x, sft);
+                                        rcv.y = __shfl_xor_sync(0xffffffffu, snd.y, sft);
+                                        rcv.z = __shfl_xor_sync(0xffffffffu, snd.z, sft);
+                                        rcv.w = __shfl_xor_sync(0xffffffffu, snd.w, sft);
+                                        if(hi)
+                                            o[c] = rcv;
+                                        else
+                                            o[c | sft] = rcv;
+                                    }
+                                }
+                                // o[k] is now quarter-line m of row k of the group
+                                if(a.bilinear)
+                                {
+                                    float4 c4[8]; // all loads of C ahead of the stores (C may be D)
+#pragma unroll
+                                    for(int k = 0; k < 8; k++)
+                                        c4[k] = rowOff[k] >= 0 ? *(const float4*)((const float*)C + rowOff[k] + first + 4 * m)
+                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                                    for(int k = 0; k < 8; k++)
+                                    {
+                                        o[k].x = __fadd_rn(o[k].x, __fmul_rn(a.beta, c4[k].x));
+                                        o[k].y = __fadd_rn(o[k].y, __fmul_rn(a.beta, c4[k].y));
+                                        o[k].z = __fadd_rn(o[k].z, __fmul_rn(a.beta, c4[k].z));
+                                        o[k].w = __fadd_rn(o[k].w, __fmul_rn(a.beta, c4[k].w));
+                                    }
+                                }
+#pragma unroll
+                                for(int k = 0; k < 8; k++)
+                                    if(rowOff[k] >= 0)
+                                        *(float4*)((float*)D + rowOff[k] + first + 4 * m) = o[k];
+                                continue;
+                            }
+                        }
+                        if(offM < 0)
+                            continue;
                         if(fullChunk && sizeof(TD) == 4 && ((offM + first) & 3) == 0)
                         {
                             float*       dst = (float*)D + offM + first;
