@@ -745,13 +745,83 @@ namespace htb
                             }
                         }
                     }
-                    if(active && offM >= 0 && part == 0 && alive)
+                    if(active && part == 0 && alive)
                     {
+                        // D offsets of the eight rows of this lane's group of eight lanes
+                        int64_t rowOff[8];
+#pragma unroll
+                        for(int k = 0; k < 8; k++)
+                            rowOff[k] = __shfl_sync(0xffffffffu, offM, (lane & ~7) + k);
 #pragma unroll
                         for(int c0 = 0; c0 < 64; c0 += 32)
                         {
                             const int64_t first     = cols[c0];
                             const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] == first + 31;
+                            if(fullChunk && __all_sync(0xffffffffu, offM < 0 || ((offM + first) & 3) == 0))
+                            {
+                                // Line-wise: the eight lanes of a group exchange quarter lines (three rounds of
+                                // shuffles, in place in the sums) so that lane m ends up with quarter-line m of each of
+                                // the group's eight rows; a load or store instruction then covers four whole 128-byte
+                                // lines instead of 32 different ones.
+                                const int m = lane & 7;
+#pragma unroll
+                                for(int j = 0; j < 32; j++)
+                                    sum[c0 + j] = __fmul_rn(a.alpha, sum[c0 + j]);
+#pragma unroll
+                                for(int sft = 4; sft >= 1; sft >>= 1)
+                                {
+                                    const bool hi = (m & sft) != 0;
+#pragma unroll
+                                    for(int c = 0; c < 8; c++)
+                                    {
+                                        if(c & sft)
+                                            continue;
+#pragma unroll
+                                        for(int e = 0; e < 4; e++)
+                                        {
+                                            float&      lo  = sum[c0 + 4 * c + e];
+                                            float&      up  = sum[c0 + 4 * (c | sft) + e];
+                                            const float rcv = __shfl_xor_sync(0xffffffffu, hi ? lo : up, sft);
+                                            if(hi)
+                                                lo = rcv;
+                                            else
+                                                up = rcv;
+                                        }
+                                    }
+                                }
+                                // sum[c0 + 4 k + e] is now element e of quarter-line m of row k of the group
+#pragma unroll
+                                for(int k0 = 0; k0 < 8; k0 += 4)
+                                {
+                                    float4 c4[4]; // loads of C ahead of the stores (C may be D)
+                                    if(a.bilinear)
+                                    {
+#pragma unroll
+                                        for(int q = 0; q < 4; q++)
+                                            c4[q] = rowOff[k0 + q] >= 0 ? *(const float4*)(C + rowOff[k0 + q] + first + 4 * m)
+                                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                                    }
+#pragma unroll
+                                    for(int q = 0; q < 4; q++)
+                                    {
+                                        const int k = k0 + q;
+                                        float4    o = make_float4(sum[c0 + 4 * k], sum[c0 + 4 * k + 1], sum[c0 + 4 * k + 2],
+                                                                  sum[c0 + 4 * k + 3]);
+                                        if(a.bilinear)
+                                        {
+                                            o.x = __fadd_rn(o.x, __fmul_rn(a.beta, c4[q].x));
+                                            o.y = __fadd_rn(o.y, __fmul_rn(a.beta, c4[q].y));
+                                            o.z = __fadd_rn(o.z, __fmul_rn(a.beta, c4[q].z));
+                                            o.w = __fadd_rn(o.w, __fmul_rn(a.beta, c4[q].w));
+                                        }
+                                        if(rowOff[k] >= 0)
+                                            *(float4*)(D + rowOff[k] + first + 4 * m) = o;
+                                    }
+                                }
+                                continue;
+                            }
+                            if(offM < 0)
+                                continue;
                             if(fullChunk && ((offM + first) & 3) == 0)
                             {
                                 // 32 consecutive floats of this row: eight 128-bit stores
