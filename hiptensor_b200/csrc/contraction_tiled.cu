@@ -379,6 +379,10 @@ namespace htb
             CtrArgs base;
             int     vecA, vecB; // 16-byte copies are legal for this operand
             int     k32; // K fits 32 bits: the producers decompose K indices with 32-bit divisions
+            // K split of problems with few tiles: a tile's K steps are cut over the 2 or 4 CTAs of a thread-block
+            // cluster. Afterwards the CTAs exchange accumulators over the cluster network so that each ends up with the
+            // full sums of its share of the tile's row blocks (summed in a fixed order) and stores that share.
+            int     parts;
             int*    status; // the handle's device status word (raised when a bounded wait runs out)
         };
 
@@ -419,9 +423,12 @@ namespace htb
             __shared__ int abortFlag;
 
             const int     tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-            const int64_t tileM = blockIdx.x / a.tilesN, tileN = blockIdx.x % a.tilesN;
+            const int     parts = args.parts, part = int(blockIdx.x) % parts; // part = rank in the tile's cluster
+            const int64_t tile  = blockIdx.x / parts;
+            const int64_t tileM = tile / a.tilesN, tileN = tile % a.tilesN;
             const int64_t m0 = tileM * DM, n0 = tileN * DN;
-            const int     nkt = int((a.K + DK - 1) / DK); // the launcher refuses K beyond 2^31 steps
+            const int     nktAll = int((a.K + DK - 1) / DK); // the launcher refuses K beyond 2^31 steps
+            const int     kt0 = int(int64_t(nktAll) * part / parts), nkt = int(int64_t(nktAll) * (part + 1) / parts) - kt0;
 
             if(tid < DM)
             {
@@ -475,7 +482,7 @@ namespace htb
                         break;
                     if(lane < DK)
                     {
-                        const int64_t kk = int64_t(kt) * DK + lane;
+                        const int64_t kk = int64_t(kt0 + kt) * DK + lane;
                         int64_t       oa = -1, ob = -1;
                         if(kk < a.K)
                         {
@@ -548,6 +555,11 @@ namespace htb
                 asm volatile("cp.async.wait_all;" ::: "memory");
                 if(lane == 0 && *abortP && args.status)
                     atomicExch(args.status, 3);
+                if(parts > 1)
+                {
+                    clusterSync(); // the two meeting points of the accumulator exchange (see the MMA warps)
+                    clusterSync();
+                }
                 return;
             }
 
@@ -598,17 +610,68 @@ namespace htb
                     ph ^= 1u;
                 }
             }
-            if(!ok)
+            if(!ok && lane == 0 && args.status)
+                atomicExch(args.status, 3);
+            if(parts > 1)
             {
-                if(lane == 0 && args.status)
-                    atomicExch(args.status, 3);
-                return;
+                // Row block i of every warp tile belongs to part i * parts / 4. Each thread sends the eight sums of a
+                // foreign row block to its owner's shared memory (the copy ring, idle once every CTA of the cluster has
+                // left its K loop), slot [sender][i % (4 / parts)][thread]; then every owner adds the parts in order.
+                const int      per  = 4 / parts; // row blocks per part
+                const uint32_t zone = smemAddr(sA);
+                clusterSync();
+#pragma unroll
+                for(int i = 0; i < 4; i++)
+                {
+                    const int owner = i / per;
+                    if(owner == part)
+                        continue;
+                    const uint32_t dst = mapToRank(zone + uint32_t(((part * per + i % per) * THREADS + tid) * 64), uint32_t(owner));
+#pragma unroll
+                    for(int j = 0; j < 4; j++)
+                        asm volatile("st.shared::cluster.v2.f64 [%0], {%1, %2};" ::"r"(dst + 16u * uint32_t(j)), "d"(acc[i][j][0]),
+                                     "d"(acc[i][j][1])
+                                     : "memory");
+                }
+                clusterSync();
+#pragma unroll
+                for(int i = 0; i < 4; i++)
+                {
+                    if(i / per != part)
+                        continue;
+                    double tot[4][2];
+#pragma unroll
+                    for(int j = 0; j < 4; j++)
+                        tot[j][0] = tot[j][1] = 0.0;
+                    for(int q = 0; q < parts; q++)
+                    {
+                        const double2* src = reinterpret_cast<const double2*>(
+                            reinterpret_cast<const unsigned char*>(sA) + size_t((q * per + i % per) * THREADS + tid) * 64);
+#pragma unroll
+                        for(int j = 0; j < 4; j++)
+                        {
+                            const double2 v = (q == part) ? make_double2(acc[i][j][0], acc[i][j][1]) : src[j];
+                            tot[j][0] += v.x;
+                            tot[j][1] += v.y;
+                        }
+                    }
+#pragma unroll
+                    for(int j = 0; j < 4; j++)
+                    {
+                        acc[i][j][0] = tot[j][0];
+                        acc[i][j][1] = tot[j][1];
+                    }
+                }
             }
+            if(!ok)
+                return;
             // C may be D, so a load of C cannot move above an earlier store to D: the eight values of C that a row
             // block needs are loaded first, then the eight results are stored (4 memory round trips instead of 32)
 #pragma unroll
             for(int i = 0; i < 4; i++)
             {
+                if(parts > 1 && i / (4 / parts) != part)
+                    continue; // another CTA of the cluster holds and stores this row block
                 const int64_t om = offDm[wm * 32 + i * 8 + (lane >> 2)];
                 if(om < 0)
                     continue;
@@ -658,9 +721,10 @@ namespace htb
         }
 
         cudaError_t launchDmma(const ContractionPlan& p, float alpha, const void* A, const void* B, float beta,
-                               const void* C, void* D, int* deviceStatus, cudaStream_t stream)
+                               const void* C, void* D, int smCountIn, int* deviceStatus, cudaStream_t stream)
         {
-            DmmaArgs args{};
+            const int smCount = smCountIn > 0 ? smCountIn : 148;
+            DmmaArgs  args{};
             args.base            = makeArgs(p, alpha, beta, C);
             CtrArgs&      a      = args.base;
             const int64_t tilesM = (p.M + DM - 1) / DM, tilesN = (p.N + DN - 1) / DN;
@@ -674,6 +738,15 @@ namespace htb
                 args.vecA = args.vecB = 0;
             args.k32    = p.K < (int64_t(1) << 31) ? 1 : 0;
             args.status = deviceStatus;
+            // few tiles and a long K: 4 or 2 CTAs per tile, at least four K steps each, never more CTAs than SMs
+            const int64_t tiles = tilesM * tilesN, steps = (p.K + kDmmaK - 1) / kDmmaK;
+            args.parts          = 1;
+            for(int q = 4; q >= 2; q >>= 1)
+                if(tiles * q <= smCount && steps >= 4 * q && getenv("HTB_DMMA_NOSPLIT") == nullptr)
+                {
+                    args.parts = q;
+                    break;
+                }
             const size_t smem = sizeof(double) * kDmmaStages * (kDmmaATile + kDmmaBTile);
             static unsigned char attr[kMaxDevices] = {};
             if(firstUseOnDevice(attr))
@@ -683,7 +756,27 @@ namespace htb
                 if(e != cudaSuccess)
                     return e;
             }
-            contraction_dmma_kernel<<<unsigned(tilesM * tilesN), kWsThreads, smem, stream>>>(
+            if(args.parts > 1)
+            {
+                cudaLaunchConfig_t  cfg{};
+                cudaLaunchAttribute attr[1];
+                attr[0].id               = cudaLaunchAttributeClusterDimension;
+                attr[0].val.clusterDim.x = unsigned(args.parts);
+                attr[0].val.clusterDim.y = 1;
+                attr[0].val.clusterDim.z = 1;
+                cfg.gridDim              = dim3(unsigned(tiles * args.parts));
+                cfg.blockDim             = dim3(kWsThreads);
+                cfg.dynamicSmemBytes     = smem;
+                cfg.stream               = stream;
+                cfg.attrs                = attr;
+                cfg.numAttrs             = 1;
+                cudaError_t e = cudaLaunchKernelEx(&cfg, contraction_dmma_kernel, (const double*)A, (const double*)B,
+                                                   (const double*)C, (double*)D, args);
+                if(e == cudaSuccess)
+                    noteLaunch("contraction_tiled_dmma");
+                return e;
+            }
+            contraction_dmma_kernel<<<unsigned(tiles), kWsThreads, smem, stream>>>(
                 (const double*)A, (const double*)B, (const double*)C, (double*)D, args);
             noteLaunch("contraction_tiled_dmma");
             return cudaGetLastError();
@@ -756,7 +849,7 @@ namespace htb
         case CUDA_R_64F:
             if(ct == HIPTENSOR_COMPUTE_64F)
             {
-                return launchDmma(plan, alpha, A, B, beta, C, D, deviceStatus, stream);
+                return launchDmma(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
             }
             return launchTiled<double, double, 0>(plan, alpha, A, B, beta, C, D, stream);
         case CUDA_R_16F:

@@ -143,11 +143,14 @@ F64_LAYOUTS = {"kk": ([0, 2], [1, 2]), "mn_mn": ([2, 0], [2, 1]), "k_mn": ([0, 2
 
 
 @pytest.mark.parametrize("layout", sorted(F64_LAYOUTS))
-@pytest.mark.parametrize("shape", [(256, 192, 96), (200, 132, 72), (130, 70, 34), (129, 67, 35), (64, 64, 8)])
+@pytest.mark.parametrize("shape", [(256, 192, 96), (200, 132, 72), (130, 70, 34), (129, 67, 35), (64, 64, 8),
+                                   (200, 132, 520), (129, 67, 131), (520, 260, 2050)])
 def test_fp64_operand_layouts(env, layout, shape):
     """fp64 on the FP64 tensor pipe with each operand contiguous along K or along its rows. Even extents take the
     16-byte asynchronous copies (pairs along the contiguous direction), odd ones the 8-byte copies; ragged M, N
-    and K tails (K not a multiple of the 16-wide step, shorter than the copy ring) are zero-filled."""
+    and K tails (K not a multiple of the 16-wide step, shorter than the copy ring) are zero-filled. The last three
+    shapes have few tiles and a long K: their K steps are cut over clusters of four or two CTAs (uneven ranges,
+    ragged last step) that exchange accumulators through shared memory."""
     ht, h = env
     M, N, K = shape
     modeA, modeB = F64_LAYOUTS[layout]
