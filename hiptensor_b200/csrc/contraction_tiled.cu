@@ -738,11 +738,12 @@ namespace htb
                 args.vecA = args.vecB = 0;
             args.k32    = p.K < (int64_t(1) << 31) ? 1 : 0;
             args.status = deviceStatus;
-            // few tiles and a long K: 4 or 2 CTAs per tile, at least four K steps each, never more CTAs than SMs
+            // few tiles and a long K: 4 or 2 CTAs per tile, at least four K steps each, never more CTAs than fit at once
+            // (two per SM)
             const int64_t tiles = tilesM * tilesN, steps = (p.K + kDmmaK - 1) / kDmmaK;
             args.parts          = 1;
             for(int q = 4; q >= 2; q >>= 1)
-                if(tiles * q <= smCount && steps >= 4 * q && getenv("HTB_DMMA_NOSPLIT") == nullptr)
+                if(tiles * q <= 2 * int64_t(smCount) && steps >= 4 * q && getenv("HTB_DMMA_NOSPLIT") == nullptr)
                 {
                     args.parts = q;
                     break;
