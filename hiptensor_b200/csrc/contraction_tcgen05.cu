@@ -1058,7 +1058,10 @@ namespace htb
             if(!encode)
                 return cudaErrorNotSupported;
             const bool  bf16 = (p.typeA == CUDA_R_16BF);
-            const bool  pair = (p.pair != 0) && getenv("HTB_TC_SINGLE") == nullptr;
+            // HTB_TC_PAIR: CTA pairs wherever they can run, not only where they pay off (tests of the pair kernel on
+            // small problems)
+            const bool  pair = (p.pair != 0 || (p.pairOk != 0 && getenv("HTB_TC_PAIR") != nullptr))
+                              && getenv("HTB_TC_SINGLE") == nullptr;
             const int*  boxN = pair ? p.boxN128 : p.boxN;
             const int   layout = (p.aMajor ? 1 : 0) | (p.bMajor ? 2 : 0);
             const RowGroupView vm = viewOf(p.m, p.nm, p.aMajor ? 0 : -1), vn = viewOf(p.n, p.nn, p.bMajor ? p.nFast : -1);

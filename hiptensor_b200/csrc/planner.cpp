@@ -553,7 +553,13 @@ namespace htb
                 out->tileK = 64;
                 out->rowsM = out->aMajor ? 128 : boxDecompose(gm, nm, 128, out->boxM);
                 out->rowsN = 0;
-                for(int tn = (out->N >= 256 ? 256 : (out->N >= 128 ? 128 : 64)); tn >= 64 && out->rowsN == 0; tn >>= 1)
+                // the widest tile that still gives half of the SMs one (small problems are latency bound: more,
+                // smaller tiles shorten the loads and the epilogue of each CTA)
+                const int64_t smsH = smCount > 0 ? smCount : 148;
+                int           tn0  = out->N >= 256 ? 256 : (out->N >= 128 ? 128 : 64);
+                while(tn0 > 64 && ((out->M + 127) / 128) * ((out->N + tn0 - 1) / tn0) < smsH / 2)
+                    tn0 >>= 1;
+                for(int tn = tn0; tn >= 64 && out->rowsN == 0; tn >>= 1)
                 {
                     out->tileN = tn;
                     out->rowsN = out->bMajor ? tn : boxDecompose(gn, nn, tn, out->boxN);
@@ -562,13 +568,17 @@ namespace htb
                 out->stages = (out->tileN == 256) ? 4 : 6;
                 // large problems: 256 x 256 tiles over CTA pairs
                 out->rowsN128 = out->bMajor ? 128 : boxDecompose(gn, nn, 128, out->boxN128);
-                out->pair     = (tc && out->tileN == 256 && out->rowsN128 == 128 && out->rowsM == 128 && out->M >= 512
-                             && out->N >= 512)
-                                    ? 1
-                                    : 0;
+                // (possible from 512 x 512 on; they pay off once the 256 x 256 tiles occupy most of the CTA pairs:
+                // measured with K = 4096, 32 tiles 34 us on single CTAs against 47 on pairs, 64 tiles 40 against 40,
+                // 128 tiles 71 against 63, 256 tiles 124 against 106)
+                out->pairOk = (tc && out->N >= 256 && out->rowsN128 == 128 && out->rowsM == 128 && out->M >= 512
+                               && out->N >= 512)
+                                  ? 1
+                                  : 0;
+                out->pair   = (out->pairOk && ((out->M + 255) / 256) * ((out->N + 255) / 256) >= (smsH * 7) / 16) ? 1 : 0;
             }
             out->kind = tc ? CK_TCGEN05 : CK_TILED_SIMT;
-            if(tc && out->pair)
+            if(tc && out->pairOk)
             {
                 // scratch for the tail split, sized for the largest need over the pair counts the
                 // device may grant (GPCs with an odd SM count lose a pair)

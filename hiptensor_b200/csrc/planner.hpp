@@ -109,6 +109,7 @@ namespace htb
         int boxM[4], boxN[4]; // TMA box extent per folded M / N mode (product = rows gathered per tile)
         int rowsM, rowsN; // rows of the tile that the boxes fill (<= tileM / tileN)
         int pair; // 256 x 256 tile over a CTA pair (tcgen05 cta_group::2), each CTA loading 128 rows of B
+        int pairOk; // CK_TCGEN05: the pair kernel can run this problem (pair says whether it is the better choice)
         int boxN128[4], rowsN128; // N boxes of one CTA's sub-tile in the pair kernels (128 rows; 64 for CK_TF32X3)
         int aKContig, bKContig; // operand has its K group folded to one stride-1 mode
         // CK_TF32X3 only: 0 = operand K-major (rows gathered by boxM / boxN), 1 = MN-major (32-row chunks along

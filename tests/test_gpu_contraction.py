@@ -17,6 +17,15 @@ from oracle import binding as orc
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(scope="module", autouse=True)
+def pairs_wherever_possible():
+    """The library takes CTA pairs (256 x 256 tiles) only from about two waves of pairs on; this module runs the
+    pair kernel on small problems too (odd tile counts, K split, half tiles), as HTB_TC_PAIR allows."""
+    os.environ["HTB_TC_PAIR"] = "1"
+    yield
+    os.environ.pop("HTB_TC_PAIR", None)
+
+
 @pytest.fixture(scope="module")
 def env():
     import hiptensor_b200 as ht

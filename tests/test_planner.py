@@ -156,6 +156,22 @@ def test_contraction_config4(ht):
     assert "kind=tcgen05" in d and "major=mn/mn" in d and "swapped=1" in d and "pair" in d
 
 
+def test_contraction_f16_tile_choice_by_size(ht):
+    """Small problems take narrow tiles on single CTAs (more CTAs, shorter epilogues); CTA pairs with 256 x 256
+    tiles are kept for problems whose tiles occupy most of the pairs."""
+    def plan(M, N, K):
+        return ht.describe_contraction_plan([M, K], [K, 1], [0, 2], ht.R_16F, [N, K], [K, 1], [1, 2], ht.R_16F, [M, N],
+                                            [N, 1], [0, 1], ht.R_32F, False, ht.COMPUTE_32F)
+
+    d = plan(512, 512, 512)
+    assert "tile=128x64x64" in d and not d.endswith("pair"), d
+    d = plan(2048, 2048, 2048)
+    assert "tile=128x256x64" in d and d.rstrip().endswith("pair"), d  # 64 pair tiles
+    d = plan(512, 4096, 4096)
+    assert "tile=128x128x64" in d and not d.rstrip().endswith("pair"), d  # 32 pair tiles: single CTAs
+    assert plan(4096, 4096, 4096).rstrip().endswith("pair")
+
+
 def test_contraction_config5(ht):
     lA, lB, lD = [16, 48, 16, 48, 16], [48, 48, 48, 48], [16, 16, 16, 48, 48]
     m0, m1, m2, n0, n1, k0, k1 = range(7)
