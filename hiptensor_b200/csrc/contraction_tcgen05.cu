@@ -58,6 +58,7 @@ namespace htb
             float   alpha, beta;
             int     bilinear;
             int     nContig; // N is one folded mode with stride 1 in D and D is 16-byte aligned
+            int     parts; // single-CTA kernel: K ranges per tile (CTAs of one cluster); 0 or 1 = no split
             int     probe; // measurement aid, bit mask: 1 = producer skips the loads, 2 = issuer skips the MMAs,
                            // 4 = epilogue skips the stores (results invalid)
             int*    status;
@@ -143,6 +144,16 @@ namespace htb
             const uint32_t aBytes     = kTileM * kTileK * 2; // the stage always reserves a full A tile
             const uint32_t stageStride = aBytes + uint32_t(tileN) * kTileK * 2;
             const int      numTiles   = a.tilesM * a.tilesN;
+            // K split of problems with few tiles: `parts` CTAs per tile (one thread-block cluster), each with a range
+            // of the K blocks; unit u = part (u % parts) of tile (u / parts). Parts 1.. hand their accumulators to
+            // part 0 through its shared memory (see the epilogue). With parts > 1 every CTA has exactly one unit.
+            const int      parts      = a.parts > 1 ? a.parts : 1;
+            const int      numUnits   = numTiles * parts;
+            auto           kRange     = [&](int u, int& kb0, int& kb1) {
+                const int part = u % parts;
+                kb0            = int((long long)a.kBlocks * part / parts);
+                kb1            = int((long long)a.kBlocks * (part + 1) / parts);
+            };
             const uint32_t tmemCols   = (2 * tileN <= 128) ? 128 : (2 * tileN <= 256 ? 256 : 512);
 
             if(threadIdx.x == 32)
@@ -186,9 +197,12 @@ namespace htb
                     int      stage = 0;
                     uint32_t phase = 0;
                     bool     ok    = true;
-                    for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x)
+                    for(int u = blockIdx.x; u < numUnits && ok; u += gridDim.x)
                     {
+                        const int t  = u / parts;
                         const int tm = t % a.tilesM, tn = t / a.tilesM;
+                        int       kb0, kb1;
+                        kRange(u, kb0, kb1);
                         int       cA[5] = {0, 0, 0, 0, 0}, cB[5] = {0, 0, 0, 0, 0};
                         TfChunks  qA{}, qB{};
                         if constexpr(LAYOUT & 1)
@@ -199,7 +213,7 @@ namespace htb
                             qB = tfChunksOf(a.gn, tfTileOf(a.gn, tn));
                         else
                             tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB + 1);
-                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        for(int kb = kb0; kb < kb1; kb++)
                         {
                             ok = mbarWait(smemAddr(&emptyBar[stage]), phase ^ 1, abortP);
                             if(!ok)
@@ -239,6 +253,12 @@ namespace htb
                         }
                     }
                 }
+                if(parts > 1)
+                {
+                    __syncwarp();
+                    clusterSync(); // the two meeting points of the K-split hand-over (see the epilogue)
+                    clusterSync();
+                }
             }
             else if(warp == 1)
             {
@@ -249,16 +269,18 @@ namespace htb
                     uint32_t phase = 0;
                     int      local = 0;
                     bool     ok    = true;
-                    for(int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, local++)
+                    for(int u = blockIdx.x; u < numUnits && ok; u += gridDim.x, local++)
                     {
                         const int      acc      = local & 1;
                         const uint32_t accPhase = (local >> 1) & 1;
+                        int            kb0, kb1;
+                        kRange(u, kb0, kb1);
                         ok = mbarWait(smemAddr(&tmemEmptyBar[acc]), accPhase ^ 1, abortP);
                         if(!ok)
                             break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint32_t dTmem = tmem + uint32_t(acc * tileN);
-                        for(int kb = 0; kb < a.kBlocks; kb++)
+                        for(int kb = kb0; kb < kb1; kb++)
                         {
                             ok = mbarWait(smemAddr(&fullBar[stage]), phase, abortP);
                             if(!ok)
@@ -273,7 +295,7 @@ namespace htb
 #pragma unroll
                             for(int k = 0; k < kTileK / 16; k++)
                             {
-                                const uint32_t accumulate = (kb | k) ? 1u : 0u;
+                                const uint32_t accumulate = (kb != kb0 || k) ? 1u : 0u;
                                 asm volatile("{\n\t.reg .pred p;\n\t"
                                              "setp.ne.b32 p, %4, 0;\n\t"
                                              "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
@@ -297,6 +319,12 @@ namespace htb
                                          : "memory");
                     }
                 }
+                if(parts > 1)
+                {
+                    __syncwarp();
+                    clusterSync();
+                    clusterSync();
+                }
             }
             else
             {
@@ -305,8 +333,23 @@ namespace htb
                 const int row  = quad * 32 + lane;
                 int64_t*  cols = colOff[quad];
                 int       local = 0;
-                for(int t = blockIdx.x; t < numTiles; t += gridDim.x, local++)
+                int       syncs = 0; // cluster meeting points of the K-split hand-over passed so far
+                auto      loadChunk = [&](uint32_t addr, uint32_t(&v)[32]) {
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]),
+                          "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]),
+                          "=r"(v[30]), "=r"(v[31])
+                        : "r"(addr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                };
+                for(int u = blockIdx.x; u < numUnits; u += gridDim.x, local++)
                 {
+                    const int      t = u / parts, part = u % parts;
                     const int      acc      = local & 1;
                     const uint32_t accPhase = (local >> 1) & 1;
                     const int      tm = t % a.tilesM, tn = t / a.tilesM;
@@ -339,20 +382,57 @@ namespace htb
                         break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(acc * tileN);
+                    // K split: parts 1.. store their raw accumulators into part 0's stage memory (idle once every CTA of
+                    // the cluster has its sums), layout [part - 1][32-column chunk][column group of four][128 rows] of
+                    // 16 bytes; part 0 adds them chunk by chunk before its usual epilogue
+                    const uint32_t zone = smemAddr(tiles) + uint32_t(row) * 16u;
+                    if(parts > 1)
+                    {
+                        clusterSync();
+                        syncs++;
+                        if(part > 0)
+                        {
+                            for(int c0 = 0; c0 < tileN; c0 += 32)
+                            {
+                                uint32_t v[32];
+                                loadChunk(taddr + uint32_t(c0), v);
+                                const uint32_t dst
+                                    = mapToRank(zone + uint32_t(((part - 1) * (tileN >> 5) + (c0 >> 5)) * 8) * 2048u, 0);
+#pragma unroll
+                                for(int j = 0; j < 8; j++)
+                                    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + uint32_t(j) * 2048u),
+                                                 "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                                                 : "memory");
+                            }
+                            clusterSync();
+                            syncs++;
+                            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                            mbarArrive(smemAddr(&tmemEmptyBar[acc]));
+                            continue;
+                        }
+                        clusterSync();
+                        syncs++;
+                    }
                     for(int c0 = 0; c0 < tileN; c0 += 32)
                     {
                         uint32_t v[32];
-                        asm volatile(
-                            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-                              "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-                              "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-                              "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-                              "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                            : "r"(taddr + uint32_t(c0)));
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        loadChunk(taddr + uint32_t(c0), v);
+                        for(int q = 0; q + 1 < parts; q++)
+                        {
+                            const uint32_t src = zone + uint32_t((q * (tileN >> 5) + (c0 >> 5)) * 8) * 2048u;
+#pragma unroll
+                            for(int j = 0; j < 8; j++)
+                            {
+                                float4 p4;
+                                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                             : "=f"(p4.x), "=f"(p4.y), "=f"(p4.z), "=f"(p4.w)
+                                             : "r"(src + uint32_t(j) * 2048u));
+                                v[4 * j]     = __float_as_uint(__uint_as_float(v[4 * j]) + p4.x);
+                                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + p4.y);
+                                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + p4.z);
+                                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + p4.w);
+                            }
+                        }
                         if(offM < 0)
                             continue;
                         const int64_t first = cols[c0];
@@ -410,6 +490,8 @@ namespace htb
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbarArrive(smemAddr(&tmemEmptyBar[acc]));
                 }
+                for(; parts > 1 && syncs < 2; syncs++)
+                    clusterSync(); // a role that gave up still meets the others
             }
 
             // ---------------------------------------------------------------- teardown
@@ -1226,7 +1308,40 @@ namespace htb
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
             if(e != cudaSuccess)
                 return e;
-            const int grid = int(std::min<int64_t>(int64_t(a.tilesM) * a.tilesN, sms));
+            // Few tiles and a long K: up to four CTAs per tile (one cluster), at least eight K blocks each (with fewer the
+            // hand-over costs more than it saves: 512^3 11.3 us whole, 13.3 split), every unit on
+            // its own SM; the accumulators of parts 1.. must fit into part 0's stages.
+            const int64_t numTiles = int64_t(a.tilesM) * a.tilesN;
+            a.parts                = 1;
+            if(getenv("HTB_TC_NOSPLIT") == nullptr)
+            {
+                const int64_t byTiles = sms / std::max<int64_t>(numTiles, 1), byK = a.kBlocks / 8;
+                const int64_t byRoom  = 1 + int64_t(size_t(a.stages) * (size_t(kTileM) + p.tileN) * kTileK * 2)
+                                               / (int64_t(kTileM) * p.tileN * 4);
+                const int64_t q = std::min<int64_t>(std::min<int64_t>(4, byTiles), std::min<int64_t>(byK, byRoom));
+                if(q >= 2)
+                    a.parts = int(q);
+            }
+            if(a.parts > 1)
+            {
+                cudaLaunchConfig_t  cfg{};
+                cudaLaunchAttribute attr[1];
+                attr[0].id               = cudaLaunchAttributeClusterDimension;
+                attr[0].val.clusterDim.x = unsigned(a.parts);
+                attr[0].val.clusterDim.y = 1;
+                attr[0].val.clusterDim.z = 1;
+                cfg.gridDim              = dim3(unsigned(numTiles * a.parts));
+                cfg.blockDim             = dim3(kThreads);
+                cfg.dynamicSmemBytes     = smem;
+                cfg.stream               = stream;
+                cfg.attrs                = attr;
+                cfg.numAttrs             = 1;
+                e = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, (const TD*)C, (TD*)D, a, idesc);
+                if(e == cudaSuccess)
+                    noteLaunch("contraction_tcgen05");
+                return e;
+            }
+            const int grid = int(std::min<int64_t>(numTiles, sms));
             kernel<<<grid, kThreads, smem, stream>>>(mapA, mapB, (const TD*)C, (TD*)D, a, idesc);
             noteLaunch("contraction_tcgen05");
             return cudaGetLastError();

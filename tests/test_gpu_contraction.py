@@ -308,6 +308,34 @@ def test_tensor_core_path_plain_matrices(env, shape):
     assert 0 <= rel_error(got, exp, td) < 1e-4
 
 
+@pytest.mark.parametrize("shape", [(256, 256, 2048), (384, 200, 1096), (128, 1000, 776), (640, 384, 520)])
+@pytest.mark.parametrize("out", [orc.F32, orc.F16])
+def test_single_cta_kernel_k_split_over_a_cluster(env, shape, out):
+    """Few tiles and a long K on the single-CTA kernel: the K blocks of a tile are cut over the 2-4 CTAs of a
+    cluster (uneven ranges, ragged last block), parts 1.. hand their accumulators to part 0 through its shared
+    memory. Results must satisfy the usual bounds, be reproducible bit for bit, and agree with the unsplit run."""
+    ht, h = env
+    M, N, K = shape
+    ext = {0: M, 1: N, 2: K}
+    runs = []
+    for _ in range(2):
+        got, exp, td = run_contraction(ht, h, ext, [0, 2], [1, 2], [0, 1], typeAB=orc.F16, typeD=out, alpha=1.5, beta=0.5,
+                                       fill="normal")
+        assert ht.last_kernel_name() == "contraction_tcgen05"
+        err = rel_error(got, exp, td)
+        assert 0 <= err < (1e-4 if out == orc.F32 else 2 * 2.0 ** -10), (shape, out, err)
+        runs.append(got)
+    assert runs[0].tobytes() == runs[1].tobytes()
+    os.environ["HTB_TC_NOSPLIT"] = "1"
+    try:
+        whole, exp, td = run_contraction(ht, h, ext, [0, 2], [1, 2], [0, 1], typeAB=orc.F16, typeD=out, alpha=1.5, beta=0.5,
+                                         fill="normal")
+    finally:
+        del os.environ["HTB_TC_NOSPLIT"]
+    # two summation orders of the tensor cores' fp32 accumulation: the bound of the comparison with the oracle
+    assert 0 <= rel_error(whole, runs[0], td) < (1e-4 if out == orc.F32 else 2 * 2.0 ** -10)
+
+
 @pytest.mark.parametrize("dt", [orc.F16, orc.BF16])
 def test_cta_pair_kernel_gathered_odd_tiles(env, dt):
     """256 x 256 tiles over CTA pairs with an odd number of 128-row sub-tiles along M and N (the last
