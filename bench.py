@@ -36,7 +36,7 @@ NOMINAL_FP64_TFLOPS = 40.0  # FP64 tensor pipe, nominal: no measured figure exis
 
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from the
 # ncu captures summarised under profiles/, full-size workloads, one launch each).
-NCU_TRAFFIC_BYTES = {"c2": 2113114000, "c3": 2153492640, "c4": 112387840, "c1": 4088320, "c5": 357141760,
+NCU_TRAFFIC_BYTES = {"c2": 2113114000, "c3": 2153492640, "c4": 127901952, "c1": 4088320, "c5": 357141760,
                      "c4f32": 637814528, "c2f16": 1025741312, "c3col": 2155740184}
 
 
