@@ -44,6 +44,8 @@ SIGNATURES = {
     "htGetDeviceStatus": (_int, [_vp, ctypes.POINTER(ctypes.c_int32)]),
     "htInjectDeviceStatus": (_int, [_vp, ctypes.c_int32]),
     "htKernelLaunchCount": (_u64, []),
+    "htReloadSwitches": (None, []),
+    "htReductionFinish": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
 }
 
 

@@ -20,7 +20,7 @@ __all__ = [
     "STATUS_SUCCESS", "STATUS_NOT_INITIALIZED", "STATUS_INVALID_VALUE", "STATUS_ARCH_MISMATCH",
     "STATUS_INTERNAL_ERROR", "STATUS_NOT_SUPPORTED", "STATUS_HIP_ERROR", "STATUS_INSUFFICIENT_WORKSPACE",
     "STATUS_EXECUTION_FAILED",
-    "error_string", "last_kernel_name", "kernel_launch_count",
+    "error_string", "last_kernel_name", "kernel_launch_count", "reload_switches",
     "describe_permutation_plan", "describe_reduction_plan", "describe_contraction_plan", "dtype_size",
 ]
 
@@ -206,6 +206,15 @@ class Handle:
                                           _lib.i32(modeC), _ptr(D), descD._p, _lib.i32(modeD), int(op_reduce),
                                           int(type_compute), _stream_ptr(stream)), "htReductionNoAlloc")
 
+    def reduction_finish(self, alpha, partial, beta, C, D, descD, type_compute, stream=None):
+        """htReductionFinish: D = alpha * partial + beta * C over descD's layout. `partial` holds the results of
+        per-device reductions (alpha 1, beta 0) of a reduced mode that was split over devices, already combined
+        across devices by one all-reduce with the reduction's operator."""
+        a = _scalar_for_compute(alpha, type_compute)
+        b = _scalar_for_compute(beta, type_compute)
+        _check(self._L.htReductionFinish(self._h, a, _ptr(partial), b, _ptr(C), _ptr(D), descD._p, int(type_compute),
+                                         _stream_ptr(stream)), "htReductionFinish")
+
     def reduction_workspace_size(self, A, descA, modeA, C, descC, modeC, D, descD, modeD, op_reduce, type_compute):
         out = ctypes.c_uint64(0)
         _check(self._L.htReductionGetWorkspaceSize(self._h, _ptr(A), descA._p, _lib.i32(modeA), _ptr(C), descC._p,
@@ -256,6 +265,11 @@ class Handle:
 
 def last_kernel_name():
     return _lib.lib().htLastKernelName().decode()
+
+
+def reload_switches():
+    """Re-reads the HTB_* variant switches from the environment (the library reads them once when loaded)."""
+    _lib.lib().htReloadSwitches()
 
 
 def kernel_launch_count():

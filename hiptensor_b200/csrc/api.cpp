@@ -5,9 +5,12 @@
 // kernel selection is the closed-form planner in planner.cpp and the kernels are this
 // library's own. Unlike the reference nothing here exits the process or blocks the host:
 // CUDA failures come back as HIPTENSOR_STATUS_HIP_ERROR.
+#include <iterator>
+#include <list>
 #include <memory>
 #include <mutex>
 #include <set>
+#include <unordered_map>
 #include <vector>
 
 #include <cuda_runtime_api.h>
@@ -59,27 +62,79 @@ namespace
 
     // Plans are owned by the library and shared between identical problems, like the
     // singleton-owned solutions the reference's plan points to
-    // (hiptensor_contraction.cpp:600-601).
+    // (hiptensor_contraction.cpp:600-601). Look-ups are hashed (by content when a plan is made, by
+    // address when it is used). The registry keeps the kCapacity most recently used plans; a caller's
+    // hiptensorContractionPlan_t whose plan has been dropped is planned again from the descriptor it
+    // carries (see hiptensorContraction), so that a service that plans ever new shapes does not grow
+    // without bound.
     struct PlanRegistry
     {
-        std::mutex                                    mutex;
-        std::vector<std::unique_ptr<ContractionPlan>> plans;
-        const ContractionPlan*                        intern(const ContractionPlan& p)
+        static constexpr std::size_t kCapacity = 4096;
+        struct Node
         {
-            std::lock_guard<std::mutex> lock(mutex);
-            for(auto& q : plans)
-                if(std::memcmp(q.get(), &p, sizeof(p)) == 0)
-                    return q.get();
-            plans.emplace_back(new ContractionPlan(p));
-            return plans.back().get();
+            ContractionPlan plan;
+            uint64_t        hash;
+        };
+        using Iter = std::list<Node>::iterator;
+        std::mutex                                        mutex;
+        std::list<Node>                                   lru; // most recently used first; nodes never move
+        std::unordered_map<const void*, Iter>             byAddress;
+        std::unordered_multimap<uint64_t, Iter>           byContent;
+        uint64_t                                          nextId = 1;
+
+        static uint64_t hashOf(const ContractionPlan& p)
+        {
+            // FNV-1a over the plan's bytes (planned with cacheId = 0; the struct is memset before it is filled)
+            const unsigned char* b = reinterpret_cast<const unsigned char*>(&p);
+            uint64_t             h = 1469598103934665603ull;
+            for(std::size_t i = 0; i < sizeof(p); i++)
+                h = (h ^ b[i]) * 1099511628211ull;
+            return h;
         }
-        bool owns(const void* ptr)
+        const ContractionPlan* intern(const ContractionPlan& fresh)
+        {
+            ContractionPlan p = fresh;
+            p.cacheId         = 0;
+            const uint64_t h  = hashOf(p);
+            std::lock_guard<std::mutex> lock(mutex);
+            auto range = byContent.equal_range(h);
+            for(auto it = range.first; it != range.second; ++it)
+            {
+                p.cacheId = it->second->plan.cacheId;
+                if(std::memcmp(&it->second->plan, &p, sizeof(p)) == 0)
+                {
+                    lru.splice(lru.begin(), lru, it->second);
+                    return &it->second->plan;
+                }
+            }
+            p.cacheId = nextId++;
+            lru.push_front(Node{p, h});
+            byAddress.emplace(&lru.front().plan, lru.begin());
+            byContent.emplace(h, lru.begin());
+            while(lru.size() > kCapacity)
+            {
+                Iter last  = std::prev(lru.end());
+                auto range2 = byContent.equal_range(last->hash);
+                for(auto it = range2.first; it != range2.second; ++it)
+                    if(it->second == last)
+                    {
+                        byContent.erase(it);
+                        break;
+                    }
+                byAddress.erase(&last->plan);
+                lru.pop_back();
+            }
+            return &lru.front().plan;
+        }
+        // the plan at this address if the registry still keeps it (marks it as used)
+        const ContractionPlan* find(const void* ptr)
         {
             std::lock_guard<std::mutex> lock(mutex);
-            for(auto& q : plans)
-                if(q.get() == ptr)
-                    return true;
-            return false;
+            auto it = byAddress.find(ptr);
+            if(it == byAddress.end())
+                return nullptr;
+            lru.splice(lru.begin(), lru, it->second);
+            return &it->second->plan;
         }
     };
     PlanRegistry& registry()
@@ -507,7 +562,7 @@ hiptensorStatus_t hiptensorReductionGetWorkspaceSize(
 // and services that forbid device allocations after start-up.
 // The two-pass scratch comes from a fixed array inside the library (htb::kStaticScratchBytes per
 // device, resident for the life of the process); no cudaMalloc, cudaFree or allocating routine
-// is called, and the host side works on stack arrays only.
+// is called, and the host side (descriptor reading, planning) works on stack arrays only.
 int htb::reductionNoAlloc(const hiptensorHandle_t* handle, const void* alpha, const void* A,
                           const hiptensorTensorDescriptor_t* descA, const int32_t* modeA, const void* beta,
                           const void* C, const hiptensorTensorDescriptor_t* descC, const int32_t* modeC, void* D,
@@ -575,6 +630,52 @@ int htb::reductionNoAlloc(const hiptensorHandle_t* handle, const void* alpha, co
     {
         HTB_LOG_ERROR(fn, "launch failed: %s (%s)", cudaGetErrorString(e),
                       hiptensorGetErrorString(HIPTENSOR_STATUS_HIP_ERROR));
+        return HIPTENSOR_STATUS_HIP_ERROR;
+    }
+    return HIPTENSOR_STATUS_SUCCESS;
+}
+
+// ---------------------------------------------------------------------------- reduction split over devices
+// Body of htReductionFinish (include/hiptensor_b200.h). The reference binds a handle to one device and has no
+// multi-device path; when a REDUCED mode is split over several devices, each device calls hiptensorReduction
+// on its share with alpha = 1 and beta = 0, the partial results are combined with one all-reduce that uses
+// the reduction's operator, and this call applies alpha and beta * C once, in the order of the reference's
+// epilogue (library/src/reduction/reduction_cpu_reference_impl.hpp:45-64).
+int htb::reductionFinish(const hiptensorHandle_t* handle, const void* alpha, const void* partial, const void* beta,
+                         const void* C, void* D, const hiptensorTensorDescriptor_t* descD, int typeComputeI,
+                         void* stream)
+{
+    const char* fn = "htReductionFinish";
+    if(!handle || !alpha || !beta || !partial || !D || !descD)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    const HandleState* st = stateOf(handle);
+    if(!st)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    const auto typeCompute = hiptensorComputeType_t(typeComputeI);
+    const auto tD          = descD->mType;
+    const bool typesOk
+        = (tD == HIP_R_16F && (typeCompute == HIPTENSOR_COMPUTE_16F || typeCompute == HIPTENSOR_COMPUTE_32F))
+          || (tD == HIP_R_16BF && (typeCompute == HIPTENSOR_COMPUTE_16BF || typeCompute == HIPTENSOR_COMPUTE_32F))
+          || (tD == HIP_R_32F && typeCompute == HIPTENSOR_COMPUTE_32F)
+          || (tD == HIP_R_64F && typeCompute == HIPTENSOR_COMPUTE_64F);
+    if(!typesOk || descD->mLengths.size() > std::size_t(kMaxGroup))
+        return HIPTENSOR_STATUS_NOT_SUPPORTED;
+    if(auto s = checkDevice(fn, st); s != HIPTENSOR_STATUS_SUCCESS)
+        return s;
+    double alphaD = 0, betaD = 0;
+    if(!readScalar(alpha, typeComputeI, &alphaD) || !readScalar(beta, typeComputeI, &betaD))
+        return HIPTENSOR_STATUS_NOT_SUPPORTED;
+    int64_t   lens[kMaxGroup], strides[kMaxGroup];
+    const int rank = int(descD->mLengths.size());
+    for(int i = 0; i < rank; i++)
+    {
+        lens[i]    = int64_t(descD->mLengths[i]);
+        strides[i] = int64_t(descD->mStrides[i]);
+    }
+    cudaError_t e = launchReductionFinish(int(tD), alphaD, partial, betaD, C, D, rank, lens, strides, cudaStream_t(stream));
+    if(e != cudaSuccess)
+    {
+        HTB_LOG_ERROR(fn, "launch failed: %s (%s)", cudaGetErrorString(e), hiptensorGetErrorString(HIPTENSOR_STATUS_HIP_ERROR));
         return HIPTENSOR_STATUS_HIP_ERROR;
     }
     return HIPTENSOR_STATUS_SUCCESS;
@@ -737,18 +838,30 @@ hiptensorStatus_t hiptensorContraction(const hiptensorHandle_t* handle, const hi
                       hiptensorGetErrorString(HIPTENSOR_STATUS_INVALID_VALUE));
         return HIPTENSOR_STATUS_INVALID_VALUE;
     }
-    if(plan->mSolution == nullptr || !registry().owns(plan->mSolution))
+    const HandleState* st = stateOf(handle);
+    if(!st)
+        return HIPTENSOR_STATUS_NOT_INITIALIZED;
+    const ContractionPlan* cp = plan->mSolution ? registry().find(plan->mSolution) : nullptr;
+    if(cp == nullptr && plan->mSolution != nullptr)
+    {
+        // the registry has dropped this plan (more than kCapacity other plans were used since): plan again
+        // from the descriptor the caller's plan carries
+        ContractionPlan again;
+        if(buildContractionPlan(&plan->mContractionDesc, st->smCount, &again) == HIPTENSOR_STATUS_SUCCESS)
+        {
+            if(again.expandBytes + again.workspaceBytes > workspaceSize)
+                again.workspaceBytes = 0;
+            cp = registry().intern(again);
+        }
+    }
+    if(cp == nullptr)
     {
         HTB_LOG_ERROR(fn, "Internal Error : solution = nullptr (%s)",
                       hiptensorGetErrorString(HIPTENSOR_STATUS_INTERNAL_ERROR));
         return HIPTENSOR_STATUS_INTERNAL_ERROR;
     }
-    const HandleState* st = stateOf(handle);
-    if(!st)
-        return HIPTENSOR_STATUS_NOT_INITIALIZED;
     if(auto s = checkDevice(fn, st); s != HIPTENSOR_STATUS_SUCCESS)
         return s;
-    const ContractionPlan* cp = static_cast<const ContractionPlan*>(plan->mSolution);
     const uint64_t needBytes = cp->expandBytes + cp->workspaceBytes;
     if(needBytes > workspaceSize || (needBytes > 0 && workspace == nullptr))
     {

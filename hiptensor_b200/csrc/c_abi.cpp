@@ -309,6 +309,17 @@ int htInjectDeviceStatus(const htHandle* handle, int32_t code)
     return HIPTENSOR_STATUS_SUCCESS;
 }
 
+int htReductionFinish(const htHandle* handle, const void* alpha, const void* partial, const void* beta, const void* C,
+                      void* D, const htTensorDescriptor* descD, int typeCompute, void* stream)
+{
+    return htb::reductionFinish(H(handle), alpha, partial, beta, C, D, TD(descD), typeCompute, stream);
+}
+
+void htReloadSwitches(void)
+{
+    htb::reloadSwitches();
+}
+
 uint64_t htKernelLaunchCount(void)
 {
     return htb::launchCount();

@@ -132,6 +132,24 @@ namespace htb
             ::htb::Logger::instance().log(HIPTENSOR_LOG_LEVEL_HEURISTICS_TRACE, func, __VA_ARGS__); \
     } while(0)
 
+    // ---- variant switches ----
+    // Environment variables that choose between shipped kernels or variants of them (tests of a
+    // variant on problems the planner would give to another one, and measurements). None of them
+    // changes a result beyond the order of summation. They are read once when the library is loaded
+    // and again on htReloadSwitches(); a launch reads no environment variable.
+    // Switches that make a kernel skip part of its work (timing one pipeline role alone) exist only in
+    // builds made with -DHTB_MEASURE and are absent from the default build.
+    struct Switches
+    {
+        bool tcSingle, tcPair, tcNoHalf, tcNoSplit, tcKsub1; // f16/bf16 tensor-core kernels
+        bool noTf32x3, tf32Pair, tf32NoInplace, tf32NoSplit; // fp32 tensor-core kernel
+        bool dmmaNoVec, dmmaNoSplit, dmmaNoTma; // FP64 tensor-pipe kernel
+        int  tcProbe, tf32Probe; // HTB_MEASURE builds only, else 0
+        int  permTile, permStages, permCtas; // HTB_MEASURE builds only, else 0
+    };
+    const Switches& switches();
+    void            reloadSwitches();
+
     // ---- launch bookkeeping (which kernel family ran; how many launches) ----
     void        noteLaunch(const char* kernelFamily, int launches = 1);
     const char* lastKernelName();

@@ -29,6 +29,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 
 #include "kernels.hpp"
@@ -59,8 +60,10 @@ namespace htb
             int     bilinear;
             int     nContig; // N is one folded mode with stride 1 in D and D is 16-byte aligned
             int     parts; // single-CTA kernel: K ranges per tile (CTAs of one cluster); 0 or 1 = no split
-            int     probe; // measurement aid, bit mask: 1 = producer skips the loads, 2 = issuer skips the MMAs,
-                           // 4 = epilogue skips the stores (results invalid)
+#ifdef HTB_MEASURE
+            int     probe; // measurement builds only, bit mask: 1 = producer skips the loads, 2 = issuer skips the
+                           // MMAs (results invalid)
+#endif
             int*    status;
             // chunked row groups of MN-major operands (kernel instantiations with LAYOUT != 0 only)
             TfGroup gm, gn;
@@ -128,7 +131,7 @@ namespace htb
         template <typename TD, int LAYOUT>
         __global__ void __launch_bounds__(kThreads, 1)
             contraction_tcgen05_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                                       const TD* __restrict__ C, TD* __restrict__ D, TcArgs a, uint32_t idesc)
+                                       const TD* C, TD* D, TcArgs a, uint32_t idesc) // C may alias D
         {
             extern __shared__ unsigned char smemRaw[];
             unsigned char* tiles = (unsigned char*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
@@ -583,8 +586,8 @@ namespace htb
         __global__ void __launch_bounds__(kThreads, 1)
             contraction_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
                                             const __grid_constant__ CUtensorMap mapB,
-                                            const __grid_constant__ CUtensorMap mapB64, const TD* __restrict__ C,
-                                            TD* __restrict__ D, TcPairArgs pa, uint32_t idesc)
+                                            const __grid_constant__ CUtensorMap mapB64, const TD* C, TD* D,
+                                            TcPairArgs pa, uint32_t idesc) // C may alias D
         {
             const TcArgs& a = pa.base;
             extern __shared__ unsigned char smemRaw[];
@@ -685,12 +688,14 @@ namespace htb
                             ok = mbarWaitTight(emptyAddr + 8 * stage, phase ^ 1, abortP);
                             if(!ok)
                                 break;
+#ifdef HTB_MEASURE
                             if(a.probe & 1)
                             {
                                 if(leader)
                                     mbarArrive(fullAddr + 8 * stage);
                             }
                             else
+#endif
                             {
                                 if(leader)
                                     mbarArriveExpectTx(fullAddr + 8 * stage, txBytes);
@@ -760,7 +765,9 @@ namespace htb
                             // descriptor address field counts 16-byte units
                             const uint64_t descA = descBaseA + uint64_t((stage * kStage) >> 4);
                             const uint64_t descB = descBaseB + uint64_t((stage * kStage + KSUB * kHalfBytes) >> 4);
+#ifdef HTB_MEASURE
                             if(!(a.probe & 2))
+#endif
                             {
 #pragma unroll
                                 for(int k = 0; k < KSUB * (kTileK / 16); k++)
@@ -1142,18 +1149,26 @@ namespace htb
             const bool  bf16 = (p.typeA == CUDA_R_16BF);
             // HTB_TC_PAIR: CTA pairs wherever they can run, not only where they pay off (tests of the pair kernel on
             // small problems)
-            const bool  pair = (p.pair != 0 || (p.pairOk != 0 && getenv("HTB_TC_PAIR") != nullptr))
-                              && getenv("HTB_TC_SINGLE") == nullptr;
+            const Switches& sw = switches();
+            const bool  pair = (p.pair != 0 || (p.pairOk != 0 && sw.tcPair)) && !sw.tcSingle;
             const int*  boxN = pair ? p.boxN128 : p.boxN;
             const int   layout = (p.aMajor ? 1 : 0) | (p.bMajor ? 2 : 0);
             const RowGroupView vm = viewOf(p.m, p.nm, p.aMajor ? 0 : -1), vn = viewOf(p.n, p.nn, p.bMajor ? p.nFast : -1);
-            CUtensorMap mapA, mapB;
-            const bool  okA = p.aMajor ? encodeOperandMn(encode, &mapA, A, bf16, vm, p.K, p.k[0].s0)
-                                       : encodeOperand(encode, &mapA, A, bf16, p.K, p.m, p.nm, p.boxM);
-            const bool  okB = p.bMajor ? encodeOperandMn(encode, &mapB, B, bf16, vn, p.K, p.k[0].s1)
-                                       : encodeOperand(encode, &mapB, B, bf16, p.K, p.n, p.nn, boxN);
-            if(!okA || !okB)
-                return cudaErrorNotSupported;
+            bool           cached = false;
+            MapCacheEntry* maps   = mapCacheFind(p.cacheId, A, B, pair ? 1 : 0, &cached);
+            CUtensorMap &  mapA = maps->mapA, &mapB = maps->mapB;
+            if(!cached)
+            {
+                const bool okA = p.aMajor ? encodeOperandMn(encode, &mapA, A, bf16, vm, p.K, p.k[0].s0)
+                                          : encodeOperand(encode, &mapA, A, bf16, p.K, p.m, p.nm, p.boxM);
+                const bool okB = p.bMajor ? encodeOperandMn(encode, &mapB, B, bf16, vn, p.K, p.k[0].s1)
+                                          : encodeOperand(encode, &mapB, B, bf16, p.K, p.n, p.nn, boxN);
+                if(!okA || !okB)
+                {
+                    maps->id = 0; // not a usable entry
+                    return cudaErrorNotSupported;
+                }
+            }
 
             TcArgs a{};
             a.nm = p.nm;
@@ -1181,8 +1196,9 @@ namespace htb
                                ? 1
                                : 0;
             a.status     = status;
-            if(const char* env = getenv("HTB_TC_PROBE"))
-                a.probe = atoi(env);
+#ifdef HTB_MEASURE
+            a.probe = sw.tcProbe;
+#endif
             if(int64_t(a.tilesM) * a.tilesN > 0x7fffffffll || a.stages > kMaxStages)
                 return cudaErrorInvalidConfiguration;
 
@@ -1200,9 +1216,7 @@ namespace htb
                                        | (uint32_t(256 >> 4) << 24);
                 // two 64-wide K blocks per stage (three 64 KiB stages) beat one (six 32 KiB stages) by 8 %
                 // on 4096^3: the same bytes are in flight with half as many barrier round trips
-                int ksub = 2;
-                if(const char* env = getenv("HTB_TC_KSUB"))
-                    ksub = atoi(env) == 1 ? 1 : 2;
+                const int ksub = sw.tcKsub1 ? 1 : 2;
                 a.stages  = 6 / ksub;
                 pa.base   = a;
                 pa.iters  = (a.kBlocks + ksub - 1) / ksub;
@@ -1215,7 +1229,7 @@ namespace htb
                      contraction_tcgen05_pair_kernel<TD, 2, 2>, contraction_tcgen05_pair_kernel<TD, 2, 3>}};
                 PairKernel kernel = kernels[ksub - 1][layout];
                 const size_t smem = size_t(6) * 2 * 128 * kTileK * 2 + 1024;
-                cudaError_t  e    = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+                cudaError_t  e    = ensureDynamicSmem((const void*)kernel, int(smem));
                 if(e != cudaSuccess)
                     return e;
                 cudaLaunchConfig_t cfg{};
@@ -1230,7 +1244,12 @@ namespace htb
                 cfg.attrs                = attr;
                 cfg.numAttrs             = 1;
                 // clusters that can be resident at once (GPCs with an odd SM count lose one SM)
-                static int maxClusters = 0; // the same for every instantiation: one CTA of 192 threads per SM
+                // (per device; the same for every instantiation: one CTA of 192 threads per SM)
+                static std::atomic<int> clustersOf[kMaxDevices];
+                int                     dev = 0;
+                cudaGetDevice(&dev);
+                const bool devOk       = dev >= 0 && dev < kMaxDevices;
+                int        maxClusters = devOk ? clustersOf[dev].load(std::memory_order_relaxed) : 0;
                 if(maxClusters == 0)
                 {
                     cfg.gridDim = dim3(unsigned(sms / 2 * 2));
@@ -1241,6 +1260,8 @@ namespace htb
                         n = sms / 2;
                     }
                     maxClusters = n;
+                    if(devOk)
+                        clustersOf[dev].store(n, std::memory_order_relaxed);
                 }
                 const int64_t pairs    = int64_t(pa.pairsM) * pa.pairsN;
                 // tail split, if the caller's workspace can hold its scratch
@@ -1252,7 +1273,7 @@ namespace htb
                     uint64_t  bytes;
                     const int tail = tailSplit(pairs, maxClusters, pa.iters, &parts, &bytes);
                     if(tail > 0 && workspace != nullptr && bytes <= workspaceBytes && (uintptr_t(workspace) & 15) == 0
-                       && getenv("HTB_TC_NOSPLIT") == nullptr)
+                       && !sw.tcNoSplit)
                     {
                         pa.fullUnits = int(pairs - tail);
                         pa.parts     = parts;
@@ -1270,15 +1291,23 @@ namespace htb
                 }
                 // Half tiles: several waves, the last at most half full. K-major B needs its 128-row sub-tile to be one
                 // box along the first N mode, so that rows 64.. are a coordinate offset; the N tiles must pair up evenly.
-                CUtensorMap mapB64 = mapB;
-                if(pa.parts == 1 && pairs > maxClusters && getenv("HTB_TC_NOHALF") == nullptr && a.tilesN % 2 == 0)
+                CUtensorMap& mapB64 = maps->mapB64;
+                if(maps->half == 0 && p.bMajor)
+                    mapB64 = mapB;
+                if(pa.parts == 1 && pairs > maxClusters && !sw.tcNoHalf && a.tilesN % 2 == 0)
                 {
                     const int64_t tail   = pairs % maxClusters;
                     bool          halfOk = tail > 0 && 2 * tail <= maxClusters;
                     if(halfOk && !p.bMajor)
                     {
-                        const int box64[4] = {64, 1, 1, 1};
-                        halfOk = p.boxN128[0] == 128 && encodeOperand(encode, &mapB64, B, bf16, p.K, p.n, p.nn, box64);
+                        if(maps->half == 0)
+                        {
+                            const int box64[4] = {64, 1, 1, 1};
+                            maps->half = (p.boxN128[0] == 128 && encodeOperand(encode, &mapB64, B, bf16, p.K, p.n, p.nn, box64))
+                                             ? 1
+                                             : 2;
+                        }
+                        halfOk = maps->half == 1;
                     }
                     if(halfOk)
                     {
@@ -1291,6 +1320,8 @@ namespace htb
                                      (long long)tail, (long long)(2 * tail));
                     }
                 }
+                if(!pa.halves && maps->half != 1)
+                    mapB64 = mapB; // unused by the kernel, but a kernel parameter must be a valid map
                 // one CTA pair per work unit, as many as can be resident
                 cfg.gridDim = dim3(unsigned(2 * std::min<int64_t>(pa.numUnits, maxClusters)));
                 e           = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, mapB64, (const TD*)C, (TD*)D, pa, idesc);
@@ -1305,7 +1336,7 @@ namespace htb
             static const Kernel kernels[4] = {contraction_tcgen05_kernel<TD, 0>, contraction_tcgen05_kernel<TD, 1>,
                                               contraction_tcgen05_kernel<TD, 2>, contraction_tcgen05_kernel<TD, 3>};
             Kernel      kernel = kernels[layout];
-            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+            cudaError_t e = ensureDynamicSmem((const void*)kernel, int(smem));
             if(e != cudaSuccess)
                 return e;
             // Few tiles and a long K: up to four CTAs per tile (one cluster), at least eight K blocks each (with fewer the
@@ -1313,7 +1344,7 @@ namespace htb
             // its own SM; the accumulators of parts 1.. must fit into part 0's stages.
             const int64_t numTiles = int64_t(a.tilesM) * a.tilesN;
             a.parts                = 1;
-            if(getenv("HTB_TC_NOSPLIT") == nullptr)
+            if(!sw.tcNoSplit)
             {
                 const int64_t byTiles = sms / std::max<int64_t>(numTiles, 1), byK = a.kBlocks / 8;
                 const int64_t byRoom  = 1 + int64_t(size_t(a.stages) * (size_t(kTileM) + p.tileN) * kTileK * 2)

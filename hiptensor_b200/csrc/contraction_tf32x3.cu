@@ -89,8 +89,13 @@ namespace htb
             // adds them in order and applies alpha/beta.
             int      parts;
             int      round; // 0: big/small split (compute f32); 1 / 2: elements rounded to f16 / bf16, one MMA per K step
-            int      probe; // measurement aid, bit mask: 1 = converter skips its work, 2 = issuer skips the MMAs,
-                            // 8 = producer skips the loads (results invalid)
+#ifdef HTB_MEASURE
+            int      probe; // measurement builds only, bit mask: 1 = converter skips its work, 2 = issuer skips the
+                            // MMAs, 8 = producer skips the loads (results invalid)
+#define HTB_TF_PROBE(args, bit) ((args).probe & (bit))
+#else
+#define HTB_TF_PROBE(args, bit) 0
+#endif
             int*     status;
         };
 
@@ -308,7 +313,7 @@ namespace htb
         template <bool PAIR, bool INPLACE>
         __global__ void __launch_bounds__(kTfThreads, 1)
             contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                                      const float* __restrict__ C, float* __restrict__ D, TfArgs a, uint32_t idesc)
+                                      const float* C, float* D, TfArgs a, uint32_t idesc) // C may alias D
         {
             extern __shared__ unsigned char smemRaw[];
             unsigned char* tiles = (unsigned char*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
@@ -465,7 +470,7 @@ namespace htb
                             if(lane == 0)
                             {
                                 const uint32_t bar = stFull + 8 * slot;
-                                if(a.probe & 8)
+                                if(HTB_TF_PROBE(a, 8))
                                     mbarArrive(bar);
                                 else
                                 {
@@ -550,7 +555,7 @@ namespace htb
                                 uint32_t aBig = descLo + slot * (kOpBytes >> 4);
                                 uint32_t aSml = aBig + (kTileBytes >> 4), bBig = aBig + (2 * kTileBytes >> 4),
                                          bSml = bBig + (kBBytes >> 4);
-                                if(!(a.probe & 2))
+                                if(!(HTB_TF_PROBE(a, 2)))
                                 {
 #pragma unroll
                                     for(int k = 0; k < kTfK / 8; k++)
@@ -906,7 +911,7 @@ namespace htb
                             if(!ok)
                                 break;
                             const uint32_t op = opAddr + oSlot * kOpBytes;
-                            if(!(a.probe & 1))
+                            if(!(HTB_TF_PROBE(a, 1)))
                             {
                                 tfConvertSmall(op, op + kTileBytes, ct, 128);
                                 tfConvertSmall(op + 2 * kTileBytes, op + 2 * kTileBytes + kBBytes, ct, a.gn.rows);
@@ -924,7 +929,7 @@ namespace htb
                                 break;
                             const uint32_t st = stagingAddr + sSlot * kStagingBytes;
                             const uint32_t op = opAddr + oSlot * kOpBytes;
-                            if(!(a.probe & 1))
+                            if(!(HTB_TF_PROBE(a, 1)))
                             {
                                 tfConvertRow(a.gm.major, st, op, op + kTileBytes, r, kh, 128, a.round);
                                 tfConvertRow(a.gn.major, st + kTileBytes, op + 2 * kTileBytes, op + 2 * kTileBytes + kBBytes, r, kh,
@@ -1034,13 +1039,8 @@ namespace htb
         {
             auto         kernel = contraction_tf32x3_kernel<PAIR, INPLACE>;
             const size_t smem   = size_t(TfRing<PAIR, INPLACE>::kTotal) + 1024;
-            static unsigned char attrSet[kMaxDevices] = {};
-            if(firstUseOnDevice(attrSet))
-            {
-                cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-                if(e != cudaSuccess)
-                    return e;
-            }
+            if(cudaError_t e = ensureDynamicSmem((const void*)kernel, int(smem)); e != cudaSuccess)
+                return e;
             const int      accCols = PAIR ? 128 : a.gn.rows;
             const uint32_t idesc   = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(accCols >> 3) << 17)
                                    | (uint32_t((PAIR ? 256 : 128) >> 4) << 24); // fp32 accumulate, tf32 x tf32, K-major
@@ -1125,19 +1125,26 @@ namespace htb
         // three ring slots instead of two) measured slower on 4096^3 (1.53 ms against 1.14 ms): the kernel is
         // bound by the latency around its rings, which the cross-CTA signalling lengthens, not by the shared-memory
         // bandwidth that a pair saves. HTB_TF32_PAIR=1 selects them.
-        bool pair = false;
-        if(const char* env = getenv("HTB_TF32_PAIR"))
-            pair = p.pair != 0 && atoi(env) != 0;
+        const Switches& sw   = switches();
+        const bool      pair = p.pair != 0 && sw.tf32Pair;
         TfArgs a{};
         fillGroup(a.gm, vm, p.aMajor, 128, p.boxM, 5);
         fillGroup(a.gn, vn, p.bMajor, pair ? 64 : p.tileN, pair ? p.boxN128 : p.boxN, 5);
-        CUtensorMap mapA, mapB;
-        const bool  okA = p.aMajor ? encodeMnMajor(encode, &mapA, A, vm, p.nk, extK, sKa, p.boxK)
-                                   : encodeKMajor(encode, &mapA, A, p.K, vm, p.boxM);
-        const bool  okB = p.bMajor ? encodeMnMajor(encode, &mapB, B, vn, p.nk, extK, sKb, p.boxK)
-                                   : encodeKMajor(encode, &mapB, B, p.K, vn, pair ? p.boxN128 : p.boxN);
-        if(!okA || !okB)
-            return cudaErrorNotSupported;
+        bool           cached = false;
+        MapCacheEntry* maps   = mapCacheFind(p.cacheId, A, B, pair ? 3 : 2, &cached);
+        CUtensorMap &  mapA = maps->mapA, &mapB = maps->mapB;
+        if(!cached)
+        {
+            const bool okA = p.aMajor ? encodeMnMajor(encode, &mapA, A, vm, p.nk, extK, sKa, p.boxK)
+                                      : encodeKMajor(encode, &mapA, A, p.K, vm, p.boxM);
+            const bool okB = p.bMajor ? encodeMnMajor(encode, &mapB, B, vn, p.nk, extK, sKb, p.boxK)
+                                      : encodeKMajor(encode, &mapB, B, p.K, vn, pair ? p.boxN128 : p.boxN);
+            if(!okA || !okB)
+            {
+                maps->id = 0;
+                return cudaErrorNotSupported;
+            }
+        }
         a.boxK[0] = p.boxK[0];
         a.boxK[1] = p.boxK[1];
         a.kTilesPerDim[0] = int((extK[0] + a.boxK[0] - 1) / a.boxK[0]);
@@ -1153,8 +1160,9 @@ namespace htb
         a.pairsN   = (a.gn.tiles + 1) / 2;
         a.status   = deviceStatus;
         a.round    = (p.computeType == HIPTENSOR_COMPUTE_16F) ? 1 : (p.computeType == HIPTENSOR_COMPUTE_16BF ? 2 : 0);
-        if(const char* env = getenv("HTB_TF32_PROBE"))
-            a.probe = atoi(env);
+#ifdef HTB_MEASURE
+        a.probe = sw.tf32Probe;
+#endif
         if(int64_t(a.gm.tiles) * a.gn.tiles > 0x7fffffffll)
             return cudaErrorInvalidConfiguration;
         HTB_LOG_HEUR("hiptensorContraction", "tf32x3: %d x %d row tiles (%d B rows each), %d K blocks, %s", a.gm.tiles,
@@ -1166,11 +1174,11 @@ namespace htb
         {
             const int64_t tiles = int64_t(a.gm.tiles) * a.gn.tiles;
             const int     parts = p.splitK;
-            if(parts > 1 && parts <= 4 && tiles * parts <= sms && a.kBlocks >= 4 * parts && getenv("HTB_TF32_NOSPLIT") == nullptr)
+            if(parts > 1 && parts <= 4 && tiles * parts <= sms && a.kBlocks >= 4 * parts && !sw.tf32NoSplit)
                 a.parts = parts;
         }
         // both operands K-major and no rounding: TMA loads straight into the operand ring
-        const bool inplace = !p.aMajor && !p.bMajor && a.round == 0 && getenv("HTB_TF32_NOINPLACE") == nullptr;
+        const bool inplace = !p.aMajor && !p.bMajor && a.round == 0 && !sw.tf32NoInplace;
         return inplace ? launchKernel<false, true>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream)
                        : launchKernel<false, false>(mapA, mapB, (const float*)C, (float*)D, a, sms, stream);
     }

@@ -734,7 +734,7 @@ namespace htb
             // operand A's rows are the M group (first strides), B's the N group (first strides); K strides: A first, B second
             args.vecA = dmmaVectorOk(A, p.m, p.nm, p.k, p.nk, false, a.aKfast != 0) ? 1 : 0;
             args.vecB = dmmaVectorOk(B, p.n, p.nn, p.k, p.nk, true, a.bKfast != 0) ? 1 : 0;
-            if(getenv("HTB_DMMA_NOVEC"))
+            if(switches().dmmaNoVec)
                 args.vecA = args.vecB = 0;
             args.k32    = p.K < (int64_t(1) << 31) ? 1 : 0;
             args.status = deviceStatus;
@@ -743,20 +743,14 @@ namespace htb
             const int64_t tiles = tilesM * tilesN, steps = (p.K + kDmmaK - 1) / kDmmaK;
             args.parts          = 1;
             for(int q = 4; q >= 2; q >>= 1)
-                if(tiles * q <= 2 * int64_t(smCount) && steps >= 4 * q && getenv("HTB_DMMA_NOSPLIT") == nullptr)
+                if(tiles * q <= 2 * int64_t(smCount) && steps >= 4 * q && !switches().dmmaNoSplit)
                 {
                     args.parts = q;
                     break;
                 }
             const size_t smem = sizeof(double) * kDmmaStages * (kDmmaATile + kDmmaBTile);
-            static unsigned char attr[kMaxDevices] = {};
-            if(firstUseOnDevice(attr))
-            {
-                cudaError_t e = cudaFuncSetAttribute(contraction_dmma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                     int(smem));
-                if(e != cudaSuccess)
-                    return e;
-            }
+            if(cudaError_t e = ensureDynamicSmem((const void*)contraction_dmma_kernel, int(smem)); e != cudaSuccess)
+                return e;
             if(args.parts > 1)
             {
                 cudaLaunchConfig_t  cfg{};
@@ -831,7 +825,7 @@ namespace htb
                 return launchContractionTcgen05(plan, alpha, A, B, beta, C, D, workspace, workspaceBytes, smCount,
                                                 deviceStatus, stream);
         }
-        if(plan.kind == CK_TF32X3 && getenv("HTB_NO_TF32X3") == nullptr)
+        if(plan.kind == CK_TF32X3 && !switches().noTf32x3)
         {
             const bool aligned = ((uintptr_t(A) | uintptr_t(B)) & 15) == 0;
             if(aligned)

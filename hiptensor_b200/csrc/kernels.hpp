@@ -36,6 +36,14 @@ namespace htb
                                              const void* A, double beta, const void* C, void* D, int device,
                                              cudaStream_t stream);
 
+    // Finish of a reduction whose reduced mode was split over devices: D = alpha * partial + beta * C over D's
+    // layout (lens / strides in elements), `partial` laid out like D. Body of htReductionFinish.
+    cudaError_t launchReductionFinish(int typeD, double alpha, const void* partial, double beta, const void* C, void* D,
+                                      int rank, const int64_t* lens, const int64_t* strides, cudaStream_t stream);
+    int         reductionFinish(const hiptensorHandle_t* handle, const void* alpha, const void* partial, const void* beta,
+                                const void* C, void* D, const hiptensorTensorDescriptor_t* descD, int typeCompute,
+                                void* stream);
+
     // body of the flat entry point htReductionNoAlloc (api.cpp)
     int reductionNoAlloc(const hiptensorHandle_t* handle, const void* alpha, const void* A,
                          const hiptensorTensorDescriptor_t* descA, const int32_t* modeA, const void* beta,
@@ -55,16 +63,23 @@ namespace htb
                                          void* workspace, uint64_t workspaceBytes, int smCount, int* deviceStatus,
                                          cudaStream_t stream);
 
-    // Function attributes (dynamic shared-memory limit) belong to one device: true the first time the calling
-    // site is reached with the current device, so that a process that drives several GPUs sets them on each.
-    inline bool firstUseOnDevice(unsigned char (&seen)[kMaxDevices])
+    // Encoded tensor maps of recent launches, per host thread: a repeated hiptensorContraction with the same plan
+    // on the same operand buffers encodes nothing. The key holds everything a map depends on: the plan (by the
+    // registry's unique number; plans without one are never found again), the two base addresses and the kernel
+    // variant (family and tile form).
+    struct MapCacheEntry
     {
-        int dev = 0;
-        if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
-            return true;
-        if(seen[dev])
-            return false;
-        seen[dev] = 1;
-        return true;
-    }
+        uint64_t    id;
+        const void *A, *B;
+        int         variant;
+        int         half; // f16 pair kernel, 64-row B map of the half tiles: 0 not made yet, 1 made, 2 cannot be made
+        CUtensorMap mapA, mapB, mapB64;
+    };
+    // The entry for this key; *hit says whether its maps are already encoded. On a miss the caller encodes into
+    // the entry (and sets id = 0 if that fails).
+    MapCacheEntry* mapCacheFind(uint64_t id, const void* A, const void* B, int variant, bool* hit);
+
+    // Raises a kernel's dynamic shared-memory limit to `bytes` on the current device unless an earlier call
+    // already did (the attribute belongs to one device; a launch then costs a table lookup, not a runtime call).
+    cudaError_t ensureDynamicSmem(const void* kernel, int bytes);
 } // namespace htb

@@ -836,18 +836,8 @@ namespace htb
             a.inStages  = tune.inStages;
             const int   smem = (a.inStages + kOutStages) * TP * TQ * 4 + 1024;
             // the limit is a property of the function on the current device; the stage count can change between calls
-            static int attrSmem[kMaxDevices] = {};
-            int        dev = 0;
-            cudaGetDevice(&dev);
-            if(dev < 0 || dev >= kMaxDevices || smem > attrSmem[dev])
-            {
-                cudaError_t e
-                    = cudaFuncSetAttribute(perm_tma_kernel<NP, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-                if(e != cudaSuccess)
-                    return e;
-                if(dev >= 0 && dev < kMaxDevices)
-                    attrSmem[dev] = smem;
-            }
+            if(cudaError_t e = ensureDynamicSmem((const void*)perm_tma_kernel<NP, NQ>, smem); e != cudaSuccess)
+                return e;
             const int       fit   = std::max(1, (227 * 1024) / (smem + 1024));
             const int       perSm = std::min(fit, tune.ctasPerSm);
             const long long grid  = std::min<long long>(tiles, (long long)(smCount > 0 ? smCount : 148) * perSm);
@@ -987,14 +977,16 @@ namespace htb
         {
             // tile shape: long runs on the store side (rows of the output tile are 32*NQ... wide)
             PermTune tune;
-            auto     envInt = [](const char* name, int& v) {
-                if(const char* e = getenv(name))
-                    v = atoi(e);
-            };
-            // overrides for tuning runs: "HTB_PERM_TILE" (22, 14, 41, 24, 42), "HTB_PERM_STAGES", "HTB_PERM_CTAS"
-            envInt("HTB_PERM_TILE", tune.shape);
-            envInt("HTB_PERM_STAGES", tune.inStages);
-            envInt("HTB_PERM_CTAS", tune.ctasPerSm);
+#ifdef HTB_MEASURE
+            // measurement builds only: tile shape (22, 14, 41, 24, 42), input stages and CTAs per SM of a tuning run
+            const Switches& sw = switches();
+            if(sw.permTile)
+                tune.shape = sw.permTile;
+            if(sw.permStages)
+                tune.inStages = sw.permStages;
+            if(sw.permCtas)
+                tune.ctasPerSm = sw.permCtas;
+#endif
             tune.inStages = std::min(std::max(tune.inStages, 1), kMaxInStages);
             cudaError_t e;
             switch(tune.shape)

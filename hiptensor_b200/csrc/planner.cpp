@@ -67,6 +67,21 @@ namespace htb
             s += "]";
         }
 
+        // stable insertion sort of the few (at most kMaxRank + 2) entries of a mode group: no heap buffer,
+        // unlike std::stable_sort, so that planning allocates nothing
+        template <typename T, typename Less>
+        void sortSmall(T* v, int n, Less less)
+        {
+            for(int i = 1; i < n; i++)
+            {
+                T   x = v[i];
+                int j = i;
+                for(; j > 0 && less(x, v[j - 1]); j--)
+                    v[j] = v[j - 1];
+                v[j] = x;
+            }
+        }
+
         bool isPow2(int64_t v)
         {
             return v > 0 && (v & (v - 1)) == 0;
@@ -280,8 +295,8 @@ namespace htb
             }
         }
         auto byS0 = [](const ModeDim& a, const ModeDim& b) { return a.s0 < b.s0; };
-        std::stable_sort(keep, keep + nk, byS0);
-        std::stable_sort(red, red + nr, byS0);
+        sortSmall(keep, nk, byS0);
+        sortSmall(red, nr, byS0);
         nk = foldGroup(keep, nk);
         nr = foldGroup(red, nr);
         out->nk   = nk;
@@ -480,9 +495,9 @@ namespace htb
         out->bilinear    = bilinear ? 1 : 0;
 
         // ---- order and fold: M by its stride in A, N by its stride in D, K by its stride in A
-        std::stable_sort(gm, gm + nm, [](const ModeDim& a, const ModeDim& b) { return a.s0 < b.s0; });
-        std::stable_sort(gn, gn + nn, [](const ModeDim& a, const ModeDim& b) { return a.s1 < b.s1; });
-        std::stable_sort(gk, gk + nk, [](const ModeDim& a, const ModeDim& b) { return a.s0 < b.s0; });
+        sortSmall(gm, nm, [](const ModeDim& a, const ModeDim& b) { return a.s0 < b.s0; });
+        sortSmall(gn, nn, [](const ModeDim& a, const ModeDim& b) { return a.s1 < b.s1; });
+        sortSmall(gk, nk, [](const ModeDim& a, const ModeDim& b) { return a.s0 < b.s0; });
         nm = foldGroup(gm, nm);
         nn = foldGroup(gn, nn);
         nk = foldGroup(gk, nk);
@@ -600,7 +615,7 @@ namespace htb
                 {
                     int      parts;
                     uint64_t bytes;
-                    tailSplit(tiles, c, kBlocks, &parts, &bytes);
+                    tailSplit(tiles, c, (kBlocks + 1) / 2, &parts, &bytes); // two K blocks per pipeline stage
                     out->workspaceBytes = std::max(out->workspaceBytes, bytes);
                 }
             }
@@ -788,8 +803,8 @@ namespace htb
                 return PLAN_INVALID;
         }
         auto byKey = [](const XMode& a, const XMode& b) { return a.key > b.key; };
-        std::stable_sort(freeM, freeM + nFree, byKey);
-        std::stable_sort(conM, conM + nCon, byKey);
+        sortSmall(freeM, nFree, byKey);
+        sortSmall(conM, nCon, byKey);
 
         // Y's modes for a packed copy: free modes by descending stride in D, contracted modes in the order of X2's
         XMode yFreeM[kMaxRank];
@@ -805,7 +820,7 @@ namespace htb
                 return PLAN_INVALID;
             yFreeM[nYFree++] = XMode{i, D.strides[id]};
         }
-        std::stable_sort(yFreeM, yFreeM + nYFree, byKey);
+        sortSmall(yFreeM, nYFree, byKey);
 
         auto planWith = [&](bool copyY, ContractionPlan* plan) -> int {
         int64_t lX[kPlanRank], sX[kPlanRank], lY[kPlanRank], sY[kPlanRank], lD[kPlanRank], sD[kPlanRank];

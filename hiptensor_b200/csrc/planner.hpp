@@ -133,6 +133,9 @@ namespace htb
         int      yCopy, yRank, yFree;
         int64_t  yExt[kMaxRank], yStride[kMaxRank];
         uint64_t yOffset;
+        // 0 from the planner. The library's plan registry gives every plan it keeps a process-wide unique
+        // number, which the launchers use as the key of their tensor-map caches (0 = do not cache).
+        uint64_t cacheId;
     };
 
     struct TensorView

@@ -19,6 +19,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cfloat>
 #include <mutex>
 #include <type_traits>
@@ -578,6 +579,44 @@ namespace htb
             epilogue<TIn, TAcc>(TAcc(accum.result()), alpha, beta, C, D, offD);
         }
 
+        // ------------------------------------------------------------ finish of a reduction split over devices
+        // Every device reduced its share of a reduced mode with alpha = 1, beta = 0 and the partial results
+        // were combined across devices (one all-reduce with the reduction's operator). This pass applies
+        // alpha and beta * C once, element by element over D's layout, in the order of the single-device
+        // epilogue. `partial` is laid out like D.
+        struct FinishArgs
+        {
+            int     n; // folded modes of D
+            int64_t ext[kMaxGroup], stride[kMaxGroup];
+            int64_t total;
+        };
+        template <typename TIn, typename TAcc>
+        __global__ void __launch_bounds__(256)
+            red_finish_kernel(const TIn* partial, const TIn* C, TIn* D, FinishArgs a, TAcc alpha, TAcc beta)
+        {
+            for(int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < a.total;
+                i += int64_t(gridDim.x) * blockDim.x)
+            {
+                int64_t off = 0, r = i;
+                for(int d = 0; d < a.n; d++)
+                {
+                    off += (r % a.ext[d]) * a.stride[d];
+                    r /= a.ext[d];
+                }
+                epilogue<TIn, TAcc>(widen<TAcc, TIn>(partial[off]), alpha, beta, C, D, off);
+            }
+        }
+        template <typename TIn, typename TAcc>
+        cudaError_t launchFinish(const FinishArgs& a, double alpha, const void* partial, double beta, const void* C,
+                                 void* D, cudaStream_t stream)
+        {
+            const int64_t blocks = std::min<int64_t>((a.total + 255) / 256, 148 * 8);
+            red_finish_kernel<TIn, TAcc><<<unsigned(blocks), 256, 0, stream>>>((const TIn*)partial, (const TIn*)C, (TIn*)D, a,
+                                                                               TAcc(alpha), TAcc(beta));
+            noteLaunch("red_finish");
+            return cudaGetLastError();
+        }
+
         template <typename TIn, typename TAcc, int OP>
         cudaError_t launchTyped(const ReducePlan& p, TAcc alpha, const void* Av, TAcc beta, const void* Cv, void* Dv,
                                 void* workspace, cudaStream_t stream)
@@ -763,6 +802,50 @@ namespace htb
         // pass 1 writes every partial slot that pass 2 reads, so nothing has to start at zero
         return launchReduction(plan, typeA, computeType, op, alpha, A, beta, C, D, plan.split > 1 ? scratch : nullptr,
                                stream);
+    }
+
+    cudaError_t launchReductionFinish(int typeD, double alpha, const void* partial, double beta, const void* C, void* D,
+                                      int rank, const int64_t* lens, const int64_t* strides, cudaStream_t stream)
+    {
+        if(rank < 0 || rank > kMaxGroup)
+            return cudaErrorInvalidValue;
+        // D's modes by ascending stride, neighbours merged where they are contiguous
+        FinishArgs a{};
+        int        order[kMaxGroup];
+        int        n = 0;
+        a.total      = 1;
+        for(int i = 0; i < rank; i++)
+        {
+            if(lens[i] <= 0)
+                return cudaSuccess; // an empty tensor
+            a.total *= lens[i];
+            if(lens[i] == 1)
+                continue;
+            int j = n++;
+            for(; j > 0 && strides[order[j - 1]] > strides[i]; j--)
+                order[j] = order[j - 1];
+            order[j] = i;
+        }
+        for(int j = 0; j < n; j++)
+        {
+            const int64_t e = lens[order[j]], st = strides[order[j]];
+            if(a.n > 0 && a.stride[a.n - 1] * a.ext[a.n - 1] == st)
+                a.ext[a.n - 1] *= e;
+            else
+            {
+                a.ext[a.n]    = e;
+                a.stride[a.n] = st;
+                a.n++;
+            }
+        }
+        switch(typeD)
+        {
+        case CUDA_R_32F: return launchFinish<float, float>(a, alpha, partial, beta, C, D, stream);
+        case CUDA_R_64F: return launchFinish<double, double>(a, alpha, partial, beta, C, D, stream);
+        case CUDA_R_16F: return launchFinish<__half, float>(a, alpha, partial, beta, C, D, stream);
+        case CUDA_R_16BF: return launchFinish<__nv_bfloat16, float>(a, alpha, partial, beta, C, D, stream);
+        }
+        return cudaErrorInvalidValue;
     }
 
     uint64_t reductionWorkspaceBytes(const ReducePlan& plan, int computeType)

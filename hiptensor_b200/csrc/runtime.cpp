@@ -112,6 +112,125 @@ namespace htb
         return HIPTENSOR_STATUS_SUCCESS;
     }
 
+    // ------------------------------------------------------------------ variant switches
+    namespace
+    {
+        Switches gSwitches;
+        bool     envSet(const char* name)
+        {
+            const char* e = getenv(name);
+            return e != nullptr && e[0] != '\0' && !(e[0] == '0' && e[1] == '\0');
+        }
+#ifdef HTB_MEASURE
+        int envInt(const char* name)
+        {
+            const char* e = getenv(name);
+            return e ? atoi(e) : 0;
+        }
+#endif
+        void readSwitches(Switches& s)
+        {
+            std::memset(&s, 0, sizeof(s));
+            s.tcSingle      = envSet("HTB_TC_SINGLE");
+            s.tcPair        = envSet("HTB_TC_PAIR");
+            s.tcNoHalf      = envSet("HTB_TC_NOHALF");
+            s.tcNoSplit     = envSet("HTB_TC_NOSPLIT");
+            s.tcKsub1       = envSet("HTB_TC_KSUB1");
+            s.noTf32x3      = envSet("HTB_NO_TF32X3");
+            s.tf32Pair      = envSet("HTB_TF32_PAIR");
+            s.tf32NoInplace = envSet("HTB_TF32_NOINPLACE");
+            s.tf32NoSplit   = envSet("HTB_TF32_NOSPLIT");
+            s.dmmaNoVec     = envSet("HTB_DMMA_NOVEC");
+            s.dmmaNoSplit   = envSet("HTB_DMMA_NOSPLIT");
+            s.dmmaNoTma     = envSet("HTB_DMMA_NOTMA");
+#ifdef HTB_MEASURE
+            s.tcProbe    = envInt("HTB_TC_PROBE");
+            s.tf32Probe  = envInt("HTB_TF32_PROBE");
+            s.permTile   = envInt("HTB_PERM_TILE");
+            s.permStages = envInt("HTB_PERM_STAGES");
+            s.permCtas   = envInt("HTB_PERM_CTAS");
+#endif
+        }
+        struct SwitchesInit
+        {
+            SwitchesInit()
+            {
+                readSwitches(gSwitches);
+            }
+        } gSwitchesInit;
+    } // namespace
+    const Switches& switches()
+    {
+        return gSwitches;
+    }
+    void reloadSwitches()
+    {
+        readSwitches(gSwitches);
+    }
+
+    // ------------------------------------------------------------------ per-device function attributes
+    cudaError_t ensureDynamicSmem(const void* kernel, int bytes)
+    {
+        struct Entry
+        {
+            const void* fn;
+            int         bytes[kMaxDevices];
+        };
+        static std::mutex mutex;
+        static Entry      table[64];
+        static int        used = 0;
+        int               dev  = 0;
+        if(cudaGetDevice(&dev) != cudaSuccess)
+            return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lock(mutex);
+        Entry*                      e = nullptr;
+        for(int i = 0; i < used && !e; i++)
+            if(table[i].fn == kernel)
+                e = &table[i];
+        if(!e && used < 64)
+        {
+            e     = &table[used++];
+            e->fn = kernel;
+            std::memset(e->bytes, 0, sizeof(e->bytes));
+        }
+        if(e && dev >= 0 && dev < kMaxDevices && e->bytes[dev] >= bytes)
+            return cudaSuccess;
+        const cudaError_t rc = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if(rc == cudaSuccess && e && dev >= 0 && dev < kMaxDevices)
+            e->bytes[dev] = bytes;
+        return rc;
+    }
+
+    // ------------------------------------------------------------------ tensor-map cache
+    MapCacheEntry* mapCacheFind(uint64_t id, const void* A, const void* B, int variant, bool* hit)
+    {
+        constexpr int              kEntries = 8;
+        thread_local MapCacheEntry entries[kEntries];
+        thread_local MapCacheEntry uncached;
+        thread_local int           next = 0;
+        *hit                            = false;
+        if(id == 0)
+        {
+            uncached.id   = 0;
+            uncached.half = 0;
+            return &uncached;
+        }
+        for(int i = 0; i < kEntries; i++)
+            if(entries[i].id == id && entries[i].A == A && entries[i].B == B && entries[i].variant == variant)
+            {
+                *hit = true;
+                return &entries[i];
+            }
+        MapCacheEntry* e = &entries[next];
+        next             = (next + 1) % kEntries;
+        e->id            = id;
+        e->A             = A;
+        e->B             = B;
+        e->variant       = variant;
+        e->half          = 0;
+        return e;
+    }
+
     // ------------------------------------------------------------------ launch bookkeeping
     static std::atomic<uint64_t>    gLaunches{0};
     static thread_local const char* tLastKernel = "";

@@ -93,18 +93,28 @@ def shard_permutation(lensA, modeA, modeB, mode, rank, world):
     return a_view, b_view
 
 
-def reduce_partials(partial, op: int, alpha: float, beta: float, C, group=None):
+_REDUCE_OPS = {3: "SUM", 5: "PRODUCT", 6: "MAX", 7: "MIN"}
+
+
+def reduce_partials(partial, op: int, alpha: float, beta: float, C, handle=None, D=None, descD=None,
+                    type_compute=None, group=None, stream=None, finish=None):
     """Finish a reduction whose reduced mode was sharded: one all-reduce of the partial results
-    (torch tensor, raw reduce values with alpha=1, beta=0), then alpha*r + beta*C applied once,
-    in the reference's order (acc *= alpha if alpha != 1; acc += C*beta if beta != 0)."""
+    (torch tensor laid out like D, raw reduce values computed with alpha=1, beta=0) with the reduction's
+    operator, then alpha*r + beta*C applied ONCE by the library's own kernel (htReductionFinish, through
+    `handle`, into D or in place when D is None) on `stream`.
+
+    `finish`, when given, is called with the combined partial results instead of the library: ranks without
+    a GPU (host-logic tests on gloo) have no device to run the kernel on and bring their own arithmetic.
+    There is no built-in CPU path."""
     import torch.distributed as dist
 
-    ops = {3: dist.ReduceOp.SUM, 5: dist.ReduceOp.PRODUCT, 6: dist.ReduceOp.MAX, 7: dist.ReduceOp.MIN}
     if dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(partial, op=ops[op], group=group)
-    out = partial
-    if alpha != 1.0:
-        out = out * alpha
-    if beta != 0.0 and C is not None:
-        out = out + C * beta
+        dist.all_reduce(partial, op=getattr(dist.ReduceOp, _REDUCE_OPS[op]), group=group)
+    if finish is not None:
+        return finish(partial)
+    if handle is None or descD is None or type_compute is None:
+        raise RuntimeError("reduce_partials needs a hiptensor_b200.Handle, D's descriptor and the compute type: "
+                           "alpha and beta*C are applied by the library's CUDA kernel, there is no CPU path")
+    out = partial if D is None else D
+    handle.reduction_finish(alpha, partial, beta, C, out, descD, type_compute, stream)
     return out

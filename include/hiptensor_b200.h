@@ -114,6 +114,16 @@ int htReductionNoAlloc(const htHandle* handle, const void* alpha, const void* A,
                        const int32_t* modeC, void* D, const htTensorDescriptor* descD, const int32_t* modeD,
                        int opReduce, int typeCompute, void* stream);
 
+/* No counterpart in the reference, whose handle is bound to one device (hiptensor_contraction.cpp:263-277).
+ * Finishes a reduction whose REDUCED mode is split over several devices: every device calls htReduction on
+ * its share of A with alpha = 1 and beta = 0, the partial results (laid out like D) are combined by one
+ * all-reduce that uses the reduction's operator (sum, product, min, max), and this call then writes
+ * D = alpha * partial + beta * C once, in the order of the single-device epilogue
+ * (library/src/reduction/reduction_cpu_reference_impl.hpp:45-64). partial, C and D share descD; C may be
+ * NULL (beta is then ignored) and partial may alias D. */
+int htReductionFinish(const htHandle* handle, const void* alpha, const void* partial, const void* beta, const void* C,
+                      void* D, const htTensorDescriptor* descD, int typeCompute, void* stream);
+
 /* hiptensor.hpp:308-338 (library/src/logger.cpp). mask: OR of 1 error, 2 perf, 4 hint, 8 heuristics, 16 api. */
 int htLoggerSetMask(int32_t mask);
 int htLoggerOpenFile(const char* logFile);
@@ -146,6 +156,10 @@ int htGetDeviceStatus(const htHandle* handle, int32_t* status);
 /* Test aid (host-side fault injection): writes the status word as a timed-out kernel would, so that the error
  * path of the next operation can be exercised without making a kernel wait. */
 int htInjectDeviceStatus(const htHandle* handle, int32_t code);
+/* The library reads its variant switches (environment variables HTB_*, which choose between shipped kernel
+ * variants and never change a result beyond the order of summation) once when it is loaded; this reads them
+ * again. For tests that set a switch after loading the library. */
+void htReloadSwitches(void);
 /* Number of kernel launches made by this library since load (all threads). */
 uint64_t htKernelLaunchCount(void);
 

@@ -12,6 +12,20 @@ SEED_PERMUTATION = 256
 SEED_REDUCTION = (17, 19)
 
 
+def set_switch(name, on):
+    """Sets or clears one of the library's HTB_* variant switches and has the library read them again
+    (it reads the environment once when it is loaded)."""
+    import os
+
+    import hiptensor_b200 as ht
+
+    if on:
+        os.environ[name] = "1"
+    else:
+        os.environ.pop(name, None)
+    ht.reload_switches()
+
+
 def torch_dtype(dt):
     import torch
 
@@ -125,9 +139,12 @@ def check_f32(got, exp, exact, terms):
 
 def run_contraction(ht, h, extent, modeA, modeB, modeD, typeAB=orc.F32, typeD=None, compute=None, alpha=1.0,
                     beta=0.0, with_c=True, first_fastest=False, stridesA=None, stridesB=None, stridesD=None,
-                    fill="uniform", sample=None, seeds=SEED_CONTRACTION, algo=None, alias=False):
+                    fill="uniform", sample=None, seeds=SEED_CONTRACTION, algo=None, alias=False, oracle=True,
+                    inputs=None):
     """extent: dict mode -> extent. Returns (got, expected, typeD) as flat memory images of D.
-    alias: C and D are the same device buffer (the reference's samples call it that way)."""
+    alias: C and D are the same device buffer (the reference's samples call it that way).
+    oracle=False skips the CPU oracle (expected is None) for callers that check the result another way;
+    inputs, a dict, receives the host arrays A, B, C and the strides that were used."""
     typeD = typeAB if typeD is None else typeD
     if compute is None:
         compute = orc.COMPUTE_64F if typeAB == orc.F64 else orc.COMPUTE_32F
@@ -161,6 +178,10 @@ def run_contraction(ht, h, extent, modeA, modeB, modeD, typeAB=orc.F32, typeD=No
         ws = torch.empty(ws_size, dtype=torch.uint8, device="cuda")
     h.contraction(plan, alpha, A_d, B_d, beta, C_d, D_d, ws, ws_size)
     got = to_host(D_d, typeD)
+    if inputs is not None:
+        inputs.update(A=A, B=B, C=C, sA=sA, sB=sB, sD=sD, lA=lA, lB=lB, lD=lD)
+    if not oracle:
+        return got, None, typeD
     exp = nan_like(nD, typeD)
     orc.contraction(alpha, A, lA, sA, modeA, typeAB, B, lB, sB, modeB, typeAB, beta, C, exp, lD, sD, modeD, typeD,
                     compute, sample=sample)

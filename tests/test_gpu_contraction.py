@@ -11,7 +11,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import check_f32, rel_error, run_contraction
+from helpers import check_f32, rel_error, run_contraction, set_switch
 from oracle import binding as orc
 
 pytestmark = pytest.mark.gpu
@@ -21,9 +21,9 @@ pytestmark = pytest.mark.gpu
 def pairs_wherever_possible():
     """The library takes CTA pairs (256 x 256 tiles) only from about two waves of pairs on; this module runs the
     pair kernel on small problems too (odd tile counts, K split, half tiles), as HTB_TC_PAIR allows."""
-    os.environ["HTB_TC_PAIR"] = "1"
+    set_switch("HTB_TC_PAIR", True)
     yield
-    os.environ.pop("HTB_TC_PAIR", None)
+    set_switch("HTB_TC_PAIR", False)
 
 
 @pytest.fixture(scope="module")
@@ -326,12 +326,12 @@ def test_single_cta_kernel_k_split_over_a_cluster(env, shape, out):
         assert 0 <= err < (1e-4 if out == orc.F32 else 2 * 2.0 ** -10), (shape, out, err)
         runs.append(got)
     assert runs[0].tobytes() == runs[1].tobytes()
-    os.environ["HTB_TC_NOSPLIT"] = "1"
+    set_switch("HTB_TC_NOSPLIT", True)
     try:
         whole, exp, td = run_contraction(ht, h, ext, [0, 2], [1, 2], [0, 1], typeAB=orc.F16, typeD=out, alpha=1.5, beta=0.5,
                                          fill="normal")
     finally:
-        del os.environ["HTB_TC_NOSPLIT"]
+        set_switch("HTB_TC_NOSPLIT", False)
     # two summation orders of the tensor cores' fp32 accumulation: the bound of the comparison with the oracle
     assert 0 <= rel_error(whole, runs[0], td) < (1e-4 if out == orc.F32 else 2 * 2.0 ** -10)
 
@@ -445,12 +445,12 @@ def test_cta_pair_kernel_half_tiles_in_last_wave(env, layout):
     assert ht.last_kernel_name() == "contraction_tcgen05_pair"
     assert not np.isnan(got).any()
     assert 0 <= rel_error(got, exp, td) < 1e-4
-    os.environ["HTB_TC_NOHALF"] = "1"
+    set_switch("HTB_TC_NOHALF", True)
     try:
         whole, _, _ = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F16, typeD=orc.F32,
                                       alpha=1.5, beta=0.5, fill="normal", sample=smp[:1])
     finally:
-        del os.environ["HTB_TC_NOHALF"]
+        set_switch("HTB_TC_NOHALF", False)
     assert np.array_equal(got.view(np.uint32), whole.view(np.uint32))
 
 
@@ -471,3 +471,21 @@ def test_c_may_alias_d(env, case):
     assert ht.last_kernel_name() == kernel
     err = rel_error(got, exp, tdo)
     assert 0 <= err < (1e-4 if dt == orc.F16 else 1e-5), (case, err)
+
+
+def test_measurement_switches_are_not_in_the_default_build(env):
+    """The switches that make a kernel skip loads, MMAs or conversion exist only in measurement builds
+    (-DHTB_MEASURE): in the shipped library an environment variable cannot make a result wrong."""
+    ht, h = env
+    os.environ["HTB_TC_PROBE"] = "7"
+    os.environ["HTB_TF32_PROBE"] = "11"
+    ht.reload_switches()
+    try:
+        for dt, k in ((orc.F16, 256), (orc.F32, 136)):
+            got, exp, td = run_contraction(ht, h, {0: 512, 1: 512, 2: k}, [0, 2], [1, 2], [0, 1], typeAB=dt,
+                                           typeD=orc.F32, alpha=1.0, beta=0.0, with_c=False, fill="normal")
+            assert ht.last_kernel_name().startswith("contraction_tcgen05" if dt == orc.F16 else "contraction_tf32x3")
+            assert 0 <= rel_error(got, exp, td) < 1e-4
+    finally:
+        del os.environ["HTB_TC_PROBE"], os.environ["HTB_TF32_PROBE"]
+        ht.reload_switches()

@@ -17,7 +17,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import SEED_CONTRACTION, check_f32, rel_error, run_contraction
+from helpers import SEED_CONTRACTION, check_f32, rel_error, run_contraction, set_switch
 from oracle import binding as orc
 
 pytestmark = pytest.mark.gpu
@@ -104,12 +104,12 @@ def test_cta_pair_kernel_forced(env, layout):
     """256 x 256 tiles on CTA pairs, forced on a problem with an odd number of 128-row sub-tiles along M and N
     (the last pair repeats a sub-tile and must not store it twice)."""
     modeA, modeB = LAYOUTS[layout]
-    os.environ["HTB_TF32_PAIR"] = "1"
+    set_switch("HTB_TF32_PAIR", True)
     try:
         run_and_check(env, {0: 640, 1: 896, 2: 104}, modeA, modeB, [0, 1], 104, alpha=0.5, beta=2.0,
                       kernel="contraction_tf32x3_pair")
     finally:
-        del os.environ["HTB_TF32_PAIR"]
+        set_switch("HTB_TF32_PAIR", False)
 
 
 @pytest.mark.parametrize("layout", ["kk", "mn_mn"])
@@ -122,12 +122,12 @@ def test_large_sampled(env, layout, pair):
     modeA, modeB = LAYOUTS[layout]
     smp = np.random.default_rng(11).integers(0, M * N, 4096)
     if pair:
-        os.environ["HTB_TF32_PAIR"] = "1"
+        set_switch("HTB_TF32_PAIR", True)
     try:
         got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F32, alpha=1.0,
                                        beta=0.5, sample=smp)
     finally:
-        os.environ.pop("HTB_TF32_PAIR", None)
+        set_switch("HTB_TF32_PAIR", False)
     assert ht.last_kernel_name() == ("contraction_tf32x3_pair" if pair else "contraction_tf32x3")
     assert not np.isnan(got).any()
     err = rel_error(got, exp, td)
@@ -191,9 +191,9 @@ def test_k_split_of_small_problems(env, layout):
         if first is None:
             first = got.copy()
     assert np.array_equal(first.view(np.uint32), got.view(np.uint32))
-    os.environ["HTB_TF32_NOSPLIT"] = "1"
+    set_switch("HTB_TF32_NOSPLIT", True)
     try:
         whole, exp, td = run_contraction(ht, h, ext, modeA, modeB, [0, 1], typeAB=orc.F32, alpha=1.5, beta=0.5)
     finally:
-        del os.environ["HTB_TF32_NOSPLIT"]
+        set_switch("HTB_TF32_NOSPLIT", False)
     assert 0 <= rel_error(whole, first, orc.F32) < 1e-5

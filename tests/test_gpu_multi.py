@@ -52,7 +52,8 @@ def _worker(rank, world, port, out):
             dD = h.tensor_descriptor(vd.lens, vd.strides, ht.R_32F)
             P = torch.zeros(64 * 128, device="cuda")
             h.reduction(1.0, A_d[va.offset:], dA, modes, 0.0, P, dD, kept, P, dD, kept, op, ht.COMPUTE_32F)
-            res = sh.reduce_partials(P, op, 1.5, 0.5, C_d)
+            res = sh.reduce_partials(P, op, 1.5, 0.5, C_d, handle=h, descD=dD, type_compute=ht.COMPUTE_32F)
+            ok.append(ht.last_kernel_name() == "red_finish")
             ok.append(np.allclose(res.cpu().numpy(), ref, rtol=2e-5, atol=2e-5))
             # kept mode 0 sharded: disjoint slabs of D, no exchange
             va, vd, exch = sh.shard_reduction(lens, sA, modes, lD, sD, kept, 0, rank, world)

@@ -9,8 +9,9 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def _pair(ht, h, lens, kept, op, dt, ct, alpha, beta, seed):
-    """(result of htReductionNoAlloc, result of htReduction with a caller workspace, kernel names)."""
+def _pair(ht, h, lens, kept, op, dt, ct, alpha, beta, seed, want_oracle=False):
+    """(result of htReductionNoAlloc, result of htReduction with a caller workspace, kernel names[, the CPU
+    oracle's result on the same inputs])."""
     import torch
 
     from helpers import to_device, to_host
@@ -32,7 +33,12 @@ def _pair(ht, h, lens, kept, op, dt, ct, alpha, beta, seed):
     h.reduction(alpha, A_d, dA, modeA, beta, C_d, dD, kept, D2, dD, kept, op, ct, ws, ws_size)
     k2 = ht.last_kernel_name()
     torch.cuda.synchronize()
-    return to_host(D1, dt), to_host(D2, dt), k1, k2
+    if not want_oracle:
+        return to_host(D1, dt), to_host(D2, dt), k1, k2
+    exp = np.zeros(C.size, dtype=orc.np_dtype(dt))
+    orc.reduction(alpha, A, lens, orc.packed_strides(lens, False), modeA, dt, beta, C, exp, lensD,
+                  orc.packed_strides(lensD, False), kept, dt, op, ct)
+    return to_host(D1, dt), to_host(D2, dt), k1, k2, exp
 
 
 def test_matches_the_workspace_entry_point_twice_in_a_row():
@@ -46,8 +52,15 @@ def test_matches_the_workspace_entry_point_twice_in_a_row():
     cases = [([3, 512, 1024], [0], orc.OP_ADD, 17), ([2, 300, 2048], [0], orc.OP_MAX, 23),
              ([700, 64, 64], [], orc.OP_ADD, 29)]
     for lens, kept, op, seed in cases:
-        got, ref, k1, k2 = _pair(ht, h, lens, kept, op, orc.F32, orc.COMPUTE_32F, 2.0, 0.5, seed)
+        got, ref, k1, k2, exp = _pair(ht, h, lens, kept, op, orc.F32, orc.COMPUTE_32F, 2.0, 0.5, seed, want_oracle=True)
         assert k1 == "red_finalize" and k2 == "red_finalize"
+        # against the CPU oracle (both entry points run the same kernels, so agreement between them alone would
+        # not show a fault they share): the reference's own bound for a sequential fp32 reduction, reduce_len * eps
+        n_red = int(np.prod(lens)) // max(int(np.prod([lens[m] for m in kept])), 1)
+        bound = n_red * float(np.finfo(np.float32).eps) if op == orc.OP_ADD else 1e-7
+        from helpers import rel_error as _rel
+
+        assert 0 <= _rel(got, exp, orc.F32) < bound
         # same kernels, same slicing, same order of operations: identical bits; the stated tolerance
         # of the reduction tests (1e-5 under the reference's metric) is the bound
         from helpers import rel_error
@@ -75,3 +88,34 @@ def test_rejects_what_does_not_fit_the_built_in_scratch():
     with pytest.raises(ht.HiptensorError) as e:
         h.reduction_no_alloc(1.0, A, dA, [0, 1], 0.0, D, dD, [0], D, dD, [0], ht.OP_ADD, ht.COMPUTE_64F)
     assert e.value.status == ht.STATUS_INSUFFICIENT_WORKSPACE
+
+
+def test_a_warm_call_allocates_no_device_memory():
+    """After the first call on the device (which looks the scratch address up), a call must leave the device's
+    free memory and the caching allocator of the test harness untouched."""
+    import torch
+
+    import hiptensor_b200 as ht
+    from helpers import to_device
+    from oracle import binding as orc
+
+    h = ht.Handle()
+    lens, kept = [3, 512, 1024], [0]
+    A_d = to_device(orc.fill_uniform(int(np.prod(lens)), orc.F32, 41), orc.F32)
+    C_d = to_device(orc.fill_uniform(3, orc.F32, 43), orc.F32)
+    D_d = torch.zeros_like(C_d)
+    dA = h.tensor_descriptor(lens, None, ht.R_32F)
+    dD = h.tensor_descriptor([3], None, ht.R_32F)
+    call = lambda: h.reduction_no_alloc(2.0, A_d, dA, [0, 1, 2], 0.5, C_d, dD, kept, D_d, dD, kept, ht.OP_ADD,  # noqa: E731
+                                        ht.COMPUTE_32F)
+    call()  # first call on this device: one-time address lookup
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    alloc0, reserved0 = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert ht.last_kernel_name() == "red_finalize"
+    assert free1 == free0
+    assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == (alloc0, reserved0)
