@@ -59,7 +59,7 @@ NCU_TRAFFIC = {
     "c2": (2113114000, "profiles/perm_tma_c2.md"),
     "c3": (2153492640, "profiles/red_row_c3.md"),
     "c3max": (2153492640, "profiles/red_row_c3.md"),
-    "c4": (127901952, "profiles/contraction_tcgen05_pair_c4.md"),
+    "c4": (None, None),
     "c5": (357141760, "profiles/contraction_dmma_c5.md"),
 }
 

@@ -510,85 +510,102 @@ namespace htb
         }
 
         // ------------------------------------------------------------------ CTA-pair kernel
-        // Two CTAs of a cluster (two neighbouring SMs) work on one 256 x 256 output tile with
-        // tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of A and 128 of the 256 rows
-        // of B, the leader CTA (cluster rank 0) issues the MMAs for both, and each CTA's tensor
-        // memory receives the accumulators of its own 128 rows. Against the single-CTA kernel
-        // this halves the B traffic per SM (L2 and shared memory) and leaves room for six stages.
+        // Two CTAs of a cluster (two neighbouring SMs) work on one output tile of 256 rows with
+        // tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of A and its half of the rows of B,
+        // the leader CTA (even cluster rank) issues the MMAs for both, and each CTA's tensor memory
+        // receives the accumulators of its own 128 rows. Against the single-CTA kernel this halves the
+        // B traffic per SM (L2 and shared memory).
         //   * the TMA loads of both CTAs complete on the LEADER's full barrier (cta_group::2 form,
-        //     barrier address mapped to rank 0), which expects the bytes of both;
+        //     barrier address mapped to the leader), which expects the bytes of both;
         //   * tcgen05.commit with a CTA mask releases a stage, or publishes an accumulator, in both
         //     CTAs at once;
         //   * the epilogue threads of both CTAs arrive on the leader's accumulator-empty barrier.
         // Loads carry no multicast qualifier: every CTA fetches its own operands.
+        //
+        // Tile width (template NSUB). The kernel is bound by the operand bytes that enter the SMs from
+        // L2 (about 10 TB/s for the whole chip), i.e. by (1 / tile rows + 1 / tile columns) per flop:
+        //   NSUB = 1  256 x 256 tiles, two accumulators in tensor memory (the epilogue of a tile overlaps the
+        //             main loop of the next), three stages of two 64-wide K blocks (64 KiB each);
+        //   NSUB = 2  256 x 512 tiles, two MMAs (N = 256) per 16-wide K step sharing the A operand, ONE
+        //             accumulator of 512 columns (all of tensor memory: the epilogue is not overlapped, eight
+        //             epilogue warps keep it short), four stages of one K block (48 KiB each). A quarter fewer
+        //             operand bytes per flop.
+        //
+        // K split (ksplit = 2). When the tiles number at most half of the CTA pairs the machine can hold, a
+        // cluster is FOUR CTAs: pair 0 (ranks 0, 1) takes the first half of the K blocks of the tile, pair 1
+        // (ranks 2, 3) the second. CTA r and CTA r ^ 2 then hold partial sums of the same 128 rows; each sends
+        // the half of its columns that the other one finishes into the other's (by then idle) stage memory
+        // (st.shared::cluster), between two cluster barriers, adds what it received to what it kept, applies
+        // alpha / beta and stores: no scratch in global memory, the exchange and the stores are spread over all
+        // four SMs, and a + b = b + a keeps the result independent of which CTA adds.
         struct TcPairArgs
         {
             TcArgs base; // boxN / tilesPerDimN / tilesN describe 128-row N sub-tiles here
-            int    pairsM, pairsN;
+            int    pairsM, groupsN; // tiles: pairsM x groupsN; a tile is 256 rows x (2 * NSUB) N sub-tiles
             int    iters; // pipeline stages per whole tile: ceil(K blocks / blocks per stage)
-            // Tail split. The first fullUnits work units are whole tiles. The tiles that would form a
-            // last, partly filled wave are cut into `parts` ranges of K blocks each, one unit per
-            // range: part 0 owns the tile (adds the other parts' partial sums, applies alpha/beta,
-            // writes D); parts 1.. write their raw accumulators to a scratch slot and raise the tile's
-            // flag. All units of the last wave run at the same time on different CTA pairs.
-            int    fullUnits, numUnits, parts;
-            float* slots; // [tail tile][part-1][256 rows][256 columns] fp32
-            int*   flags; // one counter per tail tile, zeroed before the launch
-            // Half tiles. With several waves of tiles, the tiles of a last wave that fills at most half of the
-            // CTA pairs are cut into two 256 x 128 halves along N, one unit each (halves = 1): the last wave then
-            // takes half as long. A half unit loads 64 rows of B per CTA and issues MMAs with N = 128.
-            int      halves;
+            int    numUnits;
+            int    ksplit; // 1, or 2: clusters of four CTAs, pair (rank >> 1) takes K range (rank >> 1)
+            // Half tiles (NSUB = 1 only). With several waves of tiles, the tiles of a last wave that fills at most
+            // half of the CTA pairs are cut into two 256 x 128 halves along N, one unit each (halves = 1): the last
+            // wave then takes half as long. A half unit loads 64 rows of B per CTA and issues MMAs with N = 128.
+            int      fullUnits, halves;
             uint32_t idescHalf;
         };
 
         struct TcUnit
         {
-            int tile, kbBegin, kbEnd, part, tail; // stage range [kbBegin, kbEnd); tail: index of the split tile or -1
+            int tile, kbBegin, kbEnd; // stage range [kbBegin, kbEnd)
             int half; // -1: whole tile; 0 / 1: N half of the tile
         };
-        __device__ __forceinline__ TcUnit unitOf(const TcPairArgs& pa, int u)
+        __device__ __forceinline__ TcUnit unitOf(const TcPairArgs& pa, int u, int kpart)
         {
             TcUnit w;
-            w.half = -1;
-            if(u < pa.fullUnits)
+            w.half    = -1;
+            w.tile    = u;
+            w.kbBegin = 0;
+            w.kbEnd   = pa.iters;
+            if(pa.ksplit > 1)
             {
-                w.tile    = u;
-                w.kbBegin = 0;
-                w.kbEnd   = pa.iters;
-                w.part    = 0;
-                w.tail    = -1;
+                w.kbBegin = int((long long)pa.iters * kpart / pa.ksplit);
+                w.kbEnd   = int((long long)pa.iters * (kpart + 1) / pa.ksplit);
             }
-            else if(pa.halves)
+            else if(pa.halves && u >= pa.fullUnits)
             {
                 const int x = u - pa.fullUnits;
                 w.tile      = pa.fullUnits + (x >> 1);
                 w.half      = x & 1;
-                w.kbBegin   = 0;
-                w.kbEnd     = pa.iters;
-                w.part      = 0;
-                w.tail      = -1;
-            }
-            else
-            {
-                const int x = u - pa.fullUnits;
-                w.tail      = x / pa.parts;
-                w.part      = x % pa.parts;
-                w.tile      = pa.fullUnits + w.tail;
-                w.kbBegin   = int((long long)pa.iters * w.part / pa.parts);
-                w.kbEnd     = int((long long)pa.iters * (w.part + 1) / pa.parts);
             }
             return w;
         }
 
-        // KSUB: 64-wide K blocks per pipeline stage (1: six 32 KiB stages, 2: three 64 KiB stages)
+        // barrier of the epilogue warps of one CTA (named barrier 1) that also tells every thread whether any of
+        // them raised `flag`
+        template <int THREADS>
+        __device__ __forceinline__ bool epiBarrierAny(bool flag)
+        {
+            uint32_t any;
+            asm volatile("{\n\t.reg .pred p, q;\n\t"
+                         "setp.ne.u32 q, %1, 0;\n\t"
+                         "bar.red.or.pred p, 1, %2, q;\n\t"
+                         "selp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(any)
+                         : "r"(flag ? 1u : 0u), "r"(THREADS)
+                         : "memory");
+            return any != 0;
+        }
+
         // LAYOUT as in the single-CTA kernel: bit 0 = A MN-major, bit 1 = B MN-major
-        template <typename TD, int KSUB, int LAYOUT>
-        __global__ void __launch_bounds__(kThreads, 1)
+        template <typename TD, int LAYOUT, int NSUB>
+        __global__ void __launch_bounds__(64 + 128 * NSUB, 1)
             contraction_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
                                             const __grid_constant__ CUtensorMap mapB,
                                             const __grid_constant__ CUtensorMap mapB64, const TD* C, TD* D,
                                             TcPairArgs pa, uint32_t idesc) // C may alias D
         {
+            constexpr int KSUB = (NSUB == 1) ? 2 : 1; // 64-wide K blocks per pipeline stage
+            constexpr int EPI  = 128 * NSUB; // epilogue threads per CTA
+            constexpr int NACC = 2 / NSUB; // accumulators in tensor memory
+            constexpr int W    = 256 * NSUB; // accumulator columns = tile columns
             const TcArgs& a = pa.base;
             extern __shared__ unsigned char smemRaw[];
             unsigned char* tiles = (unsigned char*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
@@ -597,15 +614,18 @@ namespace htb
             __shared__ __align__(8) unsigned long long tmemFullBar[2], tmemEmptyBar[2];
             __shared__ uint32_t tmemBase;
             __shared__ int      abortFlag;
-            __shared__ int64_t  colOff[4][256]; // one table per epilogue warp
+            __shared__ int64_t  colOff[W]; // D offset of every column of the tile, shared by the epilogue warps
 
             const int      warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
             const uint32_t rank = clusterRank();
-            const bool     leader = (rank == 0);
+            const uint32_t pairRank = rank & 1u, leaderRank = rank & ~1u;
+            const int      kpart  = int(rank >> 1); // K range of this pair (ksplit = 2), else 0
+            const bool     leader = (pairRank == 0);
             constexpr uint32_t kHalfBytes = 128 * kTileK * 2; // 16 KiB: 128 rows of one 64-wide K block
-            constexpr uint32_t kStage     = 2 * KSUB * kHalfBytes; // A blocks, then this CTA's half of the B blocks
-            const int      clusterId   = blockIdx.x >> 1;
-            const int      numClusters = gridDim.x >> 1;
+            constexpr uint32_t kStage     = KSUB * (1 + NSUB) * kHalfBytes; // A blocks, then this CTA's B blocks
+            const int      csize       = 2 * pa.ksplit;
+            const int      clusterId   = blockIdx.x / csize;
+            const int      numClusters = gridDim.x / csize;
 
             if(threadIdx.x == 32)
             {
@@ -624,7 +644,7 @@ namespace htb
                 for(int i = 0; i < 2; i++)
                 {
                     mbarInit(smemAddr(&tmemFullBar[i]), 1);
-                    mbarInit(smemAddr(&tmemEmptyBar[i]), 256);
+                    mbarInit(smemAddr(&tmemEmptyBar[i]), 2 * EPI);
                 }
                 asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             }
@@ -637,7 +657,7 @@ namespace htb
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncthreads();
-            clusterSync(); // the peer's barriers exist before anything signals them
+            clusterSync(); // the peers' barriers exist before anything signals them
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tmem   = tmemBase;
             volatile int*  abortP = &abortFlag;
@@ -649,40 +669,46 @@ namespace htb
                 // ---------------------------------------------------------------- TMA producer
                 if(lane == 0)
                 {
-                    const uint32_t leaderFull = mapToRank(fullAddr, 0);
+                    const uint32_t leaderFull = mapToRank(fullAddr, leaderRank);
                     const uint32_t txWhole    = 2 * KSUB * a.stageBytes; // both CTAs' boxes of one stage
                     uint32_t       stage = 0, phase = 0;
                     bool           ok = true;
                     for(int u = clusterId; u < pa.numUnits && ok; u += numClusters)
                     {
-                        const TcUnit w  = unitOf(pa, u);
+                        const TcUnit w  = unitOf(pa, u, kpart);
                         const int    pm = w.tile % pa.pairsM, pn = w.tile / pa.pairsM;
-                        const int    tm = min(2 * pm + int(rank), a.tilesM - 1);
-                        // B rows of this CTA: 128-row sub-tile `rank` of the tile, or 64-row piece `rank` of sub-tile
-                        // `half` (K-major: second tensor map with 64-row boxes; MN-major: one chunk instead of two)
+                        const int    tm = min(2 * pm + int(pairRank), a.tilesM - 1);
+                        // B rows of this CTA: per accumulator half h, 128-row sub-tile 2 h + pairRank of the tile; in a half
+                        // unit the 64-row piece `pairRank` of sub-tile `half` (K-major: second tensor map with 64-row boxes;
+                        // MN-major: one chunk instead of two)
                         const bool   isHalf = w.half >= 0;
-                        const int    tn = isHalf ? 2 * pn + w.half : min(2 * pn + int(rank), a.tilesN - 1);
                         const CUtensorMap* mb = isHalf ? &mapB64 : &mapB;
                         const uint32_t txBytes = isHalf ? txWhole - 2 * KSUB * 8192 : txWhole;
-                        int          cA[4] = {0, 0, 0, 0}, cB[4] = {0, 0, 0, 0};
-                        TfChunks     qA{}, qB{};
+                        int          cA[4] = {0, 0, 0, 0}, cB[NSUB][4];
+                        TfChunks     qA{}, qB[NSUB];
                         if constexpr(LAYOUT & 1)
                             qA = tfChunksOf(a.gm, tfTileOf(a.gm, tm));
                         else
                             tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cA);
-                        if constexpr(LAYOUT & 2)
-                            qB = tfChunksOf(a.gn, tfTileOf(a.gn, tn));
-                        else
-                            tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB);
+#pragma unroll
+                        for(int h = 0; h < NSUB; h++)
+                        {
+                            const int tn = isHalf ? 2 * pn + w.half : min(2 * NSUB * pn + 2 * h + int(pairRank), a.tilesN - 1);
+                            cB[h][0] = cB[h][1] = cB[h][2] = cB[h][3] = 0;
+                            qB[h] = TfChunks{};
+                            if constexpr(LAYOUT & 2)
+                                qB[h] = tfChunksOf(a.gn, tfTileOf(a.gn, tn));
+                            else
+                                tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB[h]);
+                        }
                         if(isHalf)
                         {
-                            cB[0] += int(rank) * 64;
-                            qB.c0[0] = qB.c0[rank];
-                            qB.i1[0] = qB.i1[rank];
-                            qB.i2[0] = qB.i2[rank];
+                            cB[0][0] += int(pairRank) * 64;
+                            qB[0].c0[0] = qB[0].c0[pairRank];
+                            qB[0].i1[0] = qB[0].i1[pairRank];
+                            qB[0].i2[0] = qB[0].i2[pairRank];
                         }
                         const int a1 = cA[0], a2 = cA[1], a3 = cA[2], a4 = cA[3];
-                        const int b1 = cB[0], b2 = cB[1], b3 = cB[2], b4 = cB[3];
                         for(int it = w.kbBegin; it < w.kbEnd; it++)
                         {
                             ok = mbarWaitTight(emptyAddr + 8 * stage, phase ^ 1, abortP);
@@ -713,15 +739,19 @@ namespace htb
                                     }
                                     else
                                         tmaLoadPair5(dst + q * kHalfBytes, &mapA, bar, k0, a1, a2, a3, a4);
-                                    if constexpr(LAYOUT & 2)
+#pragma unroll
+                                    for(int h = 0; h < NSUB; h++)
                                     {
-                                        tmaLoadPair5(dst + (KSUB + q) * kHalfBytes, &mapB, bar, qB.c0[0], k0, qB.i1[0], qB.i2[0], 0);
-                                        if(!isHalf)
-                                            tmaLoadPair5(dst + (KSUB + q) * kHalfBytes + 8192, &mapB, bar, qB.c0[1], k0, qB.i1[1],
-                                                         qB.i2[1], 0);
+                                        const uint32_t db = dst + (KSUB * (1 + h) + q) * kHalfBytes;
+                                        if constexpr(LAYOUT & 2)
+                                        {
+                                            tmaLoadPair5(db, &mapB, bar, qB[h].c0[0], k0, qB[h].i1[0], qB[h].i2[0], 0);
+                                            if(!isHalf)
+                                                tmaLoadPair5(db + 8192, &mapB, bar, qB[h].c0[1], k0, qB[h].i1[1], qB[h].i2[1], 0);
+                                        }
+                                        else
+                                            tmaLoadPair5(db, mb, bar, k0, cB[h][0], cB[h][1], cB[h][2], cB[h][3]);
                                     }
-                                    else
-                                        tmaLoadPair5(dst + (KSUB + q) * kHalfBytes, mb, bar, k0, b1, b2, b3, b4);
                                 }
                             }
                             if(++stage == uint32_t(a.stages))
@@ -732,24 +762,31 @@ namespace htb
                         }
                     }
                 }
+                if(pa.ksplit > 1)
+                {
+                    __syncwarp();
+                    clusterSync(); // the two meeting points of the K-split exchange (see the epilogue)
+                    clusterSync();
+                }
             }
             else if(warp == 1)
             {
-                // ---------------------------------------------------------------- MMA issuer (leader CTA)
+                // ---------------------------------------------------------------- MMA issuer (leader CTA of the pair)
                 if(lane == 0 && leader)
                 {
                     const uint64_t descBaseA = (LAYOUT & 1) ? smemDescMn(tilesAddr) : smemDesc(tilesAddr);
                     const uint64_t descBaseB = (LAYOUT & 2) ? smemDescMn(tilesAddr) : smemDesc(tilesAddr);
                     // a 16-wide K step: 2 address units along a K-major row, 128 down an MN-major chunk
                     constexpr int  stepA = (LAYOUT & 1) ? 128 : 2, stepB = (LAYOUT & 2) ? 128 : 2;
+                    const unsigned short pairMask = (unsigned short)(3u << leaderRank);
                     uint32_t       stage = 0, phase = 0;
                     int            local = 0;
                     bool           ok    = true;
                     for(int u = clusterId; u < pa.numUnits && ok; u += numClusters, local++)
                     {
-                        const TcUnit   w        = unitOf(pa, u);
-                        const int      acc      = local & 1;
-                        const uint32_t accPhase = (local >> 1) & 1;
+                        const TcUnit   w        = unitOf(pa, u, kpart);
+                        const int      acc      = local % NACC;
+                        const uint32_t accPhase = (local / NACC) & 1;
                         ok = mbarWaitTight(smemAddr(&tmemEmptyBar[acc]), accPhase ^ 1, abortP);
                         if(!ok)
                             break;
@@ -776,17 +813,20 @@ namespace htb
                                     const uint64_t offA = uint64_t((k / 4) * (kHalfBytes >> 4) + stepA * (k % 4));
                                     const uint64_t offB = uint64_t((k / 4) * (kHalfBytes >> 4) + stepB * (k % 4));
                                     const uint32_t accumulate = (it != w.kbBegin || k != 0) ? 1u : 0u;
-                                    asm volatile("{\n\t.reg .pred p;\n\t"
-                                                 "setp.ne.b32 p, %4, 0;\n\t"
-                                                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem),
-                                                 "l"(descA + offA), "l"(descB + offB), "r"(idescU), "r"(accumulate)
-                                                 : "memory");
+#pragma unroll
+                                    for(int h = 0; h < NSUB; h++)
+                                        asm volatile("{\n\t.reg .pred p;\n\t"
+                                                     "setp.ne.b32 p, %4, 0;\n\t"
+                                                     "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem + uint32_t(h * 256)),
+                                                     "l"(descA + offA), "l"(descB + offB + uint64_t(h * KSUB * (kHalfBytes >> 4))),
+                                                     "r"(idescU), "r"(accumulate)
+                                                     : "memory");
                                 }
                             }
-                            // frees the stage in both CTAs once these MMAs have read it
+                            // frees the stage in both CTAs of the pair once these MMAs have read it
                             asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
                                          "[%0], %1;" ::"r"(emptyAddr + 8 * stage),
-                                         "h"((unsigned short)3)
+                                         "h"(pairMask)
                                          : "memory");
                             if(++stage == uint32_t(a.stages))
                             {
@@ -797,148 +837,100 @@ namespace htb
                         if(ok)
                             asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
                                          "[%0], %1;" ::"r"(smemAddr(&tmemFullBar[acc])),
-                                         "h"((unsigned short)3)
+                                         "h"(pairMask)
                                          : "memory");
                     }
+                }
+                if(pa.ksplit > 1)
+                {
+                    __syncwarp();
+                    clusterSync();
+                    clusterSync();
                 }
             }
             else
             {
                 // ---------------------------------------------------------------- epilogue (both CTAs)
-                const int quad = warp & 3;
+                const int quad = warp & 3; // TMEM lane quadrant this warp may read
                 const int row  = quad * 32 + lane;
-                int64_t*  cols = colOff[quad];
+                const int et   = int(threadIdx.x) - 64; // index among the epilogue threads
+                const int colGroup = (warp - 2) >> 2; // NSUB = 2: which half of the columns this warp takes
                 int       local = 0;
+                int       syncs = 0; // cluster meeting points of the K-split exchange passed so far
+                auto      loadChunk = [&](uint32_t addr, uint32_t(&v)[32]) {
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]),
+                          "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]),
+                          "=r"(v[30]), "=r"(v[31])
+                        : "r"(addr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                };
                 for(int u = clusterId; u < pa.numUnits; u += numClusters, local++)
                 {
-                    const TcUnit   w        = unitOf(pa, u);
-                    const int      acc      = local & 1;
-                    const uint32_t accPhase = (local >> 1) & 1;
+                    const TcUnit   w        = unitOf(pa, u, kpart);
+                    const int      acc      = local % NACC;
+                    const uint32_t accPhase = (local / NACC) & 1;
                     const int      pm = w.tile % pa.pairsM, pn = w.tile / pa.pairsM;
-                    const int      tmRaw = 2 * pm + int(rank);
+                    const int      tmRaw = 2 * pm + int(pairRank);
                     const bool     dupM  = tmRaw >= a.tilesM; // this CTA repeats its peer's rows: no stores
                     const int      tm    = min(tmRaw, a.tilesM - 1);
-                    int            cM[4], cN[4];
+                    int            cM[4];
                     tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cM);
-                    __syncwarp();
-                    const int ncols = (w.half >= 0) ? 128 : 256; // a half tile: the 128 columns of sub-tile `half`
-                    for(int h = 0; h < (ncols >> 7); h++)
+                    // the table of column offsets, filled by all epilogue threads once nobody reads the previous one
+                    epiBarrierAny<EPI>(false);
+                    const int ncols = (w.half >= 0) ? 128 : W; // a half tile: the 128 columns of sub-tile `half`
+                    for(int c = et; c < ncols; c += EPI)
                     {
-                        const int tnRaw = 2 * pn + ((w.half >= 0) ? w.half : h);
-                        if constexpr(LAYOUT & 2)
+                        const int tnRaw = (w.half >= 0) ? 2 * pn + w.half : 2 * NSUB * pn + (c >> 7);
+                        int64_t   off   = -1;
+                        if(tnRaw < a.tilesN)
                         {
-                            const TfTile wn = tfTileOf(a.gn, min(tnRaw, a.tilesN - 1));
-                            for(int c = lane; c < 128; c += 32)
-                                cols[h * 128 + c] = (tnRaw < a.tilesN) ? tfRowOffset(a.gn, wn, c) : -1;
+                            if constexpr(LAYOUT & 2)
+                                off = tfRowOffset(a.gn, tfTileOf(a.gn, tnRaw), c & 127);
+                            else
+                            {
+                                int cN[4];
+                                tileCoords(tnRaw, a.tilesPerDimN, a.boxN, a.nn, cN);
+                                off = rowOffset(c & 127, cN, a.boxN, a.extN, a.sDn, a.nn);
+                            }
                         }
-                        else
-                        {
-                            tileCoords(min(tnRaw, a.tilesN - 1), a.tilesPerDimN, a.boxN, a.nn, cN);
-                            for(int c = lane; c < 128; c += 32)
-                                cols[h * 128 + c] = (tnRaw < a.tilesN) ? rowOffset(c, cN, a.boxN, a.extN, a.sDn, a.nn) : -1;
-                        }
+                        colOff[c] = off;
                     }
-                    __syncwarp();
                     const int64_t offM = dupM ? -1
                                               : ((LAYOUT & 1) ? tfRowOffset(a.gm, tfTileOf(a.gm, tm), row)
                                                               : rowOffset(row, cM, a.boxM, a.extM, a.sDm, a.nm));
-
-                    int ok = 1;
+                    // one lane waits for the accumulator; the barrier completes the table and tells every epilogue
+                    // thread of the CTA whether a wait ran out (all of them then leave together)
+                    bool failed = false;
                     if(lane == 0)
-                        ok = mbarWait(smemAddr(&tmemFullBar[acc]), accPhase, abortP) ? 1 : 0;
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if(!ok)
+                        failed = !mbarWait(smemAddr(&tmemFullBar[acc]), accPhase, abortP);
+                    if(epiBarrierAny<EPI>(failed))
                         break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(acc * 256);
-                    // scratch rows of this thread in a split tile: row = CTA rank * 128 + TMEM lane
-                    float* slotRow = nullptr;
-                    if(w.tail >= 0)
-                    {
-                        slotRow = pa.slots + (size_t(w.tail) * (pa.parts - 1)) * 65536 + size_t(rank * 128 + row) * 256;
-                        if(w.part == 0)
-                        {
-                            // owner: the other parts' partial sums must be in the scratch (8 warps each)
-                            int ready = 1;
-                            if(lane == 0)
-                            {
-                                const int       want = (pa.parts - 1) * 8;
-                                const long long t0   = clock64();
-                                for(;;)
-                                {
-                                    int seen;
-                                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(pa.flags + w.tail) : "memory");
-                                    if(seen >= want)
-                                        break;
-                                    if(*abortP || clock64() - t0 > kWaitCycles)
-                                    {
-                                        *abortP = 1;
-                                        ready   = 0;
-                                        break;
-                                    }
-                                }
-                            }
-                            ready = __shfl_sync(0xffffffffu, ready, 0);
-                            if(!ready)
-                                break;
-                        }
-                    }
                     // D offsets of the eight rows of this lane's group of eight lanes (for the line-wise stores below)
                     int64_t rowOff[8];
 #pragma unroll
                     for(int k = 0; k < 8; k++)
                         rowOff[k] = __shfl_sync(0xffffffffu, offM, (lane & ~7) + k);
-                    for(int c0 = 0; c0 < ncols; c0 += 32)
-                    {
-                        uint32_t v[32];
-                        asm volatile(
-                            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-                              "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-                              "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-                              "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-                              "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                            : "r"(taddr + uint32_t(c0)));
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        if(w.tail >= 0)
-                        {
-                            if(w.part > 0)
-                            {
-                                // contributor: raw accumulators to this part's scratch slot
-                                float4* dst = (float4*)(slotRow + size_t(w.part - 1) * 65536 + c0);
-#pragma unroll
-                                for(int j = 0; j < 8; j++)
-                                    dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                         __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                                continue;
-                            }
-                            for(int q = 0; q < pa.parts - 1; q++)
-                            {
-                                const float4* src = (const float4*)(slotRow + size_t(q) * 65536 + c0);
-#pragma unroll
-                                for(int j = 0; j < 8; j++)
-                                {
-                                    const float4 p4 = src[j];
-                                    v[4 * j]     = __float_as_uint(__uint_as_float(v[4 * j]) + p4.x);
-                                    v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + p4.y);
-                                    v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + p4.z);
-                                    v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + p4.w);
-                                }
-                            }
-                        }
-                        const int64_t first     = cols[c0];
-                        const bool    fullChunk = a.nContig && first >= 0 && cols[c0 + 31] == first + 31;
+
+                    // alpha / beta and the stores of 32 accumulator columns c0 .. c0 + 31 of this thread's row
+                    auto storeChunk = [&](uint32_t(&v)[32], int c0) {
+                        const int64_t first     = colOff[c0];
+                        const bool    fullChunk = a.nContig && first >= 0 && colOff[c0 + 31] == first + 31;
                         if constexpr(sizeof(TD) == 4)
                         {
                             // Line-wise stores. A lane holds 32 consecutive floats of its own row; stored as they are, one
                             // instruction touches 32 different lines, and that request stream was measured to slow the
-                            // MMAs of the next tile (it shares the way out of the SM with the operand traffic between the
-                            // two CTAs): the first stages of a tile took twice as long while the previous tile was being
-                            // stored. The eight lanes of a group therefore transpose their 8 x 8 blocks of four floats
-                            // with three rounds of shuffles, after which lane m holds quarter-line m of each of the
-                            // group's eight rows and one store instruction writes four whole 128-byte lines.
+                            // MMAs of the next tile: the first stages of a tile took twice as long while the previous
+                            // tile was being stored. The eight lanes of a group therefore transpose their 8 x 8 blocks of
+                            // four floats with three rounds of shuffles, after which lane m holds quarter-line m of each
+                            // of the group's eight rows and one store instruction writes four whole 128-byte lines.
                             if(fullChunk && __all_sync(0xffffffffu, offM < 0 || ((offM + first) & 3) == 0))
                             {
                                 float4 o[8];
@@ -994,11 +986,11 @@ namespace htb
                                 for(int k = 0; k < 8; k++)
                                     if(rowOff[k] >= 0)
                                         *(float4*)((float*)D + rowOff[k] + first + 4 * m) = o[k];
-                                continue;
+                                return;
                             }
                         }
                         if(offM < 0)
-                            continue;
+                            return;
                         if(fullChunk && sizeof(TD) == 4 && ((offM + first) & 3) == 0)
                         {
                             float*       dst = (float*)D + offM + first;
@@ -1040,32 +1032,87 @@ namespace htb
 #pragma unroll
                             for(int j = 0; j < 32; j++)
                             {
-                                const int64_t oc = cols[c0 + j];
+                                const int64_t oc = colOff[c0 + j];
                                 if(oc >= 0)
                                     D[offM + oc] = finish<TD>(__uint_as_float(v[j]), a.alpha, a.beta, a.bilinear != 0, C,
                                                               offM + oc);
                             }
                         }
-                    }
-                    if(w.tail >= 0 && w.part > 0)
+                    };
+
+                    if(pa.ksplit > 1)
                     {
-                        // publish this warp's rows of the partial sum
-                        __threadfence();
-                        __syncwarp();
-                        if(lane == 0)
-                            atomicAdd(pa.flags + w.tail, 1);
+                        // K-split exchange. This CTA finishes the half `kpart` of the tile's columns and sends the other
+                        // half of its partial sums to CTA rank ^ 2 (same rows, other K range). Each warp sends 128 columns
+                        // and finishes 128: layout in the receiver's stage memory [32-column chunk][column group of
+                        // four][128 rows] of 16 bytes.
+                        constexpr int kHalfW = W / 2;
+                        const int     keep = kpart * kHalfW + colGroup * 128, send = (1 - kpart) * kHalfW + colGroup * 128;
+                        const uint32_t zone = tilesAddr + uint32_t(row) * 16u + uint32_t(colGroup * 4) * 16384u;
+                        clusterSync(); // every CTA of the cluster has its sums: all stage memory is idle
+                        syncs++;
+                        const uint32_t remote = mapToRank(zone, rank ^ 2u);
+#pragma unroll 1
+                        for(int c0 = 0; c0 < 128; c0 += 32)
+                        {
+                            uint32_t v[32];
+                            loadChunk(taddr + uint32_t(send + c0), v);
+                            const uint32_t dst = remote + uint32_t(c0 >> 5) * 16384u;
+#pragma unroll
+                            for(int j = 0; j < 8; j++)
+                                asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + uint32_t(j) * 2048u),
+                                             "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                                             : "memory");
+                        }
+                        clusterSync(); // the partner's sums have arrived
+                        syncs++;
+#pragma unroll 1
+                        for(int c0 = 0; c0 < 128; c0 += 32)
+                        {
+                            uint32_t v[32];
+                            loadChunk(taddr + uint32_t(keep + c0), v);
+                            const uint32_t src = zone + uint32_t(c0 >> 5) * 16384u;
+#pragma unroll
+                            for(int j = 0; j < 8; j++)
+                            {
+                                float4 p4;
+                                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                             : "=f"(p4.x), "=f"(p4.y), "=f"(p4.z), "=f"(p4.w)
+                                             : "r"(src + uint32_t(j) * 2048u));
+                                v[4 * j]     = __float_as_uint(__uint_as_float(v[4 * j]) + p4.x);
+                                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + p4.y);
+                                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + p4.z);
+                                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + p4.w);
+                            }
+                            storeChunk(v, keep + c0);
+                        }
+                    }
+                    else
+                    {
+                        // whole tile: the two warps of a lane quadrant (NSUB = 2) take 256 columns each
+                        const int cBegin = (NSUB == 2) ? colGroup * 256 : 0;
+                        const int cEnd   = (NSUB == 2) ? cBegin + 256 : ncols;
+#pragma unroll 1
+                        for(int c0 = cBegin; c0 < cEnd; c0 += 32)
+                        {
+                            uint32_t v[32];
+                            loadChunk(taddr + uint32_t(c0), v);
+                            storeChunk(v, c0);
+                        }
                     }
                     // hand the accumulator back: every epilogue thread of the pair arrives on the leader's barrier
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    const uint32_t emptyAddr = mapToRank(smemAddr(&tmemEmptyBar[acc]), 0);
-                    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(emptyAddr) : "memory");
+                    const uint32_t emptyBarAddr = mapToRank(smemAddr(&tmemEmptyBar[acc]), leaderRank);
+                    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(emptyBarAddr) : "memory");
                 }
+                for(; pa.ksplit > 1 && syncs < 2; syncs++)
+                    clusterSync(); // a CTA whose wait ran out still meets the others
             }
 
             // ---------------------------------------------------------------- teardown
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncthreads();
-            clusterSync(); // both CTAs are done with tensor memory and with each other's barriers
+            clusterSync(); // all CTAs are done with tensor memory and with each other's barriers and shared memory
             if(threadIdx.x == 0 && abortFlag && a.status)
                 atomicExch(a.status, 3);
             if(warp == 1)
@@ -1208,27 +1255,29 @@ namespace htb
             const int      sms = smCount > 0 ? smCount : 148;
             if(pair)
             {
+                // tile width and K split: the planner's choice (cost model in planner.cpp), narrowed here by what the
+                // device grants (resident clusters) and by the variant switches
+                const int  nsub   = ((p.wide || sw.tcWide) && !sw.tcNarrow) ? 2 : 1;
+                const int  ksub   = nsub == 1 ? 2 : 1;
                 TcPairArgs pa{};
-                pa.base   = a;
-                pa.pairsM = (a.tilesM + 1) / 2;
-                pa.pairsN = (a.tilesN + 1) / 2;
+                a.stages     = 192 * 1024 / int(ksub * (1 + nsub) * 16384);
+                a.stageBytes = uint32_t(128 + nsub * 128) * kTileK * 2;
+                pa.base      = a;
+                pa.pairsM    = (a.tilesM + 1) / 2;
+                pa.groupsN   = (a.tilesN + 2 * nsub - 1) / (2 * nsub);
+                pa.iters     = (a.kBlocks + ksub - 1) / ksub;
+                pa.ksplit    = 1;
                 const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | majors | (uint32_t(256 >> 3) << 17)
                                        | (uint32_t(256 >> 4) << 24);
-                // two 64-wide K blocks per stage (three 64 KiB stages) beat one (six 32 KiB stages) by 8 %
-                // on 4096^3: the same bytes are in flight with half as many barrier round trips
-                const int ksub = sw.tcKsub1 ? 1 : 2;
-                a.stages  = 6 / ksub;
-                pa.base   = a;
-                pa.iters  = (a.kBlocks + ksub - 1) / ksub;
                 using PairKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const TD*, TD*, TcPairArgs,
                                             uint32_t);
                 static const PairKernel kernels[2][4] = {
-                    {contraction_tcgen05_pair_kernel<TD, 1, 0>, contraction_tcgen05_pair_kernel<TD, 1, 1>,
-                     contraction_tcgen05_pair_kernel<TD, 1, 2>, contraction_tcgen05_pair_kernel<TD, 1, 3>},
-                    {contraction_tcgen05_pair_kernel<TD, 2, 0>, contraction_tcgen05_pair_kernel<TD, 2, 1>,
-                     contraction_tcgen05_pair_kernel<TD, 2, 2>, contraction_tcgen05_pair_kernel<TD, 2, 3>}};
-                PairKernel kernel = kernels[ksub - 1][layout];
-                const size_t smem = size_t(6) * 2 * 128 * kTileK * 2 + 1024;
+                    {contraction_tcgen05_pair_kernel<TD, 0, 1>, contraction_tcgen05_pair_kernel<TD, 1, 1>,
+                     contraction_tcgen05_pair_kernel<TD, 2, 1>, contraction_tcgen05_pair_kernel<TD, 3, 1>},
+                    {contraction_tcgen05_pair_kernel<TD, 0, 2>, contraction_tcgen05_pair_kernel<TD, 1, 2>,
+                     contraction_tcgen05_pair_kernel<TD, 2, 2>, contraction_tcgen05_pair_kernel<TD, 3, 2>}};
+                PairKernel kernel = kernels[nsub - 1][layout];
+                const size_t smem = size_t(192) * 1024 + 1024;
                 cudaError_t  e    = ensureDynamicSmem((const void*)kernel, int(smem));
                 if(e != cudaSuccess)
                     return e;
@@ -1238,95 +1287,82 @@ namespace htb
                 attr[0].val.clusterDim.x = 2;
                 attr[0].val.clusterDim.y = 1;
                 attr[0].val.clusterDim.z = 1;
-                cfg.blockDim             = dim3(kThreads);
+                cfg.blockDim             = dim3(unsigned(64 + 128 * nsub));
                 cfg.dynamicSmemBytes     = smem;
                 cfg.stream               = stream;
                 cfg.attrs                = attr;
                 cfg.numAttrs             = 1;
-                // clusters that can be resident at once (GPCs with an odd SM count lose one SM)
-                // (per device; the same for every instantiation: one CTA of 192 threads per SM)
-                static std::atomic<int> clustersOf[kMaxDevices];
+                // clusters of two and of four CTAs that can be resident at once (GPCs with an odd SM count lose an SM);
+                // per device, the same for every instantiation: one CTA per SM
+                static std::atomic<int> clustersOf[kMaxDevices][2];
                 int                     dev = 0;
                 cudaGetDevice(&dev);
-                const bool devOk       = dev >= 0 && dev < kMaxDevices;
-                int        maxClusters = devOk ? clustersOf[dev].load(std::memory_order_relaxed) : 0;
-                if(maxClusters == 0)
-                {
-                    cfg.gridDim = dim3(unsigned(sms / 2 * 2));
-                    int n       = 0;
-                    if(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0)
+                const bool devOk  = dev >= 0 && dev < kMaxDevices;
+                auto       resident = [&](int csize) {
+                    const int slot = csize == 2 ? 0 : 1;
+                    int       n    = devOk ? clustersOf[dev][slot].load(std::memory_order_relaxed) : 0;
+                    if(n == 0)
                     {
-                        cudaGetLastError();
-                        n = sms / 2;
+                        attr[0].val.clusterDim.x = unsigned(csize);
+                        cfg.gridDim              = dim3(unsigned(sms / csize * csize));
+                        if(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0)
+                        {
+                            cudaGetLastError();
+                            n = csize == 2 ? sms / 2 : sms / 8; // a cautious guess for clusters of four
+                        }
+                        if(devOk)
+                            clustersOf[dev][slot].store(n, std::memory_order_relaxed);
                     }
-                    maxClusters = n;
-                    if(devOk)
-                        clustersOf[dev].store(n, std::memory_order_relaxed);
-                }
-                const int64_t pairs    = int64_t(pa.pairsM) * pa.pairsN;
-                // tail split, if the caller's workspace can hold its scratch
-                pa.fullUnits = int(pairs);
-                pa.numUnits  = int(pairs);
-                pa.parts     = 1;
+                    return n;
+                };
+                const int     maxClusters = resident(2);
+                const int64_t tiles       = int64_t(pa.pairsM) * pa.groupsN;
+                pa.fullUnits = int(tiles);
+                pa.numUnits  = int(tiles);
+                // K split over clusters of four CTAs: every tile gets two pairs, all of them resident at once, each
+                // K range at least eight stages long
+                if((p.ksplit == 2 || sw.tcKsplit) && !sw.tcNoSplit && pa.iters >= (sw.tcKsplit ? 2 : 16) && tiles <= resident(4))
+                    pa.ksplit = 2;
+                // Half tiles (256 x 256 tiles only): several waves, the last at most half full. K-major B needs its
+                // 128-row sub-tile to be one box along the first N mode, so that rows 64.. are a coordinate offset; the
+                // N tiles must pair up evenly.
+                CUtensorMap mapB64 = mapB; // stays a copy of B's map (unused by the kernel) unless half tiles run
+                if(nsub == 1 && pa.ksplit == 1 && tiles > maxClusters && !sw.tcNoHalf && a.tilesN % 2 == 0)
                 {
-                    int       parts;
-                    uint64_t  bytes;
-                    const int tail = tailSplit(pairs, maxClusters, pa.iters, &parts, &bytes);
-                    if(tail > 0 && workspace != nullptr && bytes <= workspaceBytes && (uintptr_t(workspace) & 15) == 0
-                       && !sw.tcNoSplit)
-                    {
-                        pa.fullUnits = int(pairs - tail);
-                        pa.parts     = parts;
-                        pa.numUnits  = pa.fullUnits + tail * parts;
-                        pa.flags     = (int*)workspace;
-                        pa.slots     = (float*)((char*)workspace + 1024);
-                        e            = cudaMemsetAsync(workspace, 0, 1024, stream);
-                        if(e != cudaSuccess)
-                            return e;
-                        if(tail > 256)
-                            return cudaErrorInvalidConfiguration;
-                    }
-                    HTB_LOG_HEUR("hiptensorContraction", "pair kernel: %lld tiles on %d CTA pairs, tail %d tiles in %d parts, %d work units",
-                                 (long long)pairs, maxClusters, tail, pa.parts, pa.numUnits);
-                }
-                // Half tiles: several waves, the last at most half full. K-major B needs its 128-row sub-tile to be one
-                // box along the first N mode, so that rows 64.. are a coordinate offset; the N tiles must pair up evenly.
-                CUtensorMap& mapB64 = maps->mapB64;
-                if(maps->half == 0 && p.bMajor)
-                    mapB64 = mapB;
-                if(pa.parts == 1 && pairs > maxClusters && !sw.tcNoHalf && a.tilesN % 2 == 0)
-                {
-                    const int64_t tail   = pairs % maxClusters;
+                    const int64_t tail   = tiles % maxClusters;
                     bool          halfOk = tail > 0 && 2 * tail <= maxClusters;
                     if(halfOk && !p.bMajor)
                     {
                         if(maps->half == 0)
                         {
                             const int box64[4] = {64, 1, 1, 1};
-                            maps->half = (p.boxN128[0] == 128 && encodeOperand(encode, &mapB64, B, bf16, p.K, p.n, p.nn, box64))
+                            maps->half = (p.boxN128[0] == 128 && encodeOperand(encode, &maps->mapB64, B, bf16, p.K, p.n, p.nn, box64))
                                              ? 1
                                              : 2;
                         }
                         halfOk = maps->half == 1;
+                        if(halfOk)
+                            mapB64 = maps->mapB64;
                     }
                     if(halfOk)
                     {
                         pa.halves    = 1;
-                        pa.fullUnits = int(pairs - tail);
-                        pa.numUnits  = int(pairs + tail);
+                        pa.fullUnits = int(tiles - tail);
+                        pa.numUnits  = int(tiles + tail);
                         pa.idescHalf = (1u << 4) | (fmt << 7) | (fmt << 10) | majors | (uint32_t(128 >> 3) << 17)
                                        | (uint32_t(256 >> 4) << 24);
-                        HTB_LOG_HEUR("hiptensorContraction", "pair kernel: last wave of %lld tiles cut into %lld half tiles",
-                                     (long long)tail, (long long)(2 * tail));
                     }
                 }
-                if(!pa.halves && maps->half != 1)
-                    mapB64 = mapB; // unused by the kernel, but a kernel parameter must be a valid map
-                // one CTA pair per work unit, as many as can be resident
-                cfg.gridDim = dim3(unsigned(2 * std::min<int64_t>(pa.numUnits, maxClusters)));
+                HTB_LOG_HEUR("hiptensorContraction",
+                             "pair kernel: %lld tiles of 256 x %d on %d CTA pairs, K split %d, %s, %d work units",
+                             (long long)tiles, 256 * nsub, maxClusters, pa.ksplit, pa.halves ? "last wave in half tiles" : "whole tiles",
+                             pa.numUnits);
+                // one cluster per work unit, as many as can be resident
+                attr[0].val.clusterDim.x = unsigned(2 * pa.ksplit);
+                cfg.gridDim = dim3(unsigned(2 * pa.ksplit * (pa.ksplit > 1 ? int64_t(pa.numUnits) : std::min<int64_t>(pa.numUnits, maxClusters))));
                 e           = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, mapB64, (const TD*)C, (TD*)D, pa, idesc);
                 if(e == cudaSuccess)
-                    noteLaunch("contraction_tcgen05_pair");
+                    noteLaunch(nsub == 2 ? "contraction_tcgen05_pair_wide" : "contraction_tcgen05_pair");
                 return e;
             }
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | majors | (uint32_t(p.tileN >> 3) << 17)

@@ -113,29 +113,28 @@ namespace htb
         return w;
     }
 
-    int tailSplit(int64_t tiles, int clusters, int kBlocks, int* parts, uint64_t* scratchBytes)
+    // Cost model of the CTA-pair tensor-core kernel (microseconds), calibrated on B200 with K = 4096 and
+    // N = 4096 (M = 512 ... 4096, kernels back to back): the kernel is bound by the operand bytes that enter the
+    // SMs from L2, M N K 2 (1 / tile rows + 1 / tile columns) at about 9 TB/s for the whole chip, or by the
+    // tensor cores when few tiles are resident, plus a fixed part (prologue, last epilogue; the accumulator of a
+    // 256 x 512 tile fills tensor memory, so its epilogue is not overlapped; a K split adds the exchange).
+    double pairKernelCost(int64_t M, int64_t N, int64_t K, int nsub, int ksplit, int sms)
     {
-        *parts        = 1;
-        *scratchBytes = 0;
-        if(clusters <= 0 || tiles <= 0)
-            return 0;
-        // Only a machine that is less than half full is worth splitting. With several waves, cutting
-        // the tiles of the last wave gained nothing on B200 (4096^3: 126 us split, 121 us unsplit):
-        // the partly filled wave already runs faster, and the scratch round trip is not free.
-        if(tiles * 2 > clusters)
-            return 0;
-        // The owner of a tile finishes only after the other parts' epilogues and its own, so a part must be
-        // long enough to pay for a second epilogue: at least 16 pipeline stages (2048 K elements). Measured on
-        // B200: 512 x 512 x 8192 49 us split in 4, 54 us whole; 1024 x 1024 x 4096 47 us split in 4, 36 us whole.
-        const int64_t tail = tiles;
-        int p = int(std::min<int64_t>(4, clusters / tail));
-        while(p > 1 && kBlocks / p < 16)
-            p--;
-        if(p < 2)
-            return 0;
-        *parts        = p;
-        *scratchBytes = 1024 + uint64_t(tail) * uint64_t(p - 1) * 256 * 256 * 4; // flags + fp32 slots
-        return int(tail);
+        const double bytesPerUs = 9.0e6, cyclesPerUs = 1500.0;
+        const int64_t pm = (M + 255) / 256, pn = (N + 256 * nsub - 1) / (256 * nsub), tiles = pm * pn;
+        const int64_t pairs = sms / 2, quads = sms / 4 - 1;
+        const int64_t kSteps = (K + 15) / 16, stages = (K + 127) / 128;
+        if(ksplit == 2 && (tiles > quads || stages < 16))
+            return 1e30;
+        const double waves  = double((tiles * ksplit + pairs - 1) / pairs);
+        const double tUnit  = double(kSteps) * 128.0 * nsub / cyclesPerUs / ksplit;
+        const double tBytes = double(pm * 256) * double(pn * 256 * nsub) * double(K) * 2.0 * (1.0 / 256.0 + 1.0 / (256.0 * nsub))
+                              / bytesPerUs;
+        double tail = 0.0;
+        if(nsub == 1 && ksplit == 1 && tiles > pairs && tiles % pairs != 0 && 2 * (tiles % pairs) <= pairs)
+            tail = -0.5 * tUnit; // the last wave runs as half tiles
+        const double fixed = (nsub == 2 ? 4.0 + 3.0 * waves : 6.0) + (ksplit == 2 ? 1.0 : 0.0);
+        return std::max(tBytes, waves * tUnit + tail) + fixed;
     }
 
     int boxDecompose(const ModeDim* dims, int n, int tile, int* box)
@@ -590,35 +589,40 @@ namespace htb
                                && out->N >= 512)
                                   ? 1
                                   : 0;
-                out->pair   = (out->pairOk && ((out->M + 255) / 256) * ((out->N + 255) / 256) >= (smsH * 7) / 16) ? 1 : 0;
-            }
-            out->kind = tc ? CK_TCGEN05 : CK_TILED_SIMT;
-            if(tc && out->pairOk)
-            {
-                // scratch for the tail split, sized for the largest need over the pair counts the
-                // device may grant (GPCs with an odd SM count lose a pair)
-                int64_t tilesM = 1, tilesN = 1;
-                if(out->aMajor)
-                    tilesM = (((gm[0].ext + 63) / 64) * (out->M / gm[0].ext) + 1) / 2;
-                else
-                    for(int i = 0; i < nm; i++)
-                        tilesM *= (gm[i].ext + out->boxM[i] - 1) / out->boxM[i];
-                if(out->bMajor)
-                    tilesN = (((gn[out->nFast].ext + 63) / 64) * (out->N / gn[out->nFast].ext) + 1) / 2;
-                else
-                    for(int i = 0; i < nn; i++)
-                        tilesN *= (gn[i].ext + out->boxN128[i] - 1) / out->boxN128[i];
-                const int64_t tiles   = ((tilesM + 1) / 2) * ((tilesN + 1) / 2);
-                const int     kBlocks = int((out->K + 63) / 64);
-                const int     maxC    = (smCount > 0 ? smCount : 148) / 2;
-                for(int c = std::max(1, maxC - 10); c <= maxC; c++)
+                out->pair   = 0;
+                out->wide   = 0;
+                out->ksplit = 1;
+                if(out->pairOk)
                 {
-                    int      parts;
-                    uint64_t bytes;
-                    tailSplit(tiles, c, (kBlocks + 1) / 2, &parts, &bytes); // two K blocks per pipeline stage
-                    out->workspaceBytes = std::max(out->workspaceBytes, bytes);
+                    // tile width and K split of the pair kernel by the cost model; below a quarter of the CTA pairs'
+                    // worth of 256 x 256 tiles, and between half and 7/8 of them without a K split, single CTAs with
+                    // their smaller tiles fill the machine better
+                    const int64_t tiles256 = ((out->M + 255) / 256) * ((out->N + 255) / 256);
+                    double        best     = 1e30;
+                    for(int nsub = 1; nsub <= 2; nsub++)
+                        for(int ks = 1; ks <= 2; ks++)
+                        {
+                            if(ks == 1 && tiles256 < (smsH * 7) / 16)
+                                continue;
+                            const double c = pairKernelCost(out->M, out->N, out->K, nsub, ks, int(smsH));
+                            if(c < best)
+                            {
+                                best        = c;
+                                out->pair   = 1;
+                                out->wide   = nsub == 2 ? 1 : 0;
+                                out->ksplit = ks;
+                            }
+                        }
+                    if(out->pair && tiles256 < smsH / 8)
+                        out->pair = 0;
+                    if(!out->pair)
+                    {
+                        out->wide   = 0;
+                        out->ksplit = 1;
+                    }
                 }
             }
+            out->kind = tc ? CK_TCGEN05 : CK_TILED_SIMT;
         }
         else if(tA == CUDA_R_32F && (computeType == 4 || computeType == 1 || computeType == 1024))
         {
@@ -989,7 +993,9 @@ namespace htb
                 snprintf(buf, sizeof(buf), "%s%d", i ? " " : "", p.boxN[i]);
                 s += buf;
             }
-            s += p.pair ? "] pair" : "]";
+            s += p.pair ? (p.wide ? "] pair 256x512" : "] pair 256x256") : "]";
+            if(p.pair && p.ksplit > 1)
+                s += " ksplit=2";
         }
         if(p.splitK > 1)
         {

@@ -110,6 +110,8 @@ namespace htb
         int rowsM, rowsN; // rows of the tile that the boxes fill (<= tileM / tileN)
         int pair; // 256 x 256 tile over a CTA pair (tcgen05 cta_group::2), each CTA loading 128 rows of B
         int pairOk; // CK_TCGEN05: the pair kernel can run this problem (pair says whether it is the better choice)
+        int wide; // CK_TCGEN05 pair kernel: 256 x 512 tiles (one accumulator filling tensor memory) instead of 256 x 256
+        int ksplit; // CK_TCGEN05 pair kernel: 2 = every tile's K range cut over the two CTA pairs of a four-CTA cluster
         int boxN128[4], rowsN128; // N boxes of one CTA's sub-tile in the pair kernels (128 rows; 64 for CK_TF32X3)
         int aKContig, bKContig; // operand has its K group folded to one stride-1 mode
         // CK_TF32X3 only: 0 = operand K-major (rows gathered by boxM / boxN), 1 = MN-major (32-row chunks along
@@ -156,10 +158,10 @@ namespace htb
                                int computeType, int smCount, ContractionPlan* out);
     std::string describe(const ContractionPlan& p);
 
-    // K split of the CTA-pair contraction kernel: when `tiles` output tiles fill less than half of the
-    // `clusters` CTA pairs, every tile is cut into `parts` K ranges so that more pairs work. Returns
-    // the number of split tiles (0: no split) and the scratch bytes the split needs.
-    int tailSplit(int64_t tiles, int clusters, int kBlocks, int* parts, uint64_t* scratchBytes);
+    // Estimated time (microseconds) of the CTA-pair tensor-core kernel on an M x N x K problem with 256 x 256
+    // (nsub = 1) or 256 x 512 (nsub = 2) tiles, whole (ksplit = 1) or with every tile's K range cut over two CTA
+    // pairs of a four-CTA cluster (ksplit = 2); 1e30 where the variant cannot run. The planner takes the minimum.
+    double pairKernelCost(int64_t M, int64_t N, int64_t K, int nsub, int ksplit, int sms);
 
     // Splits `tile` rows over the folded modes of a group, fastest mode first: a mode is taken
     // whole while it is a power of two smaller than what is left, the first mode at least as

@@ -135,7 +135,9 @@ namespace htb
             s.tcPair        = envSet("HTB_TC_PAIR");
             s.tcNoHalf      = envSet("HTB_TC_NOHALF");
             s.tcNoSplit     = envSet("HTB_TC_NOSPLIT");
-            s.tcKsub1       = envSet("HTB_TC_KSUB1");
+            s.tcNarrow      = envSet("HTB_TC_NARROW");
+            s.tcWide        = envSet("HTB_TC_WIDE");
+            s.tcKsplit      = envSet("HTB_TC_KSPLIT");
             s.noTf32x3      = envSet("HTB_NO_TF32X3");
             s.tf32Pair      = envSet("HTB_TF32_PAIR");
             s.tf32NoInplace = envSet("HTB_TF32_NOINPLACE");

@@ -240,7 +240,7 @@ def test_config4_full_size_sampled(env):
     err = rel_error(got, exp, td)
     assert 0 <= err < 1e-2, err
     assert not np.isnan(got).any()
-    assert ht.last_kernel_name() == "contraction_tcgen05_pair"
+    assert ht.last_kernel_name() == "contraction_tcgen05_pair_wide"
     got2, _, _ = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F16,
                                  typeD=orc.F32, alpha=2.0, beta=0.0, with_c=False, fill="normal", sample=smp[:8])
     assert np.array_equal(got2, 2.0 * got)  # scaling by a power of two is exact
@@ -351,48 +351,88 @@ def test_cta_pair_kernel_gathered_odd_tiles(env, dt):
     assert not np.isnan(got).any()
 
 
-@pytest.mark.parametrize("shape", [(512, 768, 4096), (640, 896, 4104), (512, 512, 8192)])
-def test_cta_pair_kernel_k_split(env, shape):
-    """Fewer tiles than half the CTA pairs: the tiles are cut along K, partial sums travel through the workspace. Same inputs without a workspace (no split) must agree closely, and both
-    must match the oracle."""
-    import torch
-
+@pytest.mark.parametrize("shape", [(512, 768, 4096), (640, 896, 4104), (512, 512, 8192), (768, 1280, 2048)])
+@pytest.mark.parametrize("wide", [False, True])
+def test_cta_pair_kernel_k_split(env, shape, wide):
+    """Few tiles and a long K on the pair kernel: a cluster is four CTAs, each pair takes half of the K blocks of the
+    tile (uneven halves, ragged last block, odd sub-tile counts), and the CTAs that hold the same rows exchange
+    halves of their partial sums through shared memory. No workspace is involved. The result must match the oracle,
+    be reproducible bit for bit, and agree closely with the unsplit run."""
     ht, h = env
     M, N, K = shape
     m, n, k = 0, 1, 2
     ext = {m: M, n: N, k: K}
     smp = np.random.default_rng(7).integers(0, M * N, 4096)
-    got, exp, td = run_contraction(ht, h, ext, [m, k], [n, k], [m, n], typeAB=orc.F16, typeD=orc.F32, alpha=1.5,
-                                   beta=0.5, fill="normal", sample=smp)
-    assert ht.last_kernel_name() == "contraction_tcgen05_pair"
-    assert not np.isnan(got).any()
-    # stated tolerance for f16 inputs is 1e-2; over 4096-8192 terms the tensor cores' truncating fp32 accumulation
-    # stays within 5e-4 of the reference's sequential fp32 sum
-    assert 0 <= rel_error(got, exp, td) < 5e-4
-    # the same problem planned with no workspace
-    from helpers import SEED_CONTRACTION as S, to_device, to_host
+    name = "contraction_tcgen05_pair_wide" if wide else "contraction_tcgen05_pair"
+    set_switch("HTB_TC_KSPLIT", True)
+    set_switch("HTB_TC_WIDE" if wide else "HTB_TC_NARROW", True)
+    try:
+        runs = []
+        for _ in range(2):
+            got, exp, td = run_contraction(ht, h, ext, [m, k], [n, k], [m, n], typeAB=orc.F16, typeD=orc.F32, alpha=1.5,
+                                           beta=0.5, fill="normal", sample=smp)
+            assert ht.last_kernel_name() == name
+            assert not np.isnan(got).any()
+            # stated tolerance for f16 inputs is 1e-2; over 2048-8192 terms the tensor cores' truncating fp32
+            # accumulation stays within 5e-4 of the reference's sequential fp32 sum
+            assert 0 <= rel_error(got, exp, td) < 5e-4
+            runs.append(got)
+        assert runs[0].tobytes() == runs[1].tobytes()
+        assert h.device_status() == 0
+        set_switch("HTB_TC_NOSPLIT", True)
+        unsplit, _, _ = run_contraction(ht, h, ext, [m, k], [n, k], [m, n], typeAB=orc.F16, typeD=orc.F32, alpha=1.5,
+                                        beta=0.5, fill="normal", sample=smp[:1])
+        assert ht.last_kernel_name() == name
+    finally:
+        for sw in ("HTB_TC_KSPLIT", "HTB_TC_WIDE", "HTB_TC_NARROW", "HTB_TC_NOSPLIT"):
+            set_switch(sw, False)
+    # regrouping 2048-8192 terms of the truncating fp32 accumulation moves results by up to 5e-4 under the metric
+    assert 0 <= rel_error(runs[0], unsplit, orc.F32) < 1e-3
+    assert runs[0].tobytes() != unsplit.tobytes()  # the split really ran another summation order
 
-    lA, lB, lD = [M, K], [N, K], [M, N]
-    A = to_device(orc.fill_normal(M * K, orc.F16, S[0], 0.5), orc.F16)
-    B = to_device(orc.fill_normal(N * K, orc.F16, S[1], 0.5), orc.F16)
-    C = to_device(orc.fill_uniform(M * N, orc.F32, S[2]), orc.F32)
-    D = torch.empty(M * N, device="cuda")
-    dA, dB, dD = (h.tensor_descriptor(l, None, t) for l, t in ((lA, ht.R_16F), (lB, ht.R_16F), (lD, ht.R_32F)))
-    cd = h.contraction_descriptor(dA, [m, k], dB, [n, k], dD, [m, n], dD, [m, n], ht.COMPUTE_32F)
-    find = h.contraction_find()
-    assert h.contraction_workspace_size(cd, find, ht.WORKSPACE_MIN) == 0
-    assert h.contraction_workspace_size(cd, find, ht.WORKSPACE_RECOMMENDED) > 0
-    plan = h.contraction_plan(cd, find, 0)
-    h.contraction(plan, 1.5, A, B, 0.5, C, D)
-    unsplit = to_host(D, orc.F32)
-    # the tensor cores' fp32 accumulation truncates and is not associative: regrouping 4096-8192 terms moves results
-    # by up to 5e-4 under the metric (the stated tolerance for f16 inputs is 1e-2)
-    assert 0 <= rel_error(got, unsplit, orc.F32) < 1e-3
+
+def test_contraction_needs_no_workspace(env):
+    """Every real contraction runs without scratch: the K splits of the tensor-core kernels meet in shared memory."""
+    ht, h = env
+    for dt, dtD in ((ht.R_16F, ht.R_32F), (ht.R_32F, ht.R_32F), (ht.R_64F, ht.R_64F)):
+        dA, dB = (h.tensor_descriptor([512, 4096], None, dt) for _ in range(2))
+        dD = h.tensor_descriptor([512, 512], None, dtD)
+        cd = h.contraction_descriptor(dA, [0, 2], dB, [1, 2], dD, [0, 1], dD, [0, 1],
+                                      ht.COMPUTE_64F if dt == ht.R_64F else ht.COMPUTE_32F)
+        find = h.contraction_find()
+        for pref in (ht.WORKSPACE_MIN, ht.WORKSPACE_RECOMMENDED, ht.WORKSPACE_MAX):
+            assert h.contraction_workspace_size(cd, find, pref) == 0
+
+
+HALF_LAYOUTS = {"kk": ([0, 2], [1, 2]), "mn_mn": ([2, 0], [2, 1]), "k_mn": ([0, 2], [2, 1]), "mn_k": ([2, 0], [1, 2])}
+HALF_OUT = {"f32": orc.F32, "f16": orc.F16}
+
+
+@pytest.mark.parametrize("layout", ["kk", "mn_mn", "k_mn", "mn_k"])
+@pytest.mark.parametrize("shape", [(640, 896, 200), (512, 1024, 72), (1280, 2560, 328)])
+@pytest.mark.parametrize("out", sorted(HALF_OUT))
+def test_cta_pair_kernel_wide_tiles(env, layout, shape, out):
+    """256 x 512 tiles (two MMAs per K step sharing A, one accumulator of 512 columns, eight epilogue warps), forced on
+    problems with odd numbers of 128-row sub-tiles (a tile's last sub-tiles are missing), for the four operand
+    layouts and both output types; several tiles per CTA pair in the largest case."""
+    ht, h = env
+    M, N, K = shape
+    modeA, modeB = HALF_LAYOUTS[layout]
+    smp = np.random.default_rng(9).integers(0, M * N, 8192) if M * N > 1 << 20 else None
+    set_switch("HTB_TC_WIDE", True)
+    try:
+        got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F16, typeD=HALF_OUT[out],
+                                       alpha=1.5, beta=0.5, fill="normal", sample=smp)
+    finally:
+        set_switch("HTB_TC_WIDE", False)
+    assert ht.last_kernel_name() == "contraction_tcgen05_pair_wide"
+    assert not np.isnan(got.astype(np.float32)).any()
+    assert 0 <= rel_error(got, exp, td) < (1e-4 if out == "f32" else 2 * 2.0 ** -10)
+    assert h.device_status() == 0
 
 
 # A / B mode orders (last mode fastest) of D[m, n] = A x B for the reference's four layout variants
 # (which of A/B has K or M/N fastest, contraction_solution_instances.cpp:40-106)
-HALF_LAYOUTS = {"kk": ([0, 2], [1, 2]), "mn_mn": ([2, 0], [2, 1]), "k_mn": ([0, 2], [2, 1]), "mn_k": ([2, 0], [1, 2])}
 
 
 @pytest.mark.parametrize("layout", sorted(HALF_LAYOUTS))
@@ -440,17 +480,23 @@ def test_cta_pair_kernel_half_tiles_in_last_wave(env, layout):
     M, N, K = 2560, 2048, 136
     modeA, modeB = HALF_LAYOUTS[layout]
     smp = np.random.default_rng(5).integers(0, M * N, 8192)
-    got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F16, typeD=orc.F32,
-                                   alpha=1.5, beta=0.5, fill="normal", sample=smp)
+    set_switch("HTB_TC_NARROW", True)
+    try:
+        got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F16, typeD=orc.F32,
+                                       alpha=1.5, beta=0.5, fill="normal", sample=smp)
+    finally:
+        set_switch("HTB_TC_NARROW", False)
     assert ht.last_kernel_name() == "contraction_tcgen05_pair"
     assert not np.isnan(got).any()
     assert 0 <= rel_error(got, exp, td) < 1e-4
     set_switch("HTB_TC_NOHALF", True)
+    set_switch("HTB_TC_NARROW", True)
     try:
         whole, _, _ = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F16, typeD=orc.F32,
                                       alpha=1.5, beta=0.5, fill="normal", sample=smp[:1])
     finally:
         set_switch("HTB_TC_NOHALF", False)
+        set_switch("HTB_TC_NARROW", False)
     assert np.array_equal(got.view(np.uint32), whole.view(np.uint32))
 
 

@@ -29,8 +29,9 @@ def bits(a):
 
 def test_config4_full_size_every_output(env):
     """f16 x f16 -> f32, extents 64 (M = N = K = 4096): all 16.7 M outputs against the fp64 product of the same
-    f16 values. Tolerance: 1e-2 stated for half-precision inputs, 1e-4 asserted (fp32 accumulation of 4096 exact
-    products)."""
+    f16 values. Tolerance: 1e-2 stated for half-precision inputs, 1e-3 asserted: the products are exact, the
+    tensor cores add them to the fp32 accumulator with truncation, so the error grows with K (1e-5 at K = 256,
+    1.6e-4 observed at K = 4096 as the maximum over all outputs)."""
     ht, h = env
     m0, m1, n0, n1, k0, k1 = range(6)
     ext = {m: 64 for m in range(6)}
@@ -38,14 +39,14 @@ def test_config4_full_size_every_output(env):
     got, _, td = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F16,
                                  typeD=orc.F32, alpha=1.0, beta=0.0, with_c=False, fill="normal", oracle=False,
                                  inputs=inp)
-    assert ht.last_kernel_name() == "contraction_tcgen05_pair"
+    assert ht.last_kernel_name() == "contraction_tcgen05_pair_wide"
     assert not np.isnan(got).any()  # D was pre-filled with NaN: every element has been written
     A = inp["A"].astype(np.float64).reshape(4096, 4096)  # [m0 m1][k0 k1], last mode fastest
     B = inp["B"].astype(np.float64).reshape(4096, 4096)  # [n0 n1][k0 k1]
     ref = A @ B.T
     err = rel_error(got.astype(np.float64), ref.reshape(-1), orc.F64)
     assert 0 <= err < 1e-2, err
-    assert err < 1e-4, err
+    assert err < 1e-3, err
 
 
 def test_config5_full_size_every_output(env):
@@ -102,11 +103,13 @@ def test_config4_slab(env, m0_local):
     got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F16,
                                    typeD=orc.F32, alpha=1.0, beta=0.0, with_c=False, fill="normal", sample=smp,
                                    inputs=inp)
-    assert ht.last_kernel_name() in ("contraction_tcgen05", "contraction_tcgen05_pair")
+    # 2048 rows: 256 x 512 tiles; 1024: the same with every tile's K range cut over two CTA pairs; 512: 256 x 256
+    # tiles with the K cut
+    assert ht.last_kernel_name() == ("contraction_tcgen05_pair" if m0_local == 8 else "contraction_tcgen05_pair_wide")
     assert not np.isnan(got).any()
-    assert 0 <= rel_error(got, exp, td) < 1e-4
+    assert 0 <= rel_error(got, exp, td) < 1e-3  # two fp32 summation orders of 4096 products
     ref = inp["A"].astype(np.float64).reshape(M, 4096) @ inp["B"].astype(np.float64).reshape(4096, 4096).T
-    assert 0 <= rel_error(got.astype(np.float64), ref.reshape(-1), orc.F64) < 1e-4
+    assert 0 <= rel_error(got.astype(np.float64), ref.reshape(-1), orc.F64) < 1e-3
 
 
 @pytest.mark.parametrize("d_local", [16, 32, 64])

@@ -121,8 +121,7 @@ def test_contraction_fp32_tensor_core_layouts(ht):
 def test_contraction_k_split_plans(ht):
     """Few tiles and a long K: the fp32 tensor-core plan cuts K into up to four ranges (at least four K blocks
     each, never more CTAs than SMs), one CTA of a cluster each; the sums meet in shared memory, so no workspace is
-    asked for. Many tiles or a short K do not split. The f16 plan asks for tail-split workspace only when the
-    tile count leaves a tail of CTA pairs."""
+    asked for. Many tiles or a short K do not split."""
     import re
 
     def plan(M, N, K, t):
@@ -138,8 +137,30 @@ def test_contraction_k_split_plans(ht):
     assert m and int(m.group(1)) == 3, d
     assert "splitK" not in plan(256, 192, 96, ht.R_32F)  # too few K blocks
     assert "splitK" not in plan(4096, 4096, 1024, ht.R_32F)  # enough tiles for every SM
-    # f16: one wave of 256 x 256 tiles has nothing to split; a few tiles more than a wave have a tail
     assert "splitK" not in plan(256, 256, 4096, ht.R_16F)
+
+
+def test_contraction_pair_kernel_variants(ht):
+    """f16 problems on the CTA-pair kernel: tile width and K split by the planner's cost model. The slabs of an
+    N-way split of a 4096^3 problem (M = 4096 / N): 256 x 512 tiles while the tiles fill the CTA pairs, the
+    same with every tile's K range cut over two pairs when they fill half of them, 256 x 256 tiles with the K
+    cut for the smallest slab; small problems stay on single CTAs."""
+    def plan(M, N, K):
+        return ht.describe_contraction_plan([M, K], [K, 1], [0, 2], ht.R_16F, [N, K], [K, 1], [1, 2], ht.R_16F, [M, N],
+                                            [N, 1], [0, 1], ht.R_32F, False, ht.COMPUTE_32F)
+
+    d = plan(4096, 4096, 4096)
+    assert "pair 256x512" in d and "ksplit" not in d, d
+    d = plan(2048, 4096, 4096)
+    assert "pair 256x512" in d and "ksplit" not in d, d
+    d = plan(1024, 4096, 4096)
+    assert "pair 256x512 ksplit=2" in d, d
+    d = plan(512, 4096, 4096)
+    assert "pair 256x256 ksplit=2" in d, d
+    assert "pair" not in plan(512, 512, 4096)  # four tiles: single CTAs with their own cluster K split
+    assert "ksplit" not in plan(1024, 4096, 512)  # a short K is not worth the exchange
+    # no contraction asks for workspace
+    assert "workspace" not in d
 
 
 def test_contraction_config4(ht):
@@ -164,12 +185,14 @@ def test_contraction_f16_tile_choice_by_size(ht):
                                             [N, 1], [0, 1], ht.R_32F, False, ht.COMPUTE_32F)
 
     d = plan(512, 512, 512)
-    assert "tile=128x64x64" in d and not d.endswith("pair"), d
+    assert "tile=128x64x64" in d and " pair" not in d, d
     d = plan(2048, 2048, 2048)
-    assert "tile=128x256x64" in d and d.rstrip().endswith("pair"), d  # 64 pair tiles
-    d = plan(512, 4096, 4096)
-    assert "tile=128x128x64" in d and not d.rstrip().endswith("pair"), d  # 32 pair tiles: single CTAs
-    assert plan(4096, 4096, 4096).rstrip().endswith("pair")
+    assert "tile=128x256x64" in d and " pair " in d, d  # 64 tiles of 256 x 256: CTA pairs
+    d = plan(1536, 1536, 4096)
+    assert " pair " in d and "ksplit=2" in d, d  # 36 tiles of 256 x 256 and a long K: pairs with the K cut
+    d = plan(768, 768, 512)
+    assert " pair" not in d, d  # nine tiles, short K: single CTAs
+    assert " pair 256x512" in plan(4096, 4096, 4096)
 
 
 def test_contraction_config5(ht):
