@@ -62,7 +62,7 @@ namespace htb
             int     parts; // single-CTA kernel: K ranges per tile (CTAs of one cluster); 0 or 1 = no split
 #ifdef HTB_MEASURE
             int     probe; // measurement builds only, bit mask: 1 = producer skips the loads, 2 = issuer skips the
-                           // MMAs (results invalid)
+                           // MMAs, 4 = the pair kernel's epilogue skips its stores (results invalid)
 #endif
             int*    status;
             // chunked row groups of MN-major operands (kernel instantiations with LAYOUT != 0 only)
@@ -921,6 +921,10 @@ namespace htb
 
                     // alpha / beta and the stores of 32 accumulator columns c0 .. c0 + 31 of this thread's row
                     auto storeChunk = [&](uint32_t(&v)[32], int c0) {
+#ifdef HTB_MEASURE
+                        if(a.probe & 4)
+                            return;
+#endif
                         const int64_t first     = colOff[c0];
                         const bool    fullChunk = a.nContig && first >= 0 && colOff[c0 + 31] == first + 31;
                         if constexpr(sizeof(TD) == 4)

@@ -58,7 +58,7 @@ def test_config5_full_size_every_output(env):
     inp = {}
     got, _, td = run_contraction(ht, h, ext, [m0, k0, m1, k1, m2], [k1, n0, k0, n1], [m0, m1, m2, n0, n1],
                                  typeAB=orc.F64, alpha=2.0, beta=0.5, oracle=False, inputs=inp)
-    assert ht.last_kernel_name() == "contraction_dmma"
+    assert ht.last_kernel_name() == "contraction_tiled_dmma"
     assert not np.isnan(got).any()
     A = inp["A"].reshape(16, 48, 16, 48, 16).transpose(0, 2, 4, 1, 3).reshape(4096, 2304)  # [m0 m1 m2][k0 k1]
     B = inp["B"].reshape(48, 48, 48, 48).transpose(1, 3, 2, 0).reshape(2304, 2304)  # [n0 n1][k0 k1]
