@@ -63,6 +63,7 @@ namespace htb
 #ifdef HTB_MEASURE
             int     probe; // measurement builds only, bit mask: 1 = producer skips the loads, 2 = issuer skips the
                            // MMAs, 4 = the pair kernel's epilogue skips its stores (results invalid)
+            unsigned long long* trace; // measurement builds only: time stamps (ns) of cluster 0's roles, or null
 #endif
             int*    status;
             // chunked row groups of MN-major operands (kernel instantiations with LAYOUT != 0 only)
@@ -538,6 +539,23 @@ namespace htb
         // (st.shared::cluster), between two cluster barriers, adds what it received to what it kept, applies
         // alpha / beta and stores: no scratch in global memory, the exchange and the stores are spread over all
         // four SMs, and a + b = b + a keeps the result independent of which CTA adds.
+#ifdef HTB_MEASURE
+        // time stamp k of `role` (0 producer, 1 issuer, 2 first epilogue thread, 3 thread 0) in work unit `unit`,
+        // cluster 0 only: trace[((rank * 4 + role) * 8 + unit) * 8 + k]
+#define HTB_STAMP(role, unit, k)                                                                                  \
+    do                                                                                                            \
+    {                                                                                                             \
+        if(a.trace && clusterId == 0 && (unit) < 8)                                                               \
+        {                                                                                                         \
+            unsigned long long t_;                                                                                \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                \
+            a.trace[((rank * 4 + (role)) * 8 + (unit)) * 8 + (k)] = t_;                                           \
+        }                                                                                                         \
+    } while(0)
+#else
+#define HTB_STAMP(role, unit, k)
+#endif
+
         struct TcPairArgs
         {
             TcArgs base; // boxN / tilesPerDimN / tilesN describe 128-row N sub-tiles here
@@ -550,6 +568,12 @@ namespace htb
             // wave then takes half as long. A half unit loads 64 rows of B per CTA and issues MMAs with N = 128.
             int      fullUnits, halves;
             uint32_t idescHalf;
+            // Output by TMA (fp32 D whose rows and columns are one folded mode each, columns contiguous, no C): the
+            // epilogue warps write their 32 x 32 blocks into 128-byte-swizzled shared memory and one lane per warp
+            // issues a bulk tensor store, which leaves the SM asynchronously (plain st.global of a 128 x 256 block
+            // was measured to take 4-7 us and cannot overlap anything). storeBufs 4 KiB slots per warp.
+            int      tmaStore, storeBufs;
+            uint32_t storeOffset; // of the slots (tmaStore) or of the column-offset table (otherwise) in the tile memory
         };
 
         struct TcUnit
@@ -599,8 +623,9 @@ namespace htb
         __global__ void __launch_bounds__(64 + 128 * NSUB, 1)
             contraction_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap mapA,
                                             const __grid_constant__ CUtensorMap mapB,
-                                            const __grid_constant__ CUtensorMap mapB64, const TD* C, TD* D,
-                                            TcPairArgs pa, uint32_t idesc) // C may alias D
+                                            const __grid_constant__ CUtensorMap mapB64,
+                                            const __grid_constant__ CUtensorMap mapD, const TD* C, TD* D, TcPairArgs pa,
+                                            uint32_t idesc) // C may alias D
         {
             constexpr int KSUB = (NSUB == 1) ? 2 : 1; // 64-wide K blocks per pipeline stage
             constexpr int EPI  = 128 * NSUB; // epilogue threads per CTA
@@ -614,7 +639,9 @@ namespace htb
             __shared__ __align__(8) unsigned long long tmemFullBar[2], tmemEmptyBar[2];
             __shared__ uint32_t tmemBase;
             __shared__ int      abortFlag;
-            __shared__ int64_t  colOff[W]; // D offset of every column of the tile, shared by the epilogue warps
+            // D offset of every column of the tile, shared by the epilogue warps (plain stores only): W entries that
+            // live behind the pipeline stages, where the TMA-store slots lie otherwise
+            int64_t* colOff = (int64_t*)(tiles + pa.storeOffset);
 
             const int      warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
             const uint32_t rank = clusterRank();
@@ -627,11 +654,15 @@ namespace htb
             const int      clusterId   = blockIdx.x / csize;
             const int      numClusters = gridDim.x / csize;
 
+            if(threadIdx.x == 0)
+                HTB_STAMP(3, 0, 0);
             if(threadIdx.x == 32)
             {
                 prefetchTensorMap(&mapA);
                 prefetchTensorMap(&mapB);
                 prefetchTensorMap(&mapB64);
+                if(pa.tmaStore)
+                    prefetchTensorMap(&mapD);
             }
             if(threadIdx.x == 0)
             {
@@ -663,12 +694,15 @@ namespace htb
             volatile int*  abortP = &abortFlag;
             const uint32_t tilesAddr = smemAddr(tiles);
             const uint32_t fullAddr = smemAddr(&fullBar[0]), emptyAddr = smemAddr(&emptyBar[0]);
+            if(threadIdx.x == 0)
+                HTB_STAMP(3, 0, 1);
 
             if(warp == 0)
             {
                 // ---------------------------------------------------------------- TMA producer
                 if(lane == 0)
                 {
+                    int            unitNo = 0;
                     const uint32_t leaderFull = mapToRank(fullAddr, leaderRank);
                     const uint32_t txWhole    = 2 * KSUB * a.stageBytes; // both CTAs' boxes of one stage
                     uint32_t       stage = 0, phase = 0;
@@ -709,11 +743,14 @@ namespace htb
                             qB[0].i2[0] = qB[0].i2[pairRank];
                         }
                         const int a1 = cA[0], a2 = cA[1], a3 = cA[2], a4 = cA[3];
+                        HTB_STAMP(0, unitNo, 0);
                         for(int it = w.kbBegin; it < w.kbEnd; it++)
                         {
                             ok = mbarWaitTight(emptyAddr + 8 * stage, phase ^ 1, abortP);
                             if(!ok)
                                 break;
+                            if(it == w.kbBegin)
+                                HTB_STAMP(0, unitNo, 1);
 #ifdef HTB_MEASURE
                             if(a.probe & 1)
                             {
@@ -760,6 +797,8 @@ namespace htb
                                 phase ^= 1;
                             }
                         }
+                        HTB_STAMP(0, unitNo, 2);
+                        unitNo++;
                     }
                 }
                 if(pa.ksplit > 1)
@@ -787,9 +826,11 @@ namespace htb
                         const TcUnit   w        = unitOf(pa, u, kpart);
                         const int      acc      = local % NACC;
                         const uint32_t accPhase = (local / NACC) & 1;
+                        HTB_STAMP(1, local, 0);
                         ok = mbarWaitTight(smemAddr(&tmemEmptyBar[acc]), accPhase ^ 1, abortP);
                         if(!ok)
                             break;
+                        HTB_STAMP(1, local, 1);
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint32_t dTmem = tmem + uint32_t(acc * 256);
                         const uint32_t idescU = (w.half >= 0) ? pa.idescHalf : idesc; // N = 128 for a half tile
@@ -798,6 +839,12 @@ namespace htb
                             ok = mbarWaitTight(fullAddr + 8 * stage, phase, abortP);
                             if(!ok)
                                 break;
+                            if(it == w.kbBegin)
+                                HTB_STAMP(1, local, 2);
+                            if(it == w.kbBegin + 1)
+                                HTB_STAMP(1, local, 3);
+                            if(it == w.kbEnd - 1)
+                                HTB_STAMP(1, local, 4);
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                             // descriptor address field counts 16-byte units
                             const uint64_t descA = descBaseA + uint64_t((stage * kStage) >> 4);
@@ -839,6 +886,7 @@ namespace htb
                                          "[%0], %1;" ::"r"(smemAddr(&tmemFullBar[acc])),
                                          "h"(pairMask)
                                          : "memory");
+                        HTB_STAMP(1, local, 5);
                     }
                 }
                 if(pa.ksplit > 1)
@@ -857,6 +905,7 @@ namespace htb
                 const int colGroup = (warp - 2) >> 2; // NSUB = 2: which half of the columns this warp takes
                 int       local = 0;
                 int       syncs = 0; // cluster meeting points of the K-split exchange passed so far
+                int       storeSeq = 0; // bulk stores this warp has issued (they rotate over its slots)
                 auto      loadChunk = [&](uint32_t addr, uint32_t(&v)[32]) {
                     asm volatile(
                         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -884,7 +933,7 @@ namespace htb
                     // the table of column offsets, filled by all epilogue threads once nobody reads the previous one
                     epiBarrierAny<EPI>(false);
                     const int ncols = (w.half >= 0) ? 128 : W; // a half tile: the 128 columns of sub-tile `half`
-                    for(int c = et; c < ncols; c += EPI)
+                    for(int c = et; c < ncols && !pa.tmaStore; c += EPI)
                     {
                         const int tnRaw = (w.half >= 0) ? 2 * pn + w.half : 2 * NSUB * pn + (c >> 7);
                         int64_t   off   = -1;
@@ -907,8 +956,13 @@ namespace htb
                     // one lane waits for the accumulator; the barrier completes the table and tells every epilogue
                     // thread of the CTA whether a wait ran out (all of them then leave together)
                     bool failed = false;
+                    if(et == 0)
+                        HTB_STAMP(2, local, 0);
                     if(lane == 0)
                         failed = !mbarWait(smemAddr(&tmemFullBar[acc]), accPhase, abortP);
+                    if(et == 0)
+                        HTB_STAMP(2, local, 1);
+                    __syncwarp();
                     if(epiBarrierAny<EPI>(failed))
                         break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -925,6 +979,52 @@ namespace htb
                         if(a.probe & 4)
                             return;
 #endif
+                        if(pa.tmaStore)
+                        {
+                            // the chunk's sub-tile; sub-tiles beyond the tensor and the rows of a CTA that repeats its
+                            // peer's rows are dropped, ragged edges are clipped by the bulk store itself
+                            const int tnRaw = (w.half >= 0) ? 2 * pn + w.half : 2 * NSUB * pn + (c0 >> 7);
+                            if(dupM || tnRaw >= a.tilesN)
+                                return;
+                            const uint32_t slot = tilesAddr + pa.storeOffset
+                                                  + uint32_t(((warp - 2) * pa.storeBufs + storeSeq % pa.storeBufs) * 4096);
+                            storeSeq++;
+                            // the slot is free once the bulk stores issued before its last use have read their data
+                            if(lane == 0)
+                            {
+                                if(pa.storeBufs >= 4)
+                                    asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+                                else if(pa.storeBufs == 2)
+                                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                                else
+                                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                            }
+                            __syncwarp();
+                            // row `lane` of the 32 x 32 block: 128 bytes, its 16-byte units permuted by the 128-byte swizzle
+                            const uint32_t rowAddr = slot + uint32_t(lane) * 128u;
+#pragma unroll
+                            for(int j = 0; j < 8; j++)
+                            {
+                                const float x0 = __fmul_rn(a.alpha, __uint_as_float(v[4 * j])),
+                                            x1 = __fmul_rn(a.alpha, __uint_as_float(v[4 * j + 1])),
+                                            x2 = __fmul_rn(a.alpha, __uint_as_float(v[4 * j + 2])),
+                                            x3 = __fmul_rn(a.alpha, __uint_as_float(v[4 * j + 3]));
+                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + uint32_t((j ^ (lane & 7)) << 4)),
+                                             "f"(x0), "f"(x1), "f"(x2), "f"(x3)
+                                             : "memory");
+                            }
+                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            __syncwarp();
+                            if(lane == 0)
+                            {
+                                const int col = tnRaw * 128 + (c0 & 127), rowC = tm * 128 + quad * 32;
+                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&mapD),
+                                             "r"(slot), "r"(col), "r"(rowC)
+                                             : "memory");
+                                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            }
+                            return;
+                        }
                         const int64_t first     = colOff[c0];
                         const bool    fullChunk = a.nContig && first >= 0 && colOff[c0 + 31] == first + 31;
                         if constexpr(sizeof(TD) == 4)
@@ -1055,6 +1155,8 @@ namespace htb
                         const uint32_t zone = tilesAddr + uint32_t(row) * 16u + uint32_t(colGroup * 4) * 16384u;
                         clusterSync(); // every CTA of the cluster has its sums: all stage memory is idle
                         syncs++;
+                        if(et == 0)
+                            HTB_STAMP(2, local, 2);
                         const uint32_t remote = mapToRank(zone, rank ^ 2u);
 #pragma unroll 1
                         for(int c0 = 0; c0 < 128; c0 += 32)
@@ -1068,13 +1170,19 @@ namespace htb
                                              "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
                                              : "memory");
                         }
+                        if(et == 0)
+                            HTB_STAMP(2, local, 3);
                         clusterSync(); // the partner's sums have arrived
                         syncs++;
+                        if(et == 0)
+                            HTB_STAMP(2, local, 4);
 #pragma unroll 1
                         for(int c0 = 0; c0 < 128; c0 += 32)
                         {
                             uint32_t v[32];
                             loadChunk(taddr + uint32_t(keep + c0), v);
+                            if(et == 0 && c0 == 0)
+                                HTB_STAMP(2, local, 6);
                             const uint32_t src = zone + uint32_t(c0 >> 5) * 16384u;
 #pragma unroll
                             for(int j = 0; j < 8; j++)
@@ -1089,6 +1197,8 @@ namespace htb
                                 v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + p4.w);
                             }
                             storeChunk(v, keep + c0);
+                            if(et == 0 && c0 == 0)
+                                HTB_STAMP(2, local, 7);
                         }
                     }
                     else
@@ -1101,9 +1211,15 @@ namespace htb
                         {
                             uint32_t v[32];
                             loadChunk(taddr + uint32_t(c0), v);
+                            if(et == 0 && c0 == cBegin)
+                                HTB_STAMP(2, local, 6);
                             storeChunk(v, c0);
+                            if(et == 0 && c0 == cBegin)
+                                HTB_STAMP(2, local, 7);
                         }
                     }
+                    if(et == 0)
+                        HTB_STAMP(2, local, 5);
                     // hand the accumulator back: every epilogue thread of the pair arrives on the leader's barrier
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     const uint32_t emptyBarAddr = mapToRank(smemAddr(&tmemEmptyBar[acc]), leaderRank);
@@ -1111,12 +1227,19 @@ namespace htb
                 }
                 for(; pa.ksplit > 1 && syncs < 2; syncs++)
                     clusterSync(); // a CTA whose wait ran out still meets the others
+                // the bulk stores of this warp have left shared memory and reached global memory
+                if(pa.tmaStore && lane == 0)
+                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
             }
 
             // ---------------------------------------------------------------- teardown
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncthreads();
+            if(threadIdx.x == 0)
+                HTB_STAMP(3, 0, 2);
             clusterSync(); // all CTAs are done with tensor memory and with each other's barriers and shared memory
+            if(threadIdx.x == 0)
+                HTB_STAMP(3, 0, 3);
             if(threadIdx.x == 0 && abortFlag && a.status)
                 atomicExch(a.status, 3);
             if(warp == 1)
@@ -1249,6 +1372,8 @@ namespace htb
             a.status     = status;
 #ifdef HTB_MEASURE
             a.probe = sw.tcProbe;
+            if(const char* env = getenv("HTB_TC_TRACE_PTR")) // device buffer of 4 * 4 * 8 * 8 words, made by the caller
+                a.trace = (unsigned long long*)strtoull(env, nullptr, 0);
 #endif
             if(int64_t(a.tilesM) * a.tilesN > 0x7fffffffll || a.stages > kMaxStages)
                 return cudaErrorInvalidConfiguration;
@@ -1273,15 +1398,17 @@ namespace htb
                 pa.ksplit    = 1;
                 const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | majors | (uint32_t(256 >> 3) << 17)
                                        | (uint32_t(256 >> 4) << 24);
-                using PairKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const TD*, TD*, TcPairArgs,
-                                            uint32_t);
+                using PairKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const TD*,
+                                            TD*, TcPairArgs, uint32_t);
                 static const PairKernel kernels[2][4] = {
                     {contraction_tcgen05_pair_kernel<TD, 0, 1>, contraction_tcgen05_pair_kernel<TD, 1, 1>,
                      contraction_tcgen05_pair_kernel<TD, 2, 1>, contraction_tcgen05_pair_kernel<TD, 3, 1>},
                     {contraction_tcgen05_pair_kernel<TD, 0, 2>, contraction_tcgen05_pair_kernel<TD, 1, 2>,
                      contraction_tcgen05_pair_kernel<TD, 2, 2>, contraction_tcgen05_pair_kernel<TD, 3, 2>}};
                 PairKernel kernel = kernels[nsub - 1][layout];
-                const size_t smem = size_t(192) * 1024 + 1024;
+                // pipeline stages, alignment slack, and 32 KiB behind the stages for the TMA-store slots (or the table of
+                // column offsets of the plain stores)
+                const size_t smem = size_t(192) * 1024 + 1024 + 32 * 1024;
                 cudaError_t  e    = ensureDynamicSmem((const void*)kernel, int(smem));
                 if(e != cudaSuccess)
                     return e;
@@ -1357,6 +1484,41 @@ namespace htb
                                        | (uint32_t(256 >> 4) << 24);
                     }
                 }
+                // Output by bulk tensor stores: fp32 D with one folded row mode and one contiguous column mode, no C
+                // (a tensor map needs 16-byte aligned base and row stride)
+                pa.storeOffset = uint32_t(192 * 1024);
+                pa.storeBufs   = 1;
+                CUtensorMap mapD = mapA; // a valid map even when unused
+                if(sizeof(TD) == 4 && p.typeD == CUDA_R_32F && !a.bilinear && !sw.tcNoTmaStore && p.nm == 1 && p.nn == 1
+                   && p.n[0].s1 == 1 && (p.m[0].s1 % 4) == 0 && (uintptr_t(D) & 15) == 0 && p.N < (int64_t(1) << 31)
+                   && p.M < (int64_t(1) << 31) && (p.m[0].ext == 1 || p.m[0].s1 >= p.N))
+                {
+                    if(maps->D != D)
+                    {
+                        cuuint64_t gdim[2] = {cuuint64_t(p.N), cuuint64_t(p.M)}, gstr[1] = {cuuint64_t(p.m[0].s1) * 4};
+                        cuuint32_t bx[2] = {32, 32}, estr[2] = {1, 1};
+                        if(gstr[0] == 0)
+                            gstr[0] = cuuint64_t(p.N) * 4;
+                        const bool ok = encode(&maps->mapD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, D, gdim, gstr, bx, estr,
+                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+                                        == CUDA_SUCCESS;
+                        maps->D = ok ? D : nullptr;
+                    }
+                    if(maps->D == D)
+                    {
+                        mapD        = maps->mapD;
+                        pa.tmaStore = 1;
+                        if(pa.ksplit > 1)
+                        {
+                            // the exchange zone takes the first (tile columns / 2) x 512 bytes of the idle stage memory
+                            pa.storeOffset = uint32_t(128 * nsub * 512);
+                            pa.storeBufs   = nsub == 1 ? 4 : 2;
+                        }
+                        else
+                            pa.storeBufs = nsub == 1 ? 2 : 1;
+                    }
+                }
                 HTB_LOG_HEUR("hiptensorContraction",
                              "pair kernel: %lld tiles of 256 x %d on %d CTA pairs, K split %d, %s, %d work units",
                              (long long)tiles, 256 * nsub, maxClusters, pa.ksplit, pa.halves ? "last wave in half tiles" : "whole tiles",
@@ -1364,7 +1526,7 @@ namespace htb
                 // one cluster per work unit, as many as can be resident
                 attr[0].val.clusterDim.x = unsigned(2 * pa.ksplit);
                 cfg.gridDim = dim3(unsigned(2 * pa.ksplit * (pa.ksplit > 1 ? int64_t(pa.numUnits) : std::min<int64_t>(pa.numUnits, maxClusters))));
-                e           = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, mapB64, (const TD*)C, (TD*)D, pa, idesc);
+                e           = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, mapB64, mapD, (const TD*)C, (TD*)D, pa, idesc);
                 if(e == cudaSuccess)
                     noteLaunch(nsub == 2 ? "contraction_tcgen05_pair_wide" : "contraction_tcgen05_pair");
                 return e;

@@ -73,7 +73,8 @@ namespace htb
         const void *A, *B;
         int         variant;
         int         half; // f16 pair kernel, 64-row B map of the half tiles: 0 not made yet, 1 made, 2 cannot be made
-        CUtensorMap mapA, mapB, mapB64;
+        const void* D; // f16 pair kernel: the output that mapD was encoded for (null: none yet)
+        CUtensorMap mapA, mapB, mapB64, mapD;
     };
     // The entry for this key; *hit says whether its maps are already encoded. On a miss the caller encodes into
     // the entry (and sets id = 0 if that fails).

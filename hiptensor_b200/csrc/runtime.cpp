@@ -138,6 +138,7 @@ namespace htb
             s.tcNarrow      = envSet("HTB_TC_NARROW");
             s.tcWide        = envSet("HTB_TC_WIDE");
             s.tcKsplit      = envSet("HTB_TC_KSPLIT");
+            s.tcNoTmaStore  = envSet("HTB_TC_NOTMASTORE");
             s.noTf32x3      = envSet("HTB_NO_TF32X3");
             s.tf32Pair      = envSet("HTB_TF32_PAIR");
             s.tf32NoInplace = envSet("HTB_TF32_NOINPLACE");
@@ -215,6 +216,7 @@ namespace htb
         {
             uncached.id   = 0;
             uncached.half = 0;
+            uncached.D    = nullptr;
             return &uncached;
         }
         for(int i = 0; i < kEntries; i++)
@@ -230,6 +232,7 @@ namespace htb
         e->B             = B;
         e->variant       = variant;
         e->half          = 0;
+        e->D             = nullptr;
         return e;
     }
 
