@@ -568,6 +568,15 @@ namespace htb
             // wave then takes half as long. A half unit loads 64 rows of B per CTA and issues MMAs with N = 128.
             int      fullUnits, halves;
             uint32_t idescHalf;
+            // A 128-column sub-tile can run alone: 64 rows of B per CTA (K-major B: second tensor map with 64-row boxes),
+            // MMAs with N = 128. Without it an odd sub-tile at the edge is paired with a repeat of itself.
+            int      singleOk;
+            // Streamed tiles (NSUB = 2, whole K). The N sub-tiles of all row blocks form one sequence of subTotal
+            // entries that is dealt to the CTA pairs in equal contiguous shares; a pair cuts its share into tiles of up
+            // to four sub-tiles of one row block (256 x 512, 384, 256 or 128). Every pair gets the same work (128 tiles of
+            // 256 x 512 on 74 pairs would take two full rounds for 1.73 rounds of work), and the pairs reach their tile
+            // ends, where the stores burst, at different times.
+            int      stream, subTotal;
             // Output by TMA (fp32 D whose rows and columns are one folded mode each, columns contiguous, no C): the
             // epilogue warps write their 32 x 32 blocks into 128-byte-swizzled shared memory and one lane per warp
             // issues a bulk tensor store, which leaves the SM asynchronously (plain st.global of a 128 x 256 block
@@ -578,28 +587,70 @@ namespace htb
 
         struct TcUnit
         {
-            int tile, kbBegin, kbEnd; // stage range [kbBegin, kbEnd)
-            int half; // -1: whole tile; 0 / 1: N half of the tile
+            int pm, s0, cnt; // row block (256 rows), first N sub-tile, number of N sub-tiles (1 .. 2 * NSUB)
+            int kbBegin, kbEnd; // stage range [kbBegin, kbEnd)
         };
-        __device__ __forceinline__ TcUnit unitOf(const TcPairArgs& pa, int u, int kpart)
+        struct TcSched
         {
-            TcUnit w;
-            w.half    = -1;
-            w.tile    = u;
-            w.kbBegin = 0;
-            w.kbEnd   = pa.iters;
+            int u, g, gEnd;
+        };
+        __device__ __forceinline__ TcSched schedInit(const TcPairArgs& pa, int clusterId, int numClusters)
+        {
+            TcSched sc;
+            sc.u    = clusterId;
+            sc.g    = int((long long)pa.subTotal * clusterId / numClusters);
+            sc.gEnd = int((long long)pa.subTotal * (clusterId + 1) / numClusters);
+            return sc;
+        }
+        // the next work unit of this cluster; false when there is none
+        template <int NSUB>
+        __device__ __forceinline__ bool schedNext(const TcPairArgs& pa, int numClusters, int kpart, TcSched& sc, TcUnit& w)
+        {
+            const int S = pa.base.tilesN;
+            w.kbBegin   = 0;
+            w.kbEnd     = pa.iters;
+            if(NSUB == 2 && pa.stream)
+            {
+                if(sc.g >= sc.gEnd)
+                    return false;
+                w.pm  = sc.g / S;
+                w.s0  = sc.g - w.pm * S;
+                w.cnt = min(min(4, S - w.s0), sc.gEnd - sc.g);
+                sc.g += w.cnt;
+                return true;
+            }
+            if(sc.u >= pa.numUnits)
+                return false;
+            const int u = sc.u;
+            sc.u += numClusters;
             if(pa.ksplit > 1)
             {
                 w.kbBegin = int((long long)pa.iters * kpart / pa.ksplit);
                 w.kbEnd   = int((long long)pa.iters * (kpart + 1) / pa.ksplit);
             }
-            else if(pa.halves && u >= pa.fullUnits)
+            int tile = u, half = -1;
+            if(pa.halves && u >= pa.fullUnits)
             {
                 const int x = u - pa.fullUnits;
-                w.tile      = pa.fullUnits + (x >> 1);
-                w.half      = x & 1;
+                tile        = pa.fullUnits + (x >> 1);
+                half        = x & 1;
             }
-            return w;
+            w.pm         = tile % pa.pairsM;
+            const int pn = tile / pa.pairsM;
+            w.s0         = 2 * NSUB * pn + (half >= 0 ? half : 0);
+            w.cnt        = half >= 0 ? 1 : min(2 * NSUB, S - w.s0);
+            return true;
+        }
+        // sub-tiles of accumulator half h of a unit: valid ones, and loaded ones (an odd one that cannot run alone
+        // is paired with a repeat)
+        __device__ __forceinline__ int subValid(const TcUnit& w, int h)
+        {
+            return max(0, min(2, w.cnt - 2 * h));
+        }
+        __device__ __forceinline__ int subLoaded(const TcPairArgs& pa, const TcUnit& w, int h)
+        {
+            const int v = subValid(w, h);
+            return (v == 1 && !pa.singleOk) ? 2 : v;
         }
 
         // barrier of the epilogue warps of one CTA (named barrier 1) that also tells every thread whether any of
@@ -704,22 +755,19 @@ namespace htb
                 {
                     int            unitNo = 0;
                     const uint32_t leaderFull = mapToRank(fullAddr, leaderRank);
-                    const uint32_t txWhole    = 2 * KSUB * a.stageBytes; // both CTAs' boxes of one stage
                     uint32_t       stage = 0, phase = 0;
                     bool           ok = true;
-                    for(int u = clusterId; u < pa.numUnits && ok; u += numClusters)
+                    TcSched        sched = schedInit(pa, clusterId, numClusters);
+                    TcUnit         w;
+                    while(ok && schedNext<NSUB>(pa, numClusters, kpart, sched, w))
                     {
-                        const TcUnit w  = unitOf(pa, u, kpart);
-                        const int    pm = w.tile % pa.pairsM, pn = w.tile / pa.pairsM;
-                        const int    tm = min(2 * pm + int(pairRank), a.tilesM - 1);
-                        // B rows of this CTA: per accumulator half h, 128-row sub-tile 2 h + pairRank of the tile; in a half
-                        // unit the 64-row piece `pairRank` of sub-tile `half` (K-major: second tensor map with 64-row boxes;
-                        // MN-major: one chunk instead of two)
-                        const bool   isHalf = w.half >= 0;
-                        const CUtensorMap* mb = isHalf ? &mapB64 : &mapB;
-                        const uint32_t txBytes = isHalf ? txWhole - 2 * KSUB * 8192 : txWhole;
-                        int          cA[4] = {0, 0, 0, 0}, cB[NSUB][4];
+                        const int    tm = min(2 * w.pm + int(pairRank), a.tilesM - 1);
+                        // B rows of this CTA, per accumulator half h: two sub-tiles -> the 128 rows of sub-tile
+                        // s0 + 2 h + pairRank; one sub-tile -> its 64-row piece `pairRank` (K-major: second tensor map
+                        // with 64-row boxes; MN-major: one chunk instead of two)
+                        int          cA[4] = {0, 0, 0, 0}, cB[NSUB][4], nl[NSUB];
                         TfChunks     qA{}, qB[NSUB];
+                        uint32_t     txBytes = 2 * KSUB * 16384; // both CTAs' A rows
                         if constexpr(LAYOUT & 1)
                             qA = tfChunksOf(a.gm, tfTileOf(a.gm, tm));
                         else
@@ -727,20 +775,24 @@ namespace htb
 #pragma unroll
                         for(int h = 0; h < NSUB; h++)
                         {
-                            const int tn = isHalf ? 2 * pn + w.half : min(2 * NSUB * pn + 2 * h + int(pairRank), a.tilesN - 1);
+                            nl[h]        = subLoaded(pa, w, h);
+                            const int tn = nl[h] == 1 ? w.s0 + 2 * h : min(w.s0 + 2 * h + int(pairRank), a.tilesN - 1);
+                            txBytes += uint32_t(nl[h]) * KSUB * 16384;
                             cB[h][0] = cB[h][1] = cB[h][2] = cB[h][3] = 0;
                             qB[h] = TfChunks{};
+                            if(nl[h] == 0)
+                                continue;
                             if constexpr(LAYOUT & 2)
                                 qB[h] = tfChunksOf(a.gn, tfTileOf(a.gn, tn));
                             else
                                 tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB[h]);
-                        }
-                        if(isHalf)
-                        {
-                            cB[0][0] += int(pairRank) * 64;
-                            qB[0].c0[0] = qB[0].c0[pairRank];
-                            qB[0].i1[0] = qB[0].i1[pairRank];
-                            qB[0].i2[0] = qB[0].i2[pairRank];
+                            if(nl[h] == 1)
+                            {
+                                cB[h][0] += int(pairRank) * 64;
+                                qB[h].c0[0] = qB[h].c0[pairRank];
+                                qB[h].i1[0] = qB[h].i1[pairRank];
+                                qB[h].i2[0] = qB[h].i2[pairRank];
+                            }
                         }
                         const int a1 = cA[0], a2 = cA[1], a3 = cA[2], a4 = cA[3];
                         HTB_STAMP(0, unitNo, 0);
@@ -779,15 +831,18 @@ namespace htb
 #pragma unroll
                                     for(int h = 0; h < NSUB; h++)
                                     {
+                                        if(nl[h] == 0)
+                                            continue;
                                         const uint32_t db = dst + (KSUB * (1 + h) + q) * kHalfBytes;
                                         if constexpr(LAYOUT & 2)
                                         {
                                             tmaLoadPair5(db, &mapB, bar, qB[h].c0[0], k0, qB[h].i1[0], qB[h].i2[0], 0);
-                                            if(!isHalf)
+                                            if(nl[h] == 2)
                                                 tmaLoadPair5(db + 8192, &mapB, bar, qB[h].c0[1], k0, qB[h].i1[1], qB[h].i2[1], 0);
                                         }
                                         else
-                                            tmaLoadPair5(db, mb, bar, k0, cB[h][0], cB[h][1], cB[h][2], cB[h][3]);
+                                            tmaLoadPair5(db, nl[h] == 2 ? &mapB : &mapB64, bar, k0, cB[h][0], cB[h][1], cB[h][2],
+                                                         cB[h][3]);
                                     }
                                 }
                             }
@@ -821,11 +876,16 @@ namespace htb
                     uint32_t       stage = 0, phase = 0;
                     int            local = 0;
                     bool           ok    = true;
-                    for(int u = clusterId; u < pa.numUnits && ok; u += numClusters, local++)
+                    TcSched        sched = schedInit(pa, clusterId, numClusters);
+                    TcUnit         w;
+                    for(; ok && schedNext<NSUB>(pa, numClusters, kpart, sched, w); local++)
                     {
-                        const TcUnit   w        = unitOf(pa, u, kpart);
                         const int      acc      = local % NACC;
                         const uint32_t accPhase = (local / NACC) & 1;
+                        int            nl[NSUB];
+#pragma unroll
+                        for(int h = 0; h < NSUB; h++)
+                            nl[h] = subLoaded(pa, w, h);
                         HTB_STAMP(1, local, 0);
                         ok = mbarWaitTight(smemAddr(&tmemEmptyBar[acc]), accPhase ^ 1, abortP);
                         if(!ok)
@@ -833,7 +893,6 @@ namespace htb
                         HTB_STAMP(1, local, 1);
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint32_t dTmem = tmem + uint32_t(acc * 256);
-                        const uint32_t idescU = (w.half >= 0) ? pa.idescHalf : idesc; // N = 128 for a half tile
                         for(int it = w.kbBegin; it < w.kbEnd; it++)
                         {
                             ok = mbarWaitTight(fullAddr + 8 * stage, phase, abortP);
@@ -862,12 +921,17 @@ namespace htb
                                     const uint32_t accumulate = (it != w.kbBegin || k != 0) ? 1u : 0u;
 #pragma unroll
                                     for(int h = 0; h < NSUB; h++)
+                                    {
+                                        if(nl[h] == 0)
+                                            continue;
+                                        // N = 256 for two sub-tiles, 128 for a single one
                                         asm volatile("{\n\t.reg .pred p;\n\t"
                                                      "setp.ne.b32 p, %4, 0;\n\t"
                                                      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(dTmem + uint32_t(h * 256)),
                                                      "l"(descA + offA), "l"(descB + offB + uint64_t(h * KSUB * (kHalfBytes >> 4))),
-                                                     "r"(idescU), "r"(accumulate)
+                                                     "r"(nl[h] == 2 ? idesc : pa.idescHalf), "r"(accumulate)
                                                      : "memory");
+                                    }
                                 }
                             }
                             // frees the stage in both CTAs of the pair once these MMAs have read it
@@ -919,25 +983,28 @@ namespace htb
                         : "r"(addr));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 };
-                for(int u = clusterId; u < pa.numUnits; u += numClusters, local++)
+                TcSched sched = schedInit(pa, clusterId, numClusters);
+                TcUnit  w;
+                for(; schedNext<NSUB>(pa, numClusters, kpart, sched, w); local++)
                 {
-                    const TcUnit   w        = unitOf(pa, u, kpart);
                     const int      acc      = local % NACC;
                     const uint32_t accPhase = (local / NACC) & 1;
-                    const int      pm = w.tile % pa.pairsM, pn = w.tile / pa.pairsM;
-                    const int      tmRaw = 2 * pm + int(pairRank);
+                    const int      tmRaw = 2 * w.pm + int(pairRank);
+                    // accumulator column c belongs to sub-tile s0 + 2 (c / 256) + (c % 256) / 128 when that one is part
+                    // of the unit
+                    auto subOf = [&](int c) { return w.s0 + 2 * (c >> 8) + ((c & 255) >> 7); };
+                    auto inUnit = [&](int c) { return ((c & 255) >> 7) < subValid(w, c >> 8); };
                     const bool     dupM  = tmRaw >= a.tilesM; // this CTA repeats its peer's rows: no stores
                     const int      tm    = min(tmRaw, a.tilesM - 1);
                     int            cM[4];
                     tileCoords(tm, a.tilesPerDimM, a.boxM, a.nm, cM);
                     // the table of column offsets, filled by all epilogue threads once nobody reads the previous one
                     epiBarrierAny<EPI>(false);
-                    const int ncols = (w.half >= 0) ? 128 : W; // a half tile: the 128 columns of sub-tile `half`
-                    for(int c = et; c < ncols && !pa.tmaStore; c += EPI)
+                    for(int c = et; c < W && !pa.tmaStore; c += EPI)
                     {
-                        const int tnRaw = (w.half >= 0) ? 2 * pn + w.half : 2 * NSUB * pn + (c >> 7);
+                        const int tnRaw = subOf(c);
                         int64_t   off   = -1;
-                        if(tnRaw < a.tilesN)
+                        if(inUnit(c) && tnRaw < a.tilesN)
                         {
                             if constexpr(LAYOUT & 2)
                                 off = tfRowOffset(a.gn, tfTileOf(a.gn, tnRaw), c & 127);
@@ -983,8 +1050,8 @@ namespace htb
                         {
                             // the chunk's sub-tile; sub-tiles beyond the tensor and the rows of a CTA that repeats its
                             // peer's rows are dropped, ragged edges are clipped by the bulk store itself
-                            const int tnRaw = (w.half >= 0) ? 2 * pn + w.half : 2 * NSUB * pn + (c0 >> 7);
-                            if(dupM || tnRaw >= a.tilesN)
+                            const int tnRaw = subOf(c0);
+                            if(dupM || !inUnit(c0) || tnRaw >= a.tilesN)
                                 return;
                             const uint32_t slot = tilesAddr + pa.storeOffset
                                                   + uint32_t(((warp - 2) * pa.storeBufs + storeSeq % pa.storeBufs) * 4096);
@@ -1205,10 +1272,12 @@ namespace htb
                     {
                         // whole tile: the two warps of a lane quadrant (NSUB = 2) take 256 columns each
                         const int cBegin = (NSUB == 2) ? colGroup * 256 : 0;
-                        const int cEnd   = (NSUB == 2) ? cBegin + 256 : ncols;
+                        const int cEnd   = cBegin + 256;
 #pragma unroll 1
                         for(int c0 = cBegin; c0 < cEnd; c0 += 32)
                         {
+                            if(!inUnit(c0))
+                                continue;
                             uint32_t v[32];
                             loadChunk(taddr + uint32_t(c0), v);
                             if(et == 0 && c0 == cBegin)
@@ -1454,35 +1523,47 @@ namespace htb
                 // K range at least eight stages long
                 if((p.ksplit == 2 || sw.tcKsplit) && !sw.tcNoSplit && pa.iters >= (sw.tcKsplit ? 2 : 16) && tiles <= resident(4))
                     pa.ksplit = 2;
-                // Half tiles (256 x 256 tiles only): several waves, the last at most half full. K-major B needs its
-                // 128-row sub-tile to be one box along the first N mode, so that rows 64.. are a coordinate offset; the
-                // N tiles must pair up evenly.
-                CUtensorMap mapB64 = mapB; // stays a copy of B's map (unused by the kernel) unless half tiles run
-                if(nsub == 1 && pa.ksplit == 1 && tiles > maxClusters && !sw.tcNoHalf && a.tilesN % 2 == 0)
+                // A 128-column sub-tile on its own (64 rows of B per CTA, MMAs with N = 128). K-major B needs its 128-row
+                // sub-tile to be one box along the first N mode, so that rows 64.. are a coordinate offset, and a second
+                // tensor map with 64-row boxes; an MN-major B loads one 64-row chunk instead of two.
+                CUtensorMap mapB64 = mapB; // stays a copy of B's map (unused by the kernel) when single sub-tiles cannot run
+                pa.singleOk        = p.bMajor ? 1 : 0;
+                if(!p.bMajor)
                 {
-                    const int64_t tail   = tiles % maxClusters;
-                    bool          halfOk = tail > 0 && 2 * tail <= maxClusters;
-                    if(halfOk && !p.bMajor)
+                    if(maps->half == 0)
                     {
-                        if(maps->half == 0)
-                        {
-                            const int box64[4] = {64, 1, 1, 1};
-                            maps->half = (p.boxN128[0] == 128 && encodeOperand(encode, &maps->mapB64, B, bf16, p.K, p.n, p.nn, box64))
-                                             ? 1
-                                             : 2;
-                        }
-                        halfOk = maps->half == 1;
-                        if(halfOk)
-                            mapB64 = maps->mapB64;
+                        const int box64[4] = {64, 1, 1, 1};
+                        maps->half = (p.boxN128[0] == 128 && encodeOperand(encode, &maps->mapB64, B, bf16, p.K, p.n, p.nn, box64))
+                                         ? 1
+                                         : 2;
                     }
-                    if(halfOk)
+                    if(maps->half == 1)
+                    {
+                        mapB64      = maps->mapB64;
+                        pa.singleOk = 1;
+                    }
+                }
+                pa.idescHalf = (1u << 4) | (fmt << 7) | (fmt << 10) | majors | (uint32_t(128 >> 3) << 17)
+                               | (uint32_t(256 >> 4) << 24);
+                // Half tiles (256 x 256 tiles): several waves, the last at most half full: its tiles run as two units of
+                // one sub-tile each. The N sub-tiles must pair up evenly.
+                if(nsub == 1 && pa.ksplit == 1 && tiles > maxClusters && !sw.tcNoHalf && a.tilesN % 2 == 0 && pa.singleOk)
+                {
+                    const int64_t tail = tiles % maxClusters;
+                    if(tail > 0 && 2 * tail <= maxClusters)
                     {
                         pa.halves    = 1;
                         pa.fullUnits = int(tiles - tail);
                         pa.numUnits  = int(tiles + tail);
-                        pa.idescHalf = (1u << 4) | (fmt << 7) | (fmt << 10) | majors | (uint32_t(128 >> 3) << 17)
-                                       | (uint32_t(256 >> 4) << 24);
                     }
+                }
+                // Streamed tiles (256 x 512 tiles, whole K): the sub-tiles of all row blocks dealt to the pairs in equal shares
+                int64_t clustersUsed = pa.ksplit > 1 ? int64_t(pa.numUnits) : std::min<int64_t>(pa.numUnits, maxClusters);
+                pa.subTotal          = int(int64_t(pa.pairsM) * a.tilesN);
+                if(nsub == 2 && pa.ksplit == 1 && pa.singleOk && !sw.tcNoStream && int64_t(pa.pairsM) * a.tilesN < (int64_t(1) << 30))
+                {
+                    pa.stream    = 1;
+                    clustersUsed = std::min<int64_t>(pa.subTotal, maxClusters);
                 }
                 // Output by bulk tensor stores: fp32 D with one folded row mode and one contiguous column mode, no C
                 // (a tensor map needs 16-byte aligned base and row stride)
@@ -1521,11 +1602,11 @@ namespace htb
                 }
                 HTB_LOG_HEUR("hiptensorContraction",
                              "pair kernel: %lld tiles of 256 x %d on %d CTA pairs, K split %d, %s, %d work units",
-                             (long long)tiles, 256 * nsub, maxClusters, pa.ksplit, pa.halves ? "last wave in half tiles" : "whole tiles",
+                             (long long)tiles, 256 * nsub, maxClusters, pa.ksplit, pa.stream ? "sub-tiles streamed over the pairs" : (pa.halves ? "last wave in half tiles" : "whole tiles"),
                              pa.numUnits);
                 // one cluster per work unit, as many as can be resident
                 attr[0].val.clusterDim.x = unsigned(2 * pa.ksplit);
-                cfg.gridDim = dim3(unsigned(2 * pa.ksplit * (pa.ksplit > 1 ? int64_t(pa.numUnits) : std::min<int64_t>(pa.numUnits, maxClusters))));
+                cfg.gridDim = dim3(unsigned(2 * pa.ksplit * clustersUsed));
                 e           = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, mapB64, mapD, (const TD*)C, (TD*)D, pa, idesc);
                 if(e == cudaSuccess)
                     noteLaunch(nsub == 2 ? "contraction_tcgen05_pair_wide" : "contraction_tcgen05_pair");
