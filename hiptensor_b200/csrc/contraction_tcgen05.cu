@@ -571,12 +571,6 @@ namespace htb
             // A 128-column sub-tile can run alone: 64 rows of B per CTA (K-major B: second tensor map with 64-row boxes),
             // MMAs with N = 128. Without it an odd sub-tile at the edge is paired with a repeat of itself.
             int      singleOk;
-            // Streamed tiles (NSUB = 2, whole K). The N sub-tiles of all row blocks form one sequence of subTotal
-            // entries that is dealt to the CTA pairs in equal contiguous shares; a pair cuts its share into tiles of up
-            // to four sub-tiles of one row block (256 x 512, 384, 256 or 128). Every pair gets the same work (128 tiles of
-            // 256 x 512 on 74 pairs would take two full rounds for 1.73 rounds of work), and the pairs reach their tile
-            // ends, where the stores burst, at different times.
-            int      stream, subTotal;
             // Output by TMA (fp32 D whose rows and columns are one folded mode each, columns contiguous, no C): the
             // epilogue warps write their 32 x 32 blocks into 128-byte-swizzled shared memory and one lane per warp
             // issues a bulk tensor store, which leaves the SM asynchronously (plain st.global of a 128 x 256 block
@@ -592,14 +586,12 @@ namespace htb
         };
         struct TcSched
         {
-            int u, g, gEnd;
+            int u;
         };
-        __device__ __forceinline__ TcSched schedInit(const TcPairArgs& pa, int clusterId, int numClusters)
+        __device__ __forceinline__ TcSched schedInit(const TcPairArgs&, int clusterId, int)
         {
             TcSched sc;
-            sc.u    = clusterId;
-            sc.g    = int((long long)pa.subTotal * clusterId / numClusters);
-            sc.gEnd = int((long long)pa.subTotal * (clusterId + 1) / numClusters);
+            sc.u = clusterId;
             return sc;
         }
         // the next work unit of this cluster; false when there is none
@@ -609,16 +601,6 @@ namespace htb
             const int S = pa.base.tilesN;
             w.kbBegin   = 0;
             w.kbEnd     = pa.iters;
-            if(NSUB == 2 && pa.stream)
-            {
-                if(sc.g >= sc.gEnd)
-                    return false;
-                w.pm  = sc.g / S;
-                w.s0  = sc.g - w.pm * S;
-                w.cnt = min(min(4, S - w.s0), sc.gEnd - sc.g);
-                sc.g += w.cnt;
-                return true;
-            }
             if(sc.u >= pa.numUnits)
                 return false;
             const int u = sc.u;
@@ -1557,14 +1539,7 @@ namespace htb
                         pa.numUnits  = int(tiles + tail);
                     }
                 }
-                // Streamed tiles (256 x 512 tiles, whole K): the sub-tiles of all row blocks dealt to the pairs in equal shares
-                int64_t clustersUsed = pa.ksplit > 1 ? int64_t(pa.numUnits) : std::min<int64_t>(pa.numUnits, maxClusters);
-                pa.subTotal          = int(int64_t(pa.pairsM) * a.tilesN);
-                if(nsub == 2 && pa.ksplit == 1 && pa.singleOk && !sw.tcNoStream && int64_t(pa.pairsM) * a.tilesN < (int64_t(1) << 30))
-                {
-                    pa.stream    = 1;
-                    clustersUsed = std::min<int64_t>(pa.subTotal, maxClusters);
-                }
+                const int64_t clustersUsed = pa.ksplit > 1 ? int64_t(pa.numUnits) : std::min<int64_t>(pa.numUnits, maxClusters);
                 // Output by bulk tensor stores: fp32 D with one folded row mode and one contiguous column mode, no C
                 // (a tensor map needs 16-byte aligned base and row stride)
                 pa.storeOffset = uint32_t(192 * 1024);
@@ -1602,7 +1577,7 @@ namespace htb
                 }
                 HTB_LOG_HEUR("hiptensorContraction",
                              "pair kernel: %lld tiles of 256 x %d on %d CTA pairs, K split %d, %s, %d work units",
-                             (long long)tiles, 256 * nsub, maxClusters, pa.ksplit, pa.stream ? "sub-tiles streamed over the pairs" : (pa.halves ? "last wave in half tiles" : "whole tiles"),
+                             (long long)tiles, 256 * nsub, maxClusters, pa.ksplit, pa.halves ? "last wave in half tiles" : "whole tiles",
                              pa.numUnits);
                 // one cluster per work unit, as many as can be resident
                 attr[0].val.clusterDim.x = unsigned(2 * pa.ksplit);

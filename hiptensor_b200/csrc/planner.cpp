@@ -113,28 +113,32 @@ namespace htb
         return w;
     }
 
-    // Cost model of the CTA-pair tensor-core kernel (microseconds), calibrated on B200 with K = 4096 and
-    // N = 4096 (M = 512 ... 4096, kernels back to back): the kernel is bound by the operand bytes that enter the
-    // SMs from L2, M N K 2 (1 / tile rows + 1 / tile columns) at about 9 TB/s for the whole chip, or by the
-    // tensor cores when few tiles are resident, plus a fixed part (prologue, last epilogue; the accumulator of a
-    // 256 x 512 tile fills tensor memory, so its epilogue is not overlapped; a K split adds the exchange).
-    double pairKernelCost(int64_t M, int64_t N, int64_t K, int nsub, int ksplit, int sms)
+    // Form of the CTA-pair tensor-core kernel for an M x N x K problem, from measurements on B200 (f16, N = K =
+    // 4096, kernels back to back, microseconds; "tiles" counts 256 x 256 tiles, 74 CTA pairs fit the chip):
+    //   tiles  M     single CTAs  256x256  256x256 K/2  256x512  256x512 K/2
+    //    32    512      30.4        30.5      23.7         -          -
+    //    64   1024       -          33-35      -          49.6      36-39
+    //   128   2048       -          65.5       -          61-64       -
+    //   256   4096       -         107-123     -         115-123      -
+    // The main loops run at the same rate per flop (a pipeline stage turns around in 2.3 - 2.7 us whatever it holds),
+    // so the wider tile only pays where it saves rounds or operand traffic, and a K split only where the tiles fill
+    // at most half of the pairs (each part must still be 16 stages long to pay for the exchange).
+    void pairKernelForm(int64_t M, int64_t N, int64_t K, int sms, int* pair, int* wide, int* ksplit)
     {
-        const double bytesPerUs = 9.0e6, cyclesPerUs = 1500.0;
-        const int64_t pm = (M + 255) / 256, pn = (N + 256 * nsub - 1) / (256 * nsub), tiles = pm * pn;
-        const int64_t pairs = sms / 2, quads = sms / 4 - 1;
-        const int64_t kSteps = (K + 15) / 16, stages = (K + 127) / 128;
-        if(ksplit == 2 && (tiles > quads || stages < 16))
-            return 1e30;
-        const double waves  = double((tiles * ksplit + pairs - 1) / pairs);
-        const double tUnit  = double(kSteps) * 128.0 * nsub / cyclesPerUs / ksplit;
-        const double tBytes = double(pm * 256) * double(pn * 256 * nsub) * double(K) * 2.0 * (1.0 / 256.0 + 1.0 / (256.0 * nsub))
-                              / bytesPerUs;
-        double tail = 0.0;
-        if(nsub == 1 && ksplit == 1 && tiles > pairs && tiles % pairs != 0 && 2 * (tiles % pairs) <= pairs)
-            tail = -0.5 * tUnit; // the last wave runs as half tiles
-        const double fixed = (nsub == 2 ? 4.0 + 3.0 * waves : 6.0) + (ksplit == 2 ? 1.0 : 0.0);
-        return std::max(tBytes, waves * tUnit + tail) + fixed;
+        const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256), pairs = sms / 2, quads = sms / 4 - 1;
+        *pair   = 0;
+        *wide   = 0;
+        *ksplit = 1;
+        if(tiles >= sms / 8 && tiles <= quads && K >= 4096)
+        {
+            *pair   = 1;
+            *ksplit = 2;
+        }
+        else if(tiles >= (int64_t(sms) * 7) / 16)
+        {
+            *pair = 1;
+            *wide = tiles > (3 * pairs) / 2 ? 1 : 0;
+        }
     }
 
     int boxDecompose(const ModeDim* dims, int n, int tile, int* box)
@@ -593,34 +597,7 @@ namespace htb
                 out->wide   = 0;
                 out->ksplit = 1;
                 if(out->pairOk)
-                {
-                    // tile width and K split of the pair kernel by the cost model; below a quarter of the CTA pairs'
-                    // worth of 256 x 256 tiles, and between half and 7/8 of them without a K split, single CTAs with
-                    // their smaller tiles fill the machine better
-                    const int64_t tiles256 = ((out->M + 255) / 256) * ((out->N + 255) / 256);
-                    double        best     = 1e30;
-                    for(int nsub = 1; nsub <= 2; nsub++)
-                        for(int ks = 1; ks <= 2; ks++)
-                        {
-                            if(ks == 1 && tiles256 < (smsH * 7) / 16)
-                                continue;
-                            const double c = pairKernelCost(out->M, out->N, out->K, nsub, ks, int(smsH));
-                            if(c < best)
-                            {
-                                best        = c;
-                                out->pair   = 1;
-                                out->wide   = nsub == 2 ? 1 : 0;
-                                out->ksplit = ks;
-                            }
-                        }
-                    if(out->pair && tiles256 < smsH / 8)
-                        out->pair = 0;
-                    if(!out->pair)
-                    {
-                        out->wide   = 0;
-                        out->ksplit = 1;
-                    }
-                }
+                    pairKernelForm(out->M, out->N, out->K, int(smsH), &out->pair, &out->wide, &out->ksplit);
             }
             out->kind = tc ? CK_TCGEN05 : CK_TILED_SIMT;
         }

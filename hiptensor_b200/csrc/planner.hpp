@@ -158,10 +158,10 @@ namespace htb
                                int computeType, int smCount, ContractionPlan* out);
     std::string describe(const ContractionPlan& p);
 
-    // Estimated time (microseconds) of the CTA-pair tensor-core kernel on an M x N x K problem with 256 x 256
-    // (nsub = 1) or 256 x 512 (nsub = 2) tiles, whole (ksplit = 1) or with every tile's K range cut over two CTA
-    // pairs of a four-CTA cluster (ksplit = 2); 1e30 where the variant cannot run. The planner takes the minimum.
-    double pairKernelCost(int64_t M, int64_t N, int64_t K, int nsub, int ksplit, int sms);
+    // Whether an M x N x K half-precision problem that the CTA-pair tensor-core kernel can run should run on it
+    // (*pair), with 256 x 512 instead of 256 x 256 tiles (*wide), and with every tile's K range cut over the two CTA
+    // pairs of a four-CTA cluster (*ksplit = 2). Rules from measurements: see planner.cpp.
+    void pairKernelForm(int64_t M, int64_t N, int64_t K, int sms, int* pair, int* wide, int* ksplit);
 
     // Splits `tile` rows over the folded modes of a group, fastest mode first: a mode is taken
     // whole while it is a power of two smaller than what is left, the first mode at least as

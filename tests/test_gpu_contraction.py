@@ -536,29 +536,3 @@ def test_measurement_switches_are_not_in_the_default_build(env):
         del os.environ["HTB_TC_PROBE"], os.environ["HTB_TF32_PROBE"]
         ht.reload_switches()
 
-
-@pytest.mark.parametrize("layout", ["kk", "mn_mn"])
-def test_cta_pair_kernel_streamed_tiles(env, layout):
-    """256 x 512 tiles with the sub-tiles of all row blocks dealt to the CTA pairs in equal shares (tiles of four,
-    three, two and one sub-tile, shares that cross row blocks): sampled outputs against the oracle, and the whole
-    output bit for bit against the same kernel with fixed 256 x 512 tiles (every output is accumulated in the same
-    order either way)."""
-    ht, h = env
-    M, N, K = 2048, 9216 + 128, 136
-    modeA, modeB = HALF_LAYOUTS[layout]
-    smp = np.random.default_rng(13).integers(0, M * N, 8192)
-    set_switch("HTB_TC_WIDE", True)
-    try:
-        got, exp, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F16, typeD=orc.F32,
-                                       alpha=1.5, beta=0.0, with_c=False, fill="normal", sample=smp)
-        assert ht.last_kernel_name() == "contraction_tcgen05_pair_wide"
-        assert not np.isnan(got).any()
-        assert 0 <= rel_error(got, exp, td) < 1e-4
-        set_switch("HTB_TC_NOSTREAM", True)
-        fixed, _, _ = run_contraction(ht, h, {0: M, 1: N, 2: K}, modeA, modeB, [0, 1], typeAB=orc.F16, typeD=orc.F32,
-                                      alpha=1.5, beta=0.0, with_c=False, fill="normal", sample=smp[:1])
-    finally:
-        set_switch("HTB_TC_WIDE", False)
-        set_switch("HTB_TC_NOSTREAM", False)
-    assert np.array_equal(got.view(np.uint32), fixed.view(np.uint32))
-    assert h.device_status() == 0

@@ -103,9 +103,9 @@ def test_config4_slab(env, m0_local):
     got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F16,
                                    typeD=orc.F32, alpha=1.0, beta=0.0, with_c=False, fill="normal", sample=smp,
                                    inputs=inp)
-    # 2048 rows: 256 x 512 tiles; 1024: the same with every tile's K range cut over two CTA pairs; 512: 256 x 256
-    # tiles with the K cut
-    assert ht.last_kernel_name() == ("contraction_tcgen05_pair" if m0_local == 8 else "contraction_tcgen05_pair_wide")
+    # 2048 rows: 256 x 512 tiles; 1024: 256 x 256 tiles; 512: 256 x 256 tiles with every tile's K range cut over two
+    # CTA pairs
+    assert ht.last_kernel_name() == ("contraction_tcgen05_pair_wide" if m0_local == 32 else "contraction_tcgen05_pair")
     assert not np.isnan(got).any()
     assert 0 <= rel_error(got, exp, td) < 1e-3  # two fp32 summation orders of 4096 products
     ref = inp["A"].astype(np.float64).reshape(M, 4096) @ inp["B"].astype(np.float64).reshape(4096, 4096).T

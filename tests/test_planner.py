@@ -141,10 +141,10 @@ def test_contraction_k_split_plans(ht):
 
 
 def test_contraction_pair_kernel_variants(ht):
-    """f16 problems on the CTA-pair kernel: tile width and K split by the planner's cost model. The slabs of an
-    N-way split of a 4096^3 problem (M = 4096 / N): 256 x 512 tiles while the tiles fill the CTA pairs, the
-    same with every tile's K range cut over two pairs when they fill half of them, 256 x 256 tiles with the K
-    cut for the smallest slab; small problems stay on single CTAs."""
+    """f16 problems on the CTA-pair kernel: tile width and K split by measured rules. The slabs of an N-way split
+    of a 4096^3 problem (M = 4096 / N): 256 x 512 tiles from one and a half rounds of 256 x 256 tiles on,
+    256 x 256 tiles for one round, 256 x 256 tiles with every tile's K range cut over two pairs when the tiles fill
+    at most half of the pairs; small problems stay on single CTAs."""
     def plan(M, N, K):
         return ht.describe_contraction_plan([M, K], [K, 1], [0, 2], ht.R_16F, [N, K], [K, 1], [1, 2], ht.R_16F, [M, N],
                                             [N, 1], [0, 1], ht.R_32F, False, ht.COMPUTE_32F)
@@ -154,7 +154,7 @@ def test_contraction_pair_kernel_variants(ht):
     d = plan(2048, 4096, 4096)
     assert "pair 256x512" in d and "ksplit" not in d, d
     d = plan(1024, 4096, 4096)
-    assert "pair 256x512 ksplit=2" in d, d
+    assert "pair 256x256" in d and "ksplit" not in d, d
     d = plan(512, 4096, 4096)
     assert "pair 256x256 ksplit=2" in d, d
     assert "pair" not in plan(512, 512, 4096)  # four tiles: single CTAs with their own cluster K split
