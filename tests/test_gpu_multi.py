@@ -65,12 +65,39 @@ def _worker(rank, world, port, out):
                         ht.COMPUTE_32F)
             dist.all_reduce(D)  # test-side gather of the disjoint slabs
             ok.append(np.allclose(D.cpu().numpy(), ref, rtol=2e-5, atol=2e-5))
+        # ---- contraction sharded along the free mode m0: every rank computes its slab of D from its slab of A (offset
+        # views of the global tensors with the global strides) and the whole of B; no exchange
+        m0, m1, n0, k0 = 0, 1, 2, 3
+        ext = {m0: 6, m1: 64, n0: 192, k0: 136}
+        mA, mB, mD = [m0, m1, k0], [n0, k0], [m0, m1, n0]
+        lA, lB, lD = ([ext[m] for m in ms] for ms in (mA, mB, mD))
+        sA2, sB2, sD2 = (sh.packed_strides(l, False) for l in (lA, lB, lD))
+        A2 = orc.fill_normal(int(np.prod(lA)), orc.F16, 255, 0.5)
+        B2 = orc.fill_normal(int(np.prod(lB)), orc.F16, 256, 0.5)
+        C2 = orc.fill_uniform(int(np.prod(lD)), orc.F32, 257)
+        full = np.zeros_like(C2)
+        orc.contraction(1.5, A2, lA, sA2, mA, orc.F16, B2, lB, sB2, mB, orc.F16, 0.5, C2, full, lD, sD2, mD, orc.F32,
+                        orc.COMPUTE_32F)
+        va, vb, vd = sh.shard_contraction(lA, sA2, mA, lB, sB2, mB, lD, sD2, mD, m0, rank, world)
+        A2_d, B2_d, C2_d = torch.from_numpy(A2).cuda(), torch.from_numpy(B2).cuda(), torch.from_numpy(C2).cuda()
+        D2_d = torch.zeros_like(C2_d)
+        dA2 = h.tensor_descriptor(va.lens, va.strides, ht.R_16F)
+        dB2 = h.tensor_descriptor(vb.lens, vb.strides, ht.R_16F)
+        dD2 = h.tensor_descriptor(vd.lens, vd.strides, ht.R_32F)
+        cd = h.contraction_descriptor(dA2, mA, dB2, mB, dD2, mD, dD2, mD, ht.COMPUTE_32F)
+        find = h.contraction_find()
+        plan = h.contraction_plan(cd, find, 0)
+        h.contraction(plan, 1.5, A2_d[va.offset:], B2_d[vb.offset:], 0.5, C2_d[vd.offset:], D2_d[vd.offset:])
+        ok.append(ht.last_kernel_name().startswith("contraction_tcgen05"))
+        dist.all_reduce(D2_d)  # test-side gather of the disjoint slabs
+        got2 = D2_d.cpu().numpy().astype(np.float64)
+        ok.append(float(np.max(np.abs(got2 - full) / (np.abs(got2) + np.abs(full) + 1.0))) < 1e-4)
         out[rank] = all(ok)
     finally:
         dist.destroy_process_group()
 
 
-def test_two_gpus_sharded_reduction():
+def test_two_gpus_sharded_reduction_and_contraction():
     import torch
     import torch.multiprocessing as mp
 
