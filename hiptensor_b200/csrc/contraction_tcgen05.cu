@@ -52,6 +52,11 @@ namespace htb
             int     tilesPerDimM[4], tilesPerDimN[4];
             int64_t extM[4], extN[4], sDm[4], sDn[4];
             int     tilesM, tilesN;
+            // K group: a 64-wide block runs along the block mode (dimension "K" of the tensor maps), at one index of
+            // each of the other K modes (at most two; extent 1 when absent). Block kb: chunk kb % kfChunks of the block
+            // mode, the rest of kb enumerates the other modes, first one fastest. kPosA / kPosB: coordinate index of
+            // the first other K mode in the operand's tensor map (the second follows).
+            int     kfChunks, kExt1, kExt2, kPosA, kPosB;
             int     kBlocks;
             int     stages;
             int     tileN;
@@ -125,6 +130,31 @@ namespace htb
                 off += g * sD[d];
             }
             return (r == 0) ? off : -1; // rows beyond the boxes' product do not exist
+        }
+
+        // K block kb -> first element along the block mode and indices of the other K modes
+        struct KCoord
+        {
+            int k0, i1, i2;
+        };
+        __device__ __forceinline__ KCoord kCoordOf(const TcArgs& a, int kb)
+        {
+            KCoord c;
+            c.k0 = kb * kTileK;
+            c.i1 = c.i2 = 0;
+            if(a.kExt1 > 1 || a.kExt2 > 1)
+            {
+                const int r = kb / a.kfChunks;
+                c.k0        = (kb - r * a.kfChunks) * kTileK;
+                c.i2        = r / a.kExt1; // beyond the last block: outside the map, the box is zero-filled
+                c.i1        = r - c.i2 * a.kExt1;
+            }
+            return c;
+        }
+        // coordinate j (1 .. 4) of a tensor map: the indices of the other K modes from position kPos on, else `row`
+        __device__ __forceinline__ int kPlace(int j, int kPos, const KCoord& c, int row)
+        {
+            return j == kPos ? c.i1 : (j == kPos + 1 ? c.i2 : row);
         }
 
         // LAYOUT: bit 0 = A is MN-major, bit 1 = B is MN-major (64-row chunks instead of boxes, transposed
@@ -224,31 +254,40 @@ namespace htb
                                 break;
                             const uint32_t bar = smemAddr(&fullBar[stage]);
                             mbarArriveExpectTx(bar, a.stageBytes);
-                            cA[0] = kb * kTileK;
-                            cB[0] = kb * kTileK;
+                            const KCoord   kc   = kCoordOf(a, kb);
                             const uint32_t dstA = smemAddr(tiles + size_t(stage) * stageStride);
                             if constexpr(LAYOUT & 1)
                             {
-                                // MN-major map {mode0, K, mode1, mode2, 1}: one [64 k][64 rows] box per chunk
+                                // MN-major map {mode0, K, mode1, mode2, ..}: one [64 k][64 rows] box per chunk
 #pragma unroll
                                 for(int j = 0; j < kTileM / 64; j++)
                                 {
-                                    const int c[5] = {qA.c0[j], kb * kTileK, qA.i1[j], qA.i2[j], 0};
+                                    const int c[5] = {qA.c0[j], kc.k0, kPlace(2, a.kPosA, kc, qA.i1[j]), kPlace(3, a.kPosA, kc, qA.i2[j]),
+                                                      kPlace(4, a.kPosA, kc, 0)};
                                     tmaLoad<5>(dstA + uint32_t(j) * 8192, &mapA, bar, c);
                                 }
                             }
                             else
-                                tmaLoad<5>(dstA, &mapA, bar, cA);
+                            {
+                                const int c[5] = {kc.k0, kPlace(1, a.kPosA, kc, cA[1]), kPlace(2, a.kPosA, kc, cA[2]),
+                                                  kPlace(3, a.kPosA, kc, cA[3]), kPlace(4, a.kPosA, kc, cA[4])};
+                                tmaLoad<5>(dstA, &mapA, bar, c);
+                            }
                             if constexpr(LAYOUT & 2)
                             {
                                 for(int j = 0; j < (tileN >> 6); j++)
                                 {
-                                    const int c[5] = {qB.c0[j], kb * kTileK, qB.i1[j], qB.i2[j], 0};
+                                    const int c[5] = {qB.c0[j], kc.k0, kPlace(2, a.kPosB, kc, qB.i1[j]), kPlace(3, a.kPosB, kc, qB.i2[j]),
+                                                      kPlace(4, a.kPosB, kc, 0)};
                                     tmaLoad<5>(dstA + aBytes + uint32_t(j) * 8192, &mapB, bar, c);
                                 }
                             }
                             else
-                                tmaLoad<5>(dstA + aBytes, &mapB, bar, cB);
+                            {
+                                const int c[5] = {kc.k0, kPlace(1, a.kPosB, kc, cB[1]), kPlace(2, a.kPosB, kc, cB[2]),
+                                                  kPlace(3, a.kPosB, kc, cB[3]), kPlace(4, a.kPosB, kc, cB[4])};
+                                tmaLoad<5>(dstA + aBytes, &mapB, bar, c);
+                            }
                             if(++stage == a.stages)
                             {
                                 stage = 0;
@@ -801,15 +840,21 @@ namespace htb
 #pragma unroll
                                 for(int q = 0; q < KSUB; q++)
                                 {
-                                    const int k0 = (it * KSUB + q) * kTileK; // beyond K: the box is zero-filled
+                                    // beyond the last K block the coordinates fall outside the map: the box is zero-filled
+                                    const KCoord kc = kCoordOf(a, it * KSUB + q);
+                                    const int    k0 = kc.k0;
                                     if constexpr(LAYOUT & 1)
                                     {
-                                        // MN-major map {mode0, K, mode1, mode2, 1}: two [64 k][64 rows] boxes
-                                        tmaLoadPair5(dst + q * kHalfBytes, &mapA, bar, qA.c0[0], k0, qA.i1[0], qA.i2[0], 0);
-                                        tmaLoadPair5(dst + q * kHalfBytes + 8192, &mapA, bar, qA.c0[1], k0, qA.i1[1], qA.i2[1], 0);
+                                        // MN-major map {mode0, K, mode1, mode2, ..}: two [64 k][64 rows] boxes
+                                        tmaLoadPair5(dst + q * kHalfBytes, &mapA, bar, qA.c0[0], k0, kPlace(2, a.kPosA, kc, qA.i1[0]),
+                                                     kPlace(3, a.kPosA, kc, qA.i2[0]), kPlace(4, a.kPosA, kc, 0));
+                                        tmaLoadPair5(dst + q * kHalfBytes + 8192, &mapA, bar, qA.c0[1], k0,
+                                                     kPlace(2, a.kPosA, kc, qA.i1[1]), kPlace(3, a.kPosA, kc, qA.i2[1]),
+                                                     kPlace(4, a.kPosA, kc, 0));
                                     }
                                     else
-                                        tmaLoadPair5(dst + q * kHalfBytes, &mapA, bar, k0, a1, a2, a3, a4);
+                                        tmaLoadPair5(dst + q * kHalfBytes, &mapA, bar, k0, kPlace(1, a.kPosA, kc, a1),
+                                                     kPlace(2, a.kPosA, kc, a2), kPlace(3, a.kPosA, kc, a3), kPlace(4, a.kPosA, kc, a4));
 #pragma unroll
                                     for(int h = 0; h < NSUB; h++)
                                     {
@@ -818,13 +863,16 @@ namespace htb
                                         const uint32_t db = dst + (KSUB * (1 + h) + q) * kHalfBytes;
                                         if constexpr(LAYOUT & 2)
                                         {
-                                            tmaLoadPair5(db, &mapB, bar, qB[h].c0[0], k0, qB[h].i1[0], qB[h].i2[0], 0);
+                                            tmaLoadPair5(db, &mapB, bar, qB[h].c0[0], k0, kPlace(2, a.kPosB, kc, qB[h].i1[0]),
+                                                         kPlace(3, a.kPosB, kc, qB[h].i2[0]), kPlace(4, a.kPosB, kc, 0));
                                             if(nl[h] == 2)
-                                                tmaLoadPair5(db + 8192, &mapB, bar, qB[h].c0[1], k0, qB[h].i1[1], qB[h].i2[1], 0);
+                                                tmaLoadPair5(db + 8192, &mapB, bar, qB[h].c0[1], k0, kPlace(2, a.kPosB, kc, qB[h].i1[1]),
+                                                             kPlace(3, a.kPosB, kc, qB[h].i2[1]), kPlace(4, a.kPosB, kc, 0));
                                         }
                                         else
-                                            tmaLoadPair5(db, nl[h] == 2 ? &mapB : &mapB64, bar, k0, cB[h][0], cB[h][1], cB[h][2],
-                                                         cB[h][3]);
+                                            tmaLoadPair5(db, nl[h] == 2 ? &mapB : &mapB64, bar, k0, kPlace(1, a.kPosB, kc, cB[h][0]),
+                                                         kPlace(2, a.kPosB, kc, cB[h][1]), kPlace(3, a.kPosB, kc, cB[h][2]),
+                                                         kPlace(4, a.kPosB, kc, cB[h][3]));
                                     }
                                 }
                             }
@@ -1300,23 +1348,28 @@ namespace htb
             }
         }
 
-        // Tensor map of one operand: dimension 0 is K (contiguous), dimensions 1.. are the folded
-        // modes of the row group. The map always has rank 5 (missing dimensions have extent 1) so
-        // that the kernels use one fixed form of the load instruction with register coordinates.
-        bool encodeOperand(PFN_encodeTiled encode, CUtensorMap* map, const void* base, bool bf16, int64_t K,
-                           const ModeDim* dims, int n, const int* box)
+        // Tensor map of a K-major operand: dimension 0 is the block K mode (contiguous), dimensions 1 .. n the folded
+        // modes of the row group, then the other K modes (box 1). The map always has rank 5 (missing dimensions have
+        // extent 1) so that the kernels use one fixed form of the load instruction with register coordinates.
+        // kOther: the K modes after the block mode, `second` selects their stride (s0: operand A, s1: operand B).
+        bool encodeOperand(PFN_encodeTiled encode, CUtensorMap* map, const void* base, bool bf16, const ModeDim* kModes,
+                           int nk, bool second, const ModeDim* dims, int n, const int* box)
         {
             cuuint64_t gdim[5], gstr[4];
             cuuint32_t bx[5], estr[5] = {1, 1, 1, 1, 1};
-            gdim[0] = cuuint64_t(K);
+            gdim[0] = cuuint64_t(kModes[0].ext);
             bx[0]   = kTileK;
+            if(n + nk - 1 > 4)
+                return false;
             for(int d = 0; d < 4; d++)
             {
-                const bool real = d < n && dims[d].ext > 1;
-                gdim[d + 1]     = real ? cuuint64_t(dims[d].ext) : 1;
+                const bool    row  = d < n, kdim = !row && d - n < nk - 1;
+                const int64_t ext  = row ? dims[d].ext : (kdim ? kModes[1 + d - n].ext : 1);
+                const int64_t str  = row ? dims[d].s0 : (kdim ? (second ? kModes[1 + d - n].s1 : kModes[1 + d - n].s0) : 0);
+                gdim[d + 1]        = ext > 1 ? cuuint64_t(ext) : 1;
                 // a degenerate mode may carry stride 0: any 16-byte multiple is legal for extent 1
-                gstr[d]   = real ? cuuint64_t(dims[d].s0) * 2 : cuuint64_t(K) * 2;
-                bx[d + 1] = (d < n) ? cuuint32_t(box[d]) : 1;
+                gstr[d]   = ext > 1 ? cuuint64_t(str) * 2 : 16;
+                bx[d + 1] = row ? cuuint32_t(box[d]) : 1;
                 if(gstr[d] % 16 != 0 || gstr[d] == 0)
                     return false;
             }
@@ -1327,17 +1380,28 @@ namespace htb
                    == CUDA_SUCCESS;
         }
 
-        // Tensor map of an MN-major operand: {mode0 (stride 1), K, mode1, mode2, 1}; one box is [64 k][64 rows]
+        // Tensor map of an MN-major operand: {mode0 (stride 1), block K mode, mode1, mode2 (those the group has), the
+        // other K modes}; one box is [64 k][64 rows]
         bool encodeOperandMn(PFN_encodeTiled encode, CUtensorMap* map, const void* base, bool bf16, const RowGroupView& g,
-                             int64_t K, int64_t sK)
+                             const ModeDim* kModes, int nk, bool second)
         {
-            cuuint64_t gdim[5] = {cuuint64_t(g.ext[0]), cuuint64_t(K), 1, 1, 1}, gstr[4] = {cuuint64_t(sK) * 2, 16, 16, 16};
+            auto kStride = [&](int i) { return second ? kModes[i].s1 : kModes[i].s0; };
+            cuuint64_t gdim[5] = {cuuint64_t(g.ext[0]), cuuint64_t(kModes[0].ext), 1, 1, 1},
+                       gstr[4] = {cuuint64_t(kStride(0)) * 2, 16, 16, 16};
             cuuint32_t bx[5] = {64, kTileK, 1, 1, 1}, estr[5] = {1, 1, 1, 1, 1};
-            for(int d = 1; d < 3; d++)
-                if(d < g.n && g.ext[d] > 1)
+            if(g.n > 3 || (g.n - 1) + (nk - 1) > 3)
+                return false;
+            for(int d = 1; d < g.n; d++)
+                if(g.ext[d] > 1)
                 {
                     gdim[1 + d] = cuuint64_t(g.ext[d]);
                     gstr[d]     = cuuint64_t(g.sOp[d]) * 2;
+                }
+            for(int i = 1; i < nk; i++)
+                if(kModes[i].ext > 1)
+                {
+                    gdim[g.n + i]     = cuuint64_t(kModes[i].ext);
+                    gstr[g.n + i - 1] = cuuint64_t(kStride(i)) * 2;
                 }
             for(int d = 0; d < 4; d++)
                 if(gstr[d] % 16 != 0 || gstr[d] == 0)
@@ -1384,10 +1448,10 @@ namespace htb
             CUtensorMap &  mapA = maps->mapA, &mapB = maps->mapB;
             if(!cached)
             {
-                const bool okA = p.aMajor ? encodeOperandMn(encode, &mapA, A, bf16, vm, p.K, p.k[0].s0)
-                                          : encodeOperand(encode, &mapA, A, bf16, p.K, p.m, p.nm, p.boxM);
-                const bool okB = p.bMajor ? encodeOperandMn(encode, &mapB, B, bf16, vn, p.K, p.k[0].s1)
-                                          : encodeOperand(encode, &mapB, B, bf16, p.K, p.n, p.nn, boxN);
+                const bool okA = p.aMajor ? encodeOperandMn(encode, &mapA, A, bf16, vm, p.k, p.nk, false)
+                                          : encodeOperand(encode, &mapA, A, bf16, p.k, p.nk, false, p.m, p.nm, p.boxM);
+                const bool okB = p.bMajor ? encodeOperandMn(encode, &mapB, B, bf16, vn, p.k, p.nk, true)
+                                          : encodeOperand(encode, &mapB, B, bf16, p.k, p.nk, true, p.n, p.nn, boxN);
                 if(!okA || !okB)
                 {
                     maps->id = 0; // not a usable entry
@@ -1408,7 +1472,15 @@ namespace htb
                 a.tilesM = a.gm.tiles;
             if(p.bMajor)
                 a.tilesN = a.gn.tiles;
-            a.kBlocks    = int((p.K + kTileK - 1) / kTileK);
+            // K blocks: 64-wide chunks of the block mode k[0], times the extents of the other K modes
+            a.kfChunks = int((p.k[0].ext + kTileK - 1) / kTileK);
+            a.kExt1    = p.nk > 1 ? int(p.k[1].ext) : 1;
+            a.kExt2    = p.nk > 2 ? int(p.k[2].ext) : 1;
+            a.kPosA    = p.nk > 1 ? (p.aMajor ? 1 + vm.n : 1 + p.nm) : 8;
+            a.kPosB    = p.nk > 1 ? (p.bMajor ? 1 + vn.n : 1 + p.nn) : 8;
+            if(p.nk > 3 || int64_t(a.kfChunks) * a.kExt1 * a.kExt2 > 0x7fffffffll)
+                return cudaErrorNotSupported;
+            a.kBlocks  = a.kfChunks * a.kExt1 * a.kExt2;
             a.tileN      = pair ? 256 : p.tileN;
             a.stages     = pair ? 6 : p.stages;
             a.stageBytes = uint32_t((p.aMajor ? 128 : p.rowsM) + (p.bMajor ? (pair ? 128 : p.tileN) : (pair ? p.rowsN128 : p.rowsN)))
@@ -1515,7 +1587,7 @@ namespace htb
                     if(maps->half == 0)
                     {
                         const int box64[4] = {64, 1, 1, 1};
-                        maps->half = (p.boxN128[0] == 128 && encodeOperand(encode, &maps->mapB64, B, bf16, p.K, p.n, p.nn, box64))
+                        maps->half = (p.boxN128[0] == 128 && encodeOperand(encode, &maps->mapB64, B, bf16, p.k, p.nk, true, p.n, p.nn, box64))
                                          ? 1
                                          : 2;
                     }

@@ -538,26 +538,60 @@ namespace htb
         }
         else if(half)
         {
-            // tcgen05 path. An operand is taken K-major (one folded stride-1 K mode, rows gathered by a TMA box
-            // over the folded modes of its row group) or MN-major (a stride-1 mode in its row group, rows taken in
-            // 64-element chunks of that mode, K one folded mode). All other strides must be multiples of 16 bytes.
-            out->aMajor = out->aKContig ? 0 : ((nk == 1 && gm[0].s0 == 1 && gm[0].ext > 1) ? 1 : -1);
-            out->bMajor = out->bKContig ? 0 : -1;
-            out->nFast  = 0;
-            for(int i = 0; i < nn && out->bMajor < 0 && nk == 1; i++)
+            // tcgen05 path. The K group may keep several folded modes (the reference's kernels take up to six,
+            // contraction_meta_traits.hpp:41-43): a 64-wide K block runs along ONE of them, the block mode kf, at
+            // one index of each of the others (at most two others fit the five dimensions of a tensor map beside the
+            // row modes). An operand is taken K-major (stride 1 along kf, rows gathered by a TMA box over the folded
+            // modes of its row group) or MN-major (a stride-1 mode in its row group, rows taken in 64-element chunks
+            // of that mode). All other strides must be multiples of 16 bytes. Among the K modes that give both
+            // operands a form, the one with more K-major operands wins, then the longer one.
+            int nFastB = -1;
+            for(int i = 0; i < nn && nFastB < 0; i++)
                 if(gn[i].s0 == 1 && gn[i].ext > 1)
+                    nFastB = i;
+            const bool aMn = gm[0].s0 == 1 && gm[0].ext > 1;
+            int        kf = -1, kfScore = -1;
+            for(int f = 0; f < nk; f++)
+            {
+                const int am = gk[f].s0 == 1 ? 0 : (aMn ? 1 : -1), bm = gk[f].s1 == 1 ? 0 : (nFastB >= 0 ? 1 : -1);
+                if(am < 0 || bm < 0 || (nk > 1 && gk[f].ext < 16))
+                    continue;
+                const int score = (am == 0) + (bm == 0);
+                if(score > kfScore || (score == kfScore && gk[f].ext > gk[kf].ext))
                 {
-                    out->bMajor = 1;
-                    out->nFast  = i;
+                    kf      = f;
+                    kfScore = score;
                 }
-            bool tc = out->aMajor >= 0 && out->bMajor >= 0 && out->K >= 64 && nm <= (out->aMajor == 1 ? 3 : 4)
-                      && nn <= (out->bMajor == 1 ? 3 : 4);
-            if(tc && (out->aMajor == 0 || out->bMajor == 0))
+            }
+            out->aMajor = out->bMajor = -1;
+            out->nFast  = 0;
+            if(kf >= 0)
+            {
+                // the block mode goes first, the others keep their order
+                const ModeDim block = gk[kf];
+                for(int i = kf; i > 0; i--)
+                    gk[i] = gk[i - 1];
+                gk[0] = block;
+                for(int i = 0; i < nk; i++)
+                    out->k[i] = gk[i];
+                out->aMajor = gk[0].s0 == 1 ? 0 : 1;
+                out->bMajor = gk[0].s1 == 1 ? 0 : 1;
+                if(out->bMajor == 1)
+                    out->nFast = nFastB;
+            }
+            out->aKContig = out->aMajor == 0 ? 1 : 0;
+            out->bKContig = out->bMajor == 0 ? 1 : 0;
+            const int kOthers = nk - 1;
+            bool tc = out->aMajor >= 0 && out->bMajor >= 0 && out->K >= 64 && kOthers <= 2 && nm + kOthers <= 4
+                      && nn + kOthers <= 4 && nm <= (out->aMajor == 1 ? 3 : 4) && nn <= (out->bMajor == 1 ? 3 : 4);
+            if(tc && nk == 1 && (out->aMajor == 0 || out->bMajor == 0))
                 tc = out->K % 8 == 0;
             if(tc && out->aMajor == 1)
-                tc = gk[0].s0 % 8 == 0 && gk[0].ext < (int64_t(1) << 31);
+                tc = gk[0].s0 % 8 == 0;
             if(tc && out->bMajor == 1)
-                tc = gk[0].s1 % 8 == 0 && gk[0].ext < (int64_t(1) << 31);
+                tc = gk[0].s1 % 8 == 0;
+            for(int i = 0; i < nk && tc; i++)
+                tc = gk[i].ext < (int64_t(1) << 31) && (i == 0 || (gk[i].s0 % 8 == 0 && gk[i].s1 % 8 == 0));
             for(int i = 0; i < nm && tc; i++)
                 tc = ((gm[i].s0 % 8 == 0 || (out->aMajor == 1 && i == 0)) && gm[i].ext < (int64_t(1) << 31));
             for(int i = 0; i < nn && tc; i++)

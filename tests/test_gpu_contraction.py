@@ -536,3 +536,71 @@ def test_measurement_switches_are_not_in_the_default_build(env):
         del os.environ["HTB_TC_PROBE"], os.environ["HTB_TF32_PROBE"]
         ht.reload_switches()
 
+
+
+# Several K modes that do not fold (the reference's kernels take up to six K modes, contraction_meta_traits.hpp:41-43;
+# its mode tests interleave K with M and N, test/01_contraction/configs/mode_test_params.yaml:15-59). Mode lists are
+# given last-mode-fastest; the K block of the tensor-core kernels runs along one K mode, the others are iterated.
+MULTI_K = {
+    # both operands contiguous along k0; k1 slower
+    "kk_2": ({"m": 256, "n": 192, "k1": 3, "k0": 48}, ["m", "k1", "k0"], ["k1", "n", "k0"], ["m", "n"]),
+    # K modes interleaved with the M modes of A, ragged block mode (136 = 2 x 64 + 8)
+    "kk_interleaved": ({"m0": 8, "m1": 32, "n": 320, "k1": 4, "k0": 136}, ["m0", "k1", "m1", "k0"], ["n", "k1", "k0"],
+                       ["m0", "m1", "n"]),
+    # three K modes in different orders in A and B
+    "kk_3": ({"m": 384, "n": 128, "k2": 2, "k1": 3, "k0": 32}, ["m", "k2", "k1", "k0"], ["n", "k1", "k2", "k0"], ["m", "n"]),
+    # A contiguous along k0, B contiguous along n
+    "k_mn_2": ({"m": 256, "n": 256, "k1": 5, "k0": 64}, ["k1", "m", "k0"], ["k1", "k0", "n"], ["m", "n"]),
+    # both operands contiguous along a row mode, two K modes
+    "mn_mn_2": ({"m": 192, "n": 256, "k1": 3, "k0": 40}, ["k1", "k0", "m"], ["k0", "k1", "n"], ["m", "n"]),
+    # large enough for the CTA-pair kernel
+    "kk_2_pair": ({"m": 1024, "n": 1536, "k1": 6, "k0": 96}, ["m", "k1", "k0"], ["k1", "n", "k0"], ["m", "n"]),
+}
+
+
+@pytest.mark.parametrize("case", sorted(MULTI_K))
+@pytest.mark.parametrize("dt", [orc.F16, orc.BF16])
+def test_tensor_core_path_several_k_modes(env, case, dt):
+    ht, h = env
+    ext_named, mA, mB, mD = MULTI_K[case]
+    names = sorted(ext_named)
+    idx = {nm: i for i, nm in enumerate(names)}
+    ext = {idx[nm]: e for nm, e in ext_named.items()}
+    K = int(np.prod([e for nm, e in ext_named.items() if nm.startswith("k")]))
+    smp = None
+    if case == "kk_2_pair":
+        smp = np.random.default_rng(3).integers(0, 1024 * 1536, 8192)
+    got, exp, td = run_contraction(ht, h, ext, [idx[x] for x in mA], [idx[x] for x in mB], [idx[x] for x in mD],
+                                   typeAB=dt, typeD=orc.F32, alpha=1.5, beta=0.5, fill="normal", sample=smp)
+    assert ht.last_kernel_name().startswith("contraction_tcgen05"), ht.last_kernel_name()
+    if case == "kk_2_pair":
+        assert ht.last_kernel_name() == "contraction_tcgen05_pair"
+    assert not np.isnan(got).any()
+    assert 0 <= rel_error(got, exp, td) < 1e-4, (case, K)
+    assert h.device_status() == 0
+
+
+def test_config5_layout_in_half_precision(env):
+    """The mode layout of configuration 5, D[m0,m1,m2,n0,n1] = A[m0,k0,m1,k1,m2] B[k1,n0,k0,n1], with f16 data: neither
+    operand is contiguous along a K mode and the K group does not fold, so both are taken MN-major with two K modes
+    (A in chunks along m2, B along n1). It must run on the tensor cores, not on the FMA kernel."""
+    ht, h = env
+    m0, m1, m2, n0, n1, k0, k1 = range(7)
+    ext = {m0: 16, m1: 16, m2: 16, n0: 48, n1: 48, k0: 48, k1: 48}
+    smp = np.random.default_rng(5).integers(0, 16 ** 3 * 48 ** 2, 4096)
+    got, exp, td = run_contraction(ht, h, ext, [m0, k0, m1, k1, m2], [k1, n0, k0, n1], [m0, m1, m2, n0, n1],
+                                   typeAB=orc.F16, typeD=orc.F32, alpha=2.0, beta=0.5, fill="normal", sample=smp)
+    assert ht.last_kernel_name().startswith("contraction_tcgen05"), ht.last_kernel_name()
+    assert not np.isnan(got).any()
+    assert 0 <= rel_error(got, exp, td) < 5e-4
+
+
+@pytest.mark.parametrize("case", range(len(MODE_CASES)))
+def test_mode_orders_half_precision(env, case):
+    """The reference's shuffled mode lists with f16 data and fp32 output (whatever kernel the planner picks)."""
+    ht, h = env
+    lens, modes = MODE_CASES[case]
+    ext = ext_of(modes, lens)
+    got, exp, td = run_contraction(ht, h, ext, modes[0], modes[1], modes[2], typeAB=orc.F16, typeD=orc.F32, alpha=1.0,
+                                   beta=2.0, fill="normal")
+    assert 0 <= rel_error(got, exp, td) < 1e-4
