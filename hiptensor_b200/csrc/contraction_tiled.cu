@@ -498,14 +498,32 @@ namespace htb
                     const uint32_t dA = sAaddr + 8u * uint32_t(st * kDmmaATile), dB = sBaddr + 8u * uint32_t(st * kDmmaBTile);
                     if(args.vecA)
                     {
-#pragma unroll 4
-                        for(int idx = first; idx < DM * DK / 2; idx += step)
+                        // step is a multiple of DM / 2 and of DK / 2: a lane keeps its row pair (rows contiguous) or its
+                        // K pair (K contiguous) for the whole stage, so that table entry is read once (the first
+                        // version read both tables for every copy: two shared loads per cp.async, with bank conflicts)
+                        if(!a.aKfast)
                         {
-                            const int r = a.aKfast ? idx / (DK / 2) : 2 * (idx % (DM / 2));
-                            const int k = a.aKfast ? 2 * (idx % (DK / 2)) : idx / (DM / 2);
-                            const int64_t om = offAm[r], ok = offAk[st][k];
-                            const bool    v  = om >= 0 && ok >= 0;
-                            cpAsync16(dA + 8u * uint32_t(r * aRS + k * aKS), v ? A + om + ok : A, v);
+                            const int     r  = 2 * (first % (DM / 2));
+                            const int64_t om = offAm[r];
+#pragma unroll 4
+                            for(int k = first / (DM / 2); k < DK; k += step / (DM / 2))
+                            {
+                                const int64_t ok = offAk[st][k];
+                                const bool    v  = om >= 0 && ok >= 0;
+                                cpAsync16(dA + 8u * uint32_t(r * aRS + k * aKS), v ? A + om + ok : A, v);
+                            }
+                        }
+                        else
+                        {
+                            const int     k  = 2 * (first % (DK / 2));
+                            const int64_t ok = offAk[st][k];
+#pragma unroll 4
+                            for(int r = first / (DK / 2); r < DM; r += step / (DK / 2))
+                            {
+                                const int64_t om = offAm[r];
+                                const bool    v  = om >= 0 && ok >= 0;
+                                cpAsync16(dA + 8u * uint32_t(r * aRS + k * aKS), v ? A + om + ok : A, v);
+                            }
                         }
                     }
                     else
@@ -522,14 +540,29 @@ namespace htb
                     }
                     if(args.vecB)
                     {
-#pragma unroll 4
-                        for(int idx = first; idx < DN * DK / 2; idx += step)
+                        if(!a.bKfast)
                         {
-                            const int r = a.bKfast ? idx / (DK / 2) : 2 * (idx % (DN / 2));
-                            const int k = a.bKfast ? 2 * (idx % (DK / 2)) : idx / (DN / 2);
-                            const int64_t on = offBn[r], ok = offBk[st][k];
-                            const bool    v  = on >= 0 && ok >= 0;
-                            cpAsync16(dB + 8u * uint32_t(r * bRS + k * bKS), v ? B + on + ok : B, v);
+                            const int     r  = 2 * (first % (DN / 2));
+                            const int64_t on = offBn[r];
+#pragma unroll 4
+                            for(int k = first / (DN / 2); k < DK; k += step / (DN / 2))
+                            {
+                                const int64_t ok = offBk[st][k];
+                                const bool    v  = on >= 0 && ok >= 0;
+                                cpAsync16(dB + 8u * uint32_t(r * bRS + k * bKS), v ? B + on + ok : B, v);
+                            }
+                        }
+                        else
+                        {
+                            const int     k  = 2 * (first % (DK / 2));
+                            const int64_t ok = offBk[st][k];
+#pragma unroll 4
+                            for(int r = first / (DK / 2); r < DN; r += step / (DK / 2))
+                            {
+                                const int64_t on = offBn[r];
+                                const bool    v  = on >= 0 && ok >= 0;
+                                cpAsync16(dB + 8u * uint32_t(r * bRS + k * bKS), v ? B + on + ok : B, v);
+                            }
                         }
                     }
                     else
