@@ -860,6 +860,23 @@ def run_gpu(args):
     names = [n for n in ORDER if (not args.only or n in args.only)]
     recs = {}
     ncores = os.cpu_count() or 1
+    if args.slab_of > 1 and world == 1:
+        # one GPU plays rank 0 of an N-way split: device-resident timing of the slab kernels only
+        for name in names:
+            cls = WORKLOADS[name]
+            if not cls.sharded:
+                continue
+            wl = cls(ht, h, 0, args.slab_of)
+            wl.setup()
+            ms, mode, repeats, own, launches, clocks = measure_device(wl, args.steps, args.warmup,
+                                                                      torch.cuda.current_stream(), barrier, 1, dist, local, True)
+            scale = 1e9 if wl.bound == "hbm" else 1e12
+            recs[name] = {"slab_of": args.slab_of, "ms_per_step": round(ms / args.steps, 6),
+                          "value_of_this_gpu": round(wl.units_local() * args.steps / (ms / 1e3) / scale, 2), "unit": wl.unit,
+                          "kernel": ht.last_kernel_name(), "clocks": clocks, "config": cls.config(args.slab_of)}
+            wl.release()
+        print(json.dumps({"slab_of": args.slab_of, "n_gpus": 1, "steps": args.steps, "configs": recs}), flush=True)
+        return
     for name in names:
         cls = WORKLOADS[name]
         rec = run_workload(cls, ht, h, args, rank, world, local, dist, barrier, pk)
@@ -943,6 +960,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--only", default="", help="comma-separated subset of c4,c1,c2,c3,c3max,c5,c3k")
+    ap.add_argument("--slab-of", type=int, default=0,
+                    help="single GPU only: run rank 0's share of an N-way split of the sharded configurations (the "
+                         "kernels and sizes one GPU of N sees), for profiling")
     ap.add_argument("--min-load-ms", type=float, default=MIN_LOAD_MS,
                     help="device time over which the K-step region is repeated (profiling runs pass a small value)")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
