@@ -59,8 +59,8 @@ NCU_TRAFFIC = {
     "c2": (2113114000, "profiles/perm_tma_c2.md"),
     "c3": (2153492640, "profiles/red_row_c3.md"),
     "c3max": (2153492640, "profiles/red_row_c3.md"),
-    "c4": (None, None),
-    "c5": (357141760, "profiles/contraction_dmma_c5.md"),
+    "c4": (128962816, "profiles/contraction_tcgen05_pair_c4.md"),
+    "c5": (398871808, "profiles/contraction_dmma_c5.md"),
 }
 
 
