@@ -141,7 +141,7 @@ namespace htb
     // builds made with -DHTB_MEASURE and are absent from the default build.
     struct Switches
     {
-        bool tcSingle, tcPair, tcNoHalf, tcNoSplit, tcNarrow, tcWide, tcKsplit, tcNoTmaStore; // f16/bf16 tensor-core kernels
+        bool tcSingle, tcPair, tcNoHalf, tcNoSplit, tcNarrow, tcWide, tcKsplit, tcNoTmaStore, tcNoPdl; // f16/bf16 tensor-core kernels
         bool noTf32x3, tf32Pair, tf32NoInplace, tf32NoSplit; // fp32 tensor-core kernel
         bool dmmaNoVec, dmmaNoSplit, dmmaNoTma; // FP64 tensor-pipe kernel
         int  tcProbe, tf32Probe; // HTB_MEASURE builds only, else 0

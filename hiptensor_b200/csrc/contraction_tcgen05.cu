@@ -728,6 +728,11 @@ namespace htb
 
             if(threadIdx.x == 0)
                 HTB_STAMP(3, 0, 0);
+            // Programmatic dependent launch: the next kernel of the stream (when it was launched with that attribute)
+            // may bring its CTAs up as soon as every CTA of this grid is here, so that its barrier set-up, tensor-memory
+            // allocation and cluster meeting overlap this grid's tail; it reads or writes global memory only after
+            // its own griddepcontrol.wait below, i.e. once this grid is complete.
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             if(threadIdx.x == 32)
             {
                 prefetchTensorMap(&mapA);
@@ -766,6 +771,8 @@ namespace htb
             volatile int*  abortP = &abortFlag;
             const uint32_t tilesAddr = smemAddr(tiles);
             const uint32_t fullAddr = smemAddr(&fullBar[0]), emptyAddr = smemAddr(&emptyBar[0]);
+            // everything above touched no global memory; from here on the kernel before this one must be complete
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             if(threadIdx.x == 0)
                 HTB_STAMP(3, 0, 1);
 
@@ -1536,16 +1543,19 @@ namespace htb
                 if(e != cudaSuccess)
                     return e;
                 cudaLaunchConfig_t cfg{};
-                cudaLaunchAttribute attr[1];
+                cudaLaunchAttribute attr[2];
                 attr[0].id               = cudaLaunchAttributeClusterDimension;
                 attr[0].val.clusterDim.x = 2;
                 attr[0].val.clusterDim.y = 1;
                 attr[0].val.clusterDim.z = 1;
+                // this kernel may start while the kernel before it in the stream drains (see griddepcontrol in the kernel)
+                attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[1].val.programmaticStreamSerializationAllowed = 1;
                 cfg.blockDim             = dim3(unsigned(64 + 128 * nsub));
                 cfg.dynamicSmemBytes     = smem;
                 cfg.stream               = stream;
                 cfg.attrs                = attr;
-                cfg.numAttrs             = 1;
+                cfg.numAttrs             = sw.tcNoPdl ? 1 : 2;
                 // clusters of two and of four CTAs that can be resident at once (GPCs with an odd SM count lose an SM);
                 // per device, the same for every instantiation: one CTA per SM
                 static std::atomic<int> clustersOf[kMaxDevices][2];

@@ -139,6 +139,7 @@ namespace htb
             s.tcWide        = envSet("HTB_TC_WIDE");
             s.tcKsplit      = envSet("HTB_TC_KSPLIT");
             s.tcNoTmaStore  = envSet("HTB_TC_NOTMASTORE");
+            s.tcNoPdl       = envSet("HTB_TC_NOPDL");
             s.noTf32x3      = envSet("HTB_NO_TF32X3");
             s.tf32Pair      = envSet("HTB_TF32_PAIR");
             s.tf32NoInplace = envSet("HTB_TF32_NOINPLACE");
