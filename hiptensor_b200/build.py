@@ -67,11 +67,14 @@ def build(force=False, verbose=False):
     if failed:
         raise RuntimeError("nvcc failed")
     if jobs or not os.path.exists(LIB):
-        cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-Xcompiler", "-fPIC"]
+        # link under another name and rename: a reader never sees a half-written library
+        tmp = LIB + ".tmp"
+        cmd = [_nvcc(), "-shared", "-o", tmp] + objs + ["-Xcompiler", "-fPIC"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             sys.stderr.write(p.stdout + p.stderr)
             raise RuntimeError("link failed")
+        os.replace(tmp, LIB)
     return LIB
 
 

@@ -143,7 +143,7 @@ namespace htb
     {
         bool tcSingle, tcPair, tcNoHalf, tcNoSplit, tcNarrow, tcWide, tcKsplit, tcNoTmaStore, tcNoPdl; // f16/bf16 tensor-core kernels
         bool noTf32x3, tf32Pair, tf32NoInplace, tf32NoSplit; // fp32 tensor-core kernel
-        bool dmmaNoVec, dmmaNoSplit, dmmaNoTma; // FP64 tensor-pipe kernel
+        bool dmmaNoVec, dmmaNoSplit, f64Compute32Fma; // FP64 tensor-pipe kernel; f64 data with compute f32 on the FMA kernel
         int  tcProbe, tf32Probe; // HTB_MEASURE builds only, else 0
         int  permTile, permStages, permCtas; // HTB_MEASURE builds only, else 0
     };

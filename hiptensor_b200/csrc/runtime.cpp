@@ -146,7 +146,7 @@ namespace htb
             s.tf32NoSplit   = envSet("HTB_TF32_NOSPLIT");
             s.dmmaNoVec     = envSet("HTB_DMMA_NOVEC");
             s.dmmaNoSplit   = envSet("HTB_DMMA_NOSPLIT");
-            s.dmmaNoTma     = envSet("HTB_DMMA_NOTMA");
+            s.f64Compute32Fma = envSet("HTB_F64_COMPUTE32_FMA");
 #ifdef HTB_MEASURE
             s.tcProbe    = envInt("HTB_TC_PROBE");
             s.tf32Probe  = envInt("HTB_TF32_PROBE");

@@ -604,3 +604,24 @@ def test_mode_orders_half_precision(env, case):
     got, exp, td = run_contraction(ht, h, ext, modes[0], modes[1], modes[2], typeAB=orc.F16, typeD=orc.F32, alpha=1.0,
                                    beta=2.0, fill="normal")
     assert 0 <= rel_error(got, exp, td) < 1e-4
+
+
+def test_f64_data_with_f32_compute_runs_on_the_fp64_tensor_pipe(env):
+    """f64 tensors with compute type f32 (a reference tuple): the FP64 tensor-pipe kernel runs it (more precision than
+    asked for, and faster than rounding to float for the FMA kernel). It must satisfy the reference's criterion
+    against the oracle, whose algorithm accumulates in float, and agree with the FMA kernel to float rounding."""
+    ht, h = env
+    m0, m1, n0, n1, k0, k1 = range(6)
+    ext = {m0: 12, m1: 11, n0: 9, n1: 14, k0: 13, k1: 10}
+    got, exp, td = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F64,
+                                   compute=orc.COMPUTE_32F, alpha=1.1, beta=2.2)
+    assert ht.last_kernel_name() == "contraction_tiled_dmma"
+    assert 0 <= rel_error(got, exp, td) < 1e-5
+    set_switch("HTB_F64_COMPUTE32_FMA", True)
+    try:
+        fma, _, _ = run_contraction(ht, h, ext, [m0, m1, k0, k1], [n0, n1, k0, k1], [m0, m1, n0, n1], typeAB=orc.F64,
+                                    compute=orc.COMPUTE_32F, alpha=1.1, beta=2.2)
+        assert ht.last_kernel_name() == "contraction_tiled_simt"
+    finally:
+        set_switch("HTB_F64_COMPUTE32_FMA", False)
+    assert 0 <= rel_error(got, fma, td) < 1e-5
