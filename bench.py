@@ -57,6 +57,7 @@ MIN_LOAD_MS = 200.0  # the K-step region is repeated until this much device time
 NCU_TRAFFIC = {
     "c1": (4088320, "profiles/contraction_tf32x3_c4f32_c1.md"),
     "c2": (2113114000, "profiles/perm_tma_c2.md"),
+    "c2f16": (1031170304, "profiles/perm_tma_c2f16.md"),
     "c3": (2153492640, "profiles/red_row_c3.md"),
     "c3max": (2153492640, "profiles/red_row_c3.md"),
     "c4": (128962816, "profiles/contraction_tcgen05_pair_c4.md"),
@@ -254,6 +255,67 @@ class PermutationC2(Workload):
         orc.permutation(1.0, orc.F32, state["A"], [e] * 4, [0, 1, 2, 3], orc.F32, state["B"], [3, 2, 1, 0], orc.F32,
                         nthreads=nthreads)
         return 2 * e ** 4 * 4, time.perf_counter() - t0, "oracle permutation of the whole tensor (1 GiB in + 1 GiB out)"
+
+
+class PermutationC2F16(PermutationC2):
+    """Not one of the five configurations: configuration 2 with f16 elements (512 MiB in + 512 MiB out)."""
+    name, dtype, sharded = "c2f16", "f16", False
+
+    def setup(self):
+        import torch
+        ht = self.ht
+        e = self.E
+        self.d_local = e
+        n = e ** 4
+        self.n = n
+        self.A_host = _fill(n, 2, 256).pin_memory()
+        self.descA = self.h.tensor_descriptor([e] * 4, None, ht.R_16F)
+        self.descB = self.descA
+        for _ in range(self.nsets()):
+            self.sets.append(BufferSet(A=self.A_host.cuda(non_blocking=True),
+                                       B=torch.empty(n, dtype=torch.float16, device="cuda"),
+                                       B_host=torch.empty(n, dtype=torch.float16).pin_memory()))
+
+    def step(self, stream, s):
+        b = self.sets[s]
+        self.h.permutation(1.0, b.A, self.descA, [0, 1, 2, 3], b.B, self.descB, [3, 2, 1, 0], self.ht.R_16F, stream)
+
+    def units_local(self):
+        return 2 * self.n * 2
+
+    def units_whole(self):
+        return 2 * self.E ** 4 * 2
+
+    def footprint(self):
+        return 2 * self.E ** 4 * 2
+
+    def h2d(self, b):
+        b.A.copy_(self.A_host, non_blocking=True)
+        return self.n * 2
+
+    def d2h(self, b):
+        b.B_host.copy_(b.B, non_blocking=True)
+        return self.n * 2
+
+    @classmethod
+    def config(cls, world):
+        return {"workload": "c2f16: configuration 2 with f16 elements, B[d,c,b,a]=A[a,b,c,d], extents 128 (512 MiB in + "
+                            "512 MiB out), alpha 1",
+                "cache": "operands exceed L2 (126 MB)",
+                "parallelism": "1 GPU" if world == 1 else "%d replicas" % world}
+
+    @classmethod
+    def cpu_step(cls, nthreads, state):
+        import numpy as np
+        from oracle import binding as orc
+        e = cls.E
+        if "A" not in state:
+            state["A"] = orc.fill_uniform(e ** 4, orc.F16, 256)
+            state["B"] = np.empty(e ** 4, dtype=np.float16)
+        t0 = time.perf_counter()
+        orc.permutation(1.0, orc.F16, state["A"], [e] * 4, [0, 1, 2, 3], orc.F16, state["B"], [3, 2, 1, 0], orc.F16,
+                        nthreads=nthreads)
+        return 2 * e ** 4 * 2, time.perf_counter() - t0, "oracle permutation of the whole tensor (512 MiB in + 512 MiB out)"
 
 
 # ----------------------------------------------------------------------------------------------- c3: reduction
@@ -554,8 +616,8 @@ class ContractionC5F16(ContractionBase):
 
 
 WORKLOADS = {"c1": ContractionC1, "c2": PermutationC2, "c3": ReductionC3, "c3max": ReductionC3Max,
-             "c4": ContractionC4, "c5": ContractionC5, "c5f16": ContractionC5F16}
-ORDER = ["c4", "c1", "c2", "c3", "c3max", "c5", "c5f16"]
+             "c4": ContractionC4, "c5": ContractionC5, "c5f16": ContractionC5F16, "c2f16": PermutationC2F16}
+ORDER = ["c4", "c1", "c2", "c3", "c3max", "c5", "c5f16", "c2f16"]
 
 
 # --------------------------------------------------------------------------------------------- timing
@@ -959,7 +1021,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--only", default="", help="comma-separated subset of c4,c1,c2,c3,c3max,c5,c3k")
+    ap.add_argument("--only", default="", help="comma-separated subset of c4,c1,c2,c3,c3max,c5,c5f16,c2f16,c3k")
     ap.add_argument("--slab-of", type=int, default=0,
                     help="single GPU only: run rank 0's share of an N-way split of the sharded configurations (the "
                          "kernels and sizes one GPU of N sees), for profiling")

@@ -515,7 +515,7 @@ namespace htb
         // Narrow maps: one dimension per folded mode (A's order / ascending stride in B).
         // Wide maps: the contiguous mode of each tensor is split into (32, extent/32), which
         // shifts every other dimension up by one.
-        __device__ __forceinline__ void permTileCoords(const PermTmaArgs& a, uint32_t tile, int NP, int NQ, int* cA,
+        __device__ __forceinline__ void permTileCoords(const PermTmaArgs& a, uint32_t tile, int NP, int NQ, int E, int* cA,
                                                        int* cB)
         {
             const int tp = int(tile % a.tilesP);
@@ -540,27 +540,30 @@ namespace htb
             if(a.wide)
             {
                 cA[1]            = tp * NP; // p: 128-byte group index
-                cA[a.q + 1]      = tq * NQ * 32; // q: rows of the input tile
+                cA[a.q + 1]      = tq * NQ * E; // q: rows of the input tile
                 cB[1]            = tq * NQ; // q: 128-byte group index
-                cB[a.posP_B + 1] = tp * NP * 32; // p: rows of the output tile
+                cB[a.posP_B + 1] = tp * NP * E; // p: rows of the output tile
             }
             else
             {
-                cA[0]        = tp * NP * 32;
-                cA[a.q]      = tq * NQ * 32;
-                cB[a.posQ_B] = tq * NQ * 32;
-                cB[a.posP_B] = tp * NP * 32;
+                cA[0]        = tp * NP * E;
+                cA[a.q]      = tq * NQ * E;
+                cB[a.posQ_B] = tq * NQ * E;
+                cB[a.posP_B] = tp * NP * E;
             }
         }
 
-        template <int NP, int NQ>
+        // ESZ: element size in bytes (4: fp32, 2: f16). A 128-byte row holds E = 128 / ESZ elements, a thread moves
+        // VEC x VEC blocks (VEC = 16 / ESZ elements per 16-byte access), sub-tiles are E x E elements.
+        template <int NP, int NQ, int ESZ>
         __global__ void __launch_bounds__(64 * NP * NQ + 32)
             perm_tma_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                             PermTmaArgs a)
         {
-            constexpr int TP = 32 * NP, TQ = 32 * NQ;
+            constexpr int E = 128 / ESZ, VEC = 16 / ESZ;
+            constexpr int TP = E * NP, TQ = E * NQ;
             constexpr int kConsumers = 64 * NP * NQ;
-            constexpr int kStageFloats = TP * TQ;
+            constexpr int kStageFloats = TP * TQ * ESZ / 4; // stage size in 4-byte words
             extern __shared__ unsigned char smemRaw[];
             float* in   = (float*)((uintptr_t(smemRaw) + 1023) & ~uintptr_t(1023));
             float* outb = in + a.inStages * kStageFloats;
@@ -598,7 +601,7 @@ namespace htb
                     for(uint32_t tile = blockIdx.x; tile < a.numTiles; tile += gridDim.x)
                     {
                         int cA[5], cB[5];
-                        permTileCoords(a, tile, NP, NQ, cA, cB);
+                        permTileCoords(a, tile, NP, NQ, E, cA, cB);
                         if(!mbarWaitBounded(smemAddr(&emptyBar[stage]), phase ^ 1, abortP))
                             break;
                         // the storing thread reads the tile's B coordinates from shared memory
@@ -620,7 +623,7 @@ namespace htb
 #pragma unroll
                             for(int i = 0; i < NP; i++)
                             {
-                                cA[0] = p0 + 32 * i;
+                                cA[0] = p0 + E * i;
                                 tmaLoadN(a.ndim, smemAddr(in + stage * kStageFloats + i * TQ * 32), &mapA, bar, cA);
                             }
                         }
@@ -666,14 +669,14 @@ namespace htb
                 }
                 // row of (sub-tile pi, tile-local q index ql) in the input stage, and of
                 // (sub-tile qj, tile-local p index pl) in the output stage
-                float4               v[4];
+                uint4                v[VEC];
                 const unsigned char* inStage = (const unsigned char*)(in + stage * kStageFloats);
 #pragma unroll
-                for(int i = 0; i < 4; i++)
+                for(int i = 0; i < VEC; i++)
                 {
-                    const int ql = 32 * qj + 4 * g + i;
+                    const int ql = E * qj + VEC * g + i;
                     const int r  = a.wide ? (pi + NP * ql) : (pi * TQ + ql);
-                    v[i]         = *(const float4*)(inStage + r * 128 + ((c ^ (r & 7)) << 4));
+                    v[i]         = *(const uint4*)(inStage + r * 128 + ((c ^ (r & 7)) << 4));
                 }
                 // this warp is done with the input stage
                 __syncwarp();
@@ -681,17 +684,47 @@ namespace htb
                     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(&emptyBar[stage])) : "memory");
 
                 unsigned char* outStage = (unsigned char*)(outb + ostage * kStageFloats);
-#pragma unroll
-                for(int j = 0; j < 4; j++)
+                if constexpr(ESZ == 4)
                 {
-                    float4 w;
-                    w.x = Elem<float>::apply(((const float*)&v[0])[j], a.alpha, a.opA, a.opB);
-                    w.y = Elem<float>::apply(((const float*)&v[1])[j], a.alpha, a.opA, a.opB);
-                    w.z = Elem<float>::apply(((const float*)&v[2])[j], a.alpha, a.opA, a.opB);
-                    w.w = Elem<float>::apply(((const float*)&v[3])[j], a.alpha, a.opA, a.opB);
-                    const int pl = 32 * pi + 4 * c + j;
-                    const int rr = a.wide ? (qj + NQ * pl) : (qj * TP + pl);
-                    *(float4*)(outStage + rr * 128 + ((g ^ (rr & 7)) << 4)) = w;
+#pragma unroll
+                    for(int j = 0; j < 4; j++)
+                    {
+                        float4 w;
+                        w.x = Elem<float>::apply(__uint_as_float(((const uint32_t*)&v[0])[j]), a.alpha, a.opA, a.opB);
+                        w.y = Elem<float>::apply(__uint_as_float(((const uint32_t*)&v[1])[j]), a.alpha, a.opA, a.opB);
+                        w.z = Elem<float>::apply(__uint_as_float(((const uint32_t*)&v[2])[j]), a.alpha, a.opA, a.opB);
+                        w.w = Elem<float>::apply(__uint_as_float(((const uint32_t*)&v[3])[j]), a.alpha, a.opA, a.opB);
+                        const int pl = E * pi + VEC * c + j;
+                        const int rr = a.wide ? (qj + NQ * pl) : (qj * TP + pl);
+                        *(float4*)(outStage + rr * 128 + ((g ^ (rr & 7)) << 4)) = w;
+                    }
+                }
+                else
+                {
+                    // 8 x 8 block of 16-bit elements: output row j takes element j of each of the eight input rows; one
+                    // byte permute builds a word from the same half of the same word of two neighbouring rows
+                    const bool plain = a.alpha == 1.0f && a.opA != 2 && a.opB != 2;
+#pragma unroll
+                    for(int j = 0; j < 8; j++)
+                    {
+                        uint32_t w[4];
+#pragma unroll
+                        for(int x = 0; x < 4; x++)
+                        {
+                            const uint32_t lo = ((const uint32_t*)&v[2 * x])[j >> 1], hi = ((const uint32_t*)&v[2 * x + 1])[j >> 1];
+                            w[x] = __byte_perm(lo, hi, (j & 1) ? 0x7632 : 0x5410);
+                            if(!plain)
+                            {
+                                __half2 hh = *reinterpret_cast<__half2*>(&w[x]);
+                                hh.x       = Elem<__half>::apply(hh.x, a.alpha, a.opA, a.opB);
+                                hh.y       = Elem<__half>::apply(hh.y, a.alpha, a.opA, a.opB);
+                                w[x]       = *reinterpret_cast<uint32_t*>(&hh);
+                            }
+                        }
+                        const int pl = E * pi + VEC * c + j;
+                        const int rr = a.wide ? (qj + NQ * pl) : (qj * TP + pl);
+                        *(uint4*)(outStage + rr * 128 + ((g ^ (rr & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
                 // generic-proxy writes -> async proxy, then one thread stores the tile
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -712,7 +745,7 @@ namespace htb
 #pragma unroll
                         for(int j = 0; j < NQ; j++)
                         {
-                            cB[a.posQ_B] = q0 + 32 * j;
+                            cB[a.posQ_B] = q0 + E * j;
                             tmaStoreN(a.ndim, &mapB, smemAddr(outb + ostage * kStageFloats + j * TP * 32), cB);
                         }
                     }
@@ -746,11 +779,12 @@ namespace htb
             int ctasPerSm = 2;
         };
 
-        template <int NP, int NQ>
+        template <int NP, int NQ, int ESZ>
         cudaError_t launchTma(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB,
                               const PermTune& tune, int smCount, int* status, cudaStream_t stream)
         {
-            constexpr int TP = 32 * NP, TQ = 32 * NQ;
+            constexpr int E = 128 / ESZ, TP = E * NP, TQ = E * NQ;
+            constexpr CUtensorMapDataType kType = ESZ == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
             PFN_encodeTiled encode = tensorMapEncoder();
             if(!encode)
                 return cudaErrorNotSupported;
@@ -761,7 +795,7 @@ namespace htb
             // Wide maps: the contiguous mode is described as (32, extent/32) so that ONE box
             // [32][NP] covers NP consecutive 128-byte pieces of a row; the pieces of one row are
             // then requested back to back and DRAM serves them from one open page.
-            const bool wide = (NP > 1 || NQ > 1) && p.ndim <= 4 && p.ext[0] % 32 == 0 && p.ext[p.q] % 32 == 0;
+            const bool wide = (NP > 1 || NQ > 1) && p.ndim <= 4 && p.ext[0] % E == 0 && p.ext[p.q] % E == 0;
             a.wide          = wide ? 1 : 0;
             const int sh    = wide ? 1 : 0;
             // A: folded modes in A's order
@@ -770,20 +804,20 @@ namespace htb
                 gdim[d + sh] = cuuint64_t(p.ext[d]);
                 box[d + sh]  = 1;
                 if(d > 0)
-                    gstr[d - 1 + sh] = cuuint64_t(p.sA[d]) * 4;
+                    gstr[d - 1 + sh] = cuuint64_t(p.sA[d]) * ESZ;
             }
             if(wide)
             {
-                gdim[0] = 32;
-                gdim[1] = cuuint64_t(p.ext[0] / 32);
+                gdim[0] = E;
+                gdim[1] = cuuint64_t(p.ext[0] / E);
                 gstr[0] = 128;
-                box[0]  = 32;
+                box[0]  = E;
                 box[1]  = NP;
             }
             else
-                box[0] = 32;
+                box[0] = E;
             box[p.q + sh] = TQ;
-            if(encode(&mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.ndim + sh, const_cast<void*>(A), gdim, gstr, box, estr,
+            if(encode(&mapA, kType, p.ndim + sh, const_cast<void*>(A), gdim, gstr, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
                != CUDA_SUCCESS)
@@ -796,22 +830,22 @@ namespace htb
                 box[i + sh]  = 1;
                 a.mapPosB[d] = i;
                 if(i > 0)
-                    gstr[i - 1 + sh] = cuuint64_t(p.sB[d]) * 4;
+                    gstr[i - 1 + sh] = cuuint64_t(p.sB[d]) * ESZ;
             }
             a.posP_B = a.mapPosB[0];
             a.posQ_B = a.mapPosB[p.q];
             if(wide)
             {
-                gdim[0] = 32;
-                gdim[1] = cuuint64_t(p.ext[p.q] / 32);
+                gdim[0] = E;
+                gdim[1] = cuuint64_t(p.ext[p.q] / E);
                 gstr[0] = 128;
-                box[0]  = 32;
+                box[0]  = E;
                 box[1]  = NQ;
             }
             else
-                box[a.posQ_B] = 32;
+                box[a.posQ_B] = E;
             box[a.posP_B + sh] = TP;
-            if(encode(&mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.ndim + sh, B, gdim, gstr, box, estr,
+            if(encode(&mapB, kType, p.ndim + sh, B, gdim, gstr, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
                != CUDA_SUCCESS)
@@ -834,14 +868,14 @@ namespace htb
                 return cudaErrorInvalidConfiguration;
             a.numTiles = uint32_t(tiles);
             a.inStages  = tune.inStages;
-            const int   smem = (a.inStages + kOutStages) * TP * TQ * 4 + 1024;
+            const int   smem = (a.inStages + kOutStages) * TP * TQ * ESZ + 1024;
             // the limit is a property of the function on the current device; the stage count can change between calls
-            if(cudaError_t e = ensureDynamicSmem((const void*)perm_tma_kernel<NP, NQ>, smem); e != cudaSuccess)
+            if(cudaError_t e = ensureDynamicSmem((const void*)perm_tma_kernel<NP, NQ, ESZ>, smem); e != cudaSuccess)
                 return e;
             const int       fit   = std::max(1, (227 * 1024) / (smem + 1024));
             const int       perSm = std::min(fit, tune.ctasPerSm);
             const long long grid  = std::min<long long>(tiles, (long long)(smCount > 0 ? smCount : 148) * perSm);
-            perm_tma_kernel<NP, NQ><<<unsigned(grid), 64 * NP * NQ + 32, smem, stream>>>(mapA, mapB, a);
+            perm_tma_kernel<NP, NQ, ESZ><<<unsigned(grid), 64 * NP * NQ + 32, smem, stream>>>(mapA, mapB, a);
             return cudaGetLastError();
         }
 
@@ -989,13 +1023,27 @@ namespace htb
 #endif
             tune.inStages = std::min(std::max(tune.inStages, 1), kMaxInStages);
             cudaError_t e;
+            if(typeA == CUDA_R_16F)
+            {
+                // 2-byte elements: 128-byte rows hold 64 elements; 128 x 128 tiles by default
+                switch(tune.shape)
+                {
+                case 11: e = launchTma<1, 1, 2>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+                case 12: e = launchTma<1, 2, 2>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+                case 21: e = launchTma<2, 1, 2>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+                default: e = launchTma<2, 2, 2>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+                }
+                if(e == cudaSuccess)
+                    noteLaunch("perm_tma");
+                return e;
+            }
             switch(tune.shape)
             {
-            case 14: e = launchTma<1, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
-            case 41: e = launchTma<4, 1>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
-            case 24: e = launchTma<2, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
-            case 42: e = launchTma<4, 2>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
-            default: e = launchTma<2, 2>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+            case 14: e = launchTma<1, 4, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+            case 41: e = launchTma<4, 1, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+            case 24: e = launchTma<2, 4, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+            case 42: e = launchTma<4, 2, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+            default: e = launchTma<2, 2, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
             }
             if(e == cudaSuccess)
                 noteLaunch("perm_tma");

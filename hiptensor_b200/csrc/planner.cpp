@@ -229,14 +229,17 @@ namespace htb
         }
         else
         {
-            bool tma = (typeA == CUDA_R_32F && typeB == CUDA_R_32F) && pointersAligned16 && n <= 5
-                       && out->ext[0] % 4 == 0 && out->ext[out->q] % 4 == 0 && out->ext[0] >= 16
-                       && out->ext[out->q] >= 16;
+            // TMA path: fp32 -> fp32 and f16 -> f16, every stride a multiple of 16 bytes (extents of the two
+            // contiguous modes multiples of 4 / 8 elements)
+            const int64_t per16 = 16 / std::max(out->elemSize, 1);
+            bool tma = ((typeA == CUDA_R_32F && typeB == CUDA_R_32F) || (typeA == CUDA_R_16F && typeB == CUDA_R_16F))
+                       && pointersAligned16 && n <= 5 && out->ext[0] % per16 == 0 && out->ext[out->q] % per16 == 0
+                       && out->ext[0] >= 4 * per16 && out->ext[out->q] >= 4 * per16;
             for(int i = 0; i < n && tma; i++)
             {
                 // cuTensorMapEncodeTiled limits: extent < 2^32, byte stride < 2^40
-                if(out->ext[i] >= (int64_t(1) << 32) || out->sA[i] * 4 >= (int64_t(1) << 40)
-                   || out->sB[i] * 4 >= (int64_t(1) << 40))
+                if(out->ext[i] >= (int64_t(1) << 32) || out->sA[i] * out->elemSize >= (int64_t(1) << 40)
+                   || out->sB[i] * out->elemSize >= (int64_t(1) << 40))
                     tma = false;
             }
             out->kind = tma ? PERM_TMA : PERM_TILE;

@@ -66,6 +66,46 @@ def test_all_rank4_orders_tma_shapes(env):
     assert "perm_tma" in kernels and "perm_copy" in kernels
 
 
+@pytest.mark.parametrize("lens", [[64, 24, 40, 72], [128, 8, 8, 136]])
+def test_all_rank4_orders_tma_shapes_f16(env, lens):
+    """f16 elements through the TMA kernel (both contiguous extents multiples of 8): every order bit-exact."""
+    ht, h = env
+    modeA = [0, 1, 2, 3]
+    kernels = set()
+    for perm in itertools.permutations(modeA):
+        got, exp = run_permutation(ht, h, lens, modeA, list(perm), typeA=orc.F16, alpha=1.0)
+        kernels.add(ht.last_kernel_name())
+        assert np.array_equal(bits(got), bits(exp)), (perm, ht.last_kernel_name())
+    assert "perm_tma" in kernels
+
+
+@pytest.mark.parametrize("alpha,ops", [(0.5, (orc.OP_IDENTITY, orc.OP_IDENTITY)), (1.0, (orc.OP_SQRT, orc.OP_IDENTITY)),
+                                       (2.0, (orc.OP_IDENTITY, orc.OP_SQRT))])
+def test_tma_f16_alpha_and_unary_ops(env, alpha, ops):
+    ht, h = env
+    A = np.abs(orc.fill_uniform(64 * 32 * 16 * 72, orc.F16, 5))
+    got, exp = run_permutation(ht, h, [64, 32, 16, 72], [0, 1, 2, 3], [3, 1, 2, 0], typeA=orc.F16, alpha=alpha,
+                               opA=ops[0], opB=ops[1], A=A)
+    assert ht.last_kernel_name() == "perm_tma"
+    assert np.array_equal(bits(got), bits(exp))
+
+
+def test_config2_full_size_f16(env):
+    """Configuration 2 with f16 elements (512 MiB in, 512 MiB out): bit-exact against an independent transpose."""
+    import torch
+
+    ht, h = env
+    e = 128
+    n = e ** 4
+    A = torch.from_numpy(orc.fill_uniform(n, orc.F16, 256)).cuda()
+    B = torch.full((n,), float("nan"), dtype=torch.float16, device="cuda")
+    d = h.tensor_descriptor([e] * 4, None, ht.R_16F)
+    h.permutation(1.0, A, d, [0, 1, 2, 3], B, d, [3, 2, 1, 0], ht.R_16F)
+    assert ht.last_kernel_name() == "perm_tma"
+    ref = A.view(e, e, e, e).permute(3, 2, 1, 0).contiguous().view(-1)
+    assert torch.equal(B.view(torch.int16), ref.view(torch.int16))
+
+
 @pytest.mark.parametrize("rank", [2, 3, 5, 6])
 def test_other_ranks(env, rank):
     ht, h = env
