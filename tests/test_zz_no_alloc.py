@@ -108,14 +108,19 @@ def test_a_warm_call_allocates_no_device_memory():
     dD = h.tensor_descriptor([3], None, ht.R_32F)
     call = lambda: h.reduction_no_alloc(2.0, A_d, dA, [0, 1, 2], 0.5, C_d, dD, kept, D_d, dD, kept, ht.OP_ADD,  # noqa: E731
                                         ht.COMPUTE_32F)
+    import gc
+
     call()  # first call on this device: one-time address lookup
+    gc.collect()  # tensors of earlier tests that are still waiting for the collector go now, not between the readings
     torch.cuda.synchronize()
     free0, _ = torch.cuda.mem_get_info()
+    events0 = torch.cuda.memory_stats().get("allocation.all.allocated", 0)
     alloc0, reserved0 = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
     for _ in range(3):
         call()
     torch.cuda.synchronize()
     free1, _ = torch.cuda.mem_get_info()
     assert ht.last_kernel_name() == "red_finalize"
-    assert free1 == free0
-    assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == (alloc0, reserved0)
+    assert free1 >= free0  # nothing taken from the device (cudaMalloc by the library would show here)
+    assert torch.cuda.memory_stats().get("allocation.all.allocated", 0) == events0  # nor from the harness' allocator
+    assert torch.cuda.memory_allocated() <= alloc0 and torch.cuda.memory_reserved() <= reserved0
