@@ -190,6 +190,9 @@ namespace htb
             };
             const uint32_t tmemCols   = (2 * tileN <= 128) ? 128 : (2 * tileN <= 256 ? 256 : 512);
 
+            // programmatic dependent launch, as in the CTA-pair kernel below: the next kernel's set-up may overlap this
+            // grid's tail, and this grid touches global memory only after its griddepcontrol.wait
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             if(threadIdx.x == 32)
             {
                 prefetchTensorMap(&mapA);
@@ -220,6 +223,7 @@ namespace htb
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncthreads();
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             const uint32_t tmem = tmemBase;
             volatile int*  abortP = &abortFlag;
 
@@ -1693,29 +1697,25 @@ namespace htb
                 if(q >= 2)
                     a.parts = int(q);
             }
-            if(a.parts > 1)
-            {
-                cudaLaunchConfig_t  cfg{};
-                cudaLaunchAttribute attr[1];
-                attr[0].id               = cudaLaunchAttributeClusterDimension;
-                attr[0].val.clusterDim.x = unsigned(a.parts);
-                attr[0].val.clusterDim.y = 1;
-                attr[0].val.clusterDim.z = 1;
-                cfg.gridDim              = dim3(unsigned(numTiles * a.parts));
-                cfg.blockDim             = dim3(kThreads);
-                cfg.dynamicSmemBytes     = smem;
-                cfg.stream               = stream;
-                cfg.attrs                = attr;
-                cfg.numAttrs             = 1;
-                e = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, (const TD*)C, (TD*)D, a, idesc);
-                if(e == cudaSuccess)
-                    noteLaunch("contraction_tcgen05");
-                return e;
-            }
-            const int grid = int(std::min<int64_t>(numTiles, sms));
-            kernel<<<grid, kThreads, smem, stream>>>(mapA, mapB, (const TD*)C, (TD*)D, a, idesc);
-            noteLaunch("contraction_tcgen05");
-            return cudaGetLastError();
+            // a cluster per tile when K is split (else clusters of one CTA), programmatic dependent launch
+            cudaLaunchConfig_t  cfg{};
+            cudaLaunchAttribute attr[2];
+            attr[0].id                                         = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x                           = unsigned(a.parts);
+            attr[0].val.clusterDim.y                           = 1;
+            attr[0].val.clusterDim.z                           = 1;
+            attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.gridDim          = dim3(unsigned(a.parts > 1 ? numTiles * a.parts : std::min<int64_t>(numTiles, sms)));
+            cfg.blockDim         = dim3(kThreads);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream           = stream;
+            cfg.attrs            = attr;
+            cfg.numAttrs         = sw.tcNoPdl ? 1 : 2;
+            e                    = cudaLaunchKernelEx(&cfg, kernel, mapA, mapB, (const TD*)C, (TD*)D, a, idesc);
+            if(e == cudaSuccess)
+                noteLaunch("contraction_tcgen05");
+            return e;
         }
     } // namespace
 
