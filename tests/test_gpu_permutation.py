@@ -137,6 +137,18 @@ def test_f16_inputs(env, typeB):
 
 
 @pytest.mark.parametrize("typeA,typeB", [(orc.F16, orc.F16), (orc.F16, orc.F32), (orc.F32, orc.F32)])
+@pytest.mark.parametrize("lens", [[63, 34, 12, 7], [129, 65, 3, 5], [1, 67, 131, 2]])
+def test_generic_tile_kernel_plain_moves(env, typeA, typeB, lens):
+    """alpha = 1 and identity operators on odd extents: the element kernel's path that moves values unchanged
+    (tiles inside the tensor without bounds checks, ragged tiles at the edges)."""
+    ht, h = env
+    for perm in ([3, 2, 1, 0], [1, 0, 2, 3], [2, 3, 0, 1]):
+        got, exp = run_permutation(ht, h, lens, [0, 1, 2, 3], perm, typeA=typeA, typeB=typeB, alpha=1.0,
+                                   type_scalar=typeA)
+        assert np.array_equal(bits(got), bits(exp)), (lens, perm, ht.last_kernel_name())
+
+
+@pytest.mark.parametrize("typeA,typeB", [(orc.F16, orc.F16), (orc.F16, orc.F32), (orc.F32, orc.F32)])
 @pytest.mark.parametrize("lens", [[70, 34, 12, 6], [66, 130, 2, 10], [64, 3, 128, 5], [63, 34, 12, 7]])
 def test_generic_tile_kernel_even_and_odd(env, typeA, typeB, lens):
     """The shared-memory tile kernel moves 2 x 2 blocks when every extent and stride involved is even (edge tiles
