@@ -1337,9 +1337,10 @@ namespace htb
                 }
                 for(; pa.ksplit > 1 && syncs < 2; syncs++)
                     clusterSync(); // a CTA whose wait ran out still meets the others
-                // the bulk stores of this warp have left shared memory and reached global memory
+                // the bulk stores of this warp have read their shared-memory slots (the end of the grid makes their
+                // writes visible, as for any store)
                 if(pa.tmaStore && lane == 0)
-                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             }
 
             // ---------------------------------------------------------------- teardown
