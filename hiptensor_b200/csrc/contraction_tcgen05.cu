@@ -40,7 +40,7 @@ namespace htb
 {
     namespace
     {
-        constexpr int kThreads   = 192;
+        constexpr int kThreads   = 224; // warps: 0 producer of A, 1 MMA issuer, 2-5 epilogue, 6 producer of B
         constexpr int kTileM     = 128;
         constexpr int kTileK     = 64; // 64 half-precision elements = one 128-byte swizzle row
         constexpr int kMaxStages = 8;
@@ -157,6 +157,22 @@ namespace htb
             return j == kPos ? c.i1 : (j == kPos + 1 ? c.i2 : row);
         }
 
+#ifdef HTB_MEASURE
+        // time stamp k of CTA 0 of the single-CTA kernel (measurement builds): trace[k]
+#define HTB_STAMP1(k)                                                             \
+    do                                                                            \
+    {                                                                             \
+        if(a.trace && blockIdx.x == 0)                                            \
+        {                                                                         \
+            unsigned long long t_;                                                \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                \
+            a.trace[k] = t_;                                                      \
+        }                                                                         \
+    } while(0)
+#else
+#define HTB_STAMP1(k)
+#endif
+
         // LAYOUT: bit 0 = A is MN-major, bit 1 = B is MN-major (64-row chunks instead of boxes, transposed
         // shared-memory descriptors); 0 = both K-major.
         template <typename TD, int LAYOUT>
@@ -190,8 +206,12 @@ namespace htb
             };
             const uint32_t tmemCols   = (2 * tileN <= 128) ? 128 : (2 * tileN <= 256 ? 256 : 512);
 
-            // programmatic dependent launch, as in the CTA-pair kernel below: the next kernel's set-up may overlap this
-            // grid's tail, and this grid touches global memory only after its griddepcontrol.wait
+            if(threadIdx.x == 0)
+                HTB_STAMP1(0);
+            // Programmatic dependent launch, as in the CTA-pair kernel below: the next kernel's set-up may overlap this
+            // grid's tail. Every thread that touches global memory runs griddepcontrol.wait right before its first
+            // access (the producer before its first load, the epilogue threads before C and D), so that the tile
+            // arithmetic ahead of it, on a cold instruction cache 1.4 us, also runs while the grid ahead drains.
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             if(threadIdx.x == 32)
             {
@@ -223,18 +243,24 @@ namespace htb
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncthreads();
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if(threadIdx.x == 0)
+                HTB_STAMP1(1);
             const uint32_t tmem = tmemBase;
             volatile int*  abortP = &abortFlag;
 
-            if(warp == 0)
+            if(warp == 0 || warp == 6)
             {
-                // ---------------------------------------------------------------- TMA producer
+                // ---------------------------------------------------------------- TMA producers
+                // Two threads of two warps walk the same stages: one arms the barrier and loads A, the other loads B.
+                // One thread needed 0.27 - 0.35 us per K block for its two load instructions, which bounded small and
+                // mid-size problems (the MMAs of a 128 x 128 x 64 block take 0.07 us). Every stage has loads of both,
+                // so neither thread can fall a ring behind the other.
+                const bool loadsA = (warp == 0);
                 if(lane == 0)
                 {
                     int      stage = 0;
                     uint32_t phase = 0;
-                    bool     ok    = true;
+                    bool     ok    = true, waited = false;
                     for(int u = blockIdx.x; u < numUnits && ok; u += gridDim.x)
                     {
                         const int t  = u / parts;
@@ -253,14 +279,25 @@ namespace htb
                             tileCoords(tn, a.tilesPerDimN, a.boxN, a.nn, cB + 1);
                         for(int kb = kb0; kb < kb1; kb++)
                         {
-                            ok = mbarWait(smemAddr(&emptyBar[stage]), phase ^ 1, abortP);
+                            ok = mbarWaitTight(smemAddr(&emptyBar[stage]), phase ^ 1, abortP);
                             if(!ok)
                                 break;
                             const uint32_t bar = smemAddr(&fullBar[stage]);
-                            mbarArriveExpectTx(bar, a.stageBytes);
+                            if(loadsA)
+                                mbarArriveExpectTx(bar, a.stageBytes);
                             const KCoord   kc   = kCoordOf(a, kb);
                             const uint32_t dstA = smemAddr(tiles + size_t(stage) * stageStride);
-                            if constexpr(LAYOUT & 1)
+                            if(!waited)
+                            {
+                                // the first read of global memory: the grid ahead of this one must be complete
+                                asm volatile("griddepcontrol.wait;" ::: "memory");
+                                waited = true;
+                                HTB_STAMP1(2);
+                            }
+                            if(!loadsA)
+                            {
+                            }
+                            else if constexpr(LAYOUT & 1)
                             {
                                 // MN-major map {mode0, K, mode1, mode2, ..}: one [64 k][64 rows] box per chunk
 #pragma unroll
@@ -277,7 +314,10 @@ namespace htb
                                                   kPlace(3, a.kPosA, kc, cA[3]), kPlace(4, a.kPosA, kc, cA[4])};
                                 tmaLoad<5>(dstA, &mapA, bar, c);
                             }
-                            if constexpr(LAYOUT & 2)
+                            if(loadsA)
+                            {
+                            }
+                            else if constexpr(LAYOUT & 2)
                             {
                                 for(int j = 0; j < (tileN >> 6); j++)
                                 {
@@ -292,6 +332,10 @@ namespace htb
                                                   kPlace(3, a.kPosB, kc, cB[3]), kPlace(4, a.kPosB, kc, cB[4])};
                                 tmaLoad<5>(dstA + aBytes, &mapB, bar, c);
                             }
+                            if(kb == kb0)
+                                HTB_STAMP1(3);
+                            if(kb == kb1 - 1)
+                                HTB_STAMP1(9);
                             if(++stage == a.stages)
                             {
                                 stage = 0;
@@ -322,16 +366,20 @@ namespace htb
                         const uint32_t accPhase = (local >> 1) & 1;
                         int            kb0, kb1;
                         kRange(u, kb0, kb1);
-                        ok = mbarWait(smemAddr(&tmemEmptyBar[acc]), accPhase ^ 1, abortP);
+                        ok = mbarWaitTight(smemAddr(&tmemEmptyBar[acc]), accPhase ^ 1, abortP);
                         if(!ok)
                             break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint32_t dTmem = tmem + uint32_t(acc * tileN);
                         for(int kb = kb0; kb < kb1; kb++)
                         {
-                            ok = mbarWait(smemAddr(&fullBar[stage]), phase, abortP);
+                            ok = mbarWaitTight(smemAddr(&fullBar[stage]), phase, abortP);
                             if(!ok)
                                 break;
+                            if(kb == kb0)
+                                HTB_STAMP1(4);
+                            if(kb == kb1 - 1)
+                                HTB_STAMP1(10);
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                             const uint32_t sa    = smemAddr(tiles + size_t(stage) * stageStride);
                             const uint64_t descA = (LAYOUT & 1) ? smemDescMn(sa) : smemDesc(sa);
@@ -364,6 +412,7 @@ namespace htb
                             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                                              smemAddr(&tmemFullBar[acc]))
                                          : "memory");
+                        HTB_STAMP1(5);
                     }
                 }
                 if(parts > 1)
@@ -427,6 +476,10 @@ namespace htb
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if(!ok)
                         break;
+                    // C is read and D written from here on (the sums exist, so the producer's own wait has long returned)
+                    asm volatile("griddepcontrol.wait;" ::: "memory");
+                    if(threadIdx.x == 64)
+                        HTB_STAMP1(6);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(acc * tileN);
                     // K split: parts 1.. store their raw accumulators into part 0's stage memory (idle once every CTA of
@@ -536,6 +589,8 @@ namespace htb
                     // hand the accumulator back to the MMA warp
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     mbarArrive(smemAddr(&tmemEmptyBar[acc]));
+                    if(threadIdx.x == 64)
+                        HTB_STAMP1(7);
                 }
                 for(; parts > 1 && syncs < 2; syncs++)
                     clusterSync(); // a role that gave up still meets the others
@@ -544,12 +599,16 @@ namespace htb
             // ---------------------------------------------------------------- teardown
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncthreads();
+            if(threadIdx.x == 0)
+                HTB_STAMP1(8);
             if(threadIdx.x == 0 && abortFlag && a.status)
                 atomicExch(a.status, 2);
             if(warp == 1)
             {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmemCols) : "memory");
+                if(lane == 0)
+                    HTB_STAMP1(11);
             }
         }
 
@@ -734,8 +793,9 @@ namespace htb
                 HTB_STAMP(3, 0, 0);
             // Programmatic dependent launch: the next kernel of the stream (when it was launched with that attribute)
             // may bring its CTAs up as soon as every CTA of this grid is here, so that its barrier set-up, tensor-memory
-            // allocation and cluster meeting overlap this grid's tail; it reads or writes global memory only after
-            // its own griddepcontrol.wait below, i.e. once this grid is complete.
+            // allocation, cluster meeting and first tile arithmetic overlap this grid's tail; its threads read or write
+            // global memory only after their own griddepcontrol.wait (the producer right before its first load, the
+            // epilogue threads before C and D), i.e. once this grid is complete.
             asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
             if(threadIdx.x == 32)
             {
@@ -775,8 +835,6 @@ namespace htb
             volatile int*  abortP = &abortFlag;
             const uint32_t tilesAddr = smemAddr(tiles);
             const uint32_t fullAddr = smemAddr(&fullBar[0]), emptyAddr = smemAddr(&emptyBar[0]);
-            // everything above touched no global memory; from here on the kernel before this one must be complete
-            asm volatile("griddepcontrol.wait;" ::: "memory");
             if(threadIdx.x == 0)
                 HTB_STAMP(3, 0, 1);
 
@@ -791,6 +849,7 @@ namespace htb
                     bool           ok = true;
                     TcSched        sched = schedInit(pa, clusterId, numClusters);
                     TcUnit         w;
+                    bool           waited = false;
                     while(ok && schedNext<NSUB>(pa, numClusters, kpart, sched, w))
                     {
                         const int    tm = min(2 * w.pm + int(pairRank), a.tilesM - 1);
@@ -848,6 +907,12 @@ namespace htb
                                     mbarArriveExpectTx(fullAddr + 8 * stage, txBytes);
                                 const uint32_t bar = leaderFull + 8 * stage;
                                 const uint32_t dst = tilesAddr + stage * kStage;
+                                if(!waited)
+                                {
+                                    // the first read of global memory: the grid ahead of this one must be complete
+                                    asm volatile("griddepcontrol.wait;" ::: "memory");
+                                    waited = true;
+                                }
 #pragma unroll
                                 for(int q = 0; q < KSUB; q++)
                                 {
@@ -1073,6 +1138,8 @@ namespace htb
                     __syncwarp();
                     if(epiBarrierAny<EPI>(failed))
                         break;
+                    // C is read and D written from here on (the sums exist, so the producer's own wait has long returned)
+                    asm volatile("griddepcontrol.wait;" ::: "memory");
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(acc * 256);
                     // D offsets of the eight rows of this lane's group of eight lanes (for the line-wise stores below)

@@ -193,6 +193,14 @@ def test_contraction_f16_tile_choice_by_size(ht):
     d = plan(768, 768, 512)
     assert " pair" not in d, d  # nine tiles, short K: single CTAs
     assert " pair 256x512" in plan(4096, 4096, 4096)
+    # measured mid-size rules: from a quarter of the SMs' worth of 256 x 256 tiles on, CTA pairs; below that, pairs with
+    # the K range of every tile cut in two from K = 2048 on; short K on few tiles stays with single CTAs
+    assert " pair " in plan(2048, 1536, 1024) and "ksplit" not in plan(2048, 1536, 1024)  # 48 tiles
+    assert " pair " in plan(1536, 1536, 512) and "ksplit" not in plan(1536, 1536, 512)  # 36 tiles, short K
+    assert "ksplit=2" in plan(1024, 1024, 2048)  # 16 tiles
+    assert "ksplit=2" in plan(1024, 768, 4096)  # 12 tiles
+    assert " pair" not in plan(1024, 1024, 1024)  # 16 tiles, K too short for the exchange
+    assert " pair" not in plan(512, 1024, 4096)  # 8 tiles: single CTAs with their own cluster K split
 
 
 def test_contraction_config5(ht):
