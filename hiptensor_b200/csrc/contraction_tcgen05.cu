@@ -40,7 +40,7 @@ namespace htb
 {
     namespace
     {
-        constexpr int kThreads   = 224; // warps: 0 producer of A, 1 MMA issuer, 2-5 epilogue, 6 producer of B
+        constexpr int kThreads   = 192;
         constexpr int kTileM     = 128;
         constexpr int kTileK     = 64; // 64 half-precision elements = one 128-byte swizzle row
         constexpr int kMaxStages = 8;
@@ -248,14 +248,11 @@ namespace htb
             const uint32_t tmem = tmemBase;
             volatile int*  abortP = &abortFlag;
 
-            if(warp == 0 || warp == 6)
+            if(warp == 0)
             {
-                // ---------------------------------------------------------------- TMA producers
-                // Two threads of two warps walk the same stages: one arms the barrier and loads A, the other loads B.
-                // One thread needed 0.27 - 0.35 us per K block for its two load instructions, which bounded small and
-                // mid-size problems (the MMAs of a 128 x 128 x 64 block take 0.07 us). Every stage has loads of both,
-                // so neither thread can fall a ring behind the other.
-                const bool loadsA = (warp == 0);
+                // ---------------------------------------------------------------- TMA producer
+                // (a second thread issuing the loads of B was measured and changed nothing: a K block's period is what
+                // the SM's path from L2 delivers, 0.2 us for the 24 KiB of a 128 x 64 tile)
                 if(lane == 0)
                 {
                     int      stage = 0;
@@ -283,8 +280,7 @@ namespace htb
                             if(!ok)
                                 break;
                             const uint32_t bar = smemAddr(&fullBar[stage]);
-                            if(loadsA)
-                                mbarArriveExpectTx(bar, a.stageBytes);
+                            mbarArriveExpectTx(bar, a.stageBytes);
                             const KCoord   kc   = kCoordOf(a, kb);
                             const uint32_t dstA = smemAddr(tiles + size_t(stage) * stageStride);
                             if(!waited)
@@ -294,10 +290,7 @@ namespace htb
                                 waited = true;
                                 HTB_STAMP1(2);
                             }
-                            if(!loadsA)
-                            {
-                            }
-                            else if constexpr(LAYOUT & 1)
+                            if constexpr(LAYOUT & 1)
                             {
                                 // MN-major map {mode0, K, mode1, mode2, ..}: one [64 k][64 rows] box per chunk
 #pragma unroll
@@ -314,10 +307,7 @@ namespace htb
                                                   kPlace(3, a.kPosA, kc, cA[3]), kPlace(4, a.kPosA, kc, cA[4])};
                                 tmaLoad<5>(dstA, &mapA, bar, c);
                             }
-                            if(loadsA)
-                            {
-                            }
-                            else if constexpr(LAYOUT & 2)
+                            if constexpr(LAYOUT & 2)
                             {
                                 for(int j = 0; j < (tileN >> 6); j++)
                                 {
