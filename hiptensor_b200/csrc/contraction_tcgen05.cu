@@ -1671,9 +1671,9 @@ namespace htb
                 }
                 pa.idescHalf = (1u << 4) | (fmt << 7) | (fmt << 10) | majors | (uint32_t(128 >> 3) << 17)
                                | (uint32_t(256 >> 4) << 24);
-                // Half tiles (256 x 256 tiles): several waves, the last at most half full: its tiles run as two units of
-                // one sub-tile each. The N sub-tiles must pair up evenly.
-                if(nsub == 1 && pa.ksplit == 1 && tiles > maxClusters && !sw.tcNoHalf && a.tilesN % 2 == 0 && pa.singleOk)
+                // Half tiles (256 x 256 tiles): a last wave (or the only one) that is at most half full: its tiles run as
+                // two units of one sub-tile each. The N sub-tiles must pair up evenly.
+                if(nsub == 1 && pa.ksplit == 1 && !sw.tcNoHalf && a.tilesN % 2 == 0 && pa.singleOk)
                 {
                     const int64_t tail = tiles % maxClusters;
                     if(tail > 0 && 2 * tail <= maxClusters)

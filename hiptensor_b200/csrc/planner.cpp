@@ -123,30 +123,30 @@ namespace htb
     // The main loops run at the same rate per flop (a pipeline stage turns around in 2.3 - 2.7 us whatever it holds),
     // so the wider tile only pays where it saves rounds or operand traffic, and a K split only where the tiles fill
     // at most half of the pairs (each part must still be 16 stages long to pay for the exchange).
-    // Mid-size problems, same protocol (single CTAs / pairs / pairs with the K split):
+    // Mid-size problems, same protocol (single CTAs / pairs, an under-filled wave in half tiles / pairs with the K split):
     //   tiles   M x N        K = 512          1024             2048             4096
-    //     9    768 x 768    6.8/8.5/8.8     9.9/10.8/10.1   12.7/15.4/12.5   18.6/26.5/18.3
-    //    16   1024 x 1024   6.9/8.5/8.8     9.6/10.8/10.1   15.1/16.3/13.1   25.8/26.7/18.4
-    //    25   1280 x 1280   8.9/8.6/10.5   11.7/11.4/12.0   17.5/17.0/14.9   28.4/27.0/20.0
-    //    32    512 x 4096   8.6/9.2/11.4   11.7/12.3/13.2   17.1/17.6/16.0   27.9/28.1/21.5
-    //    36   1536 x 1536  10.2/9.1/9.1    13.2/12.0/11.9   18.8/17.0/17.0   29.7/28.0/27.2
-    //    48   2048 x 1536  14.6/10.7/-     17.3/13.1/-      23.3/18.2/-      35.2/28.7/-
-    //    64   2048 x 2048  13.2/12.1/-     15.0/13.9/-      21.1/19.9/-      37.0/35.9/-
-    //   100   2560 x 2560  31.7/15.0/-     31.6/18.2/-      43.9/29.7/-      69.5/55.8/-
-    // A single CTA's tile has no operand sharing, so once a quarter of the SMs have a 256 x 256 tile the pairs win;
-    // below that the K split wins from K = 2048 on, and short K stays with single CTAs (narrow tiles on many SMs).
+    //     9    768 x 768    6.8/6.7/8.8     9.9/9.0/10.1    12.7/13.5/12.5   18.6/22.8/18.3
+    //    16   1024 x 1024   6.9/6.8/8.8     9.6/9.2/10.1    15.1/14.0/13.1   25.8/23.1/18.4
+    //    25   1280 x 1280   8.9/8.2/10.5   11.7/10.7/12.0   17.5/15.4/14.9   28.4/24.4/20.0
+    //    32    512 x 4096   8.6/9.0/11.4   11.7/11.5/13.2   17.1/16.0/16.0   27.9/25.5/21.5
+    //    36   1536 x 1536  10.2/9.2/9.1    13.2/11.7/11.9   18.8/16.3/17.0   29.7/25.4/27.2
+    //    48   2048 x 1536  14.6/10.5/-     17.3/13.1/-      23.3/18.2/-      35.2/28.4/-
+    //    64   2048 x 2048  13.2/11.8/-     15.0/13.9/-      21.1/19.1/-      37.0/34.8/-
+    //   100   2560 x 2560  31.7/14.5/-     31.6/18.2/-      43.9/28.1/-      69.5/53.0/-
+    // A single CTA's tile shares no operand with a neighbour and an SM takes 64 bytes per clock from L2, so the pairs win
+    // from nine tiles on unless K is short; up to 32 tiles and from K = 2048 on the K split is better still.
     void pairKernelForm(int64_t M, int64_t N, int64_t K, int sms, int* pair, int* wide, int* ksplit)
     {
         const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256), pairs = sms / 2, quads = sms / 4 - 1;
         *pair   = 0;
         *wide   = 0;
         *ksplit = 1;
-        if(tiles >= sms / 16 && tiles <= quads && K >= 2048)
+        if(tiles >= sms / 16 && tiles <= (int64_t(sms) * 7) / 32 && K >= 2048)
         {
             *pair   = 1;
             *ksplit = 2;
         }
-        else if(tiles >= quads)
+        else if(tiles >= quads || (tiles >= sms / 16 && K >= 1024))
         {
             *pair = 1;
             *wide = tiles > (3 * pairs) / 2 ? 1 : 0;

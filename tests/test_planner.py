@@ -188,8 +188,10 @@ def test_contraction_f16_tile_choice_by_size(ht):
     assert "tile=128x64x64" in d and " pair" not in d, d
     d = plan(2048, 2048, 2048)
     assert "tile=128x256x64" in d and " pair " in d, d  # 64 tiles of 256 x 256: CTA pairs
+    d = plan(1280, 1280, 4096)
+    assert " pair " in d and "ksplit=2" in d, d  # 25 tiles of 256 x 256 and a long K: pairs with the K cut
     d = plan(1536, 1536, 4096)
-    assert " pair " in d and "ksplit=2" in d, d  # 36 tiles of 256 x 256 and a long K: pairs with the K cut
+    assert " pair " in d and "ksplit" not in d, d  # 36 tiles: plain pairs (an under-filled wave runs in half tiles)
     d = plan(768, 768, 512)
     assert " pair" not in d, d  # nine tiles, short K: single CTAs
     assert " pair 256x512" in plan(4096, 4096, 4096)
@@ -199,7 +201,9 @@ def test_contraction_f16_tile_choice_by_size(ht):
     assert " pair " in plan(1536, 1536, 512) and "ksplit" not in plan(1536, 1536, 512)  # 36 tiles, short K
     assert "ksplit=2" in plan(1024, 1024, 2048)  # 16 tiles
     assert "ksplit=2" in plan(1024, 768, 4096)  # 12 tiles
-    assert " pair" not in plan(1024, 1024, 1024)  # 16 tiles, K too short for the exchange
+    d = plan(1024, 1024, 1024)
+    assert " pair " in d and "ksplit" not in d, d  # 16 tiles, K too short for the exchange: pairs (in half tiles)
+    assert " pair" not in plan(1024, 1024, 512)  # 16 tiles and a short K: single CTAs
     assert " pair" not in plan(512, 1024, 4096)  # 8 tiles: single CTAs with their own cluster K split
 
 
