@@ -469,6 +469,9 @@ namespace htb
             uint32_t  tilesP, tilesQ;
             int       inStages; // input stages in flight per CTA
             int       wide; // 1: modes p and q are split 32 x (extent/32) in the tensor maps (see launchTma)
+            // > 0: mode q stands for two modes of A that are adjacent in B (see launchTma): its first qInner elements
+            // are A's map dimension q, the rest one more dimension at the end of A's map
+            int       qInner;
             uint32_t  numTiles;
             int*      status;
         };
@@ -575,7 +578,25 @@ namespace htb
                 cA[d + sh]            = c;
                 cB[a.mapPosB[d] + sh] = c;
             }
-            if(a.wide)
+            if(a.qInner > 0)
+            {
+                // a tile's q rows are (NQ * E / qInner) whole runs of the inner mode
+                cA[a.q + sh]    = 0;
+                cA[a.ndim + sh] = tq * (NQ * E / a.qInner);
+                if(a.wide)
+                {
+                    cA[1]            = tp * NP;
+                    cB[1]            = tq * NQ;
+                    cB[a.posP_B + 1] = tp * NP * E;
+                }
+                else
+                {
+                    cA[0]        = tp * NP * E;
+                    cB[a.posQ_B] = tq * NQ * E;
+                    cB[a.posP_B] = tp * NP * E;
+                }
+            }
+            else if(a.wide)
             {
                 cA[1]            = tp * NP; // p: 128-byte group index
                 cA[a.q + 1]      = tq * NQ * E; // q: rows of the input tile
@@ -653,7 +674,7 @@ namespace htb
                         if(a.wide)
                         {
                             // one box [32][NP][..][TQ]: the NP 128-byte pieces of a row arrive together
-                            tmaLoadN(a.ndim + 1, smemAddr(in + stage * kStageFloats), &mapA, bar, cA);
+                            tmaLoadN(a.ndim + 1 + (a.qInner > 0 ? 1 : 0), smemAddr(in + stage * kStageFloats), &mapA, bar, cA);
                         }
                         else
                         {
@@ -662,7 +683,7 @@ namespace htb
                             for(int i = 0; i < NP; i++)
                             {
                                 cA[0] = p0 + E * i;
-                                tmaLoadN(a.ndim, smemAddr(in + stage * kStageFloats + i * TQ * 32), &mapA, bar, cA);
+                                tmaLoadN(a.ndim + (a.qInner > 0 ? 1 : 0), smemAddr(in + stage * kStageFloats + i * TQ * 32), &mapA, bar, cA);
                             }
                         }
                         if(++stage == a.inStages)
@@ -832,10 +853,50 @@ namespace htb
         };
 
         template <int NP, int NQ, int ESZ>
-        cudaError_t launchTma(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB,
+        cudaError_t launchTma(const PermPlan& plan, const void* A, void* B, float alpha, int opA, int opB,
                               const PermTune& tune, int smCount, int* status, cudaStream_t stream)
         {
             constexpr int E = 128 / ESZ, TP = E * NP, TQ = E * NQ;
+            // Merged q. When B's contiguous mode q is shorter than a tile's TQ rows, a tile would be mostly empty
+            // and B would be written in pieces of ext[q] elements (the slab of an output mode split over 8 GPUs:
+            // 16 floats). If the next mode of B, q2, follows q without a gap, the two form one contiguous run in B:
+            // the kernel then sees ONE mode of ext[q] * ext[q2] elements with stride 1 in B, and only A's tensor
+            // map knows that it is two of A's modes (dimension q with box ext[q], and one more dimension at the
+            // end of the map with box TQ / ext[q]: the rows of the shared tile then come in B's order).
+            PermPlan p      = plan;
+            int      qInner = 0;
+            int64_t  q2Ext = 0, q2StrideA = 0;
+            if(p.ndim >= 3 && p.ndim <= 4 && p.ext[p.q] < TQ && TQ % p.ext[p.q] == 0 && p.orderB[0] == p.q)
+            {
+                const int q2 = p.orderB[1];
+                if(q2 != 0 && p.sB[q2] == p.ext[p.q])
+                {
+                    qInner    = int(p.ext[p.q]);
+                    q2Ext     = p.ext[q2];
+                    q2StrideA = p.sA[q2];
+                    // drop q2 from the modes the kernel walks; q takes the merged extent
+                    PermPlan m = p;
+                    m.ndim     = 0;
+                    int remap[kMaxGroup];
+                    for(int d = 0; d < p.ndim; d++)
+                    {
+                        remap[d] = -1;
+                        if(d == q2)
+                            continue;
+                        remap[d]     = m.ndim;
+                        m.ext[m.ndim] = p.ext[d] * (d == p.q ? q2Ext : 1);
+                        m.sA[m.ndim]  = p.sA[d];
+                        m.sB[m.ndim]  = p.sB[d];
+                        m.ndim++;
+                    }
+                    m.q = remap[p.q];
+                    int n = 0;
+                    for(int i = 0; i < p.ndim; i++)
+                        if(p.orderB[i] != q2)
+                            m.orderB[n++] = remap[p.orderB[i]];
+                    p = m;
+                }
+            }
             constexpr CUtensorMapDataType kType = ESZ == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
             PFN_encodeTiled encode = tensorMapEncoder();
             if(!encode)
@@ -847,16 +908,24 @@ namespace htb
             // Wide maps: the contiguous mode is described as (32, extent/32) so that ONE box
             // [32][NP] covers NP consecutive 128-byte pieces of a row; the pieces of one row are
             // then requested back to back and DRAM serves them from one open page.
-            const bool wide = (NP > 1 || NQ > 1) && p.ndim <= 4 && p.ext[0] % E == 0 && p.ext[p.q] % E == 0;
+            const bool wide = (NP > 1 || NQ > 1) && p.ndim + (qInner ? 1 : 0) <= 4 && p.ext[0] % E == 0 && p.ext[p.q] % E == 0;
             a.wide          = wide ? 1 : 0;
+            a.qInner        = qInner;
             const int sh    = wide ? 1 : 0;
             // A: folded modes in A's order
             for(int d = 0; d < p.ndim; d++)
             {
-                gdim[d + sh] = cuuint64_t(p.ext[d]);
+                gdim[d + sh] = cuuint64_t(d == p.q && qInner ? qInner : p.ext[d]);
                 box[d + sh]  = 1;
                 if(d > 0)
                     gstr[d - 1 + sh] = cuuint64_t(p.sA[d]) * ESZ;
+            }
+            if(qInner)
+            {
+                // the second mode of a merged q: last dimension of A's map
+                gdim[p.ndim + sh]     = cuuint64_t(q2Ext);
+                gstr[p.ndim - 1 + sh] = cuuint64_t(q2StrideA) * ESZ;
+                box[p.ndim + sh]      = cuuint32_t(TQ / qInner);
             }
             if(wide)
             {
@@ -868,8 +937,8 @@ namespace htb
             }
             else
                 box[0] = E;
-            box[p.q + sh] = TQ;
-            if(encode(&mapA, kType, p.ndim + sh, const_cast<void*>(A), gdim, gstr, box, estr,
+            box[p.q + sh] = qInner ? cuuint32_t(qInner) : cuuint32_t(TQ);
+            if(encode(&mapA, kType, p.ndim + sh + (qInner ? 1 : 0), const_cast<void*>(A), gdim, gstr, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
                != CUDA_SUCCESS)

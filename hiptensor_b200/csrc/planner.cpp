@@ -244,9 +244,14 @@ namespace htb
             // TMA path: fp32 -> fp32 and f16 -> f16, every stride a multiple of 16 bytes (extents of the two
             // contiguous modes multiples of 4 / 8 elements)
             const int64_t per16 = 16 / std::max(out->elemSize, 1);
+            // a short contiguous mode of B (a power of two from 16 bytes on) will do when the mode after it in B makes
+            // one contiguous run with it: the kernel merges the two (launchTma, "merged q")
+            const int64_t extQ      = out->ext[out->q];
+            const bool    mergeable = n >= 3 && n <= 4 && isPow2(extQ) && out->orderB[0] == out->q && out->orderB[1] != 0
+                                   && out->sB[out->orderB[1]] == extQ;
             bool tma = ((typeA == CUDA_R_32F && typeB == CUDA_R_32F) || (typeA == CUDA_R_16F && typeB == CUDA_R_16F))
-                       && pointersAligned16 && n <= 5 && out->ext[0] % per16 == 0 && out->ext[out->q] % per16 == 0
-                       && out->ext[0] >= 4 * per16 && out->ext[out->q] >= 4 * per16;
+                       && pointersAligned16 && n <= 5 && out->ext[0] % per16 == 0 && extQ % per16 == 0
+                       && out->ext[0] >= 4 * per16 && (extQ >= 4 * per16 || mergeable);
             for(int i = 0; i < n && tma; i++)
             {
                 // cuTensorMapEncodeTiled limits: extent < 2^32, byte stride < 2^40

@@ -106,6 +106,23 @@ def test_config2_full_size_f16(env):
     assert torch.equal(B.view(torch.int16), ref.view(torch.int16))
 
 
+@pytest.mark.parametrize("typeA", [orc.F32, orc.F16])
+@pytest.mark.parametrize("lens,perm", [([128, 24, 40, 16], [3, 2, 1, 0]), ([64, 10, 38, 32], [3, 2, 1, 0]),
+                                       ([96, 50, 16], [2, 1, 0]), ([64, 6, 37, 8], [3, 2, 0, 1]),
+                                       ([128, 16, 7, 16], [3, 1, 0, 2]), ([64, 33, 16, 5], [2, 1, 3, 0]),
+                                       ([128, 12, 9, 8], [3, 2, 1, 0]), ([64, 5, 22, 4], [3, 2, 1, 0]),
+                                       ([256, 3, 130, 8], [3, 2, 0, 1])])
+def test_tma_short_contiguous_output_mode(env, typeA, lens, perm):
+    """B's contiguous mode is shorter than a tile: the TMA kernel merges it with the mode that follows it in B when the
+    two are one contiguous run there (the slab of an output mode split over several GPUs), with whole and ragged
+    numbers of runs per tile; otherwise it runs the short mode alone. Bit-exact either way."""
+    ht, h = env
+    got, exp = run_permutation(ht, h, lens, list(range(len(lens))), perm, typeA=typeA, alpha=1.0)
+    assert np.array_equal(bits(got), bits(exp)), (lens, perm, ht.last_kernel_name())
+    got, exp = run_permutation(ht, h, lens, list(range(len(lens))), perm, typeA=typeA, alpha=0.5)
+    assert np.array_equal(bits(got), bits(exp)), (lens, perm, ht.last_kernel_name())
+
+
 @pytest.mark.parametrize("rank", [2, 3, 5, 6])
 def test_other_ranks(env, rank):
     ht, h = env
