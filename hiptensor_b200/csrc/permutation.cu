@@ -472,6 +472,8 @@ namespace htb
             // > 0: mode q stands for two modes of A that are adjacent in B (see launchTma): its first qInner elements
             // are A's map dimension q, the rest one more dimension at the end of A's map
             int       qInner;
+            // the same for mode p (A's contiguous mode) and the mode that follows it in A: B's map has the extra dimension
+            int       pInner;
             uint32_t  numTiles;
             int*      status;
         };
@@ -578,23 +580,34 @@ namespace htb
                 cA[d + sh]            = c;
                 cB[a.mapPosB[d] + sh] = c;
             }
-            if(a.qInner > 0)
+            if(a.qInner > 0 || a.pInner > 0)
             {
-                // a tile's q rows are (NQ * E / qInner) whole runs of the inner mode
-                cA[a.q + sh]    = 0;
-                cA[a.ndim + sh] = tq * (NQ * E / a.qInner);
+                // a tile's rows of a merged mode are whole runs of its inner mode: coordinate 0 there, the run index
+                // in the extra dimension at the end of the other tensor's map
                 if(a.wide)
                 {
-                    cA[1]            = tp * NP;
-                    cB[1]            = tq * NQ;
-                    cB[a.posP_B + 1] = tp * NP * E;
+                    cA[1] = tp * NP;
+                    cB[1] = tq * NQ;
                 }
                 else
                 {
                     cA[0]        = tp * NP * E;
                     cB[a.posQ_B] = tq * NQ * E;
-                    cB[a.posP_B] = tp * NP * E;
                 }
+                if(a.qInner > 0)
+                {
+                    cA[a.q + sh]    = 0;
+                    cA[a.ndim + sh] = tq * (NQ * E / a.qInner);
+                }
+                else
+                    cA[a.q + sh] = tq * NQ * E;
+                if(a.pInner > 0)
+                {
+                    cB[a.posP_B + sh] = 0;
+                    cB[a.ndim + sh]   = tp * (NP * E / a.pInner);
+                }
+                else
+                    cB[a.posP_B + sh] = tp * NP * E;
             }
             else if(a.wide)
             {
@@ -810,7 +823,7 @@ namespace htb
                         cB[d] = coordOut[ostage][d];
                     if(a.wide)
                     {
-                        tmaStoreN(a.ndim + 1, &mapB, smemAddr(outb + ostage * kStageFloats), cB);
+                        tmaStoreN(a.ndim + 1 + (a.pInner > 0 ? 1 : 0), &mapB, smemAddr(outb + ostage * kStageFloats), cB);
                     }
                     else
                     {
@@ -819,7 +832,7 @@ namespace htb
                         for(int j = 0; j < NQ; j++)
                         {
                             cB[a.posQ_B] = q0 + E * j;
-                            tmaStoreN(a.ndim, &mapB, smemAddr(outb + ostage * kStageFloats + j * TP * 32), cB);
+                            tmaStoreN(a.ndim + (a.pInner > 0 ? 1 : 0), &mapB, smemAddr(outb + ostage * kStageFloats + j * TP * 32), cB);
                         }
                     }
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -897,6 +910,37 @@ namespace htb
                     p = m;
                 }
             }
+            // Merged p: the mirror image. A's contiguous mode p (folded mode 0) is shorter than a tile's TP rows and the
+            // next mode of A follows it without a gap: the kernel sees one contiguous mode of A, and B's map carries
+            // the two as dimension p (box ext[p]) and one more dimension at its end (box TP / ext[p]).
+            int     pInner = 0;
+            int64_t p2Ext = 0, p2StrideB = 0;
+            if(p.ndim >= 3 && p.ndim <= 4 && p.ext[0] < TP && TP % p.ext[0] == 0 && p.q != 1 && p.sA[1] == p.ext[0])
+            {
+                pInner     = int(p.ext[0]);
+                p2Ext      = p.ext[1];
+                p2StrideB  = p.sB[1];
+                PermPlan m = p;
+                m.ndim     = 0;
+                int remap[kMaxGroup];
+                for(int d = 0; d < p.ndim; d++)
+                {
+                    remap[d] = -1;
+                    if(d == 1)
+                        continue;
+                    remap[d]      = m.ndim;
+                    m.ext[m.ndim] = p.ext[d] * (d == 0 ? p2Ext : 1);
+                    m.sA[m.ndim]  = p.sA[d];
+                    m.sB[m.ndim]  = p.sB[d];
+                    m.ndim++;
+                }
+                m.q   = remap[p.q];
+                int n = 0;
+                for(int i = 0; i < p.ndim; i++)
+                    if(p.orderB[i] != 1)
+                        m.orderB[n++] = remap[p.orderB[i]];
+                p = m;
+            }
             constexpr CUtensorMapDataType kType = ESZ == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
             PFN_encodeTiled encode = tensorMapEncoder();
             if(!encode)
@@ -908,9 +952,11 @@ namespace htb
             // Wide maps: the contiguous mode is described as (32, extent/32) so that ONE box
             // [32][NP] covers NP consecutive 128-byte pieces of a row; the pieces of one row are
             // then requested back to back and DRAM serves them from one open page.
-            const bool wide = (NP > 1 || NQ > 1) && p.ndim + (qInner ? 1 : 0) <= 4 && p.ext[0] % E == 0 && p.ext[p.q] % E == 0;
+            const bool wide = (NP > 1 || NQ > 1) && p.ndim + ((qInner || pInner) ? 1 : 0) <= 4 && p.ext[0] % E == 0
+                              && p.ext[p.q] % E == 0;
             a.wide          = wide ? 1 : 0;
             a.qInner        = qInner;
+            a.pInner        = pInner;
             const int sh    = wide ? 1 : 0;
             // A: folded modes in A's order
             for(int d = 0; d < p.ndim; d++)
@@ -947,11 +993,18 @@ namespace htb
             for(int i = 0; i < p.ndim; i++)
             {
                 const int d  = p.orderB[i];
-                gdim[i + sh] = cuuint64_t(p.ext[d]);
+                gdim[i + sh] = cuuint64_t(d == 0 && pInner ? pInner : p.ext[d]);
                 box[i + sh]  = 1;
                 a.mapPosB[d] = i;
                 if(i > 0)
                     gstr[i - 1 + sh] = cuuint64_t(p.sB[d]) * ESZ;
+            }
+            if(pInner)
+            {
+                // the second mode of a merged p: last dimension of B's map
+                gdim[p.ndim + sh]     = cuuint64_t(p2Ext);
+                gstr[p.ndim - 1 + sh] = cuuint64_t(p2StrideB) * ESZ;
+                box[p.ndim + sh]      = cuuint32_t(TP / pInner);
             }
             a.posP_B = a.mapPosB[0];
             a.posQ_B = a.mapPosB[p.q];
@@ -965,8 +1018,8 @@ namespace htb
             }
             else
                 box[a.posQ_B] = E;
-            box[a.posP_B + sh] = TP;
-            if(encode(&mapB, kType, p.ndim + sh, B, gdim, gstr, box, estr,
+            box[a.posP_B + sh] = pInner ? cuuint32_t(pInner) : cuuint32_t(TP);
+            if(encode(&mapB, kType, p.ndim + sh + (pInner ? 1 : 0), B, gdim, gstr, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
                != CUDA_SUCCESS)

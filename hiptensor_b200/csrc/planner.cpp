@@ -249,9 +249,11 @@ namespace htb
             const int64_t extQ      = out->ext[out->q];
             const bool    mergeable = n >= 3 && n <= 4 && isPow2(extQ) && out->orderB[0] == out->q && out->orderB[1] != 0
                                    && out->sB[out->orderB[1]] == extQ;
+            // and the same for A's contiguous mode and the mode after it in A ("merged p")
+            const bool mergeableP = n >= 3 && n <= 4 && isPow2(out->ext[0]) && out->q != 1 && out->sA[1] == out->ext[0];
             bool tma = ((typeA == CUDA_R_32F && typeB == CUDA_R_32F) || (typeA == CUDA_R_16F && typeB == CUDA_R_16F))
                        && pointersAligned16 && n <= 5 && out->ext[0] % per16 == 0 && extQ % per16 == 0
-                       && out->ext[0] >= 4 * per16 && (extQ >= 4 * per16 || mergeable);
+                       && (out->ext[0] >= 4 * per16 || mergeableP) && (extQ >= 4 * per16 || mergeable);
             for(int i = 0; i < n && tma; i++)
             {
                 // cuTensorMapEncodeTiled limits: extent < 2^32, byte stride < 2^40

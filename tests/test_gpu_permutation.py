@@ -123,6 +123,22 @@ def test_tma_short_contiguous_output_mode(env, typeA, lens, perm):
     assert np.array_equal(bits(got), bits(exp)), (lens, perm, ht.last_kernel_name())
 
 
+@pytest.mark.parametrize("typeA", [orc.F32, orc.F16])
+@pytest.mark.parametrize("lens,perm", [([16, 40, 24, 128], [3, 2, 1, 0]), ([32, 38, 10, 64], [3, 2, 1, 0]),
+                                       ([16, 50, 96], [2, 1, 0]), ([8, 37, 6, 64], [3, 0, 1, 2]),
+                                       ([16, 7, 16, 128], [3, 2, 0, 1]), ([4, 22, 5, 64], [3, 2, 1, 0]),
+                                       ([16, 24, 40, 16], [3, 2, 1, 0]), ([8, 128, 8], [2, 1, 0]),
+                                       ([16, 20, 30, 8], [3, 1, 2, 0])])
+def test_tma_short_contiguous_input_mode(env, typeA, lens, perm):
+    """A's contiguous mode is shorter than a tile (the mirror image of the test above, e.g. the way back from a slab),
+    alone and together with a short contiguous mode of B. Bit-exact."""
+    ht, h = env
+    got, exp = run_permutation(ht, h, lens, list(range(len(lens))), perm, typeA=typeA, alpha=1.0)
+    assert np.array_equal(bits(got), bits(exp)), (lens, perm, ht.last_kernel_name())
+    got, exp = run_permutation(ht, h, lens, list(range(len(lens))), perm, typeA=typeA, alpha=2.0)
+    assert np.array_equal(bits(got), bits(exp)), (lens, perm, ht.last_kernel_name())
+
+
 @pytest.mark.parametrize("rank", [2, 3, 5, 6])
 def test_other_ranks(env, rank):
     ht, h = env
