@@ -857,7 +857,7 @@ namespace htb
         // Launch-time choices of the TMA kernel. Measured on B200 over the rank-4 orders of a
         // 128^4 fp32 tensor: 64x64 tiles with TWO input stages and two CTAs per SM gave the highest
         // bandwidth on every order (deeper pipelines or more CTAs per SM lost 5-25%: more tiles in
-        // flight mix more read and write streams in DRAM), see profiles/perm_tma_sweep.md.
+        // flight mix more read and write streams in DRAM).
         struct PermTune
         {
             int shape     = 22; // NP*10 + NQ
