@@ -1212,21 +1212,24 @@ namespace htb
                 case 21: e = launchTma<2, 1, 2>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
                 default: e = launchTma<2, 2, 2>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
                 }
-                if(e == cudaSuccess)
-                    noteLaunch("perm_tma");
-                return e;
             }
-            switch(tune.shape)
+            else
             {
-            case 14: e = launchTma<1, 4, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
-            case 41: e = launchTma<4, 1, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
-            case 24: e = launchTma<2, 4, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
-            case 42: e = launchTma<4, 2, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
-            default: e = launchTma<2, 2, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+                switch(tune.shape)
+                {
+                case 14: e = launchTma<1, 4, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+                case 41: e = launchTma<4, 1, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+                case 24: e = launchTma<2, 4, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+                case 42: e = launchTma<4, 2, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+                default: e = launchTma<2, 2, 4>(plan, A, B, alpha, opA, opB, tune, smCount, deviceStatus, stream); break;
+                }
             }
             if(e == cudaSuccess)
                 noteLaunch("perm_tma");
-            return e;
+            // a tensor map that the driver refuses (nothing was launched) leaves the shared-memory tile kernel
+            if(e != cudaErrorInvalidValue)
+                return e;
+            cudaGetLastError();
         }
         if(typeA == CUDA_R_32F)
             return launchPlain<float, float>(plan, A, B, alpha, opA, opB, stream);
