@@ -47,6 +47,18 @@ def test_permutation_folding(ht):
     assert "ndim=2" in d
 
 
+def test_permutation_short_contiguous_modes_stay_on_tma(ht):
+    """A contiguous mode shorter than 64 bytes keeps the TMA kernel when the mode after it in the same tensor makes one
+    contiguous run with it (the slab of an output mode split over 8 GPUs, and the way back); it must still be a
+    multiple of 16 bytes."""
+    assert "kind=tma" in ht.describe_permutation_plan([128, 128, 128, 16], [0, 1, 2, 3], [3, 2, 1, 0])
+    assert "kind=tma" in ht.describe_permutation_plan([128, 128, 128, 16], [0, 1, 2, 3], [3, 2, 1, 0], ht.R_16F, ht.R_16F)
+    assert "kind=tma" in ht.describe_permutation_plan([16, 128, 128, 128], [0, 1, 2, 3], [3, 2, 1, 0])
+    assert "kind=tma" in ht.describe_permutation_plan([128, 24, 40, 4], [0, 1, 2, 3], [3, 2, 1, 0])
+    assert "kind=tile" in ht.describe_permutation_plan([128, 128, 12], [0, 1, 2], [2, 1, 0])  # 12: not a power of two
+    assert "kind=tile" in ht.describe_permutation_plan([128, 128, 128, 4], [0, 1, 2, 3], [3, 2, 1, 0], ht.R_16F, ht.R_16F)
+
+
 def test_permutation_rejects(ht):
     with pytest.raises(ht.HiptensorError) as e:
         ht.describe_permutation_plan([4, 4], [0, 1], [0, 2])
