@@ -253,8 +253,9 @@ namespace htb
         template <typename TAcc, int OP, int G>
         __device__ __forceinline__ TAcc groupReduce(TAcc acc, TAcc* smem)
         {
+            // groups of 8 lanes (short rows) fold within the group only
 #pragma unroll
-            for(int s = 16; s > 0; s >>= 1)
+            for(int s = (G < 32 ? G / 2 : 16); s > 0; s >>= 1)
                 acc = Op<TAcc, OP>::combine(acc, __shfl_xor_sync(0xffffffffu, acc, s));
             if(G > 32)
             {
@@ -274,8 +275,9 @@ namespace htb
         }
 
         // ------------------------------------------------------------ row kernel
-        // blockDim.x = 256. G = 32: eight outputs per block; G = 256: one output per block.
-        // gridDim.y = split.
+        // blockDim.x = 256. G = 32: eight outputs per block; G = 256: one output per block; G = 8: 32 outputs
+        // per block for short rows (a warp per 1 KiB row was bound by the instructions around the loads: offsets,
+        // shuffle tree, epilogue). gridDim.y = split.
         template <typename TIn, typename TAcc, int OP, int G, int VEC>
         __global__ void __launch_bounds__(256)
             red_row_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
@@ -287,8 +289,9 @@ namespace htb
             const int64_t   o = int64_t(blockIdx.x) * perBlock + sub;
             if(G == 32 && o >= a.nOut)
                 return;
+            const bool    idle = G < 32 && o >= a.nOut; // a sub-warp group beyond the last output stays for the shuffles
             const int64_t L0 = a.rext[0], RO = a.nRed / L0;
-            int64_t       roLo = 0, roHi = RO, iLo = 0, iHi = L0;
+            int64_t       roLo = 0, roHi = idle ? 0 : RO, iLo = 0, iHi = L0;
             if(a.split > 1)
             {
                 const int64_t s = blockIdx.y;
@@ -304,7 +307,7 @@ namespace htb
                 }
             }
             int64_t offA, offD;
-            keptOffsets(a, o, offA, offD);
+            keptOffsets(a, idle ? 0 : o, offA, offD);
             Accum<TAcc, OP> accum;
             accum.init();
             for(int64_t ro = roLo; ro < roHi; ro++)
@@ -674,6 +677,12 @@ namespace htb
                             <<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta);
                     else
                         red_row_kernel<TIn, TAcc, OP, 256, 1><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta);
+                }
+                else if(p.vec == 16 / int(sizeof(TIn)) && p.nr == 1 && p.rext[0] * int64_t(sizeof(TIn)) <= 2048)
+                {
+                    // a row of at most 2 KiB: eight lanes per output, four outputs per warp
+                    dim3 grid(unsigned((p.nOut + 31) / 32), gy);
+                    red_row_kernel<TIn, TAcc, OP, 8, 16 / sizeof(TIn)><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta);
                 }
                 else
                 {

@@ -13,6 +13,10 @@ import pytest
 from helpers import check_f32, rel_error, run_reduction
 from oracle import binding as orc
 
+
+def bits(a):
+    return a.view({8: np.uint64, 4: np.uint32, 2: np.uint16}[a.dtype.itemsize])
+
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 TOL = {orc.F32: 1e-5, orc.F64: 1e-5, orc.F16: 2 * 2.0 ** -10, orc.BF16: 2 * 2.0 ** -7}
@@ -73,6 +77,30 @@ def test_layouts_and_beta(env, first_fastest, kept):
         got, exp, exact = run_reduction(ht, h, lens, modeA, kept, alpha=1.2, beta=2.1, stridesA=sA, stridesD=sD,
                                         alias=alias, want_exact=True)
         check_f32(got, exp, exact, terms)
+
+
+@pytest.mark.parametrize("op", [orc.OP_ADD, orc.OP_MAX, orc.OP_MUL])
+@pytest.mark.parametrize("dt,lens", [(orc.F32, [37, 5, 256]), (orc.F32, [9, 11, 8, 32]), (orc.F32, [70, 3, 512]),
+                                     (orc.F16, [37, 5, 512]), (orc.F16, [13, 7, 1024]), (orc.F64, [37, 5, 128])])
+def test_short_rows_eight_lanes_per_output(env, op, dt, lens):
+    """Contiguous reduced rows of at most 2 KiB run with eight lanes per output, four outputs per warp; the number of
+    outputs is not a multiple of 32, so the last block has idle groups. ADD and MUL within the reference's bound, MAX
+    bit-exact."""
+    ht, h = env
+    modeA = list(range(len(lens)))
+    kept = modeA[:2]
+    A = None
+    if op == orc.OP_MUL:  # values near 1 keep the product in range
+        A = (1.0 + orc.fill_uniform(int(np.prod(lens)), orc.F64, 3) * 1e-3).astype({orc.F32: np.float32, orc.F16: np.float16,
+                                                                                 orc.F64: np.float64}[dt])
+    got, exp = run_reduction(ht, h, lens, modeA, kept, dt=dt, op=op, alpha=1.5, beta=0.5, A=A)
+    assert ht.last_kernel_name() == "red_row"
+    terms = int(np.prod(lens[2:]))
+    if op == orc.OP_MAX:
+        assert np.array_equal(bits(got), bits(exp))
+    else:
+        eps = {orc.F32: np.finfo(np.float32).eps, orc.F16: np.finfo(np.float16).eps, orc.F64: np.finfo(np.float64).eps}[dt]
+        assert 0 <= rel_error(got, exp, dt) < max(terms * float(eps), 1e-6)
 
 
 def test_permuted_output_strides(env):
