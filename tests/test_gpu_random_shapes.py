@@ -1,7 +1,7 @@
 """Seeded random shapes through the planner's form rules, checked against references that share nothing with the
 library or the oracle: an fp64 matrix product for mid-size f16 / bf16 contractions (CTA pairs, half tiles, K split,
 single CTAs; all four operand layouts, with and without C), torch.permute for permutations (the TMA kernel with short
-and long contiguous modes, the copy kernel, the shared-memory kernels), bit-exact there."""
+and long contiguous modes, the copy kernel, the shared-memory kernels), bit-exact there; numpy in fp64 for reductions."""
 import numpy as np
 import pytest
 
@@ -78,3 +78,44 @@ def test_random_permutations(env):
         it = torch.int16 if f16 else torch.int32
         assert torch.equal(B.view(it), ref.view(it)), (lens, perm, f16, ht.last_kernel_name())
     assert {"perm_tma", "perm_copy", "perm_tile"} <= kernels
+
+
+def test_random_reductions(env):
+    """Random f32 reductions (ranks 2-5, every kind of kept subset, ADD and MAX, alpha and beta) against numpy in
+    fp64: MAX exactly, ADD within 1e-5 of the exact result."""
+    import torch
+
+    ht, h = env
+    rng = np.random.default_rng(4242)
+    choices = [2, 3, 5, 8, 16, 32, 64, 128, 256, 7, 12, 40]
+    kernels = set()
+    for _ in range(120):
+        rank = int(rng.integers(2, 6))
+        lens = [int(rng.choice(choices)) for _ in range(rank)]
+        while np.prod(lens) > 3e6:
+            lens[int(rng.integers(0, rank))] = 2
+        nkept = int(rng.integers(0, rank))
+        kept = sorted(int(x) for x in rng.choice(rank, size=nkept, replace=False))
+        op = ht.OP_MAX if rng.integers(0, 2) else ht.OP_ADD
+        A = rng.standard_normal(lens).astype(np.float32)
+        lensD = [lens[m] for m in kept] if kept else [1]
+        C = rng.standard_normal(lensD).astype(np.float32)
+        red = tuple(m for m in range(rank) if m not in kept)
+        A64 = A.astype(np.float64)
+        r = (A64.max(axis=red) if op == ht.OP_MAX else A64.sum(axis=red)) if red else A64
+        ref = 1.5 * np.asarray(r, dtype=np.float64).reshape(lensD) + 0.25 * C.astype(np.float64)
+        A_d, C_d = torch.from_numpy(A).cuda(), torch.from_numpy(C).cuda()
+        D_d = torch.full(lensD, float("nan"), device="cuda")
+        dA = h.tensor_descriptor(lens, None, ht.R_32F)
+        dD = h.tensor_descriptor(lensD if kept else [], None, ht.R_32F)  # no kept mode: a rank-0 output
+        h.reduction(1.5, A_d, dA, list(range(rank)), 0.25, C_d, dD, kept, D_d, dD, kept, op, ht.COMPUTE_32F)
+        kernels.add(ht.last_kernel_name())
+        got = D_d.cpu().numpy().astype(np.float64)
+        if op == ht.OP_MAX:
+            exp32 = (np.float32(1.5) * A.max(axis=red).reshape(lensD) if red else np.float32(1.5) * A.reshape(lensD))
+            exp32 = exp32 + np.float32(0.25) * C
+            assert np.array_equal(got.astype(np.float32), exp32.astype(np.float32)), (lens, kept, ht.last_kernel_name())
+        else:
+            scale = max(np.abs(ref).max(), 1e-30)
+            assert np.abs(got - ref).max() / scale < 1e-5, (lens, kept, ht.last_kernel_name())
+    assert "red_row" in kernels and len(kernels) >= 2
