@@ -336,6 +336,166 @@ namespace htb
             }
         }
 
+        // ------------------------------------------------------------ box kernel for short contiguous modes
+        // When A's or B's contiguous folded mode is shorter than a tile side, a (p, q) tile is mostly empty (a store
+        // instruction of the tile kernel wrote 2 of 64 lanes for an extent of 2: 0.16 TB/s). The box kernel
+        // moves a box over SEVERAL modes instead: the leading modes of A until their tile extents multiply to 64 (a
+        // contiguous run of A), the leading modes of B likewise (a contiguous run of B), every tile extent a power
+        // of two. A block reads its box in A's order (consecutive threads along A's run) into shared memory and
+        // writes it in B's order (consecutive threads along B's run); the coordinates of an element follow from its
+        // index in the box by shifts.
+        constexpr int kBoxMaxDims = 6;
+        constexpr int kBoxBits    = 13; // a box holds at most 8192 elements
+        constexpr int kBoxRounds  = 1 << (kBoxBits - 8); // elements per thread of a block of 256
+        struct PermBoxArgs
+        {
+            int      nb; // modes of the box
+            int      no; // other modes (walked by the grid)
+            // box modes in A's order (ascending stride in A): log2 of the tile extent, extent, strides
+            int      lgA[kBoxMaxDims];
+            uint32_t extA[kBoxMaxDims];
+            int64_t  sAofA[kBoxMaxDims], sBofA[kBoxMaxDims];
+            uint32_t tilesOf[kBoxMaxDims]; // tiles along each box mode (A's order)
+            uint32_t extO[kBoxMaxDims];
+            int64_t  sAO[kBoxMaxDims], sBO[kBoxMaxDims];
+            int      lgBox; // log2 of the box size
+            // Every tile extent is a power of two, so an element's offsets are sums over the BITS of its index in
+            // the box: bit k of the index in A's order adds wA[k] to the offset in A; bit k of the index in B's order
+            // adds wB[k] to the offset in B, slotB[k] to the index in A's order (where the element lies in shared
+            // memory) and belongs to box mode dimB[k] with value valB[k] there (for the bounds of an edge box).
+            int64_t  wA[kBoxBits], wB[kBoxBits];
+            uint32_t slotB[kBoxBits];
+            // the same sums for every value of the index bits above the low eight (a thread's elements differ in those)
+            int64_t  hiA[kBoxRounds], hiB[kBoxRounds];
+            uint32_t hiS[kBoxRounds];
+            float    alpha;
+            int      opA, opB;
+        };
+
+        // slot of box element i in shared memory: the low five bits are mixed with the bits above them, so that the
+        // strided reads of the write phase (strides of 32, 64, .. 4096 elements) spread over the banks
+        __device__ __forceinline__ uint32_t boxSlot(uint32_t i)
+        {
+            return i ^ (((i >> 5) ^ (i >> 10)) & 31u);
+        }
+
+        template <typename TI, typename TO, bool PLAIN>
+        __global__ void __launch_bounds__(256) perm_box_kernel(const TI* __restrict__ A, TO* __restrict__ B, PermBoxArgs a)
+        {
+            extern __shared__ __align__(16) unsigned char boxRaw[];
+            TI*      box = reinterpret_cast<TI*>(boxRaw);
+            // origin of the box and offsets of the other modes (32-bit divisions: the grid is below 2^31 blocks)
+            uint32_t bid = blockIdx.x;
+            uint32_t org[kBoxMaxDims];
+            int64_t  offA = 0, offB = 0;
+            bool     inside = true;
+#pragma unroll
+            for(int d = 0; d < kBoxMaxDims; d++)
+            {
+                org[d] = 0;
+                if(d < a.nb)
+                {
+                    const uint32_t t = bid % a.tilesOf[d];
+                    bid /= a.tilesOf[d];
+                    org[d] = t << a.lgA[d];
+                    offA += int64_t(org[d]) * a.sAofA[d];
+                    offB += int64_t(org[d]) * a.sBofA[d];
+                    inside = inside && org[d] + (1u << a.lgA[d]) <= a.extA[d];
+                }
+            }
+            for(int d = 0; d < a.no; d++)
+            {
+                const uint32_t c = bid % a.extO[d];
+                bid /= a.extO[d];
+                offA += int64_t(c) * a.sAO[d];
+                offB += int64_t(c) * a.sBO[d];
+            }
+            const uint32_t size = 1u << a.lgBox;
+            // an element of an edge box lies in the tensor when every coordinate does (index i in A's order)
+            auto valid = [&](uint32_t i) {
+                bool ok = true;
+                int  sh = 0;
+#pragma unroll
+                for(int d = 0; d < kBoxMaxDims; d++)
+                    if(d < a.nb)
+                    {
+                        ok = ok && org[d] + ((i >> sh) & ((1u << a.lgA[d]) - 1u)) < a.extA[d];
+                        sh += a.lgA[d];
+                    }
+                return ok;
+            };
+            // A thread's elements share the low eight bits of their index (blockDim.x = 256): that part of the offsets
+            // is summed once per thread; the part of the bits above comes from the launch arguments (constant memory:
+            // no load instruction competes with the element moves).
+            const uint32_t t = threadIdx.x;
+            int64_t  lowA = offA, lowB = offB;
+            uint32_t lowI = 0;
+#pragma unroll
+            for(int k = 0; k < 8; k++)
+                if((t >> k) & 1u)
+                {
+                    lowA += a.wA[k];
+                    lowB += a.wB[k];
+                    lowI += a.slotB[k];
+                }
+            const uint32_t rounds = max(size >> 8, 1u);
+            const bool     mine   = t < size; // boxes of fewer than 256 elements
+            const TI*      src    = A + lowA;
+            if(inside)
+            {
+                // eight loads in flight per thread: with elements of two or four bytes the bytes in flight bound the rate
+#pragma unroll
+                for(uint32_t k0 = 0; k0 < kBoxRounds; k0 += 8)
+                    if(k0 < rounds)
+                    {
+                        TI v[8];
+#pragma unroll
+                        for(uint32_t j = 0; j < 8; j++)
+                            if(mine && k0 + j < rounds)
+                                v[j] = src[a.hiA[k0 + j]];
+#pragma unroll
+                        for(uint32_t j = 0; j < 8; j++)
+                            if(mine && k0 + j < rounds)
+                                box[boxSlot(t | ((k0 + j) << 8))] = v[j];
+                    }
+            }
+            else
+            {
+                for(uint32_t k = 0; k < rounds; k++)
+                    if(mine && valid(t | (k << 8)))
+                        box[boxSlot(t | (k << 8))] = src[a.hiA[k]];
+            }
+            __syncthreads();
+            TO*  dst = B + lowB;
+            auto out = [&](TI v) -> TO {
+                if constexpr(PLAIN)
+                    return convertOut<TO, TI>(v);
+                else
+                    return convertOut<TO, TI>(Elem<TI>::apply(v, a.alpha, a.opA, a.opB));
+            };
+            if(inside)
+            {
+#pragma unroll
+                for(uint32_t k0 = 0; k0 < kBoxRounds; k0 += 8)
+                    if(k0 < rounds)
+                    {
+#pragma unroll
+                        for(uint32_t j = 0; j < 8; j++)
+                            if(mine && k0 + j < rounds)
+                                dst[a.hiB[k0 + j]] = out(box[boxSlot(lowI + a.hiS[k0 + j])]);
+                    }
+            }
+            else
+            {
+                for(uint32_t k = 0; k < rounds; k++)
+                {
+                    const uint32_t i = lowI + a.hiS[k];
+                    if(mine && valid(i))
+                        dst[a.hiB[k]] = out(box[boxSlot(i)]);
+                }
+            }
+        }
+
         // ------------------------------------------------------------ 128 x 128 tile kernel for f16, 4 x 4 blocks
         // Every extent and stride involved is a multiple of 4 elements: a thread loads four rows of 8 bytes
         // (4 halves along p from rows q .. q+3), transposes the 4 x 4 block in registers (eight byte permutes) and
@@ -1053,8 +1213,121 @@ namespace htb
             return cudaGetLastError();
         }
 
+        // Box of the box kernel: A's leading modes until their tile extents multiply to 64, B's leading modes likewise,
+        // then more of A's modes until the box holds 2048 to 8192 elements. False when the grid would not fit.
         template <typename TI, typename TO>
-        cudaError_t launchPlain(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB,
+        bool launchBox(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB, cudaStream_t stream,
+                       cudaError_t* err)
+        {
+            auto lgCeil = [](int64_t v) {
+                int l = 0;
+                while((int64_t(1) << l) < v)
+                    l++;
+                return l;
+            };
+            int lg[kMaxGroup] = {0, 0, 0, 0, 0, 0};
+            // A's run
+            for(int d = 0, need = 6; d < p.ndim && need > 0; d++)
+            {
+                const int l = std::min(lgCeil(p.ext[d]), need);
+                lg[d]       = std::max(lg[d], l);
+                need -= l;
+            }
+            // B's run
+            for(int i = 0, need = 6; i < p.ndim && need > 0; i++)
+            {
+                const int d = p.orderB[i], l = std::min(lgCeil(p.ext[d]), need);
+                lg[d]       = std::max(lg[d], l);
+                need -= l;
+            }
+            int total = 0;
+            for(int d = 0; d < p.ndim; d++)
+                total += lg[d];
+            // grow along A's order up to the target size
+            // larger boxes amortise a block's set-up (2.9 TB/s with 8192 elements of two bytes against 1.7 with 2048);
+            // smaller ones keep at least eight blocks per SM on tensors of a few million elements
+            int64_t count = 1;
+            for(int d = 0; d < p.ndim; d++)
+                count *= p.ext[d];
+            int target = 11;
+            while(target < kBoxBits && (count >> (target + 1)) >= 8 * 148)
+                target++;
+            for(int d = 0; d < p.ndim && total < target; d++)
+                while(total < target && lg[d] < lgCeil(p.ext[d]))
+                {
+                    lg[d]++;
+                    total++;
+                }
+            if(total > kBoxBits)
+                return false;
+            PermBoxArgs a{};
+            int64_t     grid = 1;
+            for(int d = 0; d < p.ndim; d++)
+            {
+                if(lg[d] > 0)
+                {
+                    const int k = a.nb++;
+                    a.lgA[k]    = lg[d];
+                    a.extA[k]   = uint32_t(p.ext[d]);
+                    a.sAofA[k]  = p.sA[d];
+                    a.sBofA[k]  = p.sB[d];
+                    a.tilesOf[k] = uint32_t((p.ext[d] + (int64_t(1) << lg[d]) - 1) >> lg[d]);
+                    grid *= a.tilesOf[k];
+                }
+                else
+                {
+                    const int k = a.no++;
+                    a.extO[k]   = uint32_t(p.ext[d]);
+                    a.sAO[k]    = p.sA[d];
+                    a.sBO[k]    = p.sB[d];
+                    grid *= p.ext[d];
+                }
+                if(p.ext[d] >= (int64_t(1) << 31) || grid > 0x7fffffffll)
+                    return false;
+            }
+            // weights of the index bits: A's order follows the folded modes, B's order their ascending stride in B
+            int shiftOf[kMaxGroup], bit = 0;
+            for(int d = 0; d < p.ndim; d++)
+            {
+                shiftOf[d] = bit;
+                for(int k = 0; k < lg[d]; k++, bit++)
+                    a.wA[bit] = p.sA[d] << k;
+            }
+            bit = 0;
+            for(int i = 0; i < p.ndim; i++)
+            {
+                const int d = p.orderB[i];
+                for(int k = 0; k < lg[d]; k++, bit++)
+                {
+                    a.wB[bit]    = p.sB[d] << k;
+                    a.slotB[bit] = 1u << (shiftOf[d] + k);
+                }
+            }
+            for(int r = 0; r < kBoxRounds; r++)
+                for(int k = 8; k < kBoxBits; k++)
+                    if((r >> (k - 8)) & 1)
+                    {
+                        a.hiA[r] += a.wA[k];
+                        a.hiB[r] += a.wB[k];
+                        a.hiS[r] += a.slotB[k];
+                    }
+            a.lgBox = total;
+            a.alpha = alpha;
+            a.opA   = opA;
+            a.opB   = opB;
+            const size_t smem = (size_t(1) << total) * sizeof(TI);
+            if(alpha == 1.0f && opA != 2 && opB != 2)
+                perm_box_kernel<TI, TO, true><<<unsigned(grid), 256, smem, stream>>>((const TI*)A, (TO*)B, a);
+            else
+                perm_box_kernel<TI, TO, false><<<unsigned(grid), 256, smem, stream>>>((const TI*)A, (TO*)B, a);
+            *err = cudaGetLastError();
+            if(*err == cudaSuccess)
+                noteLaunch("perm_box");
+            return true;
+        }
+
+        template <typename TI, typename TO>
+        cudaError_t launchPlain(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB, bool preferBox,
                                 cudaStream_t stream)
         {
             PermArgs a{};
@@ -1069,6 +1342,17 @@ namespace htb
             a.alpha = alpha;
             a.opA   = opA;
             a.opB   = opB;
+            // short contiguous modes: a box over several modes instead of a (p, q) tile or a (mode 0, mode 1) tile
+            {
+                const bool shortTile = p.kind != PERM_COPY && p.ndim >= 2 && (preferBox || p.ext[0] < 32 || p.ext[p.q] < 32);
+                // copies: rows of at most 128 bytes, or rows of at most 1 KiB with very few of them per tile
+                const bool shortCopy = p.kind == PERM_COPY && p.ndim >= 2
+                                       && (p.ext[0] * int64_t(sizeof(TI)) <= 128
+                                           || (p.ndim >= 3 && p.ext[1] <= 8 && p.ext[0] * int64_t(sizeof(TI)) <= 1024));
+                cudaError_t e;
+                if((shortTile || shortCopy) && launchBox<TI, TO>(p, A, B, alpha, opA, opB, stream, &e))
+                    return e;
+            }
             if(p.kind == PERM_COPY)
             {
                 // widest vector that keeps every access aligned
@@ -1186,7 +1470,22 @@ namespace htb
     {
         if(plan.total == 0)
             return cudaSuccess;
+        // A TMA tile is 2E x 2E elements (E = 128 bytes of elements). A contiguous mode much shorter than that leaves it
+        // mostly empty unless the kernel can merge the mode with its neighbour (launchTma); at a quarter full or less the box
+        // kernel is faster (4.8 TB/s against 2.0 to 2.3 on 4-byte elements, 2.9 against 2.2 to 2.4 on 2-byte ones).
+        bool sparseTiles = false;
         if(plan.kind == PERM_TMA)
+        {
+            const int64_t side = 2 * (128 / std::max(plan.elemSize, 1));
+            const bool    pow2P = (plan.ext[0] & (plan.ext[0] - 1)) == 0, pow2Q = (plan.ext[plan.q] & (plan.ext[plan.q] - 1)) == 0;
+            const bool    rank34 = plan.ndim >= 3 && plan.ndim <= 4;
+            const bool    mergeP = rank34 && pow2P && plan.q != 1;
+            const bool    mergeQ = rank34 && pow2Q && plan.orderB[0] == plan.q && plan.orderB[1] != 0;
+            const double  fillP = mergeP ? 1.0 : double(std::min(plan.ext[0], side)) / double(side);
+            const double  fillQ = mergeQ ? 1.0 : double(std::min(plan.ext[plan.q], side)) / double(side);
+            sparseTiles         = fillP * fillQ <= 0.25;
+        }
+        if(plan.kind == PERM_TMA && !sparseTiles)
         {
             // tile shape: long runs on the store side (rows of the output tile are 32*NQ... wide)
             PermTune tune;
@@ -1232,9 +1531,9 @@ namespace htb
             cudaGetLastError();
         }
         if(typeA == CUDA_R_32F)
-            return launchPlain<float, float>(plan, A, B, alpha, opA, opB, stream);
+            return launchPlain<float, float>(plan, A, B, alpha, opA, opB, sparseTiles, stream);
         if(typeB == CUDA_R_16F)
-            return launchPlain<__half, __half>(plan, A, B, alpha, opA, opB, stream);
-        return launchPlain<__half, float>(plan, A, B, alpha, opA, opB, stream);
+            return launchPlain<__half, __half>(plan, A, B, alpha, opA, opB, sparseTiles, stream);
+        return launchPlain<__half, float>(plan, A, B, alpha, opA, opB, sparseTiles, stream);
     }
 } // namespace htb

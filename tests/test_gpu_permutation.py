@@ -139,6 +139,23 @@ def test_tma_short_contiguous_input_mode(env, typeA, lens, perm):
     assert np.array_equal(bits(got), bits(exp)), (lens, perm, ht.last_kernel_name())
 
 
+@pytest.mark.parametrize("typeA,typeB", [(orc.F16, orc.F16), (orc.F16, orc.F32), (orc.F32, orc.F32)])
+@pytest.mark.parametrize("lens,perm", [([4, 128, 64, 6], [1, 2, 3, 0]), ([6, 24, 40, 12], [3, 2, 1, 0]),
+                                       ([2, 6, 130, 66], [0, 1, 3, 2]), ([2, 2, 2, 2, 2, 2], [5, 4, 3, 2, 1, 0]),
+                                       ([3, 5, 67, 31], [2, 0, 3, 1]), ([16, 32, 24, 20], [1, 0, 2, 3]),
+                                       ([6, 1000], [1, 0]), ([5, 3, 7, 129], [3, 1, 0, 2])])
+@pytest.mark.parametrize("alpha,ops", [(1.0, (orc.OP_IDENTITY, orc.OP_IDENTITY)), (0.5, (orc.OP_SQRT, orc.OP_SQRT))])
+def test_box_kernel_short_contiguous_modes(env, typeA, typeB, lens, perm, alpha, ops):
+    """Contiguous modes of a few elements on either side (input, output or both, odd extents included): one block moves
+    a box of up to 2048 elements that spans several leading modes of A and of B."""
+    ht, h = env
+    modes = list(range(len(lens)))
+    got, exp = run_permutation(ht, h, lens, modes, [modes[i] for i in perm], typeA=typeA, typeB=typeB, alpha=alpha,
+                               type_scalar=typeA, opA=ops[0], opB=ops[1])
+    assert ht.last_kernel_name() == "perm_box"
+    assert np.array_equal(bits(got), bits(exp))
+
+
 @pytest.mark.parametrize("rank", [2, 3, 5, 6])
 def test_other_ranks(env, rank):
     ht, h = env
