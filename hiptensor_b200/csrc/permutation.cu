@@ -379,16 +379,45 @@ namespace htb
             return i ^ (((i >> 5) ^ (i >> 10)) & 31u);
         }
 
-        template <typename TI, typename TO, bool PLAIN>
-        __global__ void __launch_bounds__(256) perm_box_kernel(const TI* __restrict__ A, TO* __restrict__ B, PermBoxArgs a)
+        // A unit of the box kernel: PACK neighbouring elements of the contiguous mode moved as one word of 2 to 16 bytes
+        // (PACK > 1 only when that mode is the contiguous one of A and of B).
+        template <int BYTES>
+        struct BoxWord;
+        template <>
+        struct BoxWord<2>
         {
+            using type = unsigned short;
+        };
+        template <>
+        struct BoxWord<4>
+        {
+            using type = uint32_t;
+        };
+        template <>
+        struct BoxWord<8>
+        {
+            using type = uint2;
+        };
+        template <>
+        struct BoxWord<16>
+        {
+            using type = uint4;
+        };
+
+        template <typename TI, typename TO, int PACK, bool PLAIN>
+        __global__ void __launch_bounds__(256) perm_box_kernel(const void* __restrict__ Av, void* __restrict__ Bv, PermBoxArgs a)
+        {
+            using UI = typename BoxWord<sizeof(TI) * PACK>::type;
+            using UO = typename BoxWord<sizeof(TO) * PACK>::type;
+            const UI* A = reinterpret_cast<const UI*>(Av);
+            UO*       B = reinterpret_cast<UO*>(Bv);
             extern __shared__ __align__(16) unsigned char boxRaw[];
-            TI*      box = reinterpret_cast<TI*>(boxRaw);
+            UI*      box = reinterpret_cast<UI*>(boxRaw);
             // origin of the box and offsets of the other modes (32-bit divisions: the grid is below 2^31 blocks)
             uint32_t bid = blockIdx.x;
             uint32_t org[kBoxMaxDims];
             int64_t  offA = 0, offB = 0;
-            bool     inside = true;
+            uint32_t cut = 0; // box modes that the tensor's edge cuts in this block
 #pragma unroll
             for(int d = 0; d < kBoxMaxDims; d++)
             {
@@ -400,9 +429,11 @@ namespace htb
                     org[d] = t << a.lgA[d];
                     offA += int64_t(org[d]) * a.sAofA[d];
                     offB += int64_t(org[d]) * a.sBofA[d];
-                    inside = inside && org[d] + (1u << a.lgA[d]) <= a.extA[d];
+                    if(org[d] + (1u << a.lgA[d]) > a.extA[d])
+                        cut |= 1u << d;
                 }
             }
+            const bool inside = cut == 0;
             for(int d = 0; d < a.no; d++)
             {
                 const uint32_t c = bid % a.extO[d];
@@ -411,15 +442,40 @@ namespace htb
                 offB += int64_t(c) * a.sBO[d];
             }
             const uint32_t size = 1u << a.lgBox;
-            // an element of an edge box lies in the tensor when every coordinate does (index i in A's order)
-            auto valid = [&](uint32_t i) {
+            // An element of an edge box lies in the tensor when its coordinate in every cut mode does (index i in A's
+            // order). A cut mode whose index bits all belong to the part of the index that a thread keeps through a phase
+            // (fixed) is checked once per thread (ok); the others (rest) once per element. A short odd contiguous mode cuts
+            // EVERY box, and its bits are fixed in both phases.
+            auto splitChecks = [&](uint32_t fixed, uint32_t part, bool& ok, uint32_t& rest) {
+                ok     = true;
+                rest   = 0;
+                int sh = 0;
+#pragma unroll
+                for(int d = 0; d < kBoxMaxDims; d++)
+                    if(d < a.nb)
+                    {
+                        const uint32_t m = (1u << a.lgA[d]) - 1u;
+                        if((cut >> d) & 1u)
+                        {
+                            if(((m << sh) & ~fixed) == 0)
+                                ok = ok && org[d] + ((part >> sh) & m) < a.extA[d];
+                            else
+                                rest |= 1u << d;
+                        }
+                        sh += a.lgA[d];
+                    }
+            };
+            auto valid = [&](uint32_t i, uint32_t rest) {
+                if(rest == 0)
+                    return true;
                 bool ok = true;
                 int  sh = 0;
 #pragma unroll
                 for(int d = 0; d < kBoxMaxDims; d++)
                     if(d < a.nb)
                     {
-                        ok = ok && org[d] + ((i >> sh) & ((1u << a.lgA[d]) - 1u)) < a.extA[d];
+                        if((rest >> d) & 1u)
+                            ok = ok && org[d] + ((i >> sh) & ((1u << a.lgA[d]) - 1u)) < a.extA[d];
                         sh += a.lgA[d];
                     }
                 return ok;
@@ -429,18 +485,21 @@ namespace htb
             // no load instruction competes with the element moves).
             const uint32_t t = threadIdx.x;
             int64_t  lowA = offA, lowB = offB;
-            uint32_t lowI = 0;
+            uint32_t lowI = 0, fixedB = 0;
 #pragma unroll
             for(int k = 0; k < 8; k++)
+            {
+                fixedB |= a.slotB[k];
                 if((t >> k) & 1u)
                 {
                     lowA += a.wA[k];
                     lowB += a.wB[k];
                     lowI += a.slotB[k];
                 }
+            }
             const uint32_t rounds = max(size >> 8, 1u);
             const bool     mine   = t < size; // boxes of fewer than 256 elements
-            const TI*      src    = A + lowA;
+            const UI*      src    = A + lowA;
             if(inside)
             {
                 // eight loads in flight per thread: with elements of two or four bytes the bytes in flight bound the rate
@@ -448,7 +507,7 @@ namespace htb
                 for(uint32_t k0 = 0; k0 < kBoxRounds; k0 += 8)
                     if(k0 < rounds)
                     {
-                        TI v[8];
+                        UI v[8];
 #pragma unroll
                         for(uint32_t j = 0; j < 8; j++)
                             if(mine && k0 + j < rounds)
@@ -461,17 +520,57 @@ namespace htb
             }
             else
             {
-                for(uint32_t k = 0; k < rounds; k++)
-                    if(mine && valid(t | (k << 8)))
-                        box[boxSlot(t | (k << 8))] = src[a.hiA[k]];
+                bool     ok;
+                uint32_t rest;
+                splitChecks(0xffu, t, ok, rest);
+                ok = ok && mine;
+#pragma unroll
+                for(uint32_t k0 = 0; k0 < kBoxRounds; k0 += 8)
+                    if(k0 < rounds)
+                    {
+                        UI   v[8];
+                        bool in[8];
+#pragma unroll
+                        for(uint32_t j = 0; j < 8; j++)
+                        {
+                            in[j] = ok && k0 + j < rounds && valid(t | ((k0 + j) << 8), rest);
+                            if(in[j])
+                                v[j] = src[a.hiA[k0 + j]];
+                        }
+#pragma unroll
+                        for(uint32_t j = 0; j < 8; j++)
+                            if(in[j])
+                                box[boxSlot(t | ((k0 + j) << 8))] = v[j];
+                    }
             }
             __syncthreads();
-            TO*  dst = B + lowB;
-            auto out = [&](TI v) -> TO {
-                if constexpr(PLAIN)
-                    return convertOut<TO, TI>(v);
+            UO*  dst = B + lowB;
+            auto out = [&](UI u) -> UO {
+                if constexpr(PLAIN && sizeof(TI) == sizeof(TO))
+                    return u;
                 else
-                    return convertOut<TO, TI>(Elem<TI>::apply(v, a.alpha, a.opA, a.opB));
+                {
+                    union
+                    {
+                        UI w;
+                        TI e[PACK];
+                    } in;
+                    union
+                    {
+                        UO w;
+                        TO e[PACK];
+                    } res;
+                    in.w = u;
+#pragma unroll
+                    for(int e = 0; e < PACK; e++)
+                    {
+                        if constexpr(PLAIN)
+                            res.e[e] = convertOut<TO, TI>(in.e[e]);
+                        else
+                            res.e[e] = convertOut<TO, TI>(Elem<TI>::apply(in.e[e], a.alpha, a.opA, a.opB));
+                    }
+                    return res.w;
+                }
             };
             if(inside)
             {
@@ -487,12 +586,22 @@ namespace htb
             }
             else
             {
-                for(uint32_t k = 0; k < rounds; k++)
-                {
-                    const uint32_t i = lowI + a.hiS[k];
-                    if(mine && valid(i))
-                        dst[a.hiB[k]] = out(box[boxSlot(i)]);
-                }
+                bool     ok;
+                uint32_t rest;
+                splitChecks(fixedB, lowI, ok, rest);
+                ok = ok && mine;
+#pragma unroll
+                for(uint32_t k0 = 0; k0 < kBoxRounds; k0 += 8)
+                    if(k0 < rounds)
+                    {
+#pragma unroll
+                        for(uint32_t j = 0; j < 8; j++)
+                        {
+                            const uint32_t i = lowI + a.hiS[k0 + j];
+                            if(ok && k0 + j < rounds && valid(i, rest))
+                                dst[a.hiB[k0 + j]] = out(box[boxSlot(i)]);
+                        }
+                    }
             }
         }
 
@@ -1215,9 +1324,9 @@ namespace htb
 
         // Box of the box kernel: A's leading modes until their tile extents multiply to 64, B's leading modes likewise,
         // then more of A's modes until the box holds 2048 to 8192 elements. False when the grid would not fit.
-        template <typename TI, typename TO>
-        bool launchBox(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB, cudaStream_t stream,
-                       cudaError_t* err)
+        template <typename TI, typename TO, int PACK>
+        bool launchBoxPacked(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB, cudaStream_t stream,
+                             cudaError_t* err)
         {
             auto lgCeil = [](int64_t v) {
                 int l = 0;
@@ -1225,16 +1334,22 @@ namespace htb
                     l++;
                 return l;
             };
+            if constexpr(PACK * sizeof(TI) > 16 || PACK * sizeof(TO) > 16)
+                return false;
+            else
+            {
             int lg[kMaxGroup] = {0, 0, 0, 0, 0, 0};
             // A's run
-            for(int d = 0, need = 6; d < p.ndim && need > 0; d++)
+            // 64 elements of 2 or 4 bytes; packed words need fewer for the same bytes
+            constexpr int runBits = PACK >= 8 ? 3 : PACK == 4 ? 4 : PACK == 2 ? 5 : 6;
+            for(int d = 0, need = runBits; d < p.ndim && need > 0; d++)
             {
                 const int l = std::min(lgCeil(p.ext[d]), need);
                 lg[d]       = std::max(lg[d], l);
                 need -= l;
             }
             // B's run
-            for(int i = 0, need = 6; i < p.ndim && need > 0; i++)
+            for(int i = 0, need = runBits; i < p.ndim && need > 0; i++)
             {
                 const int d = p.orderB[i], l = std::min(lgCeil(p.ext[d]), need);
                 lg[d]       = std::max(lg[d], l);
@@ -1250,7 +1365,7 @@ namespace htb
             for(int d = 0; d < p.ndim; d++)
                 count *= p.ext[d];
             int target = 11;
-            while(target < kBoxBits && (count >> (target + 1)) >= 8 * 148)
+            while(target < kBoxBits && (count >> (target + 1)) >= 8 * 148 && (sizeof(TI) * PACK << (target + 1)) <= 32768)
                 target++;
             for(int d = 0; d < p.ndim && total < target; d++)
                 while(total < target && lg[d] < lgCeil(p.ext[d]))
@@ -1258,7 +1373,7 @@ namespace htb
                     lg[d]++;
                     total++;
                 }
-            if(total > kBoxBits)
+            if(total > kBoxBits || (sizeof(TI) * PACK << total) > 48 * 1024)
                 return false;
             PermBoxArgs a{};
             int64_t     grid = 1;
@@ -1315,16 +1430,57 @@ namespace htb
             a.alpha = alpha;
             a.opA   = opA;
             a.opB   = opB;
-            const size_t smem = (size_t(1) << total) * sizeof(TI);
+            const size_t smem = (size_t(1) << total) * sizeof(TI) * PACK;
             if(alpha == 1.0f && opA != 2 && opB != 2)
-                perm_box_kernel<TI, TO, true><<<unsigned(grid), 256, smem, stream>>>((const TI*)A, (TO*)B, a);
+                perm_box_kernel<TI, TO, PACK, true><<<unsigned(grid), 256, smem, stream>>>(A, B, a);
             else
-                perm_box_kernel<TI, TO, false><<<unsigned(grid), 256, smem, stream>>>((const TI*)A, (TO*)B, a);
+                perm_box_kernel<TI, TO, PACK, false><<<unsigned(grid), 256, smem, stream>>>(A, B, a);
             *err = cudaGetLastError();
             if(*err == cudaSuccess)
                 noteLaunch("perm_box");
             return true;
+            }
         }
+
+        // Picks the word the box kernel moves and launches it.
+        template <typename TI, typename TO>
+        bool launchBox(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB, cudaStream_t stream,
+                       cudaError_t* err)
+        {
+            // Rows shared by A and B move as words of up to 16 bytes: the same permutation of fewer, larger elements.
+            int pack = 1;
+            if(p.kind == PERM_COPY && p.sA[0] == 1 && p.sB[0] == 1)
+            {
+                constexpr int wide = int(sizeof(TI) > sizeof(TO) ? sizeof(TI) : sizeof(TO));
+                for(int c = 16 / wide; c > 1 && pack == 1; c /= 2)
+                {
+                    bool ok = p.ext[0] % c == 0 && (uintptr_t)A % (c * sizeof(TI)) == 0 && (uintptr_t)B % (c * sizeof(TO)) == 0;
+                    for(int d = 1; d < p.ndim; d++)
+                        ok = ok && p.sA[d] % c == 0 && p.sB[d] % c == 0;
+                    if(ok)
+                        pack = c;
+                }
+            }
+            if(pack > 1)
+            {
+                PermPlan w = p;
+                w.kind     = PERM_TILE; // not packed again
+                w.ext[0] /= pack;
+                for(int d = 1; d < w.ndim; d++)
+                {
+                    w.sA[d] /= pack;
+                    w.sB[d] /= pack;
+                }
+                switch(pack)
+                {
+                case 2: return launchBoxPacked<TI, TO, 2>(w, A, B, alpha, opA, opB, stream, err);
+                case 4: return launchBoxPacked<TI, TO, 4>(w, A, B, alpha, opA, opB, stream, err);
+                default: return launchBoxPacked<TI, TO, 8>(w, A, B, alpha, opA, opB, stream, err);
+                }
+            }
+            return launchBoxPacked<TI, TO, 1>(p, A, B, alpha, opA, opB, stream, err);
+        }
+
 
         template <typename TI, typename TO>
         cudaError_t launchPlain(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB, bool preferBox,
@@ -1345,9 +1501,10 @@ namespace htb
             // short contiguous modes: a box over several modes instead of a (p, q) tile or a (mode 0, mode 1) tile
             {
                 const bool shortTile = p.kind != PERM_COPY && p.ndim >= 2 && (preferBox || p.ext[0] < 32 || p.ext[p.q] < 32);
-                // copies: rows of at most 128 bytes, or rows of at most 1 KiB with very few of them per tile
+                // copies: rows of at most 128 bytes, of 256 or 512 (a power of two of 16-byte words), or rows of at most 1 KiB with very few of them per tile
                 const bool shortCopy = p.kind == PERM_COPY && p.ndim >= 2
                                        && (p.ext[0] * int64_t(sizeof(TI)) <= 128
+                                           || p.ext[0] * int64_t(sizeof(TI)) == 256 || p.ext[0] * int64_t(sizeof(TI)) == 512
                                            || (p.ndim >= 3 && p.ext[1] <= 8 && p.ext[0] * int64_t(sizeof(TI)) <= 1024));
                 cudaError_t e;
                 if((shortTile || shortCopy) && launchBox<TI, TO>(p, A, B, alpha, opA, opB, stream, &e))

@@ -156,6 +156,43 @@ def test_box_kernel_short_contiguous_modes(env, typeA, typeB, lens, perm, alpha,
     assert np.array_equal(bits(got), bits(exp))
 
 
+@pytest.mark.parametrize("typeA,typeB", [(orc.F16, orc.F16), (orc.F16, orc.F32), (orc.F32, orc.F32)])
+@pytest.mark.parametrize("lens", [[8, 6, 130, 66], [16, 3, 67, 31], [32, 33, 65, 9], [12, 6, 130, 66], [6, 6, 130, 66]])
+@pytest.mark.parametrize("alpha", [1.0, 0.5])
+def test_box_kernel_short_rows_move_as_words(env, typeA, typeB, lens, alpha):
+    """Rows of at most 128 bytes shared by A and B: the box kernel moves them as words of 4 to 16 bytes."""
+    ht, h = env
+    for perm in ([0, 2, 1, 3], [0, 3, 2, 1], [0, 3, 1, 2]):
+        got, exp = run_permutation(ht, h, lens, [0, 1, 2, 3], perm, typeA=typeA, typeB=typeB, alpha=alpha,
+                                   type_scalar=typeA)
+        if lens[0] * (2 if typeA == orc.F16 else 4) <= 128:
+            assert ht.last_kernel_name() == "perm_box"
+        assert np.array_equal(bits(got), bits(exp)), (lens, perm)
+
+
+@pytest.mark.parametrize("offA,offB", [(1, 0), (0, 1), (2, 2), (4, 0)])
+def test_box_kernel_words_respect_pointer_alignment(env, offA, offB):
+    """The same short rows from pointers that are aligned to an element only: narrower words, same result."""
+    import torch
+
+    ht, h = env
+    lens, perm = [8, 5, 67, 33], [0, 2, 1, 3]
+    n = int(np.prod(lens))
+    A = orc.fill_uniform(n, orc.F16, 77)
+    exp = np.zeros(n, dtype=np.float16)
+    orc.permutation(1.0, orc.F16, A, lens, [0, 1, 2, 3], orc.F16, exp, perm, orc.F16, nthreads=0)
+    A_d = torch.zeros(n + 8, dtype=torch.float16, device="cuda")
+    A_d[offA:offA + n] = torch.from_numpy(A).cuda()
+    B_d = torch.zeros(n + 8, dtype=torch.float16, device="cuda")
+    dA = h.tensor_descriptor(lens, None, ht.R_16F)
+    dB = h.tensor_descriptor([lens[i] for i in perm], None, ht.R_16F)
+    h.permutation(1.0, A_d[offA:], dA, [0, 1, 2, 3], B_d[offB:], dB, perm, ht.R_16F)
+    assert ht.last_kernel_name() == "perm_box"
+    got = B_d.cpu().numpy()
+    assert np.array_equal(bits(got[offB:offB + n]), bits(exp))
+    assert not got[:offB].any() and not got[offB + n:].any()
+
+
 @pytest.mark.parametrize("rank", [2, 3, 5, 6])
 def test_other_ranks(env, rank):
     ht, h = env
