@@ -368,6 +368,10 @@ namespace htb
             // the same sums for every value of the index bits above the low eight (a thread's elements differ in those)
             int64_t  hiA[kBoxRounds], hiB[kBoxRounds];
             uint32_t hiS[kBoxRounds];
+            // pairs kernel only: position (A's order) of the lowest index bit of B's contiguous mode, and its weight in A
+            // in 4-byte words
+            int      betaBit;
+            int64_t  betaW;
             float    alpha;
             int      opA, opB;
         };
@@ -1322,11 +1326,141 @@ namespace htb
             return cudaGetLastError();
         }
 
+        // The box kernel for f16 transpositions with even contiguous extents: a thread loads two 4-byte words (two
+        // neighbours along A's contiguous mode, at two neighbouring coordinates of B's contiguous mode), exchanges their
+        // halves and keeps two words that are pairs along B's contiguous mode, so shared memory and the stores to B move 4-byte
+        // words as well: half the load/store instructions per element of the element-wise kernel. Index spaces, all in
+        // A's order: element index i (lgBox bits); word index j = i without bit betaBit (what shared memory holds); unit
+        // index u = j without bit 0 (what a thread loads: 2 x 2 elements).
+        template <bool PLAIN>
+        __global__ void __launch_bounds__(256) perm_box_pairs_kernel(const uint32_t* __restrict__ A, uint32_t* __restrict__ B, PermBoxArgs a)
+        {
+            extern __shared__ __align__(16) unsigned char boxRaw[];
+            uint32_t* box = reinterpret_cast<uint32_t*>(boxRaw);
+            uint32_t  bid = blockIdx.x;
+            uint32_t  org[kBoxMaxDims];
+            int64_t   offA = 0, offB = 0;
+            uint32_t  cut = 0;
+#pragma unroll
+            for(int d = 0; d < kBoxMaxDims; d++)
+            {
+                org[d] = 0;
+                if(d < a.nb)
+                {
+                    const uint32_t t = bid % a.tilesOf[d];
+                    bid /= a.tilesOf[d];
+                    org[d] = t << a.lgA[d];
+                    offA += int64_t(org[d]) * a.sAofA[d];
+                    offB += int64_t(org[d]) * a.sBofA[d];
+                    if(org[d] + (1u << a.lgA[d]) > a.extA[d])
+                        cut |= 1u << d;
+                }
+            }
+            for(int d = 0; d < a.no; d++)
+            {
+                const uint32_t c = bid % a.extO[d];
+                bid /= a.extO[d];
+                offA += int64_t(c) * a.sAO[d];
+                offB += int64_t(c) * a.sBO[d];
+            }
+            // the element offsets are even: every stride but the contiguous one is, and the contiguous extents are
+            const uint32_t words = 1u << (a.lgBox - 1), units = words >> 1;
+            const uint32_t t = threadIdx.x;
+            // both elements of a pair are inside the tensor or outside (even extents): one check per word
+            auto valid = [&](uint32_t j) {
+                if(cut == 0)
+                    return true;
+                const uint32_t m  = (1u << a.betaBit) - 1u;
+                const uint32_t i  = (j & m) | ((j & ~m) << 1);
+                bool           ok = true;
+                int            sh = 0;
+#pragma unroll
+                for(int d = 0; d < kBoxMaxDims; d++)
+                    if(d < a.nb)
+                    {
+                        if((cut >> d) & 1u)
+                            ok = ok && org[d] + ((i >> sh) & ((1u << a.lgA[d]) - 1u)) < a.extA[d];
+                        sh += a.lgA[d];
+                    }
+                return ok;
+            };
+            // slot of word j: bit 0 stays (a thread stores two neighbouring words at once), bits 1-4 are mixed with the
+            // bits above them against bank conflicts of the strided reads
+            auto slot = [](uint32_t j) { return j ^ (((j >> 5) ^ (j >> 10)) & 30u); };
+            int64_t  lowA = offA >> 1, lowB = offB >> 1;
+            uint32_t lowJ = 0;
+#pragma unroll
+            for(int k = 0; k < 8; k++)
+                if((t >> k) & 1u)
+                {
+                    lowA += a.wA[k];
+                    lowB += a.wB[k];
+                    lowJ += a.slotB[k];
+                }
+            const uint32_t  loadRounds = max(units >> 8, 1u), storeRounds = max(words >> 8, 1u);
+            const uint32_t* src = A + lowA;
+#pragma unroll
+            for(uint32_t k0 = 0; k0 < kBoxRounds / 4; k0 += 8)
+                if(k0 < loadRounds)
+                {
+                    uint32_t w0[8], w1[8];
+                    bool     in[8];
+#pragma unroll
+                    for(uint32_t n = 0; n < 8; n++)
+                    {
+                        in[n] = t < units && k0 + n < loadRounds && valid((t | ((k0 + n) << 8)) << 1);
+                        if(in[n])
+                        {
+                            w0[n] = src[a.hiA[k0 + n]];
+                            w1[n] = src[a.hiA[k0 + n] + a.betaW];
+                        }
+                    }
+#pragma unroll
+                    for(uint32_t n = 0; n < 8; n++)
+                        if(in[n])
+                        {
+                            const uint32_t j = (t | ((k0 + n) << 8)) << 1;
+                            *reinterpret_cast<uint2*>(box + slot(j))
+                                = make_uint2(__byte_perm(w0[n], w1[n], 0x5410), __byte_perm(w0[n], w1[n], 0x7632));
+                        }
+                }
+            __syncthreads();
+            uint32_t* dst = B + lowB;
+            auto      out = [&](uint32_t w) -> uint32_t {
+                if constexpr(PLAIN)
+                    return w;
+                else
+                {
+                    union
+                    {
+                        uint32_t w;
+                        __half   e[2];
+                    } v;
+                    v.w    = w;
+                    v.e[0] = Elem<__half>::apply(v.e[0], a.alpha, a.opA, a.opB);
+                    v.e[1] = Elem<__half>::apply(v.e[1], a.alpha, a.opA, a.opB);
+                    return v.w;
+                }
+            };
+#pragma unroll
+            for(uint32_t k0 = 0; k0 < kBoxRounds / 2; k0 += 8)
+                if(k0 < storeRounds)
+                {
+#pragma unroll
+                    for(uint32_t n = 0; n < 8; n++)
+                    {
+                        const uint32_t j = lowJ + a.hiS[k0 + n];
+                        if(t < words && k0 + n < storeRounds && valid(j))
+                            dst[a.hiB[k0 + n]] = out(box[slot(j)]);
+                    }
+                }
+        }
+
         // Box of the box kernel: A's leading modes until their tile extents multiply to 64, B's leading modes likewise,
         // then more of A's modes until the box holds 2048 to 8192 elements. False when the grid would not fit.
         template <typename TI, typename TO, int PACK>
-        bool launchBoxPacked(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB, cudaStream_t stream,
-                             cudaError_t* err)
+        bool launchBoxPacked(const PermPlan& p, const void* A, void* B, float alpha, int opA, int opB, bool pairs,
+                             cudaStream_t stream, cudaError_t* err)
         {
             auto lgCeil = [](int64_t v) {
                 int l = 0;
@@ -1418,6 +1552,31 @@ namespace htb
                     a.slotB[bit] = 1u << (shiftOf[d] + k);
                 }
             }
+            if(pairs)
+            {
+                // from element indices to unit indices (loads) and word indices (shared memory, stores); weights in words
+                const int beta = shiftOf[p.q];
+                int64_t   wA2[kBoxBits] = {}, wB2[kBoxBits] = {};
+                uint32_t  s2[kBoxBits] = {};
+                for(int k = 0; k + 2 < total; k++)
+                    wA2[k] = a.wA[k + 1 < beta ? k + 1 : k + 2] / 2;
+                for(int k = 0; k + 1 < total; k++)
+                {
+                    int pos = 0;
+                    while((a.slotB[k + 1] >> pos) != 1u)
+                        pos++;
+                    s2[k]  = 1u << (pos < beta ? pos : pos - 1);
+                    wB2[k] = a.wB[k + 1] / 2;
+                }
+                a.betaBit = beta;
+                a.betaW   = a.wA[beta] / 2;
+                for(int k = 0; k < kBoxBits; k++)
+                {
+                    a.wA[k]    = wA2[k];
+                    a.wB[k]    = wB2[k];
+                    a.slotB[k] = s2[k];
+                }
+            }
             for(int r = 0; r < kBoxRounds; r++)
                 for(int k = 8; k < kBoxBits; k++)
                     if((r >> (k - 8)) & 1)
@@ -1431,7 +1590,14 @@ namespace htb
             a.opA   = opA;
             a.opB   = opB;
             const size_t smem = (size_t(1) << total) * sizeof(TI) * PACK;
-            if(alpha == 1.0f && opA != 2 && opB != 2)
+            if(pairs)
+            {
+                if(alpha == 1.0f && opA != 2 && opB != 2)
+                    perm_box_pairs_kernel<true><<<unsigned(grid), 256, smem, stream>>>((const uint32_t*)A, (uint32_t*)B, a);
+                else
+                    perm_box_pairs_kernel<false><<<unsigned(grid), 256, smem, stream>>>((const uint32_t*)A, (uint32_t*)B, a);
+            }
+            else if(alpha == 1.0f && opA != 2 && opB != 2)
                 perm_box_kernel<TI, TO, PACK, true><<<unsigned(grid), 256, smem, stream>>>(A, B, a);
             else
                 perm_box_kernel<TI, TO, PACK, false><<<unsigned(grid), 256, smem, stream>>>(A, B, a);
@@ -1473,12 +1639,21 @@ namespace htb
                 }
                 switch(pack)
                 {
-                case 2: return launchBoxPacked<TI, TO, 2>(w, A, B, alpha, opA, opB, stream, err);
-                case 4: return launchBoxPacked<TI, TO, 4>(w, A, B, alpha, opA, opB, stream, err);
-                default: return launchBoxPacked<TI, TO, 8>(w, A, B, alpha, opA, opB, stream, err);
+                case 2: return launchBoxPacked<TI, TO, 2>(w, A, B, alpha, opA, opB, false, stream, err);
+                case 4: return launchBoxPacked<TI, TO, 4>(w, A, B, alpha, opA, opB, false, stream, err);
+                default: return launchBoxPacked<TI, TO, 8>(w, A, B, alpha, opA, opB, false, stream, err);
                 }
             }
-            return launchBoxPacked<TI, TO, 1>(p, A, B, alpha, opA, opB, stream, err);
+            // f16 transpositions whose contiguous extents and other strides are even: 2 x 2 elements per thread
+            bool pairs = false;
+            if constexpr(std::is_same<TI, __half>::value && std::is_same<TO, __half>::value)
+            {
+                pairs = p.kind != PERM_COPY && p.q != 0 && p.orderB[0] == p.q && p.sA[0] == 1 && p.sB[p.q] == 1 && p.ext[0] % 2 == 0
+                        && p.ext[p.q] % 2 == 0 && (uintptr_t)A % 4 == 0 && (uintptr_t)B % 4 == 0;
+                for(int d = 0; d < p.ndim; d++)
+                    pairs = pairs && (d == 0 || p.sA[d] % 2 == 0) && (d == p.q || p.sB[d] % 2 == 0);
+            }
+            return launchBoxPacked<TI, TO, 1>(p, A, B, alpha, opA, opB, pairs, stream, err);
         }
 
 
