@@ -612,7 +612,13 @@ int htb::reductionNoAlloc(const hiptensorHandle_t* handle, const void* alpha, co
     if(rc != PLAN_OK)
         return rc;
     const int internalCompute = (typeCompute == HIPTENSOR_COMPUTE_64F) ? HIPTENSOR_COMPUTE_64F : HIPTENSOR_COMPUTE_32F;
-    const uint64_t need = reductionWorkspaceBytes(plan, internalCompute);
+    uint64_t need = reductionWorkspaceBytes(plan, internalCompute);
+    if(need > kStaticScratchBytes && plan.splitOptional)
+    {
+        // the slices would only fill the GPU better: one pass without scratch
+        plan.split = 1;
+        need       = 0;
+    }
     if(need > kStaticScratchBytes)
     {
         HTB_LOG_ERROR(fn, "this reduction needs %llu bytes of scratch, the built-in scratch holds %llu: use "

@@ -364,14 +364,76 @@ namespace htb
             }
             out->vec = v;
         }
+        // A short contiguous reduced row: one load per lane covers it; 1 to 16 lanes per output instead of a warp.
+        out->shortLanes = 0;
+        out->shortVec   = 1;
+        if(out->kind == RED_ROW)
+        {
+            const int full = 16 / elemSize;
+            const int v    = out->vec == full ? full : (full >= 4 && out->vec >= full / 2 ? full / 2 : 1);
+            const int64_t loads = (out->rext[0] + v - 1) / v;
+            if(loads <= 16)
+            {
+                int g = 1;
+                while(g < loads)
+                    g <<= 1;
+                out->shortLanes = g;
+                out->shortVec   = v;
+            }
+        }
         // Few outputs and a long reduction: cut the reduced range into slices so that the
         // whole GPU works on it (two passes through a scratch buffer).
-        out->split = 1;
-        if(smCount > 0 && out->nOut < int64_t(smCount) * 4 && out->nRed >= 16384)
+        out->split         = 1;
+        out->splitOptional = 0;
+        // A contiguous kept mode: threads along the outputs (16-byte loads when extents, strides and pointers allow), the
+        // rest of the block along the innermost reduced mode. Few outputs leave few blocks: slices make up for them.
+        out->colVec = out->colTx = out->colTy = 1;
+        if(out->kind == RED_COL)
+        {
+            const int full = 16 / elemSize;
+            bool      vecOk = full > 1 && pointersAligned16 && out->ksA[0] == 1 && out->kext[0] % full == 0;
+            for(int d = 1; d < nk && vecOk; d++)
+                vecOk = out->ksA[d] % full == 0;
+            for(int d = 0; d < nr && vecOk; d++)
+                vecOk = out->rsA[d] % full == 0;
+            out->colVec         = vecOk ? full : 1;
+            const int64_t units = out->nOut / out->colVec;
+            int           tx    = 1;
+            while(tx < (vecOk ? 32 : 128) && tx < units)
+                tx <<= 1;
+            int ty = 256 / tx;
+            while(ty > 1 && ty > out->rext[0])
+                ty >>= 1;
+            out->colTx = tx;
+            out->colTy = ty;
+            const int64_t blocks = (units + tx - 1) / tx;
+            if(smCount > 0 && blocks < int64_t(smCount) * 2)
+            {
+                const int64_t want  = (int64_t(smCount) * 4 + blocks - 1) / blocks;
+                const int64_t maxBy = out->nRed / (int64_t(ty) * 16); // sixteen loads per thread at least
+                out->split          = int(std::max<int64_t>(1, std::min<int64_t>(std::min(want, maxBy), 1024)));
+                out->splitOptional  = out->split > 1 && out->nOut >= int64_t(smCount) * 4;
+            }
+        }
+        else if(smCount > 0 && out->nOut < int64_t(smCount) * 4 && out->nRed >= 16384 && out->shortLanes == 0)
         {
             int64_t want  = (int64_t(smCount) * 8 + out->nOut - 1) / out->nOut;
             int64_t maxBy = out->nRed / 4096;
             out->split    = int(std::max<int64_t>(1, std::min<int64_t>(std::min(want, maxBy), 1024)));
+        }
+        // The short-row kernel has few lanes per output and needs many outputs to fill the GPU; with fewer, slices of
+        // the outer reduced modes supply the threads.
+        if(smCount > 0 && out->split == 1 && out->shortLanes > 0)
+        {
+            const int64_t lanes   = out->shortLanes;
+            const int64_t threads = out->nOut * lanes;
+            const int64_t outer   = out->rext[0] > 0 ? out->nRed / out->rext[0] : 1; // outer reduced iterations
+            if(threads < int64_t(smCount) * 1024 && outer >= 64)
+            {
+                const int64_t want = (int64_t(smCount) * 2048 + threads - 1) / threads;
+                out->split         = int(std::max<int64_t>(1, std::min<int64_t>(std::min(want, outer / 16), 1024)));
+                out->splitOptional = out->split > 1;
+            }
         }
         return PLAN_OK;
     }

@@ -69,6 +69,14 @@ namespace htb
         int64_t rext[kMaxGroup], rsA[kMaxGroup];
         int64_t nOut, nRed;
         int     split; // >1: the reduced range is cut into this many slices (two-pass, needs scratch)
+        // Short contiguous reduced rows (RED_ROW with at most 16 loads of shortVec elements per row): lanes per output of
+        // the short-row kernel (1, 2, 4, 8 or 16), else 0.
+        int     shortLanes, shortVec;
+        // RED_COL: outputs per thread along the contiguous kept mode (16-byte loads, or 1) and the block shape: colTx
+        // threads over the outputs, colTy over the innermost reduced mode (colTx * colTy <= 256).
+        int     colVec, colTx, colTy;
+        // 1: the split only fills the GPU better; a caller without enough scratch runs the single pass instead
+        int     splitOptional;
     };
 
     int planReduction(int rankA, const int64_t* lensA, const int64_t* stridesA, const int32_t* modeA, int rankD,

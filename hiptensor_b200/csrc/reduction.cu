@@ -346,29 +346,112 @@ namespace htb
             }
         }
 
+        // ------------------------------------------------------------ short-row kernel
+        // Contiguous reduced rows of at most 16 vector loads: g lanes per output (g = 1, 2, 4, 8 or 16, a launch
+        // argument), one load per lane per row, so neighbouring lanes read neighbouring rows and a warp's load covers
+        // 32 / g outputs. With further reduced modes a group walks them like an odometer (no division per row), four
+        // rows in flight. gridDim.y = split (slices of the outer reduced index).
+        template <typename TIn, typename TAcc, int OP, int VEC>
+        __global__ void __launch_bounds__(256)
+            red_short_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
+                             TAcc alpha, TAcc beta, int g)
+        {
+            const int     lane = threadIdx.x & (g - 1), sub = threadIdx.x / g;
+            const int64_t o    = int64_t(blockIdx.x) * (256 / g) + sub;
+            const bool    idle = o >= a.nOut; // stays for the shuffles
+            const int64_t L0 = a.rext[0], RO = a.nRed / L0;
+            int64_t       roLo = 0, roHi = RO;
+            if(a.split > 1)
+            {
+                roLo = int64_t(blockIdx.y) * a.sliceLen;
+                roHi = min(RO, roLo + a.sliceLen);
+            }
+            const bool has = !idle && int64_t(lane) * VEC < L0;
+            int64_t    offA, offD;
+            keptOffsets(a, idle ? 0 : o, offA, offD);
+            // coordinates of the outer reduced modes at roLo
+            int64_t c[kMaxGroup], off = 0;
+            {
+                int64_t r = roLo;
+                for(int d = 1; d < a.nr; d++)
+                {
+                    c[d] = r % a.rext[d];
+                    r /= a.rext[d];
+                    off += c[d] * a.rsA[d];
+                }
+            }
+            auto next = [&]() {
+                for(int d = 1; d < a.nr; d++)
+                {
+                    off += a.rsA[d];
+                    if(++c[d] < a.rext[d])
+                        return;
+                    off -= a.rext[d] * a.rsA[d];
+                    c[d] = 0;
+                }
+            };
+            using V        = Vec<TIn, VEC>;
+            const TIn* row = A + offA + int64_t(lane) * VEC;
+            Accum<TAcc, OP> accum;
+            accum.init();
+            if(has)
+            {
+                int64_t ro = roLo;
+                for(; ro + 3 < roHi; ro += 4)
+                {
+                    const int64_t o0 = off;
+                    next();
+                    const int64_t o1 = off;
+                    next();
+                    const int64_t o2 = off;
+                    next();
+                    const int64_t o3 = off;
+                    next();
+                    const V v0 = *reinterpret_cast<const V*>(row + o0);
+                    const V v1 = *reinterpret_cast<const V*>(row + o1);
+                    const V v2 = *reinterpret_cast<const V*>(row + o2);
+                    const V v3 = *reinterpret_cast<const V*>(row + o3);
+#pragma unroll
+                    for(int e = 0; e < VEC; e++)
+                        accum.add4(widen<TAcc, TIn>(v0.v[e]), widen<TAcc, TIn>(v1.v[e]), widen<TAcc, TIn>(v2.v[e]),
+                                   widen<TAcc, TIn>(v3.v[e]));
+                }
+                for(; ro < roHi; ro++)
+                {
+                    const V v0 = *reinterpret_cast<const V*>(row + off);
+                    next();
+#pragma unroll
+                    for(int e = 0; e < VEC; e++)
+                        accum.add1(widen<TAcc, TIn>(v0.v[e]));
+                }
+            }
+            using Top = typename Accum<TAcc, OP>::Top;
+            Top acc   = accum.result();
+            for(int s = g >> 1; s > 0; s >>= 1)
+                acc = Op<Top, OP>::combine(acc, __shfl_xor_sync(0xffffffffu, acc, s));
+            if(lane == 0 && !idle)
+            {
+                if(a.split > 1)
+                    partial[int64_t(blockIdx.y) * a.nOut + o] = TAcc(acc);
+                else
+                    epilogue<TIn, TAcc>(TAcc(acc), alpha, beta, C, D, offD);
+            }
+        }
+
         // ------------------------------------------------------------ column kernel
-        // blockDim = (TX, TY); gridDim.x = ceil(kext0/TX) * (other kept modes); gridDim.y = split
+        // blockDim = (TX, TY); x runs over the flattened outputs (kept modes by ascending stride in A, so that lanes stay
+        // on neighbouring addresses across a short contiguous kept mode too); gridDim.x = ceil(nOut / TX); gridDim.y = split
         template <typename TIn, typename TAcc, int OP>
         __global__ void __launch_bounds__(256)
             red_col_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
-                           TAcc alpha, TAcc beta, int tiles0)
+                           TAcc alpha, TAcc beta)
         {
             __shared__ double smemRaw[256];
             const int       tx = threadIdx.x, ty = threadIdx.y, TX = blockDim.x, TY = blockDim.y;
-            int64_t         bid  = blockIdx.x;
-            const int64_t   i0   = (bid % tiles0) * TX + tx;
-            int64_t         rest = bid / tiles0;
-            const bool      ok   = i0 < a.kext[0];
-            int64_t         offA = i0 * a.ksA[0], offD = i0 * a.ksD[0], o = i0, mul = a.kext[0];
-            for(int d = 1; d < a.nk; d++)
-            {
-                int64_t c = rest % a.kext[d];
-                rest /= a.kext[d];
-                offA += c * a.ksA[d];
-                offD += c * a.ksD[d];
-                o += c * mul;
-                mul *= a.kext[d];
-            }
+            const int64_t   o  = int64_t(blockIdx.x) * TX + tx;
+            const bool      ok = o < a.nOut;
+            int64_t         offA, offD;
+            keptOffsets(a, ok ? o : 0, offA, offD);
             const int64_t L0 = a.rext[0], RO = a.nRed / L0, s0 = a.rsA[0];
             int64_t       roLo = 0, roHi = RO, iLo = 0, iHi = L0;
             if(a.split > 1)
@@ -409,10 +492,18 @@ namespace htb
             Top  acc           = accum.result();
             smem[ty * TX + tx] = acc;
             __syncthreads();
+            // TY is a power of two
+            for(int h = TY >> 1; h > 0; h >>= 1)
+            {
+                if(ty < h)
+                {
+                    acc                = Op<Top, OP>::combine(acc, smem[(ty + h) * TX + tx]);
+                    smem[ty * TX + tx] = acc;
+                }
+                __syncthreads();
+            }
             if(ty == 0 && ok)
             {
-                for(int y = 1; y < TY; y++)
-                    acc = Op<Top, OP>::combine(acc, smem[y * TX + tx]);
                 if(a.split > 1)
                     partial[int64_t(blockIdx.y) * a.nOut + o] = TAcc(acc);
                 else
@@ -427,26 +518,17 @@ namespace htb
         template <typename TIn, typename TAcc, int OP, int VEC>
         __global__ void __launch_bounds__(256)
             red_colv_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
-                            TAcc alpha, TAcc beta, int tiles0)
+                            TAcc alpha, TAcc beta)
         {
             using Top = typename Accum<TAcc, OP>::Top;
             extern __shared__ __align__(16) unsigned char smemDyn[];
             Top*          smem = (Top*)smemDyn; // [TY][TX][VEC]
             const int     tx = threadIdx.x, ty = threadIdx.y, TX = blockDim.x, TY = blockDim.y;
-            int64_t       bid  = blockIdx.x;
-            const int64_t i0   = ((bid % tiles0) * TX + tx) * VEC;
-            int64_t       rest = bid / tiles0;
-            const bool    ok   = i0 < a.kext[0];
-            int64_t       offA = i0 * a.ksA[0], offD = i0 * a.ksD[0], o = i0, mul = a.kext[0];
-            for(int d = 1; d < a.nk; d++)
-            {
-                int64_t c = rest % a.kext[d];
-                rest /= a.kext[d];
-                offA += c * a.ksA[d];
-                offD += c * a.ksD[d];
-                o += c * mul;
-                mul *= a.kext[d];
-            }
+            // VEC neighbouring outputs of the contiguous kept mode (its extent is a multiple of VEC)
+            const int64_t o  = (int64_t(blockIdx.x) * TX + tx) * VEC;
+            const bool    ok = o < a.nOut;
+            int64_t       offA, offD;
+            keptOffsets(a, ok ? o : 0, offA, offD);
             const int64_t L0 = a.rext[0], RO = a.nRed / L0, s0 = a.rsA[0];
             int64_t       roLo = 0, roHi = RO, iLo = 0, iHi = L0;
             if(a.split > 1)
@@ -502,12 +584,21 @@ namespace htb
                 smem[(ty * TX + tx) * VEC + e] = acc[e];
             }
             __syncthreads();
-            if(ty == 0 && ok)
+            for(int h = TY >> 1; h > 0; h >>= 1)
             {
-                for(int y = 1; y < TY; y++)
+                if(ty < h)
+                {
 #pragma unroll
                     for(int e = 0; e < VEC; e++)
-                        acc[e] = Op<Top, OP>::combine(acc[e], smem[(y * TX + tx) * VEC + e]);
+                    {
+                        acc[e]                         = Op<Top, OP>::combine(acc[e], smem[((ty + h) * TX + tx) * VEC + e]);
+                        smem[(ty * TX + tx) * VEC + e] = acc[e];
+                    }
+                }
+                __syncthreads();
+            }
+            if(ty == 0 && ok)
+            {
 #pragma unroll
                 for(int e = 0; e < VEC; e++)
                 {
@@ -666,7 +757,23 @@ namespace htb
             const unsigned gy = unsigned(a.split);
             if(p.nOut > 0x7fffffffll)
                 return cudaErrorInvalidConfiguration;
-            if(p.kind == RED_ROW)
+            if(p.kind == RED_ROW && p.shortLanes > 0)
+            {
+                const int  g = p.shortLanes;
+                const dim3 grid(unsigned((p.nOut + 256 / g - 1) / (256 / g)), gy);
+                if(a.split > 1 && !a.sliceOuter)
+                    return cudaErrorInvalidConfiguration; // the planner slices the outer reduced index only
+                constexpr int full = 16 / int(sizeof(TIn));
+                if(p.shortVec == full)
+                    red_short_kernel<TIn, TAcc, OP, full><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, g);
+                else if(full >= 4 && p.shortVec == full / 2)
+                    red_short_kernel<TIn, TAcc, OP, (full >= 4 ? full / 2 : 1)>
+                        <<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, g);
+                else
+                    red_short_kernel<TIn, TAcc, OP, 1><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, g);
+                noteLaunch("red_short");
+            }
+            else if(p.kind == RED_ROW)
             {
                 const bool perBlock = (p.nRed >= 8192 && p.nOut < 4096) || a.split > 1;
                 if(perBlock)
@@ -697,47 +804,30 @@ namespace htb
             }
             else if(p.kind == RED_COL)
             {
-                // 16-byte loads along the kept mode when it, the other strides and the base address allow
+                // block shape and vector width come with the plan
                 constexpr int VEC = 16 / int(sizeof(TIn));
-                bool          vecOk = VEC > 1 && p.ksA[0] == 1 && p.kext[0] % VEC == 0 && (uintptr_t(A) & 15) == 0
-                             && p.kext[0] >= 32 * VEC;
-                for(int d = 1; d < p.nk && vecOk; d++)
-                    vecOk = p.ksA[d] % VEC == 0;
-                for(int d = 0; d < p.nr && vecOk; d++)
-                    vecOk = p.rsA[d] % VEC == 0;
-                if(vecOk)
+                const int     tx = p.colTx, ty = p.colTy;
+                if(p.colVec == VEC && VEC > 1 && (uintptr_t(A) & 15) == 0)
                 {
-                    const int tx = 32;
-                    int       ty = 8;
-                    while(ty > 1 && ty > L0)
-                        ty >>= 1;
-                    const int tiles0 = int((p.kext[0] / VEC + tx - 1) / tx);
-                    int64_t   blocks = tiles0;
-                    for(int d = 1; d < p.nk; d++)
-                        blocks *= p.kext[d];
+                    const int64_t blocks = (p.nOut / VEC + tx - 1) / tx;
                     if(blocks > 0x7fffffffll)
                         return cudaErrorInvalidConfiguration;
                     using Top         = typename Accum<TAcc, OP>::Top;
                     const size_t smem = size_t(tx) * ty * VEC * sizeof(Top);
                     red_colv_kernel<TIn, TAcc, OP, VEC>
-                        <<<dim3(unsigned(blocks), gy), dim3(tx, ty), smem, stream>>>(A, C, D, partial, a, alpha, beta, tiles0);
+                        <<<dim3(unsigned(blocks), gy), dim3(tx, ty), smem, stream>>>(A, C, D, partial, a, alpha, beta);
                 }
                 else
                 {
-                    int tx = 32;
-                    while(tx < 128 && tx < p.kext[0])
-                        tx <<= 1;
-                    int ty = 256 / tx;
-                    while(ty > 1 && ty > L0)
-                        ty >>= 1;
-                    const int tiles0 = int((p.kext[0] + tx - 1) / tx);
-                    int64_t   blocks = tiles0;
-                    for(int d = 1; d < p.nk; d++)
-                        blocks *= p.kext[d];
+                    // colTx counts vectors when the plan has them; without (a pointer the planner did not see) lanes are
+                    // single outputs
+                    const int     txs    = p.colVec > 1 ? 32 : tx;
+                    const int     tys    = p.colVec > 1 ? std::min(ty, 8) : ty;
+                    const int64_t blocks = (p.nOut + txs - 1) / txs;
                     if(blocks > 0x7fffffffll)
                         return cudaErrorInvalidConfiguration;
                     red_col_kernel<TIn, TAcc, OP>
-                        <<<dim3(unsigned(blocks), gy), dim3(tx, ty), 0, stream>>>(A, C, D, partial, a, alpha, beta, tiles0);
+                        <<<dim3(unsigned(blocks), gy), dim3(txs, tys), 0, stream>>>(A, C, D, partial, a, alpha, beta);
                 }
                 noteLaunch("red_col");
             }
