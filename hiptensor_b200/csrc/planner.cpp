@@ -364,18 +364,20 @@ namespace htb
             }
             out->vec = v;
         }
-        // A short contiguous reduced row: one load per lane covers it; 1 to 16 lanes per output instead of a warp.
+        // A short contiguous reduced row: one load per lane covers it, 1 to 32 lanes per output; up to 2 KiB a few loads.
         out->shortLanes = 0;
         out->shortVec   = 1;
         if(out->kind == RED_ROW)
         {
-            const int full = 16 / elemSize;
-            const int v    = out->vec == full ? full : (full >= 4 && out->vec >= full / 2 ? full / 2 : 1);
+            const int     v     = std::max(out->vec, 1); // a power of two up to 16 bytes
             const int64_t loads = (out->rext[0] + v - 1) / v;
-            if(loads <= 16)
+            // rows of up to 2 KiB with further reduced modes, or without full vectors, take a warp per output here too
+            // (several loads per lane); full vectors and no further reduced mode keep the row kernel's eight lanes
+            const bool medium = out->rext[0] * int64_t(elemSize) <= 2048 && !(v == 16 / elemSize && nr == 1);
+            if(loads <= 16 || medium)
             {
                 int g = 1;
-                while(g < loads)
+                while(g < loads && g < 32)
                     g <<= 1;
                 out->shortLanes = g;
                 out->shortVec   = v;
@@ -398,12 +400,21 @@ namespace htb
                 vecOk = out->rsA[d] % full == 0;
             out->colVec         = vecOk ? full : 1;
             const int64_t units = out->nOut / out->colVec;
-            int           tx    = 1;
-            while(tx < (vecOk ? 32 : 128) && tx < units)
+            // Lanes first along the contiguous kept run (kext[0]: neighbours were folded into it). When the innermost
+            // reduced mode follows that run without a gap, the next lanes go along it (neighbouring rows are
+            // neighbouring memory); what is left of the block takes further outputs.
+            const bool    rowsAdjacent = out->rsA[0] == out->kext[0];
+            int           tx           = 1;
+            while(tx < 256 && tx < (rowsAdjacent ? out->kext[0] / out->colVec : units))
                 tx <<= 1;
+            // lanes along the innermost reduced mode: what the outputs leave of the block, at most its extent, and at
+            // least eight loads per thread (a short reduction is cheaper without the exchange through shared memory)
+            // (four loads in flight per thread come from one pass over that mode: a quarter of its extent at most)
             int ty = 256 / tx;
-            while(ty > 1 && ty > out->rext[0])
+            while(ty > 1 && (ty * 4 > out->rext[0] || out->nRed / ty < 8))
                 ty >>= 1;
+            while(tx * ty < 256 && tx < units)
+                tx <<= 1;
             out->colTx = tx;
             out->colTy = ty;
             const int64_t blocks = (units + tx - 1) / tx;

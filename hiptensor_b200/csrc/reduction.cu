@@ -237,6 +237,20 @@ namespace htb
                 offD += c * a.ksD[d];
             }
         }
+        // the same with 32-bit divisions, for kernels launched only when the output count fits 31 bits
+        __device__ __forceinline__ void keptOffsets32(const RedArgs& a, int64_t o, int64_t& offA, int64_t& offD)
+        {
+            offA       = 0;
+            offD       = 0;
+            uint32_t r = uint32_t(o);
+            for(int d = 0; d < a.nk; d++)
+            {
+                const uint32_t e = uint32_t(a.kext[d]), q = r / e, c = r - q * e;
+                r = q;
+                offA += int64_t(c) * a.ksA[d];
+                offD += int64_t(c) * a.ksD[d];
+            }
+        }
         // offset of outer reduced index ro (reduced modes 1..nr-1)
         __device__ __forceinline__ int64_t outerRedOffset(const RedArgs& a, int64_t ro)
         {
@@ -347,9 +361,9 @@ namespace htb
         }
 
         // ------------------------------------------------------------ short-row kernel
-        // Contiguous reduced rows of at most 16 vector loads: g lanes per output (g = 1, 2, 4, 8 or 16, a launch
-        // argument), one load per lane per row, so neighbouring lanes read neighbouring rows and a warp's load covers
-        // 32 / g outputs. With further reduced modes a group walks them like an odometer (no division per row), four
+        // Contiguous reduced rows of at most 2 KiB: g lanes per output (g = 1, 2, 4, .. 32, a launch argument). Up to 32
+        // vector loads a row takes one load per lane, so neighbouring lanes read neighbouring rows and a warp's load
+        // covers 32 / g outputs; longer rows take several loads per lane. With further reduced modes a group walks them like an odometer (no division per row), four
         // rows in flight. gridDim.y = split (slices of the outer reduced index).
         template <typename TIn, typename TAcc, int OP, int VEC>
         __global__ void __launch_bounds__(256)
@@ -368,7 +382,7 @@ namespace htb
             }
             const bool has = !idle && int64_t(lane) * VEC < L0;
             int64_t    offA, offD;
-            keptOffsets(a, idle ? 0 : o, offA, offD);
+            keptOffsets32(a, idle ? 0 : o, offA, offD);
             // coordinates of the outer reduced modes at roLo
             int64_t c[kMaxGroup], off = 0;
             {
@@ -394,7 +408,48 @@ namespace htb
             const TIn* row = A + offA + int64_t(lane) * VEC;
             Accum<TAcc, OP> accum;
             accum.init();
-            if(has)
+            if(!idle && L0 > int64_t(g) * VEC)
+            {
+                // several loads per lane and row (rows of up to 2 KiB): four in flight within the row
+                const int64_t step = int64_t(g) * VEC;
+                for(int64_t ro = roLo; ro < roHi; ro++)
+                {
+                    const TIn* r = A + offA + off;
+                    next();
+                    // the loads of a batch are issued together, the last batch of a row with predicates
+                    for(int64_t i = int64_t(lane) * VEC; i < L0; i += 4 * step)
+                    {
+                        const bool p1 = i + step < L0, p2 = i + 2 * step < L0, p3 = i + 3 * step < L0;
+                        V          v0 = *reinterpret_cast<const V*>(r + i), v1, v2, v3;
+                        if(p1)
+                            v1 = *reinterpret_cast<const V*>(r + i + step);
+                        if(p2)
+                            v2 = *reinterpret_cast<const V*>(r + i + 2 * step);
+                        if(p3)
+                            v3 = *reinterpret_cast<const V*>(r + i + 3 * step);
+                        if(p3)
+                        {
+#pragma unroll
+                            for(int e = 0; e < VEC; e++)
+                                accum.add4(widen<TAcc, TIn>(v0.v[e]), widen<TAcc, TIn>(v1.v[e]), widen<TAcc, TIn>(v2.v[e]),
+                                           widen<TAcc, TIn>(v3.v[e]));
+                        }
+                        else
+                        {
+#pragma unroll
+                            for(int e = 0; e < VEC; e++)
+                            {
+                                accum.add1(widen<TAcc, TIn>(v0.v[e]));
+                                if(p1)
+                                    accum.add1(widen<TAcc, TIn>(v1.v[e]));
+                                if(p2)
+                                    accum.add1(widen<TAcc, TIn>(v2.v[e]));
+                            }
+                        }
+                    }
+                }
+            }
+            else if(has)
             {
                 int64_t ro = roLo;
                 for(; ro + 3 < roHi; ro += 4)
@@ -451,7 +506,7 @@ namespace htb
             const int64_t   o  = int64_t(blockIdx.x) * TX + tx;
             const bool      ok = o < a.nOut;
             int64_t         offA, offD;
-            keptOffsets(a, ok ? o : 0, offA, offD);
+            keptOffsets32(a, ok ? o : 0, offA, offD);
             const int64_t L0 = a.rext[0], RO = a.nRed / L0, s0 = a.rsA[0];
             int64_t       roLo = 0, roHi = RO, iLo = 0, iHi = L0;
             if(a.split > 1)
@@ -528,7 +583,7 @@ namespace htb
             const int64_t o  = (int64_t(blockIdx.x) * TX + tx) * VEC;
             const bool    ok = o < a.nOut;
             int64_t       offA, offD;
-            keptOffsets(a, ok ? o : 0, offA, offD);
+            keptOffsets32(a, ok ? o : 0, offA, offD);
             const int64_t L0 = a.rext[0], RO = a.nRed / L0, s0 = a.rsA[0];
             int64_t       roLo = 0, roHi = RO, iLo = 0, iHi = L0;
             if(a.split > 1)
@@ -769,8 +824,13 @@ namespace htb
                 else if(full >= 4 && p.shortVec == full / 2)
                     red_short_kernel<TIn, TAcc, OP, (full >= 4 ? full / 2 : 1)>
                         <<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, g);
-                else
+                else if(full >= 8 && p.shortVec == full / 4)
+                    red_short_kernel<TIn, TAcc, OP, (full >= 8 ? full / 4 : 1)>
+                        <<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, g);
+                else if(p.shortVec == 1)
                     red_short_kernel<TIn, TAcc, OP, 1><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, g);
+                else
+                    return cudaErrorInvalidConfiguration;
                 noteLaunch("red_short");
             }
             else if(p.kind == RED_ROW)
