@@ -103,6 +103,77 @@ def test_short_rows_eight_lanes_per_output(env, op, dt, lens):
         assert 0 <= rel_error(got, exp, dt) < max(terms * float(eps), 1e-6)
 
 
+EPS = {orc.F32: float(np.finfo(np.float32).eps), orc.F16: float(np.finfo(np.float16).eps),
+       orc.F64: float(np.finfo(np.float64).eps), orc.BF16: 2.0 ** -8}
+
+
+def check_reduction(got, exp, dt, op, terms):
+    if op in (orc.OP_MAX, orc.OP_MIN):
+        assert np.array_equal(bits(got), bits(exp))
+    else:
+        assert 0 <= rel_error(got, exp, dt) < max(terms * EPS[dt], 1e-6)
+
+
+@pytest.mark.parametrize("op", [orc.OP_ADD, orc.OP_MAX])
+@pytest.mark.parametrize("dt", [orc.F32, orc.F16, orc.F64, orc.BF16])
+@pytest.mark.parametrize("row", [2, 3, 4, 8, 12, 24, 33, 64, 130])
+def test_short_contiguous_rows(env, op, dt, row):
+    """Contiguous reduced rows of 2 to 130 elements, alone and under a further reduced mode: 1 to 32 lanes per output
+    (one load per lane up to 16 loads a row, several beyond), neighbouring lanes on neighbouring rows. The output
+    count is not a multiple of the outputs per block."""
+    ht, h = env
+    # last mode contiguous: [kept 37][kept 5][row]
+    got, exp = run_reduction(ht, h, [37, 5, row], [0, 1, 2], [0, 1], dt=dt, op=op, alpha=1.5, beta=0.5)
+    size = {orc.F32: 4, orc.F16: 2, orc.F64: 8, orc.BF16: 2}[dt]
+    # rows of more than 16 full 16-byte loads and no further reduced mode stay on the row kernel's eight lanes
+    assert ht.last_kernel_name() == ("red_short" if row * size <= 256 or row * size % 16 else "red_row")
+    check_reduction(got, exp, dt, op, row)
+    # [reduced 9][kept 21][kept 3][row]: the outer reduced mode is walked without divisions
+    got, exp = run_reduction(ht, h, [9, 21, 3, row], [0, 1, 2, 3], [1, 2], dt=dt, op=op, alpha=-0.5, beta=2.0)
+    assert ht.last_kernel_name() == "red_short"
+    check_reduction(got, exp, dt, op, 9 * row)
+    # two outer reduced modes of odd extents around the kept ones
+    got, exp = run_reduction(ht, h, [7, 10, 5, 3, row], [0, 1, 2, 3, 4], [1, 3], dt=dt, op=op)
+    assert ht.last_kernel_name() == "red_short"
+    check_reduction(got, exp, dt, op, 35 * row)
+
+
+@pytest.mark.parametrize("op", [orc.OP_ADD, orc.OP_MIN])
+@pytest.mark.parametrize("dt", [orc.F32, orc.F16])
+@pytest.mark.parametrize("lens,kept", [([3000, 24, 4], [1]), ([5000, 3, 6], [1]), ([2048, 7, 16], [1]),
+                                       ([4096, 33, 130], [1])])
+def test_short_rows_few_outputs_are_sliced(env, op, dt, lens, kept):
+    """A few outputs with short rows and a long outer reduced mode: slices of the outer mode fill the GPU, a second
+    pass folds them; without a workspace one pass gives the same values within the bound."""
+    ht, h = env
+    got, exp = run_reduction(ht, h, lens, [0, 1, 2], kept, dt=dt, op=op, alpha=1.25, beta=0.75)
+    assert ht.last_kernel_name() == "red_finalize"
+    check_reduction(got, exp, dt, op, lens[0] * lens[2])
+    got, exp = run_reduction(ht, h, lens, [0, 1, 2], kept, dt=dt, op=op, alpha=1.25, beta=0.75, use_workspace=False)
+    assert ht.last_kernel_name() == "red_short"
+    check_reduction(got, exp, dt, op, lens[0] * lens[2])
+
+
+@pytest.mark.parametrize("op", [orc.OP_ADD, orc.OP_MAX])
+@pytest.mark.parametrize("dt", [orc.F32, orc.F16, orc.F64])
+@pytest.mark.parametrize("lens,kept", [([300, 40, 2], [1, 2]), ([300, 40, 4], [2]), ([64, 9, 50, 6], [1, 3]),
+                                       ([500, 16], [1]), ([12, 70, 3, 8], [1, 3]), ([8, 100, 100], [1, 2]),
+                                       ([40000, 8], [1])])
+def test_short_contiguous_kept_mode(env, op, dt, lens, kept):
+    """The contiguous mode is kept and short (2 to 16 elements): the column kernel's lanes run over the flattened outputs,
+    or along the rows of the innermost reduced mode when those follow the kept run without a gap; few outputs are
+    sliced."""
+    ht, h = env
+    modes = list(range(len(lens)))
+    got, exp = run_reduction(ht, h, lens, modes, kept, dt=dt, op=op, alpha=1.5, beta=0.5)
+    assert ht.last_kernel_name() in ("red_col", "red_finalize")
+    terms = int(np.prod([lens[i] for i in modes if i not in kept]))
+    check_reduction(got, exp, dt, op, terms)
+    got, exp = run_reduction(ht, h, lens, modes, kept, dt=dt, op=op, alpha=1.5, beta=0.5, use_workspace=False)
+    assert ht.last_kernel_name() == "red_col"
+    check_reduction(got, exp, dt, op, terms)
+
+
 def test_permuted_output_strides(env):
     """Output extents in A's order, permutation expressed by strides
     (test/03_reduction/reduction_test.cpp:334-372)."""

@@ -79,6 +79,37 @@ def test_reduction_config3_layouts(ht):
     assert "kind=col" in d and "keep=[262144:1/1]" in d and "red=[2048:262144]" in d
 
 
+def test_reduction_short_rows_and_short_kept_runs(ht):
+    """Lanes per output follow the length of the contiguous reduced row; few outputs get optional slices; a kept
+    contiguous mode decides the column kernel's block shape."""
+    def plan(lens, kept, dtype=None):
+        lD = [lens[i] for i in kept]
+        return ht.describe_reduction_plan(lens, packed(lens, False), list(range(len(lens))), lD, packed(lD, False), kept,
+                                          dtype if dtype is not None else ht.R_32F)
+
+    # rows of 4, 24 and 64 floats: 1, 8 and 16 lanes of 16-byte loads; 130 floats: 8-byte loads, eight per lane
+    assert "short=1x4" in plan([4096, 128, 4], [0, 1])
+    assert "short=8x4" in plan([4096, 128, 24], [0, 1])
+    assert "short=16x4" in plan([4096, 128, 64], [0, 1])
+    assert "short=16x2" in plan([4096, 128, 130], [0, 1])
+    # 1 KiB rows of full vectors: the row kernel alone, the short-row kernel under a further reduced mode
+    assert "short=" not in plan([4096, 128, 256], [0, 1])
+    assert "short=8x4" in plan([64, 4096, 256], [1])
+    # configuration 3 keeps its plan
+    d = plan([4096, 64, 64, 32], [0, 1])
+    assert "kind=row" in d and "short=" not in d and "split=1 " in d
+    # few outputs under a long outer mode: slices that a caller without scratch may drop
+    d = plan([3000, 24, 4], [1])
+    assert "short=1x4" in d and "optional-split" in d and int(re.search(r"split=(\d+)", d).group(1)) > 16
+    # kept contiguous mode: many outputs and a short reduction take all lanes on outputs and no exchange
+    assert "col=256x1 vec=4" in plan([8, 4096, 8192], [1, 2])
+    # a kept run of 32 floats followed by the rows of the reduced mode: lanes along those rows
+    d = plan([4096, 64, 64, 32], [3])
+    assert "col=8x32 vec=4" in d and int(re.search(r"split=(\d+)", d).group(1)) > 16
+    # a kept run below a sector: lanes over the flattened outputs
+    assert "col=256x1 vec=1" in plan([4096, 128, 128, 4], [1, 3], ht.R_16F)
+
+
 def test_reduction_split_and_errors(ht):
     lens = [3, 512, 1024]
     d = ht.describe_reduction_plan(lens, packed(lens, False), [0, 1, 2], [3], [1], [0])
