@@ -450,9 +450,17 @@ namespace htb
             // order). A cut mode whose index bits all belong to the part of the index that a thread keeps through a phase
             // (fixed) is checked once per thread (ok); the others (rest) once per element. A short odd contiguous mode cuts
             // EVERY box, and its bits are fixed in both phases.
-            auto splitChecks = [&](uint32_t fixed, uint32_t part, bool& ok, uint32_t& rest) {
+            // The first two of the others are kept as (shift, mask, room left above the thread's share of the coordinate):
+            // the share of an element's other index bits is the same for every thread, which leaves a shift, a mask and a
+            // compare per element and mode.
+            uint32_t sh0 = 0, m0 = 0, room0 = 1, sh1 = 0, m1 = 0, room1 = 1;
+            int      restN = 0;
+            auto     splitChecks = [&](uint32_t fixed, uint32_t part, bool& ok, uint32_t& rest) {
                 ok     = true;
                 rest   = 0;
+                restN  = 0;
+                sh0 = sh1 = m0 = m1 = 0;
+                room0 = room1 = 1;
                 int sh = 0;
 #pragma unroll
                 for(int d = 0; d < kBoxMaxDims; d++)
@@ -463,11 +471,35 @@ namespace htb
                         {
                             if(((m << sh) & ~fixed) == 0)
                                 ok = ok && org[d] + ((part >> sh) & m) < a.extA[d];
+                            else if(restN < 2)
+                            {
+                                // what the element's other bits may add to the thread's share of the coordinate
+                                const uint32_t mine = (part >> sh) & m, lim = a.extA[d] - org[d];
+                                ok = ok && mine < lim;
+                                if(restN == 0)
+                                {
+                                    sh0   = uint32_t(sh);
+                                    m0    = m;
+                                    room0 = lim - mine;
+                                }
+                                else
+                                {
+                                    sh1   = uint32_t(sh);
+                                    m1    = m;
+                                    room1 = lim - mine;
+                                }
+                                restN++;
+                            }
                             else
                                 rest |= 1u << d;
                         }
                         sh += a.lgA[d];
                     }
+            };
+            // others: the index bits of the element that the thread does not fix (disjoint from the thread's)
+            auto restOk = [&](uint32_t others) {
+                // (with no such mode the masks are zero and the rooms one)
+                return ((others >> sh0) & m0) < room0 && ((others >> sh1) & m1) < room1;
             };
             auto valid = [&](uint32_t i, uint32_t rest) {
                 if(rest == 0)
@@ -528,24 +560,37 @@ namespace htb
                 uint32_t rest;
                 splitChecks(0xffu, t, ok, rest);
                 ok = ok && mine;
-#pragma unroll
-                for(uint32_t k0 = 0; k0 < kBoxRounds; k0 += 8)
-                    if(k0 < rounds)
+                // (not unrolled over the batches: with the inside path the kernel would outgrow the instruction cache)
+                if(rest == 0)
+                {
+#pragma unroll 1
+                    for(uint32_t k0 = 0; k0 < rounds; k0 += 8)
                     {
-                        UI   v[8];
-                        bool in[8];
+                        // the table entry of k0 + j is the sum of those of k0 and j (disjoint bits): one indexed
+                        // constant load per batch, the rest are immediate operands
+                        const UI* base = src + a.hiA[k0];
+                        UI        v[8];
+                        bool      in[8];
 #pragma unroll
                         for(uint32_t j = 0; j < 8; j++)
                         {
-                            in[j] = ok && k0 + j < rounds && valid(t | ((k0 + j) << 8), rest);
+                            in[j] = ok && k0 + j < rounds && restOk((k0 + j) << 8);
                             if(in[j])
-                                v[j] = src[a.hiA[k0 + j]];
+                                v[j] = base[a.hiA[j]];
                         }
 #pragma unroll
                         for(uint32_t j = 0; j < 8; j++)
                             if(in[j])
                                 box[boxSlot(t | ((k0 + j) << 8))] = v[j];
                     }
+                }
+                else
+                {
+#pragma unroll 1
+                    for(uint32_t k = 0; k < rounds; k++)
+                        if(ok && restOk(k << 8) && valid(t | (k << 8), rest))
+                            box[boxSlot(t | (k << 8))] = src[a.hiA[k]];
+                }
             }
             __syncthreads();
             UO*  dst = B + lowB;
@@ -594,18 +639,32 @@ namespace htb
                 uint32_t rest;
                 splitChecks(fixedB, lowI, ok, rest);
                 ok = ok && mine;
-#pragma unroll
-                for(uint32_t k0 = 0; k0 < kBoxRounds; k0 += 8)
-                    if(k0 < rounds)
+                if(rest == 0)
+                {
+#pragma unroll 1
+                    for(uint32_t k0 = 0; k0 < rounds; k0 += 8)
                     {
+                        UO*            base = dst + a.hiB[k0];
+                        const uint32_t hs0  = a.hiS[k0];
 #pragma unroll
                         for(uint32_t j = 0; j < 8; j++)
                         {
-                            const uint32_t i = lowI + a.hiS[k0 + j];
-                            if(ok && k0 + j < rounds && valid(i, rest))
-                                dst[a.hiB[k0 + j]] = out(box[boxSlot(i)]);
+                            const uint32_t hs = hs0 + a.hiS[j];
+                            if(ok && k0 + j < rounds && restOk(hs))
+                                base[a.hiB[j]] = out(box[boxSlot(lowI + hs)]);
                         }
                     }
+                }
+                else
+                {
+#pragma unroll 1
+                    for(uint32_t k = 0; k < rounds; k++)
+                    {
+                        const uint32_t i = lowI + a.hiS[k];
+                        if(ok && restOk(a.hiS[k]) && valid(i, rest))
+                            dst[a.hiB[k]] = out(box[boxSlot(i)]);
+                    }
+                }
             }
         }
 
@@ -1366,19 +1425,68 @@ namespace htb
             // the element offsets are even: every stride but the contiguous one is, and the contiguous extents are
             const uint32_t words = 1u << (a.lgBox - 1), units = words >> 1;
             const uint32_t t = threadIdx.x;
-            // both elements of a pair are inside the tensor or outside (even extents): one check per word
-            auto valid = [&](uint32_t j) {
-                if(cut == 0)
-                    return true;
-                const uint32_t m  = (1u << a.betaBit) - 1u;
-                const uint32_t i  = (j & m) | ((j & ~m) << 1);
-                bool           ok = true;
-                int            sh = 0;
+            // Both elements of a pair are inside the tensor or outside (even extents): one check per word, on the element
+            // index with the pair's bit zero. Cut modes are split as in the element-wise kernel: those whose index bits
+            // the thread fixes for a phase are checked once, up to two others with an add and a compare per word.
+            const uint32_t bm     = (1u << a.betaBit) - 1u;
+            auto           expand = [&](uint32_t j) { return (j & bm) | ((j & ~bm) << 1); };
+            uint32_t       sh0 = 0, m0 = 0, room0 = 1, sh1 = 0, m1 = 0, room1 = 1;
+            int            restN       = 0;
+            auto           splitChecks = [&](uint32_t fixed, uint32_t part, bool& ok, uint32_t& rest) {
+                ok     = true;
+                rest   = 0;
+                restN  = 0;
+                sh0 = sh1 = m0 = m1 = 0;
+                room0 = room1 = 1;
+                int sh = 0;
 #pragma unroll
                 for(int d = 0; d < kBoxMaxDims; d++)
                     if(d < a.nb)
                     {
+                        const uint32_t m = (1u << a.lgA[d]) - 1u;
                         if((cut >> d) & 1u)
+                        {
+                            if(((m << sh) & ~fixed) == 0)
+                                ok = ok && org[d] + ((part >> sh) & m) < a.extA[d];
+                            else if(restN < 2)
+                            {
+                                // what the element's other bits may add to the thread's share of the coordinate
+                                const uint32_t mine = (part >> sh) & m, lim = a.extA[d] - org[d];
+                                ok = ok && mine < lim;
+                                if(restN == 0)
+                                {
+                                    sh0   = uint32_t(sh);
+                                    m0    = m;
+                                    room0 = lim - mine;
+                                }
+                                else
+                                {
+                                    sh1   = uint32_t(sh);
+                                    m1    = m;
+                                    room1 = lim - mine;
+                                }
+                                restN++;
+                            }
+                            else
+                                rest |= 1u << d;
+                        }
+                        sh += a.lgA[d];
+                    }
+            };
+            auto restOk = [&](uint32_t others) {
+                // (with no such mode the masks are zero and the rooms one)
+                return ((others >> sh0) & m0) < room0 && ((others >> sh1) & m1) < room1;
+            };
+            auto valid = [&](uint32_t i, uint32_t rest) {
+                if(rest == 0)
+                    return true;
+                bool ok = true;
+                int  sh = 0;
+#pragma unroll
+                for(int d = 0; d < kBoxMaxDims; d++)
+                    if(d < a.nb)
+                    {
+                        if((rest >> d) & 1u)
                             ok = ok && org[d] + ((i >> sh) & ((1u << a.lgA[d]) - 1u)) < a.extA[d];
                         sh += a.lgA[d];
                     }
@@ -1388,42 +1496,71 @@ namespace htb
             // bits above them against bank conflicts of the strided reads
             auto slot = [](uint32_t j) { return j ^ (((j >> 5) ^ (j >> 10)) & 30u); };
             int64_t  lowA = offA >> 1, lowB = offB >> 1;
-            uint32_t lowJ = 0;
+            uint32_t lowJ = 0, fixedJ = 0;
 #pragma unroll
             for(int k = 0; k < 8; k++)
+            {
+                fixedJ |= a.slotB[k];
                 if((t >> k) & 1u)
                 {
                     lowA += a.wA[k];
                     lowB += a.wB[k];
                     lowJ += a.slotB[k];
                 }
+            }
             const uint32_t  loadRounds = max(units >> 8, 1u), storeRounds = max(words >> 8, 1u);
             const uint32_t* src = A + lowA;
+            auto            put = [&](uint32_t r, uint32_t w0, uint32_t w1) {
+                const uint32_t j = (t | (r << 8)) << 1;
+                *reinterpret_cast<uint2*>(box + slot(j)) = make_uint2(__byte_perm(w0, w1, 0x5410), __byte_perm(w0, w1, 0x7632));
+            };
+            if(cut == 0)
+            {
 #pragma unroll
-            for(uint32_t k0 = 0; k0 < kBoxRounds / 4; k0 += 8)
-                if(k0 < loadRounds)
+                for(uint32_t k0 = 0; k0 < kBoxRounds / 4; k0 += 8)
+                    if(k0 < loadRounds)
+                    {
+                        uint32_t w0[8], w1[8];
+#pragma unroll
+                        for(uint32_t n = 0; n < 8; n++)
+                            if(t < units && k0 + n < loadRounds)
+                            {
+                                w0[n] = src[a.hiA[k0 + n]];
+                                w1[n] = src[a.hiA[k0 + n] + a.betaW];
+                            }
+#pragma unroll
+                        for(uint32_t n = 0; n < 8; n++)
+                            if(t < units && k0 + n < loadRounds)
+                                put(k0 + n, w0[n], w1[n]);
+                    }
+            }
+            else
+            {
+                bool     ok;
+                uint32_t rest;
+                splitChecks(expand(0x1ffu) | (1u << a.betaBit), expand(t << 1), ok, rest);
+                ok = ok && t < units;
                 {
+                    // at most eight rounds of loads (2048 units of 2 x 2 elements)
                     uint32_t w0[8], w1[8];
                     bool     in[8];
 #pragma unroll
                     for(uint32_t n = 0; n < 8; n++)
                     {
-                        in[n] = t < units && k0 + n < loadRounds && valid((t | ((k0 + n) << 8)) << 1);
+                        const uint32_t others = expand(n << 9);
+                        in[n] = ok && n < loadRounds && restOk(others) && valid(expand(t << 1) | others, rest);
                         if(in[n])
                         {
-                            w0[n] = src[a.hiA[k0 + n]];
-                            w1[n] = src[a.hiA[k0 + n] + a.betaW];
+                            w0[n] = src[a.hiA[n]];
+                            w1[n] = src[a.hiA[n] + a.betaW];
                         }
                     }
 #pragma unroll
                     for(uint32_t n = 0; n < 8; n++)
                         if(in[n])
-                        {
-                            const uint32_t j = (t | ((k0 + n) << 8)) << 1;
-                            *reinterpret_cast<uint2*>(box + slot(j))
-                                = make_uint2(__byte_perm(w0[n], w1[n], 0x5410), __byte_perm(w0[n], w1[n], 0x7632));
-                        }
+                            put(n, w0[n], w1[n]);
                 }
+            }
             __syncthreads();
             uint32_t* dst = B + lowB;
             auto      out = [&](uint32_t w) -> uint32_t {
@@ -1442,18 +1579,39 @@ namespace htb
                     return v.w;
                 }
             };
+            if(cut == 0)
+            {
 #pragma unroll
-            for(uint32_t k0 = 0; k0 < kBoxRounds / 2; k0 += 8)
-                if(k0 < storeRounds)
+                for(uint32_t k0 = 0; k0 < kBoxRounds / 2; k0 += 8)
+                    if(k0 < storeRounds)
+                    {
+#pragma unroll
+                        for(uint32_t n = 0; n < 8; n++)
+                            if(t < words && k0 + n < storeRounds)
+                                dst[a.hiB[k0 + n]] = out(box[slot(lowJ + a.hiS[k0 + n])]);
+                    }
+            }
+            else
+            {
+                bool     ok;
+                uint32_t rest;
+                splitChecks(expand(fixedJ) | (1u << a.betaBit), expand(lowJ), ok, rest);
+                ok = ok && t < words;
+#pragma unroll 1
+                for(uint32_t k0 = 0; k0 < storeRounds; k0 += 8)
                 {
+                    // the table entry of k0 + n is the sum of those of k0 and n (disjoint bits)
+                    uint32_t*      base = dst + a.hiB[k0];
+                    const uint32_t hs0  = a.hiS[k0];
 #pragma unroll
                     for(uint32_t n = 0; n < 8; n++)
                     {
-                        const uint32_t j = lowJ + a.hiS[k0 + n];
-                        if(t < words && k0 + n < storeRounds && valid(j))
-                            dst[a.hiB[k0 + n]] = out(box[slot(j)]);
+                        const uint32_t hs = hs0 + a.hiS[n], others = expand(hs);
+                        if(ok && k0 + n < storeRounds && restOk(others) && valid(expand(lowJ) | others, rest))
+                            base[a.hiB[n]] = out(box[slot(lowJ + hs)]);
                     }
                 }
+            }
         }
 
         // Box of the box kernel: A's leading modes until their tile extents multiply to 64, B's leading modes likewise,

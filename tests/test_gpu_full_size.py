@@ -88,6 +88,30 @@ def test_config2_full_size_against_the_oracle(env):
     assert np.array_equal(bits(got), bits(exp))
 
 
+def test_short_mode_permutation_above_l2(env):
+    """fp32 B[d,c,b,a] = A[a,b,c,d] with a contiguous mode of 6 elements on the input side (192 MiB in, 192 MiB out): the
+    box kernel, bit-exact against the oracle on the whole tensor."""
+    from helpers import run_permutation
+
+    ht, h = env
+    got, exp = run_permutation(ht, h, [512, 128, 128, 6], [0, 1, 2, 3], [3, 2, 1, 0])
+    assert ht.last_kernel_name() == "perm_box"
+    assert np.array_equal(bits(got), bits(exp))
+
+
+def test_short_row_reduction_above_l2(env):
+    """fp32 rows of 4 contiguous elements reduced under 2^24 outputs (256 MiB in, 64 MiB out): the short-row kernel, one
+    lane per output."""
+    ht, h = env
+    for op in (orc.OP_ADD, orc.OP_MAX):
+        got, exp = run_reduction(ht, h, [4096, 64, 64, 4], [0, 1, 2, 3], [0, 1, 2], op=op, alpha=1.0, beta=0.5)
+        assert ht.last_kernel_name() == "red_short"
+        if op == orc.OP_MAX:
+            assert np.array_equal(bits(got), bits(exp))
+        else:
+            assert 0 <= rel_error(got, exp, orc.F32) < 4 * float(np.finfo(np.float32).eps)
+
+
 # ---------------------------------------------------------------------------------------- slabs of an N-way split
 @pytest.mark.parametrize("m0_local", [8, 16, 32])
 def test_config4_slab(env, m0_local):
