@@ -409,7 +409,7 @@ namespace htb
         };
 
         template <typename TI, typename TO, int PACK, bool PLAIN>
-        __global__ void __launch_bounds__(256) perm_box_kernel(const void* __restrict__ Av, void* __restrict__ Bv, PermBoxArgs a)
+        __global__ void __launch_bounds__(256, 5) perm_box_kernel(const void* __restrict__ Av, void* __restrict__ Bv, PermBoxArgs a)
         {
             using UI = typename BoxWord<sizeof(TI) * PACK>::type;
             using UO = typename BoxWord<sizeof(TO) * PACK>::type;
