@@ -39,6 +39,7 @@ namespace htb
             int     split; // slices of the reduced range (1 = single pass)
             int     sliceOuter; // 1: slices cut the outer reduced index, 0: the innermost reduced mode
             int64_t sliceLen;
+            int64_t outer; // nRed / rext[0]: iterations over the outer reduced modes
         };
 
         enum
@@ -368,12 +369,13 @@ namespace htb
         template <typename TIn, typename TAcc, int OP, int VEC>
         __global__ void __launch_bounds__(256)
             red_short_kernel(const TIn* __restrict__ A, const TIn* C, TIn* D, TAcc* __restrict__ partial, RedArgs a,
-                             TAcc alpha, TAcc beta, int g)
+                             TAcc alpha, TAcc beta, int lgG)
         {
-            const int     lane = threadIdx.x & (g - 1), sub = threadIdx.x / g;
-            const int64_t o    = int64_t(blockIdx.x) * (256 / g) + sub;
+            // (a thread may own a single 16-byte load: no division on its way, 64-bit ones least of all)
+            const int     g = 1 << lgG, lane = threadIdx.x & (g - 1), sub = threadIdx.x >> lgG;
+            const int64_t o    = (int64_t(blockIdx.x) << (8 - lgG)) + sub;
             const bool    idle = o >= a.nOut; // stays for the shuffles
-            const int64_t L0 = a.rext[0], RO = a.nRed / L0;
+            const int64_t L0 = a.rext[0], RO = a.outer;
             int64_t       roLo = 0, roHi = RO;
             if(a.split > 1)
             {
@@ -385,6 +387,9 @@ namespace htb
             keptOffsets32(a, idle ? 0 : o, offA, offD);
             // coordinates of the outer reduced modes at roLo
             int64_t c[kMaxGroup], off = 0;
+            for(int d = 1; d < a.nr; d++)
+                c[d] = 0;
+            if(roLo != 0) // slices only
             {
                 int64_t r = roLo;
                 for(int d = 1; d < a.nr; d++)
@@ -789,6 +794,7 @@ namespace htb
             a.split = (workspace != nullptr) ? p.split : 1;
             TAcc*         partial = (TAcc*)workspace;
             const int64_t L0 = p.rext[0], RO = p.nRed / L0;
+            a.outer          = RO;
             if(a.split > 1)
             {
                 if(p.kind == RED_GENERIC)
@@ -814,21 +820,23 @@ namespace htb
                 return cudaErrorInvalidConfiguration;
             if(p.kind == RED_ROW && p.shortLanes > 0)
             {
-                const int  g = p.shortLanes;
+                int g = p.shortLanes, lgG = 0;
+                while((1 << lgG) < g)
+                    lgG++;
                 const dim3 grid(unsigned((p.nOut + 256 / g - 1) / (256 / g)), gy);
                 if(a.split > 1 && !a.sliceOuter)
                     return cudaErrorInvalidConfiguration; // the planner slices the outer reduced index only
                 constexpr int full = 16 / int(sizeof(TIn));
                 if(p.shortVec == full)
-                    red_short_kernel<TIn, TAcc, OP, full><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, g);
+                    red_short_kernel<TIn, TAcc, OP, full><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, lgG);
                 else if(full >= 4 && p.shortVec == full / 2)
                     red_short_kernel<TIn, TAcc, OP, (full >= 4 ? full / 2 : 1)>
-                        <<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, g);
+                        <<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, lgG);
                 else if(full >= 8 && p.shortVec == full / 4)
                     red_short_kernel<TIn, TAcc, OP, (full >= 8 ? full / 4 : 1)>
-                        <<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, g);
+                        <<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, lgG);
                 else if(p.shortVec == 1)
-                    red_short_kernel<TIn, TAcc, OP, 1><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, g);
+                    red_short_kernel<TIn, TAcc, OP, 1><<<grid, 256, 0, stream>>>(A, C, D, partial, a, alpha, beta, lgG);
                 else
                     return cudaErrorInvalidConfiguration;
                 noteLaunch("red_short");
