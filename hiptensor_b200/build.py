@@ -17,7 +17,8 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libhiptensor_b200.so")
 
 SOURCES = ["planner.cpp", "runtime.cpp", "api.cpp", "c_abi.cpp", "permutation.cu", "reduction.cu",
-           "contraction_tiled.cu", "contraction_tcgen05.cu", "contraction_tf32x3.cu", "contraction_complex.cu"]
+           "contraction_tiled.cu", "contraction_tcgen05.cu", "contraction_tf32x3.cu", "contraction_complex.cu",
+           "contraction_pack.cu"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",

@@ -143,7 +143,8 @@ namespace
         return r;
     }
 
-    int buildContractionPlan(const hiptensorContractionDescriptor_t* desc, int smCount, ContractionPlan* out)
+    int buildContractionPlan(const hiptensorContractionDescriptor_t* desc, int smCount, ContractionPlan* out,
+                             uint64_t workspaceLimit)
     {
         if(desc->mTensorDesc.size() != 4 || desc->mTensorMode.size() < 3)
             return HIPTENSOR_STATUS_INVALID_VALUE;
@@ -171,7 +172,7 @@ namespace
             return planComplexContraction(A, B, D, int(desc->mTensorDesc[2].mType), bilinear, int(desc->mComputeType),
                                           smCount, out);
         return planContraction(A, B, D, int(desc->mTensorDesc[2].mType), bilinear, int(desc->mComputeType), smCount,
-                               out);
+                               out, workspaceLimit);
     }
 } // namespace
 
@@ -782,7 +783,10 @@ hiptensorStatus_t hiptensorContractionGetWorkspaceSize(const hiptensorHandle_t* 
     // every real kernel runs without scratch (WORKSPACE_MIN = 0); the recommended size lets the
     // tensor-core kernels split tiles along K. Complex contractions need room for the expanded copy
     // of their smaller operand at every preference.
-    if(buildContractionPlan(desc, st ? st->smCount : 148, &plan) == HIPTENSOR_STATUS_SUCCESS)
+    // (Operands that the tensor-core kernels cannot read in place are copied into the workspace when there is one:
+    // the recommended size has room for the copies, the minimum stays 0 and leaves such problems on the FMA kernel.)
+    if(buildContractionPlan(desc, st ? st->smCount : 148, &plan, pref != HIPTENSOR_WORKSPACE_MIN ? ~uint64_t(0) : 0)
+       == HIPTENSOR_STATUS_SUCCESS)
         *workspaceSize = plan.expandBytes + (pref != HIPTENSOR_WORKSPACE_MIN ? plan.workspaceBytes : 0);
     return HIPTENSOR_STATUS_SUCCESS;
 }
@@ -807,7 +811,7 @@ hiptensorStatus_t hiptensorInitContractionPlan(const hiptensorHandle_t* handle, 
     if(auto s = checkDevice(fn, st); s != HIPTENSOR_STATUS_SUCCESS)
         return s;
     ContractionPlan cp;
-    int             rc = buildContractionPlan(desc, st->smCount, &cp);
+    int             rc = buildContractionPlan(desc, st->smCount, &cp, workspaceSize);
     if(rc != HIPTENSOR_STATUS_SUCCESS)
     {
         // the reference ends with EXECUTION_FAILED when no candidate survives its type
@@ -853,7 +857,7 @@ hiptensorStatus_t hiptensorContraction(const hiptensorHandle_t* handle, const hi
         // the registry has dropped this plan (more than kCapacity other plans were used since): plan again
         // from the descriptor the caller's plan carries
         ContractionPlan again;
-        if(buildContractionPlan(&plan->mContractionDesc, st->smCount, &again) == HIPTENSOR_STATUS_SUCCESS)
+        if(buildContractionPlan(&plan->mContractionDesc, st->smCount, &again, workspaceSize) == HIPTENSOR_STATUS_SUCCESS)
         {
             if(again.expandBytes + again.workspaceBytes > workspaceSize)
                 again.workspaceBytes = 0;
@@ -920,9 +924,12 @@ hiptensorStatus_t hiptensorContraction(const hiptensorHandle_t* handle, const hi
         readScalar(beta, cp->computeType, &betaD);
     }
     // scratch is used only up to what the plan was made for
-    cudaError_t e = launchContraction(*cp, float(alphaD), A, B, float(betaD), bilinear ? C : nullptr, D,
-                                      cp->workspaceBytes ? workspace : nullptr, cp->workspaceBytes, st->smCount,
-                                      st->deviceStatus, stream);
+    cudaError_t e = cp->packReal
+                        ? launchPackedContraction(*cp, float(alphaD), A, B, float(betaD), bilinear ? C : nullptr, D, workspace,
+                                                  needBytes, st->smCount, st->deviceStatus, stream)
+                        : launchContraction(*cp, float(alphaD), A, B, float(betaD), bilinear ? C : nullptr, D,
+                                            cp->workspaceBytes ? workspace : nullptr, cp->workspaceBytes, st->smCount,
+                                            st->deviceStatus, stream);
     if(e != cudaSuccess)
     {
         HTB_LOG_ERROR(fn, "kernel launch failed: %s (%s)", cudaGetErrorString(e),

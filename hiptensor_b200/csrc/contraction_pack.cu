@@ -1,0 +1,125 @@
+// Packed copies of the operands of a real contraction (plan.packReal).
+//
+// The tensor-core kernels read an operand through TMA: every stride but one must be a multiple of 16 bytes, and the
+// contracted modes must form a block mode both operands can be walked along. Operands that do not fit (extents of
+// 50 f16 elements, contracted modes interleaved with free ones in different orders, ...) used to run on the gathered
+// FMA kernel at 10-18 TFLOP/s whatever their size. From about a GFLOP on (planner.cpp, planContraction) each operand
+// is first copied into the caller's workspace as a matrix with one row per free index and the contracted modes
+// merged, in the same order for both operands, into one innermost mode padded with zeros to a multiple of 16 bytes;
+// the contraction of the copies runs on the tensor cores. The copies cost one pass over A and B (M K + N K elements
+// against M N K multiply-adds).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+
+#include "kernels.hpp"
+
+namespace htb
+{
+    namespace
+    {
+        struct PackDims
+        {
+            int      rank, nFree;
+            uint32_t ext[kMaxRank];
+            int64_t  stride[kMaxRank];
+        };
+
+        // One thread per element of the copy, the merged contracted index fastest: the writes are contiguous, the
+        // reads follow the source strides. Rows are padded with zeros from K to Kp.
+        template <typename T>
+        __global__ void __launch_bounds__(256)
+            contraction_pack_kernel(const T* __restrict__ X, T* __restrict__ X2, PackDims d, int64_t rows, uint32_t K, uint32_t Kp)
+        {
+            const int64_t total = rows * int64_t(Kp);
+            for(int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+            {
+                const int64_t  f = i / Kp;
+                const uint32_t k = uint32_t(i - f * Kp);
+                if(k >= K)
+                {
+                    X2[i] = T(0);
+                    continue;
+                }
+                int64_t  off = 0;
+                uint32_t rem = k;
+                for(int m = d.rank - 1; m >= d.nFree; m--)
+                {
+                    const uint32_t q = rem / d.ext[m];
+                    off += int64_t(rem - q * d.ext[m]) * d.stride[m];
+                    rem = q;
+                }
+                int64_t fr = f;
+                for(int m = d.nFree - 1; m >= 0; m--)
+                {
+                    const int64_t q = fr / d.ext[m];
+                    off += (fr - q * d.ext[m]) * d.stride[m];
+                    fr = q;
+                }
+                X2[i] = X[off];
+            }
+        }
+
+        template <typename T>
+        cudaError_t packOne(const void* X, void* X2, int rank, int nFree, const int64_t* ext, const int64_t* stride,
+                            int64_t K, int64_t Kp, int smCount, cudaStream_t stream)
+        {
+            PackDims d{};
+            d.rank  = rank;
+            d.nFree = nFree;
+            int64_t rows = 1;
+            for(int i = 0; i < rank; i++)
+            {
+                if(ext[i] >= (int64_t(1) << 31))
+                    return cudaErrorInvalidValue;
+                d.ext[i]    = uint32_t(ext[i]);
+                d.stride[i] = stride[i];
+                if(i < nFree)
+                    rows *= ext[i];
+            }
+            if(K >= (int64_t(1) << 31) || Kp >= (int64_t(1) << 31))
+                return cudaErrorInvalidValue;
+            const int64_t total = rows * Kp;
+            const int     sms   = smCount > 0 ? smCount : 148;
+            const int     grid  = int(std::min<int64_t>((total + 255) / 256, int64_t(sms) * 16));
+            contraction_pack_kernel<T><<<grid, 256, 0, stream>>>((const T*)X, (T*)X2, d, rows, uint32_t(K), uint32_t(Kp));
+            return cudaGetLastError();
+        }
+    } // namespace
+
+    cudaError_t launchPackedContraction(const ContractionPlan& plan, float alpha, const void* A, const void* B, float beta,
+                                        const void* C, void* D, void* workspace, uint64_t workspaceBytes, int smCount,
+                                        int* deviceStatus, cudaStream_t stream)
+    {
+        if(!plan.packReal || workspace == nullptr || workspaceBytes < plan.expandBytes)
+            return cudaErrorInvalidValue;
+        // plan.typeA / typeB follow the plan's swap; both operands have the same type
+        const int type = plan.typeA;
+        void*     A2   = workspace;
+        void*     B2   = static_cast<unsigned char*>(workspace) + plan.yOffset;
+        cudaError_t e;
+        if(type == CUDA_R_32F)
+        {
+            e = packOne<float>(A, A2, plan.xRank, plan.xFree, plan.xExt, plan.xStride, plan.packK, plan.packKp, smCount, stream);
+            if(e == cudaSuccess)
+                e = packOne<float>(B, B2, plan.yRank, plan.yFree, plan.yExt, plan.yStride, plan.packK, plan.packKp, smCount, stream);
+        }
+        else
+        {
+            // f16 and bf16 are moved as 16-bit words
+            e = packOne<unsigned short>(A, A2, plan.xRank, plan.xFree, plan.xExt, plan.xStride, plan.packK, plan.packKp, smCount,
+                                        stream);
+            if(e == cudaSuccess)
+                e = packOne<unsigned short>(B, B2, plan.yRank, plan.yFree, plan.yExt, plan.yStride, plan.packK, plan.packKp,
+                                            smCount, stream);
+        }
+        if(e != cudaSuccess)
+            return e;
+        noteLaunch("contraction_pack", 2);
+        unsigned char* rest = static_cast<unsigned char*>(workspace) + plan.expandBytes;
+        return launchContraction(plan, alpha, A2, B2, beta, C, D, plan.workspaceBytes ? rest : nullptr, plan.workspaceBytes,
+                                 smCount, deviceStatus, stream);
+    }
+} // namespace htb

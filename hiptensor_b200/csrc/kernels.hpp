@@ -56,6 +56,12 @@ namespace htb
                                   float beta, const void* C, void* D, void* workspace, uint64_t workspaceBytes,
                                   int smCount, int* deviceStatus, cudaStream_t stream);
 
+    // Plans with plan.packReal: copies both operands into the first plan.expandBytes of the workspace (required) as
+    // packed matrices and contracts the copies (contraction_pack.cu).
+    cudaError_t launchPackedContraction(const ContractionPlan& plan, float alpha, const void* A, const void* B, float beta,
+                                        const void* C, void* D, void* workspace, uint64_t workspaceBytes, int smCount,
+                                        int* deviceStatus, cudaStream_t stream);
+
     // Complex plans (plan.complexKind != 0): alpha and beta as (re, im); the first plan.expandBytes of the
     // workspace are required, plan.workspaceBytes more are optional.
     cudaError_t launchComplexContraction(const ContractionPlan& plan, double alphaRe, double alphaIm, const void* A,

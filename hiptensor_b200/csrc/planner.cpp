@@ -501,9 +501,122 @@ namespace htb
     } // namespace
 
     int planContraction(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
-                        int computeType, int smCount, ContractionPlan* out)
+                        int computeType, int smCount, ContractionPlan* out, uint64_t workspaceLimit)
     {
-        return planReal(A, B, D, typeC, bilinear, computeType, smCount, kMaxRank, out);
+        const int rc = planReal(A, B, D, typeC, bilinear, computeType, smCount, kMaxRank, out);
+        if(rc != PLAN_OK || out->kind != CK_TILED_SIMT || workspaceLimit == 0)
+            return rc;
+        // The gathered FMA kernel reads anything but runs at a fiftieth of the tensor cores' rate. From about a GFLOP
+        // on, two passes that copy the operands into packed matrices (contracted modes merged and innermost, rows
+        // padded to 16 bytes) cost less than they save.
+        const bool tensorType = A.type == CUDA_R_16F || A.type == CUDA_R_16BF || A.type == CUDA_R_32F;
+        if(!tensorType || out->M < 128 || out->N < 128 || out->K < 64
+           || 2.0 * double(out->M) * double(out->N) * double(out->K) < 1e9)
+            return rc;
+        const int elem = A.type == CUDA_R_32F ? 4 : 2, per16 = 16 / elem;
+        int       freeA[kMaxRank], freeB[kMaxRank], conA[kMaxRank], conB[kMaxRank], nfa = 0, nfb = 0, nc = 0;
+        for(int i = 0; i < A.rank; i++)
+        {
+            const int ib = findMode(B.modes, B.rank, A.modes[i]);
+            if(ib >= 0)
+            {
+                conA[nc] = i;
+                conB[nc] = ib;
+                nc++;
+            }
+            else
+                freeA[nfa++] = i;
+        }
+        for(int i = 0; i < B.rank; i++)
+            if(findMode(A.modes, A.rank, B.modes[i]) < 0)
+                freeB[nfb++] = i;
+        if(nc == 0 || nfa == 0 || nfb == 0 || nfa + 1 > kMaxRank || nfb + 1 > kMaxRank)
+            return rc;
+        // the rows of a copy follow D's order (slowest mode of D first): free modes that are neighbours in D are
+        // neighbours in the copy and fold into one mode of the row group
+        auto strideInD = [&](const TensorView& T, int pos) {
+            const int id = findMode(D.modes, D.rank, T.modes[pos]);
+            return id >= 0 ? D.strides[id] : int64_t(0);
+        };
+        sortSmall(freeA, nfa, [&](int x, int y) { return strideInD(A, x) > strideInD(A, y); });
+        sortSmall(freeB, nfb, [&](int x, int y) { return strideInD(B, x) > strideInD(B, y); });
+        int64_t K = 1;
+        for(int i = 0; i < nc; i++)
+            K *= A.lens[conA[i]];
+        const int64_t Kp = (K + per16 - 1) / per16 * per16;
+        // a label for the merged contracted mode that no tensor uses
+        int32_t kLabel = 0;
+        for(bool clash = true; clash; )
+        {
+            clash = findMode(A.modes, A.rank, kLabel) >= 0 || findMode(B.modes, B.rank, kLabel) >= 0
+                    || findMode(D.modes, D.rank, kLabel) >= 0;
+            if(clash)
+                kLabel++;
+        }
+        int64_t lA[kMaxRank], sA[kMaxRank], lB[kMaxRank], sB[kMaxRank];
+        int32_t mA[kMaxRank], mB[kMaxRank];
+        int64_t rowsA = 1, rowsB = 1;
+        lA[nfa] = Kp;
+        sA[nfa] = 1;
+        mA[nfa] = kLabel;
+        for(int i = nfa - 1; i >= 0; i--)
+        {
+            lA[i] = A.lens[freeA[i]];
+            mA[i] = A.modes[freeA[i]];
+            sA[i] = (i == nfa - 1) ? Kp : sA[i + 1] * lA[i + 1];
+            rowsA *= lA[i];
+        }
+        lB[nfb] = Kp;
+        sB[nfb] = 1;
+        mB[nfb] = kLabel;
+        for(int i = nfb - 1; i >= 0; i--)
+        {
+            lB[i] = B.lens[freeB[i]];
+            mB[i] = B.modes[freeB[i]];
+            sB[i] = (i == nfb - 1) ? Kp : sB[i + 1] * lB[i + 1];
+            rowsB *= lB[i];
+        }
+        const uint64_t bytesA = (uint64_t(rowsA) * uint64_t(Kp) * elem + 255u) & ~uint64_t(255);
+        const uint64_t bytesB = (uint64_t(rowsB) * uint64_t(Kp) * elem + 255u) & ~uint64_t(255);
+        if(bytesA + bytesB > workspaceLimit)
+            return rc;
+        const TensorView A2{nfa + 1, lA, sA, mA, A.type}, B2{nfb + 1, lB, sB, mB, B.type};
+        ContractionPlan  packed;
+        if(planReal(A2, B2, D, typeC, bilinear, computeType, smCount, kMaxRank, &packed) != PLAN_OK
+           || (packed.kind != CK_TCGEN05 && packed.kind != CK_TF32X3))
+            return rc;
+        packed.packReal = 1;
+        packed.packK    = K;
+        packed.packKp   = Kp;
+        packed.xRank    = nfa + nc;
+        packed.xFree    = nfa;
+        packed.yRank    = nfb + nc;
+        packed.yFree    = nfb;
+        if(packed.xRank > kMaxRank || packed.yRank > kMaxRank)
+            return rc;
+        for(int i = 0; i < nfa; i++)
+        {
+            packed.xExt[i]    = A.lens[freeA[i]];
+            packed.xStride[i] = A.strides[freeA[i]];
+        }
+        for(int i = 0; i < nfb; i++)
+        {
+            packed.yExt[i]    = B.lens[freeB[i]];
+            packed.yStride[i] = B.strides[freeB[i]];
+        }
+        for(int i = 0; i < nc; i++)
+        {
+            packed.xExt[nfa + i]    = A.lens[conA[i]];
+            packed.xStride[nfa + i] = A.strides[conA[i]];
+            packed.yExt[nfb + i]    = B.lens[conB[i]];
+            packed.yStride[nfb + i] = B.strides[conB[i]];
+        }
+        packed.yOffset     = bytesA;
+        packed.expandBytes = bytesA + bytesB;
+        if(packed.expandBytes + packed.workspaceBytes > workspaceLimit)
+            packed.workspaceBytes = 0;
+        *out = packed;
+        return PLAN_OK;
     }
 
     namespace

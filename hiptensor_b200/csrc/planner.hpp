@@ -143,6 +143,15 @@ namespace htb
         int      yCopy, yRank, yFree;
         int64_t  yExt[kMaxRank], yStride[kMaxRank];
         uint64_t yOffset;
+        // Real f16 / bf16 / f32 contraction whose operands the tensor-core kernels cannot read where they lie (a stride
+        // that is not a multiple of 16 bytes, a contracted mode contiguous in one operand and a free mode in the other
+        // ...): both operands are first copied into the workspace as packed matrices, one row per free index, the
+        // contracted modes merged into one mode of packK elements padded with zeros to packKp (a multiple of 16 bytes),
+        // and the fields above describe the contraction of the copies. A's copy is described by x*, B's by y* (extents
+        // and source strides in the copy's order: free modes, then contracted ones); B's copy lies at yOffset;
+        // expandBytes covers both.
+        int      packReal;
+        int64_t  packK, packKp;
         // 0 from the planner. The library's plan registry gives every plan it keeps a process-wide unique
         // number, which the launchers use as the key of their tensor-map caches (0 = do not cache).
         uint64_t cacheId;
@@ -159,8 +168,10 @@ namespace htb
 
     // D's modes are looked up in A first, then in B (as the reference does); C, when
     // present, is addressed with D's strides (contraction_solution_impl.hpp:125-140).
+    // workspaceLimit: bytes of scratch the caller can give; a plan that needs packed copies of the operands is made only
+    // when the copies fit.
     int planContraction(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
-                        int computeType, int smCount, ContractionPlan* out);
+                        int computeType, int smCount, ContractionPlan* out, uint64_t workspaceLimit = 0);
     // cf32 / cf64 tensors with compute type C32F / C64F: see planner.cpp
     int planComplexContraction(const TensorView& A, const TensorView& B, const TensorView& D, int typeC, bool bilinear,
                                int computeType, int smCount, ContractionPlan* out);

@@ -1,0 +1,124 @@
+"""GPU parity of the packed-operand path: real contractions whose operands the tensor-core kernels cannot read in
+place (strides that are not multiples of 16 bytes, contracted modes interleaved with free ones) and that are large
+enough (about a GFLOP) are run on packed copies in the caller's workspace. Every output against the fp64 contraction
+of the same values (numpy), sampled outputs against the CPU oracle's k order; without a workspace the same problem
+runs on the gathered FMA kernel and agrees."""
+import numpy as np
+import pytest
+
+from helpers import rel_error, run_contraction, to_device, to_host, nan_like
+from oracle import binding as orc
+
+pytestmark = pytest.mark.gpu
+
+TENSOR_CORE = ("contraction_tcgen05", "contraction_tcgen05_pair", "contraction_tcgen05_pair_wide", "contraction_tf32x3")
+
+
+@pytest.fixture(scope="module")
+def env():
+    import hiptensor_b200 as ht
+
+    return ht, ht.Handle()
+
+
+def einsum_ref(inp, modeA, modeB, modeD, typeAB, alpha, beta, typeD):
+    """fp64 contraction of the host images (strided views of the flat arrays)."""
+    def view(flat, lens, strides, dt):
+        a = orc.to_f64(flat, dt)
+        return np.lib.stride_tricks.as_strided(a, shape=lens, strides=[s * 8 for s in strides])
+
+    letters = {m: chr(ord("a") + i) for i, m in enumerate(sorted(set(modeA) | set(modeB)))}
+    sub = lambda ms: "".join(letters[m] for m in ms)
+    A = view(inp["A"], inp["lA"], inp["sA"], typeAB)
+    B = view(inp["B"], inp["lB"], inp["sB"], typeAB)
+    ref = alpha * np.einsum("%s,%s->%s" % (sub(modeA), sub(modeB), sub(modeD)), A, B, optimize=True)
+    if inp["C"] is not None and beta != 0.0:
+        ref = ref + beta * view(inp["C"], inp["lD"], inp["sD"], typeD)
+    return ref
+
+
+def written(got, inp, typeD):
+    g = orc.to_f64(got, typeD)
+    return np.lib.stride_tricks.as_strided(g, shape=inp["lD"], strides=[s * 8 for s in inp["sD"]])
+
+
+CASES = [
+    # (typeAB, typeD, extents, modeA, modeB, modeD): rank 4 x rank 4 -> rank 4
+    ("f16 extents of 30: strides of 60 bytes", orc.F16, orc.F32, 30, [0, 1, 4, 5], [2, 3, 4, 5], [0, 1, 2, 3]),
+    ("f16 interleaved modes", orc.F16, orc.F32, 32, [0, 4, 1, 5], [5, 2, 4, 3], [0, 1, 2, 3]),
+    ("bf16 extents of 30, interleaved", orc.BF16, orc.F32, 30, [0, 4, 1, 5], [5, 2, 4, 3], [0, 1, 2, 3]),
+    ("f16 in and out, extents of 33", orc.F16, orc.F16, 33, [4, 0, 5, 1], [2, 4, 3, 5], [2, 3, 0, 1]),
+    ("f32 interleaved modes", orc.F32, orc.F32, 30, [0, 4, 1, 5], [5, 2, 4, 3], [0, 1, 2, 3]),
+    ("f32 extents of 33, interleaved", orc.F32, orc.F32, 33, [0, 4, 1, 5], [5, 2, 4, 3], [3, 2, 1, 0]),
+]
+
+
+@pytest.mark.parametrize("name,typeAB,typeD,e,modeA,modeB,modeD", CASES, ids=[c[0] for c in CASES])
+@pytest.mark.parametrize("alpha,beta", [(1.0, 0.0), (1.5, 0.5)])
+def test_packed_operands_every_output(env, name, typeAB, typeD, e, modeA, modeB, modeD, alpha, beta):
+    ht, h = env
+    ext = {m: e for m in range(6)}
+    inp = {}
+    smp = np.random.default_rng(e).integers(0, e ** 4, 512)
+    got, exp, td = run_contraction(ht, h, ext, modeA, modeB, modeD, typeAB=typeAB, typeD=typeD, alpha=alpha, beta=beta,
+                                   with_c=beta != 0.0, fill="normal", sample=smp, inputs=inp)
+    assert ht.last_kernel_name() in TENSOR_CORE, ht.last_kernel_name()
+    half_out = typeD in (orc.F16, orc.BF16)
+    # tolerances: f16 / bf16 products are exact and summed in fp32 (tensor cores truncate: 1e-3 over 900 to 1089 terms);
+    # fp32 data runs as three TF32 products (1e-5, the reference's fp32 criterion); a half-precision D rounds once more
+    tol = 4e-3 if half_out else (1e-3 if typeAB != orc.F32 else 1e-5)
+    assert 0 <= rel_error(got, exp, td) < tol
+    ref = einsum_ref(inp, modeA, modeB, modeD, typeAB, alpha, beta, typeD)
+    out = written(got, inp, typeD)
+    assert not np.isnan(out).any()
+    err = float(np.max(np.abs(out - ref) / (np.abs(out) + np.abs(ref) + 1.0)))
+    assert err < tol, err
+
+
+def test_without_a_workspace_the_fma_kernel_gives_the_same(env):
+    """The plan made for a workspace of 0 bytes copies nothing: same problem, gathered FMA kernel, results within the
+    two paths' summation orders."""
+    import torch
+
+    ht, h = env
+    e, modeA, modeB, modeD = 30, [0, 4, 1, 5], [5, 2, 4, 3], [0, 1, 2, 3]
+    lens = [e] * 4
+    A = orc.fill_normal(e ** 4, orc.F16, 11, 0.5)
+    B = orc.fill_normal(e ** 4, orc.F16, 12, 0.5)
+    d16 = h.tensor_descriptor(lens, None, ht.R_16F)
+    d32 = h.tensor_descriptor(lens, None, ht.R_32F)
+    cd = h.contraction_descriptor(d16, modeA, d16, modeB, None, None, d32, modeD, ht.COMPUTE_32F)
+    find = h.contraction_find(ht.ALGO_DEFAULT)
+    assert h.contraction_workspace_size(cd, find, ht.WORKSPACE_MIN) == 0
+    need = h.contraction_workspace_size(cd, find, ht.WORKSPACE_RECOMMENDED)
+    assert need >= 2 * e ** 4 * 2  # room for both copies
+    A_d, B_d = to_device(A, orc.F16), to_device(B, orc.F16)
+    outs = []
+    for ws_size in (0, need):
+        plan = h.contraction_plan(cd, find, ws_size)
+        D_d = to_device(nan_like(e ** 4, orc.F32), orc.F32)
+        ws = torch.empty(ws_size, dtype=torch.uint8, device="cuda") if ws_size else None
+        h.contraction(plan, 1.0, A_d, B_d, 0.0, None, D_d, ws, ws_size)
+        outs.append((ht.last_kernel_name(), to_host(D_d, orc.F32)))
+    assert outs[0][0] == "contraction_tiled_simt" and outs[1][0] in TENSOR_CORE
+    assert 0 <= rel_error(outs[1][1], outs[0][1], orc.F32) < 1e-3
+    # a plan made for the copies refuses a smaller workspace at execution
+    plan = h.contraction_plan(cd, find, need)
+    D_d = to_device(nan_like(e ** 4, orc.F32), orc.F32)
+    with pytest.raises(ht.HiptensorError) as err:
+        h.contraction(plan, 1.0, A_d, B_d, 0.0, None, D_d, None, 0)
+    assert err.value.status == ht.STATUS_INSUFFICIENT_WORKSPACE
+
+
+def test_two_dimensional_odd_k(env):
+    """A[m,k] B[n,k] with K = 999 (rows of 1998 bytes): packed rows are padded to 1000 elements with zeros."""
+    ht, h = env
+    ext = {0: 1001, 1: 1003, 2: 999}
+    inp = {}
+    got, _, td = run_contraction(ht, h, ext, [0, 2], [1, 2], [0, 1], typeAB=orc.F16, typeD=orc.F32, alpha=1.0, beta=0.0,
+                                 with_c=False, fill="normal", oracle=False, inputs=inp)
+    assert ht.last_kernel_name() in TENSOR_CORE
+    ref = einsum_ref(inp, [0, 2], [1, 2], [0, 1], orc.F16, 1.0, 0.0, orc.F32)
+    out = written(got, inp, orc.F32)
+    assert not np.isnan(out).any()
+    assert float(np.max(np.abs(out - ref) / (np.abs(out) + np.abs(ref) + 1.0))) < 1e-3
