@@ -27,28 +27,29 @@ namespace htb
             int64_t  stride[kMaxRank];
         };
 
-        // One thread per element of the copy, the merged contracted index fastest: the writes are contiguous, the
-        // reads follow the source strides. Rows are padded with zeros from K to Kp.
+        // One thread per 16 bytes of the copy (V elements), the merged contracted index fastest: the writes are contiguous
+        // 16-byte stores, the reads follow the source strides. The row and the first contracted index are decoded once
+        // per thread, the following indices by stepping the contracted coordinates like an odometer. Rows are padded with
+        // zeros from K to Kp (a multiple of V).
         template <typename T>
         __global__ void __launch_bounds__(256)
             contraction_pack_kernel(const T* __restrict__ X, T* __restrict__ X2, PackDims d, int64_t rows, uint32_t K, uint32_t Kp)
         {
-            const int64_t total = rows * int64_t(Kp);
+            constexpr int  V     = 16 / int(sizeof(T));
+            const uint32_t perRow = Kp / V;
+            const int64_t  total  = rows * int64_t(perRow);
             for(int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
             {
-                const int64_t  f = i / Kp;
-                const uint32_t k = uint32_t(i - f * Kp);
-                if(k >= K)
-                {
-                    X2[i] = T(0);
-                    continue;
-                }
-                int64_t  off = 0;
-                uint32_t rem = k;
+                const int64_t  f  = i / perRow;
+                const uint32_t k0 = uint32_t(i - f * perRow) * V;
+                int64_t        off = 0;
+                uint32_t       c[kMaxRank];
+                uint32_t       rem = k0;
                 for(int m = d.rank - 1; m >= d.nFree; m--)
                 {
                     const uint32_t q = rem / d.ext[m];
-                    off += int64_t(rem - q * d.ext[m]) * d.stride[m];
+                    c[m]             = rem - q * d.ext[m];
+                    off += int64_t(c[m]) * d.stride[m];
                     rem = q;
                 }
                 int64_t fr = f;
@@ -58,7 +59,28 @@ namespace htb
                     off += (fr - q * d.ext[m]) * d.stride[m];
                     fr = q;
                 }
-                X2[i] = X[off];
+                union
+                {
+                    uint4 w;
+                    T     e[V];
+                } v;
+                v.w = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for(int e = 0; e < V; e++)
+                {
+                    if(k0 + e < K)
+                        v.e[e] = X[off];
+                    // next contracted index
+                    for(int m = d.rank - 1; m >= d.nFree; m--)
+                    {
+                        off += d.stride[m];
+                        if(++c[m] < d.ext[m])
+                            break;
+                        off -= int64_t(d.ext[m]) * d.stride[m];
+                        c[m] = 0;
+                    }
+                }
+                *reinterpret_cast<uint4*>(X2 + f * int64_t(Kp) + k0) = v.w;
             }
         }
 
@@ -81,7 +103,7 @@ namespace htb
             }
             if(K >= (int64_t(1) << 31) || Kp >= (int64_t(1) << 31))
                 return cudaErrorInvalidValue;
-            const int64_t total = rows * Kp;
+            const int64_t total = rows * (Kp / (16 / int64_t(sizeof(T))));
             const int     sms   = smCount > 0 ? smCount : 148;
             const int     grid  = int(std::min<int64_t>((total + 255) / 256, int64_t(sms) * 16));
             contraction_pack_kernel<T><<<grid, 256, 0, stream>>>((const T*)X, (T*)X2, d, rows, uint32_t(K), uint32_t(Kp));
