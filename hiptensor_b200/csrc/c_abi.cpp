@@ -277,7 +277,7 @@ int htDescribeContractionPlan(uint32_t numModesA, const int64_t* lensA, const in
     htb::ContractionPlan p;
     const bool cplx = typeCompute == HIPTENSOR_COMPUTE_C32F || typeCompute == HIPTENSOR_COMPUTE_C64F;
     int        rc   = cplx ? htb::planComplexContraction(A, B, D, dataTypeD, hasC != 0, typeCompute, 148, &p)
-                           : htb::planContraction(A, B, D, dataTypeD, hasC != 0, typeCompute, 148, &p);
+                           : htb::planContraction(A, B, D, dataTypeD, hasC != 0, typeCompute, 148, &p, ~uint64_t(0));
     if(rc != htb::PLAN_OK)
         return rc;
     return copyOut(htb::describe(p), buf, bufSize);

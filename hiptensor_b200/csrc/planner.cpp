@@ -1236,6 +1236,12 @@ namespace htb
             if(p.pair && p.ksplit > 1)
                 s += " ksplit=2";
         }
+        if(p.packReal)
+        {
+            snprintf(buf, sizeof(buf), " packed K=%lld Kp=%lld copies=%llu", (long long)p.packK, (long long)p.packKp,
+                     (unsigned long long)p.expandBytes);
+            s += buf;
+        }
         if(p.splitK > 1)
         {
             snprintf(buf, sizeof(buf), " splitK=%d workspace=%lld", p.splitK, (long long)p.workspaceBytes);

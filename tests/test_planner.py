@@ -161,6 +161,33 @@ def test_contraction_fp32_tensor_core_layouts(ht):
     assert "kind=tf32x3" in plan([K, M], [2, 0], [K, N], [2, 1], [M, N], [0, 1], ht.COMPUTE_16BF)
 
 
+def test_contraction_packed_operands(ht):
+    """Operands TMA cannot describe: large problems are planned on packed copies (contracted modes merged, rows padded
+    to 16 bytes, free modes in D's order); small ones and f64 keep the gathered kernels."""
+    def plan(e, modeA, modeB, modeD, t=None, tD=None):
+        t = ht.R_16F if t is None else t
+        tD = ht.R_32F if tD is None else tD
+        s = packed([e] * 4, False)
+        return ht.describe_contraction_plan([e] * 4, s, modeA, t, [e] * 4, s, modeB, t, [e] * 4, s, modeD, tD, False,
+                                            ht.COMPUTE_64F if t == ht.R_64F else ht.COMPUTE_32F)
+
+    # extents of 50 halves: strides of 100 bytes; K = 2500 padded to 2504
+    d = plan(50, [0, 1, 4, 5], [2, 3, 4, 5], [0, 1, 2, 3])
+    assert "kind=tcgen05" in d and "packed K=2500 Kp=2504" in d and "M=2500 N=2500 K=2504" in d
+    assert "copies=%d" % (2 * ((2500 * 2504 * 2 + 255) // 256 * 256)) in d
+    # contracted modes interleaved with free ones, in different orders in A and B
+    d = plan(48, [0, 4, 1, 5], [5, 2, 4, 3], [0, 1, 2, 3])
+    assert "kind=tcgen05" in d and "packed K=2304 Kp=2304" in d
+    d = plan(48, [0, 4, 1, 5], [5, 2, 4, 3], [0, 1, 2, 3], ht.R_32F)
+    assert "kind=tf32x3" in d and "packed K=2304 Kp=2304" in d
+    # below about a GFLOP the copies do not pay; f64 gathers in place on the FP64 tensor pipe
+    assert "kind=tiled_simt" in plan(20, [0, 4, 1, 5], [5, 2, 4, 3], [0, 1, 2, 3]) and "packed" not in plan(20, [0, 4, 1, 5], [5, 2, 4, 3], [0, 1, 2, 3])
+    d = plan(48, [0, 4, 1, 5], [5, 2, 4, 3], [0, 1, 2, 3], ht.R_64F, ht.R_64F)
+    assert "kind=tiled_dmma" in d and "packed" not in d
+    # what the tensor-core kernels read in place is not copied
+    assert "packed" not in plan(64, [0, 1, 4, 5], [2, 3, 4, 5], [0, 1, 2, 3])
+
+
 def test_contraction_k_split_plans(ht):
     """Few tiles and a long K: the fp32 tensor-core plan cuts K into up to four ranges (at least four K blocks
     each, never more CTAs than SMs), one CTA of a cluster each; the sums meet in shared memory, so no workspace is
