@@ -29,19 +29,17 @@ namespace htb
 
         // One thread per 16 bytes of the copy (V elements), the merged contracted index fastest: the writes are contiguous
         // 16-byte stores, the reads follow the source strides. The row and the first contracted index are decoded once
-        // per thread, the following indices by stepping the contracted coordinates like an odometer. Rows are padded with
-        // zeros from K to Kp (a multiple of V).
+        // per thread (32-bit divisions: the copy has fewer than 2^32 vectors), the following indices by stepping the
+        // contracted coordinates like an odometer. Rows are padded with zeros from K to Kp (a multiple of V).
         template <typename T>
         __global__ void __launch_bounds__(256)
-            contraction_pack_kernel(const T* __restrict__ X, T* __restrict__ X2, PackDims d, int64_t rows, uint32_t K, uint32_t Kp)
+            contraction_pack_kernel(const T* __restrict__ X, T* __restrict__ X2, PackDims d, uint32_t total, uint32_t K, uint32_t Kp)
         {
-            constexpr int  V     = 16 / int(sizeof(T));
+            constexpr int  V      = 16 / int(sizeof(T));
             const uint32_t perRow = Kp / V;
-            const int64_t  total  = rows * int64_t(perRow);
-            for(int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x)
+            for(uint32_t i = blockIdx.x * 256u + threadIdx.x; i < total; i += gridDim.x * 256u)
             {
-                const int64_t  f  = i / perRow;
-                const uint32_t k0 = uint32_t(i - f * perRow) * V;
+                const uint32_t f = i / perRow, k0 = (i - f * perRow) * V;
                 int64_t        off = 0;
                 uint32_t       c[kMaxRank];
                 uint32_t       rem = k0;
@@ -52,12 +50,12 @@ namespace htb
                     off += int64_t(c[m]) * d.stride[m];
                     rem = q;
                 }
-                int64_t fr = f;
+                rem = f;
                 for(int m = d.nFree - 1; m >= 0; m--)
                 {
-                    const int64_t q = fr / d.ext[m];
-                    off += (fr - q * d.ext[m]) * d.stride[m];
-                    fr = q;
+                    const uint32_t q = rem / d.ext[m];
+                    off += int64_t(rem - q * d.ext[m]) * d.stride[m];
+                    rem = q;
                 }
                 union
                 {
@@ -80,7 +78,7 @@ namespace htb
                         c[m] = 0;
                     }
                 }
-                *reinterpret_cast<uint4*>(X2 + f * int64_t(Kp) + k0) = v.w;
+                *reinterpret_cast<uint4*>(X2 + int64_t(f) * Kp + k0) = v.w;
             }
         }
 
@@ -104,9 +102,11 @@ namespace htb
             if(K >= (int64_t(1) << 31) || Kp >= (int64_t(1) << 31))
                 return cudaErrorInvalidValue;
             const int64_t total = rows * (Kp / (16 / int64_t(sizeof(T))));
-            const int     sms   = smCount > 0 ? smCount : 148;
-            const int     grid  = int(std::min<int64_t>((total + 255) / 256, int64_t(sms) * 16));
-            contraction_pack_kernel<T><<<grid, 256, 0, stream>>>((const T*)X, (T*)X2, d, rows, uint32_t(K), uint32_t(Kp));
+            if(total >= (int64_t(1) << 32) - 65536)
+                return cudaErrorInvalidValue; // more than 64 GiB of copy
+            const int sms  = smCount > 0 ? smCount : 148;
+            const int grid = int(std::min<int64_t>((total + 255) / 256, int64_t(sms) * 32));
+            contraction_pack_kernel<T><<<grid, 256, 0, stream>>>((const T*)X, (T*)X2, d, uint32_t(total), uint32_t(K), uint32_t(Kp));
             return cudaGetLastError();
         }
     } // namespace
