@@ -122,3 +122,22 @@ def test_two_dimensional_odd_k(env):
     out = written(got, inp, orc.F32)
     assert not np.isnan(out).any()
     assert float(np.max(np.abs(out - ref) / (np.abs(out) + np.abs(ref) + 1.0))) < 1e-3
+
+
+def test_strided_operands(env):
+    """Operands that are views with gaps (row pitches of 34 and 37 elements for extents of 30), first-mode-fastest D."""
+    ht, h = env
+    e = 30
+    ext = {m: e for m in range(6)}
+    modeA, modeB, modeD = [0, 4, 1, 5], [5, 2, 4, 3], [0, 1, 2, 3]
+    sA = orc.packed_strides([e, e, e, 34], False)
+    sB = orc.packed_strides([e, e, 37, e], False)
+    inp = {}
+    got, _, td = run_contraction(ht, h, ext, modeA, modeB, modeD, typeAB=orc.F16, typeD=orc.F32, alpha=2.0, beta=-1.0,
+                                 with_c=True, fill="normal", oracle=False, stridesA=sA, stridesB=sB, first_fastest=True,
+                                 inputs=inp)
+    assert ht.last_kernel_name() in TENSOR_CORE
+    ref = einsum_ref(inp, modeA, modeB, modeD, orc.F16, 2.0, -1.0, orc.F32)
+    out = written(got, inp, orc.F32)
+    assert not np.isnan(out).any()
+    assert float(np.max(np.abs(out - ref) / (np.abs(out) + np.abs(ref) + 1.0))) < 1e-3
