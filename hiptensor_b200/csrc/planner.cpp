@@ -826,7 +826,9 @@ namespace htb
                 tc = ((gn[i].s0 % 8 == 0 || (out->bMajor == 1 && i == out->nFast)) && gn[i].ext < (int64_t(1) << 31));
             // small problems do not fill the machine with 128-row tiles: leave them to the
             // gathered tiled kernel
-            tc = tc && (out->M >= 128 && out->N >= 64);
+            // (except under a long contraction: a single FMA tile walks K = 65536 in 6.5 ms, a ragged tensor-core tile
+            // with its K range cut over a cluster in tens of microseconds)
+            tc = tc && ((out->M >= 128 && out->N >= 64) || (out->K >= 1024 && out->M >= 16 && out->N >= 16));
             if(tc)
             {
                 out->tileM = 128;
@@ -868,7 +870,8 @@ namespace htb
             // fp32 data on the tensor cores (compute f32: TF32 big/small split; compute f16 / bf16: elements
             // rounded to that type, one MMA). An operand is taken K-major (one stride-1 K mode) or MN-major (a
             // stride-1 mode in its row group); all other strides must be multiples of 16 bytes for TMA.
-            bool tf = out->K >= 32 && out->M >= 128 && out->N >= 64 && nk <= 2;
+            bool tf = out->K >= 32 && ((out->M >= 128 && out->N >= 64) || (out->K >= 1024 && out->M >= 16 && out->N >= 16))
+                      && nk <= 2;
             out->aMajor = out->aKContig ? 0 : ((gm[0].s0 == 1 && gm[0].ext > 1) ? 1 : -1);
             out->bMajor = out->bKContig ? 0 : -1;
             out->nFast  = 0;

@@ -141,3 +141,32 @@ def test_strided_operands(env):
     out = written(got, inp, orc.F32)
     assert not np.isnan(out).any()
     assert float(np.max(np.abs(out - ref) / (np.abs(out) + np.abs(ref) + 1.0))) < 1e-3
+
+
+@pytest.mark.parametrize("typeAB", [orc.F16, orc.F32])
+@pytest.mark.parametrize("M,N,K,kfirst", [(64, 64, 8192, False), (16, 256, 4096, False), (24, 40, 16384, True),
+                                          (128, 32, 1024, False), (64, 64, 1016, False)])
+def test_small_outputs_under_a_long_contraction(env, typeAB, M, N, K, kfirst):
+    """M < 128 or N < 64 with K >= 1024: one ragged tensor-core tile (rows beyond M and N zero-filled by TMA, masked in
+    the epilogue) with its K range cut over a cluster, instead of one FMA tile walking all of K. Every output against
+    the oracle's k order; K = 1016 stays below the threshold on the FMA kernel."""
+    ht, h = env
+    ext = {0: M, 1: N, 2: K}
+    modeA, modeB = ([2, 0], [2, 1]) if kfirst else ([0, 2], [1, 2])
+    inp = {}
+    got, exp, td = run_contraction(ht, h, ext, modeA, modeB, [0, 1], typeAB=typeAB, typeD=orc.F32, alpha=1.25, beta=0.5,
+                                   with_c=True, fill="normal", inputs=inp)
+    if K >= 1024:
+        assert ht.last_kernel_name() in TENSOR_CORE, ht.last_kernel_name()
+    else:
+        assert ht.last_kernel_name() == "contraction_tiled_simt"
+    assert not np.isnan(got).any()
+    # against the oracle: two fp32 summation orders of K terms (the oracle adds sequentially in fp32)
+    assert 0 <= rel_error(got, exp, td) < max(1e-3 if typeAB == orc.F16 else 0.0, K * float(np.finfo(np.float32).eps))
+    # against the fp64 contraction of the same values: f16 products are exact, the tensor cores' fp32 adds truncate;
+    # fp32 data runs as three TF32 products (the reference's fp32 criterion)
+    ref = einsum_ref(inp, modeA, modeB, [0, 1], typeAB, 1.25, 0.5, orc.F32)
+    out = written(got, inp, orc.F32)
+    err = float(np.max(np.abs(out - ref) / (np.abs(out) + np.abs(ref) + 1.0)))
+    # (1e-5 up to K = 4096, growing with K: the fp32 accumulator rounds once per 8-element MMA step)
+    assert err < (1e-3 if typeAB == orc.F16 else 1e-5 * max(1.0, K / 4096.0)), err
