@@ -184,8 +184,8 @@ namespace htb
 
     // Splits `tile` rows over the folded modes of a group, fastest mode first: a mode is taken
     // whole while it is a power of two smaller than what is left, the first mode at least as
-    // large as what is left takes the rest (ragged ends are zero-filled by TMA), later modes
-    // get 1. Returns the rows covered (0 if the group cannot be boxed).
+    // large as what is left takes the rest (ragged ends are zero-filled by TMA), and so does the last mode
+    // whatever its extent; later modes get 1. Returns the rows covered (0 if the group cannot be boxed).
     int boxDecompose(const ModeDim* dims, int n, int tile, int* box);
 
     // Shared helper: fold adjacent modes of one group. dims must already be sorted by

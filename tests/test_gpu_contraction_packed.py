@@ -145,11 +145,14 @@ def test_strided_operands(env):
 
 @pytest.mark.parametrize("typeAB", [orc.F16, orc.F32])
 @pytest.mark.parametrize("M,N,K,kfirst", [(64, 64, 8192, False), (16, 256, 4096, False), (24, 40, 16384, True),
-                                          (128, 32, 1024, False), (64, 64, 1016, False)])
+                                          (128, 32, 1024, False), (64, 64, 1016, False), (100, 30, 8192, False),
+                                          (100, 30, 8192, True), (33, 33, 4096, True), (1000, 30, 1024, True)])
 def test_small_outputs_under_a_long_contraction(env, typeAB, M, N, K, kfirst):
     """M < 128 or N < 64 with K >= 1024: one ragged tensor-core tile (rows beyond M and N zero-filled by TMA, masked in
-    the epilogue) with its K range cut over a cluster, instead of one FMA tile walking all of K. Every output against
-    the oracle's k order; K = 1016 stays below the threshold on the FMA kernel."""
+    the epilogue) with its K range cut over a cluster, instead of one FMA tile walking all of K. Row extents that are
+    not powers of two take a box that reaches past the tensor; with K first and odd extents (strides of 200 or 66 bytes)
+    the operands are packed first. Every output against the oracle's k order; K = 1016 stays below the threshold on the
+    FMA kernel."""
     ht, h = env
     ext = {0: M, 1: N, 2: K}
     modeA, modeB = ([2, 0], [2, 1]) if kfirst else ([0, 2], [1, 2])
