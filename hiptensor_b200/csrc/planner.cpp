@@ -821,7 +821,10 @@ namespace htb
             out->aKContig = out->aMajor == 0 ? 1 : 0;
             out->bKContig = out->bMajor == 0 ? 1 : 0;
             const int kOthers = nk - 1;
-            bool tc = out->aMajor >= 0 && out->bMajor >= 0 && out->K >= 64 && kOthers <= 2 && nm + kOthers <= 4
+            // a short contraction under a large output is bound by the stores of D: the K block's zero-filled tail costs MMA
+            // steps that hide behind them (8192 x 8192 x 8: 0.33 ms on the FMA kernel)
+            const bool bigOutput = double(out->M) * double(out->N) >= double(1 << 22);
+            bool tc = out->aMajor >= 0 && out->bMajor >= 0 && (out->K >= 64 || (out->K >= 8 && bigOutput)) && kOthers <= 2 && nm + kOthers <= 4
                       && nn + kOthers <= 4 && nm <= (out->aMajor == 1 ? 3 : 4) && nn <= (out->bMajor == 1 ? 3 : 4);
             if(tc && nk == 1 && (out->aMajor == 0 || out->bMajor == 0))
                 tc = out->K % 8 == 0;
@@ -881,7 +884,8 @@ namespace htb
             // fp32 data on the tensor cores (compute f32: TF32 big/small split; compute f16 / bf16: elements
             // rounded to that type, one MMA). An operand is taken K-major (one stride-1 K mode) or MN-major (a
             // stride-1 mode in its row group); all other strides must be multiples of 16 bytes for TMA.
-            bool tf = out->K >= 32 && ((out->M >= 128 && out->N >= 64) || (out->K >= 1024 && out->M >= 16 && out->N >= 16))
+            const bool bigOutput = double(out->M) * double(out->N) >= double(1 << 22);
+            bool tf = (out->K >= 32 || (out->K >= 4 && bigOutput)) && ((out->M >= 128 && out->N >= 64) || (out->K >= 1024 && out->M >= 16 && out->N >= 16))
                       && nk <= 2;
             out->aMajor = out->aKContig ? 0 : ((gm[0].s0 == 1 && gm[0].ext > 1) ? 1 : -1);
             out->bMajor = out->bKContig ? 0 : -1;

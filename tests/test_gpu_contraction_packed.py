@@ -173,3 +173,19 @@ def test_small_outputs_under_a_long_contraction(env, typeAB, M, N, K, kfirst):
     err = float(np.max(np.abs(out - ref) / (np.abs(out) + np.abs(ref) + 1.0)))
     # (1e-5 up to K = 4096, growing with K: the fp32 accumulator rounds once per 8-element MMA step)
     assert err < (1e-3 if typeAB == orc.F16 else 1e-5 * max(1.0, K / 4096.0)), err
+
+
+@pytest.mark.parametrize("typeAB", [orc.F16, orc.F32])
+@pytest.mark.parametrize("M,N,K", [(4096, 2048, 8), (2048, 2048, 24), (2048, 4096, 40)])
+def test_short_contraction_under_a_large_output(env, typeAB, M, N, K):
+    """K below one K block (64 f16 / 32 f32 elements) with four million outputs or more: the tensor-core kernels run
+    with the block's tail zero-filled by TMA; the stores of D bound the time. Every output against fp64."""
+    ht, h = env
+    inp = {}
+    got, _, td = run_contraction(ht, h, {0: M, 1: N, 2: K}, [0, 2], [1, 2], [0, 1], typeAB=typeAB, typeD=orc.F32,
+                                 alpha=1.0, beta=0.0, with_c=False, fill="normal", oracle=False, inputs=inp)
+    assert ht.last_kernel_name() in TENSOR_CORE, ht.last_kernel_name()
+    ref = einsum_ref(inp, [0, 2], [1, 2], [0, 1], typeAB, 1.0, 0.0, orc.F32)
+    out = written(got, inp, orc.F32)
+    assert not np.isnan(out).any()
+    assert float(np.max(np.abs(out - ref) / (np.abs(out) + np.abs(ref) + 1.0))) < (1e-3 if typeAB == orc.F16 else 1e-5)
