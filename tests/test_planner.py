@@ -188,6 +188,25 @@ def test_contraction_packed_operands(ht):
     assert "packed" not in plan(64, [0, 1, 4, 5], [2, 3, 4, 5], [0, 1, 2, 3])
 
 
+def test_contraction_ragged_tiles_and_short_k(ht):
+    """Outside M >= 128, N >= 64, K >= one K block: small outputs under a long contraction take a ragged tensor-core
+    tile, short contractions under a large output too; the rest stays on the FMA kernel."""
+    def plan(M, N, K, t):
+        return ht.describe_contraction_plan([M, K], [K, 1], [0, 2], t, [N, K], [K, 1], [1, 2], t, [M, N], [N, 1], [0, 1],
+                                            ht.R_32F, False, ht.COMPUTE_32F)
+
+    assert "kind=tcgen05" in plan(64, 64, 65536, ht.R_16F) and "kind=tf32x3" in plan(64, 64, 65536, ht.R_32F)
+    assert "kind=tcgen05" in plan(16, 256, 1024, ht.R_16F)
+    assert "kind=tiled_simt" in plan(64, 64, 1016, ht.R_16F)  # K below 1024
+    assert "kind=tiled_simt" in plan(8, 64, 65536, ht.R_16F)  # M below 16
+    # the last row mode may be shorter than the tile whatever its extent: the box reaches past the tensor
+    d = plan(100, 30, 8192, ht.R_16F)
+    assert "kind=tcgen05" in d and "rows=128/64" in d
+    # K = 8 under 8192 x 8192 outputs; not under 1024 x 1024
+    assert "kind=tcgen05" in plan(8192, 8192, 8, ht.R_16F) and "kind=tf32x3" in plan(8192, 8192, 8, ht.R_32F)
+    assert "kind=tiled_simt" in plan(1024, 1024, 8, ht.R_16F)
+
+
 def test_contraction_k_split_plans(ht):
     """Few tiles and a long K: the fp32 tensor-core plan cuts K into up to four ranges (at least four K blocks
     each, never more CTAs than SMs), one CTA of a cluster each; the sums meet in shared memory, so no workspace is
