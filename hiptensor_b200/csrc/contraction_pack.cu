@@ -119,8 +119,11 @@ namespace htb
             return cudaErrorInvalidValue;
         // plan.typeA / typeB follow the plan's swap; both operands have the same type
         const int type = plan.typeA;
-        void*     A2   = workspace;
-        void*     B2   = static_cast<unsigned char*>(workspace) + plan.yOffset;
+        // the copies are written with 16-byte stores and read by TMA: they start at a multiple of 256 bytes whatever the
+        // caller's pointer (plan.expandBytes has 256 bytes of slack for that)
+        unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~uintptr_t(255));
+        void*          A2   = base;
+        void*          B2   = base + plan.yOffset;
         cudaError_t e;
         if(type == CUDA_R_32F)
         {
@@ -141,6 +144,9 @@ namespace htb
             return e;
         noteLaunch("contraction_pack", 2);
         unsigned char* rest = static_cast<unsigned char*>(workspace) + plan.expandBytes;
+        rest                = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(rest) + 255u) & ~uintptr_t(255));
+        if(plan.workspaceBytes && rest + plan.workspaceBytes > static_cast<unsigned char*>(workspace) + workspaceBytes)
+            return cudaErrorInvalidValue;
         return launchContraction(plan, alpha, A2, B2, beta, C, D, plan.workspaceBytes ? rest : nullptr, plan.workspaceBytes,
                                  smCount, deviceStatus, stream);
     }

@@ -589,7 +589,7 @@ namespace htb
         }
         const uint64_t bytesA = (uint64_t(rowsA) * uint64_t(Kp) * elem + 255u) & ~uint64_t(255);
         const uint64_t bytesB = (uint64_t(rowsB) * uint64_t(Kp) * elem + 255u) & ~uint64_t(255);
-        if(bytesA + bytesB > workspaceLimit)
+        if(bytesA + bytesB + 256 > workspaceLimit)
             return rc;
         const TensorView A2{nfa + 1, lA, sA, mA, A.type}, B2{nfb + 1, lB, sB, mB, B.type};
         ContractionPlan  packed;
@@ -623,7 +623,7 @@ namespace htb
             packed.yStride[nfb + i] = B.strides[conB[i]];
         }
         packed.yOffset     = bytesA;
-        packed.expandBytes = bytesA + bytesB;
+        packed.expandBytes = bytesA + bytesB + 256; // the copies start at the next multiple of 256 bytes in the workspace
         if(packed.expandBytes + packed.workspaceBytes > workspaceLimit)
             packed.workspaceBytes = 0;
         *out = packed;

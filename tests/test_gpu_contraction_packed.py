@@ -102,6 +102,13 @@ def test_without_a_workspace_the_fma_kernel_gives_the_same(env):
         outs.append((ht.last_kernel_name(), to_host(D_d, orc.F32)))
     assert outs[0][0] == "contraction_tiled_simt" and outs[1][0] in TENSOR_CORE
     assert 0 <= rel_error(outs[1][1], outs[0][1], orc.F32) < 1e-3
+    # a workspace pointer that is aligned to 2 bytes only: the copies move to the next multiple of 256 bytes
+    plan = h.contraction_plan(cd, find, need)
+    D_d = to_device(nan_like(e ** 4, orc.F32), orc.F32)
+    ws = torch.empty(need + 2, dtype=torch.uint8, device="cuda")
+    h.contraction(plan, 1.0, A_d, B_d, 0.0, None, D_d, ws[2:], need)
+    assert ht.last_kernel_name() in TENSOR_CORE
+    assert np.array_equal(to_host(D_d, orc.F32).view(np.uint32), outs[1][1].view(np.uint32))
     # a plan made for the copies refuses a smaller workspace at execution
     plan = h.contraction_plan(cd, find, need)
     D_d = to_device(nan_like(e ** 4, orc.F32), orc.F32)
