@@ -614,11 +614,14 @@ int htb::reductionNoAlloc(const hiptensorHandle_t* handle, const void* alpha, co
         return rc;
     const int internalCompute = (typeCompute == HIPTENSOR_COMPUTE_64F) ? HIPTENSOR_COMPUTE_64F : HIPTENSOR_COMPUTE_32F;
     uint64_t need = reductionWorkspaceBytes(plan, internalCompute);
-    if(need > kStaticScratchBytes && plan.splitOptional)
+    if(need > kStaticScratchBytes && (plan.splitOptional || plan.kind == RED_COL || plan.shortLanes > 0))
     {
-        // the slices would only fill the GPU better: one pass without scratch
-        plan.split = 1;
-        need       = 0;
+        // these plans are sliced by thread or block count, with many more slices than the built-in scratch holds: as
+        // many slices as fit, or one pass
+        const uint64_t acc = (internalCompute == HIPTENSOR_COMPUTE_64F) ? 8 : 4;
+        const uint64_t fit = kStaticScratchBytes / (uint64_t(plan.nOut) * acc);
+        plan.split         = fit >= 2 ? int(std::min<uint64_t>(fit, uint64_t(plan.split))) : 1;
+        need               = reductionWorkspaceBytes(plan, internalCompute);
     }
     if(need > kStaticScratchBytes)
     {

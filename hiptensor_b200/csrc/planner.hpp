@@ -64,7 +64,7 @@ namespace htb
     {
         int     nk, nr; // folded kept / reduced modes, each sorted by ascending strideA
         int     kind;
-        int     vec; // elements per vector load along the contiguous axis (1, 2 or 4)
+        int     vec; // elements per vector load along the contiguous axis (a power of two, 16 bytes at most)
         int64_t kext[kMaxGroup], ksA[kMaxGroup], ksD[kMaxGroup];
         int64_t rext[kMaxGroup], rsA[kMaxGroup];
         int64_t nOut, nRed;

@@ -100,9 +100,10 @@ int htReductionGetWorkspaceSize(const htHandle* handle, const void* A, const htT
  * range) is a fixed 8 KiB array inside the library, present on every device that loads the library until
  * the process ends; the call makes no cudaMalloc / cudaFree and uses no caller workspace. Inputs and
  * outputs are still the caller's. Limits and rules:
- *  - a reduction whose two-pass scratch would exceed 8 KiB returns 19 (INSUFFICIENT_WORKSPACE) and does
- *    nothing; use htReduction with a workspace for it (on B200 this only concerns fp64 reductions with
- *    several hundred outputs);
+ *  - a reduction of long contiguous rows whose two-pass scratch would exceed 8 KiB returns 19
+ *    (INSUFFICIENT_WORKSPACE) and does nothing; use htReduction with a workspace for it (on B200 this only
+ *    concerns fp64 reductions with several hundred outputs). Reductions of short rows or with a contiguous kept
+ *    mode use as many slices as the 8 KiB hold, or a single pass;
  *  - the first call on a device looks up the array's device address; make that first call outside any
  *    stream capture;
  *  - all calls on one device share the array, and it keeps the last call's contents. Nothing in it needs

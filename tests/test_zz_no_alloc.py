@@ -90,6 +90,28 @@ def test_rejects_what_does_not_fit_the_built_in_scratch():
     assert e.value.status == ht.STATUS_INSUFFICIENT_WORKSPACE
 
 
+def test_plans_sliced_by_thread_count_fit_the_built_in_scratch():
+    """Short rows and contiguous kept modes are sliced by thread or block count, far beyond 8 KiB of partial results with
+    a caller workspace: without one the call uses the slices that fit (or one pass) and agrees with htReduction."""
+    import hiptensor_b200 as ht
+    from oracle import binding as orc
+
+    h = ht.Handle()
+    # 130 outputs along the contiguous kept mode under 20000 reduced rows; 24 outputs of rows of 4 under 3000 outer rows
+    for lens, kept in (([20000, 130], [1]), ([3000, 24, 4], [1])):
+        from helpers import rel_error
+
+        got, ref, k1, k2, exp = _pair(ht, h, lens, kept, orc.OP_ADD, orc.F32, orc.COMPUTE_32F, 1.5, 0.5, 41,
+                                      want_oracle=True)
+        assert k1 == "red_finalize" and k2 == "red_finalize"
+        n_red = int(np.prod(lens)) // int(np.prod([lens[m] for m in kept]))
+        # the reference's bound for a sequential fp32 reduction against the oracle; the two entry points differ in
+        # the number of slices only (stated tolerance of the reduction tests between them)
+        assert 0 <= rel_error(got, exp, orc.F32) < n_red * float(np.finfo(np.float32).eps)
+        assert 0 <= rel_error(ref, exp, orc.F32) < n_red * float(np.finfo(np.float32).eps)
+        assert 0 <= rel_error(got, ref, orc.F32) < 1e-5
+
+
 def test_a_warm_call_allocates_no_device_memory():
     """After the first call on the device (which looks the scratch address up), a call must leave the device's
     free memory and the caching allocator of the test harness untouched."""
