@@ -198,7 +198,8 @@ class Handle:
         """htReductionNoAlloc: the same reduction for callers that may not allocate device memory (hosts
         that own the device heap, latency-critical loops, services with an allocation ban after start-up). Scratch is an 8 KiB array inside
         the library, shared by all calls on the device: do not overlap two such calls on one device; a
-        reduction that needs more raises STATUS_INSUFFICIENT_WORKSPACE. The first call per device does a
+        reduction of long contiguous rows that needs more raises STATUS_INSUFFICIENT_WORKSPACE (other plans use the
+        slices that fit, or one pass). The first call per device does a
         one-time address lookup and belongs outside stream capture."""
         a = _scalar_for_compute(alpha, type_compute)
         b = _scalar_for_compute(beta, type_compute)
