@@ -589,8 +589,10 @@ class ContractionC5F16(ContractionBase):
     @classmethod
     def config(cls, world):
         return {"workload": "c5f16: configuration 5's layout D[m0,m1,m2,n0,n1]=2.0*A[m0,k0,m1,k1,m2]*B[k1,n0,k0,n1]+0.5*C "
-                            "with f16 data and fp32 output (folded M=4096, N=K=2304): both operands MN-major in chunks of "
-                            "16 (m2) and 48 (n1) valid rows out of 64, two K modes",
+                            "with f16 data and fp32 output (folded M=4096, N=K=2304): in place both operands are MN-major in "
+                            "chunks of 16 (m2) and 48 (n1) valid rows out of 64 with two K modes, so each step first "
+                            "copies them into the workspace as packed K-major matrices (two copy kernels, timed with "
+                            "the contraction)",
                 "cache": "operand sets rotate so that 3 x L2 is touched between reuses",
                 "parallelism": "1 GPU" if world == 1 else "%d replicas (not a sharded configuration)" % world}
 

@@ -511,7 +511,24 @@ namespace htb
                         int computeType, int smCount, ContractionPlan* out, uint64_t workspaceLimit)
     {
         const int rc = planReal(A, B, D, typeC, bilinear, computeType, smCount, kMaxRank, out);
-        if(rc != PLAN_OK || out->kind != CK_TILED_SIMT || workspaceLimit == 0)
+        if(rc != PLAN_OK || workspaceLimit == 0)
+            return rc;
+        // Operands that the f16 tensor-core kernel reads in place but in mostly empty pieces are packed too: an MN-major
+        // operand is cut into 64-element chunks of its stride-1 mode, K into blocks of 64 along the block mode, and a mode
+        // of 16 or 48 elements fills a quarter or three quarters of each (configuration 5's layout with f16 data: 0.14
+        // of the MMA work is useful).
+        double fill = 1.0;
+        if(out->kind == CK_TCGEN05)
+        {
+            auto chunkFill = [](int64_t e) { return double(e) / double((e + 63) / 64 * 64); };
+            if(out->aMajor == 1)
+                fill *= chunkFill(out->m[0].ext);
+            if(out->bMajor == 1)
+                fill *= chunkFill(out->n[out->nFast].ext);
+            fill *= chunkFill(out->k[0].ext);
+        }
+        const bool sparse = out->kind == CK_TCGEN05 && fill < 0.5;
+        if(out->kind != CK_TILED_SIMT && !sparse)
             return rc;
         // The gathered FMA kernel reads anything but runs at a fiftieth of the tensor cores' rate. From about a GFLOP
         // on, two passes that copy the operands into packed matrices (contracted modes merged and innermost, rows
@@ -522,7 +539,7 @@ namespace htb
         const bool large = out->M >= 128 && out->N >= 128 && out->K >= 64
                            && 2.0 * double(out->M) * double(out->N) * double(out->K) >= 1e9;
         const bool longK = out->K >= 1024 && out->M >= 16 && out->N >= 16;
-        if(!tensorType || !(large || longK))
+        if(!tensorType || !(large || (longK && !sparse)))
             return rc;
         const int elem = A.type == CUDA_R_32F ? 4 : 2, per16 = 16 / elem;
         int       freeA[kMaxRank], freeB[kMaxRank], conA[kMaxRank], conB[kMaxRank], nfa = 0, nfb = 0, nc = 0;
