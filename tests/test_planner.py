@@ -186,6 +186,20 @@ def test_contraction_packed_operands(ht):
     assert "kind=tiled_dmma" in d and "packed" not in d
     # what the tensor-core kernels read in place is not copied
     assert "packed" not in plan(64, [0, 1, 4, 5], [2, 3, 4, 5], [0, 1, 2, 3])
+    # ... unless it is read in mostly empty chunks: configuration 5's layout with f16 data (chunks of 16 and 48 of 64,
+    # K blocks of 48 of 64: 0.14 of the MMA work useful); with m2 = n1 = k = 64 every chunk is full
+    m0, m1, m2, n0, n1, k0, k1 = range(7)
+
+    def c5(ext):
+        mA, mB, mD = [m0, k0, m1, k1, m2], [k1, n0, k0, n1], [m0, m1, m2, n0, n1]
+        lA, lB, lD = ([ext[m] for m in ms] for ms in (mA, mB, mD))
+        return ht.describe_contraction_plan(lA, packed(lA, False), mA, ht.R_16F, lB, packed(lB, False), mB, ht.R_16F, lD,
+                                            packed(lD, False), mD, ht.R_32F, True, ht.COMPUTE_32F)
+
+    d = c5({m0: 16, m1: 16, m2: 16, n0: 48, n1: 48, k0: 48, k1: 48})
+    assert "kind=tcgen05" in d and "packed K=2304 Kp=2304" in d and "major=k/k" in d
+    d = c5({m0: 8, m1: 8, m2: 64, n0: 32, n1: 64, k0: 32, k1: 64})
+    assert "kind=tcgen05" in d and "packed" not in d and "major=mn/mn" in d
 
 
 def test_contraction_ragged_tiles_and_short_k(ht):
