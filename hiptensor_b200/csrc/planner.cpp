@@ -527,7 +527,9 @@ namespace htb
                 fill *= chunkFill(out->n[out->nFast].ext);
             fill *= chunkFill(out->k[0].ext);
         }
-        const bool sparse = out->kind == CK_TCGEN05 && fill < 0.5;
+        // (The copies cost about 3200 / min(M, N) times the packed contraction's own time: they pay from a quarter of
+        // useful work down, on outputs of a thousand rows and columns or more.)
+        const bool sparse = out->kind == CK_TCGEN05 && fill < 0.25 && out->M >= 1024 && out->N >= 1024;
         if(out->kind != CK_TILED_SIMT && !sparse)
             return rc;
         // The gathered FMA kernel reads anything but runs at a fiftieth of the tensor cores' rate. From about a GFLOP
